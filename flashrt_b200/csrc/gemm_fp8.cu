@@ -1,0 +1,499 @@
+// FP8 E4M3 x E4M3 -> bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline,
+// tcgen05.mma (kind::f8f6f4) issued by one thread, fp32 accumulator in TMEM,
+// tcgen05.ld epilogue with the per-tensor scales (device pointers), optional
+// bias, bf16 store.
+//
+// Replaces, for sm_100a, the reference entry points
+//   GemmRunner::fp8_nn_dev / fp8_nt_dev     csrc/gemm/gemm_runner.cu:67-76 (cuBLASLt)
+//   fp8_gemm_descale_bf16out               csrc/kernels/decoder_fused.cu:310-468
+//   cutlass_fp8_{sq,t1,wide,plain}_bf16out csrc/gemm/cutlass_sm100.cu:75-125
+//
+// Math: D(M,N) = alpha * A(M,K) . W(N,K)^T (+ bias), alpha = sa * sb * alpha_host,
+// products exact, fp32 accumulation, bf16 RN-even result.
+//
+// Both operands are K-major ("NT": activations (M,K) row-major, weights (N,K)
+// row-major).  One CTA computes one 128 x BN accumulator tile; the 128 TMEM lanes
+// are fed by the "lane operand", the BN columns by the "column operand":
+//   * SWAP = true  (small M): lanes = 128 weight rows, columns = the (<= 256)
+//     activation rows.  Every weight byte is streamed exactly once and the MMA
+//     M-dimension is fully used even for M = 16 or 50.
+//   * SWAP = false (large M): lanes = 128 activation rows, columns = BN weight rows.
+// Split-K: the CTAs of one thread-block cluster (1 x 1 x S, S <= 8) each
+// accumulate a slice of K, exchange fp32 partials through distributed shared
+// memory and each reduces 1/S of the tile's columns in fixed order (split 0, 1, ...).
+// There is no global-memory workspace and the result is deterministic.
+//
+// Each TMA copy lands in the issuing CTA's own shared memory.
+#include "common.cuh"
+#include "tc05.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace frt {
+
+// ------------------------------------------------------------------ status word
+__device__ int g_gemm_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
+
+// ------------------------------------------------------------------ tensor maps (host)
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled g_encode = nullptr;
+static std::mutex g_mu;
+
+static int ensure_encode() {
+    if (g_encode) return FRT_OK;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_encode) return FRT_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return FRT_ERR_UNSUPPORTED;
+    g_encode = (PFN_encodeTiled)fn;
+    return FRT_OK;
+}
+
+// 2D byte matrix (rows x row_bytes, row pitch = pitch_bytes), box = 128 bytes x box_rows, 128-byte swizzle.
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t pitch_bytes,
+                    uint32_t box_rows) {
+    int rc = ensure_encode();
+    if (rc) return rc;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15) || box_rows == 0 || box_rows > 256)
+        return FRT_ERR_INVALID;
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FRT_OK : FRT_ERR_INVALID;
+}
+
+// ------------------------------------------------------------------ kernel
+struct GemmParams {
+    __nv_bfloat16* out;        // (M, N) row-major
+    const float* sa;           // device scalars (may be null = 1)
+    const float* sb;
+    float alpha_host;
+    const __nv_bfloat16* bias; // (N,) or null
+    int M, N;
+    int kb_total;              // ceil(K / 128)
+    int lane_rows;             // extent of the lane operand (N if SWAP else M)
+    int col_rows;              // extent of the column operand (M if SWAP else N)
+    int w_is_lane;             // which operand holds the weights (prefetched before the PDL wait)
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int BK = 128;                       // bytes == fp8 elements per k-block
+    static constexpr int L_BYTES = 128 * BK;             // 16 KB
+    static constexpr int C_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = L_BYTES + C_BYTES;
+    static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
+    static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+    static constexpr int RED_BYTES = 128 * BN * 4;
+    static_assert(RED_BYTES <= STAGES * STAGE_BYTES, "split-K staging must fit in the pipeline buffers");
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // power of two >= 32
+};
+
+enum { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(128, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum_bar = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* issued = abort_flag + 1;
+    volatile int* consumed = abort_flag + 2;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int lane0 = blockIdx.x * 128;              // first row of the lane operand
+    const int col0 = blockIdx.y * BN;                // first row of the column operand
+    const uint32_t S = tc::cluster_nctarank();
+    const uint32_t rank = tc::cluster_ctarank();
+    const int kb_begin = (int)((long long)p.kb_total * rank / S);
+    const int kb_end = (int)((long long)p.kb_total * (rank + 1) / S);
+    const int nkb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        tc::mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        *issued = 0;
+        *consumed = 0;
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&tmL);
+        tc::tma_prefetch_desc(&tmC);
+    }
+    if (warp == 2) {
+        tc::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_d = *tmem_slot;
+
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer
+        const CUtensorMap* tmW = p.w_is_lane ? &tmL : &tmC;
+        const CUtensorMap* tmX = p.w_is_lane ? &tmC : &tmL;
+        const int w_off = p.w_is_lane ? 0 : Cfg::L_BYTES;
+        const int x_off = p.w_is_lane ? Cfg::L_BYTES : 0;
+        const int w_row = p.w_is_lane ? lane0 : col0;
+        const int x_row = p.w_is_lane ? col0 : lane0;
+        const int pre = nkb < STAGES ? nkb : STAGES;
+        // weights do not depend on the producer grid: start streaming them now
+        for (int i = 0; i < pre; ++i) {
+            tc::mbar_arrive_expect_tx(&full[i], Cfg::STAGE_BYTES);
+            tc::tma_load_2d(stage_base + i * Cfg::STAGE_BYTES + w_off, tmW, &full[i], (kb_begin + i) * 128, w_row);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tc::tma_load_2d(stage_base + i * Cfg::STAGE_BYTES + x_off, tmX, &full[i], (kb_begin + i) * 128, x_row);
+        *issued = pre;
+        for (int i = pre; i < nkb; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = ((i / STAGES) - 1) & 1;
+            bool ok = false;
+            for (uint32_t it = 0; it < FRT_WAIT_POLLS && !*abort_flag; ++it) {
+                if (tc::mbar_try_wait(&empty[s], ph)) { ok = true; break; }
+                if (it > 64) __nanosleep(64);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(&g_gemm_status, 0, ERR_PRODUCER | (blockIdx.x << 8));
+                break;
+            }
+            tc::mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+            tc::tma_load_2d(stage_base + s * Cfg::STAGE_BYTES + w_off, tmW, &full[s], (kb_begin + i) * 128, w_row);
+            tc::tma_load_2d(stage_base + s * Cfg::STAGE_BYTES + x_off, tmX, &full[s], (kb_begin + i) * 128, x_row);
+            *issued = i + 1;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        constexpr uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN);
+        bool failed = false;
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (i / STAGES) & 1;
+            bool ok = false;
+            for (uint32_t it = 0; it < FRT_WAIT_POLLS && !*abort_flag; ++it) {
+                if (tc::mbar_try_wait(&full[s], ph)) { ok = true; break; }
+                if (it > 64) __nanosleep(32);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(&g_gemm_status, 0, ERR_MMA | (blockIdx.x << 8));
+                failed = true;
+                break;
+            }
+            tc::tc_fence_after_sync();
+            const uint32_t sL = tc::smem_u32(stage_base + s * Cfg::STAGE_BYTES);
+            const uint32_t sC = sL + Cfg::L_BYTES;
+            const uint64_t dL = tc::make_desc_kmajor_sw128(sL);
+            const uint64_t dC = tc::make_desc_kmajor_sw128(sC);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)   // 4 x (K = 32) per 128-byte k-block; +32 bytes = +2 in the address field
+                tc::mma_f8(tmem_d, dL + 2 * k, dC + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            tc::mma_commit(&empty[s]);
+            *consumed = i + 1;
+        }
+        if (!failed) tc::mma_commit(accum_bar);
+    }
+    __syncwarp();
+
+    // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w .. 32w+31
+    pdl_wait();
+    bool have_acc = false;
+    for (uint32_t it = 0; it < FRT_WAIT_POLLS && !*abort_flag; ++it) {
+        if (tc::mbar_try_wait(accum_bar, 0)) { have_acc = true; break; }
+        if (it > 32) __nanosleep(64);
+    }
+    if (!have_acc && !*abort_flag) {
+        *abort_flag = 1;
+        atomicCAS(&g_gemm_status, 0, ERR_EPILOGUE | (blockIdx.x << 8));
+    }
+    tc::tc_fence_after_sync();
+
+    float alpha = p.alpha_host;
+    if (p.sa) alpha *= *p.sa;
+    if (p.sb) alpha *= *p.sb;
+    const int lrow = lane0 + warp * 32 + lane;                 // global row of the lane operand
+    const uint32_t trow = tmem_d + ((uint32_t)(warp * 32) << 16);
+
+    if (S == 1) {
+        if (have_acc) {
+            if (SWAP) {
+                // lanes = output columns n, TMEM columns = output rows m
+                const int n = lrow;
+                const float b = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    if (BN >= 32) tc::tmem_ld32(trow + c, v); else tc::tmem_ld16(trow + c, v);
+                    tc::tmem_ld_wait();
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < (BN >= 32 ? 32 : 16); ++j) {
+                            const int m = col0 + c + j;
+                            if (m < p.M)
+                                p.out[(size_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]) * alpha + b);
+                        }
+                    }
+                }
+            } else {
+                const int m = lrow;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    if (BN >= 32) tc::tmem_ld32(trow + c, v); else tc::tmem_ld16(trow + c, v);
+                    tc::tmem_ld_wait();
+                    if (m < p.M) {
+                        const int nb = col0 + c;
+                        __nv_bfloat16* orow = p.out + (size_t)m * p.N + nb;
+#pragma unroll
+                        for (int j = 0; j < (BN >= 32 ? 32 : 16); j += 8) {
+                            if (nb + j + 8 <= p.N && ((reinterpret_cast<uintptr_t>(orow + j) & 15) == 0)) {
+                                float f[8];
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) {
+                                    f[q] = __uint_as_float(v[j + q]) * alpha;
+                                    if (p.bias) f[q] += __bfloat162float(p.bias[nb + j + q]);
+                                }
+                                uint4 o;
+                                o.x = pack_bf16x2(f[0], f[1]);
+                                o.y = pack_bf16x2(f[2], f[3]);
+                                o.z = pack_bf16x2(f[4], f[5]);
+                                o.w = pack_bf16x2(f[6], f[7]);
+                                st_global_v4(orow + j, o);
+                            } else {
+                                for (int q = 0; q < 8; ++q)
+                                    if (nb + j + q < p.N) {
+                                        float f = __uint_as_float(v[j + q]) * alpha;
+                                        if (p.bias) f += __bfloat162float(p.bias[nb + j + q]);
+                                        orow[j + q] = __float2bfloat16_rn(f);
+                                    }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- split-K: stage partials as red[col][lane] (fp32), reduce across the cluster
+        float* red = reinterpret_cast<float*>(stage_base);
+        if (have_acc) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                if (BN >= 32) tc::tmem_ld32(trow + c, v); else tc::tmem_ld16(trow + c, v);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < (BN >= 32 ? 32 : 16); ++j)
+                    red[(c + j) * 128 + warp * 32 + lane] = __uint_as_float(v[j]);
+            }
+        }
+        tc::cluster_sync_all();
+        if (!*abort_flag) {
+            const int cols_per = (BN + (int)S - 1) / (int)S;
+            const int cbeg = (int)rank * cols_per;
+            const int cend = cbeg + cols_per < BN ? cbeg + cols_per : BN;
+            const int col_limit = SWAP ? p.M : p.N;
+            const int lane_limit = SWAP ? p.N : p.M;
+            for (int c = cbeg; c < cend; ++c) {
+                const int gcol = col0 + c;
+                if (gcol >= col_limit) break;
+                const uint32_t a = tc::smem_u32(&red[c * 128 + warp * 32 + lane]);
+                float acc = 0.0f;
+                for (uint32_t s = 0; s < S; ++s) acc += tc::dsmem_ld_f32(tc::dsmem_map(a, s));
+                if (lrow < lane_limit) {
+                    const int m = SWAP ? gcol : lrow;
+                    const int n = SWAP ? lrow : gcol;
+                    float f = acc * alpha;
+                    if (p.bias) f += __bfloat162float(p.bias[n]);
+                    p.out[(size_t)m * p.N + n] = __float2bfloat16_rn(f);
+                }
+            }
+        }
+        tc::cluster_sync_all();
+    }
+
+    // ---------------- teardown
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // give copies that were issued but never consumed a bounded chance to land
+        for (int i = *consumed; i < *issued; ++i) {
+            const int s = i % STAGES;
+            for (int it = 0; it < 4096; ++it) {
+                if (tc::mbar_try_wait(&full[s], (i / STAGES) & 1)) break;
+                __nanosleep(256);
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 2) tc::tmem_dealloc(tmem_d, Cfg::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host launch
+struct TmapKey {
+    const void* base; uint64_t rows, row_bytes, pitch; uint32_t box_rows;
+    bool operator==(const TmapKey& o) const {
+        return base == o.base && rows == o.rows && row_bytes == o.row_bytes && pitch == o.pitch && box_rows == o.box_rows;
+    }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        h ^= k.rows * 0x9e3779b97f4a7c15ull + (h << 6);
+        h ^= k.row_bytes * 0xc2b2ae3d27d4eb4full + (h >> 3);
+        h ^= (k.pitch << 8) ^ k.box_rows;
+        return h;
+    }
+};
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
+
+int get_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t pitch,
+                   uint32_t box_rows) {
+    TmapKey k{base, rows, row_bytes, pitch, box_rows};
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_tmaps.find(k);
+        if (it != g_tmaps.end()) { *out = it->second; return FRT_OK; }
+    }
+    int rc = make_tmap_2d_u8(out, base, rows, row_bytes, pitch, box_rows);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_tmaps.size() > 65536) g_tmaps.clear();
+    g_tmaps[k] = *out;
+    return FRT_OK;
+}
+
+template <int BN, bool SWAP>
+static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int splits, bool pdl, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        attr_done = true;
+    }
+    const void* lane_ptr = SWAP ? W : A;
+    const void* col_ptr = SWAP ? A : W;
+    p.lane_rows = SWAP ? p.N : p.M;
+    p.col_rows = SWAP ? p.M : p.N;
+    p.w_is_lane = SWAP ? 1 : 0;
+    CUtensorMap tmL, tmC;
+    int rc = get_tmap_2d_u8(&tmL, lane_ptr, (uint64_t)p.lane_rows, (uint64_t)K, (uint64_t)K, 128);
+    if (rc) return rc;
+    rc = get_tmap_2d_u8(&tmC, col_ptr, (uint64_t)p.col_rows, (uint64_t)K, (uint64_t)K, BN);
+    if (rc) return rc;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.lane_rows + 127) / 128, (p.col_rows + BN - 1) / BN, splits);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = splits;
+    ++na;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, SWAP>, tmL, tmC, p);
+    return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
+}
+
+static int pick_splits(int tiles, int kb_total, int requested) {
+    if (requested > 0) {
+        int s = requested > 8 ? 8 : requested;
+        return s > kb_total ? kb_total : s;
+    }
+    // fill the machine: aim for >= ~128 CTAs, keep at least 2 k-blocks per split
+    int s = 1;
+    while (s < 8 && tiles * s * 2 <= 148 && kb_total / (s * 2) >= 2) s *= 2;
+    return s;
+}
+
+}  // namespace frt
+
+using namespace frt;
+
+extern "C" {
+
+// D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . W(N,K)^T + bias
+// A, W: FP8 E4M3 row-major, K contiguous.  K % 16 == 0; A, W 16-byte aligned.
+// splits: 0 = choose, otherwise the split-K factor (clamped to [1, 8]).
+// flags: bit0 = programmatic dependent launch.
+int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
+                         const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
+                         void* stream) {
+    if (!A || !W || !D || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if (K % 16) return FRT_ERR_UNSUPPORTED;
+    if (M == 0) return FRT_OK;
+    GemmParams p = {};
+    p.out = (__nv_bfloat16*)D;
+    p.sa = d_scale_a;
+    p.sb = d_scale_b;
+    p.alpha_host = alpha_host;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.M = M;
+    p.N = N;
+    p.kb_total = (K + 127) / 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    bool pdl = flags & 1;
+    if (M <= 256) {
+        int tiles = (N + 127) / 128;
+        int sp = pick_splits(tiles, p.kb_total, splits);
+        if (M <= 16) return launch_gemm<16, true>(A, W, p, K, sp, pdl, s);
+        if (M <= 32) return launch_gemm<32, true>(A, W, p, K, sp, pdl, s);
+        if (M <= 64) return launch_gemm<64, true>(A, W, p, K, sp, pdl, s);
+        if (M <= 128) return launch_gemm<128, true>(A, W, p, K, sp, pdl, s);
+        return launch_gemm<256, true>(A, W, p, K, sp, pdl, s);
+    }
+    int sp = splits > 0 ? pick_splits(1, p.kb_total, splits) : 1;
+    if (N >= 256) return launch_gemm<256, false>(A, W, p, K, sp, pdl, s);
+    if (N > 64) return launch_gemm<128, false>(A, W, p, K, sp, pdl, s);
+    return launch_gemm<64, false>(A, W, p, K, sp, pdl, s);
+}
+
+// returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)
+int frt_b200_gemm_status(int reset) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int));
+    if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+    if (reset && v) {
+        int z = 0;
+        cudaMemcpyToSymbol(g_gemm_status, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,193 @@
+"""Drop-in stand-in for the reference's ``flash_rt.flash_rt_kernels`` pybind module
+(``csrc/bindings.cpp``) for the denoise hot path, backed by the sm_100a C-ABI library.
+
+Same names, same positional / keyword arguments, same calling convention: every
+pointer is a Python ``int`` holding a device address, ``stream`` is an ``int``
+(0 = default stream), scales are device ``float*`` passed as ``int`` (``d_scale``).
+Functions the reference declares ``void`` raise :class:`flashrt_b200._lib.KernelError`
+on a non-zero status instead of failing silently.  Entry points of the reference that
+lie outside the denoise path raise :class:`NotBuilt` (the analogue of the reference's
+"extension not built" refusal, ``flash_rt/_extensions.py:67-108``).
+
+Optional keyword ``pdl=True`` (not in the reference) launches with programmatic
+dependent launch; the B200 pipeline uses it, reference call sites never pass it.
+"""
+from __future__ import annotations
+
+from . import _lib
+from ._lib import KernelError, call  # noqa: F401  (re-exported)
+
+
+class NotBuilt(RuntimeError):
+    """Raised for reference entry points that this library does not provide."""
+
+
+class _NotBuiltAttr(NotBuilt, AttributeError):
+    """Module-attribute form, so that ``hasattr(fvk, name)`` answers False instead of raising."""
+
+
+def _f(pdl: bool) -> int:
+    return 1 if pdl else 0
+
+
+# ------------------------------------------------------------------ norms (csrc/bindings.cpp:854-947,1144-1162)
+def rms_norm(x, weight, out, seq_len, dim, eps=1e-6, stream=0, *, pdl=False):
+    call("frt_b200_norm_bf16", x, None, None, 0, weight, None, 0, out, None, seq_len, dim, eps, _f(pdl), stream)
+
+
+def rms_norm_fp8(x, weight, out, seq_len, dim, eps=1e-6, d_scale=0, stream=0, *, pdl=False):
+    call("frt_b200_norm_fp8", x, None, None, 0, weight, None, 0, out, None, seq_len, dim, eps, d_scale, _f(pdl),
+         stream)
+
+
+def ada_rms_norm_style(x, weight, style, out, gate_out, seq_len, dim, eps=1e-6, stream=0, *, pdl=False,
+                       style_stride=None):
+    ss = 3 * dim if style_stride is None else style_stride
+    call("frt_b200_norm_bf16", x, None, None, 0, weight, style, ss, out, gate_out or None, seq_len, dim, eps,
+         _f(pdl), stream)
+
+
+def ada_rms_norm_style_fp8(x, weight, style, out, gate_out, seq_len, dim, eps=1e-6, d_scale=0, stream=0, *,
+                           pdl=False, style_stride=None):
+    ss = 3 * dim if style_stride is None else style_stride
+    call("frt_b200_norm_fp8", x, None, None, 0, weight, style, ss, out, gate_out or None, seq_len, dim, eps,
+         d_scale, _f(pdl), stream)
+
+
+def residual_add_rms_norm_fp8(residual, x, weight, out, seq_len, dim, eps=1e-6, d_scale=0, stream=0, *,
+                              pdl=False):
+    call("frt_b200_norm_fp8", residual, x, None, 0, weight, None, 0, out, None, seq_len, dim, eps, d_scale,
+         _f(pdl), stream)
+
+
+def residual_add_rms_norm(residual, x, weight, out, seq_len, dim, eps=1e-6, stream=0, *, pdl=False):
+    call("frt_b200_norm_bf16", residual, x, None, 0, weight, None, 0, out, None, seq_len, dim, eps, _f(pdl),
+         stream)
+
+
+def gate_residual_ada_norm_fp8(residual, x, gate, weight, style, out, gate_out, seq_len, dim, eps=1e-6,
+                               d_scale=0, stream=0, *, pdl=False, style_stride=None, gate_stride=None):
+    ss = 3 * dim if style_stride is None else style_stride
+    gs = dim if gate_stride is None else gate_stride
+    call("frt_b200_norm_fp8", residual, x, gate, gs, weight, style, ss, out, gate_out or None, seq_len, dim, eps,
+         d_scale, _f(pdl), stream)
+
+
+# ------------------------------------------------------------------ activation (csrc/bindings.cpp:1031-1044)
+def gate_geglu_merged(merged, out, seq, half_dim, stream=0, *, pdl=False):
+    call("frt_b200_geglu_bf16", merged, out, seq, half_dim, _f(pdl), stream)
+
+
+def gate_geglu_merged_fp8(merged, out, seq, half_dim, d_scale=0, stream=0, *, pdl=False):
+    call("frt_b200_geglu_fp8", merged, out, seq, half_dim, d_scale, _f(pdl), stream)
+
+
+# ------------------------------------------------------------------ RoPE (csrc/bindings.cpp:1071-1099)
+def qkv_split_rope(qkv, rope_weights, Q, K, V, seq, q_dim, k_dim, v_dim, head_dim, stream=0, *, pdl=False):
+    call("frt_b200_qkv_split_rope", qkv, rope_weights, Q, K, V, None, seq, q_dim, k_dim, v_dim, head_dim, _f(pdl),
+         stream)
+
+
+def qkv_split_rope_devpos(qkv, rope_weights, Q, K, V, devpos, seq, q_dim, k_dim, v_dim, head_dim, stream=0, *,
+                          pdl=False):
+    call("frt_b200_qkv_split_rope", qkv, rope_weights, Q, K, V, devpos, seq, q_dim, k_dim, v_dim, head_dim,
+         _f(pdl), stream)
+
+
+# ------------------------------------------------------------------ elementwise (csrc/bindings.cpp:1103-1119)
+def gate_mul_residual(residual, x, gate, n, stream=0, *, pdl=False):
+    # flat form of the reference: gate has the same n elements as residual
+    call("frt_b200_gate_mul_residual", residual, x, gate, n, 1, n, _f(pdl), stream)
+
+
+def bias_residual(residual, x, bias, seq_len, dim, stream=0, *, pdl=False):
+    call("frt_b200_bias_residual", residual, x, bias, seq_len, dim, _f(pdl), stream)
+
+
+def residual_add(residual, x, n, stream=0, *, pdl=False):
+    call("frt_b200_residual_add", residual, x, n, _f(pdl), stream)
+
+
+def gpu_copy(dst, src, nbytes, stream=0):
+    call("frt_b200_copy", dst, src, nbytes, stream)
+
+
+# ------------------------------------------------------------------ quantise (csrc/bindings.cpp:1191-1211)
+def quantize_fp8_static(input, output, d_scale, n, stream=0, *, pdl=False):  # noqa: A002 (reference kwarg name)
+    call("frt_b200_quantize_fp8_static", input, output, d_scale, n, _f(pdl), stream)
+
+
+def quantize_fp8_device(input, output, d_scale, n, stream=0):  # noqa: A002
+    call("frt_b200_quantize_fp8_device", input, output, d_scale, n, stream)
+
+
+def fp8_accumulate_scale_max(src_scale, dst_scale, stream=0):
+    call("frt_b200_fp8_accumulate_scale_max", src_scale, dst_scale, stream)
+
+
+# ------------------------------------------------------------------ GEMM (csrc/bindings.cpp:605-803,2062-2069)
+def fp8_gemm_descale_bf16out(A, B, C, M, N, K, act_descale, w_descale, stream=0, *, pdl=False, splits=0):
+    """C(M,N) bf16 = act_descale * w_descale * A(M,K) . B(N,K)^T  (B = weights, K contiguous)."""
+    call("frt_b200_gemm_fp8_nt", A, B, C, M, N, K, act_descale, w_descale, 1.0, None, splits, _f(pdl), stream)
+
+
+class GemmRunner:
+    """Stand-in for the reference's cuBLASLt ``GemmRunner`` (``csrc/gemm/gemm_runner.h``).
+
+    Only the methods the denoise path calls exist.  There is nothing to autotune (the
+    kernel is chosen from the shape), so the ``autotune_*`` methods accept the
+    reference's arguments and return immediately.
+    """
+
+    def fp8_nt_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None):
+        """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form."""
+        call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits, _f(pdl), stream)
+
+    def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, **kw):
+        raise NotBuilt(
+            "fp8_nn_dev (weights stored (K,N)) is not provided: this library keeps FP8 weights K-contiguous "
+            "(N,K); use fp8_nt_dev, the reference's own fp8_layout='nk' path (csrc/bindings.cpp:717-727)")
+
+    def bf16_nn(self, A, B, D, M, N, K, stream=0, *, pdl=False, bias=None, accumulate=False):
+        if not (N <= 64 or K <= 64):
+            raise NotBuilt("bf16_nn is provided for the 32<->1024 action projections only (N <= 64 or K <= 64)")
+        call("frt_b200_gemm_bf16_nn_small", A, B, D, bias, M, N, K, 1 if accumulate else 0, _f(pdl), stream)
+
+    # the reference measures cuBLASLt algorithms here; nothing to do for a shape-selected kernel
+    def autotune_bf16_nn(self, *a, **k):
+        return 0
+
+    def autotune_fp8_nn_dev(self, *a, **k):
+        return 0
+
+    def autotune_fp8_nt_dev(self, *a, **k):
+        return 0
+
+
+# ------------------------------------------------------------------ capability probes (csrc/bindings.cpp:2424-2459)
+def has_cutlass_sm100() -> bool:
+    """The reference reports whether its CUTLASS Sm100 kernels were compiled in; here the tcgen05 path is
+    the only path."""
+    return True
+
+
+def has_nvfp4() -> bool:
+    return False
+
+
+def get_sm_version() -> int:
+    v = _lib.call_status("frt_b200_sm_version")
+    if v < 0:
+        raise KernelError(f"frt_b200_sm_version failed: status {v}")
+    return v
+
+
+def tensor_core_status(reset: bool = True) -> int:
+    """0 unless a bounded wait inside a tensor-core kernel gave up (see ``frt_b200_gemm_status``)."""
+    return _lib.call_status("frt_b200_gemm_status", 1 if reset else 0)
+
+
+def __getattr__(name: str):
+    if name.startswith("__"):
+        raise AttributeError(name)
+    raise _NotBuiltAttr(f"flash_rt_kernels.{name} is outside the denoise hot path and is not provided by flashrt_b200")

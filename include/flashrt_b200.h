@@ -1,0 +1,130 @@
+/*
+ * flashrt_b200 -- C ABI of the sm_100a (B200) denoise-path kernel library.
+ *
+ * Plain pointers and sizes only: every pointer is a device pointer unless a
+ * comment says "host"; `stream` is a cudaStream_t passed as void* (NULL = the
+ * default stream).  Nothing here allocates device memory unless its comment
+ * says so, nothing synchronises the device, every launch is capturable in a
+ * CUDA graph.  The caller owns all buffers.
+ *
+ * Return value: 0 on success, otherwise
+ *   -1  invalid argument (null pointer, negative size, misaligned pointer)
+ *   -2  unsupported shape / feature
+ *   -3  a bounded device-side wait gave up (see frt_b200_gemm_status)
+ *   -(1000 + cudaError_t) for a CUDA runtime failure at launch.
+ *
+ * `flags` bit 0: launch with programmatic dependent launch (the kernel starts
+ * its input-independent prologue before the previous kernel in the stream has
+ * finished; only set it when scales / weights / styles are not written by that
+ * previous kernel).
+ *
+ * Citations name the reference entry point each function stands in for, as
+ * path:line inside the FlashRT source tree.
+ */
+#ifndef FLASHRT_B200_H
+#define FLASHRT_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- fused norm + quantise
+ * One kernel family for
+ *   rms_norm_fp8                csrc/bindings.cpp:899-907  -> csrc/kernels/norm.cu:286-343
+ *   ada_rms_norm_style_fp8      csrc/bindings.cpp:909-921  -> csrc/kernels/norm.cu:392-442
+ *   residual_add_rms_norm_fp8   csrc/bindings.cpp:923-935  -> csrc/kernels/norm.cu:445-495
+ *   gate_residual_ada_norm_fp8  csrc/bindings.cpp:1144-1162 -> csrc/kernels/fusion.cu:15-81
+ *
+ *   if x:        residual <- bf16(residual + x * gate_in)      (gate_in NULL: residual + x)
+ *   rms        = 1 / sqrt(mean(r^2) + eps)                     (r unrounded when updated)
+ *   y          = bf16(residual) * rms * weight                 (weight NULL: ones)
+ *   if style:    y = y * (1 + scale) + shift ; gate_out <- gate   (style row = [scale|shift|gate])
+ *   out_fp8    = e4m3(clamp(y * (1 / *d_scale), +-448))
+ *
+ * residual (rows, dim) bf16 in/out; x (rows, dim) bf16 or NULL; gate_in bf16 rows at
+ * gate_in + r * gate_in_stride (stride in elements; 0 = one row shared by all);
+ * style rows of 3*dim at style + r * style_stride (0 = shared); gate_out (rows, dim) or NULL.
+ * dim % 8 == 0, dim <= 8192; pointers 16-byte aligned (out_fp8: 8).
+ */
+int frt_b200_norm_fp8(void* residual, const void* x, const void* gate_in, long long gate_in_stride,
+                      const void* weight, const void* style, long long style_stride, void* out_fp8,
+                      void* gate_out, int rows, int dim, float eps, const float* d_scale, int flags,
+                      void* stream);
+
+/* Same with a bf16 result instead of FP8:
+ *   rms_norm                    csrc/bindings.cpp:854-862
+ *   ada_rms_norm_style          csrc/bindings.cpp:887-897  -> csrc/kernels/norm.cu:345-389
+ *   residual_add_rms_norm       csrc/bindings.cpp:937-947  -> csrc/kernels/norm.cu:498-539 */
+int frt_b200_norm_bf16(void* residual, const void* x, const void* gate_in, long long gate_in_stride,
+                       const void* weight, const void* style, long long style_stride, void* out_bf16,
+                       void* gate_out, int rows, int dim, float eps, int flags, void* stream);
+
+/* ---------------------------------------------------------------- activation / quantise
+ * gate_geglu_merged_fp8        csrc/bindings.cpp:1037-1044 -> csrc/kernels/activation.cu:249-279
+ *   merged (rows, 2*half_dim) bf16 = [gate | up];  out (rows, half_dim) e4m3 =
+ *   e4m3(clamp(gelu_tanh(gate) * up * (1 / *d_scale), +-448)).  half_dim % 8 == 0. */
+int frt_b200_geglu_fp8(const void* merged, void* out_fp8, int rows, int half_dim, const float* d_scale,
+                       int flags, void* stream);
+/* gate_geglu_merged            csrc/bindings.cpp:1031-1035 (bf16 result) */
+int frt_b200_geglu_bf16(const void* merged, void* out_bf16, int rows, int half_dim, int flags, void* stream);
+
+/* quantize_fp8_static          csrc/bindings.cpp:1191-1196 -> csrc/kernels/quantize.cu:61-75,297-304 */
+int frt_b200_quantize_fp8_static(const void* in_bf16, void* out_fp8, const float* d_scale, long long n,
+                                 int flags, void* stream);
+/* quantize_fp8_device          csrc/bindings.cpp:1198-1204 -> csrc/kernels/quantize.cu:131-156
+ *   *d_scale <- max(absmax(in) / 448, 1e-12), then quantise with it (4 stream operations). */
+int frt_b200_quantize_fp8_device(const void* in_bf16, void* out_fp8, float* d_scale, long long n, void* stream);
+/* fp8_accumulate_scale_max     csrc/bindings.cpp:1205-1211 -> csrc/kernels/quantize.cu:137-146 */
+int frt_b200_fp8_accumulate_scale_max(const float* src_scale, float* dst_scale, void* stream);
+
+/* ---------------------------------------------------------------- residual-style adds (bf16, in place)
+ * residual_add                 csrc/bindings.cpp:1116-1119 -> csrc/kernels/elementwise.cu:302 */
+int frt_b200_residual_add(void* residual, const void* x, long long n, int flags, void* stream);
+/* bias_residual                csrc/bindings.cpp:1108-1114 -> csrc/kernels/elementwise.cu:207 */
+int frt_b200_bias_residual(void* residual, const void* x, const void* bias, int rows, int dim, int flags,
+                           void* stream);
+/* gate_mul_residual            csrc/bindings.cpp:1103-1106 -> csrc/kernels/elementwise.cu:34
+ *   residual += x * gate; gate rows at gate + r * gate_stride (0 = shared row) */
+int frt_b200_gate_mul_residual(void* residual, const void* x, const void* gate, long long gate_stride, int rows,
+                               int dim, int flags, void* stream);
+
+/* ---------------------------------------------------------------- RoPE + QKV split + KV-cache append
+ * qkv_split_rope               csrc/bindings.cpp:1071-1082 -> csrc/kernels/rope.cu:135-208
+ * qkv_split_rope_devpos        csrc/bindings.cpp:1086-1099 -> csrc/kernels/rope.cu:215-277
+ *   qkv (seq, q_dim+k_dim+v_dim) bf16; rope (seq, head_dim) bf16 = [cos0,sin0,cos1,sin1,...];
+ *   Q (seq, q_dim); K/V rows written at row (*devpos + t) (devpos NULL: row t). */
+int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K, void* V, const int* devpos,
+                            int seq, int q_dim, int k_dim, int v_dim, int head_dim, int flags, void* stream);
+
+/* ---------------------------------------------------------------- FP8 GEMM (tcgen05 / TMEM / TMA)
+ * GemmRunner::fp8_nt_dev       csrc/bindings.cpp:717-727   -> csrc/gemm/gemm_runner.cu (cuBLASLt)
+ * fp8_gemm_descale_bf16out     csrc/bindings.cpp:2062-2069 -> csrc/kernels/decoder_fused.cu:310-468
+ * cutlass_fp8_*_bf16out        csrc/bindings.cpp:2388-2422 -> csrc/gemm/cutlass_sm100.cu:75-125
+ *   D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . W(N,K)^T + bias(N)
+ *   A, W: E4M3, row-major, K contiguous, 16-byte aligned, K % 16 == 0.  d_scale_* and bias may be NULL.
+ *   splits: 0 = choose; else split-K factor in [1, 8] (reduced inside a thread-block cluster). */
+int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
+                         const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
+                         void* stream);
+/* Reads (and optionally clears) the device status word of the tensor-core kernels.  0 = no bounded wait
+ * ever gave up; otherwise (code | blockIdx.x << 8), code 1 = TMA producer, 2 = MMA issuer, 3 = epilogue.
+ * Synchronises the device (a cudaMemcpyFromSymbol): do not call inside graph capture. */
+int frt_b200_gemm_status(int reset);
+
+/* ---------------------------------------------------------------- small bf16 projections, copies, queries
+ * GemmRunner::bf16_nn          csrc/bindings.cpp:662-667  (action in/out projections 32 <-> 1024)
+ *   D(M,N) bf16 = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate != 0); B row-major (K,N). */
+int frt_b200_gemm_bf16_nn_small(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                                int accumulate, int flags, void* stream);
+/* gpu_copy                     csrc/bindings.cpp:2533-2537  (device-to-device, async on stream) */
+int frt_b200_copy(void* dst, const void* src, long long nbytes, void* stream);
+/* get_sm_version               csrc/bindings.cpp:2447-2453  (returns major*10+minor, 100 on B200) */
+int frt_b200_sm_version(void);
+
+/* number of SMs of the current device (grid sizing) */
+int frt_b200_device_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHRT_B200_H */
