@@ -1,0 +1,556 @@
+// Flash attention forward for sm_100a: bf16 Q/K/V, tcgen05 MMAs with S and O
+// accumulators in TMEM, TMA-fed operands, non-causal, MHA / GQA / MQA.
+//
+// Replaces, for sm_100a, the reference attention entry points
+//   fa2.fwd_bf16 / fwd_bf16_seqused[_splitkv]   csrc/fa2_bindings.cpp:142-183 -> csrc/attention/fa2_wrapper.cu
+//   (call site RtxFlashAttnBackend.decoder_attn, flash_rt/hardware/rtx/attn_backend.py:633-660)
+// and covers the two shapes of the denoise path:
+//   * MQA cross-attention of the action expert: 50 x 8 query rows of width 256
+//     against one KV head of 768 prefix + 50 fresh keys;
+//   * long bidirectional self-attention of a video DiT (head_dim 128).
+//
+// Work split.  The G = Hq / Hkv query heads that share a KV head are packed into
+// the MMA M-dimension (row = token * G + head-in-group), so one 128-row tile holds
+// 128 / G tokens and K/V are read once for all of them.  grid = (row tiles,
+// Hkv * batch, kv splits).  The kv splits of one tile form a thread-block cluster
+// (1 x 1 x C, C <= 8): each CTA runs an online-softmax pass over its slice of the
+// keys, then the partial (max, sum, O) triples are combined through distributed
+// shared memory, each CTA finishing 1/C of the head dimension.  No global scratch.
+//
+// Per CTA and per chunk of BKV keys:  S = Q K^T (UMMA 128 x BKV x 16, both operands
+// K-major) -> TMEM;  four softmax warps (one thread per row) read S with tcgen05.ld,
+// keep the running max / sum, write P as bf16 into shared memory in the 128-byte
+// swizzled K-major layout;  O += P V (UMMA 128 x D x 16, V is the MN-major B
+// operand straight from its (key, d) layout).
+//
+// Floating point: cosine >= 0.999 and max-abs <= 2e-2 x RMS against the fp32
+// reference is the acceptance bar; exp2 uses the hardware approximation.
+#include "common.cuh"
+#include "tc05.cuh"
+
+#include <mutex>
+
+namespace frt {
+
+__device__ int g_attn_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
+
+// ------------------------------------------------------------------ tensor maps (bf16, up to 5-D)
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled g_encode_attn = nullptr;
+static std::mutex g_attn_mu;
+
+static int ensure_encode_attn() {
+    std::lock_guard<std::mutex> lk(g_attn_mu);
+    if (g_encode_attn) return FRT_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return FRT_ERR_UNSUPPORTED;
+    g_encode_attn = (PFN_encodeTiled)fn;
+    return FRT_OK;
+}
+
+// dims[0] is the contiguous one (elements); strides_bytes[i] is the pitch of dims[i+1]
+static int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box) {
+    int rc = ensure_encode_attn();
+    if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(base) & 15) return FRT_ERR_INVALID;
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], e[5];
+    for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) {
+        if (strides_bytes[i] & 15) return FRT_ERR_INVALID;
+        s[i] = strides_bytes[i];
+    }
+    CUresult r = g_encode_attn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), d, s, b, e,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FRT_OK : FRT_ERR_INVALID;
+}
+
+namespace tc {
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+        "[%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, "
+        "%7}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+}  // namespace tc
+
+// ------------------------------------------------------------------ kernel
+struct AttnParams {
+    __nv_bfloat16* O;            // (B, Sq, Hq, D) with the strides below (elements)
+    uint8_t* O_fp8;              // optional second result: e4m3(clamp(O / *out_scale)), same indexing, or null
+    const float* out_scale;      // device scalar for O_fp8
+    float* lse;                  // optional (B, Hq, Sq) fp32 natural-log-sum-exp, or null
+    const int* seqused_k;        // optional device int: number of valid keys (<= Skv), or null
+    long long o_bs, o_rs, o_hs;
+    int B, Sq, Skv, Hq, Hkv, G;
+    int chunks_total;            // ceil(Skv / BKV)
+    float scale_log2;            // softmax_scale * log2(e)
+};
+
+template <int D, int BKV>
+struct AttnCfg {
+    static constexpr int DB = D / 64;                      // 64-element (128-byte) blocks along the head dim
+    static constexpr int Q_BYTES = 128 * D * 2;
+    static constexpr int KV_BYTES = BKV * D * 2;           // one of K or V
+    static constexpr int PB = (BKV + 63) / 64;             // 64-key blocks of P
+    static constexpr int P_BYTES = PB * 128 * 128;
+    static constexpr int OFF_K = Q_BYTES;
+    static constexpr int OFF_V = OFF_K + KV_BYTES;
+    static constexpr int OFF_P = OFF_V + KV_BYTES;
+    static constexpr int DATA_BYTES = OFF_P + P_BYTES;
+    static constexpr int RED_BYTES = D * 128 * 4;          // partial O staged as [d][row] fp32
+    static constexpr int ML_BYTES = 2 * 128 * 4;
+    static constexpr int BODY = (DATA_BYTES > RED_BYTES ? DATA_BYTES : RED_BYTES);
+    static constexpr int SMEM_BYTES = BODY + ML_BYTES + 256 + 1024;
+    static constexpr int S_COL = 0;
+    static constexpr int O_COL = 256;
+    static constexpr int TMEM_COLS = 512;
+    static_assert(BKV % 16 == 0 && BKV <= 256, "key chunk must be a multiple of 16, at most 256");
+    static_assert(D % 64 == 0 && D <= 256, "head dim must be a multiple of 64, at most 256");
+    static_assert(KV_BYTES % 1024 == 0 && Q_BYTES % 1024 == 0, "tiles must keep 1024-byte alignment");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+enum { AERR_PRODUCER = 0x11, AERR_MMA = 0x12, AERR_SOFTMAX = 0x13 };
+
+#define ATTN_WAIT(bar, parity, code)                                                     \
+    do {                                                                                 \
+        if (!tc::mbar_wait_until((bar), (parity), deadline, abort_flag)) {               \
+            if (!*abort_flag) atomicCAS(&g_attn_status, 0, (code) | (blockIdx.x << 8));  \
+            *abort_flag = 1;                                                             \
+        }                                                                                \
+    } while (0)
+
+template <int D, int BKV>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+    using Cfg = AttnCfg<D, BKV>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + Cfg::OFF_K;
+    uint8_t* sV = smem + Cfg::OFF_V;
+    uint8_t* sP = smem + Cfg::OFF_P;
+    float* red = reinterpret_cast<float*>(smem);                       // aliases the operand tiles after the last MMA
+    float* s_m = reinterpret_cast<float*>(smem + Cfg::BODY);           // per-row running max (log2 domain)
+    float* s_l = s_m + 128;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BODY + Cfg::ML_BYTES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* v_full = bars + 2;
+    uint64_t* kv_empty = bars + 3;    // K and V tiles may be overwritten (PV of the chunk has completed)
+    uint64_t* s_full = bars + 4;      // S = Q K^T is in TMEM
+    uint64_t* p_ready = bars + 5;     // P is in shared memory, O has been rescaled (128 arrivals)
+    uint64_t* o_full = bars + 6;      // O += P V has completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t C = tc::cluster_nctarank();
+    const uint32_t rank = tc::cluster_ctarank();
+    const int tile = blockIdx.x;
+    const int hk = blockIdx.y % p.Hkv;
+    const int b = blockIdx.y / p.Hkv;
+    const int tok0 = tile * (128 / p.G);                                // first token of this row tile
+    const int c_begin = (int)((long long)p.chunks_total * rank / C);
+    const int c_end = (int)((long long)p.chunks_total * (rank + 1) / C);
+    const int nchunks = c_end - c_begin;
+
+    if (threadIdx.x == 0) {
+        tc::mbar_init(q_full, 1);
+        tc::mbar_init(k_full, 1);
+        tc::mbar_init(v_full, 1);
+        tc::mbar_init(kv_empty, 1);
+        tc::mbar_init(s_full, 1);
+        tc::mbar_init(p_ready, 128);
+        tc::mbar_init(o_full, 1);
+        *abort_flag = 0;
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&tmQ);
+        tc::tma_prefetch_desc(&tmK);
+        tc::tma_prefetch_desc(&tmV);
+    }
+    if (warp == 5) {
+        tc::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_S = tmem + Cfg::S_COL;
+    const uint32_t tmem_O = tmem + Cfg::O_COL;
+
+    pdl_launch_dependents();
+    pdl_wait();                       // Q (and the freshly appended K/V rows) come from the previous kernel
+
+    int kv_len = p.Skv;
+    if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
+
+    if (warp == 4 && lane == 0) {
+        // ---------------- TMA producer
+        tc::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+        for (int db = 0; db < Cfg::DB; ++db)
+            tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, q_full, db * 64, 0, hk, tok0, b);
+        for (int i = 0; i < nchunks && !*abort_flag; ++i) {
+            if (i > 0) ATTN_WAIT(kv_empty, (uint32_t)((i - 1) & 1), AERR_PRODUCER);
+            if (*abort_flag) break;
+            const int key0 = (c_begin + i) * BKV;
+            tc::mbar_arrive_expect_tx(k_full, Cfg::KV_BYTES);
+            for (int db = 0; db < Cfg::DB; ++db)
+                tc::tma_load_4d(sK + db * (BKV * 128), &tmK, k_full, db * 64, hk, key0, b);
+            tc::mbar_arrive_expect_tx(v_full, Cfg::KV_BYTES);
+            for (int db = 0; db < Cfg::DB; ++db)
+                tc::tma_load_4d(sV + db * (BKV * 128), &tmV, v_full, db * 64, hk, key0, b);
+        }
+    } else if (warp == 5 && lane == 0) {
+        // ---------------- MMA issuer
+        constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);   // bf16 x bf16, both K-major
+        constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, D);     // B (= V) is MN-major
+        ATTN_WAIT(q_full, 0u, AERR_MMA);
+        for (int i = 0; i < nchunks && !*abort_flag; ++i) {
+            const uint32_t ph = (uint32_t)(i & 1);
+            ATTN_WAIT(k_full, ph, AERR_MMA);
+            if (*abort_flag) break;
+            tc::tc_fence_after_sync();
+            // S = Q K^T : D / 16 steps of K = 16; a step advances 32 bytes inside a 128-byte block
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+                const uint64_t dq = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ + (k / 4) * (128 * 128))) + 2 * (k % 4);
+                const uint64_t dk = tc::make_desc_kmajor_sw128(tc::smem_u32(sK + (k / 4) * (BKV * 128))) + 2 * (k % 4);
+                tc::mma_f16(tmem_S, dq, dk, idesc_s, k > 0 ? 1u : 0u);
+            }
+            tc::mma_commit(s_full);
+            ATTN_WAIT(p_ready, ph, AERR_MMA);
+            ATTN_WAIT(v_full, ph, AERR_MMA);
+            if (*abort_flag) break;
+            tc::tc_fence_after_sync();
+            // O += P V : BKV / 16 steps over the keys
+#pragma unroll
+            for (int k = 0; k < BKV / 16; ++k) {
+                const uint64_t dp = tc::make_desc_kmajor_sw128(tc::smem_u32(sP + (k / 4) * (128 * 128))) + 2 * (k % 4);
+                const uint64_t dv = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV + k * 16 * 128), BKV * 128);
+                tc::mma_f16(tmem_O, dp, dv, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+            }
+            tc::mma_commit(kv_empty);
+            tc::mma_commit(o_full);
+        }
+    } else if (warp < 4) {
+        // ---------------- softmax: thread = row (TMEM lane 32*warp + lane)
+        const int row = warp * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        float m_run = -INFINITY, l_run = 0.0f;
+        for (int i = 0; i < nchunks; ++i) {
+            const uint32_t ph = (uint32_t)(i & 1);
+            ATTN_WAIT(s_full, ph, AERR_SOFTMAX);
+            __syncwarp();
+            if (__any_sync(0xffffffffu, *abort_flag != 0)) break;      // leave the loop as a whole warp
+            tc::tc_fence_after_sync();
+            const int key0 = (c_begin + i) * BKV;
+            float s[BKV];
+#pragma unroll
+            for (int c = 0; c < BKV; c += 16) {
+                uint32_t v[16];
+                tc::tmem_ld16(tmem_S + lane_off + c, v);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    s[c + j] = (key0 + c + j < kv_len) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
+            }
+            float mx = m_run;
+#pragma unroll
+            for (int j = 0; j < BKV; ++j) mx = fmaxf(mx, s[j]);
+            const float m_use = (mx == -INFINITY) ? 0.0f : mx;
+            const float alpha = tc::ex2_approx(m_run - m_use);       // m_run = -inf -> 0
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < BKV; ++j) {
+                s[j] = tc::ex2_approx(s[j] - m_use);
+                sum += s[j];
+            }
+            l_run = l_run * alpha + sum;
+            m_run = mx;
+            // P -> shared memory, K-major rows of 128 bytes, 16-byte chunk index xor (row & 7)
+#pragma unroll
+            for (int c8 = 0; c8 < BKV / 8; ++c8) {
+                uint4 w;
+                w.x = pack_bf16x2(s[c8 * 8 + 0], s[c8 * 8 + 1]);
+                w.y = pack_bf16x2(s[c8 * 8 + 2], s[c8 * 8 + 3]);
+                w.z = pack_bf16x2(s[c8 * 8 + 4], s[c8 * 8 + 5]);
+                w.w = pack_bf16x2(s[c8 * 8 + 6], s[c8 * 8 + 7]);
+                const int blk = c8 / 8, ch = c8 % 8;
+                *reinterpret_cast<uint4*>(sP + blk * (128 * 128) + row * 128 + ((ch ^ (row & 7)) << 4)) = w;
+            }
+            // rescale the running O (the previous P V has completed: o_full phase i-1)
+            if (i > 0) {
+                ATTN_WAIT(o_full, (uint32_t)((i - 1) & 1), AERR_SOFTMAX);
+                __syncwarp();
+                tc::tc_fence_after_sync();
+                // tcgen05.ld / st are warp-collective: the decision to rescale must be uniform across the warp
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t v[32];
+                        tc::tmem_ld32(tmem_O + lane_off + c, v);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                        tc::tmem_st32(tmem_O + lane_off + c, v);
+                    }
+                    tc::tmem_st_wait();
+                }
+            }
+            tc::fence_proxy_async_smem();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(p_ready);
+        }
+        // ---------------- stage the partial result for the cluster combine
+        if (nchunks > 0) {
+            ATTN_WAIT(o_full, (uint32_t)((nchunks - 1) & 1), AERR_SOFTMAX);
+            tc::tc_fence_after_sync();
+        }
+        __syncwarp();
+        s_m[row] = m_run;
+        s_l[row] = l_run;
+        if (!__any_sync(0xffffffffu, *abort_flag != 0)) {
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t v[32];
+                if (nchunks > 0) {
+                    tc::tmem_ld32(tmem_O + lane_off + c, v);
+                    tc::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) red[(c + j) * 128 + row] = __uint_as_float(v[j]);
+            }
+        }
+    }
+    __syncwarp();
+    tc::cluster_sync_all();
+
+    // ---------------- combine across the kv splits: this CTA finishes columns [d0, d1)
+    if (warp < 4 && !*abort_flag) {
+        const int row = warp * 32 + lane;
+        const int dper = ((D / 8 + (int)C - 1) / (int)C) * 8;           // multiple of 8 columns per rank
+        const int d0 = (int)rank * dper;
+        const int d1 = d0 + dper < D ? d0 + dper : D;
+        const int t = tok0 + row / p.G;
+        const int hq = hk * p.G + row % p.G;
+        if (d0 < D && t < p.Sq) {
+            float w[8];
+            float M = -INFINITY;
+            const uint32_t a_m = tc::smem_u32(&s_m[row]);
+            const uint32_t a_l = tc::smem_u32(&s_l[row]);
+            for (uint32_t s = 0; s < C; ++s) {
+                w[s] = tc::dsmem_ld_f32(tc::dsmem_map(a_m, s));
+                M = fmaxf(M, w[s]);
+            }
+            float L = 0.0f;
+            for (uint32_t s = 0; s < C; ++s) {
+                w[s] = (w[s] == -INFINITY) ? 0.0f : tc::ex2_approx(w[s] - M);
+                L += w[s] * tc::dsmem_ld_f32(tc::dsmem_map(a_l, s));
+            }
+            const float invL = L > 0.0f ? 1.0f / L : 0.0f;
+            for (uint32_t s = 0; s < C; ++s) w[s] *= invL;
+            const size_t obase = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs;
+            const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+            for (int d = d0; d < d1; d += 8) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+                for (uint32_t s = 0; s < C; ++s) {
+                    if (w[s] == 0.0f) continue;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        acc[j] += w[s] * tc::dsmem_ld_f32(tc::dsmem_map(tc::smem_u32(&red[(d + j) * 128 + row]), s));
+                }
+                uint4 o;
+                o.x = pack_bf16x2(acc[0], acc[1]);
+                o.y = pack_bf16x2(acc[2], acc[3]);
+                o.z = pack_bf16x2(acc[4], acc[5]);
+                o.w = pack_bf16x2(acc[6], acc[7]);
+                st_global_v4(p.O + obase + d, o);
+                if (p.O_fp8) {
+                    // quantise the bf16-rounded value, as a separate quantise kernel reading O would
+                    float q[8];
+                    unpack_bf16x2(o.x, q[0], q[1]);
+                    unpack_bf16x2(o.y, q[2], q[3]);
+                    unpack_bf16x2(o.z, q[4], q[5]);
+                    unpack_bf16x2(o.w, q[6], q[7]);
+                    uint2 o8;
+                    o8.x = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[0], inv_os)), clamp448(__fmul_rn(q[1], inv_os)),
+                                           clamp448(__fmul_rn(q[2], inv_os)), clamp448(__fmul_rn(q[3], inv_os)));
+                    o8.y = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[4], inv_os)), clamp448(__fmul_rn(q[5], inv_os)),
+                                           clamp448(__fmul_rn(q[6], inv_os)), clamp448(__fmul_rn(q[7], inv_os)));
+                    st_global_v2(p.O_fp8 + obase + d, o8);
+                }
+            }
+            if (p.lse && rank == 0)
+                p.lse[((size_t)b * p.Hq + hq) * p.Sq + t] = (L > 0.0f) ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+        }
+    }
+    tc::cluster_sync_all();
+
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+}
+
+template <int D, int BKV>
+static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
+                       const long long* ks, const long long* vs, int splits, bool pdl, cudaStream_t stream) {
+    using Cfg = AttnCfg<D, BKV>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        attr_done = true;
+    }
+    // Q as {d, head-in-group, kv head, token, batch}; strides in elements: qs = {batch, row, head}
+    CUtensorMap tmQ, tmK, tmV;
+    {
+        uint64_t dims[5] = {(uint64_t)D, (uint64_t)p.G, (uint64_t)p.Hkv, (uint64_t)p.Sq, (uint64_t)p.B};
+        uint64_t str[4] = {(uint64_t)qs[2] * 2, (uint64_t)qs[2] * 2 * p.G, (uint64_t)qs[1] * 2, (uint64_t)qs[0] * 2};
+        uint32_t box[5] = {64, (uint32_t)p.G, 1, (uint32_t)(128 / p.G), 1};
+        int rc = make_tmap_bf16(&tmQ, Q, 5, dims, str, box);
+        if (rc) return rc;
+    }
+    {
+        uint64_t dims[4] = {(uint64_t)D, (uint64_t)p.Hkv, (uint64_t)p.Skv, (uint64_t)p.B};
+        uint64_t strk[3] = {(uint64_t)ks[2] * 2, (uint64_t)ks[1] * 2, (uint64_t)ks[0] * 2};
+        uint64_t strv[3] = {(uint64_t)vs[2] * 2, (uint64_t)vs[1] * 2, (uint64_t)vs[0] * 2};
+        uint32_t box[4] = {64, 1, (uint32_t)BKV, 1};
+        int rc = make_tmap_bf16(&tmK, K, 4, dims, strk, box);
+        if (rc) return rc;
+        rc = make_tmap_bf16(&tmV, V, 4, dims, strv, box);
+        if (rc) return rc;
+    }
+    p.chunks_total = (p.Skv + BKV - 1) / BKV;
+    if (splits > p.chunks_total) splits = p.chunks_total;
+    if (splits < 1) splits = 1;
+    const int tiles = (p.Sq * p.G + 127) / 128;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, p.Hkv * p.B, splits);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = splits;
+    ++na;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<D, BKV>, tmQ, tmK, tmV, p);
+    return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
+}
+
+}  // namespace frt
+
+using namespace frt;
+
+extern "C" {
+
+// Non-causal attention forward, bf16.  Layouts (strides in elements, innermost head_dim contiguous):
+//   Q, O: (batch, seqlen_q, num_heads_q, head_dim)   q_strides / o_strides = {batch, row, head}
+//   K, V: (batch, seqlen_k, num_heads_kv, head_dim)  k_strides / v_strides = {batch, row, head}
+// O_fp8 / out_scale: optional fused e4m3 copy of O (null to skip).  lse: optional (batch, heads_q, seqlen_q).
+// seqused_k: optional device int limiting the valid keys.  kv_splits: 0 = choose, else 1..8.
+int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
+                                const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
+                                int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
+                                const long long* q_strides, const long long* k_strides, const long long* v_strides,
+                                const long long* o_strides, float softmax_scale, int kv_splits, int flags,
+                                void* stream) {
+    if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return FRT_ERR_INVALID;
+    if (batch <= 0 || seqlen_q < 0 || seqlen_k <= 0 || num_heads_q <= 0 || num_heads_kv <= 0) return FRT_ERR_INVALID;
+    if (O_fp8 && !out_scale) return FRT_ERR_INVALID;
+    if (num_heads_q % num_heads_kv) return FRT_ERR_INVALID;
+    const int G = num_heads_q / num_heads_kv;
+    if (G > 128 || (128 % G)) return FRT_ERR_UNSUPPORTED;
+    if (head_dim != 128 && head_dim != 256) return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(O) & 15) || (o_strides[1] & 7) || (o_strides[2] & 7) || (o_strides[0] & 7))
+        return FRT_ERR_INVALID;
+    if (seqlen_q == 0) return FRT_OK;
+    AttnParams p = {};
+    p.O = (__nv_bfloat16*)O;
+    p.O_fp8 = (uint8_t*)O_fp8;
+    p.out_scale = out_scale;
+    p.lse = lse;
+    p.seqused_k = seqused_k;
+    p.o_bs = o_strides[0];
+    p.o_rs = o_strides[1];
+    p.o_hs = o_strides[2];
+    p.B = batch;
+    p.Sq = seqlen_q;
+    p.Skv = seqlen_k;
+    p.Hq = num_heads_q;
+    p.Hkv = num_heads_kv;
+    p.G = G;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool pdl = flags & 1;
+    const int tiles = ((seqlen_q * G + 127) / 128) * num_heads_kv * batch;
+    if (head_dim == 256) {
+        constexpr int BKV = 112;
+        int chunks = (seqlen_k + BKV - 1) / BKV;
+        int sp = kv_splits > 0 ? kv_splits : (tiles >= 74 ? 1 : (chunks < 8 ? chunks : 8));
+        if (sp > 8) sp = 8;
+        return launch_attn<256, BKV>(Q, K, V, p, q_strides, k_strides, v_strides, sp, pdl, s);
+    }
+    constexpr int BKV = 128;
+    int chunks = (seqlen_k + BKV - 1) / BKV;
+    int sp = kv_splits > 0 ? kv_splits : (tiles >= 74 ? 1 : (chunks < 8 ? chunks : 8));
+    if (sp > 8) sp = 8;
+    return launch_attn<128, BKV>(Q, K, V, p, q_strides, k_strides, v_strides, sp, pdl, s);
+}
+
+// returns (and optionally clears) the attention kernels' device status word; 0 = no bounded wait gave up.
+// code 0x11 = TMA producer, 0x12 = MMA issuer, 0x13 = softmax warps.  Synchronises the device.
+int frt_b200_attention_status(int reset) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int));
+    if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+    if (reset && v) {
+        int z = 0;
+        cudaMemcpyToSymbol(g_attn_status, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // extern "C"

@@ -117,6 +117,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     volatile int* issued = abort_flag + 1;
     volatile int* consumed = abort_flag + 2;
 
+    const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int lane0 = blockIdx.x * 128;              // first row of the lane operand
@@ -172,11 +173,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
         for (int i = pre; i < nkb; ++i) {
             const int s = i % STAGES;
             const uint32_t ph = ((i / STAGES) - 1) & 1;
-            bool ok = false;
-            for (uint32_t it = 0; it < FRT_WAIT_POLLS && !*abort_flag; ++it) {
-                if (tc::mbar_try_wait(&empty[s], ph)) { ok = true; break; }
-                if (it > 64) __nanosleep(64);
-            }
+            const bool ok = tc::mbar_wait_until(&empty[s], ph, deadline, abort_flag);
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(&g_gemm_status, 0, ERR_PRODUCER | (blockIdx.x << 8));
@@ -194,11 +191,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
         for (int i = 0; i < nkb; ++i) {
             const int s = i % STAGES;
             const uint32_t ph = (i / STAGES) & 1;
-            bool ok = false;
-            for (uint32_t it = 0; it < FRT_WAIT_POLLS && !*abort_flag; ++it) {
-                if (tc::mbar_try_wait(&full[s], ph)) { ok = true; break; }
-                if (it > 64) __nanosleep(32);
-            }
+            const bool ok = tc::mbar_wait_until(&full[s], ph, deadline, abort_flag);
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(&g_gemm_status, 0, ERR_MMA | (blockIdx.x << 8));
@@ -222,15 +215,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
 
     // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w .. 32w+31
     pdl_wait();
-    bool have_acc = false;
-    for (uint32_t it = 0; it < FRT_WAIT_POLLS && !*abort_flag; ++it) {
-        if (tc::mbar_try_wait(accum_bar, 0)) { have_acc = true; break; }
-        if (it > 32) __nanosleep(64);
-    }
+    const bool acc_seen = tc::mbar_wait_until(accum_bar, 0, deadline, abort_flag);
+    const bool have_acc = __all_sync(0xffffffffu, acc_seen);   // tcgen05.ld below is warp-collective
     if (!have_acc && !*abort_flag) {
         *abort_flag = 1;
         atomicCAS(&g_gemm_status, 0, ERR_EPILOGUE | (blockIdx.x << 8));
     }
+    __syncwarp();
     tc::tc_fence_after_sync();
 
     float alpha = p.alpha_host;

@@ -41,28 +41,39 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One bounded poll: suspends for at most ~1 us (the explicit time hint), returns whether the phase completed.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, P;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  try_wait itself blocks for a hardware-defined slice, so the
-// poll budget below corresponds to roughly a second before giving up.
-#ifndef FRT_WAIT_POLLS
-#define FRT_WAIT_POLLS (1u << 22)
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Every wait of a kernel shares one wall-clock deadline taken at kernel start, so a protocol error
+// ends the whole kernel after FRT_KERNEL_DEADLINE_NS instead of spinning.
+#ifndef FRT_KERNEL_DEADLINE_NS
+#define FRT_KERNEL_DEADLINE_NS 2000000000ull
 #endif
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < FRT_WAIT_POLLS; ++i) {
+// poll budget kept for call sites that count polls; each poll is bounded by the hint above
+#ifndef FRT_WAIT_POLLS
+#define FRT_WAIT_POLLS (1u << 21)
+#endif
+__device__ __forceinline__ bool mbar_wait_until(uint64_t* bar, uint32_t parity, uint64_t deadline_ns,
+                                                volatile int* abort_flag) {
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(64);
+        if (*abort_flag) return false;
+        if ((i & 15) == 15 && global_timer_ns() > deadline_ns) return false;
     }
-    return false;
 }
 
 // ---------------------------------------------------------------- TMA (tiled, 2D / 3D loads)

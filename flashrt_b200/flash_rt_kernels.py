@@ -184,7 +184,8 @@ def get_sm_version() -> int:
 
 def tensor_core_status(reset: bool = True) -> int:
     """0 unless a bounded wait inside a tensor-core kernel gave up (see ``frt_b200_gemm_status``)."""
-    return _lib.call_status("frt_b200_gemm_status", 1 if reset else 0)
+    r = 1 if reset else 0
+    return _lib.call_status("frt_b200_gemm_status", r) or _lib.call_status("frt_b200_attention_status", r)
 
 
 def __getattr__(name: str):

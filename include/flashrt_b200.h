@@ -111,6 +111,25 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
  * Synchronises the device (a cudaMemcpyFromSymbol): do not call inside graph capture. */
 int frt_b200_gemm_status(int reset);
 
+/* ---------------------------------------------------------------- flash attention forward (tcgen05 / TMEM / TMA)
+ * fa2.fwd_bf16                 csrc/fa2_bindings.cpp:173-183  -> csrc/attention/fa2_wrapper.cu
+ * fa2.fwd_bf16_seqused[_splitkv] csrc/fa2_bindings.cpp:142-160
+ *   Non-causal softmax(Q K^T * softmax_scale) V, bf16 in / bf16 out, fp32 softmax and accumulation.
+ *   Q, O: (batch, seqlen_q, num_heads_q, head_dim); K, V: (batch, seqlen_k, num_heads_kv, head_dim);
+ *   *_strides: host arrays of 3 element strides {batch, row, head}; head_dim (128 or 256) contiguous.
+ *   num_heads_q / num_heads_kv must divide 128.  O_fp8 + out_scale: optional fused
+ *   e4m3(clamp(O * (1 / *out_scale), +-448)) written with O's indexing (NULL to skip).
+ *   lse: optional (batch, num_heads_q, seqlen_q) fp32; seqused_k: optional device int (valid keys).
+ *   kv_splits: 0 = choose, else 1..8 (combined inside a thread-block cluster; no scratch buffers). */
+int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
+                                const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
+                                int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
+                                const long long* q_strides, const long long* k_strides, const long long* v_strides,
+                                const long long* o_strides, float softmax_scale, int kv_splits, int flags,
+                                void* stream);
+/* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
+int frt_b200_attention_status(int reset);
+
 /* ---------------------------------------------------------------- small bf16 projections, copies, queries
  * GemmRunner::bf16_nn          csrc/bindings.cpp:662-667  (action in/out projections 32 <-> 1024)
  *   D(M,N) bf16 = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate != 0); B row-major (K,N). */

@@ -179,3 +179,34 @@ def gemm_fp8(A, B, sa, sb, b_is_nk=True, want_f32=False):
     lib().orc_gemm_fp8(_p(A), _p(B), _p(D), _p(Df), C.c_int(M), C.c_int(N), C.c_int(K), C.c_float(sa),
                        C.c_float(sb), C.c_int(1 if b_is_nk else 0))
     return (D, Df) if want_f32 else D
+
+
+# ---------------------------------------------------------------- attention (numpy, fp64)
+def attention(q_bits, k_bits, v_bits, scale, kv_len=None):
+    """Masked-softmax attention restated from the reference's torch ground truth
+    (flash_rt/structures/catalog/attention_core/reference.py:8-36; call site
+    flash_rt/hardware/rtx/attn_backend.py:633-660: non-causal, the query heads of a group share
+    one KV head, keys = prefix followed by the fresh tokens).
+
+    q (B, Sq, Hq, D), k / v (B, Skv, Hkv, D) as bf16 bit patterns; returns (out fp32 (B, Sq, Hq, D),
+    lse fp64 (B, Hq, Sq)).  Only the first ``kv_len`` keys count when given.
+    """
+    q = bf16_bits_to_f32(q_bits).astype(np.float64)
+    k = bf16_bits_to_f32(k_bits).astype(np.float64)
+    v = bf16_bits_to_f32(v_bits).astype(np.float64)
+    B, Sq, Hq, D = q.shape
+    Hkv = k.shape[2]
+    g = Hq // Hkv
+    if kv_len is not None:
+        k, v = k[:, :kv_len], v[:, :kv_len]
+    out = np.zeros((B, Sq, Hq, D), np.float64)
+    lse = np.zeros((B, Hq, Sq), np.float64)
+    for b in range(B):
+        for h in range(Hq):
+            s = (q[b, :, h, :] @ k[b, :, h // g, :].T) * scale
+            m = s.max(-1, keepdims=True)
+            p = np.exp(s - m)
+            l = p.sum(-1, keepdims=True)
+            out[b, :, h, :] = (p / l) @ v[b, :, h // g, :]
+            lse[b, h, :] = (m + np.log(l))[:, 0]
+    return out.astype(np.float32), lse

@@ -189,14 +189,15 @@ def test_adds(fvk, rows, dim):
     res, x, gate = _mk(rng, rows, dim), _mk(rng, rows, dim), _mk(rng, rows, dim)
     bias = _mk(rng, 1, dim)[0]
     n = rows * dim
+    d_x, d_gate, d_bias = Dev(x), Dev(gate), Dev(bias)     # keep every device buffer alive across the launch
     d = Dev(res)
-    fvk.residual_add(d.ptr, Dev(x).ptr, n, 0)
+    fvk.residual_add(d.ptr, d_x.ptr, n, 0)
     assert np.array_equal(d.get(), O.add(res, x, mode=0))
     d = Dev(res)
-    fvk.bias_residual(d.ptr, Dev(x).ptr, Dev(bias).ptr, rows, dim, 0)
+    fvk.bias_residual(d.ptr, d_x.ptr, d_bias.ptr, rows, dim, 0)
     assert np.array_equal(d.get(), O.add(res, x, aux=bias, mode=1))
     d = Dev(res)
-    fvk.gate_mul_residual(d.ptr, Dev(x).ptr, Dev(gate).ptr, n, 0)
+    fvk.gate_mul_residual(d.ptr, d_x.ptr, d_gate.ptr, n, 0)
     assert np.array_equal(d.get(), O.add(res, x, aux=gate, aux_stride=dim, mode=2))
 
 

@@ -69,10 +69,10 @@ def test_gemm_fp8_matches_fp64_oracle_exact_products():
     A = torch.from_numpy(rng.choice(vals, (M, K))).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
     W = torch.from_numpy(rng.choice(vals, (N, K))).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
     ref = O.gemm_fp8(A, W, 0.5, 0.25, b_is_nk=True)
+    d_sa, d_sb = f32(0.5), f32(0.25)
     for splits in (1, 4):
         d_A, d_W, d_D = Dev(A), Dev(W), zeros((M, N), np.uint16)
-        fvk.fp8_gemm_descale_bf16out(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, f32(0.5).ptr, f32(0.25).ptr, 0,
-                                     splits=splits)
+        fvk.fp8_gemm_descale_bf16out(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits)
         assert np.array_equal(d_D.get(), ref)
 
 
@@ -84,8 +84,8 @@ def test_gemm_fp8_large_m(M, N, K):
     rng = np.random.default_rng(M + N + K)
     A, sa = _fp8_operand(rng, M, K, 1.0)
     W, sb = _fp8_operand(rng, N, K, 0.02)
-    d_A, d_W, d_D = Dev(A), Dev(W), zeros((M, N), np.uint16)
-    fvk.GemmRunner().fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, f32(sa).ptr, f32(sb).ptr, 0)
+    d_A, d_W, d_D, d_sa, d_sb = Dev(A), Dev(W), zeros((M, N), np.uint16), f32(sa), f32(sb)
+    fvk.GemmRunner().fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0)
     got = d_D.get()
     assert fvk.tensor_core_status() == 0
     _check(got, _ref(A, W, sa, sb))
@@ -102,11 +102,12 @@ def test_gemm_bias_and_linearity():
     bias = rand_bf16(rng, (N,), 0.5)
     d_A, d_W, d_D, d_b = Dev(A), Dev(W), zeros((M, N), np.uint16), Dev(bias)
     g = fvk.GemmRunner()
-    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, f32(sa).ptr, f32(sb).ptr, 0, bias=d_b.ptr)
+    d_sa, d_sb, d_sa4 = f32(sa), f32(sb), f32(sa * 4)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr)
     _check(d_D.get(), _ref(A, W, sa, sb, bias))
     d_D2 = zeros((M, N), np.uint16)
-    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, f32(sa).ptr, f32(sb).ptr, 0)
-    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D2.ptr, M, N, K, f32(sa * 4).ptr, f32(sb).ptr, 0)   # x4 is exact in bf16
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D2.ptr, M, N, K, d_sa4.ptr, d_sb.ptr, 0)   # x4 is exact in bf16
     assert np.array_equal(O.bf16_bits_to_f32(d_D.get()) * 4, O.bf16_bits_to_f32(d_D2.get()))
 
 
@@ -119,13 +120,13 @@ def test_small_bf16_projections():
         A, B = rand_bf16(rng, (M, K)), rand_bf16(rng, (K, N), 0.02)
         bias = rand_bf16(rng, (N,), 0.1)
         ref = O.bf16_bits_to_f32(A).astype(np.float64) @ O.bf16_bits_to_f32(B).astype(np.float64)
-        d_D = zeros((M, N), np.uint16)
-        g.bf16_nn(Dev(A).ptr, Dev(B).ptr, d_D.ptr, M, N, K, 0)
+        d_D, d_A, d_B, d_bias = zeros((M, N), np.uint16), Dev(A), Dev(B), Dev(bias)
+        g.bf16_nn(d_A.ptr, d_B.ptr, d_D.ptr, M, N, K, 0)
         got = O.bf16_bits_to_f32(d_D.get())
         rms = np.sqrt(np.mean(ref ** 2))
         assert np.abs(got - ref).max() <= np.abs(ref).max() * 2.0 ** -8 + 1e-3 * rms
         d_D2 = zeros((M, N), np.uint16)
-        g.bf16_nn(Dev(A).ptr, Dev(B).ptr, d_D2.ptr, M, N, K, 0, bias=Dev(bias).ptr)
+        g.bf16_nn(d_A.ptr, d_B.ptr, d_D2.ptr, M, N, K, 0, bias=d_bias.ptr)
         got2 = O.bf16_bits_to_f32(d_D2.get())
         ref2 = ref + O.bf16_bits_to_f32(bias)[None, :]
         assert np.abs(got2 - ref2).max() <= np.abs(ref2).max() * 2.0 ** -8 + 1e-3 * rms
