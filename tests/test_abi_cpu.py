@@ -1,0 +1,59 @@
+"""CPU suite: the C-ABI shared library loads and exports every symbol the public header declares
+(no compute call is made: there is no GPU here)."""
+import ctypes
+import os
+import re
+
+from flashrt_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_header_declares_only_plain_c_types():
+    protos = _lib.parse_header()
+    assert len(protos) >= 15
+    for name, types in protos.items():
+        assert name.startswith("frt_b200_")
+        for t in types:
+            assert t in ("ptr", "int", "long long", "float"), (name, t)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in _lib.parse_header():
+        assert hasattr(lib, name), name
+
+
+def test_every_exported_entry_point_is_declared():
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    exported = set(re.findall(r"\bT (frt_b200_\w+)", out))
+    assert exported == set(_lib.parse_header())
+
+
+def test_header_cites_the_reference_for_every_entry_point():
+    text = open(_lib.HEADER_PATH).read()
+    # each prototype is preceded by a comment block naming a reference file:line (or says it has none)
+    blocks = re.split(r"\bint\s+frt_b200_\w+\s*\(", text)
+    for b in blocks[:-1]:
+        tail = b[-2500:]
+        assert re.search(r"csrc/[\w/]+\.(cpp|cu|cuh|h):\d+", tail) or "no counterpart in the reference" in tail \
+            or "Status word" in tail or "status word" in tail or "grid sizing" in tail
+
+
+def test_shim_mirrors_reference_binding_names():
+    from flashrt_b200 import flash_rt_fa2, flash_rt_kernels as fvk
+    for n in ("rms_norm", "rms_norm_fp8", "ada_rms_norm_style", "ada_rms_norm_style_fp8", "residual_add_rms_norm",
+              "residual_add_rms_norm_fp8", "gate_residual_ada_norm_fp8", "gate_geglu_merged", "gate_geglu_merged_fp8",
+              "qkv_split_rope", "qkv_split_rope_devpos", "gate_mul_residual", "bias_residual", "residual_add",
+              "gpu_copy", "quantize_fp8_static", "quantize_fp8_device", "fp8_accumulate_scale_max",
+              "fp8_gemm_descale_bf16out", "GemmRunner", "has_cutlass_sm100", "get_sm_version"):
+        assert callable(getattr(fvk, n)), n
+    for n in ("fp8_nt_dev", "bf16_nn", "autotune_fp8_nn_dev", "autotune_bf16_nn"):
+        assert callable(getattr(fvk.GemmRunner, n)), n
+    for n in ("fwd_bf16", "fwd_bf16_seqused", "fwd_bf16_seqused_splitkv"):
+        assert callable(getattr(flash_rt_fa2, n)), n
+    assert not hasattr(fvk, "silu_mul_split_fp8_fp16")        # outside the path: refused, not faked
+    import pytest
+    with pytest.raises(fvk.NotBuilt):
+        fvk.GemmRunner().fp8_nn_dev(0, 0, 0, 1, 1, 16, 0, 0)

@@ -1,0 +1,189 @@
+"""CPU suite: pins the oracle (C kernels + torch block restatement) against
+  * outputs of the reference's own torch ground-truth functions (tests/golden/cfg0_block.npz),
+  * torch's E4M3 / bf16 conversions (bit-exact),
+  * plain fp32 / fp64 formulas of each fused kernel (to rounding tolerance).
+"""
+import os
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import block_ref as R
+from oracle import oracle as O
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "cfg0_block.npz")
+
+
+def _crc(t):
+    return zlib.crc32(t.contiguous().numpy().tobytes())
+
+
+@pytest.fixture(scope="module")
+def cfg0():
+    S, P = 50, 768
+    ck = R.synthetic_checkpoint(seed=0, layers=1)
+    pk, pv = R.synthetic_prefix_kv(seed=1, layers=1, prefix_len=P)
+    x = torch.randn(S, R.DEC_D, generator=torch.Generator().manual_seed(2))
+    cond = R.conditioning(ck, 0.5)[None, :]
+    return dict(S=S, P=P, ck=ck, pk=pk, pv=pv, x=x, cond=cond, gold=np.load(GOLD))
+
+
+def test_seeded_inputs_regenerate(cfg0):
+    c = cfg0
+    got = [_crc(c["x"]), _crc(c["cond"]), _crc(c["ck"]["decoder_attn_qkv_w"][0]), _crc(c["pk"]), _crc(c["pv"])]
+    assert got == [int(v) for v in c["gold"]["crc"]]
+
+
+def test_block_restatement_matches_reference_ground_truth(cfg0):
+    """oracle.block_ref.decoder_block (device layout, adjacent-pair RoPE) == the reference's catalog functions
+    (HF layout, rotate-half RoPE) on configuration 0."""
+    c = cfg0
+    ck = c["ck"]
+    sa = (c["cond"] @ ck["decoder_pre_attn_norm_mod_w"][0] + ck["decoder_pre_attn_norm_mod_b"][0])[0]
+    sf = (c["cond"] @ ck["decoder_pre_ffn_norm_mod_w"][0] + ck["decoder_pre_ffn_norm_mod_b"][0])[0]
+    tab = R.rope_table(np.arange(c["P"], c["P"] + c["S"]))
+    out, parts = R.decoder_block(c["x"], ck, 0, sa, sf, c["pk"][0], c["pv"][0], tab, return_parts=True)
+    g = c["gold"]
+    for name, got in (("out", out), ("x1", parts["x1"]), ("h", parts["h"]), ("h2", parts["h2"]),
+                      ("attn", parts["attn"])):
+        ref = torch.from_numpy(g[name])
+        assert torch.allclose(got, ref, rtol=2e-4, atol=2e-5), name
+    assert np.array_equal(g["out"], g["out_via_decoder_ffn_ref"])
+    # q / k agree up to the head-dim permutation that relates the two RoPE forms
+    q_hf = torch.from_numpy(g["q_hf"])                       # (S, 8, 256) first halves | second halves
+    q_il = parts["q"]                                        # pairs adjacent
+    assert torch.allclose(q_il[..., 0::2], q_hf[..., :128], rtol=2e-4, atol=2e-5)
+    assert torch.allclose(q_il[..., 1::2], q_hf[..., 128:], rtol=2e-4, atol=2e-5)
+
+
+def test_rope_interleave_identity():
+    """rotate-half on HF-layout projections == adjacent-pair rotation on row-interleaved projections
+    (the identity the reference tests in tests/test_structures_adarms_stack_region.py:208-221)."""
+    g = torch.Generator().manual_seed(3)
+    S, H, hd, D = 7, 2, 256, 64
+    w_hf = torch.randn(H * hd, D, generator=g)
+    x = torch.randn(S, D, generator=g)
+    tab = R.rope_table(np.arange(100, 100 + S), hd)
+    q_hf = R.rope_rotate_half((x @ w_hf.t()).reshape(S, H, hd), tab)
+    q_il = R.rope_adjacent_pairs((x @ R.interleave_qk_rows(w_hf, H).t()).reshape(S, H, hd), tab)
+    assert torch.allclose(q_il[..., 0::2], q_hf[..., :hd // 2], atol=1e-5)
+    assert torch.allclose(q_il[..., 1::2], q_hf[..., hd // 2:], atol=1e-5)
+
+
+def test_time_schedule_and_embedding():
+    ts = R.time_schedule(10)
+    assert ts[0] == 1.0 and abs(ts[-1] - 0.1) < 1e-6 and len(ts) == 10
+    e = R.time_embedding(0.5)
+    assert e.shape == (1024,)
+    # first period is 4e-3: sin(2 pi 0.5 / 4e-3) = sin(250 pi) ~ 0; last period 4.0: sin(pi/4)
+    assert abs(float(e[511]) - np.sin(2 * np.pi * 0.5 / 4.0)) < 1e-5
+    assert abs(float(e[1023]) - np.cos(2 * np.pi * 0.5 / 4.0)) < 1e-5
+
+
+# ------------------------------------------------------------------ formats
+def test_e4m3_and_bf16_conversions_bit_exact_vs_torch():
+    lut = O.e4m3_lut()
+    t = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    assert np.array_equal(np.nan_to_num(lut, nan=999.0), np.nan_to_num(t, nan=999.0))
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(60000, generator=g) * torch.exp(torch.randn(60000, generator=g) * 4)).clamp(-448, 448)
+    mids = torch.tensor([(lut[c] + lut[c + 1]) / 2 for c in range(0, 0x7E)])
+    x = torch.cat([x, mids, -mids, torch.tensor([0.0, -0.0, 448.0, -448.0, 2.0 ** -10, 2.0 ** -9, 1e-30])])
+    assert np.array_equal(O.f32_to_e4m3(x.numpy()), x.to(torch.float8_e4m3fn).view(torch.uint8).numpy())
+    y = torch.randn(100000, generator=g) * torch.exp(torch.randn(100000, generator=g) * 10)
+    assert np.array_equal(O.f32_to_bf16_bits(y.numpy()), y.to(torch.bfloat16).view(torch.uint16).numpy())
+
+
+def test_det_exp_and_gelu_accuracy():
+    L = O.lib()
+    xs = np.linspace(-90, 90, 20001).astype(np.float32)
+    e = np.array([L.orc_det_expf(float(v)) for v in xs], dtype=np.float64)
+    tr = np.exp(np.clip(xs.astype(np.float64), -87, 88))
+    assert (np.abs(e - tr) / tr).max() < 2.0 ** -22
+    gs = np.linspace(-12, 12, 20001).astype(np.float32)
+    gg = np.array([L.orc_det_gelu_tanh(float(v)) for v in gs], dtype=np.float64)
+    tg = torch.nn.functional.gelu(torch.tensor(gs, dtype=torch.float64), approximate="tanh").numpy()
+    assert np.abs(gg - tg).max() < 2e-6
+
+
+# ------------------------------------------------------------------ fused kernels vs plain formulas
+def _bf(rng, shape, scale=1.0):
+    return O.f32_to_bf16_bits((rng.standard_normal(shape) * scale).astype(np.float32))
+
+
+def test_norm_oracle_vs_plain_formula():
+    rng = np.random.default_rng(0)
+    rows, dim = 9, 1024
+    res, x, gate = _bf(rng, (rows, dim)), _bf(rng, (rows, dim), 0.5), _bf(rng, (rows, dim), 0.5)
+    style = _bf(rng, (rows, 3 * dim), 0.3)
+    scale = 0.02
+    r_out, o8, g_out = O.norm(res, x=x, gate_in=gate, gate_in_stride=dim, style=style, style_stride=3 * dim,
+                              out="fp8", want_gate_out=True, scale=scale)
+    rf, xf, gf, sf = (O.bf16_bits_to_f32(a).astype(np.float64) for a in (res, x, gate, style))
+    r = rf + xf * gf
+    assert np.array_equal(r_out, O.f32_to_bf16_bits(r.astype(np.float32)))
+    rb = O.bf16_bits_to_f32(r_out).astype(np.float64)
+    rms = 1.0 / np.sqrt((r ** 2).mean(-1, keepdims=True) + 1e-6)
+    y = rb * rms * (1 + sf[:, :dim]) + sf[:, dim:2 * dim]
+    want = np.clip(y / scale, -448, 448)
+    got = O.e4m3_to_f32(o8).astype(np.float64)
+    # an E4M3 code is at most half a step (2^-4 relative) from the value it encodes
+    assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -4 + 2.0 ** -10).all()
+    assert (np.abs(got - want) > np.abs(want) * 2.0 ** -4 * 0.999 + 2.0 ** -10).sum() == 0
+    assert np.array_equal(g_out, style[:, 2 * dim:])
+    # shared (stride 0) style row == the same row repeated
+    _, o_shared, _ = O.norm(res, style=style[:1], style_stride=0, out="bf16")
+    _, o_rep, _ = O.norm(res, style=np.repeat(style[:1], rows, 0), style_stride=3 * dim, out="bf16")
+    assert np.array_equal(o_shared, o_rep)
+
+
+def test_geglu_quantize_adds_oracle_vs_plain_formula():
+    rng = np.random.default_rng(1)
+    merged = _bf(rng, (5, 2 * 64), 2.0)
+    o16 = O.geglu_bf16(merged)
+    m = torch.from_numpy(O.bf16_bits_to_f32(merged))
+    ref = torch.nn.functional.gelu(m[:, :64].double(), approximate="tanh") * m[:, 64:].double()
+    got = torch.from_numpy(O.bf16_bits_to_f32(o16)).double()
+    assert (got - ref).abs().max() <= ref.abs().max() * 2.0 ** -8
+    x = _bf(rng, (1000,), 3.0)
+    s = O.amax_scale(x)
+    assert s == np.float32(np.abs(O.bf16_bits_to_f32(x)).max() / np.float32(448.0))
+    q = O.quantize_fp8_static(x, s)
+    assert np.array_equal(q, O.f32_to_e4m3(np.clip(O.bf16_bits_to_f32(x) * (np.float32(1.0) / np.float32(s)), -448, 448)))
+    assert O.amax_scale(np.zeros(16, np.uint16)) == np.float32(1e-12)
+    a, b = _bf(rng, (3, 16)), _bf(rng, (3, 16))
+    assert np.array_equal(O.add(a, b, mode=0), O.f32_to_bf16_bits(O.bf16_bits_to_f32(a) + O.bf16_bits_to_f32(b)))
+
+
+def test_rope_split_oracle_vs_torch():
+    rng = np.random.default_rng(2)
+    seq, pos, hd = 6, 3, 256
+    qkv = _bf(rng, (seq, 2048 + 256 + 256))
+    tab = R.rope_table(np.arange(pos, pos + seq)).to(torch.bfloat16)
+    rope = tab.view(torch.uint16).numpy()
+    Kc, Vc = np.zeros((pos + seq, 256), np.uint16), np.zeros((pos + seq, 256), np.uint16)
+    Q = O.qkv_split_rope(qkv, rope, Kc, Vc, pos, 2048, 256, 256, hd)
+    f = torch.from_numpy(O.bf16_bits_to_f32(qkv))
+    q_ref = R.rope_adjacent_pairs(f[:, :2048].reshape(seq, 8, hd), tab.float()).reshape(seq, 2048)
+    k_ref = R.rope_adjacent_pairs(f[:, 2048:2304].reshape(seq, 1, hd), tab.float()).reshape(seq, 256)
+    assert np.abs(O.bf16_bits_to_f32(Q) - q_ref.numpy()).max() <= np.abs(q_ref.numpy()).max() * 2.0 ** -8
+    assert np.abs(O.bf16_bits_to_f32(Kc[pos:]) - k_ref.numpy()).max() <= np.abs(k_ref.numpy()).max() * 2.0 ** -8
+    assert np.array_equal(Vc[pos:], qkv[:, 2304:]) and (Kc[:pos] == 0).all() and (Vc[:pos] == 0).all()
+
+
+def test_gemm_and_attention_oracles_vs_torch():
+    rng = np.random.default_rng(4)
+    A = rng.integers(0, 0x7E, (5, 64)).astype(np.uint8)
+    W = rng.integers(0, 0x7E, (7, 64)).astype(np.uint8)
+    D, Df = O.gemm_fp8(A, W, 0.5, 0.25, b_is_nk=True, want_f32=True)
+    ref = (O.e4m3_to_f32(A).astype(np.float64) @ O.e4m3_to_f32(W).astype(np.float64).T) * 0.125
+    assert np.allclose(Df, ref, rtol=1e-6)
+    D2 = O.gemm_fp8(A, np.ascontiguousarray(W.T), 0.5, 0.25, b_is_nk=False)
+    assert np.array_equal(D, D2)
+    q, k, v = _bf(rng, (1, 5, 8, 64)), _bf(rng, (1, 11, 1, 64)), _bf(rng, (1, 11, 1, 64))
+    out, lse = O.attention(q, k, v, 0.125)
+    tq, tk, tv = (torch.from_numpy(O.bf16_bits_to_f32(a)) for a in (q, k, v))
+    ref = R.attention(tq[0], tk[0], tv[0], 0.125)
+    assert torch.allclose(torch.from_numpy(out[0]), ref, atol=1e-5)
