@@ -15,10 +15,15 @@ namespace frt {
 // serves move < 100 KB; the shape of the grid only has to cover the machine.
 constexpr int SG_COLS = 32, SG_KS = 8, SG_ROWS = 4, SG_KCHUNK = 1024;
 
+template <bool A_F32, bool D_F32>
 __global__ void __launch_bounds__(SG_COLS * SG_KS)
-small_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ B,
-                       __nv_bfloat16* __restrict__ D, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+small_gemm_bf16_kernel(const void* __restrict__ Av, const __nv_bfloat16* __restrict__ B,
+                       void* __restrict__ Dv, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                        int accumulate) {
+    const __nv_bfloat16* A = reinterpret_cast<const __nv_bfloat16*>(Av);
+    const float* Af = reinterpret_cast<const float*>(Av);
+    __nv_bfloat16* D = reinterpret_cast<__nv_bfloat16*>(Dv);
+    float* Df = reinterpret_cast<float*>(Dv);
     __shared__ float a_s[SG_ROWS][SG_KCHUNK];
     __shared__ float part[SG_KS][SG_ROWS][SG_COLS];
     const int tx = threadIdx.x % SG_COLS;
@@ -32,7 +37,10 @@ small_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
         __syncthreads();
         for (int i = threadIdx.x; i < SG_ROWS * kc; i += blockDim.x) {
             const int r = i / kc, k = i - r * kc;
-            a_s[r][k] = (m0 + r < M) ? __bfloat162float(A[(size_t)(m0 + r) * K + k0 + k]) : 0.0f;
+            const size_t ai = (size_t)(m0 + r) * K + k0 + k;
+            // an fp32 operand is rounded to bf16 first: the projection multiplies bf16 by bf16
+            a_s[r][k] = (m0 + r < M) ? (A_F32 ? __bfloat162float(__float2bfloat16_rn(Af[ai])) : __bfloat162float(A[ai]))
+                                     : 0.0f;
         }
         __syncthreads();
         if (n < N) {
@@ -54,8 +62,13 @@ small_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
         for (int q = 0; q < SG_KS; ++q) s += part[q][r][tx];
         if (bias) s += __bfloat162float(bias[n]);
         const size_t o = (size_t)(m0 + r) * N + n;
-        if (accumulate) s += __bfloat162float(D[o]);
-        D[o] = __float2bfloat16_rn(s);
+        if (D_F32) {
+            if (accumulate) s += Df[o];
+            Df[o] = s;
+        } else {
+            if (accumulate) s += __bfloat162float(D[o]);
+            D[o] = __float2bfloat16_rn(s);
+        }
     }
 }
 
@@ -65,8 +78,9 @@ using namespace frt;
 
 extern "C" {
 
+// io: bit0 = A is fp32 (rounded to bf16 on load), bit1 = D is fp32
 int frt_b200_gemm_bf16_nn_small(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
-                                int accumulate, int flags, void* stream) {
+                                int accumulate, int io, int flags, void* stream) {
     if (!A || !B || !D || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
     if (M == 0) return FRT_OK;
     cudaLaunchConfig_t cfg = {};
@@ -78,9 +92,15 @@ int frt_b200_gemm_bf16_nn_small(const void* A, const void* B, void* D, const voi
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & 1) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, small_gemm_bf16_kernel, (const __nv_bfloat16*)A,
-                                       (const __nv_bfloat16*)B, (__nv_bfloat16*)D, (const __nv_bfloat16*)bias, M, N,
-                                       K, accumulate);
+    const __nv_bfloat16* Bp = (const __nv_bfloat16*)B;
+    const __nv_bfloat16* bp = (const __nv_bfloat16*)bias;
+    cudaError_t e;
+    switch (io & 3) {
+        case 0: e = cudaLaunchKernelEx(&cfg, small_gemm_bf16_kernel<false, false>, A, Bp, D, bp, M, N, K, accumulate); break;
+        case 1: e = cudaLaunchKernelEx(&cfg, small_gemm_bf16_kernel<true, false>, A, Bp, D, bp, M, N, K, accumulate); break;
+        case 2: e = cudaLaunchKernelEx(&cfg, small_gemm_bf16_kernel<false, true>, A, Bp, D, bp, M, N, K, accumulate); break;
+        default: e = cudaLaunchKernelEx(&cfg, small_gemm_bf16_kernel<true, true>, A, Bp, D, bp, M, N, K, accumulate); break;
+    }
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
 

@@ -148,10 +148,12 @@ class GemmRunner:
             "fp8_nn_dev (weights stored (K,N)) is not provided: this library keeps FP8 weights K-contiguous "
             "(N,K); use fp8_nt_dev, the reference's own fp8_layout='nk' path (csrc/bindings.cpp:717-727)")
 
-    def bf16_nn(self, A, B, D, M, N, K, stream=0, *, pdl=False, bias=None, accumulate=False):
+    def bf16_nn(self, A, B, D, M, N, K, stream=0, *, pdl=False, bias=None, accumulate=False, a_f32=False,
+                d_f32=False):
         if not (N <= 64 or K <= 64):
             raise NotBuilt("bf16_nn is provided for the 32<->1024 action projections only (N <= 64 or K <= 64)")
-        call("frt_b200_gemm_bf16_nn_small", A, B, D, bias, M, N, K, 1 if accumulate else 0, _f(pdl), stream)
+        call("frt_b200_gemm_bf16_nn_small", A, B, D, bias, M, N, K, 1 if accumulate else 0,
+             (1 if a_f32 else 0) | (2 if d_f32 else 0), _f(pdl), stream)
 
     # the reference measures cuBLASLt algorithms here; nothing to do for a shape-selected kernel
     def autotune_bf16_nn(self, *a, **k):

@@ -1,0 +1,436 @@
+"""Pi0.5 action-expert denoise loop on B200: the frontend (weights -> FP8, conditioning tables, calibration,
+graph capture, ``infer``) and the pointer-only kernel composition it captures.
+
+Host-side mirror of the reference's
+  * ``Pi05TorchFrontendRtx``  (flash_rt/frontends/torch/pi05_rtx.py:456-1614): weight conversion, FP8 weight
+    quantisation (:344-350, :718-762), style precompute (:369-448), calibration (:1312-1463), ``infer`` (:1547-1614)
+  * ``Pi05Pipeline.transformer_decoder`` / ``_decoder_layer`` / ``record_infer_graph`` / ``forward_decode_only``
+    (flash_rt/models/pi05/pipeline_rtx.py:1451-1749, 1980-2049, 2175-2196)
+restricted to the decoder: the prefix keys / values that the vision tower and the Gemma-2B encoder would leave
+in the per-layer KV cache are an input (``set_prefix``).
+
+What differs from the reference's composition (same arithmetic, fewer launches and bytes):
+  * conditioning rows are stored once per (step, layer) and read with row stride 0 instead of being expanded to
+    one copy per action token; the gate of the next residual is read straight from the style row;
+  * the attention kernel also emits the FP8 copy the output projection reads (no separate quantise launch);
+  * FP8 weights are (N, K) K-contiguous (``fp8_nt_dev``);
+  * the action out-projection adds its bias and accumulates into the noise buffer in the same launch, and that
+    Euler state is held in fp32 (the reference keeps it in bf16, whose half-ulp at |x| ~ 4 is already 0.016);
+  * kernels are chained with programmatic dependent launch inside the captured graph.
+PyTorch only provides device memory, streams and graph capture here.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from . import flash_rt_fa2 as fa2
+from . import flash_rt_kernels as fvk
+from .weight_loader import (Attr, DictSource, FlatCat, FusedGateUp, FusedQKV, Item, LayerBlock, ModelWeightSpec,
+                            Quant, SafetensorsSource, Scale, TensorList, ToBf16, WeightLoader, tT)
+
+DEC_D, DEC_H, DEC_NH, DEC_NKV, DEC_HD, DEC_L = 1024, 4096, 8, 1, 256, 18
+ACTION_DIM = 32
+NUM_STEPS_DEFAULT = 10
+CHUNK_DEFAULT = 50
+BF16 = torch.bfloat16
+
+
+# ------------------------------------------------------------------ weight spec (plugin contract)
+def build_spec(layers: int = DEC_L, num_steps: int = NUM_STEPS_DEFAULT) -> ModelWeightSpec:
+    """HF key names of the Gemma expert and the action heads (pi05_rtx.py:216-283)."""
+    dp = "paligemma_with_expert.gemma_expert.model.layers.{i}"
+    dec = LayerBlock(prefix_fmt="", num_layers=layers, name="decoder", items=[
+        Item("qkv_w", FusedQKV(q=f"{dp}.self_attn.q_proj.weight", k=f"{dp}.self_attn.k_proj.weight",
+                               v=f"{dp}.self_attn.v_proj.weight", interleave_q_heads=DEC_NH,
+                               interleave_k_heads=DEC_NKV),
+             [Quant()], FlatCat("w_qkv"), scale_into="ws_qkv"),
+        Item("o_w", f"{dp}.self_attn.o_proj.weight", [Quant()], FlatCat("w_o"), scale_into="ws_o"),
+        Item("gu_w", FusedGateUp(gate=f"{dp}.mlp.gate_proj.weight", up=f"{dp}.mlp.up_proj.weight"),
+             [Quant()], FlatCat("w_gu"), scale_into="ws_gu"),
+        Item("d_w", f"{dp}.mlp.down_proj.weight", [Quant()], FlatCat("w_d"), scale_into="ws_d"),
+    ])
+    mods = LayerBlock(prefix_fmt="", num_layers=layers, name="decoder_mods", items=[
+        Item("attn_mod_w", f"{dp}.input_layernorm.dense.weight", [tT(), ToBf16()], TensorList("attn_mod_w")),
+        Item("attn_mod_b", f"{dp}.input_layernorm.dense.bias", [ToBf16()], TensorList("attn_mod_b")),
+        Item("ffn_mod_w", f"{dp}.post_attention_layernorm.dense.weight", [tT(), ToBf16()], TensorList("ffn_mod_w")),
+        Item("ffn_mod_b", f"{dp}.post_attention_layernorm.dense.bias", [ToBf16()], TensorList("ffn_mod_b")),
+    ])
+    fin = "paligemma_with_expert.gemma_expert.model.norm.dense"
+    singles = [
+        Item("final_mod_w", f"{fin}.weight", [tT(), ToBf16()], Attr("final_mod_w")),
+        Item("final_mod_b", f"{fin}.bias", [ToBf16()], Attr("final_mod_b")),
+        Item("time_in_w", "time_mlp_in.weight", [tT(), ToBf16()], Attr("time_in_w")),
+        Item("time_in_b", "time_mlp_in.bias", [ToBf16()], Attr("time_in_b")),
+        Item("time_out_w", "time_mlp_out.weight", [tT(), ToBf16()], Attr("time_out_w")),
+        Item("time_out_b", "time_mlp_out.bias", [ToBf16()], Attr("time_out_b")),
+        Item("action_in_w", "action_in_proj.weight", [tT(), ToBf16()], Attr("action_in_w")),       # (32, D)
+        Item("action_in_b", "action_in_proj.bias", [ToBf16()], Attr("action_in_b")),
+        # x <- x + dt * v with dt = -1/N is folded into the out-projection (pi05_rtx.py:587-593)
+        Item("action_out_w", "action_out_proj.weight", [tT(), ToBf16(), Scale(-1.0 / num_steps), ToBf16()],
+             Attr("action_out_w")),                                                                # (D, 32)
+        Item("action_out_b", "action_out_proj.bias", [ToBf16(), Scale(-1.0 / num_steps), ToBf16()],
+             Attr("action_out_b")),
+    ]
+    return ModelWeightSpec(framework="torch", blocks=[dec, mods], singletons=singles,
+                           dims={"D": DEC_D, "H": DEC_H, "L": layers})
+
+
+def synthetic_state_dict(seed: int = 0, layers: int = DEC_L) -> dict:
+    """Random-init checkpoint with the HF key names and shapes of the Pi0.5 action expert
+    (matrices ~ N(0, 0.02), biases zero) — stands in for a trained checkpoint, which this build cannot reach."""
+    g = torch.Generator().manual_seed(seed)
+
+    def w(*shape):
+        return torch.randn(*shape, generator=g) * 0.02
+
+    sd = {}
+    for i in range(layers):
+        p = f"paligemma_with_expert.gemma_expert.model.layers.{i}"
+        sd[f"{p}.self_attn.q_proj.weight"] = w(DEC_NH * DEC_HD, DEC_D)
+        sd[f"{p}.self_attn.k_proj.weight"] = w(DEC_NKV * DEC_HD, DEC_D)
+        sd[f"{p}.self_attn.v_proj.weight"] = w(DEC_NKV * DEC_HD, DEC_D)
+        sd[f"{p}.self_attn.o_proj.weight"] = w(DEC_D, DEC_NH * DEC_HD)
+        sd[f"{p}.mlp.gate_proj.weight"] = w(DEC_H, DEC_D)
+        sd[f"{p}.mlp.up_proj.weight"] = w(DEC_H, DEC_D)
+        sd[f"{p}.mlp.down_proj.weight"] = w(DEC_D, DEC_H)
+        sd[f"{p}.input_layernorm.dense.weight"] = w(3 * DEC_D, DEC_D)
+        sd[f"{p}.input_layernorm.dense.bias"] = torch.zeros(3 * DEC_D)
+        sd[f"{p}.post_attention_layernorm.dense.weight"] = w(3 * DEC_D, DEC_D)
+        sd[f"{p}.post_attention_layernorm.dense.bias"] = torch.zeros(3 * DEC_D)
+    sd["paligemma_with_expert.gemma_expert.model.norm.dense.weight"] = w(3 * DEC_D, DEC_D)
+    sd["paligemma_with_expert.gemma_expert.model.norm.dense.bias"] = torch.zeros(3 * DEC_D)
+    sd["time_mlp_in.weight"], sd["time_mlp_in.bias"] = w(DEC_D, DEC_D), torch.zeros(DEC_D)
+    sd["time_mlp_out.weight"], sd["time_mlp_out.bias"] = w(DEC_D, DEC_D), torch.zeros(DEC_D)
+    sd["action_in_proj.weight"], sd["action_in_proj.bias"] = w(DEC_D, ACTION_DIM), torch.zeros(DEC_D)
+    sd["action_out_proj.weight"], sd["action_out_proj.bias"] = w(ACTION_DIM, DEC_D), torch.zeros(ACTION_DIM)
+    return sd
+
+
+# ------------------------------------------------------------------ conditioning tables (load time, host)
+def _bf(t: torch.Tensor) -> torch.Tensor:
+    return t.to(BF16).float()
+
+
+def precompute_styles(fe, num_steps: int, layers: int):
+    """Time embedding -> time MLP (SiLU in fp32) -> per-norm modulation rows [scale | shift | gate], with the
+    reference's bf16 rounding points (pi05_rtx.py:394-437).  Returns bf16 tensors (N, L, 3D), (N, L, 3D), (N, 3D)."""
+    dt = torch.tensor(-1.0 / num_steps, dtype=torch.float32)
+    t = torch.tensor(1.0, dtype=torch.float32)
+    fraction = torch.linspace(0.0, 1.0, DEC_D // 2, dtype=torch.float32)
+    period = 4e-3 * (4.0 / 4e-3) ** fraction
+    sa = torch.empty(num_steps, layers, 3 * DEC_D)
+    sf = torch.empty(num_steps, layers, 3 * DEC_D)
+    fin = torch.empty(num_steps, 3 * DEC_D)
+    silu = lambda z: z * torch.sigmoid(z)  # noqa: E731
+    for s in range(num_steps):
+        sinus = t * (1.0 / period) * 2 * math.pi
+        te = _bf(torch.cat([torch.sin(sinus), torch.cos(sinus)], dim=-1))
+        h = _bf(_bf(te @ fe.time_in_w.float()) + fe.time_in_b.float())
+        h = _bf(silu(h))
+        h = _bf(_bf(h @ fe.time_out_w.float()) + fe.time_out_b.float())
+        c = _bf(silu(h))
+        for i in range(layers):
+            sa[s, i] = _bf(_bf(c @ fe.attn_mod_w[i].float()) + fe.attn_mod_b[i].float())
+            sf[s, i] = _bf(_bf(c @ fe.ffn_mod_w[i].float()) + fe.ffn_mod_b[i].float())
+        fin[s] = _bf(_bf(c @ fe.final_mod_w.float()) + fe.final_mod_b.float())
+        t = t + dt
+    return sa.to(BF16), sf.to(BF16), fin.to(BF16)
+
+
+def rope_table(start: int, count: int) -> torch.Tensor:
+    """bf16 (count, 256) rows [cos0, sin0, cos1, sin1, ...] for positions start .. start+count-1, theta 10000,
+    phases in fp64 (pipeline_rtx.py:473-505)."""
+    inv_freq = 1.0 / (10000 ** (np.arange(0, DEC_HD, 2, dtype=np.float64) / DEC_HD))
+    phase = np.arange(start, start + count, dtype=np.float64)[:, None] * inv_freq[None, :]
+    tab = np.stack([np.cos(phase), np.sin(phase)], axis=-1).reshape(count, DEC_HD)
+    return torch.from_numpy(tab.astype(np.float32)).to(BF16)
+
+
+# ------------------------------------------------------------------ kernel composition
+SITES = ("qkv", "o", "gu", "d")
+
+
+class Pi05DecoderPipeline:
+    """Pointer-only composition of the denoise loop (what gets captured in the graph)."""
+
+    def __init__(self, fe: "Pi05DecoderB200"):
+        self.fe = fe
+        self.gemm = fvk.GemmRunner()
+        dev = fe.device
+        S, L, N = fe.chunk_size, fe.layers, fe.num_steps
+        z = lambda *shape, dtype=BF16: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
+        self.noise = z(S, ACTION_DIM, dtype=torch.float32)   # Euler state, kept in fp32 across the steps
+        self.x = z(S, DEC_D)
+        self.xn = z(S, DEC_D)
+        self.h_bf16 = z(S, DEC_D)                      # calibration only: un-quantised norm output
+        self.qkv = z(S, (DEC_NH + 2 * DEC_NKV) * DEC_HD)
+        self.q = z(S, DEC_NH * DEC_HD)
+        self.attn = z(S, DEC_NH * DEC_HD)
+        self.merged = z(S, 2 * DEC_H)
+        self.hidden = z(S, DEC_H)                      # calibration only
+        self.act8 = z(S, DEC_D, dtype=torch.uint8)
+        self.attn8 = z(S, DEC_NH * DEC_HD, dtype=torch.uint8)
+        self.hid8 = z(S, DEC_H, dtype=torch.uint8)
+        self.ones = torch.ones(DEC_D, dtype=BF16, device=dev)
+        # activation scales: one per GEMM input site, per layer, per denoise step (pipeline_rtx.py:649-660)
+        self.act_scale = torch.ones(N, L, len(SITES), dtype=torch.float32, device=dev)
+        self.scratch_scale = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.calibrated = False
+
+    # ---- small helpers -------------------------------------------------
+    def _scale_ptr(self, step, layer, site):
+        return self.act_scale[step, layer, SITES.index(site)].data_ptr()
+
+    def _style(self, which, step, layer=None):
+        fe = self.fe
+        t = {"attn": fe.style_attn, "ffn": fe.style_ffn, "final": fe.style_final}[which]
+        row = t[step] if layer is None else t[step, layer]
+        return row.data_ptr()
+
+    def _gemm(self, a8, w8, wscale, out, M, N, K, ascale_ptr, stream, pdl):
+        self.gemm.fp8_nt_dev(a8.data_ptr(), w8.data_ptr(), out.data_ptr(), M, N, K, ascale_ptr, wscale.data_ptr(),
+                             stream, pdl=pdl)
+
+    def _attention(self, layer, stream, pdl, out8_scale_ptr):
+        fe = self.fe
+        S, T = fe.chunk_size, fe.prefix_len + fe.chunk_size
+        qs = (S * DEC_NH * DEC_HD, DEC_NH * DEC_HD, DEC_HD)
+        ks = (fe.kv_rows * DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD)
+        fa2.fwd_bf16(self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
+                     self.attn.data_ptr(), 0, 0, 0, 1, S, T, DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
+                     1.0 / math.sqrt(DEC_HD), fe.sm_count, stream, pdl=pdl,
+                     out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0, out_scale=out8_scale_ptr or 0)
+
+    # ---- the loop --------------------------------------------------------
+    def transformer_decoder(self, stream: int = 0, calibrate: bool = False, step_hook=None) -> None:
+        """Run the N-step denoise on ``self.noise`` in place (pipeline_rtx.py:1451-1504).
+
+        ``calibrate=True`` is the eager dynamic-scale pass: every FP8 input is produced in bf16, its
+        amax / 448 is measured on the device and folded (max) into the per-site per-step scale table.
+        ``step_hook(step)`` (eager runs only) is called after each Euler step, e.g. to snapshot the state."""
+        fe, g = self.fe, self.gemm
+        S, L = fe.chunk_size, fe.layers
+        pdl = fe.use_pdl and not calibrate
+        for step in range(fe.num_steps):
+            # C0: action tokens -> width D, + bias
+            g.bf16_nn(self.noise.data_ptr(), fe.action_in_w.data_ptr(), self.x.data_ptr(), S, DEC_D, ACTION_DIM,
+                      stream, pdl=pdl, bias=fe.action_in_b.data_ptr(), a_f32=True)
+            for i in range(L):
+                # C1: adaRMS(style_attn) -> FP8 (layer 0 only; later layers get it from C7 of the previous one)
+                if i == 0:
+                    self._norm(None, None, "attn", step, i, "qkv", stream, pdl, calibrate)
+                # C2: QKV projection, split + RoPE, K/V appended behind the prefix
+                self._gemm(self.act8, fe.w_qkv[i], fe.ws_qkv_t[i], self.qkv, S, 2560, DEC_D,
+                           self._scale_ptr(step, i, "qkv"), stream, pdl)
+                fvk.qkv_split_rope(self.qkv.data_ptr(), fe.rope.data_ptr(), self.q.data_ptr(),
+                                   fe.k_cache[i, fe.prefix_len:].data_ptr(), fe.v_cache[i, fe.prefix_len:].data_ptr(),
+                                   S, DEC_NH * DEC_HD, DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
+                # C3 + C4: attention (FP8 copy fused), output projection
+                if calibrate:
+                    self._attention(i, stream, False, 0)
+                    self._dyn_quant(self.attn, self.attn8, step, i, "o", stream)
+                else:
+                    self._attention(i, stream, pdl, self._scale_ptr(step, i, "o"))
+                self._gemm(self.attn8, fe.w_o[i], fe.ws_o_t[i], self.xn, S, DEC_D, DEC_NH * DEC_HD,
+                           self._scale_ptr(step, i, "o"), stream, pdl)
+                # C5: x += o * gate_attn ; adaRMS(style_ffn) -> FP8 ; gate|up projection
+                self._norm(self.xn, ("attn", step, i), "ffn", step, i, "gu", stream, pdl, calibrate)
+                self._gemm(self.act8, fe.w_gu[i], fe.ws_gu_t[i], self.merged, S, 2 * DEC_H, DEC_D,
+                           self._scale_ptr(step, i, "gu"), stream, pdl)
+                # C6: GeGLU -> FP8 ; down projection
+                if calibrate:
+                    fvk.gate_geglu_merged(self.merged.data_ptr(), self.hidden.data_ptr(), S, DEC_H, stream)
+                    self._dyn_quant(self.hidden, self.hid8, step, i, "d", stream)
+                else:
+                    fvk.gate_geglu_merged_fp8(self.merged.data_ptr(), self.hid8.data_ptr(), S, DEC_H,
+                                              self._scale_ptr(step, i, "d"), stream, pdl=pdl)
+                self._gemm(self.hid8, fe.w_d[i], fe.ws_d_t[i], self.xn, S, DEC_D, DEC_H,
+                           self._scale_ptr(step, i, "d"), stream, pdl)
+                # C7: x += f * gate_ffn ; next layer's adaRMS(style_attn) -> FP8
+                if i < L - 1:
+                    self._norm(self.xn, ("ffn", step, i), "attn", step, i + 1, "qkv", stream, pdl, calibrate)
+                else:
+                    fvk.call("frt_b200_gate_mul_residual", self.x.data_ptr(), self.xn.data_ptr(),
+                             self._style("ffn", step, i) + 2 * DEC_D * 2, 0, S, DEC_D, 1 if pdl else 0, stream)
+            # C8: final adaRMS (bf16), out-projection (+bias, pre-scaled by -1/N) accumulated into the noise
+            fvk.ada_rms_norm_style(self.x.data_ptr(), self.ones.data_ptr(), self._style("final", step),
+                                   self.xn.data_ptr(), 0, S, DEC_D, 1e-6, stream, pdl=pdl, style_stride=0)
+            g.bf16_nn(self.xn.data_ptr(), fe.action_out_w.data_ptr(), self.noise.data_ptr(), S, ACTION_DIM, DEC_D,
+                      stream, pdl=pdl, bias=fe.action_out_b.data_ptr(), accumulate=True, d_f32=True)
+            if step_hook is not None:
+                step_hook(step)
+
+    def _norm(self, delta, gate_from, style_kind, step, layer, site, stream, pdl, calibrate):
+        """(x += delta * gate) ; adaRMS(style) -> FP8 for GEMM site ``site`` of ``layer``."""
+        S = self.fe.chunk_size
+        style = self._style(style_kind, step, layer)
+        gate = (self._style(*gate_from) + 2 * DEC_D * 2) if gate_from else None
+        if not calibrate:
+            fvk.call("frt_b200_norm_fp8", self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                     gate, 0, None, style, 0, self.act8.data_ptr(), None, S, DEC_D, 1e-6,
+                     self._scale_ptr(step, layer, site), 1 if pdl else 0, stream)
+            return
+        fvk.call("frt_b200_norm_bf16", self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                 gate, 0, None, style, 0, self.h_bf16.data_ptr(), None, S, DEC_D, 1e-6, 0, stream)
+        self._dyn_quant(self.h_bf16, self.act8, step, layer, site, stream)
+
+    def _dyn_quant(self, src, dst8, step, layer, site, stream):
+        """Dynamic quantisation used while calibrating (pipeline_rtx.py:804-821): scale of this call into the
+        scratch word, running max into the table; the GEMM of this pass then reads the table entry."""
+        fvk.quantize_fp8_device(src.data_ptr(), dst8.data_ptr(), self.scratch_scale.data_ptr(), src.numel(), stream)
+        fvk.fp8_accumulate_scale_max(self.scratch_scale.data_ptr(), self._scale_ptr(step, layer, site), stream)
+        # quantise again with the accumulated scale so that codes and GEMM scale agree
+        fvk.quantize_fp8_static(src.data_ptr(), dst8.data_ptr(), self._scale_ptr(step, layer, site), src.numel(),
+                                stream)
+
+
+class Pi05DecoderB200:
+    """Decoder-only Pi0.5 frontend for B200 (duck type of the reference frontends: ``infer``, ``calibrate``,
+    ``calibrated``; ``set_prefix`` takes the place of ``set_prompt`` because the prefix producer is not part of
+    this path)."""
+
+    WEIGHT_SPEC = None  # built per instance (layer count / step count are constructor arguments)
+
+    def __init__(self, checkpoint, *, num_steps: int = NUM_STEPS_DEFAULT, chunk_size: int = CHUNK_DEFAULT,
+                 prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
+                 use_cuda_graph: bool = True, **_ignored):
+        if not torch.cuda.is_available():
+            raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        torch.cuda.set_device(self.device)
+        if fvk.get_sm_version() != 100:
+            raise RuntimeError(f"flashrt_b200 is built for sm_100a only; device reports sm_{fvk.get_sm_version()}")
+        self.num_steps, self.chunk_size, self.prefix_len, self.layers = num_steps, chunk_size, prefix_len, layers
+        self.use_pdl, self.use_cuda_graph = use_pdl, use_cuda_graph
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.kv_rows = prefix_len + chunk_size
+        self.WEIGHT_SPEC = build_spec(layers, num_steps)
+        if isinstance(checkpoint, dict):
+            source = DictSource(checkpoint)
+        elif isinstance(checkpoint, str) and checkpoint.startswith("synthetic"):
+            seed = int(checkpoint.split(":")[1]) if ":" in checkpoint else 0
+            source = DictSource(synthetic_state_dict(seed, layers))
+        else:
+            source = SafetensorsSource(str(checkpoint))
+        WeightLoader(source, target=self, spec=self.WEIGHT_SPEC).run()
+        dev = self.device
+        # FP8 weights as raw bytes on the device, (L, N, K)
+        for n in ("w_qkv", "w_o", "w_gu", "w_d"):
+            setattr(self, n, getattr(self, n).view(torch.uint8).to(dev))
+        for n in ("ws_qkv", "ws_o", "ws_gu", "ws_d"):
+            setattr(self, n + "_t", torch.tensor(getattr(self, n), dtype=torch.float32, device=dev))
+        sa, sf, fin = precompute_styles(self, num_steps, layers)
+        self.style_attn, self.style_ffn, self.style_final = sa.to(dev), sf.to(dev), fin.to(dev)
+        for n in ("action_in_w", "action_in_b", "action_out_w", "action_out_b"):
+            setattr(self, n, getattr(self, n).contiguous().to(dev))
+        self.rope = rope_table(prefix_len, chunk_size).to(dev)
+        self.k_cache = torch.zeros(layers, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.pipeline = Pi05DecoderPipeline(self)
+        self.stream = torch.cuda.Stream(device=dev)
+        self.graph = None
+        self._pinned_in = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32).pin_memory()
+        self._pinned_out = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32).pin_memory()
+        self._dev_in = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32, device=dev)
+        self._dev_out = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32, device=dev)
+        self.latency_records: list[float] = []
+
+    # ---- prefix (what the encoder would have written) ---------------------
+    def set_prefix(self, prefix_k: torch.Tensor, prefix_v: torch.Tensor) -> None:
+        """prefix_k / prefix_v: (layers, prefix_len, 256); K already carries its RoPE, as in the encoder's cache."""
+        assert prefix_k.shape == (self.layers, self.prefix_len, DEC_NKV * DEC_HD), prefix_k.shape
+        self.k_cache[:, :self.prefix_len].copy_(prefix_k.to(BF16))
+        self.v_cache[:, :self.prefix_len].copy_(prefix_v.to(BF16))
+        torch.cuda.synchronize(self.device)
+
+    # ---- calibration --------------------------------------------------------
+    @property
+    def calibrated(self) -> bool:
+        return self.pipeline.calibrated
+
+    def calibrate(self, noises, percentile: float | None = None) -> None:
+        """Static per-tensor activation scales from ``noises`` (list of (chunk, 32) tensors).  Each sample runs
+        the eager dynamic-scale pass; the table keeps the max over samples (``percentile`` None) or the given
+        percentile of the per-sample scales (flash_rt/core/calibration.py:38-64)."""
+        p = self.pipeline
+        per_sample = []
+        with torch.cuda.stream(self.stream):
+            for nz in noises:
+                p.act_scale.zero_()
+                p.noise.copy_(nz.to(self.device, torch.float32))
+                p.transformer_decoder(self.stream.cuda_stream, calibrate=True)
+                self.stream.synchronize()
+                per_sample.append(p.act_scale.clone())
+            stack = torch.stack(per_sample, 0)
+            if percentile is None:
+                p.act_scale.copy_(stack.max(0).values)
+            else:
+                p.act_scale.copy_(torch.quantile(stack, percentile / 100.0, dim=0))
+            p.act_scale.clamp_(min=1e-12)
+        self.stream.synchronize()
+        if fvk.tensor_core_status() != 0:
+            raise RuntimeError("a tensor-core kernel reported a timed-out wait during calibration")
+        p.calibrated = True
+        self.graph = None
+
+    # ---- graph --------------------------------------------------------------
+    def record_infer_graph(self) -> None:
+        """Warm up, then capture the input copy, the whole N-step loop and the output copy as one graph
+        (pipeline_rtx.py:1980-2049)."""
+        if not self.calibrated:
+            raise RuntimeError("calibrate() first: the captured loop uses static activation scales")
+        p = self.pipeline
+        s = self.stream
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._enqueue(s)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s, capture_error_mode="relaxed"):
+                self._enqueue(s)
+        s.synchronize()
+        self.graph = g
+
+    def _enqueue(self, s) -> None:
+        p = self.pipeline
+        p.noise.copy_(self._dev_in)
+        p.transformer_decoder(s.cuda_stream, calibrate=False)
+        self._dev_out.copy_(p.noise)
+
+    def forward_decode_only(self) -> None:
+        """Replay the captured loop on the frontend's stream (pipeline_rtx.py:2175-2196)."""
+        if self.graph is None:
+            if self.use_cuda_graph:
+                self.record_infer_graph()
+            else:
+                with torch.cuda.stream(self.stream):
+                    self._enqueue(self.stream)
+                return
+        with torch.cuda.stream(self.stream):
+            self.graph.replay()
+
+    # ---- public call ------------------------------------------------------------
+    def infer(self, obs: dict) -> dict:
+        """obs["noise"]: (chunk, 32) array or tensor on the HOST (a fresh N(0,1) draw if absent).  Uploads it,
+        replays the loop, downloads the actions (pi05_rtx.py:1547-1614)."""
+        nz = obs.get("noise") if obs else None
+        if nz is None:
+            nz = torch.randn(self.chunk_size, ACTION_DIM)
+        nz = torch.as_tensor(nz, dtype=torch.float32)
+        self._pinned_in.copy_(nz)
+        with torch.cuda.stream(self.stream):
+            self._dev_in.copy_(self._pinned_in, non_blocking=True)
+        self.forward_decode_only()
+        with torch.cuda.stream(self.stream):
+            self._pinned_out.copy_(self._dev_out, non_blocking=True)
+        self.stream.synchronize()
+        return {"actions": self._pinned_out.numpy().copy()}
+
+    def kernels_per_loop(self) -> int:
+        """Launches of this library's kernels inside one replay (for reporting)."""
+        L, N = self.layers, self.num_steps
+        per_layer = 9  # qkv gemm, rope split, attention, o gemm, norm, gate|up gemm, geglu, down gemm, norm
+        return N * (1 + 1 + per_layer * L + 2)

@@ -132,9 +132,11 @@ int frt_b200_attention_status(int reset);
 
 /* ---------------------------------------------------------------- small bf16 projections, copies, queries
  * GemmRunner::bf16_nn          csrc/bindings.cpp:662-667  (action in/out projections 32 <-> 1024)
- *   D(M,N) bf16 = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate != 0); B row-major (K,N). */
+ *   D(M,N) = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate != 0); B bf16 row-major (K,N).
+ *   io bit0: A is fp32 (each element rounded to bf16 on load) instead of bf16; io bit1: D is fp32 instead of
+ *   bf16 (lets the Euler state x <- x + dt*v stay in fp32 across the denoise steps). */
 int frt_b200_gemm_bf16_nn_small(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
-                                int accumulate, int flags, void* stream);
+                                int accumulate, int io, int flags, void* stream);
 /* gpu_copy                     csrc/bindings.cpp:2533-2537  (device-to-device, async on stream) */
 int frt_b200_copy(void* dst, const void* src, long long nbytes, void* stream);
 /* get_sm_version               csrc/bindings.cpp:2447-2453  (returns major*10+minor, 100 on B200) */

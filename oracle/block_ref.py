@@ -249,3 +249,39 @@ def denoise_loop(noise, ckpt: dict, prefix_k, prefix_v, num_steps: int = 10, lay
         x_act = x_act + dt * v
         traj.append(x_act.clone())
     return (x_act, traj) if return_trajectory else x_act
+
+
+# ------------------------------------------------------------------ HF state dict -> kernel-layout dictionary
+def from_hf_state_dict(sd: dict, layers: int = DEC_L) -> dict:
+    """Restates the decoder part of the reference's checkpoint conversion (pi05_rtx.py:216-283): projections
+    transposed to [K, N], q / k output rows interleaved for adjacent-pair RoPE, q|k|v concatenated."""
+    dp = "paligemma_with_expert.gemma_expert.model.layers"
+    f = lambda k: sd[k].float()  # noqa: E731
+    qkv, o, gate, up, down, amw, amb, fmw, fmb = ([] for _ in range(9))
+    for i in range(layers):
+        q = interleave_qk_rows(f(f"{dp}.{i}.self_attn.q_proj.weight"), DEC_NH)
+        k = interleave_qk_rows(f(f"{dp}.{i}.self_attn.k_proj.weight"), DEC_NKV)
+        v = f(f"{dp}.{i}.self_attn.v_proj.weight")
+        qkv.append(torch.cat([q, k, v], dim=0).t())
+        o.append(f(f"{dp}.{i}.self_attn.o_proj.weight").t())
+        gate.append(f(f"{dp}.{i}.mlp.gate_proj.weight").t())
+        up.append(f(f"{dp}.{i}.mlp.up_proj.weight").t())
+        down.append(f(f"{dp}.{i}.mlp.down_proj.weight").t())
+        amw.append(f(f"{dp}.{i}.input_layernorm.dense.weight").t())
+        amb.append(f(f"{dp}.{i}.input_layernorm.dense.bias"))
+        fmw.append(f(f"{dp}.{i}.post_attention_layernorm.dense.weight").t())
+        fmb.append(f(f"{dp}.{i}.post_attention_layernorm.dense.bias"))
+    st = torch.stack
+    fin = "paligemma_with_expert.gemma_expert.model.norm.dense"
+    return {
+        "decoder_attn_qkv_w": st(qkv), "decoder_attn_o_w": st(o), "decoder_ffn_gate_w": st(gate),
+        "decoder_ffn_up_w": st(up), "decoder_ffn_down_w": st(down),
+        "decoder_pre_attn_norm_mod_w": st(amw), "decoder_pre_attn_norm_mod_b": st(amb),
+        "decoder_pre_ffn_norm_mod_w": st(fmw), "decoder_pre_ffn_norm_mod_b": st(fmb),
+        "decoder_final_norm_mod_w": f(f"{fin}.weight").t(), "decoder_final_norm_mod_b": f(f"{fin}.bias"),
+        "decoder_time_mlp_in_w": f("time_mlp_in.weight").t(), "decoder_time_mlp_in_b": f("time_mlp_in.bias"),
+        "decoder_time_mlp_out_w": f("time_mlp_out.weight").t(), "decoder_time_mlp_out_b": f("time_mlp_out.bias"),
+        "decoder_action_in_proj_w": f("action_in_proj.weight").t(), "decoder_action_in_proj_b": f("action_in_proj.bias"),
+        "decoder_action_out_proj_w": f("action_out_proj.weight").t(),
+        "decoder_action_out_proj_b": f("action_out_proj.bias"),
+    }

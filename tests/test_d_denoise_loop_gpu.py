@@ -1,0 +1,89 @@
+"""GPU parity of the whole path: the FP8 action-expert denoise loop (eager and as one CUDA graph, through
+``load_model(...).predict(...)``) against the fp32 torch oracle on identical seeded weights, prefix KV and noise.
+Bar (stated by the task): cosine >= 0.999 and max-abs <= 2e-2 x RMS of the reference output, per denoise step and
+after the full loop."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import block_ref as R  # noqa: E402
+
+
+def _cos(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(a @ b / (a.norm() * b.norm()))
+
+
+@pytest.fixture(scope="module")
+def small_model():
+    """4 layers keep the CPU oracle to a few seconds; the 18-layer shape is covered below."""
+    from flashrt_b200 import load_model
+    from flashrt_b200.pi05_decoder import synthetic_state_dict
+    L = 4
+    sd = synthetic_state_dict(seed=0, layers=L)
+    model = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768)
+    pk, pv = R.synthetic_prefix_kv(seed=1, layers=L, prefix_len=768)
+    pk_b, pv_b = pk.to(torch.bfloat16), pv.to(torch.bfloat16)
+    model.set_prefix(pk_b, pv_b)
+    model.calibrate([R.synthetic_noise(100 + j) for j in range(8)])
+    ck = R.from_hf_state_dict({k: v.to(torch.bfloat16).float() for k, v in sd.items()}, layers=L)
+    return dict(model=model, ck=ck, pk=pk_b.float(), pv=pv_b.float(), L=L)
+
+
+def test_loop_matches_fp32_oracle_per_step_and_final(small_model):
+    m = small_model
+    fe = m["model"].frontend
+    noise = R.synthetic_noise(1)
+    noise_b = noise.to(torch.bfloat16).float()
+    ref_final, ref_traj = R.denoise_loop(noise_b, m["ck"], m["pk"], m["pv"], num_steps=10, layers=m["L"],
+                                         return_trajectory=True)
+    # eager run with a snapshot after every Euler step
+    p = fe.pipeline
+    snaps = []
+    with torch.cuda.stream(fe.stream):
+        p.noise.copy_(noise_b.to(fe.device))
+        p.transformer_decoder(fe.stream.cuda_stream, calibrate=False,
+                              step_hook=lambda s: snaps.append(p.noise.float().clone()))
+    fe.stream.synchronize()
+    from flashrt_b200 import flash_rt_kernels as fvk
+    assert fvk.tensor_core_status() == 0
+    for s, (got, ref) in enumerate(zip(snaps, ref_traj)):
+        got = got.cpu()
+        rms = float(ref.pow(2).mean().sqrt())
+        assert _cos(got, ref) >= 0.999, f"step {s}"
+        assert float((got - ref).abs().max()) <= 2e-2 * rms, f"step {s}"
+    # the captured graph through the public API gives the same numbers as the eager run
+    out = m["model"].predict(noise=noise_b.numpy())
+    assert np.array_equal(out, snaps[-1].cpu().numpy())
+    out2 = m["model"].predict(noise=noise_b.numpy())
+    assert np.array_equal(out, out2)                       # replay is deterministic
+    assert _cos(torch.from_numpy(out), ref_final) >= 0.999
+
+
+def test_full_depth_loop_runs_and_is_finite():
+    """18 layers, 10 steps, one graph: finite output, unit-scale actions, deterministic replays."""
+    from flashrt_b200 import load_model
+    model = load_model("synthetic:0", config="pi05")
+    pk, pv = R.synthetic_prefix_kv(seed=1)
+    model.set_prefix(pk, pv)
+    model.calibrate([R.synthetic_noise(100 + j) for j in range(2)])
+    noise = R.synthetic_noise(1).numpy()
+    a = model.predict(noise=noise)
+    b = model.predict(noise=noise)
+    assert a.shape == (50, 32) and np.isfinite(a).all()
+    assert np.array_equal(a, b)
+    assert 0.05 < float(np.abs(a).mean()) < 50
+    assert model.frontend.kernels_per_loop() == 10 * (2 + 9 * 18 + 2)
+
+
+def test_refuses_wrong_inputs():
+    from flashrt_b200 import load_model
+    with pytest.raises(ValueError):
+        load_model("synthetic", framework="jax")
+    with pytest.raises(ValueError):
+        load_model("synthetic", config="groot")
+    m = load_model("synthetic:0", config="pi05", layers=1)
+    with pytest.raises(RuntimeError):
+        m.predict(noise=np.zeros((50, 32), np.float32))     # not calibrated
