@@ -171,11 +171,11 @@ def run_ours(args):
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import ACTION_DIM
     gsd = torch.Generator().manual_seed(1)
-    model = load_model("synthetic:0", config="pi05", device=local)
+    model = load_model("synthetic:0", config="pi05", device=local, use_pdl=not args.no_pdl)
     fe = model.frontend
     L, P = fe.layers, fe.prefix_len
     model.set_prefix(torch.randn(L, P, 256, generator=gsd), torch.randn(L, P, 256, generator=gsd))
-    cal = [torch.randn(fe.chunk_size, ACTION_DIM, generator=torch.Generator().manual_seed(100 + j)) for j in range(8)]
+    cal = [torch.randn(fe.chunk_size, ACTION_DIM, generator=torch.Generator().manual_seed(100 + j)) for j in range(args.calib_samples)]
     model.calibrate(cal)
     noise = torch.randn(fe.chunk_size, ACTION_DIM, generator=torch.Generator().manual_seed(7)).numpy()
     model.predict(noise=noise)            # captures the graph
@@ -192,12 +192,14 @@ def run_ours(args):
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
+    torch.cuda.profiler.start()      # no-op unless a profiler was attached with --profile-from-start off
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(s)
     for _ in range(args.steps):
         fe.forward_decode_only()
     e1.record(s)
     barrier()
+    torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     # ---- end to end through the public API: host noise in, host actions out
     for _ in range(3):
@@ -219,8 +221,14 @@ def run_ours(args):
     if rank == 0:
         from flashrt_b200 import flash_rt_kernels as fvk
         status = fvk.tensor_core_status()
-        gemm_us, gemm_bytes, _ = gemm_roofline(fe)
         peak, peak_src = _peaks()
+        if args.lean:
+            print(json.dumps({"metric": METRIC, "value": round(ms, 4), "unit": "ms", "lean": True,
+                              "e2e_ms": round(e2e_ms, 4), "tensor_core_status": status}), flush=True)
+            if world > 1:
+                dist.destroy_process_group()
+            return
+        gemm_us, gemm_bytes, _ = gemm_roofline(fe)
         achieved = gemm_bytes / (gemm_us * 1e-6) / 1e9
         # algorithmic HBM bytes of one loop: FP8 weights + prefix/fresh KV per layer per step
         loop_bytes = fe.num_steps * L * (17301504 + 2 * (P + fe.chunk_size) * 256 * 2)
@@ -233,6 +241,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world} (no collective)",
                        "l2": "working set 326 MB per Euler step exceeds the 126 MB L2; no explicit flush",
                        "kernels_per_loop": fe.kernels_per_loop(), "pdl": fe.use_pdl,
+                       "calibration_samples": args.calib_samples,
                        "tensor_core_status": status, "actions_finite": bool((out == out).all())},
             "e2e": {"value": round(e2e_ms, 4), "unit": "ms", "h2d_bytes_per_step": int(noise.nbytes),
                     "d2h_bytes_per_step": int(out.nbytes)},
@@ -259,6 +268,12 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--calib-samples", type=int, default=8, help="calibration noises (8 = the named config)")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="chain kernels with plain stream order instead of programmatic dependent launch "
+                         "(Nsight Compute cannot profile programmatically dependent launches)")
+    ap.add_argument("--lean", action="store_true",
+                    help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
