@@ -105,6 +105,7 @@ struct AttnParams {
     long long o_bs, o_rs, o_hs;
     int B, Sq, Skv, Hq, Hkv, G;
     int chunks_total;            // ceil(Skv / BKV)
+    int kv_static_rows;          // leading K/V rows that the previous kernel in the stream does not write
     float scale_log2;            // softmax_scale * log2(e)
 };
 
@@ -179,6 +180,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int c_begin = (int)((long long)p.chunks_total * rank / C);
     const int c_end = (int)((long long)p.chunks_total * (rank + 1) / C);
     const int nchunks = c_end - c_begin;
+    const int dper = D / (int)C;                      // head-dim columns finished by each rank (C is a power of two)
+    const int swz = (dper >> 2) - 1 < 7 ? (dper >> 2) - 1 : 7;
 
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
@@ -206,28 +209,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t tmem_O = tmem + Cfg::O_COL;
 
     pdl_launch_dependents();
-    pdl_wait();                       // Q (and the freshly appended K/V rows) come from the previous kernel
-
-    int kv_len = p.Skv;
-    if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
 
     if (warp == 4 && lane == 0) {
         // ---------------- TMA producer
-        tc::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-        for (int db = 0; db < Cfg::DB; ++db)
-            tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, q_full, db * 64, 0, hk, tok0, b);
-        for (int i = 0; i < nchunks && !*abort_flag; ++i) {
-            if (i > 0) ATTN_WAIT(kv_empty, (uint32_t)((i - 1) & 1), AERR_PRODUCER);
-            if (*abort_flag) break;
-            const int key0 = (c_begin + i) * BKV;
+        auto load_kv = [&](int chunk) {
+            const int key0 = chunk * BKV;
             tc::mbar_arrive_expect_tx(k_full, Cfg::KV_BYTES);
             for (int db = 0; db < Cfg::DB; ++db)
                 tc::tma_load_4d(sK + db * (BKV * 128), &tmK, k_full, db * 64, hk, key0, b);
             tc::mbar_arrive_expect_tx(v_full, Cfg::KV_BYTES);
             for (int db = 0; db < Cfg::DB; ++db)
                 tc::tma_load_4d(sV + db * (BKV * 128), &tmV, v_full, db * 64, hk, key0, b);
+        };
+        // keys that the previous kernel does not write (the prefix) can be fetched while it still runs
+        const bool early = nchunks > 0 && (c_begin + 1) * BKV <= p.kv_static_rows;
+        if (early) load_kv(c_begin);
+        pdl_wait();                   // Q and the freshly appended K/V rows come from the previous kernel
+        tc::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+        for (int db = 0; db < Cfg::DB; ++db)
+            tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, q_full, db * 64, 0, hk, tok0, b);
+        for (int i = early ? 1 : 0; i < nchunks && !*abort_flag; ++i) {
+            if (i > 0) ATTN_WAIT(kv_empty, (uint32_t)((i - 1) & 1), AERR_PRODUCER);
+            if (*abort_flag) break;
+            load_kv(c_begin + i);
         }
     } else if (warp == 5 && lane == 0) {
+        pdl_wait();
         // ---------------- MMA issuer
         constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);   // bf16 x bf16, both K-major
         constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, D);     // B (= V) is MN-major
@@ -261,6 +268,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
     } else if (warp < 4) {
         // ---------------- softmax: thread = row (TMEM lane 32*warp + lane)
+        pdl_wait();
+        int kv_len = p.Skv;
+        if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
         const int row = warp * 32 + lane;
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
         float m_run = -INFINITY, l_run = 0.0f;
@@ -347,23 +357,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0u;
                 }
+                // staged as [slice of dper columns][row][dper] with the 16-byte chunks of a row xor-swizzled by
+                // (row & mask): conflict-free 16-byte writes here and 16-byte remote reads in the combine
 #pragma unroll
-                for (int j = 0; j < 32; ++j) red[(c + j) * 128 + row] = __uint_as_float(v[j]);
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const int d = c + j4 * 4;
+                    const int slice = d / dper, ch = (d % dper) >> 2;
+                    float4 w4 = make_float4(__uint_as_float(v[j4 * 4]), __uint_as_float(v[j4 * 4 + 1]),
+                                            __uint_as_float(v[j4 * 4 + 2]), __uint_as_float(v[j4 * 4 + 3]));
+                    *reinterpret_cast<float4*>(&red[((size_t)(slice * 128 + row)) * dper + ((ch ^ (row & swz)) << 2)]) = w4;
+                }
             }
         }
     }
     __syncwarp();
     tc::cluster_sync_all();
 
-    // ---------------- combine across the kv splits: this CTA finishes columns [d0, d1)
+    // ---------------- combine across the kv splits: this CTA finishes columns [rank*dper, (rank+1)*dper)
     if (warp < 4 && !*abort_flag) {
         const int row = warp * 32 + lane;
-        const int dper = ((D / 8 + (int)C - 1) / (int)C) * 8;           // multiple of 8 columns per rank
         const int d0 = (int)rank * dper;
-        const int d1 = d0 + dper < D ? d0 + dper : D;
         const int t = tok0 + row / p.G;
         const int hq = hk * p.G + row % p.G;
-        if (d0 < D && t < p.Sq) {
+        if (t < p.Sq) {
             float w[8];
             float M = -INFINITY;
             const uint32_t a_m = tc::smem_u32(&s_m[row]);
@@ -381,22 +397,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (uint32_t s = 0; s < C; ++s) w[s] *= invL;
             const size_t obase = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs;
             const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
-            for (int d = d0; d < d1; d += 8) {
+            const uint32_t my_row = tc::smem_u32(&red[((size_t)((int)rank * 128 + row)) * dper]);
+            uint32_t rbase[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) rbase[s] = tc::dsmem_map(my_row, (uint32_t)s < C ? s : 0);
+            for (int d = 0; d < dper; d += 8) {
                 float acc[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-                for (uint32_t s = 0; s < C; ++s) {
-                    if (w[s] == 0.0f) continue;
+                const uint32_t off0 = (uint32_t)((((d >> 2)) ^ (row & swz)) << 4);
+                const uint32_t off1 = (uint32_t)((((d >> 2) + 1) ^ (row & swz)) << 4);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        acc[j] += w[s] * tc::dsmem_ld_f32(tc::dsmem_map(tc::smem_u32(&red[(d + j) * 128 + row]), s));
+                for (int g = 0; g < 8; g += 2) {
+                    if ((uint32_t)g >= C) break;
+                    // four 16-byte remote loads in flight per block: ranks g, g+1 x two chunks
+                    float4 x0, x1, y0, y1;
+                    asm volatile(
+                        "ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%16];\n\t"
+                        "ld.shared::cluster.v4.f32 {%4,%5,%6,%7}, [%17];\n\t"
+                        "ld.shared::cluster.v4.f32 {%8,%9,%10,%11}, [%18];\n\t"
+                        "ld.shared::cluster.v4.f32 {%12,%13,%14,%15}, [%19];"
+                        : "=f"(x0.x), "=f"(x0.y), "=f"(x0.z), "=f"(x0.w), "=f"(x1.x), "=f"(x1.y), "=f"(x1.z), "=f"(x1.w),
+                          "=f"(y0.x), "=f"(y0.y), "=f"(y0.z), "=f"(y0.w), "=f"(y1.x), "=f"(y1.y), "=f"(y1.z), "=f"(y1.w)
+                        : "r"(rbase[g] + off0), "r"(rbase[g] + off1),
+                          "r"(rbase[(uint32_t)(g + 1) < C ? g + 1 : g] + off0),
+                          "r"(rbase[(uint32_t)(g + 1) < C ? g + 1 : g] + off1)
+                        : "memory");
+                    const float w0 = w[g], w1 = (uint32_t)(g + 1) < C ? w[g + 1] : 0.0f;
+                    acc[0] += w0 * x0.x; acc[1] += w0 * x0.y; acc[2] += w0 * x0.z; acc[3] += w0 * x0.w;
+                    acc[4] += w0 * x1.x; acc[5] += w0 * x1.y; acc[6] += w0 * x1.z; acc[7] += w0 * x1.w;
+                    acc[0] += w1 * y0.x; acc[1] += w1 * y0.y; acc[2] += w1 * y0.z; acc[3] += w1 * y0.w;
+                    acc[4] += w1 * y1.x; acc[5] += w1 * y1.y; acc[6] += w1 * y1.z; acc[7] += w1 * y1.w;
                 }
                 uint4 o;
                 o.x = pack_bf16x2(acc[0], acc[1]);
                 o.y = pack_bf16x2(acc[2], acc[3]);
                 o.z = pack_bf16x2(acc[4], acc[5]);
                 o.w = pack_bf16x2(acc[6], acc[7]);
-                st_global_v4(p.O + obase + d, o);
+                st_global_v4(p.O + obase + d0 + d, o);
                 if (p.O_fp8) {
                     // quantise the bf16-rounded value, as a separate quantise kernel reading O would
                     float q[8];
@@ -409,7 +447,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                            clamp448(__fmul_rn(q[2], inv_os)), clamp448(__fmul_rn(q[3], inv_os)));
                     o8.y = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[4], inv_os)), clamp448(__fmul_rn(q[5], inv_os)),
                                            clamp448(__fmul_rn(q[6], inv_os)), clamp448(__fmul_rn(q[7], inv_os)));
-                    st_global_v2(p.O_fp8 + obase + d, o8);
+                    st_global_v2(p.O_fp8 + obase + d0 + d, o8);
                 }
             }
             if (p.lse && rank == 0)
@@ -456,6 +494,7 @@ static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p
     p.chunks_total = (p.Skv + BKV - 1) / BKV;
     if (splits > p.chunks_total) splits = p.chunks_total;
     if (splits < 1) splits = 1;
+    while (splits & (splits - 1)) --splits;            // power of two: each rank finishes D / splits columns
     const int tiles = (p.Sq * p.G + 127) / 128;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, p.Hkv * p.B, splits);
@@ -490,13 +529,15 @@ extern "C" {
 //   Q, O: (batch, seqlen_q, num_heads_q, head_dim)   q_strides / o_strides = {batch, row, head}
 //   K, V: (batch, seqlen_k, num_heads_kv, head_dim)  k_strides / v_strides = {batch, row, head}
 // O_fp8 / out_scale: optional fused e4m3 copy of O (null to skip).  lse: optional (batch, heads_q, seqlen_q).
-// seqused_k: optional device int limiting the valid keys.  kv_splits: 0 = choose, else 1..8.
+// seqused_k: optional device int limiting the valid keys.  kv_splits: 0 = choose, else 1..8 (rounded down to a
+// power of two).  kv_static_rows: number of leading K/V rows NOT written by the previous kernel in the stream
+// (they may be fetched before that kernel finishes when flags bit0 is set); 0 if unsure.
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
                                 int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
                                 const long long* q_strides, const long long* k_strides, const long long* v_strides,
-                                const long long* o_strides, float softmax_scale, int kv_splits, int flags,
-                                void* stream) {
+                                const long long* o_strides, float softmax_scale, int kv_splits, int kv_static_rows,
+                                int flags, void* stream) {
     if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return FRT_ERR_INVALID;
     if (batch <= 0 || seqlen_q < 0 || seqlen_k <= 0 || num_heads_q <= 0 || num_heads_kv <= 0) return FRT_ERR_INVALID;
     if (O_fp8 && !out_scale) return FRT_ERR_INVALID;
@@ -523,6 +564,7 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
     p.Hkv = num_heads_kv;
     p.G = G;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.kv_static_rows = kv_static_rows;
     cudaStream_t s = (cudaStream_t)stream;
     const bool pdl = flags & 1;
     const int tiles = ((seqlen_q * G + 127) / 128) * num_heads_kv * batch;

@@ -6,6 +6,8 @@
 // Replaces, for sm_100a, the reference entry points
 //   GemmRunner::fp8_nn_dev / fp8_nt_dev     csrc/gemm/gemm_runner.cu:67-76 (cuBLASLt)
 //   fp8_gemm_descale_bf16out               csrc/kernels/decoder_fused.cu:310-468
+//   (+ fused epilogues standing in for qkv_split_rope, csrc/kernels/rope.cu:135-277, and
+//      gate_silu_mul_merged_fp8, csrc/kernels/activation.cu:249-279, after the M <= 256 GEMM)
 //   cutlass_fp8_{sq,t1,wide,plain}_bf16out csrc/gemm/cutlass_sm100.cu:75-125
 //
 // Math: D(M,N) = alpha * A(M,K) . W(N,K)^T (+ bias), alpha = sa * sb * alpha_host,
@@ -18,7 +20,7 @@
 //     activation rows.  Every weight byte is streamed exactly once and the MMA
 //     M-dimension is fully used even for M = 16 or 50.
 //   * SWAP = false (large M): lanes = 128 activation rows, columns = BN weight rows.
-// Split-K: the CTAs of one thread-block cluster (1 x 1 x S, S <= 8) each
+// Split-K: the CTAs of one thread-block cluster (1 x 1 x S, S <= 16) each
 // accumulate a slice of K, exchange fp32 partials through distributed shared
 // memory and each reduces 1/S of the tile's columns in fixed order (split 0, 1, ...).
 // There is no global-memory workspace and the result is deterministic.
@@ -34,6 +36,15 @@ namespace frt {
 
 // ------------------------------------------------------------------ status word
 __device__ int g_gemm_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
+
+#ifdef FRT_TRACE
+__device__ long long g_trace[64];
+#define TRACE(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 96) g_trace[i] = clock64(); } while (0)
+#define TRACE_MMA(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_trace[i] = clock64(); } while (0)
+#else
+#define TRACE(i)
+#define TRACE_MMA(i)
+#endif
 
 // ------------------------------------------------------------------ tensor maps (host)
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -83,7 +94,19 @@ struct GemmParams {
     int lane_rows;             // extent of the lane operand (N if SWAP else M)
     int col_rows;              // extent of the column operand (M if SWAP else N)
     int w_is_lane;             // which operand holds the weights (prefetched before the PDL wait)
+    // fused epilogues (SWAP kernels only)
+    const __nv_bfloat16* rope; // EPI_ROPE_SPLIT: (M, head_dim) rows [cos0, sin0, cos1, sin1, ...]
+    __nv_bfloat16* outQ;       //   Q (M, q_dim); K, V rows written at (*devpos + m)
+    __nv_bfloat16* outK;
+    __nv_bfloat16* outV;
+    const int* devpos;
+    int q_dim, k_dim, v_dim, head_dim;
+    uint8_t* out8;             // EPI_GEGLU_FP8: (M, half) e4m3 codes
+    const float* out_scale;    //   device scalar: quantisation scale of the GeGLU result
+    int half;                  //   hidden width; weight rows [0, half) = gate, [half, 2 half) = up
 };
+
+enum { EPI_BF16 = 0, EPI_ROPE_SPLIT = 1, EPI_GEGLU_FP8 = 2 };
 
 template <int BN>
 struct GemmCfg {
@@ -101,9 +124,46 @@ struct GemmCfg {
 
 enum { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
 
-template <int BN, bool SWAP>
+// one asm block = eight independent distributed-shared-memory loads in flight
+__device__ __forceinline__ void dsmem_ld8(const uint32_t* a, float* v) {
+    asm volatile(
+        "ld.shared::cluster.f32 %0, [%8];\n\t"
+        "ld.shared::cluster.f32 %1, [%9];\n\t"
+        "ld.shared::cluster.f32 %2, [%10];\n\t"
+        "ld.shared::cluster.f32 %3, [%11];\n\t"
+        "ld.shared::cluster.f32 %4, [%12];\n\t"
+        "ld.shared::cluster.f32 %5, [%13];\n\t"
+        "ld.shared::cluster.f32 %6, [%14];\n\t"
+        "ld.shared::cluster.f32 %7, [%15];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7])
+        : "memory");
+}
+
+// Sum over the S cluster ranks (fixed order 0, 1, ...) of the staged partial at byte offset `off` inside
+// every rank's staging buffer.  rank_base[s] = cluster address of rank s's buffer.
+template <int MAXS>
+__device__ __forceinline__ float reduce_ranks(const uint32_t* rank_base, uint32_t S, uint32_t off) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int g = 0; g < MAXS; g += 8) {
+        if ((uint32_t)g >= S) break;
+        uint32_t a[8];
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = rank_base[(uint32_t)(g + j) < S ? g + j : 0] + off;
+        dsmem_ld8(a, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if ((uint32_t)(g + j) < S) acc += v[j];
+    }
+    return acc;
+}
+
+template <int BN, bool SWAP, int EPI>
 __global__ void __launch_bounds__(128, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+    static_assert(EPI == EPI_BF16 || SWAP, "fused epilogues exist for the small-M (swapped) kernel only");
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -118,9 +178,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     volatile int* consumed = abort_flag + 2;
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
+    TRACE(0);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int lane0 = blockIdx.x * 128;              // first row of the lane operand
+    // first row of the lane operand; with the GeGLU epilogue a tile is 64 gate rows + the 64 matching up rows
+    const int lane0 = (EPI == EPI_GEGLU_FP8) ? blockIdx.x * 64 : blockIdx.x * 128;
     const int col0 = blockIdx.y * BN;                // first row of the column operand
     const uint32_t S = tc::cluster_nctarank();
     const uint32_t rank = tc::cluster_ctarank();
@@ -149,6 +211,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_d = *tmem_slot;
+    TRACE(1);
 
     pdl_launch_dependents();
 
@@ -162,9 +225,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
         const int x_row = p.w_is_lane ? col0 : lane0;
         const int pre = nkb < STAGES ? nkb : STAGES;
         // weights do not depend on the producer grid: start streaming them now
+        auto load_w = [&](int stage, int kb) {
+            uint8_t* dst = stage_base + stage * Cfg::STAGE_BYTES + w_off;
+            if (EPI == EPI_GEGLU_FP8) {   // tmL has a 64-row box here
+                tc::tma_load_2d(dst, tmW, &full[stage], kb * 128, w_row);
+                tc::tma_load_2d(dst + 64 * 128, tmW, &full[stage], kb * 128, p.half + w_row);
+            } else {
+                tc::tma_load_2d(dst, tmW, &full[stage], kb * 128, w_row);
+            }
+        };
         for (int i = 0; i < pre; ++i) {
             tc::mbar_arrive_expect_tx(&full[i], Cfg::STAGE_BYTES);
-            tc::tma_load_2d(stage_base + i * Cfg::STAGE_BYTES + w_off, tmW, &full[i], (kb_begin + i) * 128, w_row);
+            load_w(i, kb_begin + i);
         }
         pdl_wait();
         for (int i = 0; i < pre; ++i)
@@ -180,7 +252,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 break;
             }
             tc::mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-            tc::tma_load_2d(stage_base + s * Cfg::STAGE_BYTES + w_off, tmW, &full[s], (kb_begin + i) * 128, w_row);
+            load_w(s, kb_begin + i);
             tc::tma_load_2d(stage_base + s * Cfg::STAGE_BYTES + x_off, tmX, &full[s], (kb_begin + i) * 128, x_row);
             *issued = i + 1;
         }
@@ -199,6 +271,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 break;
             }
             tc::tc_fence_after_sync();
+            if (i == 0) TRACE_MMA(10);
+            if (i == nkb - 1) TRACE_MMA(11);
             const uint32_t sL = tc::smem_u32(stage_base + s * Cfg::STAGE_BYTES);
             const uint32_t sC = sL + Cfg::L_BYTES;
             const uint64_t dL = tc::make_desc_kmajor_sw128(sL);
@@ -214,7 +288,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     __syncwarp();
 
     // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w .. 32w+31
+    TRACE(2);
     pdl_wait();
+    TRACE(3);
     const bool acc_seen = tc::mbar_wait_until(accum_bar, 0, deadline, abort_flag);
     const bool have_acc = __all_sync(0xffffffffu, acc_seen);   // tcgen05.ld below is warp-collective
     if (!have_acc && !*abort_flag) {
@@ -223,6 +299,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     }
     __syncwarp();
     tc::tc_fence_after_sync();
+    TRACE(4);
 
     float alpha = p.alpha_host;
     if (p.sa) alpha *= *p.sa;
@@ -230,7 +307,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     const int lrow = lane0 + warp * 32 + lane;                 // global row of the lane operand
     const uint32_t trow = tmem_d + ((uint32_t)(warp * 32) << 16);
 
-    if (S == 1) {
+    if (S == 1 && EPI == EPI_BF16 && !SWAP) {
         if (have_acc) {
             if (SWAP) {
                 // lanes = output columns n, TMEM columns = output rows m
@@ -289,7 +366,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
             }
         }
     } else {
-        // ---------------- split-K: stage partials as red[col][lane] (fp32), reduce across the cluster
+        // ---------------- staged path: partials as red[col][lane] (fp32) in shared memory, then every rank of
+        // the cluster finishes a slice of the columns, summing the ranks in fixed order through DSMEM.
         float* red = reinterpret_cast<float*>(stage_base);
         if (have_acc) {
 #pragma unroll 1
@@ -302,29 +380,164 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                     red[(c + j) * 128 + warp * 32 + lane] = __uint_as_float(v[j]);
             }
         }
-        tc::cluster_sync_all();
-        if (!*abort_flag) {
+        TRACE(5);
+        if (S > 1) tc::cluster_sync_all(); else __syncthreads();
+        TRACE(6);
+        if (!*abort_flag && SWAP) {
+            // Work item = (column c of this rank's slice, group of 8 consecutive lanes): every remote read is a
+            // 16-byte load, every global store a full 16-byte (bf16) or 8-byte (fp8) vector, and all loads of an
+            // item are in flight together.  Ranks are summed in fixed order 0, 1, ...
+            const uint32_t red_addr = tc::smem_u32(red);
+            uint32_t rank_base[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) rank_base[r] = tc::dsmem_map(red_addr, (uint32_t)r < S ? r : 0);
+            const int cols_per = (BN + (int)S - 1) / (int)S;
+            const int cbeg = (int)rank * cols_per;
+            int cend = cbeg + cols_per < BN ? cbeg + cols_per : BN;
+            if (col0 + cend > p.M) cend = p.M - col0;                       // columns are tokens
+            constexpr int GROUPS = (EPI == EPI_GEGLU_FP8) ? 8 : 16;        // 8-lane groups per column that carry output
+            const int items = (cend > cbeg ? cend - cbeg : 0) * GROUPS;
+            const float inv_os = (EPI == EPI_GEGLU_FP8) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+            const int pos = (EPI == EPI_ROPE_SPLIT && p.devpos) ? *p.devpos : 0;
+            for (int it = threadIdx.x; it < items; it += 128) {
+                const int c = cbeg + it / GROUPS;
+                const int g = it % GROUPS;
+                const int m = col0 + c;
+                const uint32_t off = (uint32_t)(c * 128 + g * 8) * 4u;
+                float a[8], b[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.0f;
+                // lanes g*8 .. g*8+7 (and, for GeGLU, the matching up lanes 64 further on)
+#pragma unroll
+                for (uint32_t r0 = 0; r0 < 16; r0 += 2) {
+                    if (r0 >= S) break;
+                    const uint32_t ra = rank_base[r0] + off;
+                    const uint32_t rb = rank_base[r0 + 1 < S ? r0 + 1 : r0] + off;
+                    float4 x0, x1, y0, y1;
+                    asm volatile(
+                        "ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%16];\n\t"
+                        "ld.shared::cluster.v4.f32 {%4,%5,%6,%7}, [%17];\n\t"
+                        "ld.shared::cluster.v4.f32 {%8,%9,%10,%11}, [%18];\n\t"
+                        "ld.shared::cluster.v4.f32 {%12,%13,%14,%15}, [%19];"
+                        : "=f"(x0.x), "=f"(x0.y), "=f"(x0.z), "=f"(x0.w), "=f"(x1.x), "=f"(x1.y), "=f"(x1.z), "=f"(x1.w),
+                          "=f"(y0.x), "=f"(y0.y), "=f"(y0.z), "=f"(y0.w), "=f"(y1.x), "=f"(y1.y), "=f"(y1.z), "=f"(y1.w)
+                        : "r"(ra), "r"(ra + 16u), "r"(rb), "r"(rb + 16u));
+                    a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w;
+                    a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
+                    if (r0 + 1 < S) {
+                        a[0] += y0.x; a[1] += y0.y; a[2] += y0.z; a[3] += y0.w;
+                        a[4] += y1.x; a[5] += y1.y; a[6] += y1.z; a[7] += y1.w;
+                    }
+                    if (EPI == EPI_GEGLU_FP8) {
+                        asm volatile(
+                            "ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%16];\n\t"
+                            "ld.shared::cluster.v4.f32 {%4,%5,%6,%7}, [%17];\n\t"
+                            "ld.shared::cluster.v4.f32 {%8,%9,%10,%11}, [%18];\n\t"
+                            "ld.shared::cluster.v4.f32 {%12,%13,%14,%15}, [%19];"
+                            : "=f"(x0.x), "=f"(x0.y), "=f"(x0.z), "=f"(x0.w), "=f"(x1.x), "=f"(x1.y), "=f"(x1.z), "=f"(x1.w),
+                              "=f"(y0.x), "=f"(y0.y), "=f"(y0.z), "=f"(y0.w), "=f"(y1.x), "=f"(y1.y), "=f"(y1.z), "=f"(y1.w)
+                            : "r"(ra + 256u), "r"(ra + 272u), "r"(rb + 256u), "r"(rb + 272u));
+                        b[0] += x0.x; b[1] += x0.y; b[2] += x0.z; b[3] += x0.w;
+                        b[4] += x1.x; b[5] += x1.y; b[6] += x1.z; b[7] += x1.w;
+                        if (r0 + 1 < S) {
+                            b[0] += y0.x; b[1] += y0.y; b[2] += y0.z; b[3] += y0.w;
+                            b[4] += y1.x; b[5] += y1.y; b[6] += y1.z; b[7] += y1.w;
+                        }
+                    }
+                }
+                if (EPI == EPI_BF16) {
+                    const int n = lane0 + g * 8;
+                    float f[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        f[j] = a[j] * alpha;
+                        if (p.bias && n + j < p.N) f[j] += __bfloat162float(p.bias[n + j]);
+                    }
+                    __nv_bfloat16* dst = p.out + (size_t)m * p.N + n;
+                    if (n + 8 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        uint4 o;
+                        o.x = pack_bf16x2(f[0], f[1]);
+                        o.y = pack_bf16x2(f[2], f[3]);
+                        o.z = pack_bf16x2(f[4], f[5]);
+                        o.w = pack_bf16x2(f[6], f[7]);
+                        st_global_v4(dst, o);
+                    } else {
+                        for (int j = 0; j < 8; ++j)
+                            if (n + j < p.N) dst[j] = __float2bfloat16_rn(f[j]);
+                    }
+                } else if (EPI == EPI_ROPE_SPLIT) {
+                    // same rounding points as the separate kernels: bf16 GEMM result, fp32 rotation, bf16 store
+                    const int n = lane0 + g * 8;                     // 8 features of the fused q|k|v row
+                    if (n >= p.N) continue;
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(a[j] * alpha));
+                    const bool is_q = n < p.q_dim;
+                    const bool is_k = !is_q && n < p.q_dim + p.k_dim;
+                    const int nr = is_q ? n : (is_k ? n - p.q_dim : n - p.q_dim - p.k_dim);
+                    uint4 o;
+                    if (is_q || is_k) {
+                        const uint4 t = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
+                        const uint32_t* tw = &t.x;
+                        uint32_t* ow = &o.x;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            float cs, sn;
+                            unpack_bf16x2(tw[k], cs, sn);
+                            ow[k] = pack_bf16x2(__fmaf_rn(v[2 * k], cs, -__fmul_rn(v[2 * k + 1], sn)),
+                                                __fmaf_rn(v[2 * k + 1], cs, __fmul_rn(v[2 * k], sn)));
+                        }
+                    } else {
+                        o.x = pack_bf16x2(v[0], v[1]);
+                        o.y = pack_bf16x2(v[2], v[3]);
+                        o.z = pack_bf16x2(v[4], v[5]);
+                        o.w = pack_bf16x2(v[6], v[7]);
+                    }
+                    __nv_bfloat16* dst = is_q ? p.outQ + (size_t)m * p.q_dim + nr
+                                              : (is_k ? p.outK + (size_t)(pos + m) * p.k_dim + nr
+                                                      : p.outV + (size_t)(pos + m) * p.v_dim + nr);
+                    st_global_v4(dst, o);
+                } else {
+                    // GeGLU: a = gate partial sums (lanes g*8..), b = up partial sums (lanes 64 + g*8..)
+                    const int h = lane0 + g * 8;
+                    if (h >= p.half) continue;
+                    float q[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float gt = __bfloat162float(__float2bfloat16_rn(a[j] * alpha));
+                        const float up = __bfloat162float(__float2bfloat16_rn(b[j] * alpha));
+                        q[j] = clamp448(__fmul_rn(__fmul_rn(det_gelu_tanh(gt), up), inv_os));
+                    }
+                    uint2 o8;
+                    o8.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+                    o8.y = f32x4_to_e4m3x4(q[4], q[5], q[6], q[7]);
+                    st_global_v2(p.out8 + (size_t)m * p.half + h, o8);
+                }
+            }
+        } else if (!*abort_flag) {
+            // large-M kernel with split-K: lanes = rows m, columns = n (scalar, rarely used)
+            const uint32_t red_addr = tc::smem_u32(red);
+            uint32_t rank_base[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) rank_base[r] = tc::dsmem_map(red_addr, (uint32_t)r < S ? r : 0);
             const int cols_per = (BN + (int)S - 1) / (int)S;
             const int cbeg = (int)rank * cols_per;
             const int cend = cbeg + cols_per < BN ? cbeg + cols_per : BN;
-            const int col_limit = SWAP ? p.M : p.N;
-            const int lane_limit = SWAP ? p.N : p.M;
+            const int tl = warp * 32 + lane;
             for (int c = cbeg; c < cend; ++c) {
                 const int gcol = col0 + c;
-                if (gcol >= col_limit) break;
-                const uint32_t a = tc::smem_u32(&red[c * 128 + warp * 32 + lane]);
-                float acc = 0.0f;
-                for (uint32_t s = 0; s < S; ++s) acc += tc::dsmem_ld_f32(tc::dsmem_map(a, s));
-                if (lrow < lane_limit) {
-                    const int m = SWAP ? gcol : lrow;
-                    const int n = SWAP ? lrow : gcol;
+                if (gcol >= p.N) break;
+                const float acc = reduce_ranks<16>(rank_base, S, (uint32_t)(c * 128 + tl) * 4u);
+                if (lrow < p.M) {
                     float f = acc * alpha;
-                    if (p.bias) f += __bfloat162float(p.bias[n]);
-                    p.out[(size_t)m * p.N + n] = __float2bfloat16_rn(f);
+                    if (p.bias) f += __bfloat162float(p.bias[gcol]);
+                    p.out[(size_t)lrow * p.N + gcol] = __float2bfloat16_rn(f);
                 }
             }
         }
-        tc::cluster_sync_all();
+        TRACE(7);
+        if (S > 1) tc::cluster_sync_all();
+        TRACE(8);
     }
 
     // ---------------- teardown
@@ -342,6 +555,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     }
     __syncthreads();
     if (warp == 2) tc::tmem_dealloc(tmem_d, Cfg::TMEM_COLS);
+    TRACE(9);
 }
 
 // ------------------------------------------------------------------ host launch
@@ -378,13 +592,15 @@ int get_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t r
     return FRT_OK;
 }
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, int EPI>
 static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int splits, bool pdl, cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Cfg::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
         attr_done = true;
     }
@@ -394,13 +610,15 @@ static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int sp
     p.col_rows = SWAP ? p.M : p.N;
     p.w_is_lane = SWAP ? 1 : 0;
     CUtensorMap tmL, tmC;
-    int rc = get_tmap_2d_u8(&tmL, lane_ptr, (uint64_t)p.lane_rows, (uint64_t)K, (uint64_t)K, 128);
+    int rc = get_tmap_2d_u8(&tmL, lane_ptr, (uint64_t)p.lane_rows, (uint64_t)K, (uint64_t)K,
+                            EPI == EPI_GEGLU_FP8 ? 64 : 128);
     if (rc) return rc;
     rc = get_tmap_2d_u8(&tmC, col_ptr, (uint64_t)p.col_rows, (uint64_t)K, (uint64_t)K, BN);
     if (rc) return rc;
 
+    const int lane_tiles = EPI == EPI_GEGLU_FP8 ? (p.half + 63) / 64 : (p.lane_rows + 127) / 128;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.lane_rows + 127) / 128, (p.col_rows + BN - 1) / BN, splits);
+    cfg.gridDim = dim3(lane_tiles, (p.col_rows + BN - 1) / BN, splits);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
@@ -418,19 +636,31 @@ static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int sp
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, SWAP>, tmL, tmC, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, SWAP, EPI>, tmL, tmC, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
 
+// Split-K factor: the largest power of two (<= 16, the cluster limit with the non-portable size enabled) that
+// keeps tiles x splits within one wave of the SMs and leaves every split at least one k-block.
 static int pick_splits(int tiles, int kb_total, int requested) {
     if (requested > 0) {
-        int s = requested > 8 ? 8 : requested;
+        int s = requested > 16 ? 16 : requested;
         return s > kb_total ? kb_total : s;
     }
-    // fill the machine: aim for >= ~128 CTAs, keep at least 2 k-blocks per split
     int s = 1;
-    while (s < 8 && tiles * s * 2 <= 148 && kb_total / (s * 2) >= 2) s *= 2;
+    while (s < 8 && tiles * s * 2 <= 148 && s * 2 <= kb_total) s *= 2;
     return s;
+}
+
+template <int EPI>
+static int dispatch_small_m(const void* A, const void* W, GemmParams p, int K, int M, int tiles, int splits,
+                            bool pdl, cudaStream_t s) {
+    int sp = pick_splits(tiles, p.kb_total, splits);
+    if (M <= 16) return launch_gemm<16, true, EPI>(A, W, p, K, sp, pdl, s);
+    if (M <= 32) return launch_gemm<32, true, EPI>(A, W, p, K, sp, pdl, s);
+    if (M <= 64) return launch_gemm<64, true, EPI>(A, W, p, K, sp, pdl, s);
+    if (M <= 128) return launch_gemm<128, true, EPI>(A, W, p, K, sp, pdl, s);
+    return launch_gemm<256, true, EPI>(A, W, p, K, sp, pdl, s);
 }
 
 }  // namespace frt
@@ -460,19 +690,67 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     p.kb_total = (K + 127) / 128;
     cudaStream_t s = (cudaStream_t)stream;
     bool pdl = flags & 1;
-    if (M <= 256) {
-        int tiles = (N + 127) / 128;
-        int sp = pick_splits(tiles, p.kb_total, splits);
-        if (M <= 16) return launch_gemm<16, true>(A, W, p, K, sp, pdl, s);
-        if (M <= 32) return launch_gemm<32, true>(A, W, p, K, sp, pdl, s);
-        if (M <= 64) return launch_gemm<64, true>(A, W, p, K, sp, pdl, s);
-        if (M <= 128) return launch_gemm<128, true>(A, W, p, K, sp, pdl, s);
-        return launch_gemm<256, true>(A, W, p, K, sp, pdl, s);
-    }
-    int sp = splits > 0 ? pick_splits(1, p.kb_total, splits) : 1;
-    if (N >= 256) return launch_gemm<256, false>(A, W, p, K, sp, pdl, s);
-    if (N > 64) return launch_gemm<128, false>(A, W, p, K, sp, pdl, s);
-    return launch_gemm<64, false>(A, W, p, K, sp, pdl, s);
+    if (M <= 256) return dispatch_small_m<EPI_BF16>(A, W, p, K, M, (N + 127) / 128, splits, pdl, s);
+    int sp = splits > 0 ? pick_splits(1, p.kb_total, splits > 8 ? 8 : splits) : 1;
+    if (N >= 256) return launch_gemm<256, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
+    if (N > 64) return launch_gemm<128, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
+    return launch_gemm<64, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
+}
+
+// QKV projection with the RoPE + split + KV-append epilogue fused (M <= 256):
+//   row = alpha * A(M,K) . W(N,K)^T rounded to bf16, N = q_dim + k_dim + v_dim; q and k parts rotated pairwise
+//   with rope (M, head_dim) = [cos0, sin0, ...]; Q -> (M, q_dim); K, V rows -> row (*devpos + m) (devpos NULL: m).
+// Byte-identical to frt_b200_gemm_fp8_nt followed by frt_b200_qkv_split_rope.
+int frt_b200_gemm_fp8_nt_rope_split(const void* A, const void* W, int M, int K, const float* d_scale_a,
+                                    const float* d_scale_b, const void* rope, void* Q, void* Kout, void* Vout,
+                                    const int* devpos, int q_dim, int k_dim, int v_dim, int head_dim, int splits,
+                                    int flags, void* stream) {
+    if (!A || !W || !rope || !Q || !Kout || !Vout || M < 0 || K <= 0) return FRT_ERR_INVALID;
+    if (q_dim <= 0 || k_dim <= 0 || v_dim <= 0 || head_dim <= 0) return FRT_ERR_INVALID;
+    if ((K % 16) || M > 256 || (head_dim & 1) || (q_dim % head_dim) || (k_dim % head_dim) || (q_dim & 1) ||
+        (k_dim & 1))
+        return FRT_ERR_UNSUPPORTED;
+    if (M == 0) return FRT_OK;
+    GemmParams p = {};
+    p.sa = d_scale_a;
+    p.sb = d_scale_b;
+    p.alpha_host = 1.0f;
+    p.M = M;
+    p.N = q_dim + k_dim + v_dim;
+    p.kb_total = (K + 127) / 128;
+    p.rope = (const __nv_bfloat16*)rope;
+    p.outQ = (__nv_bfloat16*)Q;
+    p.outK = (__nv_bfloat16*)Kout;
+    p.outV = (__nv_bfloat16*)Vout;
+    p.devpos = devpos;
+    p.q_dim = q_dim;
+    p.k_dim = k_dim;
+    p.v_dim = v_dim;
+    p.head_dim = head_dim;
+    return dispatch_small_m<EPI_ROPE_SPLIT>(A, W, p, K, M, (p.N + 127) / 128, splits, flags & 1, (cudaStream_t)stream);
+}
+
+// gate|up projection with the GeGLU -> FP8 epilogue fused (M <= 256):
+//   W (2*half, K): rows [0, half) = gate, [half, 2*half) = up.  out8 (M, half) =
+//   e4m3(clamp(gelu_tanh(bf16(gate)) * bf16(up) * (1 / *d_out_scale), +-448)).  half % 64 == 0.
+// Byte-identical to frt_b200_gemm_fp8_nt followed by frt_b200_geglu_fp8.
+int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int M, int half, int K,
+                                   const float* d_scale_a, const float* d_scale_b, const float* d_out_scale,
+                                   int splits, int flags, void* stream) {
+    if (!A || !W || !out8 || !d_out_scale || M < 0 || half <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if ((K % 16) || M > 256 || (half % 64)) return FRT_ERR_UNSUPPORTED;
+    if (M == 0) return FRT_OK;
+    GemmParams p = {};
+    p.sa = d_scale_a;
+    p.sb = d_scale_b;
+    p.alpha_host = 1.0f;
+    p.M = M;
+    p.N = 2 * half;
+    p.kb_total = (K + 127) / 128;
+    p.out8 = (uint8_t*)out8;
+    p.out_scale = d_out_scale;
+    p.half = half;
+    return dispatch_small_m<EPI_GEGLU_FP8>(A, W, p, K, M, half / 64, splits, flags & 1, (cudaStream_t)stream);
 }
 
 // returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)
@@ -486,5 +764,11 @@ int frt_b200_gemm_status(int reset) {
     }
     return v;
 }
+
+#ifdef FRT_TRACE
+int frt_trace_read(long long* host64) {
+    return (int)cudaMemcpyFromSymbol(host64, g_trace, sizeof(long long) * 64);
+}
+#endif
 
 }  // extern "C"

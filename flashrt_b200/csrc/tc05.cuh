@@ -41,15 +41,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// One bounded poll: suspends for at most ~1 us (the explicit time hint), returns whether the phase completed.
+// One poll.  try_wait may suspend the thread for a system-dependent (short) time and wakes as soon as the phase
+// completes; an explicit suspend-time hint made every wait cost its full hint here, so none is given.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, P;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
+        : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
@@ -72,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait_until(uint64_t* bar, uint32_t parity, 
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if ((i & 15) == 15 && global_timer_ns() > deadline_ns) return false;
+        if ((i & 3) == 3 && global_timer_ns() > deadline_ns) return false;
     }
 }
 

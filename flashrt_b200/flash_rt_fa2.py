@@ -19,12 +19,12 @@ def _s3(t):
 
 def _fwd(Q, K, V, O, softmax_lse, seqused_k, batch, seqlen_q, seqlen_k, num_heads_q, num_heads_kv, head_dim,
          q_strides, k_strides, v_strides, o_strides, softmax_scale, stream, *, pdl=False, kv_splits=0,
-         out_fp8=0, out_scale=0):
+         out_fp8=0, out_scale=0, kv_static_rows=0):
     call("frt_b200_attention_fwd_bf16", Q, K, V, O, out_fp8 or None, out_scale or None, softmax_lse or None,
          seqused_k or None, batch, seqlen_q, seqlen_k, num_heads_q, num_heads_kv, head_dim,
          C.cast(_s3(q_strides), C.c_void_p), C.cast(_s3(k_strides), C.c_void_p),
          C.cast(_s3(v_strides), C.c_void_p), C.cast(_s3(o_strides), C.c_void_p),
-         softmax_scale, kv_splits, 1 if pdl else 0, stream)
+         softmax_scale, kv_splits, kv_static_rows, 1 if pdl else 0, stream)
 
 
 def fwd_bf16(Q, K, V, O, softmax_lse, softmax_lse_accum=0, o_accum=0, batch=1, seqlen_q=0, seqlen_k=0,

@@ -143,6 +143,19 @@ class GemmRunner:
         """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form."""
         call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits, _f(pdl), stream)
 
+    # -- fused forms (no reference counterpart as single calls; each equals two reference calls) ------------
+    def fp8_nt_dev_rope_split(self, A, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc, Vc, q_dim, k_dim, v_dim,
+                              head_dim, stream=0, *, devpos=0, pdl=False, splits=0):
+        """``fp8_nt_dev`` into a (M, q+k+v) buffer followed by ``qkv_split_rope[_devpos]``, in one launch."""
+        call("frt_b200_gemm_fp8_nt_rope_split", A, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc, Vc,
+             devpos or None, q_dim, k_dim, v_dim, head_dim, splits, _f(pdl), stream)
+
+    def fp8_nt_dev_geglu_fp8(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, stream=0, *,
+                             pdl=False, splits=0):
+        """``fp8_nt_dev`` into a merged (M, 2*half) buffer followed by ``gate_geglu_merged_fp8``, in one launch."""
+        call("frt_b200_gemm_fp8_nt_geglu_fp8", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, splits,
+             _f(pdl), stream)
+
     def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, **kw):
         raise NotBuilt(
             "fp8_nn_dev (weights stored (K,N)) is not provided: this library keeps FP8 weights K-contiguous "

@@ -13,6 +13,8 @@ What differs from the reference's composition (same arithmetic, fewer launches a
   * conditioning rows are stored once per (step, layer) and read with row stride 0 instead of being expanded to
     one copy per action token; the gate of the next residual is read straight from the style row;
   * the attention kernel also emits the FP8 copy the output projection reads (no separate quantise launch);
+  * RoPE + split + KV append run in the epilogue of the QKV GEMM and GeGLU -> FP8 in the epilogue of the gate|up
+    GEMM (byte-identical to the separate kernels, which the calibration pass still uses);
   * FP8 weights are (N, K) K-contiguous (``fp8_nt_dev``);
   * the action out-projection adds its bias and accumulates into the noise buffer in the same launch, and that
     Euler state is held in fp32 (the reference keeps it in bf16, whose half-ulp at |x| ~ 4 is already 0.016);
@@ -202,7 +204,8 @@ class Pi05DecoderPipeline:
         fa2.fwd_bf16(self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
                      self.attn.data_ptr(), 0, 0, 0, 1, S, T, DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
                      1.0 / math.sqrt(DEC_HD), fe.sm_count, stream, pdl=pdl,
-                     out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0, out_scale=out8_scale_ptr or 0)
+                     out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0, out_scale=out8_scale_ptr or 0,
+                     kv_static_rows=fe.prefix_len)
 
     # ---- the loop --------------------------------------------------------
     def transformer_decoder(self, stream: int = 0, calibrate: bool = False, step_hook=None) -> None:
@@ -222,12 +225,21 @@ class Pi05DecoderPipeline:
                 # C1: adaRMS(style_attn) -> FP8 (layer 0 only; later layers get it from C7 of the previous one)
                 if i == 0:
                     self._norm(None, None, "attn", step, i, "qkv", stream, pdl, calibrate)
-                # C2: QKV projection, split + RoPE, K/V appended behind the prefix
-                self._gemm(self.act8, fe.w_qkv[i], fe.ws_qkv_t[i], self.qkv, S, 2560, DEC_D,
-                           self._scale_ptr(step, i, "qkv"), stream, pdl)
-                fvk.qkv_split_rope(self.qkv.data_ptr(), fe.rope.data_ptr(), self.q.data_ptr(),
-                                   fe.k_cache[i, fe.prefix_len:].data_ptr(), fe.v_cache[i, fe.prefix_len:].data_ptr(),
-                                   S, DEC_NH * DEC_HD, DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
+                # C2: QKV projection, split + RoPE, K/V appended behind the prefix (one launch when not calibrating)
+                if calibrate or not fe.fuse_epilogues:
+                    self._gemm(self.act8, fe.w_qkv[i], fe.ws_qkv_t[i], self.qkv, S, 2560, DEC_D,
+                               self._scale_ptr(step, i, "qkv"), stream, pdl)
+                    fvk.qkv_split_rope(self.qkv.data_ptr(), fe.rope.data_ptr(), self.q.data_ptr(),
+                                       fe.k_cache[i, fe.prefix_len:].data_ptr(),
+                                       fe.v_cache[i, fe.prefix_len:].data_ptr(), S, DEC_NH * DEC_HD,
+                                       DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
+                else:
+                    g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
+                                            self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
+                                            fe.rope.data_ptr(), self.q.data_ptr(),
+                                            fe.k_cache[i, fe.prefix_len:].data_ptr(),
+                                            fe.v_cache[i, fe.prefix_len:].data_ptr(), DEC_NH * DEC_HD,
+                                            DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
                 # C3 + C4: attention (FP8 copy fused), output projection
                 if calibrate:
                     self._attention(i, stream, False, 0)
@@ -238,15 +250,21 @@ class Pi05DecoderPipeline:
                            self._scale_ptr(step, i, "o"), stream, pdl)
                 # C5: x += o * gate_attn ; adaRMS(style_ffn) -> FP8 ; gate|up projection
                 self._norm(self.xn, ("attn", step, i), "ffn", step, i, "gu", stream, pdl, calibrate)
-                self._gemm(self.act8, fe.w_gu[i], fe.ws_gu_t[i], self.merged, S, 2 * DEC_H, DEC_D,
-                           self._scale_ptr(step, i, "gu"), stream, pdl)
-                # C6: GeGLU -> FP8 ; down projection
+                # C6: GeGLU -> FP8 (fused into the gate|up GEMM when not calibrating) ; down projection
                 if calibrate:
+                    self._gemm(self.act8, fe.w_gu[i], fe.ws_gu_t[i], self.merged, S, 2 * DEC_H, DEC_D,
+                               self._scale_ptr(step, i, "gu"), stream, pdl)
                     fvk.gate_geglu_merged(self.merged.data_ptr(), self.hidden.data_ptr(), S, DEC_H, stream)
                     self._dyn_quant(self.hidden, self.hid8, step, i, "d", stream)
-                else:
+                elif not fe.fuse_epilogues:
+                    self._gemm(self.act8, fe.w_gu[i], fe.ws_gu_t[i], self.merged, S, 2 * DEC_H, DEC_D,
+                               self._scale_ptr(step, i, "gu"), stream, pdl)
                     fvk.gate_geglu_merged_fp8(self.merged.data_ptr(), self.hid8.data_ptr(), S, DEC_H,
                                               self._scale_ptr(step, i, "d"), stream, pdl=pdl)
+                else:
+                    g.fp8_nt_dev_geglu_fp8(self.act8.data_ptr(), fe.w_gu[i].data_ptr(), self.hid8.data_ptr(), S,
+                                           DEC_H, DEC_D, self._scale_ptr(step, i, "gu"), fe.ws_gu_t[i].data_ptr(),
+                                           self._scale_ptr(step, i, "d"), stream, pdl=pdl)
                 self._gemm(self.hid8, fe.w_d[i], fe.ws_d_t[i], self.xn, S, DEC_D, DEC_H,
                            self._scale_ptr(step, i, "d"), stream, pdl)
                 # C7: x += f * gate_ffn ; next layer's adaRMS(style_attn) -> FP8
@@ -296,7 +314,7 @@ class Pi05DecoderB200:
 
     def __init__(self, checkpoint, *, num_steps: int = NUM_STEPS_DEFAULT, chunk_size: int = CHUNK_DEFAULT,
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
-                 use_cuda_graph: bool = True, **_ignored):
+                 use_cuda_graph: bool = True, fuse_epilogues: bool = True, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -304,7 +322,7 @@ class Pi05DecoderB200:
         if fvk.get_sm_version() != 100:
             raise RuntimeError(f"flashrt_b200 is built for sm_100a only; device reports sm_{fvk.get_sm_version()}")
         self.num_steps, self.chunk_size, self.prefix_len, self.layers = num_steps, chunk_size, prefix_len, layers
-        self.use_pdl, self.use_cuda_graph = use_pdl, use_cuda_graph
+        self.use_pdl, self.use_cuda_graph, self.fuse_epilogues = use_pdl, use_cuda_graph, fuse_epilogues
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.kv_rows = prefix_len + chunk_size
         self.WEIGHT_SPEC = build_spec(layers, num_steps)
@@ -432,5 +450,6 @@ class Pi05DecoderB200:
     def kernels_per_loop(self) -> int:
         """Launches of this library's kernels inside one replay (for reporting)."""
         L, N = self.layers, self.num_steps
-        per_layer = 9  # qkv gemm, rope split, attention, o gemm, norm, gate|up gemm, geglu, down gemm, norm
+        # qkv gemm (+rope split), attention, o gemm, norm, gate|up gemm (+geglu), down gemm, norm
+        per_layer = 7 if self.fuse_epilogues else 9
         return N * (1 + 1 + per_layer * L + 2)

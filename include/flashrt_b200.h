@@ -102,10 +102,27 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
  * cutlass_fp8_*_bf16out        csrc/bindings.cpp:2388-2422 -> csrc/gemm/cutlass_sm100.cu:75-125
  *   D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . W(N,K)^T + bias(N)
  *   A, W: E4M3, row-major, K contiguous, 16-byte aligned, K % 16 == 0.  d_scale_* and bias may be NULL.
- *   splits: 0 = choose; else split-K factor in [1, 8] (reduced inside a thread-block cluster). */
+ *   splits: 0 = choose; else split-K factor in [1, 16] (reduced inside a thread-block cluster). */
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream);
+/* The same GEMM (M <= 256) with the kernel that follows it in the decoder fused into its epilogue.
+ *
+ * QKV projection + qkv_split_rope[_devpos] (csrc/bindings.cpp:1071-1099 -> csrc/kernels/rope.cu:135-277):
+ *   the (M, q_dim+k_dim+v_dim) result is rounded to bf16, q and k parts are rotated pairwise with
+ *   rope (M, head_dim) = [cos0, sin0, cos1, sin1, ...]; Q -> (M, q_dim); K / V rows -> row (*devpos + m)
+ *   of Kout / Vout (devpos NULL: row m).  Byte-identical to frt_b200_gemm_fp8_nt (same `splits`) followed by
+ *   frt_b200_qkv_split_rope. */
+int frt_b200_gemm_fp8_nt_rope_split(const void* A, const void* W, int M, int K, const float* d_scale_a,
+                                    const float* d_scale_b, const void* rope, void* Q, void* Kout, void* Vout,
+                                    const int* devpos, int q_dim, int k_dim, int v_dim, int head_dim, int splits,
+                                    int flags, void* stream);
+/* gate|up projection + gate_geglu_merged_fp8 (csrc/bindings.cpp:1037-1044 -> csrc/kernels/activation.cu:249-279):
+ *   W (2*half, K), rows [0, half) = gate, [half, 2*half) = up; out8 (M, half) e4m3 with scale *d_out_scale.
+ *   half % 64 == 0.  Byte-identical to frt_b200_gemm_fp8_nt (same `splits`) followed by frt_b200_geglu_fp8. */
+int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int M, int half, int K,
+                                   const float* d_scale_a, const float* d_scale_b, const float* d_out_scale,
+                                   int splits, int flags, void* stream);
 /* Reads (and optionally clears) the device status word of the tensor-core kernels.  0 = no bounded wait
  * ever gave up; otherwise (code | blockIdx.x << 8), code 1 = TMA producer, 2 = MMA issuer, 3 = epilogue.
  * Synchronises the device (a cudaMemcpyFromSymbol): do not call inside graph capture. */
@@ -120,13 +137,15 @@ int frt_b200_gemm_status(int reset);
  *   num_heads_q / num_heads_kv must divide 128.  O_fp8 + out_scale: optional fused
  *   e4m3(clamp(O * (1 / *out_scale), +-448)) written with O's indexing (NULL to skip).
  *   lse: optional (batch, num_heads_q, seqlen_q) fp32; seqused_k: optional device int (valid keys).
- *   kv_splits: 0 = choose, else 1..8 (combined inside a thread-block cluster; no scratch buffers). */
+ *   kv_splits: 0 = choose, else 1..8, rounded down to a power of two (combined inside a thread-block cluster;
+ *   no scratch buffers).  kv_static_rows: leading K/V rows that the previous kernel in the stream does not
+ *   write (with flags bit0 they are fetched before that kernel has finished); pass 0 if unsure. */
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
                                 int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
                                 const long long* q_strides, const long long* k_strides, const long long* v_strides,
-                                const long long* o_strides, float softmax_scale, int kv_splits, int flags,
-                                void* stream);
+                                const long long* o_strides, float softmax_scale, int kv_splits, int kv_static_rows,
+                                int flags, void* stream);
 /* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
 int frt_b200_attention_status(int reset);
 

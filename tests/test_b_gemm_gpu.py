@@ -130,3 +130,74 @@ def test_small_bf16_projections():
         got2 = O.bf16_bits_to_f32(d_D2.get())
         ref2 = ref + O.bf16_bits_to_f32(bias)[None, :]
         assert np.abs(got2 - ref2).max() <= np.abs(ref2).max() * 2.0 ** -8 + 1e-3 * rms
+
+
+@pytest.mark.parametrize("M,splits", [(50, 4), (50, 1), (10, 8), (64, 2)])
+def test_fused_rope_split_epilogue_equals_two_kernels(M, splits):
+    """QKV GEMM with the RoPE/split/KV-append epilogue == GEMM then qkv_split_rope, byte for byte
+    (the reference's own fused-vs-unfused contract, tests/test_pi05_decoder_fp4_kernels.py:45-61)."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M + splits)
+    K, q_dim, k_dim, v_dim, hd, pos = 1024, 2048, 256, 256, 256, 768
+    N = q_dim + k_dim + v_dim
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    inv_freq = 1.0 / (10000 ** (np.arange(0, hd, 2, dtype=np.float64) / hd))
+    ph = np.arange(pos, pos + M, dtype=np.float64)[:, None] * inv_freq[None, :]
+    rope = O.f32_to_bf16_bits(np.stack([np.cos(ph), np.sin(ph)], -1).reshape(M, hd).astype(np.float32))
+    d_A, d_W, d_sa, d_sb, d_rope = Dev(A), Dev(W), f32(sa), f32(sb), Dev(rope)
+    g = fvk.GemmRunner()
+    cache0 = rand_bf16(rng, (pos + M + 2, 256))
+    # two kernels
+    d_qkv, d_Q1, d_K1, d_V1 = zeros((M, N), np.uint16), zeros((M, q_dim), np.uint16), Dev(cache0), Dev(cache0)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_qkv.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits)
+    fvk.qkv_split_rope(d_qkv.ptr, d_rope.ptr, d_Q1.ptr, d_K1.ptr + pos * 512, d_V1.ptr + pos * 512, M, q_dim, k_dim,
+                       v_dim, hd, 0)
+    # one kernel
+    d_Q2, d_K2, d_V2 = zeros((M, q_dim), np.uint16), Dev(cache0), Dev(cache0)
+    g.fp8_nt_dev_rope_split(d_A.ptr, d_W.ptr, M, K, d_sa.ptr, d_sb.ptr, d_rope.ptr, d_Q2.ptr, d_K2.ptr + pos * 512,
+                            d_V2.ptr + pos * 512, q_dim, k_dim, v_dim, hd, 0, splits=splits)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_Q1.get(), d_Q2.get())
+    assert np.array_equal(d_K1.get(), d_K2.get())
+    assert np.array_equal(d_V1.get(), d_V2.get())
+    # and both agree with the oracle chain on the oracle's GEMM
+    Kr, Vr = cache0.copy(), cache0.copy()
+    Q_ref = O.qkv_split_rope(d_qkv.get(), rope, Kr, Vr, pos, q_dim, k_dim, v_dim, hd)
+    assert np.array_equal(d_Q2.get(), Q_ref) and np.array_equal(d_K2.get(), Kr) and np.array_equal(d_V2.get(), Vr)
+
+
+@pytest.mark.parametrize("M,splits", [(50, 2), (50, 1), (16, 8), (100, 2)])
+def test_fused_geglu_epilogue_equals_two_kernels(M, splits):
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(M * 3 + splits)
+    K, H = 1024, 4096
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, 2 * H, K, 0.03)
+    d_A, d_W, d_sa, d_sb, d_so = Dev(A), Dev(W), f32(sa), f32(sb), f32(0.004)
+    g = fvk.GemmRunner()
+    d_merged, d_o1, d_o2 = zeros((M, 2 * H), np.uint16), zeros((M, H), np.uint8), zeros((M, H), np.uint8)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_merged.ptr, M, 2 * H, K, d_sa.ptr, d_sb.ptr, 0, splits=splits)
+    fvk.gate_geglu_merged_fp8(d_merged.ptr, d_o1.ptr, M, H, d_so.ptr, 0)
+    g.fp8_nt_dev_geglu_fp8(d_A.ptr, d_W.ptr, d_o2.ptr, M, H, K, d_sa.ptr, d_sb.ptr, d_so.ptr, 0, splits=splits)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_o1.get(), d_o2.get())
+    assert np.array_equal(d_o2.get(), O.geglu_fp8(d_merged.get(), 0.004))
+    assert (d_o2.get() != 0).mean() > 0.5
+
+
+@pytest.mark.parametrize("N,K,splits", [(1024, 2048, 16), (1024, 4096, 16), (2560, 1024, 4)])
+def test_split_k_over_large_clusters(N, K, splits):
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(N + K)
+    M = 50
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    d_A, d_W, d_D, d_sa, d_sb = Dev(A), Dev(W), zeros((M, N), np.uint16), f32(sa), f32(sb)
+    fvk.GemmRunner().fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits)
+    got = d_D.get()
+    assert fvk.tensor_core_status() == 0
+    _check(got, _ref(A, W, sa, sb))

@@ -75,7 +75,7 @@ def test_full_depth_loop_runs_and_is_finite():
     assert a.shape == (50, 32) and np.isfinite(a).all()
     assert np.array_equal(a, b)
     assert 0.05 < float(np.abs(a).mean()) < 50
-    assert model.frontend.kernels_per_loop() == 10 * (2 + 9 * 18 + 2)
+    assert model.frontend.kernels_per_loop() == 10 * (2 + 7 * 18 + 2)
 
 
 def test_refuses_wrong_inputs():
