@@ -640,15 +640,16 @@ static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int sp
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
 
-// Split-K factor: the largest power of two (<= 16, the cluster limit with the non-portable size enabled) that
-// keeps tiles x splits within one wave of the SMs and leaves every split at least one k-block.
+// Split-K factor.  Measured on B200 at M = 50 (graph of back-to-back launches): the cluster exchange costs about
+// as much as streaming 64 KB per CTA, so splitting pays only while it at least halves the bytes per CTA and the
+// grid still fits well inside one wave; clusters larger than 4 were never faster.
 static int pick_splits(int tiles, int kb_total, int requested) {
     if (requested > 0) {
         int s = requested > 16 ? 16 : requested;
         return s > kb_total ? kb_total : s;
     }
     int s = 1;
-    while (s < 8 && tiles * s * 2 <= 148 && s * 2 <= kb_total) s *= 2;
+    while (s < 4 && tiles * s * 2 <= 120 && s * 2 <= kb_total) s *= 2;
     return s;
 }
 
