@@ -112,6 +112,53 @@ def gpu_copy(dst, src, nbytes, stream=0):
     call("frt_b200_copy", dst, src, nbytes, stream)
 
 
+# ------------------------------------------------------------------ video-DiT producers (csrc/bindings.cpp:879,1122,2802-2826,3427-3726)
+def layer_norm(x, weight, bias, out, seq_len, dim, eps=1e-6, stream=0, *, pdl=False):
+    call("frt_b200_layer_norm", x, weight, bias or None, None, None, 0, None, out, None, seq_len, dim, eps, _f(pdl),
+         stream)
+
+
+def ada_layer_norm_bf16(x, scale, shift, out, seq_len, dim, eps=1e-6, stream=0, *, pdl=False):
+    """scale / shift: one (dim,) row shared by all tokens."""
+    call("frt_b200_layer_norm", x, None, None, scale, shift, 0, None, out, None, seq_len, dim, eps, _f(pdl), stream)
+
+
+def ada_layer_norm_bf16_per_token(x, scale, shift, out, seq_len, dim, eps=1e-6, stream=0, *, pdl=False):
+    """scale / shift: (seq_len, dim), one row per token."""
+    call("frt_b200_layer_norm", x, None, None, scale, shift, dim, None, out, None, seq_len, dim, eps, _f(pdl), stream)
+
+
+def ada_layer_norm_fp8(x_bf16, scale_bf16, shift_bf16, out_fp8, act_scale, seq_len, dim, eps=1e-6, stream=0, *,
+                       pdl=False, mod_stride=0):
+    call("frt_b200_layer_norm", x_bf16, None, None, scale_bf16, shift_bf16, mod_stride, out_fp8, None, act_scale,
+         seq_len, dim, eps, _f(pdl), stream)
+
+
+def qkv_split_norm_rope_bf16(packed_qkv, norm_q_w, norm_k_w, freqs_re, freqs_im, q_rope_out, k_rope_out, B, L_v, N,
+                             D_h, seq_len, eps=1e-6, stream=0, *, pdl=False):
+    call("frt_b200_qkv_split_norm_rope", packed_qkv, norm_q_w, norm_k_w, freqs_re, freqs_im, q_rope_out, k_rope_out,
+         B, L_v, N, D_h, seq_len, eps, _f(pdl), stream)
+
+
+def bias_gelu_quantize_fp8_static_bf16(in_bf16, bias_bf16, out_fp8, act_scale, M, N, stream=0, *, pdl=False):
+    call("frt_b200_bias_gelu_quantize_fp8", in_bf16, bias_bf16 or None, out_fp8, act_scale, M, N, _f(pdl), stream)
+
+
+def bias_gate_mul_residual_bf16(residual, x, bias, gate, seq_len, dim, stream=0, *, pdl=False, gate_stride=None):
+    gs = dim if gate_stride is None else gate_stride
+    call("frt_b200_bias_gate_mul_residual", residual, x, bias or None, gate, gs, seq_len, dim, _f(pdl), stream)
+
+
+def add_bias_bf16(x, b, S, D, stream=0, *, pdl=False):
+    call("frt_b200_add_bias", x, b, S, D, _f(pdl), stream)
+
+
+def adaln_modulation6_bf16(adaln_params, layer_modulation, out0, out1, out2, out3, out4, out5, B, S, D, stream=0, *,
+                           pdl=False):
+    call("frt_b200_adaln_modulation6", adaln_params, layer_modulation, out0, out1, out2, out3, out4, out5, B, S, D,
+         _f(pdl), stream)
+
+
 # ------------------------------------------------------------------ quantise (csrc/bindings.cpp:1191-1211)
 def quantize_fp8_static(input, output, d_scale, n, stream=0, *, pdl=False):  # noqa: A002 (reference kwarg name)
     call("frt_b200_quantize_fp8_static", input, output, d_scale, n, _f(pdl), stream)

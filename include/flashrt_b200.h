@@ -149,6 +149,40 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
 /* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
 int frt_b200_attention_status(int reset);
 
+/* ---------------------------------------------------------------- video-DiT (Wan-shape) fused producers
+ * ada_layer_norm_fp8                 csrc/bindings.cpp:3482-3495 -> csrc/quantize/ada_layer_norm_fp8.cu:58-147
+ * ada_layer_norm_bf16[_per_token]    csrc/bindings.cpp:2802-2816 -> csrc/kernels/dit_bf16.cu:151-278
+ * layer_norm                         csrc/bindings.cpp:879-885   -> csrc/kernels/norm.cu:113-162
+ *   y = (x - mean) * inv_std  [* weight + bias]  [* (1 + scale) + shift], statistics over `dim` per row, eps inside
+ *   the square root; scale / shift rows at + r * mod_stride (0 = one shared (dim,) row); weight / bias (dim,).
+ *   out_fp8 != NULL: e4m3(clamp(bf16(y) * (1 / *d_scale), +-448)) (the value is rounded through bf16 first, as the
+ *   reference does); otherwise out_bf16 = bf16(y).  Exactly one of out_fp8 / out_bf16.  dim % 8 == 0, dim <= 8192. */
+int frt_b200_layer_norm(const void* x, const void* weight, const void* bias, const void* scale, const void* shift,
+                        long long mod_stride, void* out_fp8, void* out_bf16, const float* d_scale, int rows, int dim,
+                        float eps, int flags, void* stream);
+/* qkv_split_norm_rope_bf16           csrc/bindings.cpp:3574 -> csrc/quantize/qkv_split_norm_rope_bf16.cu:16-140
+ *   packed_qkv (B*L, 3*dim) bf16 = [q | k | v], dim = N * D_h.  q, k: RMSNorm over the full width dim with weights
+ *   norm_q_w / norm_k_w, then complex pairs (2c, 2c+1) of every head multiplied by freqs_re/im[t, c] (fp32,
+ *   (>= seq_len, D_h/2)); rows with t = row % L >= seq_len are normalised but not rotated.  V stays in packed_qkv. */
+int frt_b200_qkv_split_norm_rope(const void* packed_qkv, const void* norm_q_w, const void* norm_k_w,
+                                 const float* freqs_re, const float* freqs_im, void* q_out, void* k_out, int B, int L,
+                                 int N, int D_h, int seq_len, float eps, int flags, void* stream);
+/* bias_gelu_quantize_fp8_static_bf16 csrc/bindings.cpp:3427-3440 -> csrc/quantize/bias_gelu_quantize_fp8.cu:24-49
+ *   out (M, N) e4m3 = clamp(gelu_tanh(in + bias) * (1 / *d_scale), +-448); bias (N,) or NULL; N % 8 == 0. */
+int frt_b200_bias_gelu_quantize_fp8(const void* in_bf16, const void* bias, void* out_fp8, const float* d_scale,
+                                    long long M, int N, int flags, void* stream);
+/* bias_gate_mul_residual_bf16        csrc/bindings.cpp:1122-1131 -> csrc/kernels/elementwise.cu:1648-1683
+ *   residual (rows, dim) += (x + bias) * gate; gate rows at + r * gate_stride (0 = shared row); bias (dim,) or NULL. */
+int frt_b200_bias_gate_mul_residual(void* residual, const void* x, const void* bias, const void* gate,
+                                    long long gate_stride, long long rows, int dim, int flags, void* stream);
+/* add_bias_bf16                      csrc/bindings.cpp:2818-2826:  x (rows, dim) += bias (dim,) */
+int frt_b200_add_bias(void* x, const void* bias, long long rows, int dim, int flags, void* stream);
+/* adaln_modulation6_bf16             csrc/bindings.cpp:3705-3726 -> csrc/kernels/elementwise.cu:603-645
+ *   out_j (B, S, D) bf16 = adaln_params (B, S, 6, D) fp32 [:, :, j, :] + layer_modulation (6, D) fp32 [j], j = 0..5 */
+int frt_b200_adaln_modulation6(const float* adaln_params, const float* layer_modulation, void* out0, void* out1,
+                               void* out2, void* out3, void* out4, void* out5, int B, int S, int D, int flags,
+                               void* stream);
+
 /* ---------------------------------------------------------------- small bf16 projections, copies, queries
  * GemmRunner::bf16_nn          csrc/bindings.cpp:662-667  (action in/out projections 32 <-> 1024)
  *   D(M,N) = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate != 0); B bf16 row-major (K,N).

@@ -45,6 +45,8 @@ def lib() -> C.CDLL:
         L.orc_det_gelu_tanh.restype = C.c_float
         L.orc_det_gelu_tanh.argtypes = [C.c_float]
         L.orc_amax_scale.restype = C.c_float
+        L.orc_det_gelu_tanh_form.restype = C.c_float
+        L.orc_det_gelu_tanh_form.argtypes = [C.c_float]
         _LIB = L
     return _LIB
 
@@ -210,3 +212,54 @@ def attention(q_bits, k_bits, v_bits, scale, kv_len=None):
             out[b, :, h, :] = (p / l) @ v[b, :, h // g, :]
             lse[b, h, :] = (m + np.log(l))[:, 0]
     return out.astype(np.float32), lse
+
+
+# ---------------------------------------------------------------- video-DiT producers
+def layer_norm(x, weight=None, bias=None, scale=None, shift=None, mod_stride=0, out="bf16", eps=1e-6, qscale=1.0):
+    x = _u16(x)
+    rows, dim = x.shape
+    o8 = np.zeros((rows, dim), np.uint8) if out == "fp8" else None
+    o16 = np.zeros((rows, dim), np.uint16) if out != "fp8" else None
+    a = [None if t is None else _u16(t) for t in (weight, bias, scale, shift)]
+    lib().orc_layer_norm(_p(x), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), C.c_longlong(mod_stride), _p(o8), _p(o16),
+                         C.c_int(rows), C.c_int(dim), C.c_float(eps), C.c_float(qscale))
+    return o8 if out == "fp8" else o16
+
+
+def qkv_split_norm_rope(packed, wq, wk, fre, fim, B, L, N, D_h, seq_len, eps=1e-6):
+    packed, wq, wk = _u16(packed), _u16(wq), _u16(wk)
+    fre = np.ascontiguousarray(fre, np.float32)
+    fim = np.ascontiguousarray(fim, np.float32)
+    dim = N * D_h
+    q = np.zeros((B * L, dim), np.uint16)
+    k = np.zeros((B * L, dim), np.uint16)
+    lib().orc_qkv_split_norm_rope(_p(packed), _p(wq), _p(wk), _p(fre), _p(fim), _p(q), _p(k), C.c_int(B), C.c_int(L),
+                                  C.c_int(N), C.c_int(D_h), C.c_int(seq_len), C.c_float(eps))
+    return q, k
+
+
+def bias_gelu_quantize_fp8(x, bias, scale):
+    x = _u16(x)
+    M, N = x.shape
+    out = np.zeros((M, N), np.uint8)
+    lib().orc_bias_gelu_quantize_fp8(_p(x), _p(None if bias is None else _u16(bias)), _p(out), C.c_longlong(M),
+                                     C.c_int(N), C.c_float(scale))
+    return out
+
+
+def bias_gate_mul_residual(res, x, bias, gate, gate_stride):
+    res = _u16(res).copy()
+    rows, dim = res.shape
+    lib().orc_bias_gate_mul_residual(_p(res), _p(None if x is None else _u16(x)), _p(None if bias is None else _u16(bias)),
+                                     _p(None if gate is None else _u16(gate)), C.c_longlong(gate_stride),
+                                     C.c_longlong(rows), C.c_int(dim))
+    return res
+
+
+def adaln_modulation6(params, layer_mod):
+    params = np.ascontiguousarray(params, np.float32)
+    layer_mod = np.ascontiguousarray(layer_mod, np.float32)
+    BS, six, D = params.reshape(-1, 6, params.shape[-1]).shape
+    out = np.zeros((6, BS, D), np.uint16)
+    lib().orc_adaln_modulation6(_p(params), _p(layer_mod), _p(out), C.c_longlong(BS), C.c_int(D))
+    return out

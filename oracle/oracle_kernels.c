@@ -336,3 +336,155 @@ void orc_gemm_fp8(const uint8_t* A, const uint8_t* B, uint16_t* D, float* Df, in
             if (Df) Df[(size_t)m * N + n] = v;
         }
 }
+
+/* ------------------------------------------------------------------ video-DiT (Wan-shape) producers */
+/* block-wide sum as the kernels do it: threads own 8 consecutive elements, xor-butterfly per 32 threads,
+ * warp totals added in order.  part[] holds the per-thread partial sums. */
+static float tree_sum_threads(const float* part, int nthreads) {
+    float tot = 0.0f;
+    for (int w = 0; w < nthreads / 32; ++w) {
+        float lane[32], nxt[32];
+        memcpy(lane, part + w * 32, sizeof(lane));
+        for (int off = 16; off >= 1; off >>= 1) {
+            for (int l = 0; l < 32; ++l) nxt[l] = lane[l] + lane[l ^ off];
+            memcpy(lane, nxt, sizeof(lane));
+        }
+        tot = (w == 0) ? lane[0] : tot + lane[0];
+    }
+    return tot;
+}
+
+/* 0.5 x (1 + tanh(0.7978845608 (x + 0.044715 x^3))), tanh(u) = 1 - 2 / (1 + e^{2u})
+ * csrc/quantize/bias_gelu_quantize_fp8.cu:18-23 */
+static inline float det_gelu_tanh_form(float x) {
+    float x3 = (x * x) * x;
+    float u = 0.7978845608f * fmaf(0.044715f, x3, x);
+    float e = det_expf(2.0f * u);
+    float th = 1.0f - 2.0f / (1.0f + e);
+    return (0.5f * x) * (1.0f + th);
+}
+float orc_det_gelu_tanh_form(float x) { return det_gelu_tanh_form(x); }
+
+/* ada_layer_norm_fp8 (csrc/quantize/ada_layer_norm_fp8.cu:58-147), ada_layer_norm_bf16[_per_token]
+ * (csrc/kernels/dit_bf16.cu:151-278), layer_norm (csrc/kernels/norm.cu:113-162).
+ * Two-pass statistics (mean, then mean of squared deviations), modulated value rounded through bf16 before FP8. */
+void orc_layer_norm(const uint16_t* x, const uint16_t* weight, const uint16_t* bias, const uint16_t* scale,
+                    const uint16_t* shift, long long mod_stride, uint8_t* out_fp8, uint16_t* out_bf16, int rows,
+                    int dim, float eps, float qscale) {
+    int nthreads = ((dim / 8 + 31) / 32) * 32;
+    float inv_a = 1.0f / qscale;
+    static float part[1024], v[8192];
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + (size_t)r * dim;
+        for (int t = 0; t < nthreads; ++t) {
+            float s = 0.0f;
+            for (int i = 0; i < 8; ++i) {
+                int c = t * 8 + i;
+                if (c < dim) { v[c] = bf16_to_f32(xr[c]); s = s + v[c]; }
+            }
+            part[t] = s;
+        }
+        float mean = tree_sum_threads(part, nthreads) / (float)dim;
+        for (int t = 0; t < nthreads; ++t) {
+            float q = 0.0f;
+            for (int i = 0; i < 8; ++i) {
+                int c = t * 8 + i;
+                if (c < dim) { v[c] = v[c] - mean; q = fmaf(v[c], v[c], q); }
+            }
+            part[t] = q;
+        }
+        float var = tree_sum_threads(part, nthreads) / (float)dim + eps;
+        float inv_std = 1.0f / sqrtf(var);
+        for (int c = 0; c < dim; ++c) {
+            float n = v[c] * inv_std;
+            if (weight) n = fmaf(n, bf16_to_f32(weight[c]), bias ? bf16_to_f32(bias[c]) : 0.0f);
+            if (scale) n = fmaf(n, 1.0f + bf16_to_f32(scale[(size_t)r * mod_stride + c]),
+                                bf16_to_f32(shift[(size_t)r * mod_stride + c]));
+            uint16_t b16 = f32_to_bf16(n);
+            if (out_bf16) out_bf16[(size_t)r * dim + c] = b16;
+            else out_fp8[(size_t)r * dim + c] = f32_to_e4m3(clamp448(bf16_to_f32(b16) * inv_a));
+        }
+    }
+}
+
+/* qkv_split_norm_rope_bf16, csrc/quantize/qkv_split_norm_rope_bf16.cu:16-140 */
+void orc_qkv_split_norm_rope(const uint16_t* packed, const uint16_t* wq, const uint16_t* wk, const float* fre,
+                             const float* fim, uint16_t* q_out, uint16_t* k_out, int B, int L, int N, int D_h,
+                             int seq_len, float eps) {
+    int dim = N * D_h;
+    int nthreads = ((dim / 8 + 31) / 32) * 32;
+    static float pq[1024], pk[1024];
+    for (int row = 0; row < B * L; ++row) {
+        int t = row % L;
+        const uint16_t* q = packed + (size_t)row * 3 * dim;
+        const uint16_t* k = q + dim;
+        for (int th = 0; th < nthreads; ++th) {
+            float sq = 0.0f, sk = 0.0f;
+            for (int i = 0; i < 8; ++i) {
+                int c = th * 8 + i;
+                if (c < dim) {
+                    float a = bf16_to_f32(q[c]), b = bf16_to_f32(k[c]);
+                    sq = fmaf(a, a, sq);
+                    sk = fmaf(b, b, sk);
+                }
+            }
+            pq[th] = sq;
+            pk[th] = sk;
+        }
+        float inv_q = 1.0f / sqrtf(tree_sum_threads(pq, nthreads) / (float)dim + eps);
+        float inv_k = 1.0f / sqrtf(tree_sum_threads(pk, nthreads) / (float)dim + eps);
+        for (int c = 0; c < dim; c += 2) {
+            int cp = (c % D_h) >> 1;
+            float qre = (bf16_to_f32(q[c]) * inv_q) * bf16_to_f32(wq[c]);
+            float qim = (bf16_to_f32(q[c + 1]) * inv_q) * bf16_to_f32(wq[c + 1]);
+            float kre = (bf16_to_f32(k[c]) * inv_k) * bf16_to_f32(wk[c]);
+            float kim = (bf16_to_f32(k[c + 1]) * inv_k) * bf16_to_f32(wk[c + 1]);
+            uint16_t* qo = q_out + (size_t)row * dim + c;
+            uint16_t* ko = k_out + (size_t)row * dim + c;
+            if (t < seq_len) {
+                float fr = fre[(size_t)t * (D_h / 2) + cp], fi = fim[(size_t)t * (D_h / 2) + cp];
+                qo[0] = f32_to_bf16(fmaf(qre, fr, -(qim * fi)));
+                qo[1] = f32_to_bf16(fmaf(qre, fi, qim * fr));
+                ko[0] = f32_to_bf16(fmaf(kre, fr, -(kim * fi)));
+                ko[1] = f32_to_bf16(fmaf(kre, fi, kim * fr));
+            } else {
+                qo[0] = f32_to_bf16(qre); qo[1] = f32_to_bf16(qim);
+                ko[0] = f32_to_bf16(kre); ko[1] = f32_to_bf16(kim);
+            }
+        }
+    }
+}
+
+/* bias_gelu_quantize_fp8_static_bf16, csrc/quantize/bias_gelu_quantize_fp8.cu:24-49 */
+void orc_bias_gelu_quantize_fp8(const uint16_t* in, const uint16_t* bias, uint8_t* out, long long M, int N,
+                                float scale) {
+    float inv_s = 1.0f / scale;
+    for (long long i = 0; i < M * N; ++i) {
+        float v = bf16_to_f32(in[i]);
+        if (bias) v = v + bf16_to_f32(bias[i % N]);
+        out[i] = f32_to_e4m3(clamp448(det_gelu_tanh_form(v) * inv_s));
+    }
+}
+
+/* bias_gate_mul_residual_bf16 (csrc/kernels/elementwise.cu:1648-1683): r += (x + bias) * gate;
+ * add_bias_bf16: x += bias (gate == NULL) */
+void orc_bias_gate_mul_residual(uint16_t* res, const uint16_t* x, const uint16_t* bias, const uint16_t* gate,
+                                long long gate_stride, long long rows, int dim) {
+    for (long long r = 0; r < rows; ++r)
+        for (int c = 0; c < dim; ++c) {
+            size_t i = (size_t)r * dim + c;
+            float b = bias ? bf16_to_f32(bias[c]) : 0.0f;
+            float o;
+            if (gate) o = fmaf(bf16_to_f32(x[i]) + b, bf16_to_f32(gate[(size_t)r * gate_stride + c]), bf16_to_f32(res[i]));
+            else o = bf16_to_f32(res[i]) + b;
+            res[i] = f32_to_bf16(o);
+        }
+}
+
+/* adaln_modulation6_bf16, csrc/kernels/elementwise.cu:603-645 */
+void orc_adaln_modulation6(const float* params, const float* layer_mod, uint16_t* out6, long long BS, int D) {
+    for (long long bs = 0; bs < BS; ++bs)
+        for (int j = 0; j < 6; ++j)
+            for (int d = 0; d < D; ++d)
+                out6[((size_t)j * BS + bs) * D + d] = f32_to_bf16(params[(bs * 6 + j) * D + d] + layer_mod[(size_t)j * D + d]);
+}

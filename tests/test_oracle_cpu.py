@@ -187,3 +187,36 @@ def test_gemm_and_attention_oracles_vs_torch():
     tq, tk, tv = (torch.from_numpy(O.bf16_bits_to_f32(a)) for a in (q, k, v))
     ref = R.attention(tq[0], tk[0], tv[0], 0.125)
     assert torch.allclose(torch.from_numpy(out[0]), ref, atol=1e-5)
+
+
+def test_video_dit_oracle_vs_plain_formulas():
+    rng = np.random.default_rng(7)
+    rows, dim = 6, 3072
+    x = _bf(rng, (rows, dim), 1.5)
+    sc, sh = _bf(rng, (1, dim), 0.3), _bf(rng, (1, dim), 0.3)
+    got = torch.from_numpy(O.bf16_bits_to_f32(O.layer_norm(x, scale=sc, shift=sh, out="bf16"))).double()
+    xf = torch.from_numpy(O.bf16_bits_to_f32(x)).double()
+    n = (xf - xf.mean(-1, keepdim=True)) * torch.rsqrt(xf.var(-1, keepdim=True, unbiased=False) + 1e-6)
+    ref = n * (1 + torch.from_numpy(O.bf16_bits_to_f32(sc)).double()) + torch.from_numpy(O.bf16_bits_to_f32(sh)).double()
+    assert (got - ref).abs().max() <= ref.abs().max() * 2.0 ** -8
+    # tanh-form GELU
+    L = O.lib()
+    gs = np.linspace(-10, 10, 4001).astype(np.float32)
+    gg = np.array([L.orc_det_gelu_tanh_form(float(v)) for v in gs], dtype=np.float64)
+    tg = torch.nn.functional.gelu(torch.tensor(gs, dtype=torch.float64), approximate="tanh").numpy()
+    assert np.abs(gg - tg).max() < 3e-6
+    # q/k RMSNorm over the full width + complex-pair rotation
+    B, Lt, N, Dh = 1, 3, 2, 64
+    packed = _bf(rng, (B * Lt, 3 * N * Dh))
+    wq, wk = _bf(rng, (N * Dh,)), _bf(rng, (N * Dh,))
+    ang = rng.uniform(0, 6.28, (Lt, Dh // 2))
+    q, k = O.qkv_split_norm_rope(packed, wq, wk, np.cos(ang), np.sin(ang), B, Lt, N, Dh, seq_len=2)
+    pf = torch.from_numpy(O.bf16_bits_to_f32(packed)).double()
+    qf = pf[:, :N * Dh]
+    qn = qf * torch.rsqrt(qf.pow(2).mean(-1, keepdim=True) + 1e-6) * torch.from_numpy(O.bf16_bits_to_f32(wq)).double()
+    qc = torch.view_as_complex(qn.reshape(Lt, N, Dh // 2, 2).contiguous())
+    rot = torch.polar(torch.ones(Lt, Dh // 2, dtype=torch.float64), torch.from_numpy(ang))
+    ref = torch.view_as_real(qc * rot[:, None, :]).reshape(Lt, N * Dh)
+    got = torch.from_numpy(O.bf16_bits_to_f32(q)).double()
+    assert (got[:2] - ref[:2]).abs().max() <= 2.0 ** -7 * ref.abs().max()
+    assert (got[2] - qn[2]).abs().max() <= 2.0 ** -7 * qn.abs().max()       # row beyond seq_len: not rotated
