@@ -34,6 +34,15 @@ namespace frt {
 
 __device__ int g_attn_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
 
+#ifdef FRT_TRACE
+__device__ long long g_atrace[64];
+#define ATRACE(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_atrace[i] = clock64(); } while (0)
+#define ATRACE0(i) do { if (threadIdx.x == 0) ATRACE(i); } while (0)
+#else
+#define ATRACE(i)
+#define ATRACE0(i)
+#endif
+
 // ------------------------------------------------------------------ tensor maps (bf16, up to 5-D)
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -106,6 +115,10 @@ struct AttnParams {
     int B, Sq, Skv, Hq, Hkv, G;
     int chunks_total;            // ceil(Skv / BKV)
     int kv_static_rows;          // leading K/V rows that the previous kernel in the stream does not write
+    // split-KV through global scratch (same buffers and layouts as the reference's FA2 split-kv path):
+    float* o_accum;              // (splits, B, Hq, Sq, D) fp32, each split's O already divided by its row sum
+    float* lse_accum;            // (splits, B, Hq, Sq) fp32, log2-domain log-sum-exp of the split (-inf if empty)
+    unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals, readers; zero before first use
     float scale_log2;            // softmax_scale * log2(e)
 };
 
@@ -169,10 +182,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
+    ATRACE0(0);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t C = tc::cluster_nctarank();
-    const uint32_t rank = tc::cluster_ctarank();
+    // kv splits are either the CTAs of a cluster (combined through DSMEM) or, when scratch buffers are given,
+    // independent CTAs along grid z (combined through global memory)
+    const bool via_scratch = p.o_accum != nullptr;
+    const uint32_t C = via_scratch ? gridDim.z : tc::cluster_nctarank();
+    const uint32_t rank = via_scratch ? blockIdx.z : tc::cluster_ctarank();
     const int tile = blockIdx.x;
     const int hk = blockIdx.y % p.Hkv;
     const int b = blockIdx.y / p.Hkv;
@@ -344,9 +361,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc::tc_fence_after_sync();
         }
         __syncwarp();
+        ATRACE0(10);
         s_m[row] = m_run;
         s_l[row] = l_run;
-        if (!__any_sync(0xffffffffu, *abort_flag != 0)) {
+        if (via_scratch) {
+            // partial of this row (O / l, log2-domain lse) -> shared memory, row-major with xor-swizzled 16-byte
+            // chunks; the whole CTA then copies full rows to the global scratch with coalesced stores
+            const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
+            if (!aborted) {
+                const float invl = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                s_m[row] = l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    if (nchunks > 0) {                   // warp-uniform: tcgen05.ld is warp-collective
+                        tc::tmem_ld32(tmem_O + lane_off + c, v);
+                        tc::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0u;
+                    }
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const int ch = (c >> 2) + j4;
+                        *reinterpret_cast<float4*>(&red[(size_t)row * D + ((ch ^ (row & 7)) << 2)]) =
+                            make_float4(__uint_as_float(v[j4 * 4]) * invl, __uint_as_float(v[j4 * 4 + 1]) * invl,
+                                        __uint_as_float(v[j4 * 4 + 2]) * invl, __uint_as_float(v[j4 * 4 + 3]) * invl);
+                    }
+                }
+            }
+            ATRACE0(11);
+        } else if (!__any_sync(0xffffffffu, *abort_flag != 0)) {
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
                 uint32_t v[32];
@@ -371,9 +416,125 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
     }
     __syncwarp();
+    if (via_scratch) {
+        // ---------------- combine through global scratch.  All CTAs of the grid are co-resident (the host keeps
+        // the grid within one wave), each publishes its partial, waits (bounded) for the C partials of its tile and
+        // finishes D / C columns of every row.  Every global access below is coalesced: consecutive lanes touch
+        // consecutive 16-byte chunks of one row.
+        const unsigned tile_id = (unsigned)((b * p.Hkv + hk) * gridDim.x + tile);
+        unsigned* cnt = p.counters + 2 * tile_id;
+        const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;
+        __syncthreads();
+        ATRACE0(12);
+        // G divides 128, so it is a power of two: row -> (token, head) by shift / mask
+        const int gshift = 31 - __clz(p.G);
+        int rows_valid = (p.Sq - tok0) << gshift;
+        rows_valid = rows_valid > 128 ? 128 : rows_valid;
+        if (!*abort_flag) {
+#pragma unroll 4
+            for (int r = warp; r < rows_valid; r += 6) {
+                const int t = tok0 + (r >> gshift);
+                const int hq = hk * p.G + (r & (p.G - 1));
+                const size_t ridx = rank * split_stride + ((size_t)b * p.Hq + hq) * p.Sq + t;
+                float4* dst = reinterpret_cast<float4*>(p.o_accum + ridx * D);
+#pragma unroll
+                for (int ch = lane; ch < D / 4; ch += 32)
+                    __stcg(dst + ch, *reinterpret_cast<const float4*>(&red[(size_t)r * D + ((ch ^ (r & 7)) << 2)]));
+                if (lane == 0) __stcg(p.lse_accum + ridx, s_m[r]);
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        ATRACE0(13);
+        if (threadIdx.x == 0) {
+            atomicAdd(cnt, 1u);
+            bool ok = false;
+            for (uint32_t it = 0;; ++it) {
+                unsigned seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
+                if (seen >= C) { ok = true; break; }
+                if (*abort_flag) break;
+                if ((it & 15) == 15 && tc::global_timer_ns() > deadline) break;
+                __nanosleep(20);
+            }
+            if (!ok) {
+                if (!*abort_flag) atomicCAS(&g_attn_status, 0, AERR_SOFTMAX | (blockIdx.x << 8));
+                *abort_flag = 1;
+            }
+        }
+        __syncthreads();
+        ATRACE0(14);
+        if (!*abort_flag) {
+            const int cpr = dper >> 2;                            // 16-byte chunks of this rank's slice per row
+            const int d0 = (int)rank * dper;
+            const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+            const int cshift = 31 - __clz(cpr);                   // cpr is a power of two
+#pragma unroll 2
+            for (int idx = threadIdx.x; idx < rows_valid * cpr; idx += 192) {
+                const int r = idx >> cshift, ch = idx & (cpr - 1);
+                const int t = tok0 + (r >> gshift);
+                const int hq = hk * p.G + (r & (p.G - 1));
+                const size_t r0 = ((size_t)b * p.Hq + hq) * p.Sq + t;
+                float w[8];
+                float4 x[8];
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    if ((uint32_t)sidx < C) {
+                        w[sidx] = __ldcg(p.lse_accum + sidx * split_stride + r0);
+                        x[sidx] = __ldcg(reinterpret_cast<const float4*>(p.o_accum + (sidx * split_stride + r0) * D + d0) + ch);
+                    } else {
+                        w[sidx] = -INFINITY;
+                        x[sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                float M = -INFINITY;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) M = fmaxf(M, w[sidx]);
+                float Lw = 0.0f;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    w[sidx] = (w[sidx] == -INFINITY) ? 0.0f : tc::ex2_approx(w[sidx] - M);
+                    Lw += w[sidx];
+                }
+                const float invL = Lw > 0.0f ? 1.0f / Lw : 0.0f;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    const float ws = w[sidx] * invL;
+                    a0 += ws * x[sidx].x; a1 += ws * x[sidx].y; a2 += ws * x[sidx].z; a3 += ws * x[sidx].w;
+                }
+                const size_t o = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs + d0 + ch * 4;
+                uint2 ob;
+                ob.x = pack_bf16x2(a0, a1);
+                ob.y = pack_bf16x2(a2, a3);
+                st_global_v2(p.O + o, ob);
+                if (p.O_fp8) {
+                    float q0, q1, q2, q3;                         // quantise the bf16-rounded value
+                    unpack_bf16x2(ob.x, q0, q1);
+                    unpack_bf16x2(ob.y, q2, q3);
+                    *reinterpret_cast<uint32_t*>(p.O_fp8 + o) =
+                        f32x4_to_e4m3x4(clamp448(__fmul_rn(q0, inv_os)), clamp448(__fmul_rn(q1, inv_os)),
+                                        clamp448(__fmul_rn(q2, inv_os)), clamp448(__fmul_rn(q3, inv_os)));
+                }
+                if (p.lse && rank == 0 && ch == 0)
+                    p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
+            }
+        }
+        // the last CTA of the tile to finish reading re-arms the counters for the next launch
+        __syncthreads();
+        ATRACE0(15);
+        if (threadIdx.x == 0) {
+            const unsigned done = atomicAdd(cnt + 1, 1u);
+            if (done == C - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
+        }
+        tc::tc_fence_before_sync();
+        __syncthreads();
+        if (warp == 5) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+        return;
+    }
     tc::cluster_sync_all();
 
-    // ---------------- combine across the kv splits: this CTA finishes columns [rank*dper, (rank+1)*dper)
+    // ---------------- combine across the kv splits (cluster path): this CTA finishes D / C columns
     if (warp < 4 && !*abort_flag) {
         const int row = warp * 32 + lane;
         const int d0 = (int)rank * dper;
@@ -506,7 +667,7 @@ static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p
     attr[na].id = cudaLaunchAttributeClusterDimension;
     attr[na].val.clusterDim.x = 1;
     attr[na].val.clusterDim.y = 1;
-    attr[na].val.clusterDim.z = splits;
+    attr[na].val.clusterDim.z = p.o_accum ? 1 : splits;
     ++na;
     if (pdl) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -515,6 +676,14 @@ static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
+    if (p.o_accum && splits > 1) {
+        // the CTAs of a tile wait for one another: the whole grid has to be resident at once
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if ((long long)tiles * p.Hkv * p.B * splits > sms) return FRT_ERR_UNSUPPORTED;
+    }
+    if (splits == 1) p.o_accum = nullptr;              // nothing to combine: plain path
     cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<D, BKV>, tmQ, tmK, tmV, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
@@ -532,12 +701,17 @@ extern "C" {
 // seqused_k: optional device int limiting the valid keys.  kv_splits: 0 = choose, else 1..8 (rounded down to a
 // power of two).  kv_static_rows: number of leading K/V rows NOT written by the previous kernel in the stream
 // (they may be fetched before that kernel finishes when flags bit0 is set); 0 if unsure.
+// o_accum / lse_accum / counters: optional split-KV scratch, all three or none.  o_accum (splits, batch, heads_q,
+// seqlen_q, head_dim) fp32, lse_accum (splits, batch, heads_q, seqlen_q) fp32 (the reference's FA2 split-kv
+// buffers), counters: 2 unsigned per (128-row tile, kv head, batch), zeroed once by the caller (the kernel re-arms
+// them).  With scratch the kv splits are ordinary CTAs that combine through global memory (faster than the
+// cluster exchange at the action-expert shape); the grid must fit the device in one wave (else -2).
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
                                 int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
                                 const long long* q_strides, const long long* k_strides, const long long* v_strides,
                                 const long long* o_strides, float softmax_scale, int kv_splits, int kv_static_rows,
-                                int flags, void* stream) {
+                                float* o_accum, float* lse_accum, void* counters, int flags, void* stream) {
     if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return FRT_ERR_INVALID;
     if (batch <= 0 || seqlen_q < 0 || seqlen_k <= 0 || num_heads_q <= 0 || num_heads_kv <= 0) return FRT_ERR_INVALID;
     if (O_fp8 && !out_scale) return FRT_ERR_INVALID;
@@ -565,6 +739,11 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
     p.G = G;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.kv_static_rows = kv_static_rows;
+    if (o_accum && lse_accum && counters) {
+        p.o_accum = o_accum;
+        p.lse_accum = lse_accum;
+        p.counters = (unsigned*)counters;
+    }
     cudaStream_t s = (cudaStream_t)stream;
     const bool pdl = flags & 1;
     const int tiles = ((seqlen_q * G + 127) / 128) * num_heads_kv * batch;
@@ -594,5 +773,11 @@ int frt_b200_attention_status(int reset) {
     }
     return v;
 }
+
+#ifdef FRT_TRACE
+int frt_atrace_read(long long* host64) {
+    return (int)cudaMemcpyFromSymbol(host64, g_atrace, sizeof(long long) * 64);
+}
+#endif
 
 }  // extern "C"

@@ -177,6 +177,11 @@ class Pi05DecoderPipeline:
         self.attn8 = z(S, DEC_NH * DEC_HD, dtype=torch.uint8)
         self.hid8 = z(S, DEC_H, dtype=torch.uint8)
         self.ones = torch.ones(DEC_D, dtype=BF16, device=dev)
+        # split-KV scratch of the attention kernel (the reference's FA2 o_accum / softmax_lse_accum buffers)
+        self.attn_splits = 8
+        self.o_accum = z(self.attn_splits, S, DEC_NH, DEC_HD, dtype=torch.float32)
+        self.lse_accum = z(self.attn_splits, DEC_NH, S, dtype=torch.float32)
+        self.attn_counters = z(2 * ((S * DEC_NH + 127) // 128), dtype=torch.int32)
         # activation scales: one per GEMM input site, per layer, per denoise step (pipeline_rtx.py:649-660)
         self.act_scale = torch.ones(N, L, len(SITES), dtype=torch.float32, device=dev)
         self.scratch_scale = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -202,10 +207,11 @@ class Pi05DecoderPipeline:
         qs = (S * DEC_NH * DEC_HD, DEC_NH * DEC_HD, DEC_HD)
         ks = (fe.kv_rows * DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD)
         fa2.fwd_bf16(self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
-                     self.attn.data_ptr(), 0, 0, 0, 1, S, T, DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
+                     self.attn.data_ptr(), 0, self.lse_accum.data_ptr(), self.o_accum.data_ptr(), 1, S, T, DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
                      1.0 / math.sqrt(DEC_HD), fe.sm_count, stream, pdl=pdl,
                      out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0, out_scale=out8_scale_ptr or 0,
-                     kv_static_rows=fe.prefix_len)
+                     kv_static_rows=fe.prefix_len, kv_splits=self.attn_splits,
+                     counters=self.attn_counters.data_ptr())
 
     # ---- the loop --------------------------------------------------------
     def transformer_decoder(self, stream: int = 0, calibrate: bool = False, step_hook=None) -> None:

@@ -139,13 +139,18 @@ int frt_b200_gemm_status(int reset);
  *   lse: optional (batch, num_heads_q, seqlen_q) fp32; seqused_k: optional device int (valid keys).
  *   kv_splits: 0 = choose, else 1..8, rounded down to a power of two (combined inside a thread-block cluster;
  *   no scratch buffers).  kv_static_rows: leading K/V rows that the previous kernel in the stream does not
- *   write (with flags bit0 they are fetched before that kernel has finished); pass 0 if unsure. */
+ *   write (with flags bit0 they are fetched before that kernel has finished); pass 0 if unsure.
+ *   o_accum, lse_accum, counters: optional split-KV scratch (all three or none): o_accum (splits, batch,
+ *   num_heads_q, seqlen_q, head_dim) fp32 and lse_accum (splits, batch, num_heads_q, seqlen_q) fp32 -- the
+ *   reference's FA2 split-kv buffers -- and counters = 2 unsigned per (128-row tile, kv head, batch), zeroed once
+ *   by the caller.  Given scratch, the kv splits combine through global memory instead of the cluster; the grid
+ *   (tiles x kv heads x batch x splits) must then fit the device in one wave, else -2 is returned. */
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
                                 int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
                                 const long long* q_strides, const long long* k_strides, const long long* v_strides,
                                 const long long* o_strides, float softmax_scale, int kv_splits, int kv_static_rows,
-                                int flags, void* stream);
+                                float* o_accum, float* lse_accum, void* counters, int flags, void* stream);
 /* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
 int frt_b200_attention_status(int reset);
 

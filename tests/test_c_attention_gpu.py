@@ -8,7 +8,7 @@ pytestmark = pytest.mark.gpu
 from oracle import oracle as O  # noqa: E402
 
 
-def _run(B, Sq, Skv, Hq, Hkv, D, splits, seed, seqused=None, fused_fp8=False, kv_extra=0):
+def _run(B, Sq, Skv, Hq, Hkv, D, splits, seed, seqused=None, fused_fp8=False, kv_extra=0, scratch=False):
     from flashrt_b200 import flash_rt_fa2 as fa2
     from gpu_util import Dev, cosine, f32, rand_bf16, zeros
     rng = np.random.default_rng(seed)
@@ -21,18 +21,25 @@ def _run(B, Sq, Skv, Hq, Hkv, D, splits, seed, seqused=None, fused_fp8=False, kv
     ks = ((Skv + kv_extra) * Hkv * D, Hkv * D, D)
     scale = 1.0 / np.sqrt(D)
     kw = dict(kv_splits=splits)
+    if scratch:      # split-KV through global scratch (FA2's o_accum / lse_accum layout) instead of the cluster
+        ns = max(splits, 1)
+        d_oacc, d_lacc = zeros((ns, B, Hq, Sq, D), np.float32), zeros((ns, B, Hq, Sq), np.float32)
+        d_cnt = zeros((2 * ((Sq * (Hq // Hkv) + 127) // 128) * Hkv * B,), np.int32)
+        kw.update(counters=d_cnt.ptr)
+    acc = (d_lacc.ptr, d_oacc.ptr) if scratch else (0, 0)
     d_o8 = d_s = None
     if fused_fp8:
         d_o8, d_s = zeros((B, Sq, Hq, D), np.uint8), f32(0.01)
         kw.update(out_fp8=d_o8.ptr, out_scale=d_s.ptr)
     if seqused is None:
-        fa2.fwd_bf16(d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, d_lse.ptr, 0, 0, B, Sq, Skv, Hq, Hkv, D, qs, ks, ks, qs,
-                     scale, 148, 0, **kw)
+        fa2.fwd_bf16(d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, d_lse.ptr, acc[0], acc[1], B, Sq, Skv, Hq, Hkv, D, qs, ks, ks,
+                     qs, scale, 148, 0, **kw)
         kv_len = Skv
     else:
         d_u = Dev(np.array([seqused], np.int32))
-        fa2.fwd_bf16_seqused(d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, d_lse.ptr, d_u.ptr, B, Sq, Skv, Hq, Hkv, D, qs, ks,
-                             ks, qs, scale, 148, 0, **kw)
+        (fa2.fwd_bf16_seqused_splitkv if scratch else fa2.fwd_bf16_seqused)(
+            d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, d_lse.ptr, d_u.ptr, *(acc if scratch else ()), B, Sq, Skv, Hq, Hkv, D,
+            qs, ks, ks, qs, scale, 148, 0, **kw)
         kv_len = seqused
     got_bits = d_o.get()
     assert fa2.attention_status() == 0
@@ -47,6 +54,8 @@ def _run(B, Sq, Skv, Hq, Hkv, D, splits, seed, seqused=None, fused_fp8=False, kv
     if fused_fp8:
         # the fused FP8 copy is the bit-exact static quantisation of the bf16 result
         assert np.array_equal(d_o8.get(), O.quantize_fp8_static(got_bits, 0.01))
+    if scratch:
+        assert (d_cnt.get() == 0).all()        # the kernel re-arms its arrival counters
 
 
 @pytest.mark.parametrize("splits", [1, 2, 8, 0])
@@ -88,3 +97,13 @@ def test_long_sequence_rows_sum_property():
     got = O.bf16_bits_to_f32(d_o.get())
     assert fa2.attention_status() == 0
     assert np.abs(got - 1.0).max() <= 2.0 ** -7
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_split_kv_through_global_scratch(splits):
+    """Same attention with the kv splits combined through the FA2-layout scratch buffers; run twice on the same
+    counters to check that they are re-armed."""
+    _run(1, 50, 818, 8, 1, 256, splits, seed=20 + splits, scratch=True)
+    _run(1, 50, 818, 8, 1, 256, splits, seed=30 + splits, scratch=True, fused_fp8=True)
+    _run(1, 17, 500, 8, 1, 256, splits, seed=40 + splits, scratch=True, seqused=333)
+    _run(2, 130, 260, 8, 2, 128, 2, seed=50 + splits, scratch=True)
