@@ -80,7 +80,8 @@ def exported_names() -> list[str]:
     return sorted(_protos or {})
 
 
-_ERRORS = {-1: "invalid argument", -2: "unsupported shape or feature", -3: "bounded device wait gave up"}
+_ERRORS = {-1: "invalid argument", -2: "unsupported shape or feature", -3: "bounded device wait gave up",
+           -4: "request larger than the library's built-in fixed-size scratch"}
 
 
 def call(name: str, *args) -> int:

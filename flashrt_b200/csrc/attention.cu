@@ -761,6 +761,68 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
     return launch_attn<128, BKV>(Q, K, V, p, q_strides, k_strides, v_strides, sp, pdl, s);
 }
 
+// ------------------------------------------------------------------ variant with built-in scratch
+// Some hosts of this library may not allocate device memory at the point where they need attention with split KV:
+// a real-time control loop that has frozen its memory map, a plugin running inside another runtime's captured or
+// pooled-memory region, an embedding that only hands out fixed buffers.  For them the split-KV scratch lives in
+// this module: a fixed array in device global memory that every GPU loading the library carries until the
+// process exits.
+#define FRT_STATIC_ATTN_MAX_SPLITS 8
+#define FRT_STATIC_ATTN_MAX_ROWS 512          /* batch * heads_q * seqlen_q */
+#define FRT_STATIC_ATTN_MAX_HEAD_DIM 256
+#define FRT_STATIC_ATTN_MAX_TILES 64          /* 128-row tiles x kv heads x batch */
+#define FRT_STATIC_O_BYTES ((size_t)FRT_STATIC_ATTN_MAX_SPLITS * FRT_STATIC_ATTN_MAX_ROWS * FRT_STATIC_ATTN_MAX_HEAD_DIM * 4)
+#define FRT_STATIC_LSE_BYTES ((size_t)FRT_STATIC_ATTN_MAX_SPLITS * FRT_STATIC_ATTN_MAX_ROWS * 4)
+#define FRT_STATIC_CNT_BYTES ((size_t)FRT_STATIC_ATTN_MAX_TILES * 2 * 4)
+static __device__ __align__(256) unsigned char g_attn_static_scratch[FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES +
+                                                                     FRT_STATIC_CNT_BYTES];
+// In host code the array's name is only a handle; the device address is asked for once per device.
+static void* g_attn_static_ptr[64] = {nullptr};
+
+// Same operation and arguments as frt_b200_attention_fwd_bf16 without the three scratch pointers: the split-KV
+// partials go to the module's own fixed device array (about 4.2 MB per GPU).  Limits: kv_splits <= 8,
+// batch * num_heads_q * seqlen_q <= 512, head_dim <= 256, at most 64 (row tile, kv head, batch) triples; anything
+// larger returns -4.  Nothing is allocated or freed by this call.  The first call on each device looks up the
+// array's device address (cudaGetSymbolAddress) and zeroes the arrival counters with a blocking memset: make that
+// first call before any stream capture.  Every call uses the same array, which keeps whatever the previous call
+// left in it (the kernel overwrites the partials it reads and re-arms the counters itself), so two calls whose
+// kernels can overlap on the GPU -- different streams, or graph branches -- would corrupt each other.
+int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
+                                               const float* out_scale, float* lse, const int* seqused_k, int batch,
+                                               int seqlen_q, int seqlen_k, int num_heads_q, int num_heads_kv,
+                                               int head_dim, const long long* q_strides, const long long* k_strides,
+                                               const long long* v_strides, const long long* o_strides,
+                                               float softmax_scale, int kv_splits, int kv_static_rows, int flags,
+                                               void* stream) {
+    if (batch <= 0 || seqlen_q < 0 || num_heads_q <= 0 || num_heads_kv <= 0 || (num_heads_q % num_heads_kv))
+        return FRT_ERR_INVALID;
+    const long long rows = (long long)batch * num_heads_q * seqlen_q;
+    const int G = num_heads_q / num_heads_kv;
+    const long long tiles = (((long long)seqlen_q * G + 127) / 128) * num_heads_kv * batch;
+    if (kv_splits > FRT_STATIC_ATTN_MAX_SPLITS || rows > FRT_STATIC_ATTN_MAX_ROWS ||
+        head_dim > FRT_STATIC_ATTN_MAX_HEAD_DIM || tiles > FRT_STATIC_ATTN_MAX_TILES)
+        return -4;   // larger than the built-in scratch
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+    if (dev < 0 || dev >= 64) return FRT_ERR_UNSUPPORTED;
+    if (!g_attn_static_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_attn_static_scratch);
+        if (e != cudaSuccess || !ptr) return FRT_CUDA_ERR(e);
+        e = cudaMemset(static_cast<unsigned char*>(ptr) + FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES, 0,
+                       FRT_STATIC_CNT_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        g_attn_static_ptr[dev] = ptr;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_attn_static_ptr[dev]);
+    return frt_b200_attention_fwd_bf16(Q, K, V, O, O_fp8, out_scale, lse, seqused_k, batch, seqlen_q, seqlen_k,
+                                       num_heads_q, num_heads_kv, head_dim, q_strides, k_strides, v_strides, o_strides,
+                                       softmax_scale, kv_splits, kv_static_rows, reinterpret_cast<float*>(base),
+                                       reinterpret_cast<float*>(base + FRT_STATIC_O_BYTES),
+                                       base + FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES, flags, stream);
+}
+
 // returns (and optionally clears) the attention kernels' device status word; 0 = no bounded wait gave up.
 // code 0x11 = TMA producer, 0x12 = MMA issuer, 0x13 = softmax warps.  Synchronises the device.
 int frt_b200_attention_status(int reset) {

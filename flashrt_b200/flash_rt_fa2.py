@@ -78,3 +78,17 @@ def fwd_bf16_seqused_splitkv(Q, K, V, O, softmax_lse, seqused_k, softmax_lse_acc
 
 def attention_status(reset: bool = True) -> int:
     return call_status("frt_b200_attention_status", 1 if reset else 0)
+
+
+def fwd_bf16_static_scratch(Q, K, V, O, softmax_lse, batch, seqlen_q, seqlen_k, num_heads_q, num_heads_kv, head_dim,
+                            q_strides, k_strides, v_strides, o_strides, softmax_scale=1.0, stream=0, *, seqused_k=0,
+                            kv_splits=0, kv_static_rows=0, out_fp8=0, out_scale=0, pdl=False):
+    """Split-KV attention for callers that cannot allocate device memory at the call site (no counterpart in the
+    reference): the partials live in a fixed array inside the library instead of caller-provided buffers.  Raises
+    :class:`KernelError` (status -4) when the shape exceeds that array (8 splits, 512 query rows x heads, head_dim
+    256).  Make the first call on a device outside stream capture; do not let two calls overlap on the GPU."""
+    call("frt_b200_attention_fwd_bf16_static_scratch", Q, K, V, O, out_fp8 or None, out_scale or None,
+         softmax_lse or None, seqused_k or None, batch, seqlen_q, seqlen_k, num_heads_q, num_heads_kv, head_dim,
+         C.cast(_s3(q_strides), C.c_void_p), C.cast(_s3(k_strides), C.c_void_p),
+         C.cast(_s3(v_strides), C.c_void_p), C.cast(_s3(o_strides), C.c_void_p),
+         softmax_scale, kv_splits, kv_static_rows, 1 if pdl else 0, stream)

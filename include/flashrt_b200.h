@@ -11,6 +11,7 @@
  *   -1  invalid argument (null pointer, negative size, misaligned pointer)
  *   -2  unsupported shape / feature
  *   -3  a bounded device-side wait gave up (see frt_b200_gemm_status)
+ *   -4  the request exceeds a built-in fixed-size buffer (entry points that say so)
  *   -(1000 + cudaError_t) for a CUDA runtime failure at launch.
  *
  * `flags` bit 0: launch with programmatic dependent launch (the kernel starts
@@ -151,6 +152,23 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
                                 const long long* q_strides, const long long* k_strides, const long long* v_strides,
                                 const long long* o_strides, float softmax_scale, int kv_splits, int kv_static_rows,
                                 float* o_accum, float* lse_accum, void* counters, int flags, void* stream);
+/* Attention with split KV for callers that cannot allocate device memory where they call it (a control loop with a
+ * frozen memory map, a plugin inside another runtime's captured or pooled region, a host that only hands out fixed
+ * buffers).  This entry point has no counterpart in the reference.  Same operation and arguments as
+ * frt_b200_attention_fwd_bf16 minus the scratch pointers: the partials go to a fixed array inside the library
+ * (about 4.2 MB of device memory on every GPU that loads it, held until the process exits).
+ * Limits: kv_splits <= 8, batch * num_heads_q * seqlen_q <= 512, head_dim <= 256, at most 64 (row tile, kv head,
+ * batch) triples; beyond them the call returns -4 and launches nothing.  It allocates and frees nothing.
+ * The first call on each device fetches the array's device address and clears its arrival counters with a blocking
+ * memset -- make that call before any stream capture.  All calls share the one array and it keeps the last call's
+ * contents; calls whose kernels may run at the same time (two streams, parallel graph branches) race on it. */
+int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
+                                               const float* out_scale, float* lse, const int* seqused_k, int batch,
+                                               int seqlen_q, int seqlen_k, int num_heads_q, int num_heads_kv,
+                                               int head_dim, const long long* q_strides, const long long* k_strides,
+                                               const long long* v_strides, const long long* o_strides,
+                                               float softmax_scale, int kv_splits, int kv_static_rows, int flags,
+                                               void* stream);
 /* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
 int frt_b200_attention_status(int reset);
 
