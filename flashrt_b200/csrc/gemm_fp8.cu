@@ -399,6 +399,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
             const int items = (cend > cbeg ? cend - cbeg : 0) * GROUPS;
             const float inv_os = (EPI == EPI_GEGLU_FP8) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
             const int pos = (EPI == EPI_ROPE_SPLIT && p.devpos) ? *p.devpos : 0;
+#pragma unroll 2
             for (int it = threadIdx.x; it < items; it += 128) {
                 const int c = cbeg + it / GROUPS;
                 const int g = it % GROUPS;
@@ -408,9 +409,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.0f;
                 // lanes g*8 .. g*8+7 (and, for GeGLU, the matching up lanes 64 further on)
+                if (S == 1) {
+                    // single split: the partials are in this CTA's own shared memory -- ordinary loads, which the
+                    // compiler is free to overlap across work items
+                    const float4* src = reinterpret_cast<const float4*>(&red[c * 128 + g * 8]);
+                    const float4 x0 = src[0], x1 = src[1];
+                    a[0] = x0.x; a[1] = x0.y; a[2] = x0.z; a[3] = x0.w;
+                    a[4] = x1.x; a[5] = x1.y; a[6] = x1.z; a[7] = x1.w;
+                    if (EPI == EPI_GEGLU_FP8) {
+                        const float4 y0 = src[16], y1 = src[17];
+                        b[0] = y0.x; b[1] = y0.y; b[2] = y0.z; b[3] = y0.w;
+                        b[4] = y1.x; b[5] = y1.y; b[6] = y1.z; b[7] = y1.w;
+                    }
+                }
 #pragma unroll
                 for (uint32_t r0 = 0; r0 < 16; r0 += 2) {
-                    if (r0 >= S) break;
+                    if (S == 1 || r0 >= S) break;
                     const uint32_t ra = rank_base[r0] + off;
                     const uint32_t rb = rank_base[r0 + 1 < S ? r0 + 1 : r0] + off;
                     float4 x0, x1, y0, y1;
