@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(1024)
 qkv_split_norm_rope_kernel(const __nv_bfloat16* __restrict__ packed, const __nv_bfloat16* __restrict__ wq,
                            const __nv_bfloat16* __restrict__ wk, const float* __restrict__ fre,
                            const float* __restrict__ fim, __nv_bfloat16* __restrict__ q_out,
-                           __nv_bfloat16* __restrict__ k_out, int L, int dim, int D_h, int seq_len, float eps) {
+                           __nv_bfloat16* __restrict__ k_out, int L, int dim, int D_h, int seq_len, float eps,
+                           const float* __restrict__ ext_ssq_q, const float* __restrict__ ext_ssq_k, int full_dim) {
     __shared__ float warp_tot[32];
     const int row = blockIdx.x;
     const int t = row % L;
@@ -188,8 +189,17 @@ qkv_split_norm_rope_kernel(const __nv_bfloat16* __restrict__ packed, const __nv_
         }
     }
     pdl_launch_dependents();
-    const float inv_q = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(block_sum_fixed(sq, warp_tot), (float)dim), eps)));
-    const float inv_k = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(block_sum_fixed(sk, warp_tot), (float)dim), eps)));
+    // tensor-parallel use: this CTA only sees its heads' slice of the row; the sums over the full width come in
+    float tq, tk;
+    if (ext_ssq_q) {
+        tq = ext_ssq_q[row];
+        tk = ext_ssq_k[row];
+    } else {
+        tq = block_sum_fixed(sq, warp_tot);
+        tk = block_sum_fixed(sk, warp_tot);
+    }
+    const float inv_q = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tq, (float)full_dim), eps)));
+    const float inv_k = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tk, (float)full_dim), eps)));
     if (!active) return;
     const uint32_t* wqw = &wqv.x;
     const uint32_t* wkw = &wkv.x;
@@ -315,6 +325,62 @@ modulation6_kernel(const float* __restrict__ params, const float* __restrict__ l
     pdl_launch_dependents();
 }
 
+// ------------------------------------------------------------------ tensor-parallel helpers for full-width norms
+// out[r] (+)= sum over `ncols` columns of x[r, col0 + c]^2   (one warp per row, fp32)
+__global__ void __launch_bounds__(256)
+row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, long long row_stride, int col0, int ncols,
+                 float* __restrict__ out, long long rows) {
+    pdl_wait();
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const __nv_bfloat16* xr = x + row * row_stride + col0;
+    float s = 0.0f;
+    for (int c = lane * 8; c < ncols; c += 256) {
+        uint4 v = ld_global_v4(xr + c);
+        const uint32_t* w = &v.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float a, b;
+            unpack_bf16x2(w[i], a, b);
+            s = __fmaf_rn(a, a, s);
+            s = __fmaf_rn(b, b, s);
+        }
+    }
+    s = warp_sum_butterfly(s);
+    if (lane == 0) out[row] = s;
+}
+
+// y[r, :] = bf16(x[r, :] * rsqrt(ssq[r] / full_dim + eps) * w[:]) on a column slice of width `dim`
+__global__ void __launch_bounds__(256)
+rms_norm_ext_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const __nv_bfloat16* __restrict__ w,
+                    const float* __restrict__ ssq, __nv_bfloat16* __restrict__ out, long long out_stride,
+                    long long rows, int dim, int full_dim, float eps) {
+    pdl_wait();
+    const int vec_per_row = dim >> 3;
+    const long long total = rows * vec_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / vec_per_row;
+        const int col = (int)(i - row * vec_per_row) << 3;
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq[row], (float)full_dim), eps)));
+        uint4 xv = ld_global_v4(x + row * x_stride + col);
+        uint4 wv = ld_global_v4(w + col);
+        const uint32_t* xw = &xv.x;
+        const uint32_t* ww = &wv.x;
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float a, b, w0, w1;
+            unpack_bf16x2(xw[k], a, b);
+            unpack_bf16x2(ww[k], w0, w1);
+            ow[k] = pack_bf16x2(__fmul_rn(__fmul_rn(a, inv), w0), __fmul_rn(__fmul_rn(b, inv), w1));
+        }
+        st_global_v4(out + row * out_stride + col, o);
+    }
+}
+
 template <typename K, typename... Args>
 static int launch_k(K kernel, unsigned grid, unsigned block, cudaStream_t stream, bool pdl, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -372,7 +438,8 @@ int frt_b200_layer_norm(const void* x, const void* weight, const void* bias, con
 // packed_qkv (B*L, 3*dim) bf16, dim = N * D_h; q_out / k_out (B*L, dim); freqs (seq_len.., D_h/2) fp32.
 int frt_b200_qkv_split_norm_rope(const void* packed_qkv, const void* norm_q_w, const void* norm_k_w,
                                  const float* freqs_re, const float* freqs_im, void* q_out, void* k_out, int B, int L,
-                                 int N, int D_h, int seq_len, float eps, int flags, void* stream) {
+                                 int N, int D_h, int seq_len, float eps, const float* ext_ssq_q,
+                                 const float* ext_ssq_k, int full_dim, int flags, void* stream) {
     if (!packed_qkv || !norm_q_w || !norm_k_w || !freqs_re || !freqs_im || !q_out || !k_out) return FRT_ERR_INVALID;
     if (B < 0 || L <= 0 || N <= 0 || D_h <= 0) return FRT_ERR_INVALID;
     const long long dim = (long long)N * D_h;
@@ -384,7 +451,33 @@ int frt_b200_qkv_split_norm_rope(const void* packed_qkv, const void* norm_q_w, c
     const unsigned threads = (unsigned)(((dim / 8 + 31) / 32) * 32);
     return launch_k(qkv_split_norm_rope_kernel, (unsigned)(B * L), threads, (cudaStream_t)stream, flags & 1,
                     (const __nv_bfloat16*)packed_qkv, (const __nv_bfloat16*)norm_q_w, (const __nv_bfloat16*)norm_k_w,
-                    freqs_re, freqs_im, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, L, (int)dim, D_h, seq_len, eps);
+                    freqs_re, freqs_im, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, L, (int)dim, D_h, seq_len, eps,
+                    (ext_ssq_q && ext_ssq_k) ? ext_ssq_q : (const float*)nullptr,
+                    (ext_ssq_q && ext_ssq_k) ? ext_ssq_k : (const float*)nullptr,
+                    (ext_ssq_q && ext_ssq_k && full_dim > 0) ? full_dim : (int)dim);
+}
+
+// out[r] = sum_c x[r, col0 + c]^2 over ncols columns (fp32); x rows are row_stride elements apart.  ncols % 8 == 0.
+int frt_b200_row_sumsq(const void* x, long long row_stride, int col0, int ncols, float* out, long long rows, int flags,
+                       void* stream) {
+    if (!x || !out || rows < 0 || ncols <= 0 || col0 < 0) return FRT_ERR_INVALID;
+    if ((ncols & 7) || (col0 & 7) || (row_stride & 7) || mis(x, 16)) return FRT_ERR_UNSUPPORTED;
+    if (rows == 0) return FRT_OK;
+    return launch_k(row_sumsq_kernel, (unsigned)((rows + 7) / 8), 256, (cudaStream_t)stream, flags & 1,
+                    (const __nv_bfloat16*)x, row_stride, col0, ncols, out, rows);
+}
+
+// out[r, 0:dim] = bf16(x[r, 0:dim] * rsqrt(ssq[r] / full_dim + eps) * weight[0:dim]); row pitches in elements.
+int frt_b200_rms_norm_ext(const void* x, long long x_stride, const void* weight, const float* ssq, void* out,
+                          long long out_stride, long long rows, int dim, int full_dim, float eps, int flags,
+                          void* stream) {
+    if (!x || !weight || !ssq || !out || rows < 0 || dim <= 0 || full_dim <= 0) return FRT_ERR_INVALID;
+    if ((dim & 7) || (x_stride & 7) || (out_stride & 7) || mis(x, 16) || mis(weight, 16) || mis(out, 16))
+        return FRT_ERR_UNSUPPORTED;
+    if (rows == 0) return FRT_OK;
+    return launch_k(rms_norm_ext_kernel, cap_grid(rows * (dim >> 3), 256), 256, (cudaStream_t)stream, flags & 1,
+                    (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)weight, ssq, (__nv_bfloat16*)out,
+                    out_stride, rows, dim, full_dim, eps);
 }
 
 // out (M, N) e4m3 = clamp(gelu_tanh(in + bias) * (1 / *d_scale)); bias (N,) or NULL.

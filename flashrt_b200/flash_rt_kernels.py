@@ -135,9 +135,17 @@ def ada_layer_norm_fp8(x_bf16, scale_bf16, shift_bf16, out_fp8, act_scale, seq_l
 
 
 def qkv_split_norm_rope_bf16(packed_qkv, norm_q_w, norm_k_w, freqs_re, freqs_im, q_rope_out, k_rope_out, B, L_v, N,
-                             D_h, seq_len, eps=1e-6, stream=0, *, pdl=False):
+                             D_h, seq_len, eps=1e-6, stream=0, *, pdl=False, ext_ssq_q=0, ext_ssq_k=0, full_dim=0):
     call("frt_b200_qkv_split_norm_rope", packed_qkv, norm_q_w, norm_k_w, freqs_re, freqs_im, q_rope_out, k_rope_out,
-         B, L_v, N, D_h, seq_len, eps, _f(pdl), stream)
+         B, L_v, N, D_h, seq_len, eps, ext_ssq_q or None, ext_ssq_k or None, full_dim, _f(pdl), stream)
+
+
+def row_sumsq(x, row_stride, col0, ncols, out, rows, stream=0, *, pdl=False):
+    call("frt_b200_row_sumsq", x, row_stride, col0, ncols, out, rows, _f(pdl), stream)
+
+
+def rms_norm_ext(x, x_stride, weight, ssq, out, out_stride, rows, dim, full_dim, eps=1e-6, stream=0, *, pdl=False):
+    call("frt_b200_rms_norm_ext", x, x_stride, weight, ssq, out, out_stride, rows, dim, full_dim, eps, _f(pdl), stream)
 
 
 def bias_gelu_quantize_fp8_static_bf16(in_bf16, bias_bf16, out_fp8, act_scale, M, N, stream=0, *, pdl=False):

@@ -186,10 +186,23 @@ int frt_b200_layer_norm(const void* x, const void* weight, const void* bias, con
 /* qkv_split_norm_rope_bf16           csrc/bindings.cpp:3574 -> csrc/quantize/qkv_split_norm_rope_bf16.cu:16-140
  *   packed_qkv (B*L, 3*dim) bf16 = [q | k | v], dim = N * D_h.  q, k: RMSNorm over the full width dim with weights
  *   norm_q_w / norm_k_w, then complex pairs (2c, 2c+1) of every head multiplied by freqs_re/im[t, c] (fp32,
- *   (>= seq_len, D_h/2)); rows with t = row % L >= seq_len are normalised but not rotated.  V stays in packed_qkv. */
+ *   (>= seq_len, D_h/2)); rows with t = row % L >= seq_len are normalised but not rotated.  V stays in packed_qkv.
+ *   ext_ssq_q / ext_ssq_k (rows,) fp32 + full_dim: optional precomputed sums of squares over the FULL model width
+ *   (tensor parallelism: N is then the local head count); NULL = reduce over the N * D_h columns given. */
 int frt_b200_qkv_split_norm_rope(const void* packed_qkv, const void* norm_q_w, const void* norm_k_w,
                                  const float* freqs_re, const float* freqs_im, void* q_out, void* k_out, int B, int L,
-                                 int N, int D_h, int seq_len, float eps, int flags, void* stream);
+                                 int N, int D_h, int seq_len, float eps, const float* ext_ssq_q,
+                                 const float* ext_ssq_k, int full_dim, int flags, void* stream);
+/* Helpers for the same norms under tensor parallelism (they have no counterpart in the reference, which has no
+ * multi-GPU path): a rank holds only its heads' columns, so the per-row sums of squares are formed per rank
+ * (frt_b200_row_sumsq), summed across ranks by the caller (an all-reduce of one float per row) and handed back
+ * through ext_ssq_q / ext_ssq_k + full_dim above, or to frt_b200_rms_norm_ext for a plain RMSNorm of a slice. */
+int frt_b200_row_sumsq(const void* x, long long row_stride, int col0, int ncols, float* out, long long rows, int flags,
+                       void* stream);
+/* RMSNorm of a column slice with the full-width sum of squares supplied (no counterpart in the reference). */
+int frt_b200_rms_norm_ext(const void* x, long long x_stride, const void* weight, const float* ssq, void* out,
+                          long long out_stride, long long rows, int dim, int full_dim, float eps, int flags,
+                          void* stream);
 /* bias_gelu_quantize_fp8_static_bf16 csrc/bindings.cpp:3427-3440 -> csrc/quantize/bias_gelu_quantize_fp8.cu:24-49
  *   out (M, N) e4m3 = clamp(gelu_tanh(in + bias) * (1 / *d_scale), +-448); bias (N,) or NULL; N % 8 == 0. */
 int frt_b200_bias_gelu_quantize_fp8(const void* in_bf16, const void* bias, void* out_fp8, const float* d_scale,
