@@ -266,6 +266,99 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------------
+WAN_METRIC = "video-DiT step ms"
+WAN_WORKLOAD = ("wan2.2-5B-shape DiT step: 30 blocks, width 3072, 24 heads x 128, FFN 14336 GELU-tanh, adaLN, "
+                "cross-attention to 512 text tokens of width 4096, 13x30x52 = 20280 latent tokens, batch 2, "
+                "FP8 E4M3 GEMMs + bf16 attention")
+
+
+def run_wan(args):
+    """BASELINE configs[4]: one denoise step of the video DiT, tensor-parallel over the N GPUs (strong scaling)."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from flashrt_b200.wan_dit import WanDiTB200, synthetic_wan_state
+    layers = args.wan_layers
+    state = synthetic_wan_state(0, layers=1)
+    grid, B, T = (13, 30, 52), 2, 512
+    model = WanDiTB200(state, grid=grid, batch=B, text_len=T, device=local, tp_rank=rank, tp_size=world,
+                       repeat_blocks=layers)
+    L, D = model.L, model.dim
+    g = torch.Generator().manual_seed(1)
+    x_host = torch.randn(B, L, D, generator=g).to(torch.bfloat16).pin_memory()
+    ctx = torch.randn(B, T, 4096, generator=g)
+    tproj = torch.randn(B, 6, D, generator=g) * 0.3
+    x_dev = x_host.to(f"cuda:{local}")
+    model.set_context(ctx)
+    model.calibrate(x_dev, tproj)
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warm):
+        model.step(x_dev, tproj)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = model.step(x_dev, tproj)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        xd = x_host.to(f"cuda:{local}", non_blocking=True)
+        out_host = model.step(xd, tproj).cpu()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    clocks = sampler.stop()
+    barrier()
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        from flashrt_b200 import flash_rt_kernels as fvk
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+            os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops_sustained": 1400.0}
+        gemm_flop = 2.0 * B * L * (3072 * 9216 + 3 * 3072 * 3072 + 2 * 3072 * 14336) * layers
+        attn_flop = 4.0 * L * L * 3072 * B * layers + 4.0 * L * T * 3072 * B * layers
+        achieved = (gemm_flop + attn_flop) / world / (ms * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        line = {
+            "metric": WAN_METRIC, "value": round(ms, 2), "unit": "ms", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": round(ms, 2), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3 GEMMs (fp32 accumulate), bf16 attention", "data": "synthetic",
+            "config": {"workload": WAN_WORKLOAD, "layers": layers, "parallelism": f"tp{world} (heads + FFN columns, "
+                       "NCCL all-reduce after attention-out, cross-attention-out and FFN-down)",
+                       "l2": "activations of one step (> 1 GB) exceed the 126 MB L2; no explicit flush",
+                       "tensor_core_status": fvk.tensor_core_status(), "finite": bool(torch.isfinite(out.float()).all())},
+            "e2e": {"value": round(e2e_ms, 2), "unit": "ms", "h2d_bytes_per_step": int(x_host.numel() * 2),
+                    "d2h_bytes_per_step": int(out_host.numel() * 2)},
+            "gpu_launches": model.launches_per_step * steps,
+            "roofline": {"bound": "tensor", "kernel": "whole step (FP8 GEMMs + bf16 attention), per GPU",
+                         "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
+                         "frac": round(achieved / peak, 4), "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (bf16 peak; FP8 GEMMs can exceed it)",
+                         "flop_per_step": gemm_flop + attn_flop},
+            "cpu_baseline": None, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -278,7 +371,13 @@ def main():
                          "(Nsight Compute cannot profile programmatically dependent launches)")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
+    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan"],
+                    help="pi05 = the headline action-expert loop (default); wan = the video-DiT step (configs[4])")
+    ap.add_argument("--wan-layers", type=int, default=30)
     args = ap.parse_args()
+    if args.workload == "wan" and args.impl != "reference":
+        run_wan(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -97,7 +97,7 @@ SITES = ("qkv", "o", "cq", "co", "f1", "f2")
 
 class WanDiTB200:
     def __init__(self, state: dict, *, grid=(13, 30, 52), batch: int = 2, text_len: int = 512, device=0,
-                 tp_rank: int = 0, tp_size: int = 1, tp_group=None):
+                 tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device)
@@ -139,6 +139,12 @@ class WanDiTB200:
             b["norm3_w"], b["norm3_b"] = bw["norm3_w"].to(dev, BF16), bw["norm3_b"].to(dev, BF16)
             b["modulation"] = bw["modulation"].to(dev, torch.float32)
             self.blocks.append(b)
+        # synthetic benchmarking at full depth without generating 5 GB of random numbers on the host: every extra
+        # block gets its own device copy of the weights, so that each block still streams distinct memory
+        base = list(self.blocks)
+        for _ in range(repeat_blocks - 1):
+            for b in base:
+                self.blocks.append({k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in b.items()})
         fre, fim = rope_3d_freqs(grid, self.hd)
         self.fre, self.fim = fre.to(dev), fim.to(dev)
         M, D, dl, fl = self.M, self.dim, self.dl, self.fl
