@@ -104,22 +104,34 @@ struct GemmParams {
     uint8_t* out8;             // EPI_GEGLU_FP8: (M, half) e4m3 codes
     const float* out_scale;    //   device scalar: quantisation scale of the GeGLU result
     int half;                  //   hidden width; weight rows [0, half) = gate, [half, 2 half) = up
+    // NVFP4 kernels: unsigned-E4M3 block scales of both operands in 512-byte atoms (128 rows x 4 blocks)
+    const uint8_t* sf_lane;
+    const uint8_t* sf_col;
+    int sf_katoms;             //   atoms along K = K / 64
+    int sf_col_rblocks;        //   128-row atom rows of the column operand's scale buffer
 };
 
 enum { EPI_BF16 = 0, EPI_ROPE_SPLIT = 1, EPI_GEGLU_FP8 = 2 };
 
-template <int BN>
+template <int BN, bool FP4 = false>
 struct GemmCfg {
-    static constexpr int BK = 128;                       // bytes == fp8 elements per k-block
+    static constexpr int BK = 128;                       // bytes per k-block: 128 fp8 or 256 packed fp4 elements
     static constexpr int L_BYTES = 128 * BK;             // 16 KB
     static constexpr int C_BYTES = BN * BK;
-    static constexpr int STAGE_BYTES = L_BYTES + C_BYTES;
+    static constexpr int CB = (BN + 127) / 128;          // 128-row scale atoms spanned by the column operand
+    static constexpr int SFL_BYTES = FP4 ? 4 * 512 : 0;  // 4 atoms (one per K = 64 step) of the lane operand
+    static constexpr int SFC_BYTES = FP4 ? 4 * 512 * CB : 0;
+    static constexpr int STAGE_BYTES = L_BYTES + C_BYTES + SFL_BYTES + SFC_BYTES;
     static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
     static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
     static constexpr int RED_BYTES = 128 * BN * 4;
     static_assert(RED_BYTES <= STAGES * STAGE_BYTES, "split-K staging must fit in the pipeline buffers");
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // power of two >= 32
+    static constexpr int ACC_COLS = BN < 32 ? 32 : BN;
+    static constexpr int SF_COLS = FP4 ? 16 + 16 * CB : 0;   // 4 columns per atom, 4 K-steps, both operands
+    static constexpr int NEED_COLS = ACC_COLS + SF_COLS;
+    static constexpr int TMEM_COLS = NEED_COLS <= 32 ? 32 : NEED_COLS <= 64 ? 64 : NEED_COLS <= 128 ? 128
+                                     : NEED_COLS <= 256 ? 256 : 512;   // power of two >= 32
 };
 
 enum { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
@@ -160,11 +172,12 @@ __device__ __forceinline__ float reduce_ranks(const uint32_t* rank_base, uint32_
     return acc;
 }
 
-template <int BN, bool SWAP, int EPI>
+template <int BN, bool SWAP, int EPI, bool FP4 = false>
 __global__ void __launch_bounds__(128, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__ CUtensorMap tmC, GemmParams p) {
     static_assert(EPI == EPI_BF16 || SWAP, "fused epilogues exist for the small-M (swapped) kernel only");
-    using Cfg = GemmCfg<BN>;
+    static_assert(!FP4 || (BN >= 32 && EPI != EPI_GEGLU_FP8), "NVFP4: column tiles start on 32-row scale groups");
+    using Cfg = GemmCfg<BN, FP4>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -234,13 +247,35 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 tc::tma_load_2d(dst, tmW, &full[stage], kb * 128, w_row);
             }
         };
+        // NVFP4: the scale atoms of a k-block (4 K-steps) are 2048 contiguous bytes per 128-row group
+        int c_atoms = Cfg::CB;
+        if (FP4) {
+            const int left = p.sf_col_rblocks - col0 / 128;
+            c_atoms = left < Cfg::CB ? left : Cfg::CB;
+        }
+        const uint32_t stage_tx = Cfg::STAGE_BYTES - (FP4 ? (Cfg::CB - c_atoms) * 2048 : 0);
+        auto load_sf_lane = [&](int stage, int kb) {
+            uint8_t* dst = stage_base + stage * Cfg::STAGE_BYTES + Cfg::L_BYTES + Cfg::C_BYTES;
+            tc::bulk_load(dst, p.sf_lane + ((size_t)(lane0 / 128) * p.sf_katoms + (size_t)kb * 4) * 512, 2048,
+                          &full[stage]);
+        };
+        auto load_sf_col = [&](int stage, int kb) {
+            uint8_t* dst = stage_base + stage * Cfg::STAGE_BYTES + Cfg::L_BYTES + Cfg::C_BYTES + Cfg::SFL_BYTES;
+            for (int j = 0; j < c_atoms; ++j)
+                tc::bulk_load(dst + j * 2048,
+                              p.sf_col + ((size_t)(col0 / 128 + j) * p.sf_katoms + (size_t)kb * 4) * 512, 2048,
+                              &full[stage]);
+        };
         for (int i = 0; i < pre; ++i) {
-            tc::mbar_arrive_expect_tx(&full[i], Cfg::STAGE_BYTES);
+            tc::mbar_arrive_expect_tx(&full[i], stage_tx);
             load_w(i, kb_begin + i);
+            if (FP4) { if (p.w_is_lane) load_sf_lane(i, kb_begin + i); else load_sf_col(i, kb_begin + i); }
         }
         pdl_wait();
-        for (int i = 0; i < pre; ++i)
+        for (int i = 0; i < pre; ++i) {
             tc::tma_load_2d(stage_base + i * Cfg::STAGE_BYTES + x_off, tmX, &full[i], (kb_begin + i) * 128, x_row);
+            if (FP4) { if (p.w_is_lane) load_sf_col(i, kb_begin + i); else load_sf_lane(i, kb_begin + i); }
+        }
         *issued = pre;
         for (int i = pre; i < nkb; ++i) {
             const int s = i % STAGES;
@@ -251,14 +286,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 atomicCAS(&g_gemm_status, 0, ERR_PRODUCER | (blockIdx.x << 8));
                 break;
             }
-            tc::mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+            tc::mbar_arrive_expect_tx(&full[s], stage_tx);
             load_w(s, kb_begin + i);
             tc::tma_load_2d(stage_base + s * Cfg::STAGE_BYTES + x_off, tmX, &full[s], (kb_begin + i) * 128, x_row);
+            if (FP4) {
+                load_sf_lane(s, kb_begin + i);
+                load_sf_col(s, kb_begin + i);
+            }
             *issued = i + 1;
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        constexpr uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN);
+        constexpr uint32_t idesc = FP4 ? tc::make_idesc_nvfp4(128, BN) : tc::make_idesc(0, 0, 0, 0, 128, BN);
+        // NVFP4 scale factors in tensor memory, behind the accumulator: 4 columns per (operand atom, K-step)
+        const uint32_t tmem_sfl = tmem_d + Cfg::ACC_COLS;
+        const uint32_t tmem_sfc = tmem_sfl + 16;
+        const uint32_t sfc_off = BN < 128 ? (uint32_t)((col0 & 127) >> 5) : 0u;   // 32-row group of this column tile
         bool failed = false;
         for (int i = 0; i < nkb; ++i) {
             const int s = i % STAGES;
@@ -277,9 +320,25 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
             const uint32_t sC = sL + Cfg::L_BYTES;
             const uint64_t dL = tc::make_desc_kmajor_sw128(sL);
             const uint64_t dC = tc::make_desc_kmajor_sw128(sC);
+            if (FP4) {
+                const uint32_t sSFL = sC + Cfg::C_BYTES;
+                const uint32_t sSFC = sSFL + Cfg::SFL_BYTES;
 #pragma unroll
-            for (int k = 0; k < 4; ++k)   // 4 x (K = 32) per 128-byte k-block; +32 bytes = +2 in the address field
-                tc::mma_f8(tmem_d, dL + 2 * k, dC + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) {
+                    tc::tmem_cp_sf_atom(tmem_sfl + 4 * k, sSFL + 512 * k);
+#pragma unroll
+                    for (int j = 0; j < Cfg::CB; ++j)
+                        tc::tmem_cp_sf_atom(tmem_sfc + k * 4 * Cfg::CB + 4 * j, sSFC + j * 2048 + 512 * k);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k)   // 4 x (K = 64 e2m1 = 32 bytes) per 128-byte k-block
+                    tc::mma_nvfp4(tmem_d, dL + 2 * k, dC + 2 * k, idesc, tmem_sfl + 4 * k,
+                                  tmem_sfc + k * 4 * Cfg::CB + sfc_off, (i > 0 || k > 0) ? 1u : 0u);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)   // 4 x (K = 32) per 128-byte k-block; +32 bytes = +2 in the address field
+                    tc::mma_f8(tmem_d, dL + 2 * k, dC + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            }
             tc::mma_commit(&empty[s]);
             *consumed = i + 1;
         }
@@ -606,15 +665,16 @@ int get_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t r
     return FRT_OK;
 }
 
-template <int BN, bool SWAP, int EPI>
+// K counts elements; a row holds K bytes (FP8) or K / 2 bytes (packed NVFP4)
+template <int BN, bool SWAP, int EPI, bool FP4 = false>
 static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int splits, bool pdl, cudaStream_t stream) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, FP4>;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI, FP4>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI, FP4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
         attr_done = true;
     }
@@ -623,11 +683,17 @@ static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int sp
     p.lane_rows = SWAP ? p.N : p.M;
     p.col_rows = SWAP ? p.M : p.N;
     p.w_is_lane = SWAP ? 1 : 0;
+    if (FP4) {
+        if (SWAP) { const uint8_t* t = p.sf_lane; p.sf_lane = p.sf_col; p.sf_col = t; }   // callers pass (A, W) order
+        p.sf_katoms = K / 64;
+        p.sf_col_rblocks = (p.col_rows + 127) / 128;
+    }
+    const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
     CUtensorMap tmL, tmC;
-    int rc = get_tmap_2d_u8(&tmL, lane_ptr, (uint64_t)p.lane_rows, (uint64_t)K, (uint64_t)K,
+    int rc = get_tmap_2d_u8(&tmL, lane_ptr, (uint64_t)p.lane_rows, row_bytes, row_bytes,
                             EPI == EPI_GEGLU_FP8 ? 64 : 128);
     if (rc) return rc;
-    rc = get_tmap_2d_u8(&tmC, col_ptr, (uint64_t)p.col_rows, (uint64_t)K, (uint64_t)K, BN);
+    rc = get_tmap_2d_u8(&tmC, col_ptr, (uint64_t)p.col_rows, row_bytes, row_bytes, BN);
     if (rc) return rc;
 
     const int lane_tiles = EPI == EPI_GEGLU_FP8 ? (p.half + 63) / 64 : (p.lane_rows + 127) / 128;
@@ -650,7 +716,7 @@ static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int sp
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, SWAP, EPI>, tmL, tmC, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, SWAP, EPI, FP4>, tmL, tmC, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
 
@@ -676,6 +742,16 @@ static int dispatch_small_m(const void* A, const void* W, GemmParams p, int K, i
     if (M <= 64) return launch_gemm<64, true, EPI>(A, W, p, K, sp, pdl, s);
     if (M <= 128) return launch_gemm<128, true, EPI>(A, W, p, K, sp, pdl, s);
     return launch_gemm<256, true, EPI>(A, W, p, K, sp, pdl, s);
+}
+
+template <int EPI>
+static int dispatch_small_m_nvfp4(const void* A, const void* W, GemmParams p, int K, int M, int tiles, int splits,
+                                  bool pdl, cudaStream_t s) {
+    int sp = pick_splits(tiles, p.kb_total, splits);
+    if (M <= 32) return launch_gemm<32, true, EPI, true>(A, W, p, K, sp, pdl, s);
+    if (M <= 64) return launch_gemm<64, true, EPI, true>(A, W, p, K, sp, pdl, s);
+    if (M <= 128) return launch_gemm<128, true, EPI, true>(A, W, p, K, sp, pdl, s);
+    return launch_gemm<256, true, EPI, true>(A, W, p, K, sp, pdl, s);
 }
 
 }  // namespace frt
@@ -766,6 +842,69 @@ int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int
     p.out_scale = d_out_scale;
     p.half = half;
     return dispatch_small_m<EPI_GEGLU_FP8>(A, W, p, K, M, half / 64, splits, flags & 1, (cudaStream_t)stream);
+}
+
+// NVFP4 block-scaled GEMM: D(M,N) bf16 = alpha * (*d_alpha) * (A . SFA)(M,K) . (W . SFW)(N,K)^T + bias.
+// A, W: packed e2m1, two per byte, K contiguous (row = K / 2 bytes); SFA, SFW: unsigned-E4M3 scales per 16
+// elements in 512-byte atoms of 128 rows x 4 blocks (frt_b200_nvfp4_sf_bytes; padding zero-filled).
+// K % 256 == 0.  d_alpha: optional device float (e.g. the product of two FP32 global scales).
+int frt_b200_gemm_nvfp4_nt(const void* A, const void* SFA, const void* W, const void* SFW, void* D, int M, int N,
+                           int K, float alpha, const float* d_alpha, const void* bias, int splits, int flags,
+                           void* stream) {
+    if (!A || !SFA || !W || !SFW || !D || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if (K % 256) return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(SFA) & 15) || (reinterpret_cast<uintptr_t>(SFW) & 15)) return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    GemmParams p = {};
+    p.out = (__nv_bfloat16*)D;
+    p.sa = d_alpha;
+    p.alpha_host = alpha;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.M = M;
+    p.N = N;
+    p.kb_total = K / 256;
+    p.sf_lane = (const uint8_t*)SFA;
+    p.sf_col = (const uint8_t*)SFW;
+    cudaStream_t s = (cudaStream_t)stream;
+    bool pdl = flags & 1;
+    if (M <= 256) return dispatch_small_m_nvfp4<EPI_BF16>(A, W, p, K, M, (N + 127) / 128, splits, pdl, s);
+    int sp = splits > 0 ? pick_splits(1, p.kb_total, splits > 8 ? 8 : splits) : 1;
+    if (N >= 256) return launch_gemm<256, false, EPI_BF16, true>(A, W, p, K, sp, pdl, s);
+    if (N > 64) return launch_gemm<128, false, EPI_BF16, true>(A, W, p, K, sp, pdl, s);
+    return launch_gemm<64, false, EPI_BF16, true>(A, W, p, K, sp, pdl, s);
+}
+
+// NVFP4 QKV projection with the RoPE + split + KV-append epilogue (M <= 256); arguments as
+// frt_b200_gemm_fp8_nt_rope_split with the operand scales replaced by the block-scale buffers.
+int frt_b200_gemm_nvfp4_nt_rope_split(const void* A, const void* SFA, const void* W, const void* SFW, int M, int K,
+                                      float alpha, const void* rope, void* Q, void* Kout, void* Vout,
+                                      const int* devpos, int q_dim, int k_dim, int v_dim, int head_dim, int splits,
+                                      int flags, void* stream) {
+    if (!A || !SFA || !W || !SFW || !rope || !Q || !Kout || !Vout || M < 0 || K <= 0) return FRT_ERR_INVALID;
+    if (q_dim <= 0 || k_dim <= 0 || v_dim <= 0 || head_dim <= 0) return FRT_ERR_INVALID;
+    if ((K % 256) || M > 256 || (head_dim & 1) || (q_dim % head_dim) || (k_dim % head_dim) || (q_dim & 1) ||
+        (k_dim & 1))
+        return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(SFA) & 15) || (reinterpret_cast<uintptr_t>(SFW) & 15)) return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    GemmParams p = {};
+    p.alpha_host = alpha;
+    p.M = M;
+    p.N = q_dim + k_dim + v_dim;
+    p.kb_total = K / 256;
+    p.sf_lane = (const uint8_t*)SFA;
+    p.sf_col = (const uint8_t*)SFW;
+    p.rope = (const __nv_bfloat16*)rope;
+    p.outQ = (__nv_bfloat16*)Q;
+    p.outK = (__nv_bfloat16*)Kout;
+    p.outV = (__nv_bfloat16*)Vout;
+    p.devpos = devpos;
+    p.q_dim = q_dim;
+    p.k_dim = k_dim;
+    p.v_dim = v_dim;
+    p.head_dim = head_dim;
+    return dispatch_small_m_nvfp4<EPI_ROPE_SPLIT>(A, W, p, K, M, (p.N + 127) / 128, splits, flags & 1,
+                                                  (cudaStream_t)stream);
 }
 
 // returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)

@@ -24,9 +24,11 @@
 // Reduction tree (fixed, mirrored by the C oracle): per thread a sequential
 // fma chain over its 8 elements; xor-butterfly over the 32 lanes; warp totals
 // summed in warp order by every thread.
-#include "common.cuh"
+#include "nvfp4.cuh"
 
 namespace frt {
+
+enum { OUT_BF16 = 0, OUT_E4M3 = 1, OUT_NVFP4_A = 2, OUT_NVFP4_B = 3 };
 
 struct NormArgs {
     __nv_bfloat16* residual;       // in/out row-major (rows, dim); or input x when !HAS_X
@@ -36,7 +38,8 @@ struct NormArgs {
     const __nv_bfloat16* weight;   // (dim,) or null (= ones)
     const __nv_bfloat16* style;    // rows of [scale | shift | gate], 3*dim each (HAS_STYLE)
     long long style_stride;        // elements between style rows (0 = one shared row)
-    void* out;                     // fp8 (rows, dim) or bf16 (rows, dim)
+    void* out;                     // fp8 (rows, dim), bf16 (rows, dim) or packed e2m1 (rows, dim / 2)
+    uint8_t* sf_out;               // NVFP4 block scales in the GEMM's scale-factor atoms
     __nv_bfloat16* gate_out;       // copy of the style gate chunk, or null
     const float* d_scale;          // device scalar: quantisation scale (OUT_FP8)
     int rows;
@@ -44,9 +47,11 @@ struct NormArgs {
     float eps;
 };
 
-template <bool HAS_X, bool HAS_GATE, bool HAS_STYLE, bool OUT_FP8>
+template <bool HAS_X, bool HAS_GATE, bool HAS_STYLE, int OUT>
 __global__ void __launch_bounds__(1024)
 norm_row_kernel(NormArgs a) {
+    constexpr bool OUT_FP8 = OUT == OUT_E4M3;
+    constexpr bool OUT_FP4 = OUT == OUT_NVFP4_A || OUT == OUT_NVFP4_B;
     __shared__ float warp_tot[32];
     const int row = blockIdx.x;
     const int tid = threadIdx.x;
@@ -127,7 +132,7 @@ norm_row_kernel(NormArgs a) {
     const float var = __fadd_rn(__fdiv_rn(tot, (float)a.dim), a.eps);
     const float rms = __fdiv_rn(1.0f, __fsqrt_rn(var));
 
-    if (!active) return;
+    if (!OUT_FP4 && !active) return;   // the NVFP4 path shuffles between lane pairs: every lane stays
 
     float v[8];
     const uint32_t* ww = &wv.x;
@@ -149,6 +154,26 @@ norm_row_kernel(NormArgs a) {
         v[2 * i] = n0;
         v[2 * i + 1] = n1;
     }
+    if (OUT_FP4) {
+        // The modulated value is rounded to bf16 (what the bf16-output kernel stores) and then quantised in
+        // blocks of 16 = this thread's 8 values and its lane neighbour's; the even lane writes the scale byte.
+        constexpr int FAM = OUT == OUT_NVFP4_A ? 0 : 1;
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+            amax = fmaxf(amax, fabsf(v[i]));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        float inv;
+        const uint32_t sb = nvfp4::block_scale<FAM>(amax, inv);
+        if (active) {
+            *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.out) + (roff >> 1)) = nvfp4::pack8<FAM>(v, inv);
+            if ((tid & 1) == 0) a.sf_out[nvfp4::sf_offset(row, col >> 4, (a.dim + 63) >> 6)] = (uint8_t)sb;
+            if (HAS_STYLE && a.gate_out) st_global_v4(a.gate_out + roff, gt);
+        }
+        return;
+    }
     if (OUT_FP8) {
         uint2 o;
         o.x = f32x4_to_e4m3x4(clamp448(__fmul_rn(v[0], inv_scale)), clamp448(__fmul_rn(v[1], inv_scale)),
@@ -167,7 +192,7 @@ norm_row_kernel(NormArgs a) {
     if (HAS_STYLE && a.gate_out) st_global_v4(a.gate_out + roff, gt);
 }
 
-template <bool HAS_X, bool HAS_GATE, bool HAS_STYLE, bool OUT_FP8>
+template <bool HAS_X, bool HAS_GATE, bool HAS_STYLE, int OUT>
 static int launch_norm(const NormArgs& a, cudaStream_t stream, bool pdl) {
     if (a.rows < 0 || a.dim <= 0 || (a.dim & 7) || a.dim > 8192) return FRT_ERR_UNSUPPORTED;
     if (a.rows == 0) return FRT_OK;
@@ -182,7 +207,7 @@ static int launch_norm(const NormArgs& a, cudaStream_t stream, bool pdl) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, norm_row_kernel<HAS_X, HAS_GATE, HAS_STYLE, OUT_FP8>, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, norm_row_kernel<HAS_X, HAS_GATE, HAS_STYLE, OUT>, a);
     if (e != cudaSuccess) return FRT_CUDA_ERR(e);
     return FRT_OK;
 }
@@ -190,6 +215,20 @@ static int launch_norm(const NormArgs& a, cudaStream_t stream, bool pdl) {
 }  // namespace frt
 
 using namespace frt;
+
+template <int OUT>
+static int dispatch_norm_nvfp4(const NormArgs& a, bool has_x, bool has_gate, bool has_style, cudaStream_t s, bool pdl) {
+    if (has_x) {
+        if (has_gate) {
+            if (has_style) return launch_norm<true, true, true, OUT>(a, s, pdl);
+            return launch_norm<true, true, false, OUT>(a, s, pdl);
+        }
+        if (has_style) return launch_norm<true, false, true, OUT>(a, s, pdl);
+        return launch_norm<true, false, false, OUT>(a, s, pdl);
+    }
+    if (has_style) return launch_norm<false, false, true, OUT>(a, s, pdl);
+    return launch_norm<false, false, false, OUT>(a, s, pdl);
+}
 
 static inline bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
 
@@ -215,6 +254,7 @@ int frt_b200_norm_fp8(void* residual, const void* x, const void* gate_in, long l
     a.style = (const __nv_bfloat16*)style;
     a.style_stride = style_stride;
     a.out = out_fp8;
+    a.sf_out = nullptr;
     a.gate_out = (__nv_bfloat16*)gate_out;
     a.d_scale = d_scale;
     a.rows = rows;
@@ -224,14 +264,14 @@ int frt_b200_norm_fp8(void* residual, const void* x, const void* gate_in, long l
     bool pdl = flags & 1;
     if (x) {
         if (gate_in) {
-            if (style) return launch_norm<true, true, true, true>(a, s, pdl);
-            return launch_norm<true, true, false, true>(a, s, pdl);
+            if (style) return launch_norm<true, true, true, OUT_E4M3>(a, s, pdl);
+            return launch_norm<true, true, false, OUT_E4M3>(a, s, pdl);
         }
-        if (style) return launch_norm<true, false, true, true>(a, s, pdl);
-        return launch_norm<true, false, false, true>(a, s, pdl);
+        if (style) return launch_norm<true, false, true, OUT_E4M3>(a, s, pdl);
+        return launch_norm<true, false, false, OUT_E4M3>(a, s, pdl);
     }
-    if (style) return launch_norm<false, false, true, true>(a, s, pdl);
-    return launch_norm<false, false, false, true>(a, s, pdl);
+    if (style) return launch_norm<false, false, true, OUT_E4M3>(a, s, pdl);
+    return launch_norm<false, false, false, OUT_E4M3>(a, s, pdl);
 }
 
 int frt_b200_norm_bf16(void* residual, const void* x, const void* gate_in, long long gate_in_stride,
@@ -252,6 +292,7 @@ int frt_b200_norm_bf16(void* residual, const void* x, const void* gate_in, long 
     a.style = (const __nv_bfloat16*)style;
     a.style_stride = style_stride;
     a.out = out_bf16;
+    a.sf_out = nullptr;
     a.gate_out = (__nv_bfloat16*)gate_out;
     a.d_scale = nullptr;
     a.rows = rows;
@@ -261,14 +302,49 @@ int frt_b200_norm_bf16(void* residual, const void* x, const void* gate_in, long 
     bool pdl = flags & 1;
     if (x) {
         if (gate_in) {
-            if (style) return launch_norm<true, true, true, false>(a, s, pdl);
-            return launch_norm<true, true, false, false>(a, s, pdl);
+            if (style) return launch_norm<true, true, true, OUT_BF16>(a, s, pdl);
+            return launch_norm<true, true, false, OUT_BF16>(a, s, pdl);
         }
-        if (style) return launch_norm<true, false, true, false>(a, s, pdl);
-        return launch_norm<true, false, false, false>(a, s, pdl);
+        if (style) return launch_norm<true, false, true, OUT_BF16>(a, s, pdl);
+        return launch_norm<true, false, false, OUT_BF16>(a, s, pdl);
     }
-    if (style) return launch_norm<false, false, true, false>(a, s, pdl);
-    return launch_norm<false, false, false, false>(a, s, pdl);
+    if (style) return launch_norm<false, false, true, OUT_BF16>(a, s, pdl);
+    return launch_norm<false, false, false, OUT_BF16>(a, s, pdl);
+}
+
+// Same fused norm with an NVFP4 result: packed e2m1 (rows, dim / 2) and block scales in the GEMM's scale-factor
+// atoms (zero-filled by the caller once).  The modulated value is rounded to bf16 first, so the result equals
+// frt_b200_norm_bf16 followed by frt_b200_quantize_nvfp4 byte for byte.  dim % 16 == 0.  family: 0 / 1.
+int frt_b200_norm_nvfp4(void* residual, const void* x, const void* gate_in, long long gate_in_stride,
+                        const void* weight, const void* style, long long style_stride, void* out_packed,
+                        void* out_sf, void* gate_out, int rows, int dim, float eps, int family, int flags,
+                        void* stream) {
+    if (!residual || !out_packed || !out_sf) return FRT_ERR_INVALID;
+    if (gate_in && !x) return FRT_ERR_INVALID;
+    if (family != 0 && family != 1) return FRT_ERR_INVALID;
+    if (dim % 16) return FRT_ERR_UNSUPPORTED;
+    if (misaligned16(residual) || misaligned16(x) || misaligned16(gate_in) || misaligned16(weight) ||
+        misaligned16(style) || misaligned16(gate_out) || (reinterpret_cast<uintptr_t>(out_packed) & 3))
+        return FRT_ERR_INVALID;
+    if ((gate_in_stride & 7) || (style_stride & 7)) return FRT_ERR_INVALID;
+    NormArgs a;
+    a.residual = (__nv_bfloat16*)residual;
+    a.x = (const __nv_bfloat16*)x;
+    a.gate_in = (const __nv_bfloat16*)gate_in;
+    a.gate_in_stride = gate_in_stride;
+    a.weight = (const __nv_bfloat16*)weight;
+    a.style = (const __nv_bfloat16*)style;
+    a.style_stride = style_stride;
+    a.out = out_packed;
+    a.sf_out = (uint8_t*)out_sf;
+    a.gate_out = (__nv_bfloat16*)gate_out;
+    a.d_scale = nullptr;
+    a.rows = rows;
+    a.dim = dim;
+    a.eps = eps;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (family == 0) return dispatch_norm_nvfp4<OUT_NVFP4_A>(a, x != nullptr, gate_in != nullptr, style != nullptr, s, flags & 1);
+    return dispatch_norm_nvfp4<OUT_NVFP4_B>(a, x != nullptr, gate_in != nullptr, style != nullptr, s, flags & 1);
 }
 
 }  // extern "C"

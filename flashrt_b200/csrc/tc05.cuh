@@ -102,6 +102,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+// untiled bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, bytes % 16 == 0
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -241,6 +248,29 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uin
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Block-scaled NVFP4 (kind::mxf4nvf4, one unsigned-E4M3 scale per 16 elements, K = 64 per instruction).
+// Instruction descriptor: [7,10) A format, [10,13) B format (1 = e2m1), [17,23) N >> 3, [23] scale format
+// (0 = UE4M3), [24,29) M >> 4; the scale-factor ids (bits 4-5 and 29-30) stay 0 with four scales per row.
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) {
+    return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+// Scale factors of 128 rows x 4 blocks (one 512-byte atom: 32 rows of 16 bytes) from shared memory into
+// 4 tensor-memory columns at `taddr`, replicated into all four 32-lane sub-partitions: row r's four scale
+// bytes land in lane r % 32, column r / 32.  Issued by the thread that issues the MMAs; ordered with them.
+__device__ __forceinline__ void tmem_cp_sf_atom(uint32_t taddr, uint32_t saddr) {
+    // no-swizzle K-major descriptor: 8-row core matrices of 16-byte rows, 128 bytes apart
+    const uint64_t desc = make_smem_desc(saddr, 0, 128, 0);
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_nvfp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
         : "memory");
 }
 // all MMAs issued so far by this thread -> one arrival on `bar` when they complete

@@ -73,6 +73,38 @@ def gate_residual_ada_norm_fp8(residual, x, gate, weight, style, out, gate_out, 
          d_scale, _f(pdl), stream)
 
 
+# ------------------------------------------------------------------ NVFP4 producers of this module (family 0:
+# ceil-rounded UE4M3 block scale, '<' thresholds; csrc/bindings.cpp:1277-1285,1475-1590)
+def quantize_bf16_to_nvfp4_swizzled(input, fp4_data, scale_factors, rows, cols, stream=0, *, pdl=False):
+    call("frt_b200_quantize_nvfp4", input, fp4_data, scale_factors, rows, cols, 0, None, _f(pdl), stream)
+
+
+quantize_bf16_to_nvfp4_swizzled_v2 = quantize_bf16_to_nvfp4_swizzled
+
+
+def rms_norm_to_nvfp4_swizzled_bf16(x, weight, packed, sf_swz, rows, cols, eps=1e-6, stream=0, *, pdl=False):
+    call("frt_b200_norm_nvfp4", x, None, None, 0, weight, None, 0, packed, sf_swz, None, rows, cols, eps, 0,
+         _f(pdl), stream)
+
+
+rms_norm_to_nvfp4_swizzled_bf16_v2 = rms_norm_to_nvfp4_swizzled_bf16
+rms_norm_to_nvfp4_swizzled_bf16_v3 = rms_norm_to_nvfp4_swizzled_bf16
+
+
+def residual_add_rms_norm_to_nvfp4_swizzled_bf16(h_in, attn_proj, h_post, weight, packed, sf_swz, rows, cols,
+                                                 eps=1e-6, stream=0, *, pdl=False):
+    """h_post = h_in + attn_proj; NVFP4(rms_norm(h_post) * weight).  The kernel updates in place, so a distinct
+    h_post is first filled with h_in."""
+    if h_post != h_in:
+        call("frt_b200_copy", h_post, h_in, rows * cols * 2, stream)
+        pdl = False
+    call("frt_b200_norm_nvfp4", h_post, attn_proj, None, 0, weight, None, 0, packed, sf_swz, None, rows, cols, eps,
+         0, _f(pdl), stream)
+
+
+residual_add_rms_norm_to_nvfp4_swizzled_bf16_v2 = residual_add_rms_norm_to_nvfp4_swizzled_bf16
+
+
 # ------------------------------------------------------------------ activation (csrc/bindings.cpp:1031-1044)
 def gate_geglu_merged(merged, out, seq, half_dim, stream=0, *, pdl=False):
     call("frt_b200_geglu_bf16", merged, out, seq, half_dim, _f(pdl), stream)

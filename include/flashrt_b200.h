@@ -219,6 +219,56 @@ int frt_b200_adaln_modulation6(const float* adaln_params, const float* layer_mod
                                void* out2, void* out3, void* out4, void* out5, int B, int S, int D, int flags,
                                void* stream);
 
+/* ---------------------------------------------------------------- NVFP4 (e2m1 x 16-element blocks x unsigned-E4M3 scales)
+ * Packed data: two elements per byte, low nibble = even element, row = K / 2 bytes.
+ * Scales: one byte per 16 elements, stored in 512-byte atoms of 128 rows x 4 blocks --
+ *   offset(row, blk) = ((row / 128) * ceil(K / 64) + blk / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + blk % 4
+ * (csrc/kernels/quantize.cu:476-486; CUTLASS Sm1xxBlockScaledConfig<16> at csrc/quantize/quantize_fp4_sfa.cu:191-206).
+ * Scale buffers are zero-filled once by the caller: padding entries are never written (flash_rt/executors/fp4_utils.py:78-86).
+ * `family` selects the reference's quantiser convention:
+ *   0 = flash_rt_kernels  (scale = smallest UE4M3 >= amax / 6, thresholds '<')   csrc/kernels/nvfp4_convert.cuh:31-105
+ *   1 = flash_rt_fp4      (scale = RN-even E4M3 of max(amax / 6, 1e-12), '<=')   csrc/quantize/quantize_fp4_sfa.cu:31-109
+ * The reference's quantisers carry no FP32 global scale; here an optional device float g divides the input first
+ * and the caller folds g into the GEMM's alpha. */
+
+/* sfa_size_bytes               csrc/fp4_bindings.cpp:349-352  (*out_bytes is a host pointer) */
+int frt_b200_nvfp4_sf_bytes(long long rows, int K, long long* out_bytes);
+/* quantize_bf16_to_nvfp4_swizzled        csrc/bindings.cpp:1277-1285 -> csrc/kernels/quantize.cu:450-526   (family 0)
+ * quantize_fp4_dynamic_sfa_bf16_vec      csrc/fp4_bindings.cpp:1124-1137                                    (family 1)
+ * quantize_fp4_dynamic_sfa_fp16[_vec]    csrc/fp4_bindings.cpp:299-333 -> csrc/quantize/quantize_fp4_sfa.cu:63-109
+ *   in (rows, D) bf16 -> packed (rows, D / 2), sf.  D % 16 == 0.  The same call quantises weights (is_sfb). */
+int frt_b200_quantize_nvfp4(const void* in, void* packed, void* sf, long long rows, int D, int family,
+                            const float* d_global_scale, int flags, void* stream);
+/* gate_geglu_fp4_sfa[_v2,_vec]_fp16      csrc/fp4_bindings.cpp:711-753 -> csrc/fused_fp4/silu_mul_fp4_sfa_vec.cu:50-107
+ *   merged (rows, 2H) bf16 = [gate | up] -> NVFP4 of the fp32 product gelu_tanh(gate) * up.  H % 16 == 0. */
+int frt_b200_geglu_nvfp4(const void* merged, void* packed, void* sf, int rows, int H, int family, int flags,
+                         void* stream);
+/* pi05_adarms_fp4_sfa[_native]_fp16              csrc/fp4_bindings.cpp:547-570,602-625
+ * pi05_gate_res_adarms_fp4_sfa[_native]_fp16     csrc/fp4_bindings.cpp:572-600,627-657 -> csrc/fused_fp4/norm_silu_fp4_sfa.cu:147-268
+ * rms_norm_fp4_sfa_fp16, residual_add_rms_norm_fp4_sfa[_v2]_fp16   csrc/fp4_bindings.cpp:501-545
+ * rms_norm_to_nvfp4_swizzled_bf16, residual_add_rms_norm_to_nvfp4_swizzled_bf16   csrc/bindings.cpp:1475-1590 -> csrc/kernels/quantize.cu:1656-1755,2114-2226
+ *   the fused norm of frt_b200_norm_fp8 with an NVFP4 result: the modulated value is rounded to bf16 and then
+ *   block-quantised, i.e. byte-identical to frt_b200_norm_bf16 followed by frt_b200_quantize_nvfp4.
+ *   Any row count and any dim % 16 == 0 (the reference's pi05 entries accept seq_len 10, dim 1024 only). */
+int frt_b200_norm_nvfp4(void* residual, const void* x, const void* gate_in, long long gate_in_stride,
+                        const void* weight, const void* style, long long style_stride, void* out_packed,
+                        void* out_sf, void* gate_out, int rows, int dim, float eps, int family, int flags,
+                        void* stream);
+/* cutlass_fp4_gemm_variant, cutlass_fp4_sq_fp16   csrc/fp4_bindings.cpp:85-99,355-370 -> csrc/gemm/fp4/cutlass_fp4_gemm.cu
+ * cutlass_fp4_gemm_bias_bf16                       csrc/fp4_bindings.cpp:1139-1155
+ *   D(M,N) bf16 = alpha * (*d_alpha) * (A.SFA)(M,K) . (W.SFW)(N,K)^T + bias;  d_alpha, bias optional;  K % 256 == 0;
+ *   beta is not supported (the decoder path calls with beta = 0).  One kernel for every variant index. */
+int frt_b200_gemm_nvfp4_nt(const void* A, const void* SFA, const void* W, const void* SFW, void* D, int M, int N,
+                           int K, float alpha, const float* d_alpha, const void* bias, int splits, int flags,
+                           void* stream);
+/* cutlass_fp4_gemm_variant (csrc/fp4_bindings.cpp:355-370) + qkv_split_rope_kvcache_fp16[_devpos,_vec] fused, the pair
+ * called at flash_rt/models/pi05/pipeline_thor.py:366-385:
+ *   the NVFP4 form of frt_b200_gemm_fp8_nt_rope_split. */
+int frt_b200_gemm_nvfp4_nt_rope_split(const void* A, const void* SFA, const void* W, const void* SFW, int M, int K,
+                                      float alpha, const void* rope, void* Q, void* Kout, void* Vout,
+                                      const int* devpos, int q_dim, int k_dim, int v_dim, int head_dim, int splits,
+                                      int flags, void* stream);
+
 /* ---------------------------------------------------------------- small bf16 projections, copies, queries
  * GemmRunner::bf16_nn          csrc/bindings.cpp:662-667  (action in/out projections 32 <-> 1024)
  *   D(M,N) = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate != 0); B bf16 row-major (K,N).

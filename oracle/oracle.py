@@ -47,6 +47,14 @@ def lib() -> C.CDLL:
         L.orc_amax_scale.restype = C.c_float
         L.orc_det_gelu_tanh_form.restype = C.c_float
         L.orc_det_gelu_tanh_form.argtypes = [C.c_float]
+        L.orc_ue4m3_to_f32.restype = C.c_float
+        L.orc_ue4m3_to_f32.argtypes = [C.c_uint8]
+        L.orc_ue4m3_ceil.restype = C.c_uint8
+        L.orc_ue4m3_ceil.argtypes = [C.c_float]
+        L.orc_nvfp4_sf_offset.restype = C.c_longlong
+        L.orc_nvfp4_sf_offset.argtypes = [C.c_longlong, C.c_int, C.c_int]
+        L.orc_nvfp4_sf_size.restype = C.c_longlong
+        L.orc_nvfp4_sf_size.argtypes = [C.c_longlong, C.c_int]
         _LIB = L
     return _LIB
 
@@ -263,3 +271,62 @@ def adaln_modulation6(params, layer_mod):
     out = np.zeros((6, BS, D), np.uint16)
     lib().orc_adaln_modulation6(_p(params), _p(layer_mod), _p(out), C.c_longlong(BS), C.c_int(D))
     return out
+
+
+# ---------------------------------------------------------------- NVFP4
+E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float32)
+
+
+def nvfp4_sf_size(rows: int, K: int) -> int:
+    return int(lib().orc_nvfp4_sf_size(rows, K))
+
+
+def nvfp4_sf_offsets(rows: int, K: int) -> np.ndarray:
+    """(rows, K/16) table of scale-byte offsets."""
+    r = np.arange(rows, dtype=np.int64)[:, None]
+    b = np.arange(K // 16, dtype=np.int64)[None, :]
+    katoms = (K + 63) // 64
+    return ((r // 128) * katoms + b // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4
+
+
+def quantize_nvfp4(x, family: int, global_scale: float = 1.0):
+    """x: bf16 bit patterns (uint16) or float32, shape (rows, D).  Returns (packed (rows, D/2), sf bytes)."""
+    x = np.ascontiguousarray(x)
+    rows, D = x.shape
+    packed = np.zeros((rows, D // 2), np.uint8)
+    sf = np.zeros(nvfp4_sf_size(rows, D), np.uint8)
+    fn = lib().orc_nvfp4_quantize_bf16 if x.dtype == np.uint16 else lib().orc_nvfp4_quantize_f32
+    assert x.dtype in (np.uint16, np.float32)
+    fn(_p(x), _p(packed), _p(sf), C.c_longlong(rows), C.c_int(D), C.c_int(family), C.c_float(global_scale))
+    return packed, sf
+
+
+def dequantize_nvfp4(packed, sf, global_scale: float = 1.0) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, np.uint8)
+    sf = np.ascontiguousarray(sf, np.uint8)
+    rows, half = packed.shape
+    out = np.zeros((rows, 2 * half), np.float32)
+    lib().orc_nvfp4_dequantize(_p(packed), _p(sf), _p(out), C.c_longlong(rows), C.c_int(2 * half),
+                               C.c_float(global_scale))
+    return out
+
+
+def geglu_nvfp4(merged, family: int = 1):
+    merged = _u16(merged)
+    rows, two_h = merged.shape
+    H = two_h // 2
+    packed = np.zeros((rows, H // 2), np.uint8)
+    sf = np.zeros(nvfp4_sf_size(rows, H), np.uint8)
+    lib().orc_geglu_nvfp4(_p(merged), _p(packed), _p(sf), C.c_int(rows), C.c_int(H), C.c_int(family))
+    return packed, sf
+
+
+def gemm_nvfp4(a_packed, a_sf, w_packed, w_sf, alpha: float = 1.0, bias=None, want_f32: bool = False):
+    """D = alpha * dequant(A) . dequant(W)^T (+ bias), float64 accumulation, bf16 bits out (or float32)."""
+    A = dequantize_nvfp4(a_packed, a_sf).astype(np.float64)
+    W = dequantize_nvfp4(w_packed, w_sf).astype(np.float64)
+    D = (A @ W.T) * float(alpha)
+    if bias is not None:
+        D = D + bf16_bits_to_f32(_u16(bias)).astype(np.float64)[None, :]
+    D = D.astype(np.float32)
+    return D if want_f32 else f32_to_bf16_bits(D)

@@ -32,6 +32,7 @@
  */
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 /* ------------------------------------------------------------------ formats */
@@ -487,4 +488,140 @@ void orc_adaln_modulation6(const float* params, const float* layer_mod, uint16_t
         for (int j = 0; j < 6; ++j)
             for (int d = 0; d < D; ++d)
                 out6[((size_t)j * BS + bs) * D + d] = f32_to_bf16(params[(bs * 6 + j) * D + d] + layer_mod[(size_t)j * D + d]);
+}
+
+/* ================================================================== NVFP4
+ * e2m1 elements (+-{0, .5, 1, 1.5, 2, 3, 4, 6}), 16-element blocks, one unsigned E4M3 scale per block,
+ * scale bytes in the 128-row x 4-block atoms of the block-scaled GEMM.  Two quantiser conventions exist
+ * in the reference and both are restated here:
+ *   family 0 ("A", flash_rt_kernels: quantize_bf16_to_nvfp4[_swizzled], csrc/kernels/quantize.cu:375-526,
+ *             conversions csrc/kernels/nvfp4_convert.cuh:31-105): scale = ceil_UE4M3(amax / 6) (rounded up,
+ *             top code 0xFE, zero block -> 0), inv = scale > 0 ? 1 / scale : 0, thresholds compared with '<'
+ *             (a tie goes to the larger magnitude);
+ *   family 1 ("B", flash_rt_fp4: quantize_fp4_dynamic_sfa_*, csrc/quantize/quantize_fp4_sfa.cu:31-109 and the
+ *             fused producers csrc/fused_fp4/norm_silu_fp4_sfa.cu:64-147, silu_mul_fp4_sfa_vec.cu:33-107):
+ *             scale = RN-even E4M3 of max(amax / 6, 1e-12), inv = 1 / scale (IEEE: a zero scale gives inf and
+ *             0 * inf = NaN, which falls through every '<=' test to code 7), thresholds compared with '<='
+ *             (a tie goes to the smaller magnitude).
+ * Low nibble = even element.  An optional FP32 global scale g divides the input first (x * (1 / g)); the
+ * reference's quantisers carry none (g = 1).  Divisions are IEEE here; the reference builds with fast-math. */
+
+static inline float ue4m3_to_f32(uint8_t c) {
+    int e = (c >> 3) & 0xF, m = c & 7;
+    if (e == 0) return ldexpf((float)m * 0.125f, -6);
+    return ldexpf(1.0f + (float)m * 0.125f, e - 7);
+}
+float orc_ue4m3_to_f32(uint8_t c) { return ue4m3_to_f32(c); }
+
+/* smallest unsigned-E4M3 value >= v (top code 0xFE above 240, as the reference) */
+static inline uint8_t ue4m3_ceil(float v) {
+    if (!(v > 0.0f)) return 0;
+    if (v > 240.0f) return 0xFE;
+    if (v < 0.015625f) {                       /* below 2^-6: subnormal step 2^-9 */
+        int m = (int)ceilf(v * 512.0f);
+        if (m > 7) return 0x08;                /* smallest normal */
+        return (uint8_t)(m < 1 ? 1 : m);
+    }
+    int e;
+    float f = frexpf(v, &e);                   /* v = f * 2^e, f in [0.5, 1) */
+    float t = (f * 2.0f - 1.0f) * 8.0f;        /* exact: mantissa steps of 1/8 above 2^(e-1) */
+    int m = (int)ceilf(t);
+    int ex = e - 1 + 7;
+    if (m >= 8) { m = 0; ex += 1; }
+    if (ex >= 15) return 0xFE;
+    return (uint8_t)((ex << 3) | m);
+}
+uint8_t orc_ue4m3_ceil(float v) { return ue4m3_ceil(v); }
+
+static inline uint8_t e2m1_code(float v, int family) {
+    static const float th[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.0f};
+    uint8_t sign = (v < 0.0f) ? 8u : 0u;
+    float a = fabsf(v);
+    int below = 0;                             /* thresholds the magnitude stays under; NaN stays under none */
+    for (int i = 0; i < 7; ++i) below += family ? (a <= th[i]) : (a < th[i]);
+    return (uint8_t)(sign | (7 - below));
+}
+static inline float e2m1_to_f32(uint8_t c) {
+    static const float lut[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    float m = lut[c & 7];
+    return (c & 8) ? -m : m;
+}
+
+/* byte offset of the scale of (row, 16-element block blk) for a row length of K elements */
+long long orc_nvfp4_sf_offset(long long row, int blk, int K) {
+    long long katoms = (K + 63) / 64;
+    return ((row / 128) * katoms + blk / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + blk % 4;
+}
+long long orc_nvfp4_sf_size(long long rows, int K) {
+    return ((rows + 127) / 128) * (long long)((K + 63) / 64) * 512;
+}
+
+/* quantise one block of 16 fp32 values; returns the scale byte */
+static uint8_t nvfp4_block(const float* v, uint8_t* packed8, int family) {
+    float amax = 0.0f;
+    for (int i = 0; i < 16; ++i) { float a = fabsf(v[i]); if (a > amax) amax = a; }
+    uint8_t sb;
+    float inv;
+    if (family == 0) {
+        sb = ue4m3_ceil(amax / 6.0f);
+        float s = ue4m3_to_f32(sb);
+        inv = s > 0.0f ? 1.0f / s : 0.0f;
+    } else {
+        float d = amax / 6.0f;
+        if (d < 1e-12f) d = 1e-12f;
+        sb = f32_to_e4m3(d);
+        inv = 1.0f / e4m3_to_f32(sb);
+    }
+    for (int p = 0; p < 8; ++p) {
+        uint8_t lo = e2m1_code(v[2 * p] * inv, family);
+        uint8_t hi = e2m1_code(v[2 * p + 1] * inv, family);
+        packed8[p] = (uint8_t)(lo | (hi << 4));
+    }
+    return sb;
+}
+
+/* in: fp32 (rows, D), D % 16 == 0.  packed (rows, D/2); sf: orc_nvfp4_sf_size(rows, D) bytes, zeroed by the caller */
+void orc_nvfp4_quantize_f32(const float* in, uint8_t* packed, uint8_t* sf, long long rows, int D, int family,
+                            float global_scale) {
+    float inv_g = 1.0f / global_scale;
+    for (long long r = 0; r < rows; ++r)
+        for (int b = 0; b < D / 16; ++b) {
+            float v[16];
+            for (int i = 0; i < 16; ++i) {
+                float x = in[r * D + b * 16 + i];
+                v[i] = (global_scale == 1.0f) ? x : x * inv_g;
+            }
+            sf[orc_nvfp4_sf_offset(r, b, D)] = nvfp4_block(v, packed + r * (D / 2) + b * 8, family);
+        }
+}
+void orc_nvfp4_quantize_bf16(const uint16_t* in, uint8_t* packed, uint8_t* sf, long long rows, int D, int family,
+                             float global_scale) {
+    float* tmp = (float*)malloc(sizeof(float) * (size_t)rows * D);
+    for (long long i = 0; i < rows * D; ++i) tmp[i] = bf16_to_f32(in[i]);
+    orc_nvfp4_quantize_f32(tmp, packed, sf, rows, D, family, global_scale);
+    free(tmp);
+}
+/* out fp32 (rows, D) = e2m1 * block scale * global_scale */
+void orc_nvfp4_dequantize(const uint8_t* packed, const uint8_t* sf, float* out, long long rows, int D,
+                          float global_scale) {
+    for (long long r = 0; r < rows; ++r)
+        for (int c = 0; c < D; ++c) {
+            uint8_t byte = packed[r * (D / 2) + c / 2];
+            uint8_t code = (c & 1) ? (byte >> 4) : (byte & 15);
+            float s = ue4m3_to_f32(sf[orc_nvfp4_sf_offset(r, c / 16, D)] & 0x7F);
+            out[r * D + c] = e2m1_to_f32(code) * s * global_scale;
+        }
+}
+/* GeGLU straight to NVFP4 (gate_geglu_fp4_sfa_vec, csrc/fused_fp4/silu_mul_fp4_sfa_vec.cu:50-107): the fp32
+ * product gelu(gate) * up is quantised without an intermediate 16-bit rounding. */
+void orc_geglu_nvfp4(const uint16_t* merged, uint8_t* packed, uint8_t* sf, int rows, int H, int family) {
+    float* tmp = (float*)malloc(sizeof(float) * (size_t)rows * H);
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < H; ++c) {
+            float g = bf16_to_f32(merged[(size_t)r * 2 * H + c]);
+            float u = bf16_to_f32(merged[(size_t)r * 2 * H + H + c]);
+            tmp[(size_t)r * H + c] = det_gelu_tanh(g) * u;
+        }
+    orc_nvfp4_quantize_f32(tmp, packed, sf, rows, H, family, 1.0f);
+    free(tmp);
 }

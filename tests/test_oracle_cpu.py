@@ -220,3 +220,83 @@ def test_video_dit_oracle_vs_plain_formulas():
     got = torch.from_numpy(O.bf16_bits_to_f32(q)).double()
     assert (got[:2] - ref[:2]).abs().max() <= 2.0 ** -7 * ref.abs().max()
     assert (got[2] - qn[2]).abs().max() <= 2.0 ** -7 * qn.abs().max()       # row beyond seq_len: not rotated
+
+
+# ---------------------------------------------------------------- NVFP4 restatement
+def test_nvfp4_sf_layout_matches_cutlass_table():
+    """The closed-form scale-factor offset equals CUTLASS's Sm1xxBlockScaledConfig<16> layout (fixture generated
+    by tests/golden/make_sf_layout_golden.py) for SFA and SFB, including ragged rows and K not a multiple of 64."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "sf_layout.npz"))
+    cases = sorted(k[5:] for k in z.files if k.startswith("offs_"))
+    assert len(cases) >= 6
+    for c in cases:
+        rows, K, _ = (int(v) for v in c.split("_"))
+        assert O.nvfp4_sf_size(rows, K) == int(z["size_" + c][0])
+        table = O.nvfp4_sf_offsets(rows, K)
+        assert np.array_equal(table, z["offs_" + c])
+        for r, b in [(0, 0), (rows - 1, K // 16 - 1), (rows // 2, 1)]:
+            assert O.lib().orc_nvfp4_sf_offset(r, b, K) == table[r, b]
+
+
+def test_nvfp4_scale_conversions():
+    L = O.lib()
+    vals = np.array([L.orc_ue4m3_to_f32(c) for c in range(0x7F)], np.float64)
+    assert (np.diff(vals) > 0).all() and vals[0] == 0 and vals[0x38] == 1.0 and vals[0x7E] == 448.0
+    # the unsigned E4M3 decode agrees with the signed E4M3 table on non-negative codes
+    assert np.array_equal(vals.astype(np.float32), O.e4m3_lut()[:0x7F])
+    rng = np.random.default_rng(0)
+    samples = np.concatenate([np.exp(rng.uniform(np.log(1e-4), np.log(240.0), 4000)), vals[1:0x78],
+                              vals[1:0x78] * (1 + 1e-6), [240.0]]).astype(np.float32)
+    for v in samples:
+        c = L.orc_ue4m3_ceil(float(v))
+        if v > 240.0:
+            assert c == 0xFE
+            continue
+        assert vals[c] >= v                      # never below the input ...
+        assert c == 1 or vals[c - 1] < v         # ... and the smallest such code
+    assert L.orc_ue4m3_ceil(0.0) == 0 and L.orc_ue4m3_ceil(-1.0) == 0 and L.orc_ue4m3_ceil(241.0) == 0xFE
+
+
+def test_nvfp4_quantise_conventions():
+    """Ties and zero blocks behave as the two reference conventions say (nvfp4_convert.cuh:31-45,78-105;
+    quantize_fp4_sfa.cu:31-50,89-108)."""
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0],
+                    np.float32)[None, :]
+    pa, sa = O.quantize_nvfp4(ties, 0)
+    pb, sb = O.quantize_nvfp4(ties, 1)
+    assert sa[0] == 0x38 and sb[0] == 0x38                      # amax 6 -> scale 1.0 in both families
+    codes = lambda p: np.stack([p[0] & 15, p[0] >> 4], 1).ravel()
+    assert list(codes(pa)) == [1, 2, 3, 4, 5, 6, 7, 7, 9, 10, 11, 12, 13, 14, 15, 15]   # '<': tie -> larger magnitude
+    assert list(codes(pb)) == [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15]    # '<=': tie -> smaller; -0.25 -> -0
+    zero = np.zeros((1, 16), np.float32)
+    pa, sa = O.quantize_nvfp4(zero, 0)
+    pb, sb = O.quantize_nvfp4(zero, 1)
+    assert sa[0] == 0 and (pa == 0).all()
+    assert sb[0] == 0 and (pb == 0x77).all()                    # 0 * inf = NaN falls through to code 7; scale 0 keeps it inert
+    assert (O.dequantize_nvfp4(pb, sb) == 0).all()
+    # the widest e2m1 gap (4 -> 6) is two scale units, the scale at most amax / 6 * (1 + 1/8)
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((64, 256)) * 3).astype(np.float32)
+    for fam in (0, 1):
+        p, s = O.quantize_nvfp4(x, fam)
+        d = O.dequantize_nvfp4(p, s)
+        blk_amax = np.abs(x).reshape(64, 16, 16).max(-1)
+        err = np.abs(d - x).reshape(64, 16, 16).max(-1)
+        assert (err <= blk_amax / 6.0 * 1.13 + 1e-6).all()
+    # global scale: x / g quantised, dequantised value * g
+    p, s = O.quantize_nvfp4(x, 1, 0.5)
+    assert np.allclose(O.dequantize_nvfp4(p, s, 0.5), x, atol=np.abs(x).max() / 6)
+
+
+def test_nvfp4_gemm_oracle_shapes():
+    rng = np.random.default_rng(2)
+    a = O.f32_to_bf16_bits(rng.standard_normal((5, 64)).astype(np.float32))
+    w = O.f32_to_bf16_bits(rng.standard_normal((7, 64)).astype(np.float32))
+    Ap, Asf = O.quantize_nvfp4(a, 1)
+    Wp, Wsf = O.quantize_nvfp4(w, 1)
+    D = O.gemm_nvfp4(Ap, Asf, Wp, Wsf, want_f32=True)
+    ref = O.bf16_bits_to_f32(a) @ O.bf16_bits_to_f32(w).T
+    assert D.shape == (5, 7)
+    from_cos = float((D.ravel() @ ref.ravel()) / (np.linalg.norm(D) * np.linalg.norm(ref)))
+    assert from_cos > 0.98
