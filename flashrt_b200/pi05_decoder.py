@@ -41,10 +41,27 @@ BF16 = torch.bfloat16
 
 
 # ------------------------------------------------------------------ weight spec (plugin contract)
-def build_spec(layers: int = DEC_L, num_steps: int = NUM_STEPS_DEFAULT) -> ModelWeightSpec:
-    """HF key names of the Gemma expert and the action heads (pi05_rtx.py:216-283)."""
+def build_spec(layers: int = DEC_L, num_steps: int = NUM_STEPS_DEFAULT, precision: str = "fp8") -> ModelWeightSpec:
+    """HF key names of the Gemma expert and the action heads (pi05_rtx.py:216-283).  ``precision="nvfp4"`` keeps
+    the four projections in bf16 (N, K) for the device-side NVFP4 quantiser (fp4_utils.py:62-99)."""
     dp = "paligemma_with_expert.gemma_expert.model.layers.{i}"
-    dec = LayerBlock(prefix_fmt="", num_layers=layers, name="decoder", items=[
+    if precision == "nvfp4":
+        dec = LayerBlock(prefix_fmt="", num_layers=layers, name="decoder", items=[
+            Item("qkv_w", FusedQKV(q=f"{dp}.self_attn.q_proj.weight", k=f"{dp}.self_attn.k_proj.weight",
+                                   v=f"{dp}.self_attn.v_proj.weight", interleave_q_heads=DEC_NH,
+                                   interleave_k_heads=DEC_NKV), [ToBf16()], TensorList("wb_qkv")),
+            Item("o_w", f"{dp}.self_attn.o_proj.weight", [ToBf16()], TensorList("wb_o")),
+            Item("gu_w", FusedGateUp(gate=f"{dp}.mlp.gate_proj.weight", up=f"{dp}.mlp.up_proj.weight"),
+                 [ToBf16()], TensorList("wb_gu")),
+            Item("d_w", f"{dp}.mlp.down_proj.weight", [ToBf16()], TensorList("wb_d")),
+        ])
+    else:
+        dec = _fp8_decoder_block(dp, layers)
+    return _finish_spec(dec, dp, layers, num_steps)
+
+
+def _fp8_decoder_block(dp: str, layers: int) -> LayerBlock:
+    return LayerBlock(prefix_fmt="", num_layers=layers, name="decoder", items=[
         Item("qkv_w", FusedQKV(q=f"{dp}.self_attn.q_proj.weight", k=f"{dp}.self_attn.k_proj.weight",
                                v=f"{dp}.self_attn.v_proj.weight", interleave_q_heads=DEC_NH,
                                interleave_k_heads=DEC_NKV),
@@ -54,6 +71,9 @@ def build_spec(layers: int = DEC_L, num_steps: int = NUM_STEPS_DEFAULT) -> Model
              [Quant()], FlatCat("w_gu"), scale_into="ws_gu"),
         Item("d_w", f"{dp}.mlp.down_proj.weight", [Quant()], FlatCat("w_d"), scale_into="ws_d"),
     ])
+
+
+def _finish_spec(dec: LayerBlock, dp: str, layers: int, num_steps: int) -> ModelWeightSpec:
     mods = LayerBlock(prefix_fmt="", num_layers=layers, name="decoder_mods", items=[
         Item("attn_mod_w", f"{dp}.input_layernorm.dense.weight", [tT(), ToBf16()], TensorList("attn_mod_w")),
         Item("attn_mod_b", f"{dp}.input_layernorm.dense.bias", [ToBf16()], TensorList("attn_mod_b")),
@@ -320,7 +340,8 @@ class Pi05DecoderB200:
 
     def __init__(self, checkpoint, *, num_steps: int = NUM_STEPS_DEFAULT, chunk_size: int = CHUNK_DEFAULT,
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
-                 use_cuda_graph: bool = True, fuse_epilogues: bool = True, **_ignored):
+                 use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
+                 **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -331,7 +352,14 @@ class Pi05DecoderB200:
         self.use_pdl, self.use_cuda_graph, self.fuse_epilogues = use_pdl, use_cuda_graph, fuse_epilogues
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.kv_rows = prefix_len + chunk_size
-        self.WEIGHT_SPEC = build_spec(layers, num_steps)
+        if precision not in ("fp8", "nvfp4"):
+            raise ValueError(f"precision must be 'fp8' or 'nvfp4', got {precision!r}")
+        if batch != 1 and precision != "nvfp4":
+            raise ValueError("a batch of chunks is implemented for precision='nvfp4' only")
+        if batch < 1 or batch * ((chunk_size * DEC_NH + 127) // 128) * 8 > self.sm_count:
+            raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")
+        self.precision, self.batch = precision, batch
+        self.WEIGHT_SPEC = build_spec(layers, num_steps, precision)
         if isinstance(checkpoint, dict):
             source = DictSource(checkpoint)
         elif isinstance(checkpoint, str) and checkpoint.startswith("synthetic"):
@@ -341,33 +369,53 @@ class Pi05DecoderB200:
             source = SafetensorsSource(str(checkpoint))
         WeightLoader(source, target=self, spec=self.WEIGHT_SPEC).run()
         dev = self.device
-        # FP8 weights as raw bytes on the device, (L, N, K)
-        for n in ("w_qkv", "w_o", "w_gu", "w_d"):
-            setattr(self, n, getattr(self, n).view(torch.uint8).to(dev))
-        for n in ("ws_qkv", "ws_o", "ws_gu", "ws_d"):
-            setattr(self, n + "_t", torch.tensor(getattr(self, n), dtype=torch.float32, device=dev))
+        if precision == "nvfp4":
+            from .pi05_decoder_nvfp4 import Nvfp4Weight
+            self.w4 = []
+            for i in range(layers):
+                self.w4.append({k: Nvfp4Weight(getattr(self, "wb_" + k)[i].to(dev)) for k in ("qkv", "o", "gu", "d")})
+            for k in ("qkv", "o", "gu", "d"):
+                delattr(self, "wb_" + k)
+        else:
+            # FP8 weights as raw bytes on the device, (L, N, K)
+            for n in ("w_qkv", "w_o", "w_gu", "w_d"):
+                setattr(self, n, getattr(self, n).view(torch.uint8).to(dev))
+            for n in ("ws_qkv", "ws_o", "ws_gu", "ws_d"):
+                setattr(self, n + "_t", torch.tensor(getattr(self, n), dtype=torch.float32, device=dev))
         sa, sf, fin = precompute_styles(self, num_steps, layers)
         self.style_attn, self.style_ffn, self.style_final = sa.to(dev), sf.to(dev), fin.to(dev)
         for n in ("action_in_w", "action_in_b", "action_out_w", "action_out_b"):
             setattr(self, n, getattr(self, n).contiguous().to(dev))
         self.rope = rope_table(prefix_len, chunk_size).to(dev)
-        self.k_cache = torch.zeros(layers, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
-        self.v_cache = torch.zeros_like(self.k_cache)
-        self.pipeline = Pi05DecoderPipeline(self)
+        if precision == "nvfp4":
+            from .pi05_decoder_nvfp4 import Pi05DecoderNvfp4Pipeline
+            # one cache per batch element: (layers, batch, prefix + chunk, 256)
+            self.k_cache = torch.zeros(layers, batch, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
+            self.v_cache = torch.zeros_like(self.k_cache)
+            self.pipeline = Pi05DecoderNvfp4Pipeline(self)
+        else:
+            self.k_cache = torch.zeros(layers, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
+            self.v_cache = torch.zeros_like(self.k_cache)
+            self.pipeline = Pi05DecoderPipeline(self)
         self.stream = torch.cuda.Stream(device=dev)
         self.graph = None
-        self._pinned_in = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32).pin_memory()
-        self._pinned_out = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32).pin_memory()
-        self._dev_in = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32, device=dev)
-        self._dev_out = torch.zeros(chunk_size, ACTION_DIM, dtype=torch.float32, device=dev)
+        rows = batch * chunk_size
+        self._pinned_in = torch.zeros(rows, ACTION_DIM, dtype=torch.float32).pin_memory()
+        self._pinned_out = torch.zeros(rows, ACTION_DIM, dtype=torch.float32).pin_memory()
+        self._dev_in = torch.zeros(rows, ACTION_DIM, dtype=torch.float32, device=dev)
+        self._dev_out = torch.zeros(rows, ACTION_DIM, dtype=torch.float32, device=dev)
         self.latency_records: list[float] = []
 
     # ---- prefix (what the encoder would have written) ---------------------
     def set_prefix(self, prefix_k: torch.Tensor, prefix_v: torch.Tensor) -> None:
         """prefix_k / prefix_v: (layers, prefix_len, 256); K already carries its RoPE, as in the encoder's cache."""
         assert prefix_k.shape == (self.layers, self.prefix_len, DEC_NKV * DEC_HD), prefix_k.shape
-        self.k_cache[:, :self.prefix_len].copy_(prefix_k.to(BF16))
-        self.v_cache[:, :self.prefix_len].copy_(prefix_v.to(BF16))
+        if self.precision == "nvfp4":      # every batch element attends to the same prefix
+            self.k_cache[:, :, :self.prefix_len].copy_(prefix_k.to(BF16).unsqueeze(1).expand(-1, self.batch, -1, -1))
+            self.v_cache[:, :, :self.prefix_len].copy_(prefix_v.to(BF16).unsqueeze(1).expand(-1, self.batch, -1, -1))
+        else:
+            self.k_cache[:, :self.prefix_len].copy_(prefix_k.to(BF16))
+            self.v_cache[:, :self.prefix_len].copy_(prefix_v.to(BF16))
         torch.cuda.synchronize(self.device)
 
     # ---- calibration --------------------------------------------------------
@@ -380,6 +428,8 @@ class Pi05DecoderB200:
         the eager dynamic-scale pass; the table keeps the max over samples (``percentile`` None) or the given
         percentile of the per-sample scales (flash_rt/core/calibration.py:38-64)."""
         p = self.pipeline
+        if self.precision == "nvfp4":
+            return                      # block scales are computed by the producing kernels at run time
         per_sample = []
         with torch.cuda.stream(self.stream):
             for nz in noises:
@@ -441,21 +491,24 @@ class Pi05DecoderB200:
         """obs["noise"]: (chunk, 32) array or tensor on the HOST (a fresh N(0,1) draw if absent).  Uploads it,
         replays the loop, downloads the actions (pi05_rtx.py:1547-1614)."""
         nz = obs.get("noise") if obs else None
+        shape = (self.chunk_size, ACTION_DIM) if self.batch == 1 else (self.batch, self.chunk_size, ACTION_DIM)
         if nz is None:
-            nz = torch.randn(self.chunk_size, ACTION_DIM)
+            nz = torch.randn(*shape)
         nz = torch.as_tensor(nz, dtype=torch.float32)
-        self._pinned_in.copy_(nz)
+        self._pinned_in.copy_(nz.reshape(self._pinned_in.shape))
         with torch.cuda.stream(self.stream):
             self._dev_in.copy_(self._pinned_in, non_blocking=True)
         self.forward_decode_only()
         with torch.cuda.stream(self.stream):
             self._pinned_out.copy_(self._dev_out, non_blocking=True)
         self.stream.synchronize()
-        return {"actions": self._pinned_out.numpy().copy()}
+        return {"actions": self._pinned_out.numpy().reshape(shape).copy()}
 
     def kernels_per_loop(self) -> int:
         """Launches of this library's kernels inside one replay (for reporting)."""
         L, N = self.layers, self.num_steps
+        if self.precision == "nvfp4":
+            return N * (1 + 1 + self.pipeline.launches_per_layer() * L + 2)
         # qkv gemm (+rope split), attention, o gemm, norm, gate|up gemm (+geglu), down gemm, norm
         per_layer = 7 if self.fuse_epilogues else 9
         return N * (1 + 1 + per_layer * L + 2)

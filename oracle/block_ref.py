@@ -197,6 +197,64 @@ def attention(q, k, v, scale):
     return torch.einsum("hsk,khd->shd", p, vv)
 
 
+class Nvfp4Linears:
+    """W4A4 NVFP4 stand-in for the four projections of every layer, restating the arithmetic of the NVFP4
+    decoder (flash_rt/models/pi05/pipeline_thor.py:255-490; quantisers csrc/quantize/quantize_fp4_sfa.cu:63-109):
+    weights quantised once (e2m1, 16-element blocks, RN-even E4M3 block scale) after division by an FP32
+    global scale amax / (448 * 6); activations quantised per call, block scales only; the product is taken on
+    the dequantised values in fp32 and rounded to bf16 as the GEMM kernel stores it."""
+
+    def __init__(self, W: dict, layers: int, weight_global_scale: bool = True):
+        from . import oracle as O
+        self.O = O
+        self.w = {}
+        for name in ("decoder_attn_qkv_w", "decoder_attn_o_w", "decoder_ffn_gate_w", "decoder_ffn_up_w",
+                     "decoder_ffn_down_w"):
+            for i in range(layers):
+                wt = W[name][i].float().t().contiguous()                       # (N, K)
+                wb = O.f32_to_bf16_bits(wt.numpy())
+                g = float(np.float32(np.abs(O.bf16_bits_to_f32(wb)).max()) / np.float32(448.0 * 6.0)) \
+                    if weight_global_scale else 1.0
+                g = max(g, 1e-30)
+                p, sf = O.quantize_nvfp4(wb, 1, g)
+                self.w[(name, i)] = torch.from_numpy(O.dequantize_nvfp4(p, sf, g)).t().contiguous()   # (K, N)
+
+    def act(self, h: torch.Tensor, round_bf16: bool = True) -> torch.Tensor:
+        O = self.O
+        a = h.detach().float().numpy()
+        src = O.f32_to_bf16_bits(a) if round_bf16 else np.ascontiguousarray(a, np.float32)
+        p, sf = O.quantize_nvfp4(src, 1)
+        return torch.from_numpy(O.dequantize_nvfp4(p, sf))
+
+    def __call__(self, h_q: torch.Tensor, name: str, i: int) -> torch.Tensor:
+        return (h_q @ self.w[(name, i)]).to(torch.bfloat16).float()
+
+
+def decoder_block_nvfp4(x, lin: "Nvfp4Linears", i: int, style_attn_row, style_ffn_row, prefix_k, prefix_v,
+                        rope_tab):
+    """The layer of ``decoder_block`` with NVFP4 projections and the device path's 16-bit rounding points
+    (bf16 GEMM outputs, bf16 attention output, GeGLU product quantised straight from fp32)."""
+    S = x.shape[0]
+    bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    h, gate_a = ada_rms(x, style_attn_row)
+    qkv = lin(lin.act(h), "decoder_attn_qkv_w", i)
+    q = qkv[:, :DEC_NH * DEC_HD].reshape(S, DEC_NH, DEC_HD)
+    k = qkv[:, DEC_NH * DEC_HD:(DEC_NH + DEC_NKV) * DEC_HD].reshape(S, DEC_NKV, DEC_HD)
+    v = qkv[:, (DEC_NH + DEC_NKV) * DEC_HD:].reshape(S, DEC_NKV, DEC_HD)
+    q = bf(rope_adjacent_pairs(q, rope_tab))
+    k = bf(rope_adjacent_pairs(k, rope_tab))
+    keys = torch.cat([prefix_k.reshape(-1, DEC_NKV, DEC_HD).float(), k], dim=0)
+    vals = torch.cat([prefix_v.reshape(-1, DEC_NKV, DEC_HD).float(), v], dim=0)
+    a = bf(attention(q, keys, vals, DEC_HD ** -0.5).reshape(S, DEC_NH * DEC_HD))
+    o = lin(lin.act(a), "decoder_attn_o_w", i)
+    x1 = bf(x + o * gate_a)
+    h2, gate_f = ada_rms(x1, style_ffn_row)
+    h2q = lin.act(h2)
+    hidden = gelu_tanh(lin(h2q, "decoder_ffn_gate_w", i)) * lin(h2q, "decoder_ffn_up_w", i)
+    f = lin(lin.act(hidden, round_bf16=False), "decoder_ffn_down_w", i)
+    return bf(x1 + f * gate_f)
+
+
 def decoder_block(x, W: dict, i: int, style_attn_row, style_ffn_row, prefix_k, prefix_v, rope_tab,
                   return_parts: bool = False):
     """One action-expert layer in fp32.  x (S, D); prefix_k / prefix_v (P, 256); returns the new x."""
@@ -223,12 +281,14 @@ def decoder_block(x, W: dict, i: int, style_attn_row, style_ffn_row, prefix_k, p
 
 
 def denoise_loop(noise, ckpt: dict, prefix_k, prefix_v, num_steps: int = 10, layers: int = DEC_L,
-                 prefix_len: int | None = None, styles_bf16: bool = True, return_trajectory: bool = False):
+                 prefix_len: int | None = None, styles_bf16: bool = True, return_trajectory: bool = False,
+                 nvfp4: "Nvfp4Linears | None" = None):
     """10-step Euler flow matching in fp32: x <- x + dt * v(x, t), dt = -1/N, t from 1 down.
 
     ``styles_bf16``: the conditioning tables are data the device path reads from a bf16 precompute
     (pi05_rtx.py:369-448), so by default they are rounded the same way here and the comparison isolates the
-    loop itself.  Returns the final actions (S, 32) and, optionally, the list of states after each step.
+    loop itself.  ``nvfp4``: run the four projections of every layer through :class:`Nvfp4Linears`.
+    Returns the final actions (S, 32) and, optionally, the list of states after each step.
     """
     W = ckpt
     S = noise.shape[0]
@@ -243,7 +303,10 @@ def denoise_loop(noise, ckpt: dict, prefix_k, prefix_v, num_steps: int = 10, lay
     for s in range(num_steps):
         x = x_act @ W["decoder_action_in_proj_w"].float() + W["decoder_action_in_proj_b"].float()
         for i in range(layers):
-            x = decoder_block(x, W, i, sa[s, i], sf[s, i], prefix_k[i, :P], prefix_v[i, :P], tab)
+            if nvfp4 is not None:
+                x = decoder_block_nvfp4(x, nvfp4, i, sa[s, i], sf[s, i], prefix_k[i, :P], prefix_v[i, :P], tab)
+            else:
+                x = decoder_block(x, W, i, sa[s, i], sf[s, i], prefix_k[i, :P], prefix_v[i, :P], tab)
         h, _ = ada_rms(x, fin[s])
         v = h @ W["decoder_action_out_proj_w"].float() + W["decoder_action_out_proj_b"].float()
         x_act = x_act + dt * v
