@@ -30,6 +30,9 @@ sys.path.insert(0, ROOT)
 METRIC = "bs1 10-step action-expert denoise ms"
 WORKLOAD = ("pi05 action expert: 18 blocks x 10 Euler steps, 50 action tokens, 768-token prefix KV, FP8 E4M3 "
             "weights+activations, one CUDA graph, batch 1")
+WORKLOAD_NVFP4 = ("pi05 action expert (BASELINE configs[3]): 18 blocks x 10 Euler steps, 50 action tokens, 768-token "
+                  "prefix KV, NVFP4 weights (FP32 global scale) + activations in all four projections, bf16 "
+                  "attention, one CUDA graph, batch %d")
 
 
 def _peaks():
@@ -128,15 +131,23 @@ def gemm_roofline(fe, reps: int = 20):
     CUDA events on the launching stream."""
     import torch
     p, s = fe.pipeline, fe.stream
-    S, L = fe.chunk_size, fe.layers
-    shapes = [("w_qkv", "ws_qkv_t", p.act8, p.qkv, 2560, 1024), ("w_o", "ws_o_t", p.attn8, p.xn, 1024, 2048),
-              ("w_gu", "ws_gu_t", p.act8, p.merged, 8192, 1024), ("w_d", "ws_d_t", p.hid8, p.xn, 1024, 4096)]
+    S, L = fe.chunk_size * fe.batch, fe.layers
+    nv = fe.precision == "nvfp4"
+    if nv:
+        shapes = [("qkv", None, (p.act4, p.act4_sf), p.qkv, 2560, 1024), ("o", None, (p.ctx4, p.ctx4_sf), p.xn, 1024, 2048),
+                  ("gu", None, (p.act4, p.act4_sf), p.merged, 8192, 1024), ("d", None, (p.hid4, p.hid4_sf), p.xn, 1024, 4096)]
+    else:
+        shapes = [("w_qkv", "ws_qkv_t", p.act8, p.qkv, 2560, 1024), ("w_o", "ws_o_t", p.attn8, p.xn, 1024, 2048),
+                  ("w_gu", "ws_gu_t", p.act8, p.merged, 8192, 1024), ("w_d", "ws_d_t", p.hid8, p.xn, 1024, 4096)]
 
     def enqueue():
         for i in range(L):
             for wn, sn, a8, out, N, K in shapes:
-                p._gemm(a8, getattr(fe, wn)[i], getattr(fe, sn)[i], out, S, N, K, p._scale_ptr(0, i, "qkv"),
-                        s.cuda_stream, fe.use_pdl)
+                if nv:
+                    p._gemm(a8[0], a8[1], fe.w4[i][wn], out, s.cuda_stream, fe.use_pdl)
+                else:
+                    p._gemm(a8, getattr(fe, wn)[i], getattr(fe, sn)[i], out, S, N, K, p._scale_ptr(0, i, "qkv"),
+                            s.cuda_stream, fe.use_pdl)
 
     with torch.cuda.stream(s):
         enqueue()
@@ -154,7 +165,8 @@ def gemm_roofline(fe, reps: int = 20):
         s.synchronize()
     launches = len(shapes) * L
     us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
-    bytes_per_launch = sum(N * K + S * K + 2 * S * N for *_, N, K in shapes) / len(shapes)
+    eb = 0.5625 if nv else 1.0          # bytes per operand element (NVFP4: 4 bits + one scale byte per 16)
+    bytes_per_launch = sum(eb * (N * K + S * K) + 2 * S * N for *_, N, K in shapes) / len(shapes)
     return us, bytes_per_launch, launches
 
 
@@ -171,13 +183,16 @@ def run_ours(args):
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import ACTION_DIM
     gsd = torch.Generator().manual_seed(1)
-    model = load_model("synthetic:0", config="pi05", device=local, use_pdl=not args.no_pdl)
+    nv = args.precision == "nvfp4"
+    model = load_model("synthetic:0", config="pi05", device=local, use_pdl=not args.no_pdl,
+                       precision=args.precision, batch=args.batch)
     fe = model.frontend
     L, P = fe.layers, fe.prefix_len
     model.set_prefix(torch.randn(L, P, 256, generator=gsd), torch.randn(L, P, 256, generator=gsd))
     cal = [torch.randn(fe.chunk_size, ACTION_DIM, generator=torch.Generator().manual_seed(100 + j)) for j in range(args.calib_samples)]
-    model.calibrate(cal)
-    noise = torch.randn(fe.chunk_size, ACTION_DIM, generator=torch.Generator().manual_seed(7)).numpy()
+    model.calibrate(cal)                  # no-op for NVFP4 (block scales are computed at run time)
+    nshape = (fe.chunk_size, ACTION_DIM) if fe.batch == 1 else (fe.batch, fe.chunk_size, ACTION_DIM)
+    noise = torch.randn(*nshape, generator=torch.Generator().manual_seed(7)).numpy()
     model.predict(noise=noise)            # captures the graph
 
     def barrier():
@@ -229,18 +244,25 @@ def run_ours(args):
                 dist.destroy_process_group()
             return
         gemm_us, gemm_bytes, _ = gemm_roofline(fe)
-        gemm_out_bytes = 2 * fe.chunk_size * (2560 + 1024 + 8192 + 1024) / 4
+        M = fe.batch * fe.chunk_size
+        gemm_out_bytes = 2 * M * (2560 + 1024 + 8192 + 1024) / 4
         achieved = gemm_bytes / (gemm_us * 1e-6) / 1e9
-        # algorithmic HBM bytes of one loop: FP8 weights + prefix/fresh KV per layer per step
-        loop_bytes = fe.num_steps * L * (17301504 + 2 * (P + fe.chunk_size) * 256 * 2)
+        # algorithmic HBM bytes of one loop: weights (FP8: 1 byte, NVFP4: 0.5625 byte per element with the
+        # block scales) + prefix/fresh KV per layer per step (per batch element)
+        wbytes = 17301504 * (0.5625 if nv else 1.0)
+        loop_bytes = int(fe.num_steps * L * (wbytes + fe.batch * 2 * (P + fe.chunk_size) * 256 * 2))
         cpu_ms, cores = cpu_reference_loop(3, 1, L)
         line = {
             "metric": METRIC, "value": round(ms, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 residual stream)",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": ("nvfp4_e2m1 (ue4m3 block scales, fp32 accumulate, bf16 residual stream)" if nv
+                      else "fp8_e4m3 (fp32 accumulate, bf16 residual stream)"),
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world} (no collective)",
-                       "l2": "working set 326 MB per Euler step exceeds the 126 MB L2; no explicit flush",
+            "config": {"workload": (WORKLOAD_NVFP4 % fe.batch) if nv else WORKLOAD,
+                       "parallelism": f"replicas x{world} (no collective)",
+                       "l2": ("working set %d MB per Euler step exceeds the 126 MB L2; no explicit flush"
+                              % (loop_bytes // fe.num_steps // 1000000)),
                        "kernels_per_loop": fe.kernels_per_loop(), "pdl": fe.use_pdl,
                        "calibration_samples": args.calib_samples,
                        "tensor_core_status": status, "actions_finite": bool((out == out).all())},
@@ -250,7 +272,8 @@ def run_ours(args):
             "aggregate_loops_per_s": round(world * 1e3 / ms, 2),
             "loop_hbm_floor": {"algorithmic_bytes": loop_bytes, "floor_ms": round(loop_bytes / (peak * 1e9) * 1e3, 4),
                                "frac": round(loop_bytes / (peak * 1e9) * 1e3 / ms, 4)},
-            "roofline": {"bound": "hbm", "kernel": "gemm_fp8_kernel<64,true> (M=50 weight streaming)",
+            "roofline": {"bound": "hbm", "kernel": ("gemm_fp8_kernel<..,true,..,NVFP4> (M=%d weight streaming)" % M
+                                                    if nv else "gemm_fp8_kernel<64,true> (M=50 weight streaming)"),
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
                          # dram read+write of one launch from the ncu capture in profiles/ (1.005 x the algorithmic
@@ -359,6 +382,113 @@ def run_wan(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------------
+def run_ops(args):
+    """Operator sweep (BASELINE configs[1]) on one GPU: fused residual + RMSNorm + FP8 quantise over row widths,
+    FP8 and NVFP4 GEMMs over M x (N, K).  Every case is timed as a CUDA graph of launches that cycle through
+    enough distinct buffers to exceed L2, with CUDA events around the replays.  One JSON line; the table is in
+    ``config.table`` (GB/s for the norm, TFLOP/s for the GEMMs, with the fraction of the measured peak)."""
+    import torch
+    from flashrt_b200 import _lib
+    from flashrt_b200 import flash_rt_fp4 as fp4
+    torch.cuda.set_device(0)
+    peak_hbm, _ = _peaks()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            bf16_tf = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        bf16_tf = 1590.0
+    fp8_peak, fp4_peak = 2 * bf16_tf, 4 * bf16_tf
+    s = torch.cuda.Stream()
+    L2 = 160e6
+    launches = 0
+
+    def timed(enqueue, n_launch, reps=5):
+        with torch.cuda.stream(s):
+            enqueue()
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s, capture_error_mode="relaxed"):
+                enqueue()
+            for _ in range(3):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            for _ in range(reps):
+                g.replay()
+            e1.record(s)
+            s.synchronize()
+        nonlocal launches
+        launches += n_launch * (1 + 3 + reps)
+        return e0.elapsed_time(e1) * 1e-3 / (reps * n_launch)
+
+    table = []
+    one = torch.ones(1, dtype=torch.float32, device="cuda")
+    # ---- K3 fused residual + RMSNorm + FP8 quantise
+    for W in (1024, 2048, 3072, 4096):
+        rows = 81920
+        nbuf = max(2, int(L2 // (rows * W * 7)) + 1)
+        res = [torch.randn(rows, W, device="cuda").bfloat16() for _ in range(nbuf)]
+        x = [torch.randn(rows, W, device="cuda").bfloat16() for _ in range(nbuf)]
+        out = [torch.empty(rows, W, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+        wt = torch.ones(W, device="cuda").bfloat16()
+        def enq():
+            for i in range(nbuf):
+                _lib.call("frt_b200_norm_fp8", res[i].data_ptr(), x[i].data_ptr(), None, 0, wt.data_ptr(), None, 0,
+                          out[i].data_ptr(), None, rows, W, 1e-6, one.data_ptr(), 0, s.cuda_stream)
+        t = timed(enq, nbuf)
+        gbs = rows * W * 7 / t / 1e9
+        table.append({"op": "residual_add_rms_norm_fp8", "rows": rows, "width": W, "us": round(t * 1e6, 2),
+                      "GB/s": round(gbs, 1), "frac_hbm": round(gbs / peak_hbm, 3)})
+        del res, x, out
+    # ---- GEMMs
+    NK = [(1024, 1024), (4096, 1024), (1024, 4096), (3072, 3072), (14336, 3072), (3072, 14336)]
+    for kind in ("fp8", "nvfp4"):
+        for M in (16, 50, 256, 2048, 8192, 20480):
+            for N, K in NK:
+                eb = 1.0 if kind == "fp8" else 0.5
+                wbytes = N * K * eb
+                nbuf = max(1, min(160, int(L2 // wbytes) + 1)) if M <= 256 else 2
+                A = torch.randint(0, 256, (M, int(K * eb)), dtype=torch.uint8, device="cuda")
+                Ws = [torch.randint(0, 120, (N, int(K * eb)), dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+                D = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+                if kind == "fp8":
+                    A &= 0x77                      # finite E4M3 codes
+                    def enq():
+                        for w in Ws:
+                            _lib.call("frt_b200_gemm_fp8_nt", A.data_ptr(), w.data_ptr(), D.data_ptr(), M, N, K,
+                                      one.data_ptr(), one.data_ptr(), 1.0, None, 0, 0, s.cuda_stream)
+                else:
+                    sfa = torch.full((fp4.sfa_size_bytes(M, K),), 0x38, dtype=torch.uint8, device="cuda")
+                    sfw = torch.full((fp4.sfa_size_bytes(N, K),), 0x30, dtype=torch.uint8, device="cuda")
+                    def enq():
+                        for w in Ws:
+                            _lib.call("frt_b200_gemm_nvfp4_nt", A.data_ptr(), sfa.data_ptr(), w.data_ptr(),
+                                      sfw.data_ptr(), D.data_ptr(), M, N, K, 1.0, None, None, 0, 0, s.cuda_stream)
+                t = timed(enq, nbuf, reps=3 if M >= 2048 else 10)
+                tf = 2.0 * M * N * K / t / 1e12
+                ob = 0.5625 if kind == "nvfp4" else 1.0
+                gbs = (ob * (N * K + M * K) + 2 * M * N) / t / 1e9
+                table.append({"op": "gemm_" + kind, "M": M, "N": N, "K": K, "us": round(t * 1e6, 2),
+                              "TFLOP/s": round(tf, 1),
+                              "frac_tensor": round(tf / (fp8_peak if kind == "fp8" else fp4_peak), 3),
+                              "GB/s": round(gbs, 1), "frac_hbm": round(gbs / peak_hbm, 3)})
+                del A, Ws, D
+    from flashrt_b200 import flash_rt_kernels as fvk
+    big = [r for r in table if r["op"] == "gemm_fp8" and r["M"] >= 2048]
+    line = {"metric": "operator sweep (configs[1])", "value": round(statistics.mean(r["frac_tensor"] for r in big), 4),
+            "unit": "mean fraction of 2 x measured bf16 peak over the FP8 GEMMs with M >= 2048", "n_gpus": 1,
+            "steps": 1, "warmup": 3, "higher_is_better": True, "data": "synthetic", "dtype": "fp8_e4m3 / nvfp4 / bf16",
+            "config": {"workload": "configs[1] operator sweep", "peaks": {"hbm_gbs": peak_hbm, "fp8_tflops": fp8_peak,
+                                                                           "nvfp4_tflops": fp4_peak,
+                                                                           "note": "tensor peaks = 2x / 4x the measured cuBLAS bf16 burst"},
+                       "l2": ("norm and M <= 256 GEMM cases cycle through distinct row / weight buffers totalling more than "
+                              "L2; M >= 2048 GEMM cases alternate two weight buffers (tensor-bound)"),
+                       "tensor_core_status": fvk.tensor_core_status(), "table": table},
+            "gpu_launches": launches}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -371,12 +501,19 @@ def main():
                          "(Nsight Compute cannot profile programmatically dependent launches)")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
-    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan"],
-                    help="pi05 = the headline action-expert loop (default); wan = the video-DiT step (configs[4])")
+    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops"],
+                    help="pi05 = the headline action-expert loop (default); wan = the video-DiT step (configs[4]); "
+                         "ops = the operator sweep of configs[1] (norm / FP8 GEMM / NVFP4 GEMM)")
+    ap.add_argument("--precision", default="fp8", choices=["fp8", "nvfp4"],
+                    help="pi05 workload: fp8 = configs[2] (default, the headline), nvfp4 = configs[3]")
+    ap.add_argument("--batch", type=int, default=1, help="pi05 workload with --precision nvfp4: chunks per loop (1 or 4)")
     ap.add_argument("--wan-layers", type=int, default=30)
     args = ap.parse_args()
     if args.workload == "wan" and args.impl != "reference":
         run_wan(args)
+        return
+    if args.workload == "ops" and args.impl != "reference":
+        run_ops(args)
         return
     if args.impl == "reference":
         run_reference(args)
