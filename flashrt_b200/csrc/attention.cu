@@ -622,6 +622,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (warp == 5) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
 }
 
+#include "attention_pair.cuh"
+
 template <int D, int BKV>
 static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
                        const long long* ks, const long long* vs, int splits, bool pdl, cudaStream_t stream) {
@@ -758,6 +760,9 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
     int chunks = (seqlen_k + BKV - 1) / BKV;
     int sp = kv_splits > 0 ? kv_splits : (tiles >= 74 ? 1 : (chunks < 8 ? chunks : 8));
     if (sp > 8) sp = 8;
+    // one split and at least two row tiles: the two-tile ping-pong kernel (softmax overlapped with the MMAs)
+    if (sp == 1 && (seqlen_q * G + 127) / 128 >= 2)
+        return launch_attn_pair(Q, K, V, p, q_strides, k_strides, v_strides, pdl, s);
     return launch_attn<128, BKV>(Q, K, V, p, q_strides, k_strides, v_strides, sp, pdl, s);
 }
 

@@ -107,3 +107,53 @@ def test_split_kv_through_global_scratch(splits):
     _run(1, 50, 818, 8, 1, 256, splits, seed=30 + splits, scratch=True, fused_fp8=True)
     _run(1, 17, 500, 8, 1, 256, splits, seed=40 + splits, scratch=True, seqused=333)
     _run(2, 130, 260, 8, 2, 128, 2, seed=50 + splits, scratch=True)
+
+
+# ------------------------------------------------------------------ two-tile ping-pong kernel (head_dim 128, one kv split)
+@pytest.mark.parametrize("B,Sq,Skv,Hq,Hkv", [(1, 300, 300, 4, 4), (2, 257, 257, 24, 24), (1, 130, 777, 8, 2),
+                                             (1, 129, 128, 2, 2), (1, 1000, 1000, 3, 3), (2, 520, 512, 4, 1)])
+def test_pair_kernel_head_dim_128(B, Sq, Skv, Hq, Hkv):
+    """kv_splits = 1 with at least two row tiles routes to the kernel that overlaps softmax and MMAs over two
+    query tiles; ragged query tails, a half-empty last tile pair, partial last key chunks, GQA packing."""
+    _run(B, Sq, Skv, Hq, Hkv, 128, 1, seed=B * 7 + Sq + Skv + Hq)
+
+
+def test_pair_kernel_fp8_seqused_and_wide_scores():
+    _run(1, 300, 640, 4, 4, 128, 1, seed=61, fused_fp8=True)
+    _run(1, 300, 640, 4, 4, 128, 1, seed=62, seqused=333)
+    _run(1, 300, 640, 4, 4, 128, 1, seed=63, seqused=1)
+    # scores spread over +-60 (log2 domain): the row maximum keeps growing by more than the lazy-rescale
+    # threshold across chunks, so the O rescale path runs
+    from flashrt_b200 import flash_rt_fa2 as fa2
+    from gpu_util import Dev, cosine, rand_bf16, zeros
+    rng = np.random.default_rng(64)
+    B, S, H, D = 1, 640, 2, 128
+    q, k, v = rand_bf16(rng, (B, S, H, D), 1.0), rand_bf16(rng, (B, S, H, D), 1.0), rand_bf16(rng, (B, S, H, D), 1.0)
+    d_q, d_k, d_v, d_o = Dev(q), Dev(k), Dev(v), zeros((B, S, H, D), np.uint16)
+    st = (S * H * D, H * D, D)
+    scale = 4.0 / np.sqrt(D)
+    fa2.fwd_bf16(d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, 0, 0, 0, B, S, S, H, H, D, st, st, st, st, scale, 148, 0,
+                 kv_splits=1)
+    assert fa2.attention_status() == 0
+    ref, _ = O.attention(q, k, v, scale, S)
+    got = O.bf16_bits_to_f32(d_o.get())
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    assert cosine(got, ref) >= 0.9995
+    assert (np.abs(got - ref) <= 2e-2 * rms + np.abs(ref) * 2.0 ** -8).all()
+
+
+def test_pair_kernel_long_sequence_rows_sum_property():
+    """20 280 keys (the video-DiT length, 158 full chunks + 56 keys): with V = all ones every output is 1."""
+    from flashrt_b200 import flash_rt_fa2 as fa2
+    from gpu_util import Dev, rand_bf16, zeros
+    rng = np.random.default_rng(10)
+    B, Sq, Skv, H, D = 1, 2048, 20280, 2, 128
+    q, k = rand_bf16(rng, (B, Sq, H, D)), rand_bf16(rng, (B, Skv, H, D))
+    v = np.full((B, Skv, H, D), 0x3F80, np.uint16)
+    d_q, d_k, d_v, d_o = Dev(q), Dev(k), Dev(v), zeros((B, Sq, H, D), np.uint16)
+    qs, ks = (Sq * H * D, H * D, D), (Skv * H * D, H * D, D)
+    fa2.fwd_bf16(d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, 0, 0, 0, B, Sq, Skv, H, H, D, qs, ks, ks, qs, 1.0 / np.sqrt(D),
+                 148, 0, kv_splits=1)
+    got = O.bf16_bits_to_f32(d_o.get())
+    assert fa2.attention_status() == 0
+    assert np.abs(got - 1.0).max() <= 2.0 ** -7
