@@ -110,25 +110,29 @@ attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // ---------------- MMA issuer
         constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);   // bf16 x bf16, both K-major
         constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, D);     // A = P from TMEM, B = V MN-major
+        // descriptors differ only in their start-address field (units of 16 bytes): build the bases once
+        const uint64_t dq_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ));
+        const uint64_t dk_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sK));
+        const uint64_t dv_base = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV), BKV * 128);
         auto qk = [&](int t, int j) {
-            const int st = j & 1;
+            const uint64_t dq = dq_base + (uint64_t)(t * (Cfg::Q_BYTES >> 4));
+            const uint64_t dk = dk_base + (uint64_t)((j & 1) * (Cfg::KV_BYTES >> 4));
+            const uint32_t d_tm = tmem + t * 128;
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
-                const uint64_t dq =
-                    tc::make_desc_kmajor_sw128(tc::smem_u32(sQ + t * Cfg::Q_BYTES + (k / 4) * (128 * 128))) + 2 * (k % 4);
-                const uint64_t dk =
-                    tc::make_desc_kmajor_sw128(tc::smem_u32(sK + st * Cfg::KV_BYTES + (k / 4) * (BKV * 128))) + 2 * (k % 4);
-                tc::mma_f16(tmem + t * 128, dq, dk, idesc_s, k > 0 ? 1u : 0u);
+                // 64-element block k / 4 (16 KB apart), 32 bytes per K = 16 step inside the 128-byte row
+                const uint64_t off = (uint64_t)((k / 4) * ((128 * 128) >> 4) + 2 * (k % 4));
+                tc::mma_f16(d_tm, dq + off, dk + off, idesc_s, k > 0 ? 1u : 0u);
             }
             tc::mma_commit(&s_full[t]);
         };
         auto pv = [&](int t, int j) {
-            const int st = j & 1;
+            const uint64_t dv = dv_base + (uint64_t)((j & 1) * (Cfg::KV_BYTES >> 4));
+            const uint32_t d_tm = tmem + 256 + t * 128, a_tm = tmem + t * 128;
 #pragma unroll
-            for (int k = 0; k < BKV / 16; ++k) {
-                const uint64_t dv = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV + st * Cfg::KV_BYTES + k * 16 * 128), BKV * 128);
-                tc::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + 8 * k, dv, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-            }
+            for (int k = 0; k < BKV / 16; ++k)       // 16 keys = 16 rows of 128 bytes further on
+                tc::mma_f16_ts(d_tm, a_tm + 8 * k, dv + (uint64_t)(k * ((16 * 128) >> 4)), idesc_o,
+                               (j > 0 || k > 0) ? 1u : 0u);
         };
         ATTN_WAIT(q_full, 0u, AERR_MMA);
         if (nchunks > 0 && !*abort_flag) {
@@ -180,17 +184,25 @@ attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (__any_sync(0xffffffffu, *abort_flag != 0)) { alive = false; break; }
             tc::tc_fence_after_sync();
             const int valid = kv_len - j * BKV;                 // keys of this chunk that count (warp-uniform)
-            // pass 1: row maximum of the raw scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BKV; c += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tmem_S + c, v);
-                tc::tmem_ld_wait();
+            // the whole row of S (128 fp32) comes into registers with one wait
+            uint32_t sv[BKV];
+            tc::tmem_ld32(tmem_S + 0, sv + 0);
+            tc::tmem_ld32(tmem_S + 32, sv + 32);
+            tc::tmem_ld32(tmem_S + 64, sv + 64);
+            tc::tmem_ld32(tmem_S + 96, sv + 96);
+            tc::tmem_ld_wait();
+            if (valid < BKV) {                                  // last, partial chunk (warp-uniform branch)
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (c + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < BKV; ++i)
+                    if (i >= valid) sv[i] = 0xff800000u;        // -inf
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < BKV; i += 4) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], __uint_as_float(sv[i + q]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float mx_s = mx * p.scale_log2;               // scale_log2 > 0
             // keep the stale maximum unless it is exceeded by more than the threshold
             const bool grow = mx_s > m_run + Cfg::RESCALE_THRESHOLD || (m_run == -INFINITY && mx_s > -INFINITY);
@@ -211,25 +223,21 @@ attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             m_run = m_new;
             const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-            // pass 2: P = 2^(s * scale - m), row sum, bf16 pairs into TMEM over the consumed part of S
-            float sum = 0.0f;
-#pragma unroll 1
+            // P = 2^(s * scale - m) (2^-inf = 0 for masked keys), row sum, bf16 pairs into TMEM over S
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
             for (int c = 0; c < BKV; c += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tmem_S + c, v);
-                tc::tmem_ld_wait();
                 uint32_t u[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float a = (c + 2 * i < valid)
-                                        ? tc::ex2_approx(__fmaf_rn(__uint_as_float(v[2 * i]), p.scale_log2, -m_use)) : 0.0f;
-                    const float bb = (c + 2 * i + 1 < valid)
-                                         ? tc::ex2_approx(__fmaf_rn(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_use)) : 0.0f;
-                    sum += a + bb;
-                    u[i] = pack_bf16x2(a, bb);
+                    const float a = tc::ex2_approx(__fmaf_rn(__uint_as_float(sv[c + 2 * i]), p.scale_log2, -m_use));
+                    const float bb = tc::ex2_approx(__fmaf_rn(__uint_as_float(sv[c + 2 * i + 1]), p.scale_log2, -m_use));
+                    sum4[i & 3] += a + bb;
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u[i]) : "f"(bb), "f"(a));   // low half = first key
                 }
                 tc::tmem_st16(tmem_S + (c >> 1), u);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             tc::tmem_st_wait();
             l_run += sum;
             tc::tc_fence_before_sync();
