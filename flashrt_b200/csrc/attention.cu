@@ -255,6 +255,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // ---------------- MMA issuer
         constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);   // bf16 x bf16, both K-major
         constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, D);     // B (= V) is MN-major
+        // descriptors differ only in their start-address field (units of 16 bytes): build the bases once
+        const uint64_t dq_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ));
+        const uint64_t dk_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sK));
+        const uint64_t dp_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sP));
+        const uint64_t dv_base = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV), BKV * 128);
         ATTN_WAIT(q_full, 0u, AERR_MMA);
         for (int i = 0; i < nchunks && !*abort_flag; ++i) {
             const uint32_t ph = (uint32_t)(i & 1);
@@ -263,11 +268,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc::tc_fence_after_sync();
             // S = Q K^T : D / 16 steps of K = 16; a step advances 32 bytes inside a 128-byte block
 #pragma unroll
-            for (int k = 0; k < D / 16; ++k) {
-                const uint64_t dq = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ + (k / 4) * (128 * 128))) + 2 * (k % 4);
-                const uint64_t dk = tc::make_desc_kmajor_sw128(tc::smem_u32(sK + (k / 4) * (BKV * 128))) + 2 * (k % 4);
-                tc::mma_f16(tmem_S, dq, dk, idesc_s, k > 0 ? 1u : 0u);
-            }
+            for (int k = 0; k < D / 16; ++k)
+                tc::mma_f16(tmem_S, dq_base + (uint64_t)((k / 4) * ((128 * 128) >> 4) + 2 * (k % 4)),
+                            dk_base + (uint64_t)((k / 4) * ((BKV * 128) >> 4) + 2 * (k % 4)), idesc_s, k > 0 ? 1u : 0u);
             tc::mma_commit(s_full);
             ATTN_WAIT(p_ready, ph, AERR_MMA);
             ATTN_WAIT(v_full, ph, AERR_MMA);
@@ -275,11 +278,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc::tc_fence_after_sync();
             // O += P V : BKV / 16 steps over the keys
 #pragma unroll
-            for (int k = 0; k < BKV / 16; ++k) {
-                const uint64_t dp = tc::make_desc_kmajor_sw128(tc::smem_u32(sP + (k / 4) * (128 * 128))) + 2 * (k % 4);
-                const uint64_t dv = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV + k * 16 * 128), BKV * 128);
-                tc::mma_f16(tmem_O, dp, dv, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-            }
+            for (int k = 0; k < BKV / 16; ++k)
+                tc::mma_f16(tmem_O, dp_base + (uint64_t)((k / 4) * ((128 * 128) >> 4) + 2 * (k % 4)),
+                            dv_base + (uint64_t)(k * ((16 * 128) >> 4)), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
             tc::mma_commit(kv_empty);
             tc::mma_commit(o_full);
         }
