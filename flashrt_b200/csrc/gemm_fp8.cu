@@ -744,6 +744,8 @@ static int dispatch_small_m(const void* A, const void* W, GemmParams p, int K, i
     return launch_gemm<256, true, EPI>(A, W, p, K, sp, pdl, s);
 }
 
+#include "gemm_persistent.cuh"
+
 template <int EPI>
 static int dispatch_small_m_nvfp4(const void* A, const void* W, GemmParams p, int K, int M, int tiles, int splits,
                                   bool pdl, cudaStream_t s) {
@@ -783,6 +785,10 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     bool pdl = flags & 1;
     if (M <= 256) return dispatch_small_m<EPI_BF16>(A, W, p, K, M, (N + 127) / 128, splits, pdl, s);
     int sp = splits > 0 ? pick_splits(1, p.kb_total, splits > 8 ? 8 : splits) : 1;
+    if (sp == 1 && !(flags & 2)) {      // flags bit1 keeps the one-tile-per-CTA kernel (for comparison runs)
+        if (N >= 256) return launch_gemm_persistent<256, EPI_P_BF16>(A, W, p, K, pdl, s);
+        if (N > 64) return launch_gemm_persistent<128, EPI_P_BF16>(A, W, p, K, pdl, s);
+    }
     if (N >= 256) return launch_gemm<256, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
     if (N > 64) return launch_gemm<128, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
     return launch_gemm<64, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
@@ -905,6 +911,29 @@ int frt_b200_gemm_nvfp4_nt_rope_split(const void* A, const void* SFA, const void
     p.head_dim = head_dim;
     return dispatch_small_m_nvfp4<EPI_ROPE_SPLIT>(A, W, p, K, M, (p.N + 127) / 128, splits, flags & 1,
                                                   (cudaStream_t)stream);
+}
+
+// FFN-up projection with bias + GELU(tanh) + FP8 quantise in the epilogue (M > 256):
+//   out8 (M, N) e4m3 = clamp(gelu_tanh(bf16(alpha * A . W^T) + bias) * (1 / *d_out_scale), +-448)
+// Byte-identical to frt_b200_gemm_fp8_nt followed by frt_b200_bias_gelu_quantize_fp8.  N % 8 == 0.
+int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8, int M, int N, int K,
+                                       const float* d_scale_a, const float* d_scale_b, const void* bias,
+                                       const float* d_out_scale, int flags, void* stream) {
+    if (!A || !W || !out8 || !d_out_scale || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if ((K % 16) || (N % 8) || M <= 256 || N < 128) return FRT_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(out8) & 7) return FRT_ERR_INVALID;
+    GemmParams p = {};
+    p.sa = d_scale_a;
+    p.sb = d_scale_b;
+    p.alpha_host = 1.0f;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.M = M;
+    p.N = N;
+    p.kb_total = (K + 127) / 128;
+    p.out8 = (uint8_t*)out8;
+    p.out_scale = d_out_scale;
+    if (N >= 256) return launch_gemm_persistent<256, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
+    return launch_gemm_persistent<128, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
 }
 
 // returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)

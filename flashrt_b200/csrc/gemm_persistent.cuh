@@ -1,0 +1,262 @@
+// Large-M FP8 GEMM as a persistent kernel: one CTA per SM walks a static list of 128 x BN output tiles.
+//
+// Included by gemm_fp8.cu inside namespace frt (GemmParams, tensor-map cache, status word).
+//
+// Why: with one tile per CTA the prologue (barriers, TMEM allocation, first TMA round trip) and the epilogue
+// (TMEM -> registers -> global) of every tile are exposed; at K = 1024 they cost more than the MMAs.  Here
+//   * the TMA producer runs ahead across tile boundaries (the shared-memory ring never drains),
+//   * two accumulators live in TMEM (2 x BN columns): the MMA warp fills one while eight epilogue warps drain
+//     the other, so the epilogue -- including the bias + GELU + FP8 form -- hides behind the next mainloop,
+//   * consecutive tiles of the list share their weight columns (tile = n_tile * m_tiles + m_tile), so the CTAs
+//     of one wave read the same BN weight rows from L2.
+// Warps: 0 TMA producer, 1 MMA issuer (+ TMEM owner), 2..9 epilogue (lane quadrant = warp % 4, column half =
+// (warp - 2) / 4).  Every wait is bounded by the kernel deadline; on expiry the status word is set and all roles
+// leave their loops.
+#pragma once
+
+enum { EPI_P_BF16 = 0, EPI_P_BIAS_GELU_FP8 = 1 };
+
+// tanh-form GELU with explicitly rounded fp32 operations, the same sequence as bias_gelu_fp8_kernel
+// (csrc/quantize/bias_gelu_quantize_fp8.cu:24-49 in the reference)
+__device__ __forceinline__ float gelu_tanh_form_rn(float x) {
+    const float x3 = __fmul_rn(__fmul_rn(x, x), x);
+    const float u = __fmul_rn(0.7978845608f, __fmaf_rn(0.044715f, x3, x));
+    const float e = det_expf(__fmul_rn(2.0f, u));
+    const float th = __fsub_rn(1.0f, __fdiv_rn(2.0f, __fadd_rn(1.0f, e)));
+    return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, th));
+}
+
+template <int BN>
+struct PGemmCfg {
+    static constexpr int L_BYTES = 128 * 128;
+    static constexpr int C_BYTES = BN * 128;
+    static constexpr int STAGE_BYTES = L_BYTES + C_BYTES;
+    static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
+    static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int TMEM_COLS = 2 * BN;          // BN in {128, 256}
+    static constexpr int EPI_THREADS = 256;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(320, 1)
+gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                           GemmParams p) {
+    using Cfg = PGemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;      // [2]
+    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m_tiles = (p.M + 127) / 128;
+    const int n_tiles = (p.N + BN - 1) / BN;
+    const int total = m_tiles * n_tiles;
+    const int kbt = p.kb_total;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(&acc_full[i], 1);
+            tc::mbar_init(&acc_empty[i], Cfg::EPI_THREADS);
+        }
+        *abort_flag = 0;
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&tmA);
+        tc::tma_prefetch_desc(&tmW);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer: runs ahead over tile boundaries
+        pdl_wait();
+        long long kc = 0;
+        for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
+            const int m0 = (t % m_tiles) * 128, n0 = (t / m_tiles) * BN;
+            for (int kb = 0; kb < kbt; ++kb, ++kc) {
+                const int s = (int)(kc % STAGES);
+                if (kc >= STAGES &&
+                    !tc::mbar_wait_until(&empty[s], (uint32_t)(((kc / STAGES) - 1) & 1), deadline, abort_flag)) {
+                    if (!*abort_flag) atomicCAS(&g_gemm_status, 0, ERR_PRODUCER | (blockIdx.x << 8));
+                    *abort_flag = 1;
+                    break;
+                }
+                uint8_t* dst = smem + s * Cfg::STAGE_BYTES;
+                tc::mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                tc::tma_load_2d(dst, &tmA, &full[s], kb * 128, m0);
+                tc::tma_load_2d(dst + Cfg::L_BYTES, &tmW, &full[s], kb * 128, n0);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer: accumulator i & 1 for the CTA's i-th tile
+        constexpr uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN);
+        const uint64_t dL0 = tc::make_desc_kmajor_sw128(tc::smem_u32(smem));
+        const uint64_t dC0 = tc::make_desc_kmajor_sw128(tc::smem_u32(smem + Cfg::L_BYTES));
+        long long kc = 0;
+        int i = 0;
+        for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            if (i >= 2 && !tc::mbar_wait_until(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1), deadline, abort_flag)) {
+                if (!*abort_flag) atomicCAS(&g_gemm_status, 0, ERR_MMA | (blockIdx.x << 8));
+                *abort_flag = 1;
+                break;
+            }
+            tc::tc_fence_after_sync();
+            const uint32_t d_tm = tmem + buf * BN;
+            for (int kb = 0; kb < kbt; ++kb, ++kc) {
+                const int s = (int)(kc % STAGES);
+                if (!tc::mbar_wait_until(&full[s], (uint32_t)((kc / STAGES) & 1), deadline, abort_flag)) {
+                    if (!*abort_flag) atomicCAS(&g_gemm_status, 0, ERR_MMA | (blockIdx.x << 8));
+                    *abort_flag = 1;
+                    break;
+                }
+                tc::tc_fence_after_sync();
+                const uint64_t so = (uint64_t)(s * (Cfg::STAGE_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    tc::mma_f8(d_tm, dL0 + so + 2 * k, dC0 + so + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tc::mma_commit(&empty[s]);
+            }
+            if (*abort_flag) break;
+            tc::mma_commit(&acc_full[buf]);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue: eight warps drain one accumulator while the other one fills
+        pdl_wait();
+        const int q = warp & 3;                         // TMEM lane quadrant this warp may access
+        const int half = (warp - 2) >> 2;               // which half of the BN columns
+        const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+        float alpha = p.alpha_host;
+        if (p.sa) alpha *= *p.sa;
+        if (p.sb) alpha *= *p.sb;
+        const float inv_os = (EPI == EPI_P_BIAS_GELU_FP8) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+        int i = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const bool ok = tc::mbar_wait_until(&acc_full[buf], (uint32_t)((i >> 1) & 1), deadline, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) {          // leave as a whole warp: tcgen05.ld is warp-collective
+                if (!*abort_flag) atomicCAS(&g_gemm_status, 0, ERR_EPILOGUE | (blockIdx.x << 8));
+                *abort_flag = 1;
+                break;
+            }
+            tc::tc_fence_after_sync();
+            const int m = (t % m_tiles) * 128 + q * 32 + lane;
+            const int n0 = (t / m_tiles) * BN + half * (BN / 2);
+            const uint32_t t_src = tmem + buf * BN + half * (BN / 2) + lane_off;
+#pragma unroll 1
+            for (int c = 0; c < BN / 2; c += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(t_src + c, v);
+                tc::tmem_ld_wait();
+                if (m < p.M) {
+                    const int nb = n0 + c;
+                    if (EPI == EPI_P_BF16) {
+                        __nv_bfloat16* orow = p.out + (size_t)m * p.N + nb;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (nb + j + 8 <= p.N && ((reinterpret_cast<uintptr_t>(orow + j) & 15) == 0)) {
+                                float f[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    f[e] = __uint_as_float(v[j + e]) * alpha;
+                                    if (p.bias) f[e] += __bfloat162float(p.bias[nb + j + e]);
+                                }
+                                uint4 o;
+                                o.x = pack_bf16x2(f[0], f[1]);
+                                o.y = pack_bf16x2(f[2], f[3]);
+                                o.z = pack_bf16x2(f[4], f[5]);
+                                o.w = pack_bf16x2(f[6], f[7]);
+                                st_global_v4(orow + j, o);
+                            } else {
+                                for (int e = 0; e < 8; ++e)
+                                    if (nb + j + e < p.N) {
+                                        float f = __uint_as_float(v[j + e]) * alpha;
+                                        if (p.bias) f += __bfloat162float(p.bias[nb + j + e]);
+                                        orow[j + e] = __float2bfloat16_rn(f);
+                                    }
+                            }
+                        }
+                    } else {
+                        // bf16(alpha * acc) + bias -> GELU -> e4m3: the rounding points of GEMM -> bias_gelu_quantize
+                        uint8_t* orow = p.out8 + (size_t)m * p.N + nb;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (nb + j + 8 <= p.N) {
+                                float g[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j + e]) * alpha));
+                                    if (p.bias) x = __fadd_rn(x, __bfloat162float(p.bias[nb + j + e]));
+                                    g[e] = clamp448(__fmul_rn(gelu_tanh_form_rn(x), inv_os));
+                                }
+                                uint2 o8;
+                                o8.x = f32x4_to_e4m3x4(g[0], g[1], g[2], g[3]);
+                                o8.y = f32x4_to_e4m3x4(g[4], g[5], g[6], g[7]);
+                                st_global_v2(orow + j, o8);
+                            }
+                        }
+                    }
+                }
+            }
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    __syncwarp();
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+}
+
+template <int BN, int EPI>
+static int launch_gemm_persistent(const void* A, const void* W, GemmParams p, int K, bool pdl, cudaStream_t stream) {
+    using Cfg = PGemmCfg<BN>;
+    static bool attr_done = false;
+    static int sms = 0;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_persistent_kernel<BN, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        attr_done = true;
+    }
+    CUtensorMap tmA, tmW;
+    int rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, (uint64_t)K, (uint64_t)K, 128);
+    if (rc) return rc;
+    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, BN);
+    if (rc) return rc;
+    const int total = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(total < sms ? total : sms);
+    cfg.blockDim = dim3(320);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_persistent_kernel<BN, EPI>, tmA, tmW, p);
+    return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
+}

@@ -226,9 +226,19 @@ class GemmRunner:
     reference's arguments and return immediately.
     """
 
-    def fp8_nt_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None):
-        """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form."""
-        call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits, _f(pdl), stream)
+    def fp8_nt_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
+                   one_tile_per_cta=False):
+        """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form.
+        ``one_tile_per_cta`` selects the non-persistent large-M kernel (same result; kept for comparison runs)."""
+        call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits,
+             _f(pdl) | (2 if one_tile_per_cta else 0), stream)
+
+    def fp8_nt_dev_bias_gelu_fp8(self, A, B, out, M, N, K, d_scale_a, d_scale_b, bias, d_scale_out, stream=0, *,
+                                 pdl=False):
+        """``fp8_nt_dev`` followed by ``bias_gelu_quantize_fp8_static_bf16`` (csrc/bindings.cpp:3427-3440) in one
+        launch, M > 256: the video-DiT FFN-up projection writes its FP8 mid-activation directly."""
+        call("frt_b200_gemm_fp8_nt_bias_gelu_fp8", A, B, out, M, N, K, d_scale_a, d_scale_b, bias or None,
+             d_scale_out, _f(pdl), stream)
 
     # -- fused forms (no reference counterpart as single calls; each equals two reference calls) ------------
     def fp8_nt_dev_rope_split(self, A, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc, Vc, q_dim, k_dim, v_dim,

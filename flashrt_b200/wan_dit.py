@@ -97,7 +97,8 @@ SITES = ("qkv", "o", "cq", "co", "f1", "f2")
 
 class WanDiTB200:
     def __init__(self, state: dict, *, grid=(13, 30, 52), batch: int = 2, text_len: int = 512, device=0,
-                 tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1):
+                 tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1,
+                 fuse_epilogues: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device)
@@ -164,6 +165,7 @@ class WanDiTB200:
         self.scales = torch.ones(len(self.blocks), len(SITES), dtype=torch.float32, device=dev)
         self.scratch = torch.zeros(1, dtype=torch.float32, device=dev)
         self.gemm = fvk.GemmRunner()
+        self.fuse_epilogues = fuse_epilogues
         self.calibrated = False
         self.launches_per_step = 0
 
@@ -287,15 +289,22 @@ class WanDiTB200:
             fvk.residual_add(self.x.data_ptr(), self.o.data_ptr(), M * D, st)
             # ---- FFN
             self._adaln(i, "f1", e_out[4], e_out[3], st, calibrate)
-            self._gemm(self.h8, b["f18"], b["f1_s"], self.f1, M, fl, D, self._sp(i, "f1"), st)
-            if calibrate:
-                # scale of the GELU output: measured on a bf16 copy made with the add / GELU kernels of this library
-                tmp = self.f1.clone()
-                fvk.add_bias_bf16(tmp.data_ptr(), b["f1_b"].data_ptr(), M, fl, st)
-                act = torch.nn.functional.gelu(tmp.float(), approximate="tanh").to(BF16)
-                self._quant(act, self.f8, i, "f2", st, True)
-            fvk.bias_gelu_quantize_fp8_static_bf16(self.f1.data_ptr(), b["f1_b"].data_ptr(), self.f8.data_ptr(),
-                                                   self._sp(i, "f2"), M, fl, st)
+            if calibrate or not self.fuse_epilogues or M <= 256 or fl < 128:
+                self._gemm(self.h8, b["f18"], b["f1_s"], self.f1, M, fl, D, self._sp(i, "f1"), st)
+                if calibrate:
+                    # scale of the GELU output, measured on a bf16 copy (calibration only; host-side torch math)
+                    tmp = self.f1.clone()
+                    fvk.add_bias_bf16(tmp.data_ptr(), b["f1_b"].data_ptr(), M, fl, st)
+                    act = torch.nn.functional.gelu(tmp.float(), approximate="tanh").to(BF16)
+                    self._quant(act, self.f8, i, "f2", st, True)
+                fvk.bias_gelu_quantize_fp8_static_bf16(self.f1.data_ptr(), b["f1_b"].data_ptr(), self.f8.data_ptr(),
+                                                       self._sp(i, "f2"), M, fl, st)
+            else:
+                # FFN-up projection with bias + GELU + FP8 quantise in the GEMM epilogue (same bytes, one launch)
+                self.gemm.fp8_nt_dev_bias_gelu_fp8(self.h8.data_ptr(), b["f18"].data_ptr(), self.f8.data_ptr(), M, fl,
+                                                   D, self._sp(i, "f1"), b["f1_s"].data_ptr(), b["f1_b"].data_ptr(),
+                                                   self._sp(i, "f2"), st)
+                self.launches_per_step += 1
             self._gemm(self.f8, b["f28"], b["f2_s"], self.o, M, D, fl, self._sp(i, "f2"), st, bias=b["f2_b"])
             self._allreduce(self.o)
             self._gated_residual(self.o, e_out[5], st)

@@ -103,7 +103,9 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
  * cutlass_fp8_*_bf16out        csrc/bindings.cpp:2388-2422 -> csrc/gemm/cutlass_sm100.cu:75-125
  *   D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . W(N,K)^T + bias(N)
  *   A, W: E4M3, row-major, K contiguous, 16-byte aligned, K % 16 == 0.  d_scale_* and bias may be NULL.
- *   splits: 0 = choose; else split-K factor in [1, 16] (reduced inside a thread-block cluster). */
+ *   splits: 0 = choose; else split-K factor in [1, 16] (reduced inside a thread-block cluster).
+ *   M > 256 runs as a persistent kernel (one CTA per SM walking the tile list, two accumulators in tensor memory so
+ *   that the epilogue overlaps the next tile's MMAs); flags bit 1 selects the one-tile-per-CTA kernel instead. */
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream);
@@ -218,6 +220,14 @@ int frt_b200_add_bias(void* x, const void* bias, long long rows, int dim, int fl
 int frt_b200_adaln_modulation6(const float* adaln_params, const float* layer_modulation, void* out0, void* out1,
                                void* out2, void* out3, void* out4, void* out5, int B, int S, int D, int flags,
                                void* stream);
+
+/* fp8 GEMM (GemmRunner::fp8_nt_dev, csrc/bindings.cpp:717-727) + bias_gelu_quantize_fp8_static_bf16
+ * (csrc/bindings.cpp:3427-3440 -> csrc/quantize/bias_gelu_quantize_fp8.cu:24-49) in one launch, M > 256, N >= 128:
+ *   out8 (M, N) e4m3 = clamp(gelu_tanh(bf16(sa * sb * A . W^T) + bias) * (1 / *d_out_scale), +-448)
+ * byte-identical to the two separate calls. */
+int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8, int M, int N, int K,
+                                       const float* d_scale_a, const float* d_scale_b, const void* bias,
+                                       const float* d_out_scale, int flags, void* stream);
 
 /* ---------------------------------------------------------------- NVFP4 (e2m1 x 16-element blocks x unsigned-E4M3 scales)
  * Packed data: two elements per byte, low nibble = even element, row = K / 2 bytes.

@@ -201,3 +201,45 @@ def test_split_k_over_large_clusters(N, K, splits):
     got = d_D.get()
     assert fvk.tensor_core_status() == 0
     _check(got, _ref(A, W, sa, sb))
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (1000, 200, 4096), (4096, 3072, 1024), (300, 512, 256)])
+def test_gemm_fp8_persistent_equals_one_tile_per_cta(M, N, K):
+    """The persistent large-M kernel (two accumulators in tensor memory, overlapped epilogue) and the
+    one-tile-per-CTA kernel accumulate every output in the same order: identical bytes."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M * 3 + N + K)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    bias = rand_bf16(rng, (N,), 0.3)
+    d_A, d_W, d_b, d_sa, d_sb = Dev(A), Dev(W), Dev(bias), f32(sa), f32(sb)
+    d_1, d_2 = zeros((M, N), np.uint16), zeros((M, N), np.uint16)
+    g = fvk.GemmRunner()
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_1.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_2.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr, one_tile_per_cta=True)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_1.get(), d_2.get())
+    _check(d_1.get(), _ref(A, W, sa, sb, bias))
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (1000, 200, 512), (3000, 14336 // 8, 3072)])
+def test_gemm_fp8_bias_gelu_epilogue_equals_pair(M, N, K):
+    """GEMM with bias + GELU + FP8 quantise in the epilogue == GEMM -> bias_gelu_quantize_fp8, byte for byte."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M + 5 * N + K)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    bias = rand_bf16(rng, (N,), 0.3)
+    d_A, d_W, d_b, d_sa, d_sb, d_so = Dev(A), Dev(W), Dev(bias), f32(sa), f32(sb), f32(0.013)
+    g = fvk.GemmRunner()
+    d_mid, d_pair, d_fused = zeros((M, N), np.uint16), zeros((M, N), np.uint8), zeros((M, N), np.uint8)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_mid.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0)
+    fvk.bias_gelu_quantize_fp8_static_bf16(d_mid.ptr, d_b.ptr, d_pair.ptr, d_so.ptr, M, N, 0)
+    g.fp8_nt_dev_bias_gelu_fp8(d_A.ptr, d_W.ptr, d_fused.ptr, M, N, K, d_sa.ptr, d_sb.ptr, d_b.ptr, d_so.ptr, 0)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_pair.get(), d_fused.get())
+    # and against the oracle
+    ref = O.bias_gelu_quantize_fp8(d_mid.get(), bias, 0.013)
+    assert np.array_equal(d_fused.get(), ref)
