@@ -26,23 +26,26 @@ __device__ __forceinline__ float gelu_tanh_form_rn(float x) {
     return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, th));
 }
 
-template <int BN>
+template <int BN, bool FP4 = false>
 struct PGemmCfg {
+    static_assert(!FP4 || BN == 128, "NVFP4: two 128-column accumulators plus the scale columns fill tensor memory");
     static constexpr int L_BYTES = 128 * 128;
     static constexpr int C_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = L_BYTES + C_BYTES;
+    static constexpr int SF_BYTES = FP4 ? 2048 : 0;    // four 512-byte scale atoms (one per K = 64 step) per operand
+    static constexpr int STAGE_BYTES = L_BYTES + C_BYTES + 2 * SF_BYTES;
     static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
     static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-    static constexpr int TMEM_COLS = 2 * BN;          // BN in {128, 256}
+    static constexpr int SF_COL = 2 * BN;             // NVFP4: 16 scale columns per operand behind the accumulators
+    static constexpr int TMEM_COLS = FP4 ? 512 : 2 * BN;   // BN in {128, 256}
     static constexpr int EPI_THREADS = 256;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool FP4 = false>
 __global__ void __launch_bounds__(320, 1)
 gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                            GemmParams p) {
-    using Cfg = PGemmCfg<BN>;
+    using Cfg = PGemmCfg<BN, FP4>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -104,11 +107,20 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                 tc::mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
                 tc::tma_load_2d(dst, &tmA, &full[s], kb * 128, m0);
                 tc::tma_load_2d(dst + Cfg::L_BYTES, &tmW, &full[s], kb * 128, n0);
+                if (FP4) {      // activations are the lane operand here: sf_lane = SFA, sf_col = SFW
+                    uint8_t* sf = dst + Cfg::L_BYTES + Cfg::C_BYTES;
+                    tc::bulk_load(sf, p.sf_lane + ((size_t)(m0 / 128) * p.sf_katoms + (size_t)kb * 4) * 512, 2048,
+                                  &full[s]);
+                    tc::bulk_load(sf + 2048, p.sf_col + ((size_t)(n0 / 128) * p.sf_katoms + (size_t)kb * 4) * 512,
+                                  2048, &full[s]);
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer: accumulator i & 1 for the CTA's i-th tile
-        constexpr uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN);
+        constexpr uint32_t idesc = FP4 ? tc::make_idesc_nvfp4(128, BN) : tc::make_idesc(0, 0, 0, 0, 128, BN);
+        const uint32_t sf_smem0 = tc::smem_u32(smem + Cfg::L_BYTES + Cfg::C_BYTES);
+        const uint32_t tmem_sfa = tmem + Cfg::SF_COL, tmem_sfw = tmem + Cfg::SF_COL + 16;
         const uint64_t dL0 = tc::make_desc_kmajor_sw128(tc::smem_u32(smem));
         const uint64_t dC0 = tc::make_desc_kmajor_sw128(tc::smem_u32(smem + Cfg::L_BYTES));
         long long kc = 0;
@@ -131,9 +143,22 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                 }
                 tc::tc_fence_after_sync();
                 const uint64_t so = (uint64_t)(s * (Cfg::STAGE_BYTES >> 4));
+                if (FP4) {
+                    const uint32_t sf = sf_smem0 + (uint32_t)(s * Cfg::STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    tc::mma_f8(d_tm, dL0 + so + 2 * k, dC0 + so + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k) {
+                        tc::tmem_cp_sf_atom(tmem_sfa + 4 * k, sf + 512 * k);
+                        tc::tmem_cp_sf_atom(tmem_sfw + 4 * k, sf + 2048 + 512 * k);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc::mma_nvfp4(d_tm, dL0 + so + 2 * k, dC0 + so + 2 * k, idesc, tmem_sfa + 4 * k,
+                                      tmem_sfw + 4 * k, (kb > 0 || k > 0) ? 1u : 0u);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc::mma_f8(d_tm, dL0 + so + 2 * k, dC0 + so + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
                 tc::mma_commit(&empty[s]);
             }
             if (*abort_flag) break;
@@ -227,13 +252,13 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     if (warp == 1) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool FP4 = false>
 static int launch_gemm_persistent(const void* A, const void* W, GemmParams p, int K, bool pdl, cudaStream_t stream) {
-    using Cfg = PGemmCfg<BN>;
+    using Cfg = PGemmCfg<BN, FP4>;
     static bool attr_done = false;
     static int sms = 0;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_persistent_kernel<BN, EPI>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_persistent_kernel<BN, EPI, FP4>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
         int dev = 0;
@@ -242,9 +267,11 @@ static int launch_gemm_persistent(const void* A, const void* W, GemmParams p, in
         attr_done = true;
     }
     CUtensorMap tmA, tmW;
-    int rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, (uint64_t)K, (uint64_t)K, 128);
+    const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
+    if (FP4) p.sf_katoms = K / 64;
+    int rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, row_bytes, row_bytes, 128);
     if (rc) return rc;
-    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, BN);
+    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, row_bytes, row_bytes, BN);
     if (rc) return rc;
     const int total = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
     cudaLaunchConfig_t cfg = {};
@@ -257,6 +284,6 @@ static int launch_gemm_persistent(const void* A, const void* W, GemmParams p, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_persistent_kernel<BN, EPI>, tmA, tmW, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_persistent_kernel<BN, EPI, FP4>, tmA, tmW, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }

@@ -105,12 +105,12 @@ residual_add_rms_norm_fp4_sfa_v2_fp16 = residual_add_rms_norm_fp4_sfa_fp16      
 
 # ------------------------------------------------------------------ GEMM
 def cutlass_fp4_gemm_variant(idx, A, SFA, B, SFB, D, M, N, K, alpha=1.0, beta=0.0, stream=0, *, pdl=False,
-                             splits=0, d_alpha=0) -> int:
+                             splits=0, d_alpha=0, one_tile_per_cta=False) -> int:
     """D (M, N) bf16 = alpha * (A.SFA) (B.SFB)^T (csrc/fp4_bindings.cpp:355-370); beta must be 0."""
     if beta != 0.0:
         raise NotBuilt("NVFP4 GEMM with beta != 0 (the decoder path calls with beta = 0)")
     return call_status("frt_b200_gemm_nvfp4_nt", A, SFA, B, SFB, D, M, N, K, alpha, d_alpha or None, None, splits,
-                       _f(pdl), stream)
+                       _f(pdl) | (2 if one_tile_per_cta else 0), stream)
 
 
 def cutlass_fp4_sq_fp16(A, SFA, B, SFB, D, M, N, K, alpha=1.0, beta=0.0, stream=0, **kw) -> int:   # :85-99

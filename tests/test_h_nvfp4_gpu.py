@@ -222,3 +222,22 @@ def test_gemm_nvfp4_rope_split_equals_pair():
     assert np.array_equal(k1.get(), k2.get())
     assert np.array_equal(v1.get(), v2.get())
     assert fvk.tensor_core_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (1000, 200, 768), (4096, 3072, 1024)])
+def test_gemm_nvfp4_persistent_equals_one_tile_per_cta(M, N, K):
+    """M > 256 runs as a persistent kernel (two accumulators + the scale columns in tensor memory); the
+    one-tile-per-CTA kernel accumulates in the same order: identical bytes."""
+    from flashrt_b200 import flash_rt_fp4 as fp4, flash_rt_kernels as fvk
+    from gpu_util import Dev, zeros
+    rng = np.random.default_rng(M + N + K + 1)
+    Ap, Asf = _operand(rng, M, K, 1.0)
+    Wp, Wsf = _operand(rng, N, K, 0.02)
+    d = [Dev(Ap), Dev(Asf), Dev(Wp), Dev(Wsf)]
+    d_1, d_2 = zeros((M, N), np.uint16), zeros((M, N), np.uint16)
+    assert fp4.cutlass_fp4_gemm_variant(0, d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_1.ptr, M, N, K) == 0
+    assert fp4.cutlass_fp4_gemm_variant(0, d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_2.ptr, M, N, K,
+                                        one_tile_per_cta=True) == 0
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_1.get(), d_2.get())
+    _check(d_1.get(), O.gemm_nvfp4(Ap, Asf, Wp, Wsf, want_f32=True))
