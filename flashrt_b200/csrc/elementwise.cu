@@ -8,6 +8,7 @@
 //   fp8_accumulate_scale_max     csrc/kernels/quantize.cu:137-146
 //   residual_add / bias_residual / gate_mul_residual   csrc/kernels/elementwise.cu:34,207,302
 //   qkv_split_rope[_devpos]      csrc/kernels/rope.cu:135-277
+//   cfg_combine_into_residual    csrc/kernels/elementwise.cu:2299-2338
 //
 // All kernels move 16 bytes per thread per access, fully coalesced, and use a
 // grid-stride loop over a grid capped at a multiple of the SM count.
@@ -269,6 +270,26 @@ qkv_split_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16
     pdl_launch_dependents();
 }
 
+// ------------------------------------------------------------------ classifier-free guidance combine
+// residual[i] += v_uncond[i] + beta * (v_cond[i] - v_uncond[i])   (one fma for the guided velocity, one add)
+template <typename T>
+__global__ void __launch_bounds__(256)
+cfg_combine_kernel(T* __restrict__ residual, const T* __restrict__ v_cond, const T* __restrict__ v_uncond,
+                   float beta, long long n) {
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float r, vc, vu;
+        if constexpr (sizeof(T) == 4) {
+            r = residual[i]; vc = v_cond[i]; vu = v_uncond[i];
+        } else {
+            r = __bfloat162float(residual[i]); vc = __bfloat162float(v_cond[i]); vu = __bfloat162float(v_uncond[i]);
+        }
+        const float out = __fadd_rn(r, __fmaf_rn(beta, __fsub_rn(vc, vu), vu));
+        if constexpr (sizeof(T) == 4) residual[i] = out; else residual[i] = __float2bfloat16_rn(out);
+    }
+    pdl_launch_dependents();
+}
+
 }  // namespace frt
 
 using namespace frt;
@@ -369,6 +390,20 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
     return launch(qkv_split_rope_kernel, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
                   (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)rope, (__nv_bfloat16*)Q, (__nv_bfloat16*)K,
                   (__nv_bfloat16*)V, devpos, seq, q_dim, k_dim, v_dim, head_dim);
+}
+
+// residual <- residual + (v_uncond + beta * (v_cond - v_uncond)), n elements; F32 = 1: all three arrays fp32 (the
+// Euler state of this library), else bf16 as in the reference.  n % 2 == 0 as there.
+int frt_b200_cfg_combine_into_residual(void* residual, const void* v_cond, const void* v_uncond, float beta,
+                                       long long n, int f32, int flags, void* stream) {
+    if (!residual || !v_cond || !v_uncond || n < 0) return FRT_ERR_INVALID;
+    if (n & 1) return FRT_ERR_UNSUPPORTED;
+    if (n == 0) return FRT_OK;
+    if (f32)
+        return launch(cfg_combine_kernel<float>, grid_for(n, 256, 8), 256, (cudaStream_t)stream, flags & 1,
+                      (float*)residual, (const float*)v_cond, (const float*)v_uncond, beta, n);
+    return launch(cfg_combine_kernel<__nv_bfloat16>, grid_for(n, 256, 8), 256, (cudaStream_t)stream, flags & 1,
+                  (__nv_bfloat16*)residual, (const __nv_bfloat16*)v_cond, (const __nv_bfloat16*)v_uncond, beta, n);
 }
 
 int frt_b200_device_sm_count(void) { return sm_count(); }

@@ -126,6 +126,13 @@ def qkv_split_rope_devpos(qkv, rope_weights, Q, K, V, devpos, seq, q_dim, k_dim,
          _f(pdl), stream)
 
 
+# ------------------------------------------------------------------ classifier-free guidance (csrc/bindings.cpp:1133-1141)
+def cfg_combine_into_residual(residual, v_cond, v_uncond, beta, n, stream=0, *, pdl=False, f32=False):
+    """residual += v_uncond + beta * (v_cond - v_uncond).  ``f32=True`` (not in the reference): fp32 arrays."""
+    call("frt_b200_cfg_combine_into_residual", residual, v_cond, v_uncond, float(beta), n, 1 if f32 else 0, _f(pdl),
+         stream)
+
+
 # ------------------------------------------------------------------ elementwise (csrc/bindings.cpp:1103-1119)
 def gate_mul_residual(residual, x, gate, n, stream=0, *, pdl=False):
     # flat form of the reference: gate has the same n elements as residual

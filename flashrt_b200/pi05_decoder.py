@@ -175,16 +175,61 @@ def rope_table(start: int, count: int) -> torch.Tensor:
 SITES = ("qkv", "o", "gu", "d")
 
 
-class Pi05DecoderPipeline:
+class StepIO:
+    """Entry and exit of one Euler step, shared by the FP8 and NVFP4 compositions.
+
+    Plain / batched: ``noise`` is (batch * chunk, 32); the in-projection covers all rows, the out-projection
+    (pre-scaled by dt) accumulates into it.  Classifier-free guidance (``fe.cfg_beta`` set, batch 2: slot 0 =
+    conditioned prefix, slot 1 = unconditioned): ``noise`` is (chunk, 32) and feeds both slots; the out-projection
+    writes the two velocities and ``cfg_combine_into_residual`` folds them into the noise
+    (flash_rt/models/pi05/pipeline_rtx_cfg_batched.py:313-417)."""
+
+    def _alloc_step_io(self):
+        fe = self.fe
+        rows = fe.chunk_size if fe.cfg_beta is not None else fe.batch * fe.chunk_size
+        self.noise = torch.zeros(rows, ACTION_DIM, dtype=torch.float32, device=fe.device)   # Euler state, fp32
+        self.v = (torch.zeros(fe.batch * fe.chunk_size, ACTION_DIM, dtype=torch.float32, device=fe.device)
+                  if fe.cfg_beta is not None else None)
+
+    def _step_in(self, stream, pdl):
+        fe, g = self.fe, self.gemm
+        S, M = fe.chunk_size, fe.batch * fe.chunk_size
+        if fe.cfg_beta is None:
+            g.bf16_nn(self.noise.data_ptr(), fe.action_in_w.data_ptr(), self.x.data_ptr(), M, DEC_D, ACTION_DIM,
+                      stream, pdl=pdl, bias=fe.action_in_b.data_ptr(), a_f32=True)
+        else:
+            for b in range(fe.batch):
+                g.bf16_nn(self.noise.data_ptr(), fe.action_in_w.data_ptr(), self.x[b * S:].data_ptr(), S, DEC_D,
+                          ACTION_DIM, stream, pdl=pdl and b == 0, bias=fe.action_in_b.data_ptr(), a_f32=True)
+
+    def _step_out(self, stream, pdl):
+        fe, g = self.fe, self.gemm
+        S, M = fe.chunk_size, fe.batch * fe.chunk_size
+        if fe.cfg_beta is None:
+            g.bf16_nn(self.xn.data_ptr(), fe.action_out_w.data_ptr(), self.noise.data_ptr(), M, ACTION_DIM, DEC_D,
+                      stream, pdl=pdl, bias=fe.action_out_b.data_ptr(), accumulate=True, d_f32=True)
+        else:
+            g.bf16_nn(self.xn.data_ptr(), fe.action_out_w.data_ptr(), self.v.data_ptr(), M, ACTION_DIM, DEC_D,
+                      stream, pdl=pdl, bias=fe.action_out_b.data_ptr(), accumulate=False, d_f32=True)
+            fvk.cfg_combine_into_residual(self.noise.data_ptr(), self.v.data_ptr(), self.v[S:].data_ptr(),
+                                          fe.cfg_beta, S * ACTION_DIM, stream, pdl=pdl, f32=True)
+
+    def step_io_launches(self) -> int:
+        fe = self.fe
+        return (fe.batch + 2) if fe.cfg_beta is not None else 2
+
+
+class Pi05DecoderPipeline(StepIO):
     """Pointer-only composition of the denoise loop (what gets captured in the graph)."""
 
     def __init__(self, fe: "Pi05DecoderB200"):
         self.fe = fe
         self.gemm = fvk.GemmRunner()
         dev = fe.device
-        S, L, N = fe.chunk_size, fe.layers, fe.num_steps
+        S, L, N = fe.batch * fe.chunk_size, fe.layers, fe.num_steps     # S = rows of every activation buffer
+        self.M = S
         z = lambda *shape, dtype=BF16: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
-        self.noise = z(S, ACTION_DIM, dtype=torch.float32)   # Euler state, kept in fp32 across the steps
+        self._alloc_step_io()
         self.x = z(S, DEC_D)
         self.xn = z(S, DEC_D)
         self.h_bf16 = z(S, DEC_D)                      # calibration only: un-quantised norm output
@@ -201,7 +246,7 @@ class Pi05DecoderPipeline:
         self.attn_splits = 8
         self.o_accum = z(self.attn_splits, S, DEC_NH, DEC_HD, dtype=torch.float32)
         self.lse_accum = z(self.attn_splits, DEC_NH, S, dtype=torch.float32)
-        self.attn_counters = z(2 * ((S * DEC_NH + 127) // 128), dtype=torch.int32)
+        self.attn_counters = z(2 * fe.batch * ((fe.chunk_size * DEC_NH + 127) // 128), dtype=torch.int32)
         # activation scales: one per GEMM input site, per layer, per denoise step (pipeline_rtx.py:649-660)
         self.act_scale = torch.ones(N, L, len(SITES), dtype=torch.float32, device=dev)
         self.scratch_scale = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -227,7 +272,8 @@ class Pi05DecoderPipeline:
         qs = (S * DEC_NH * DEC_HD, DEC_NH * DEC_HD, DEC_HD)
         ks = (fe.kv_rows * DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD)
         fa2.fwd_bf16(self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
-                     self.attn.data_ptr(), 0, self.lse_accum.data_ptr(), self.o_accum.data_ptr(), 1, S, T, DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
+                     self.attn.data_ptr(), 0, self.lse_accum.data_ptr(), self.o_accum.data_ptr(), fe.batch, S, T,
+                     DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
                      1.0 / math.sqrt(DEC_HD), fe.sm_count, stream, pdl=pdl,
                      out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0, out_scale=out8_scale_ptr or 0,
                      kv_static_rows=fe.prefix_len, kv_splits=self.attn_splits,
@@ -241,30 +287,31 @@ class Pi05DecoderPipeline:
         amax / 448 is measured on the device and folded (max) into the per-site per-step scale table.
         ``step_hook(step)`` (eager runs only) is called after each Euler step, e.g. to snapshot the state."""
         fe, g = self.fe, self.gemm
-        S, L = fe.chunk_size, fe.layers
+        S, L, B, CS = self.M, fe.layers, fe.batch, fe.chunk_size    # S = batch * chunk rows
         pdl = fe.use_pdl and not calibrate
         for step in range(fe.num_steps):
             # C0: action tokens -> width D, + bias
-            g.bf16_nn(self.noise.data_ptr(), fe.action_in_w.data_ptr(), self.x.data_ptr(), S, DEC_D, ACTION_DIM,
-                      stream, pdl=pdl, bias=fe.action_in_b.data_ptr(), a_f32=True)
+            self._step_in(stream, pdl)
             for i in range(L):
                 # C1: adaRMS(style_attn) -> FP8 (layer 0 only; later layers get it from C7 of the previous one)
                 if i == 0:
                     self._norm(None, None, "attn", step, i, "qkv", stream, pdl, calibrate)
                 # C2: QKV projection, split + RoPE, K/V appended behind the prefix (one launch when not calibrating)
-                if calibrate or not fe.fuse_epilogues:
+                if calibrate or not fe.fuse_epilogues or B > 1:
                     self._gemm(self.act8, fe.w_qkv[i], fe.ws_qkv_t[i], self.qkv, S, 2560, DEC_D,
                                self._scale_ptr(step, i, "qkv"), stream, pdl)
-                    fvk.qkv_split_rope(self.qkv.data_ptr(), fe.rope.data_ptr(), self.q.data_ptr(),
-                                       fe.k_cache[i, fe.prefix_len:].data_ptr(),
-                                       fe.v_cache[i, fe.prefix_len:].data_ptr(), S, DEC_NH * DEC_HD,
-                                       DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
+                    for b in range(B):      # every batch element appends to its own cache
+                        fvk.qkv_split_rope(self.qkv[b * CS:].data_ptr(), fe.rope.data_ptr(),
+                                           self.q[b * CS:].data_ptr(), fe.k_cache[i, b, fe.prefix_len:].data_ptr(),
+                                           fe.v_cache[i, b, fe.prefix_len:].data_ptr(), CS, DEC_NH * DEC_HD,
+                                           DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream,
+                                           pdl=pdl and b == 0)
                 else:
                     g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
                                             self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                             fe.rope.data_ptr(), self.q.data_ptr(),
-                                            fe.k_cache[i, fe.prefix_len:].data_ptr(),
-                                            fe.v_cache[i, fe.prefix_len:].data_ptr(), DEC_NH * DEC_HD,
+                                            fe.k_cache[i, 0, fe.prefix_len:].data_ptr(),
+                                            fe.v_cache[i, 0, fe.prefix_len:].data_ptr(), DEC_NH * DEC_HD,
                                             DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
                 # C3 + C4: attention (FP8 copy fused), output projection
                 if calibrate:
@@ -302,14 +349,19 @@ class Pi05DecoderPipeline:
             # C8: final adaRMS (bf16), out-projection (+bias, pre-scaled by -1/N) accumulated into the noise
             fvk.ada_rms_norm_style(self.x.data_ptr(), self.ones.data_ptr(), self._style("final", step),
                                    self.xn.data_ptr(), 0, S, DEC_D, 1e-6, stream, pdl=pdl, style_stride=0)
-            g.bf16_nn(self.xn.data_ptr(), fe.action_out_w.data_ptr(), self.noise.data_ptr(), S, ACTION_DIM, DEC_D,
-                      stream, pdl=pdl, bias=fe.action_out_b.data_ptr(), accumulate=True, d_f32=True)
+            self._step_out(stream, pdl)
             if step_hook is not None:
                 step_hook(step)
 
+    def launches_per_layer(self) -> int:
+        fe = self.fe
+        if fe.batch == 1 and fe.fuse_epilogues:
+            return 7        # qkv gemm (+rope split), attention, o gemm, norm, gate|up gemm (+geglu), down gemm, norm
+        return (1 + fe.batch) + 1 + 1 + 1 + (1 if fe.fuse_epilogues else 2) + 1 + 1
+
     def _norm(self, delta, gate_from, style_kind, step, layer, site, stream, pdl, calibrate):
         """(x += delta * gate) ; adaRMS(style) -> FP8 for GEMM site ``site`` of ``layer``."""
-        S = self.fe.chunk_size
+        S = self.M
         style = self._style(style_kind, step, layer)
         gate = (self._style(*gate_from) + 2 * DEC_D * 2) if gate_from else None
         if not calibrate:
@@ -341,7 +393,7 @@ class Pi05DecoderB200:
     def __init__(self, checkpoint, *, num_steps: int = NUM_STEPS_DEFAULT, chunk_size: int = CHUNK_DEFAULT,
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
-                 **_ignored):
+                 cfg_beta: float | None = None, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -354,8 +406,9 @@ class Pi05DecoderB200:
         self.kv_rows = prefix_len + chunk_size
         if precision not in ("fp8", "nvfp4"):
             raise ValueError(f"precision must be 'fp8' or 'nvfp4', got {precision!r}")
-        if batch != 1 and precision != "nvfp4":
-            raise ValueError("a batch of chunks is implemented for precision='nvfp4' only")
+        if cfg_beta is not None and batch != 2:
+            raise ValueError("classifier-free guidance runs the conditioned and the unconditioned slot: batch must be 2")
+        self.cfg_beta = None if cfg_beta is None else float(cfg_beta)
         if batch < 1 or batch * ((chunk_size * DEC_NH + 127) // 128) * 8 > self.sm_count:
             raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")
         self.precision, self.batch = precision, batch
@@ -387,19 +440,17 @@ class Pi05DecoderB200:
         for n in ("action_in_w", "action_in_b", "action_out_w", "action_out_b"):
             setattr(self, n, getattr(self, n).contiguous().to(dev))
         self.rope = rope_table(prefix_len, chunk_size).to(dev)
+        # one cache per batch element: (layers, batch, prefix + chunk, 256)
+        self.k_cache = torch.zeros(layers, batch, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
         if precision == "nvfp4":
             from .pi05_decoder_nvfp4 import Pi05DecoderNvfp4Pipeline
-            # one cache per batch element: (layers, batch, prefix + chunk, 256)
-            self.k_cache = torch.zeros(layers, batch, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
-            self.v_cache = torch.zeros_like(self.k_cache)
             self.pipeline = Pi05DecoderNvfp4Pipeline(self)
         else:
-            self.k_cache = torch.zeros(layers, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
-            self.v_cache = torch.zeros_like(self.k_cache)
             self.pipeline = Pi05DecoderPipeline(self)
         self.stream = torch.cuda.Stream(device=dev)
         self.graph = None
-        rows = batch * chunk_size
+        rows = chunk_size if self.cfg_beta is not None else batch * chunk_size
         self._pinned_in = torch.zeros(rows, ACTION_DIM, dtype=torch.float32).pin_memory()
         self._pinned_out = torch.zeros(rows, ACTION_DIM, dtype=torch.float32).pin_memory()
         self._dev_in = torch.zeros(rows, ACTION_DIM, dtype=torch.float32, device=dev)
@@ -408,15 +459,21 @@ class Pi05DecoderB200:
 
     # ---- prefix (what the encoder would have written) ---------------------
     def set_prefix(self, prefix_k: torch.Tensor, prefix_v: torch.Tensor) -> None:
-        """prefix_k / prefix_v: (layers, prefix_len, 256); K already carries its RoPE, as in the encoder's cache."""
-        assert prefix_k.shape == (self.layers, self.prefix_len, DEC_NKV * DEC_HD), prefix_k.shape
-        if self.precision == "nvfp4":      # every batch element attends to the same prefix
-            self.k_cache[:, :, :self.prefix_len].copy_(prefix_k.to(BF16).unsqueeze(1).expand(-1, self.batch, -1, -1))
-            self.v_cache[:, :, :self.prefix_len].copy_(prefix_v.to(BF16).unsqueeze(1).expand(-1, self.batch, -1, -1))
-        else:
-            self.k_cache[:, :self.prefix_len].copy_(prefix_k.to(BF16))
-            self.v_cache[:, :self.prefix_len].copy_(prefix_v.to(BF16))
+        """prefix_k / prefix_v: (layers, prefix_len, 256), shared by every batch element, or
+        (layers, batch, prefix_len, 256) with one prefix per element (classifier-free guidance: slot 0 = conditioned
+        prompt, slot 1 = unconditioned).  K already carries its RoPE, as in the encoder's cache."""
+        if prefix_k.dim() == 3:
+            prefix_k, prefix_v = (t.unsqueeze(1).expand(-1, self.batch, -1, -1) for t in (prefix_k, prefix_v))
+        assert prefix_k.shape == (self.layers, self.batch, self.prefix_len, DEC_NKV * DEC_HD), prefix_k.shape
+        self.k_cache[:, :, :self.prefix_len].copy_(prefix_k.to(BF16))
+        self.v_cache[:, :, :self.prefix_len].copy_(prefix_v.to(BF16))
         torch.cuda.synchronize(self.device)
+
+    def set_prefix_pair(self, cond_k, cond_v, uncond_k, uncond_v) -> None:
+        """Conditioned / unconditioned prefixes of the classifier-free-guidance pair
+        (``set_language_embeds_pair``, flash_rt/models/pi05/pipeline_rtx_cfg_batched.py:197-229, one level later:
+        the per-layer K/V the two prompts leave in the cache)."""
+        self.set_prefix(torch.stack([cond_k, uncond_k], dim=1), torch.stack([cond_v, uncond_v], dim=1))
 
     # ---- calibration --------------------------------------------------------
     @property
@@ -434,7 +491,7 @@ class Pi05DecoderB200:
         with torch.cuda.stream(self.stream):
             for nz in noises:
                 p.act_scale.zero_()
-                p.noise.copy_(nz.to(self.device, torch.float32))
+                p.noise.copy_(nz.to(self.device, torch.float32).reshape(p.noise.shape))
                 p.transformer_decoder(self.stream.cuda_stream, calibrate=True)
                 self.stream.synchronize()
                 per_sample.append(p.act_scale.clone())
@@ -491,7 +548,8 @@ class Pi05DecoderB200:
         """obs["noise"]: (chunk, 32) array or tensor on the HOST (a fresh N(0,1) draw if absent).  Uploads it,
         replays the loop, downloads the actions (pi05_rtx.py:1547-1614)."""
         nz = obs.get("noise") if obs else None
-        shape = (self.chunk_size, ACTION_DIM) if self.batch == 1 else (self.batch, self.chunk_size, ACTION_DIM)
+        single = self.batch == 1 or self.cfg_beta is not None
+        shape = (self.chunk_size, ACTION_DIM) if single else (self.batch, self.chunk_size, ACTION_DIM)
         if nz is None:
             nz = torch.randn(*shape)
         nz = torch.as_tensor(nz, dtype=torch.float32)
@@ -507,8 +565,6 @@ class Pi05DecoderB200:
     def kernels_per_loop(self) -> int:
         """Launches of this library's kernels inside one replay (for reporting)."""
         L, N = self.layers, self.num_steps
-        if self.precision == "nvfp4":
-            return N * (1 + 1 + self.pipeline.launches_per_layer() * L + 2)
-        # qkv gemm (+rope split), attention, o gemm, norm, gate|up gemm (+geglu), down gemm, norm
-        per_layer = 7 if self.fuse_epilogues else 9
-        return N * (1 + 1 + per_layer * L + 2)
+        p = self.pipeline
+        # in-projection(s), first norm, the blocks, final residual + final norm, out-projection (+ guidance combine)
+        return N * (p.step_io_launches() + 1 + p.launches_per_layer() * L + 1)

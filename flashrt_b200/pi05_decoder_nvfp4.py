@@ -22,7 +22,7 @@ import torch
 from . import flash_rt_fa2 as fa2
 from . import flash_rt_fp4 as fp4
 from . import flash_rt_kernels as fvk
-from .pi05_decoder import ACTION_DIM, BF16, DEC_D, DEC_H, DEC_HD, DEC_NH, DEC_NKV
+from .pi05_decoder import ACTION_DIM, BF16, DEC_D, DEC_H, DEC_HD, DEC_NH, DEC_NKV, StepIO
 
 QKV_N = (DEC_NH + 2 * DEC_NKV) * DEC_HD
 
@@ -46,7 +46,7 @@ class Nvfp4Weight:
         torch.cuda.synchronize(dev)
 
 
-class Pi05DecoderNvfp4Pipeline:
+class Pi05DecoderNvfp4Pipeline(StepIO):
     """Pointer-only composition of the NVFP4 denoise loop (what gets captured in the graph)."""
 
     def __init__(self, fe):
@@ -58,7 +58,7 @@ class Pi05DecoderNvfp4Pipeline:
         self.M = M
         z = lambda *shape, dtype=BF16: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         sfb = lambda K: z(fp4.sfa_size_bytes(M, K), dtype=torch.uint8)               # noqa: E731  zero-filled once
-        self.noise = z(M, ACTION_DIM, dtype=torch.float32)
+        self._alloc_step_io()
         self.x = z(M, DEC_D)
         self.xn = z(M, DEC_D)
         self.qkv = z(M, QKV_N)
@@ -111,8 +111,7 @@ class Pi05DecoderNvfp4Pipeline:
         B, S, L, M = fe.batch, fe.chunk_size, fe.layers, self.M
         pdl = fe.use_pdl
         for step in range(fe.num_steps):
-            g.bf16_nn(self.noise.data_ptr(), fe.action_in_w.data_ptr(), self.x.data_ptr(), M, DEC_D, ACTION_DIM,
-                      stream, pdl=pdl, bias=fe.action_in_b.data_ptr(), a_f32=True)
+            self._step_in(stream, pdl)
             for i in range(L):
                 if i == 0:
                     self._norm(None, None, "attn", step, i, stream, pdl)
@@ -154,8 +153,7 @@ class Pi05DecoderNvfp4Pipeline:
                              self._style("ffn", step, i) + 2 * DEC_D * 2, 0, M, DEC_D, 1 if pdl else 0, stream)
             fvk.ada_rms_norm_style(self.x.data_ptr(), self.ones.data_ptr(), self._style("final", step),
                                    self.xn.data_ptr(), 0, M, DEC_D, 1e-6, stream, pdl=pdl, style_stride=0)
-            g.bf16_nn(self.xn.data_ptr(), fe.action_out_w.data_ptr(), self.noise.data_ptr(), M, ACTION_DIM, DEC_D,
-                      stream, pdl=pdl, bias=fe.action_out_b.data_ptr(), accumulate=True, d_f32=True)
+            self._step_out(stream, pdl)
             if step_hook is not None:
                 step_hook(step)
 

@@ -291,6 +291,13 @@ int frt_b200_copy(void* dst, const void* src, long long nbytes, void* stream);
 /* get_sm_version               csrc/bindings.cpp:2447-2453  (returns major*10+minor, 100 on B200) */
 int frt_b200_sm_version(void);
 
+/* cfg_combine_into_residual    csrc/bindings.cpp:1133-1141 -> csrc/kernels/elementwise.cu:2299-2338
+ *   residual[i] += v_uncond[i] + beta * (v_cond[i] - v_uncond[i]), i < n (classifier-free guidance, Eq. 13 of the
+ *   reference's flash_rt/refs/pi05_cfg_reference.py:8-15).  f32 = 0: bf16 arrays as in the reference; f32 = 1: fp32
+ *   arrays (the Euler state of this library).  n % 2 == 0. */
+int frt_b200_cfg_combine_into_residual(void* residual, const void* v_cond, const void* v_uncond, float beta,
+                                       long long n, int f32, int flags, void* stream);
+
 /* number of SMs of the current device (grid sizing) */
 int frt_b200_device_sm_count(void);
 

@@ -314,6 +314,36 @@ def denoise_loop(noise, ckpt: dict, prefix_k, prefix_v, num_steps: int = 10, lay
     return (x_act, traj) if return_trajectory else x_act
 
 
+def denoise_loop_cfg(noise, ckpt: dict, cond_kv, uncond_kv, beta: float, num_steps: int = 10, layers: int = DEC_L,
+                     styles_bf16: bool = True, return_trajectory: bool = False):
+    """Classifier-free guidance (flash_rt/refs/pi05_cfg_reference.py:8-15, Eq. 13 of the paper it cites): every
+    Euler step runs the velocity network twice -- with the conditioned and with the unconditioned prefix -- and
+    advances with v = (1 - beta) * v_uncond + beta * v_cond.  cond_kv / uncond_kv = (prefix_k, prefix_v)."""
+    W = ckpt
+    S = noise.shape[0]
+    P = cond_kv[0].shape[1]
+    sa, sf, fin = styles(ckpt, num_steps, layers, round_bf16=styles_bf16)
+    tab = rope_table(np.arange(P, P + S))
+    if styles_bf16:
+        tab = tab.to(torch.bfloat16).float()
+    x_act = noise.float().clone()
+    traj = []
+    dt = -1.0 / num_steps
+
+    def velocity(x_in, s, kv):
+        x = x_in @ W["decoder_action_in_proj_w"].float() + W["decoder_action_in_proj_b"].float()
+        for i in range(layers):
+            x = decoder_block(x, W, i, sa[s, i], sf[s, i], kv[0][i, :P], kv[1][i, :P], tab)
+        h, _ = ada_rms(x, fin[s])
+        return h @ W["decoder_action_out_proj_w"].float() + W["decoder_action_out_proj_b"].float()
+
+    for s in range(num_steps):
+        v_c, v_u = velocity(x_act, s, cond_kv), velocity(x_act, s, uncond_kv)
+        x_act = x_act + dt * (v_u + beta * (v_c - v_u))
+        traj.append(x_act.clone())
+    return (x_act, traj) if return_trajectory else x_act
+
+
 # ------------------------------------------------------------------ HF state dict -> kernel-layout dictionary
 def from_hf_state_dict(sd: dict, layers: int = DEC_L) -> dict:
     """Restates the decoder part of the reference's checkpoint conversion (pi05_rtx.py:216-283): projections

@@ -330,3 +330,13 @@ def gemm_nvfp4(a_packed, a_sf, w_packed, w_sf, alpha: float = 1.0, bias=None, wa
         D = D + bf16_bits_to_f32(_u16(bias)).astype(np.float64)[None, :]
     D = D.astype(np.float32)
     return D if want_f32 else f32_to_bf16_bits(D)
+
+
+def cfg_combine(residual, v_cond, v_uncond, beta: float):
+    """residual + (v_uncond + beta * (v_cond - v_uncond)); bf16 bit patterns (uint16) or float32 arrays."""
+    r = np.ascontiguousarray(residual).copy()
+    vc, vu = np.ascontiguousarray(v_cond), np.ascontiguousarray(v_uncond)
+    assert r.dtype == vc.dtype == vu.dtype and r.dtype in (np.uint16, np.float32)
+    fn = lib().orc_cfg_combine_bf16 if r.dtype == np.uint16 else lib().orc_cfg_combine_f32
+    fn(_p(r), _p(vc), _p(vu), C.c_float(beta), C.c_longlong(r.size))
+    return r

@@ -625,3 +625,15 @@ void orc_geglu_nvfp4(const uint16_t* merged, uint8_t* packed, uint8_t* sf, int r
     orc_nvfp4_quantize_f32(tmp, packed, sf, rows, H, family, 1.0f);
     free(tmp);
 }
+
+/* ------------------------------------------------------------------ classifier-free guidance combine
+ * cfg_combine_kernel, csrc/kernels/elementwise.cu:2299-2324: residual += v_uncond + beta * (v_cond - v_uncond) */
+void orc_cfg_combine_bf16(uint16_t* residual, const uint16_t* vc, const uint16_t* vu, float beta, long long n) {
+    for (long long i = 0; i < n; ++i) {
+        float c = bf16_to_f32(vc[i]), u = bf16_to_f32(vu[i]);
+        residual[i] = f32_to_bf16(bf16_to_f32(residual[i]) + fmaf(beta, c - u, u));
+    }
+}
+void orc_cfg_combine_f32(float* residual, const float* vc, const float* vu, float beta, long long n) {
+    for (long long i = 0; i < n; ++i) residual[i] = residual[i] + fmaf(beta, vc[i] - vu[i], vu[i]);
+}
