@@ -34,8 +34,8 @@ class VLAModel:
     def set_prefix(self, prefix_k, prefix_v) -> None:
         self._fe.set_prefix(prefix_k, prefix_v)
 
-    def calibrate(self, noises, percentile: float | None = None) -> None:
-        self._fe.calibrate(noises, percentile=percentile)
+    def calibrate(self, noises, percentile: float | None = None, **kw) -> None:
+        self._fe.calibrate(noises, percentile=percentile, **kw)
 
     def infer(self, obs: dict) -> dict:
         return self._fe.infer(obs)

@@ -413,13 +413,19 @@ class Pi05DecoderB200:
             raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")
         self.precision, self.batch = precision, batch
         self.WEIGHT_SPEC = build_spec(layers, num_steps, precision)
+        self.checkpoint_path = None
         if isinstance(checkpoint, dict):
             source = DictSource(checkpoint)
         elif isinstance(checkpoint, str) and checkpoint.startswith("synthetic"):
             seed = int(checkpoint.split(":")[1]) if ":" in checkpoint else 0
             source = DictSource(synthetic_state_dict(seed, layers))
         else:
-            source = SafetensorsSource(str(checkpoint))
+            import os
+            ck = str(checkpoint)
+            if os.path.isdir(ck):
+                ck = os.path.join(ck, "model.safetensors")
+            self.checkpoint_path = ck
+            source = SafetensorsSource(ck)
         WeightLoader(source, target=self, spec=self.WEIGHT_SPEC).run()
         dev = self.device
         if precision == "nvfp4":
@@ -480,13 +486,32 @@ class Pi05DecoderB200:
     def calibrated(self) -> bool:
         return self.pipeline.calibrated
 
-    def calibrate(self, noises, percentile: float | None = None) -> None:
+    def _cache_meta(self, n_samples: int, percentile) -> dict:
+        return {"layers": self.layers, "num_steps": self.num_steps, "chunk": self.chunk_size, "batch": self.batch,
+                "samples": n_samples, "percentile": percentile, "sites": list(SITES)}
+
+    def calibrate(self, noises, percentile: float | None = None, use_cache: bool = False, cache_dir=None) -> None:
         """Static per-tensor activation scales from ``noises`` (list of (chunk, 32) tensors).  Each sample runs
         the eager dynamic-scale pass; the table keeps the max over samples (``percentile`` None) or the given
-        percentile of the per-sample scales (flash_rt/core/calibration.py:38-64)."""
+        percentile of the per-sample scales (flash_rt/core/calibration.py:38-64).  ``use_cache``: when the model
+        was loaded from a file, reuse / store the table in the on-disk calibration cache
+        (flash_rt/core/quant/calibrator.py:28-145) keyed by checkpoint hash and prefix length."""
         p = self.pipeline
         if self.precision == "nvfp4":
             return                      # block scales are computed by the producing kernels at run time
+        from . import calibration_cache as cc
+        cacheable = use_cache and self.checkpoint_path is not None
+        if cacheable:
+            hit = cc.load_calibration(self.checkpoint_path, self.prefix_len, expected_count=p.act_scale.numel(),
+                                      cache_dir=cache_dir, metadata=self._cache_meta(len(noises), percentile))
+            if hit is not None:
+                p.act_scale.copy_(torch.tensor(hit["ae_scales"], dtype=torch.float32).reshape(p.act_scale.shape))
+                torch.cuda.synchronize(self.device)
+                p.calibrated = True
+                self.graph = None
+                self.calibration_source = "cache"
+                return
+        self.calibration_source = "measured"
         per_sample = []
         with torch.cuda.stream(self.stream):
             for nz in noises:
@@ -506,6 +531,9 @@ class Pi05DecoderB200:
             raise RuntimeError("a tensor-core kernel reported a timed-out wait during calibration")
         p.calibrated = True
         self.graph = None
+        if cacheable:
+            cc.save_calibration(self.checkpoint_path, self.prefix_len, p.act_scale.flatten().cpu().tolist(),
+                                metadata=self._cache_meta(len(noises), percentile), cache_dir=cache_dir)
 
     # ---- graph --------------------------------------------------------------
     def record_infer_graph(self) -> None:

@@ -87,3 +87,29 @@ def test_refuses_wrong_inputs():
     m = load_model("synthetic:0", config="pi05", layers=1)
     with pytest.raises(RuntimeError):
         m.predict(noise=np.zeros((50, 32), np.float32))     # not calibrated
+
+
+def test_checkpoint_file_and_calibration_cache_end_to_end(tmp_path):
+    """load_model(path to a .safetensors file) -> calibrate -> predict, then a second model of the same file takes
+    its scales from the on-disk calibration cache and reproduces the actions bit for bit."""
+    from flashrt_b200 import load_model
+    from flashrt_b200.calibration_cache import write_synthetic_checkpoint
+    L = 2
+    path = write_synthetic_checkpoint(str(tmp_path / "ckpt"), seed=5, layers=L)
+    pk, pv = R.synthetic_prefix_kv(seed=1, layers=L, prefix_len=256)
+    cal = [R.synthetic_noise(100 + j) for j in range(3)]
+    noise = R.synthetic_noise(1).numpy()
+    outs, sources = [], []
+    for _ in range(2):
+        m = load_model(path, config="pi05", layers=L, num_steps=4, chunk_size=50, prefix_len=256)
+        m.set_prefix(pk, pv)
+        m.calibrate(cal, use_cache=True, cache_dir=str(tmp_path / "cache"))
+        sources.append(m.frontend.calibration_source)
+        outs.append(m.predict(noise=noise))
+    assert sources == ["measured", "cache"]
+    assert np.array_equal(outs[0], outs[1])
+    # a different prefix length is a different cache key
+    m = load_model(path, config="pi05", layers=L, num_steps=4, chunk_size=50, prefix_len=128)
+    m.set_prefix(pk[:, :128], pv[:, :128])
+    m.calibrate(cal, use_cache=True, cache_dir=str(tmp_path / "cache"))
+    assert m.frontend.calibration_source == "measured"

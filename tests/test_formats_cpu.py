@@ -1,0 +1,72 @@
+"""CPU tests of the on-disk formats: calibration cache (keying, validation, atomic write) and the synthetic
+safetensors checkpoint read back through the weight loader."""
+import json
+
+import numpy as np
+import torch
+
+from flashrt_b200 import calibration_cache as cc
+
+
+def test_calibration_cache_roundtrip_and_validation(tmp_path):
+    ck = tmp_path / "model.safetensors"
+    ck.write_bytes(b"A" * 100000)
+    scales = [0.5 + i * 1e-3 for i in range(10 * 18 * 4)]
+    meta = {"layers": 18, "samples": 8}
+    f = cc.save_calibration(str(ck), 768, scales, metadata=meta, cache_dir=tmp_path / "cache")
+    assert f.name == f"{cc.checkpoint_hash(str(ck))}_Se768.json"
+    rec = cc.load_calibration(str(ck), 768, expected_count=720, cache_dir=tmp_path / "cache", metadata=meta)
+    assert rec is not None and rec["ae_scales"] == scales and rec["version"] == 1 and rec["num_ae_scales"] == 720
+    # every mismatch is a miss, never an exception
+    assert cc.load_calibration(str(ck), 512, cache_dir=tmp_path / "cache") is None                    # other Se
+    assert cc.load_calibration(str(ck), 768, expected_count=10, cache_dir=tmp_path / "cache") is None  # other count
+    assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache", metadata={"layers": 4}) is None
+    assert cc.load_calibration(str(tmp_path / "missing.safetensors"), 768, cache_dir=tmp_path / "cache") is None
+    other = tmp_path / "other.safetensors"
+    other.write_bytes(b"B" * 100000)
+    assert cc.load_calibration(str(other), 768, cache_dir=tmp_path / "cache") is None                  # other checkpoint
+    # the hash covers the first 64 KB and the size
+    same_head = tmp_path / "longer.safetensors"
+    same_head.write_bytes(b"A" * 100001)
+    assert cc.checkpoint_hash(str(same_head)) != cc.checkpoint_hash(str(ck))
+    # a damaged or foreign-version file is a miss
+    data = json.loads(f.read_text())
+    data["version"] = 2
+    f.write_text(json.dumps(data))
+    assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache") is None
+    f.write_text("{not json")
+    assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache") is None
+    # directory form of the checkpoint path
+    d = tmp_path / "ckpt_dir"
+    d.mkdir()
+    (d / "model.safetensors").write_bytes(b"C" * 1000)
+    cc.save_calibration(str(d), 768, [1.0, 2.0], cache_dir=tmp_path / "cache")
+    assert cc.load_calibration(str(d), 768, cache_dir=tmp_path / "cache")["ae_scales"] == [1.0, 2.0]
+
+
+def test_synthetic_checkpoint_reads_back_through_the_weight_loader(tmp_path):
+    from flashrt_b200.pi05_decoder import build_spec, synthetic_state_dict
+    from flashrt_b200.weight_loader import SafetensorsSource, WeightLoader
+    L = 2
+    path = cc.write_synthetic_checkpoint(str(tmp_path / "ckpt"), seed=3, layers=L)
+    assert path.endswith("model.safetensors")
+    sd = synthetic_state_dict(3, L)
+    src = SafetensorsSource(path)
+    for k in ("time_mlp_in.weight", "paligemma_with_expert.gemma_expert.model.layers.1.mlp.down_proj.weight"):
+        assert src.has(k)
+        assert torch.equal(src.get(k).to(torch.bfloat16), sd[k].to(torch.bfloat16))
+    assert not src.has("no.such.key")
+
+    class Target:
+        pass
+    a, b = Target(), Target()
+    WeightLoader(src, target=a, spec=build_spec(L, 10)).run()
+    from flashrt_b200.weight_loader import DictSource
+    WeightLoader(DictSource({k: v.to(torch.bfloat16) for k, v in sd.items()}), target=b, spec=build_spec(L, 10)).run()
+    assert a.w_qkv.shape == (L, 2560, 1024) and a.w_d.shape == (L, 1024, 4096)
+    assert torch.equal(a.w_qkv.view(torch.uint8), b.w_qkv.view(torch.uint8))
+    assert np.allclose(a.ws_gu, b.ws_gu)
+    # the NVFP4 spec keeps bf16 (N, K) weights for the device-side quantiser
+    c = Target()
+    WeightLoader(src, target=c, spec=build_spec(L, 10, "nvfp4")).run()
+    assert len(c.wb_qkv) == L and c.wb_qkv[0].shape == (2560, 1024) and c.wb_qkv[0].dtype == torch.bfloat16
