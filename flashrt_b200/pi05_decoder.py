@@ -218,6 +218,43 @@ class StepIO:
         fe = self.fe
         return (fe.batch + 2) if fe.cfg_beta is not None else 2
 
+    # -- where the fresh K / V rows go, and how the attention sees the cache ---------------------------------
+    def _kv_dst(self, layer, b):
+        """(K pointer, V pointer, devpos pointer) for the KV append of batch element ``b``.  Fixed-shape mode
+        (flash_rt/hardware/rtx/attn_backend.py:272-282, 481-537): cache base + a device-side row offset, so that
+        one captured graph serves every valid prefix length."""
+        fe = self.fe
+        if fe.fixed_shape:
+            return fe.k_cache[layer, b].data_ptr(), fe.v_cache[layer, b].data_ptr(), fe.dec_devpos.data_ptr()
+        return (fe.k_cache[layer, b, fe.prefix_len:].data_ptr(), fe.v_cache[layer, b, fe.prefix_len:].data_ptr(), 0)
+
+    def _split_rope(self, layer, b, qkv, q, rows, stream, pdl):
+        fe = self.fe
+        kp, vp, dp = self._kv_dst(layer, b)
+        args = (qkv.data_ptr(), fe.rope.data_ptr(), q.data_ptr(), kp, vp)
+        dims = (rows, DEC_NH * DEC_HD, DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream)
+        if dp:
+            fvk.qkv_split_rope_devpos(*args, dp, *dims, pdl=pdl)
+        else:
+            fvk.qkv_split_rope(*args, *dims, pdl=pdl)
+
+    def _attend(self, layer, stream, pdl, out_fp8=0, out_scale=0):
+        fe = self.fe
+        S, T = fe.chunk_size, fe.prefix_len + fe.chunk_size
+        qs = (S * DEC_NH * DEC_HD, DEC_NH * DEC_HD, DEC_HD)
+        ks = (fe.kv_rows * DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD)
+        kw = dict(pdl=pdl, out_fp8=out_fp8, out_scale=out_scale, kv_splits=self.attn_splits,
+                  counters=self.attn_counters.data_ptr())
+        common = (fe.batch, S, T, DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs, 1.0 / math.sqrt(DEC_HD), fe.sm_count, stream)
+        q, k, v, o = (self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
+                      self.attn.data_ptr())
+        if fe.fixed_shape:      # keys beyond *dec_seqused are masked; nothing may be fetched before the producer ends
+            fa2.fwd_bf16_seqused_splitkv(q, k, v, o, 0, fe.dec_seqused.data_ptr(), self.lse_accum.data_ptr(),
+                                         self.o_accum.data_ptr(), *common, kv_static_rows=0, **kw)
+        else:
+            fa2.fwd_bf16(q, k, v, o, 0, self.lse_accum.data_ptr(), self.o_accum.data_ptr(), *common,
+                         kv_static_rows=fe.prefix_len, **kw)
+
 
 class Pi05DecoderPipeline(StepIO):
     """Pointer-only composition of the denoise loop (what gets captured in the graph)."""
@@ -267,17 +304,8 @@ class Pi05DecoderPipeline(StepIO):
                              stream, pdl=pdl)
 
     def _attention(self, layer, stream, pdl, out8_scale_ptr):
-        fe = self.fe
-        S, T = fe.chunk_size, fe.prefix_len + fe.chunk_size
-        qs = (S * DEC_NH * DEC_HD, DEC_NH * DEC_HD, DEC_HD)
-        ks = (fe.kv_rows * DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD)
-        fa2.fwd_bf16(self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
-                     self.attn.data_ptr(), 0, self.lse_accum.data_ptr(), self.o_accum.data_ptr(), fe.batch, S, T,
-                     DEC_NH, DEC_NKV, DEC_HD, qs, ks, ks, qs,
-                     1.0 / math.sqrt(DEC_HD), fe.sm_count, stream, pdl=pdl,
-                     out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0, out_scale=out8_scale_ptr or 0,
-                     kv_static_rows=fe.prefix_len, kv_splits=self.attn_splits,
-                     counters=self.attn_counters.data_ptr())
+        self._attend(layer, stream, pdl, out_fp8=self.attn8.data_ptr() if out8_scale_ptr else 0,
+                     out_scale=out8_scale_ptr or 0)
 
     # ---- the loop --------------------------------------------------------
     def transformer_decoder(self, stream: int = 0, calibrate: bool = False, step_hook=None) -> None:
@@ -301,18 +329,13 @@ class Pi05DecoderPipeline(StepIO):
                     self._gemm(self.act8, fe.w_qkv[i], fe.ws_qkv_t[i], self.qkv, S, 2560, DEC_D,
                                self._scale_ptr(step, i, "qkv"), stream, pdl)
                     for b in range(B):      # every batch element appends to its own cache
-                        fvk.qkv_split_rope(self.qkv[b * CS:].data_ptr(), fe.rope.data_ptr(),
-                                           self.q[b * CS:].data_ptr(), fe.k_cache[i, b, fe.prefix_len:].data_ptr(),
-                                           fe.v_cache[i, b, fe.prefix_len:].data_ptr(), CS, DEC_NH * DEC_HD,
-                                           DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream,
-                                           pdl=pdl and b == 0)
+                        self._split_rope(i, b, self.qkv[b * CS:], self.q[b * CS:], CS, stream, pdl and b == 0)
                 else:
+                    kp, vp, dp = self._kv_dst(i, 0)
                     g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
                                             self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
-                                            fe.rope.data_ptr(), self.q.data_ptr(),
-                                            fe.k_cache[i, 0, fe.prefix_len:].data_ptr(),
-                                            fe.v_cache[i, 0, fe.prefix_len:].data_ptr(), DEC_NH * DEC_HD,
-                                            DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl)
+                                            fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, DEC_NH * DEC_HD,
+                                            DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, devpos=dp, pdl=pdl)
                 # C3 + C4: attention (FP8 copy fused), output projection
                 if calibrate:
                     self._attention(i, stream, False, 0)
@@ -393,7 +416,7 @@ class Pi05DecoderB200:
     def __init__(self, checkpoint, *, num_steps: int = NUM_STEPS_DEFAULT, chunk_size: int = CHUNK_DEFAULT,
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
-                 cfg_beta: float | None = None, **_ignored):
+                 cfg_beta: float | None = None, fixed_shape: bool = False, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -409,6 +432,9 @@ class Pi05DecoderB200:
         if cfg_beta is not None and batch != 2:
             raise ValueError("classifier-free guidance runs the conditioned and the unconditioned slot: batch must be 2")
         self.cfg_beta = None if cfg_beta is None else float(cfg_beta)
+        # fixed-shape mode: prefix_len is the LARGEST prefix; the valid length is a device-side value
+        self.fixed_shape = bool(fixed_shape)
+        self.valid_prefix_len = prefix_len
         if batch < 1 or batch * ((chunk_size * DEC_NH + 127) // 128) * 8 > self.sm_count:
             raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")
         self.precision, self.batch = precision, batch
@@ -446,6 +472,8 @@ class Pi05DecoderB200:
         for n in ("action_in_w", "action_in_b", "action_out_w", "action_out_b"):
             setattr(self, n, getattr(self, n).contiguous().to(dev))
         self.rope = rope_table(prefix_len, chunk_size).to(dev)
+        self.dec_devpos = torch.full((1,), prefix_len, dtype=torch.int32, device=dev)
+        self.dec_seqused = torch.full((1,), prefix_len + chunk_size, dtype=torch.int32, device=dev)
         # one cache per batch element: (layers, batch, prefix + chunk, 256)
         self.k_cache = torch.zeros(layers, batch, self.kv_rows, DEC_NKV * DEC_HD, dtype=BF16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
@@ -473,6 +501,21 @@ class Pi05DecoderB200:
         assert prefix_k.shape == (self.layers, self.batch, self.prefix_len, DEC_NKV * DEC_HD), prefix_k.shape
         self.k_cache[:, :, :self.prefix_len].copy_(prefix_k.to(BF16))
         self.v_cache[:, :, :self.prefix_len].copy_(prefix_v.to(BF16))
+        torch.cuda.synchronize(self.device)
+
+    def set_valid_prefix_len(self, valid: int) -> None:
+        """Fixed-shape mode: the first ``valid`` rows of the prefix are real, the rest padding.  Updates the three
+        device-side values the captured graph reads -- KV append row, number of keys the attention sees, RoPE rows
+        of the action tokens -- without re-capturing (``set_valid_prefix_len``,
+        flash_rt/hardware/rtx/attn_backend.py:519-537)."""
+        if not self.fixed_shape:
+            raise RuntimeError("set_valid_prefix_len needs fixed_shape=True")
+        if not 0 <= valid <= self.prefix_len:
+            raise ValueError(f"valid prefix length {valid} outside [0, {self.prefix_len}]")
+        self.valid_prefix_len = int(valid)
+        self.dec_devpos.fill_(valid)
+        self.dec_seqused.fill_(valid + self.chunk_size)
+        self.rope.copy_(rope_table(valid, self.chunk_size).to(self.device))
         torch.cuda.synchronize(self.device)
 
     def set_prefix_pair(self, cond_k, cond_v, uncond_k, uncond_v) -> None:

@@ -96,14 +96,7 @@ class Pi05DecoderNvfp4Pipeline(StepIO):
                  1 if pdl else 0, stream)
 
     def _attention(self, layer, stream, pdl):
-        fe = self.fe
-        B, S, T = fe.batch, fe.chunk_size, fe.prefix_len + fe.chunk_size
-        qs = (S * DEC_NH * DEC_HD, DEC_NH * DEC_HD, DEC_HD)
-        ks = (fe.kv_rows * DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD)
-        fa2.fwd_bf16(self.q.data_ptr(), fe.k_cache[layer].data_ptr(), fe.v_cache[layer].data_ptr(),
-                     self.attn.data_ptr(), 0, self.lse_accum.data_ptr(), self.o_accum.data_ptr(), B, S, T, DEC_NH,
-                     DEC_NKV, DEC_HD, qs, ks, ks, qs, 1.0 / math.sqrt(DEC_HD), fe.sm_count, stream, pdl=pdl,
-                     kv_static_rows=fe.prefix_len, kv_splits=self.attn_splits, counters=self.attn_counters.data_ptr())
+        self._attend(layer, stream, pdl)
 
     def transformer_decoder(self, stream: int = 0, calibrate: bool = False, step_hook=None) -> None:
         """Run the N-step denoise on ``self.noise`` in place (pipeline_thor.py:355-490)."""
@@ -117,21 +110,18 @@ class Pi05DecoderNvfp4Pipeline(StepIO):
                     self._norm(None, None, "attn", step, i, stream, pdl)
                 w = fe.w4[i]
                 if B == 1 and fe.fuse_epilogues:
+                    kp, vp, dp = self._kv_dst(i, 0)
                     rc = fp4.cutlass_fp4_gemm_rope_split(
                         self.act4.data_ptr(), self.act4_sf.data_ptr(), w["qkv"].packed.data_ptr(),
-                        w["qkv"].sf.data_ptr(), fe.rope.data_ptr(), self.q.data_ptr(),
-                        fe.k_cache[i, 0, fe.prefix_len:].data_ptr(), fe.v_cache[i, 0, fe.prefix_len:].data_ptr(), M,
-                        DEC_D, DEC_NH * DEC_HD, DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, alpha=w["qkv"].g,
-                        stream=stream, pdl=pdl)
+                        w["qkv"].sf.data_ptr(), fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, M,
+                        DEC_D, DEC_NH * DEC_HD, DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, devpos=dp,
+                        alpha=w["qkv"].g, stream=stream, pdl=pdl)
                     if rc != 0:
                         raise fvk.KernelError(f"NVFP4 QKV GEMM failed: status {rc}")
                 else:
                     self._gemm(self.act4, self.act4_sf, w["qkv"], self.qkv, stream, pdl)
                     for b in range(B):
-                        fvk.qkv_split_rope(self.qkv[b * S:].data_ptr(), fe.rope.data_ptr(),
-                                           self.q[b * S:].data_ptr(), fe.k_cache[i, b, fe.prefix_len:].data_ptr(),
-                                           fe.v_cache[i, b, fe.prefix_len:].data_ptr(), S, DEC_NH * DEC_HD,
-                                           DEC_NKV * DEC_HD, DEC_NKV * DEC_HD, DEC_HD, stream, pdl=pdl and b == 0)
+                        self._split_rope(i, b, self.qkv[b * S:], self.q[b * S:], S, stream, pdl and b == 0)
                 self._attention(i, stream, pdl)
                 rc = fp4.quantize_fp4_dynamic_sfa_bf16_vec(self.attn.data_ptr(), self.ctx4.data_ptr(),
                                                            self.ctx4_sf.data_ptr(), M, DEC_NH * DEC_HD, False, stream,

@@ -113,3 +113,40 @@ def test_checkpoint_file_and_calibration_cache_end_to_end(tmp_path):
     m.set_prefix(pk[:, :128], pv[:, :128])
     m.calibrate(cal, use_cache=True, cache_dir=str(tmp_path / "cache"))
     assert m.frontend.calibration_source == "measured"
+
+
+@pytest.mark.parametrize("precision", ["fp8", "nvfp4"])
+def test_fixed_shape_graph_serves_every_prefix_length(precision):
+    """One captured graph at the largest prefix (768); the valid length is a device-side value (KV append row,
+    keys seen by the attention, RoPE rows).  For each valid length the result matches a model built for exactly
+    that prefix length, and switching lengths needs no re-capture."""
+    from flashrt_b200 import load_model
+    from flashrt_b200.pi05_decoder import synthetic_state_dict
+    L = 2
+    sd = synthetic_state_dict(seed=0, layers=L)
+    pk, pv = R.synthetic_prefix_kv(seed=1, layers=L, prefix_len=768)
+    cal = [R.synthetic_noise(100 + j) for j in range(3)]
+    noise = R.synthetic_noise(1).numpy()
+    kw = dict(config="pi05", layers=L, num_steps=5, chunk_size=50, precision=precision)
+    fixed = load_model(sd, prefix_len=768, fixed_shape=True, **kw)
+    fe = fixed.frontend
+    fixed.set_prefix(pk, pv)
+    fe.set_valid_prefix_len(500)
+    fixed.calibrate(cal)
+    graphs = []
+    for valid in (500, 768, 113, 500):
+        fe.set_valid_prefix_len(valid)
+        got = fixed.predict(noise=noise)
+        graphs.append(fe.graph)
+        exact = load_model(sd, prefix_len=valid, **kw)
+        exact.set_prefix(pk[:, :valid], pv[:, :valid])
+        if precision == "fp8":      # same static scales, so that only the kernel path differs
+            exact.frontend.pipeline.act_scale.copy_(fe.pipeline.act_scale)
+            exact.frontend.pipeline.calibrated = True
+        ref = exact.predict(noise=noise)
+        assert _cos(torch.from_numpy(got), torch.from_numpy(ref)) >= 0.9999, valid
+        bar = 2e-2 if precision == "fp8" else 5e-2          # 4-bit codes may flip on last-bit differences
+        assert np.abs(got - ref).max() <= bar * float(np.sqrt((ref ** 2).mean())), valid
+    assert all(g is graphs[0] for g in graphs)          # never re-captured
+    from flashrt_b200 import flash_rt_fa2 as fa2
+    assert fa2.attention_status() == 0
