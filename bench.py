@@ -489,6 +489,70 @@ def run_ops(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+def run_prefix(args):
+    """The step in front of the denoise path: 18 Gemma-2B encoder layers (FP8) turning a 768-token prefix into the
+    per-layer K / V of the action expert.  One "step" = one encode() of the whole prefix."""
+    import torch
+    from flashrt_b200.pi05_prefix import ENC_D, ENC_H, ENC_L, Pi05PrefixEncoderB200, QKV_N
+    torch.cuda.set_device(0)
+    seq, L = 768, ENC_L
+    enc = Pi05PrefixEncoderB200("synthetic:0", layers=L, max_seq=seq)
+    g = torch.Generator().manual_seed(3)
+    embeds = torch.randn(seq, ENC_D, generator=g).to(torch.bfloat16)
+    enc.calibrate([embeds])
+    k = torch.zeros(L, seq + 50, 256, dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros_like(k)
+    emb_dev = embeds.cuda()
+    st = enc.stream
+    for _ in range(max(args.warmup, 3)):
+        enc.encode(emb_dev, k, v)
+    sampler = ClockSampler(0)
+    sampler.start()
+    steps = max(1, min(args.steps, 50))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st):
+        enc.x[:seq].copy_(emb_dev)
+        e0.record(st)
+        for _ in range(steps):
+            enc.transformer_encoder(seq, k, v, st.cuda_stream, False)
+        e1.record(st)
+    st.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    embeds_pin = embeds.pin_memory()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        enc.encode(embeds_pin, k, v)
+        probe = k[L - 1, seq - 1, :8].cpu()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    clocks = sampler.stop()
+    from flashrt_b200 import flash_rt_kernels as fvk
+    flop = (L - 1) * (2.0 * seq * ENC_D * (QKV_N + 2048 + 2 * ENC_H + ENC_H) + 4.0 * seq * seq * 2048) \
+        + 2.0 * seq * ENC_D * QKV_N
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            bf16_tf = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        bf16_tf = 1590.0
+    launches = (L - 1) * 9 + 3
+    line = {"metric": "prefix encoder ms (768 tokens, 18 Gemma-2B layers, FP8)", "value": round(ms, 4), "unit": "ms",
+            "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 GEMMs, bf16 attention",
+            "data": "synthetic",
+            "config": {"workload": "pi05 prefix producer: 768 x 2048 embeddings -> per-layer K/V (18 layers, FFN 16384)",
+                       "l2": "2.0 GB of FP8 weights per pass exceed L2", "tensor_core_status": fvk.tensor_core_status(),
+                       "finite": bool(torch.isfinite(probe.float()).all())},
+            "e2e": {"value": round(e2e_ms, 4), "unit": "ms", "h2d_bytes_per_step": int(embeds.numel() * 2),
+                    "d2h_bytes_per_step": 16},
+            "gpu_launches": launches * steps,
+            "roofline": {"bound": "tensor", "kernel": "whole pass (FP8 GEMMs at M = 768 + attention)",
+                         "achieved": round(flop / (ms * 1e-3) / 1e12, 1), "peak": 2 * bf16_tf, "unit": "TFLOP/s",
+                         "frac": round(flop / (ms * 1e-3) / 1e12 / (2 * bf16_tf), 4), "traffic": None,
+                         "peak_source": "2 x measured bf16 burst (MEASURED_PEAKS.json)"},
+            "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -501,7 +565,7 @@ def main():
                          "(Nsight Compute cannot profile programmatically dependent launches)")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
-    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops"],
+    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops", "prefix"],
                     help="pi05 = the headline action-expert loop (default); wan = the video-DiT step (configs[4]); "
                          "ops = the operator sweep of configs[1] (norm / FP8 GEMM / NVFP4 GEMM)")
     ap.add_argument("--precision", default="fp8", choices=["fp8", "nvfp4"],
@@ -514,6 +578,9 @@ def main():
         return
     if args.workload == "ops" and args.impl != "reference":
         run_ops(args)
+        return
+    if args.workload == "prefix" and args.impl != "reference":
+        run_prefix(args)
         return
     if args.impl == "reference":
         run_reference(args)

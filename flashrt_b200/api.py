@@ -34,6 +34,20 @@ class VLAModel:
     def set_prefix(self, prefix_k, prefix_v) -> None:
         self._fe.set_prefix(prefix_k, prefix_v)
 
+    def set_prefix_from_encoder(self, encoder, embeds, slot: int = 0) -> int:
+        """Run the prefix producer (``flashrt_b200.pi05_prefix.Pi05PrefixEncoderB200``) on ``embeds`` (seq, 2048) and
+        let it write the per-layer keys / values straight into this model's cache rows [0, seq) of batch ``slot``
+        -- the part of the reference's ``set_prompt`` + encoder forward that precedes the denoise loop."""
+        fe = self._fe
+        if encoder.layers != fe.layers:
+            raise ValueError(f"encoder has {encoder.layers} layers, the action expert {fe.layers}")
+        seq = encoder.encode(embeds, fe.k_cache[:, slot], fe.v_cache[:, slot])
+        if seq != fe.prefix_len and not getattr(fe, "fixed_shape", False):
+            raise ValueError(f"prefix of {seq} tokens, model built for {fe.prefix_len} (use fixed_shape=True)")
+        if getattr(fe, "fixed_shape", False):
+            fe.set_valid_prefix_len(seq)
+        return seq
+
     def calibrate(self, noises, percentile: float | None = None, **kw) -> None:
         self._fe.calibrate(noises, percentile=percentile, **kw)
 

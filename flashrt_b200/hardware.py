@@ -15,6 +15,7 @@ ARCH_B200 = "b200_sm100"
 _PIPELINE_MAP: dict[tuple[str, str, str], tuple[str, str]] = {
     ("pi05", "torch", ARCH_B200): ("flashrt_b200.pi05_decoder", "Pi05DecoderB200"),
     ("pi05_decoder", "torch", ARCH_B200): ("flashrt_b200.pi05_decoder", "Pi05DecoderB200"),
+    ("pi05_prefix_encoder", "torch", ARCH_B200): ("flashrt_b200.pi05_prefix", "Pi05PrefixEncoderB200"),
 }
 
 

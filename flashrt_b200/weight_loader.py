@@ -130,6 +130,19 @@ class FusedQKV:
 
 
 @dataclass
+class FoldNorm:
+    """Wrap a (composite) weight key: multiply every input column of the (out, in) weight by ``1 + norm_weight``,
+    in fp32, so that the RMSNorm in front of the projection runs with unit weight (pi05_rtx.py:180-206; folding in
+    bf16 would round 1 + w to 0 for weights near -1)."""
+    inner: Any
+    norm: str
+
+    def resolve(self, source, ctx: LoaderContext) -> torch.Tensor:
+        w = self.inner.resolve(source, ctx) if hasattr(self.inner, "resolve") else source.get(ctx.subkey(self.inner))
+        return w.float() * (1.0 + source.get(ctx.subkey(self.norm)).float()).unsqueeze(0)
+
+
+@dataclass
 class FusedGateUp:
     """gate | up projection weights, each (out, in), concatenated along ``out`` (merged [gate | up] layout)."""
     gate: str
