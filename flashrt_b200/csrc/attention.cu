@@ -624,6 +624,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 #include "attention_pair.cuh"
+#include "attention_d256.cuh"
 
 template <int D, int BKV>
 static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
@@ -751,6 +752,15 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
     const bool pdl = flags & 1;
     const int tiles = ((seqlen_q * G + 127) / 128) * num_heads_kv * batch;
     if (head_dim == 256) {
+        // pipelined kernel (64-key chunks, double-buffered K/V and S, P in tensor memory): whenever the splits combine
+        // through the caller's scratch, or there is nothing to combine; flags bit 1 keeps the single-tile kernel
+        if (!(flags & 2)) {
+            const int chunks64 = (seqlen_k + 63) / 64;
+            int sp64 = kv_splits > 0 ? kv_splits : (tiles >= 74 ? 1 : (chunks64 < 8 ? chunks64 : 8));
+            if (sp64 > 8) sp64 = 8;
+            if (p.o_accum || sp64 == 1)
+                return launch_attn_d256(Q, K, V, p, q_strides, k_strides, v_strides, p.o_accum ? sp64 : 1, pdl, s);
+        }
         constexpr int BKV = 112;
         int chunks = (seqlen_k + BKV - 1) / BKV;
         int sp = kv_splits > 0 ? kv_splits : (tiles >= 74 ? 1 : (chunks < 8 ? chunks : 8));

@@ -1,0 +1,487 @@
+// Pipelined flash attention for head_dim 256 (the action expert's MQA cross-attention), sm_100a.
+//
+// Included by attention.cu inside namespace frt (AttnParams, tensor-map helpers, ATTN_WAIT).
+//
+// The single-tile kernel keeps one K and one V chunk of 112 keys in shared memory (Q + K + V + P fill it), so every
+// chunk pays a full TMA round trip before its MMAs: measured 4.5 us per additional chunk.  Here
+//   * chunks are 64 keys, K/V are double-buffered (Q 64 KB + 2 x (32 + 32) KB), the producer runs two chunks ahead;
+//   * S is double-buffered in TMEM (2 x 64 columns) so QK(j+1) is issued before the softmax of chunk j has finished;
+//   * P (bf16) overlays its S buffer and feeds the PV MMA as the A operand from TMEM -- no shared-memory round trip;
+//   * the row of S lives in registers (one tcgen05.wait per chunk); O is rescaled only when a row maximum grows by
+//     more than 2^8.
+// KV splits: none (gridDim.z = 1, result written directly) or through the caller's scratch (same layout, arrival
+// counters and combine as the single-tile kernel's scratch path).  Warps: 0-3 softmax (thread = row), 4 TMA, 5 MMA.
+#pragma once
+
+struct D256Cfg {
+    static constexpr int D = 256, BKV = 64;
+    static constexpr int Q_BYTES = 128 * D * 2;            // 64 KB
+    static constexpr int KV_BYTES = BKV * D * 2;           // 32 KB, one of K or V, one stage
+    static constexpr int OFF_K = Q_BYTES;
+    static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+    static constexpr int DATA_BYTES = OFF_V + 2 * KV_BYTES;   // 192 KB >= the 128 KB partial staged for the combine
+    static constexpr int ML_BYTES = 128 * 4;
+    static constexpr int SMEM_BYTES = DATA_BYTES + ML_BYTES + 256 + 1024;
+    static constexpr int S_COL = 0;                        // two S buffers of 64 columns
+    static constexpr int O_COL = 128;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr float RESCALE_THRESHOLD = 8.0f;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+    using Cfg = D256Cfg;
+    constexpr int D = Cfg::D, BKV = Cfg::BKV;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + Cfg::OFF_K;
+    uint8_t* sV = smem + Cfg::OFF_V;
+    float* red = reinterpret_cast<float*>(smem);                       // aliases the operand tiles after the last MMA
+    float* s_lse = reinterpret_cast<float*>(smem + Cfg::DATA_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::DATA_BYTES + Cfg::ML_BYTES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;      // [2]
+    uint64_t* v_full = bars + 3;      // [2]
+    uint64_t* kv_empty = bars + 5;    // [2]
+    uint64_t* s_full = bars + 7;      // [2] one per S buffer
+    uint64_t* p_ready = bars + 9;     // [2] 128 arrivals per chunk, one barrier per S / P buffer
+    uint64_t* o_full = bars + 11;     // PV of a chunk has completed (read only where the count is known to within one)
+    uint64_t* o_done = bars + 12;     // every PV of this CTA has completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const bool via_scratch = p.o_accum != nullptr;
+    const uint32_t C = gridDim.z;
+    const uint32_t rank = blockIdx.z;
+    const int tile = blockIdx.x;
+    const int hk = blockIdx.y % p.Hkv;
+    const int b = blockIdx.y / p.Hkv;
+    const int tok0 = tile * (128 / p.G);
+    const int c_begin = (int)((long long)p.chunks_total * rank / C);
+    const int c_end = (int)((long long)p.chunks_total * (rank + 1) / C);
+    const int nchunks = c_end - c_begin;
+
+    if (threadIdx.x == 0) {
+        tc::mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(&k_full[i], 1);
+            tc::mbar_init(&v_full[i], 1);
+            tc::mbar_init(&kv_empty[i], 1);
+            tc::mbar_init(&s_full[i], 1);
+        }
+        tc::mbar_init(&p_ready[0], 128);
+        tc::mbar_init(&p_ready[1], 128);
+        tc::mbar_init(o_full, 1);
+        tc::mbar_init(o_done, 1);
+        *abort_flag = 0;
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&tmQ);
+        tc::tma_prefetch_desc(&tmK);
+        tc::tma_prefetch_desc(&tmV);
+    }
+    if (warp == 5) {
+        tc::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    pdl_launch_dependents();
+
+    if (warp == 4 && lane == 0) {
+        // ---------------- TMA producer
+        auto load_kv = [&](int j) {
+            const int st = j & 1;
+            const int key0 = (c_begin + j) * BKV;
+            tc::mbar_arrive_expect_tx(&k_full[st], Cfg::KV_BYTES);
+            for (int db = 0; db < 4; ++db)
+                tc::tma_load_4d(sK + st * Cfg::KV_BYTES + db * (BKV * 128), &tmK, &k_full[st], db * 64, hk, key0, b);
+            tc::mbar_arrive_expect_tx(&v_full[st], Cfg::KV_BYTES);
+            for (int db = 0; db < 4; ++db)
+                tc::tma_load_4d(sV + st * Cfg::KV_BYTES + db * (BKV * 128), &tmV, &v_full[st], db * 64, hk, key0, b);
+        };
+        // chunks that lie inside the rows the previous kernel does not write may be fetched while it still runs
+        int early = 0;
+        while (early < 2 && early < nchunks && (c_begin + early + 1) * BKV <= p.kv_static_rows) {
+            load_kv(early);
+            ++early;
+        }
+        pdl_wait();
+        tc::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+        for (int db = 0; db < 4; ++db)
+            tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, q_full, db * 64, 0, hk, tok0, b);
+        for (int j = early; j < nchunks && !*abort_flag; ++j) {
+            if (j >= 2) ATTN_WAIT(&kv_empty[j & 1], (uint32_t)(((j >> 1) - 1) & 1), AERR_PRODUCER);
+            if (*abort_flag) break;
+            load_kv(j);
+        }
+    } else if (warp == 5 && lane == 0) {
+        // ---------------- MMA issuer
+        constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);
+        constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, D);     // A = P from TMEM, B = V MN-major
+        const uint64_t dq_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ));
+        const uint64_t dk_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sK));
+        const uint64_t dv_base = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV), BKV * 128);
+        auto qk = [&](int j) {
+            const uint64_t dk = dk_base + (uint64_t)((j & 1) * (Cfg::KV_BYTES >> 4));
+            const uint32_t d_tm = tmem + Cfg::S_COL + (j & 1) * 64;
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k)
+                tc::mma_f16(d_tm, dq_base + (uint64_t)((k / 4) * ((128 * 128) >> 4) + 2 * (k % 4)),
+                            dk + (uint64_t)((k / 4) * ((BKV * 128) >> 4) + 2 * (k % 4)), idesc_s, k > 0 ? 1u : 0u);
+            tc::mma_commit(&s_full[j & 1]);
+        };
+        ATTN_WAIT(q_full, 0u, AERR_MMA);
+        if (nchunks > 0 && !*abort_flag) {
+            ATTN_WAIT(&k_full[0], 0u, AERR_MMA);
+            if (!*abort_flag) {
+                tc::tc_fence_after_sync();
+                qk(0);
+            }
+        }
+        for (int j = 0; j < nchunks && !*abort_flag; ++j) {
+            if (j + 1 < nchunks) {      // S of the next chunk goes to the other buffer while the softmax works on this one
+                ATTN_WAIT(&k_full[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1), AERR_MMA);
+                if (*abort_flag) break;
+                tc::tc_fence_after_sync();
+                qk(j + 1);
+            }
+            ATTN_WAIT(&p_ready[j & 1], (uint32_t)((j >> 1) & 1), AERR_MMA);
+            ATTN_WAIT(&v_full[j & 1], (uint32_t)((j >> 1) & 1), AERR_MMA);
+            if (*abort_flag) break;
+            tc::tc_fence_after_sync();
+            const uint64_t dv = dv_base + (uint64_t)((j & 1) * (Cfg::KV_BYTES >> 4));
+            const uint32_t a_tm = tmem + Cfg::S_COL + (j & 1) * 64;
+#pragma unroll
+            for (int k = 0; k < BKV / 16; ++k)
+                tc::mma_f16_ts(tmem + Cfg::O_COL, a_tm + 8 * k, dv + (uint64_t)(k * ((16 * 128) >> 4)), idesc_o,
+                               (j > 0 || k > 0) ? 1u : 0u);
+            tc::mma_commit(&kv_empty[j & 1]);
+            tc::mma_commit(o_full);
+        }
+        if (!*abort_flag) tc::mma_commit(o_done);
+    } else if (warp < 4) {
+        // ---------------- softmax: thread = row
+        pdl_wait();
+        int kv_len = p.Skv;
+        if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
+        const int row = warp * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        const uint32_t tmem_O = tmem + Cfg::O_COL + lane_off;
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool alive = true;
+        for (int j = 0; j < nchunks; ++j) {
+            ATTN_WAIT(&s_full[j & 1], (uint32_t)((j >> 1) & 1), AERR_SOFTMAX);
+            __syncwarp();
+            if (__any_sync(0xffffffffu, *abort_flag != 0)) { alive = false; break; }
+            tc::tc_fence_after_sync();
+            const uint32_t tmem_S = tmem + Cfg::S_COL + (j & 1) * 64 + lane_off;
+            const int valid = kv_len - (c_begin + j) * BKV;
+            uint32_t sv[BKV];
+            tc::tmem_ld32(tmem_S + 0, sv + 0);
+            tc::tmem_ld32(tmem_S + 32, sv + 32);
+            tc::tmem_ld_wait();
+            if (valid < BKV) {
+#pragma unroll
+                for (int i = 0; i < BKV; ++i)
+                    if (i >= valid) sv[i] = 0xff800000u;        // -inf
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < BKV; i += 4) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], __uint_as_float(sv[i + q]));
+            }
+            const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            const bool grow = mx_s > m_run + Cfg::RESCALE_THRESHOLD || (m_run == -INFINITY && mx_s > -INFINITY);
+            const float m_new = grow ? mx_s : m_run;
+            if (__any_sync(0xffffffffu, grow && j > 0)) {
+                // O holds the chunks up to j - 1: their PV must have completed before it is rescaled.  s_full(j) was
+                // committed after PV(j - 2), so o_full has completed j - 1 or j times here: the parity wait is exact
+                ATTN_WAIT(o_full, (uint32_t)((j - 1) & 1), AERR_SOFTMAX);
+                __syncwarp();
+                tc::tc_fence_after_sync();
+                const float alpha = grow ? tc::ex2_approx(m_run - m_new) : 1.0f;
+                l_run *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld32(tmem_O + c, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tc::tmem_st32(tmem_O + c, v);
+                }
+                tc::tmem_st_wait();
+            }
+            m_run = m_new;
+            const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < BKV; c += 32) {
+                uint32_t u[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float a = tc::ex2_approx(__fmaf_rn(__uint_as_float(sv[c + 2 * i]), p.scale_log2, -m_use));
+                    const float bb = tc::ex2_approx(__fmaf_rn(__uint_as_float(sv[c + 2 * i + 1]), p.scale_log2, -m_use));
+                    sum4[i & 3] += a + bb;
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u[i]) : "f"(bb), "f"(a));   // low half = first key
+                }
+                tc::tmem_st16(tmem_S + (c >> 1), u);
+            }
+            tc::tmem_st_wait();
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&p_ready[j & 1]);
+        }
+        // ---------------- the accumulated O of this split (o_full may be two completions behind here: use o_done)
+        if (alive) {
+            if (nchunks > 0) ATTN_WAIT(o_done, 0u, AERR_SOFTMAX);
+            __syncwarp();
+            alive = !__any_sync(0xffffffffu, *abort_flag != 0);
+        }
+        if (alive) {
+            tc::tc_fence_after_sync();
+            const float invl = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            if (via_scratch) {
+                // O / l (log2-domain lse alongside) -> shared memory, rows with xor-swizzled 16-byte chunks; the whole
+                // CTA then copies full rows to the global scratch with coalesced stores
+                s_lse[row] = l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    if (nchunks > 0) {
+                        tc::tmem_ld32(tmem_O + c, v);
+                        tc::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0u;
+                    }
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const int ch = (c >> 2) + j4;
+                        *reinterpret_cast<float4*>(&red[(size_t)row * D + ((ch ^ (row & 7)) << 2)]) =
+                            make_float4(__uint_as_float(v[j4 * 4]) * invl, __uint_as_float(v[j4 * 4 + 1]) * invl,
+                                        __uint_as_float(v[j4 * 4 + 2]) * invl, __uint_as_float(v[j4 * 4 + 3]) * invl);
+                    }
+                }
+            } else {
+                // single split: the result leaves directly, one row per thread
+                const int tok = tok0 + row / p.G;
+                const int hq = hk * p.G + row % p.G;
+                const bool store = tok < p.Sq;
+                const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+                const size_t obase = (size_t)b * p.o_bs + (size_t)(store ? tok : 0) * p.o_rs + (size_t)hq * p.o_hs;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    if (nchunks > 0) {
+                        tc::tmem_ld32(tmem_O + c, v);
+                        tc::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0u;
+                    }
+                    if (store) {
+#pragma unroll
+                        for (int i8 = 0; i8 < 4; ++i8) {
+                            uint4 o;
+                            uint32_t* ow = &o.x;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                ow[i] = pack_bf16x2(__uint_as_float(v[i8 * 8 + 2 * i]) * invl,
+                                                    __uint_as_float(v[i8 * 8 + 2 * i + 1]) * invl);
+                            st_global_v4(p.O + obase + c + i8 * 8, o);
+                            if (p.O_fp8) {
+                                float q[8];
+                                unpack_bf16x2(o.x, q[0], q[1]);
+                                unpack_bf16x2(o.y, q[2], q[3]);
+                                unpack_bf16x2(o.z, q[4], q[5]);
+                                unpack_bf16x2(o.w, q[6], q[7]);
+                                uint2 o8;
+                                o8.x = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[0], inv_os)), clamp448(__fmul_rn(q[1], inv_os)),
+                                                       clamp448(__fmul_rn(q[2], inv_os)), clamp448(__fmul_rn(q[3], inv_os)));
+                                o8.y = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[4], inv_os)), clamp448(__fmul_rn(q[5], inv_os)),
+                                                       clamp448(__fmul_rn(q[6], inv_os)), clamp448(__fmul_rn(q[7], inv_os)));
+                                st_global_v2(p.O_fp8 + obase + c + i8 * 8, o8);
+                            }
+                        }
+                    }
+                }
+                if (store && p.lse)
+                    p.lse[((size_t)b * p.Hq + hq) * p.Sq + tok] =
+                        (l_run > 0.0f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+            }
+        }
+    }
+    __syncwarp();
+    if (via_scratch) {
+        // ---------------- combine through global scratch: every CTA of the tile publishes its partial, waits
+        // (bounded) for all C of them and finishes D / C columns of every row; all global accesses coalesced
+        const unsigned tile_id = (unsigned)((b * p.Hkv + hk) * gridDim.x + tile);
+        unsigned* cnt = p.counters + 2 * tile_id;
+        const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;
+        const int dper = D / (int)C;
+        __syncthreads();
+        const int gshift = 31 - __clz(p.G);
+        int rows_valid = (p.Sq - tok0) << gshift;
+        rows_valid = rows_valid > 128 ? 128 : rows_valid;
+        if (!*abort_flag) {
+#pragma unroll 4
+            for (int r = warp; r < rows_valid; r += 6) {
+                const int t = tok0 + (r >> gshift);
+                const int hq = hk * p.G + (r & (p.G - 1));
+                const size_t ridx = rank * split_stride + ((size_t)b * p.Hq + hq) * p.Sq + t;
+                float4* dst = reinterpret_cast<float4*>(p.o_accum + ridx * D);
+#pragma unroll
+                for (int ch = lane; ch < D / 4; ch += 32)
+                    __stcg(dst + ch, *reinterpret_cast<const float4*>(&red[(size_t)r * D + ((ch ^ (r & 7)) << 2)]));
+                if (lane == 0) __stcg(p.lse_accum + ridx, s_lse[r]);
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            atomicAdd(cnt, 1u);
+            bool ok = false;
+            for (uint32_t it = 0;; ++it) {
+                unsigned seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
+                if (seen >= C) { ok = true; break; }
+                if (*abort_flag) break;
+                if ((it & 15) == 15 && tc::global_timer_ns() > deadline) break;
+                __nanosleep(20);
+            }
+            if (!ok) {
+                if (!*abort_flag) atomicCAS(&g_attn_status, 0, AERR_SOFTMAX | (blockIdx.x << 8));
+                *abort_flag = 1;
+            }
+        }
+        __syncthreads();
+        if (!*abort_flag) {
+            const int cpr = dper >> 2;
+            const int d0 = (int)rank * dper;
+            const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+            const int cshift = 31 - __clz(cpr);
+#pragma unroll 2
+            for (int idx = threadIdx.x; idx < rows_valid * cpr; idx += 192) {
+                const int r = idx >> cshift, ch = idx & (cpr - 1);
+                const int t = tok0 + (r >> gshift);
+                const int hq = hk * p.G + (r & (p.G - 1));
+                const size_t r0 = ((size_t)b * p.Hq + hq) * p.Sq + t;
+                float w[8];
+                float4 x[8];
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    if ((uint32_t)sidx < C) {
+                        w[sidx] = __ldcg(p.lse_accum + sidx * split_stride + r0);
+                        x[sidx] = __ldcg(reinterpret_cast<const float4*>(p.o_accum + (sidx * split_stride + r0) * D + d0) + ch);
+                    } else {
+                        w[sidx] = -INFINITY;
+                        x[sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                float M = -INFINITY;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) M = fmaxf(M, w[sidx]);
+                float Lw = 0.0f;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    w[sidx] = (w[sidx] == -INFINITY) ? 0.0f : tc::ex2_approx(w[sidx] - M);
+                    Lw += w[sidx];
+                }
+                const float invL = Lw > 0.0f ? 1.0f / Lw : 0.0f;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    const float ws = w[sidx] * invL;
+                    a0 += ws * x[sidx].x; a1 += ws * x[sidx].y; a2 += ws * x[sidx].z; a3 += ws * x[sidx].w;
+                }
+                const size_t o = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs + d0 + ch * 4;
+                uint2 ob;
+                ob.x = pack_bf16x2(a0, a1);
+                ob.y = pack_bf16x2(a2, a3);
+                st_global_v2(p.O + o, ob);
+                if (p.O_fp8) {
+                    float q0, q1, q2, q3;
+                    unpack_bf16x2(ob.x, q0, q1);
+                    unpack_bf16x2(ob.y, q2, q3);
+                    *reinterpret_cast<uint32_t*>(p.O_fp8 + o) =
+                        f32x4_to_e4m3x4(clamp448(__fmul_rn(q0, inv_os)), clamp448(__fmul_rn(q1, inv_os)),
+                                        clamp448(__fmul_rn(q2, inv_os)), clamp448(__fmul_rn(q3, inv_os)));
+                }
+                if (p.lse && rank == 0 && ch == 0)
+                    p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned done = atomicAdd(cnt + 1, 1u);
+            if (done == C - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+}
+
+static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
+                            const long long* ks, const long long* vs, int splits, bool pdl, cudaStream_t stream) {
+    using Cfg = D256Cfg;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        attr_done = true;
+    }
+    CUtensorMap tmQ, tmK, tmV;
+    {
+        uint64_t dims[5] = {(uint64_t)Cfg::D, (uint64_t)p.G, (uint64_t)p.Hkv, (uint64_t)p.Sq, (uint64_t)p.B};
+        uint64_t str[4] = {(uint64_t)qs[2] * 2, (uint64_t)qs[2] * 2 * p.G, (uint64_t)qs[1] * 2, (uint64_t)qs[0] * 2};
+        uint32_t box[5] = {64, (uint32_t)p.G, 1, (uint32_t)(128 / p.G), 1};
+        int rc = make_tmap_bf16(&tmQ, Q, 5, dims, str, box);
+        if (rc) return rc;
+    }
+    {
+        uint64_t dims[4] = {(uint64_t)Cfg::D, (uint64_t)p.Hkv, (uint64_t)p.Skv, (uint64_t)p.B};
+        uint64_t strk[3] = {(uint64_t)ks[2] * 2, (uint64_t)ks[1] * 2, (uint64_t)ks[0] * 2};
+        uint64_t strv[3] = {(uint64_t)vs[2] * 2, (uint64_t)vs[1] * 2, (uint64_t)vs[0] * 2};
+        uint32_t box[4] = {64, 1, (uint32_t)Cfg::BKV, 1};
+        int rc = make_tmap_bf16(&tmK, K, 4, dims, strk, box);
+        if (rc) return rc;
+        rc = make_tmap_bf16(&tmV, V, 4, dims, strv, box);
+        if (rc) return rc;
+    }
+    p.chunks_total = (p.Skv + Cfg::BKV - 1) / Cfg::BKV;
+    if (splits > p.chunks_total) splits = p.chunks_total;
+    if (splits < 1) splits = 1;
+    while (splits & (splits - 1)) --splits;            // power of two: each split finishes D / splits columns
+    if (splits == 1) p.o_accum = nullptr;
+    const int tiles = (p.Sq * p.G + 127) / 128;
+    if (p.o_accum) {
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if ((long long)tiles * p.Hkv * p.B * splits > sms) return FRT_ERR_UNSUPPORTED;   // the CTAs of a tile wait for one another
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, p.Hkv * p.B, splits);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_d256_kernel, tmQ, tmK, tmV, p);
+    return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
+}

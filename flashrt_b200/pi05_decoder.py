@@ -280,7 +280,7 @@ class Pi05DecoderPipeline(StepIO):
         self.hid8 = z(S, DEC_H, dtype=torch.uint8)
         self.ones = torch.ones(DEC_D, dtype=BF16, device=dev)
         # split-KV scratch of the attention kernel (the reference's FA2 o_accum / softmax_lse_accum buffers)
-        self.attn_splits = 8
+        self.attn_splits = fe.attn_splits
         self.o_accum = z(self.attn_splits, S, DEC_NH, DEC_HD, dtype=torch.float32)
         self.lse_accum = z(self.attn_splits, DEC_NH, S, dtype=torch.float32)
         self.attn_counters = z(2 * fe.batch * ((fe.chunk_size * DEC_NH + 127) // 128), dtype=torch.int32)
@@ -416,7 +416,7 @@ class Pi05DecoderB200:
     def __init__(self, checkpoint, *, num_steps: int = NUM_STEPS_DEFAULT, chunk_size: int = CHUNK_DEFAULT,
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
-                 cfg_beta: float | None = None, fixed_shape: bool = False, **_ignored):
+                 cfg_beta: float | None = None, fixed_shape: bool = False, attn_splits: int = 8, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -434,6 +434,7 @@ class Pi05DecoderB200:
         self.cfg_beta = None if cfg_beta is None else float(cfg_beta)
         # fixed-shape mode: prefix_len is the LARGEST prefix; the valid length is a device-side value
         self.fixed_shape = bool(fixed_shape)
+        self.attn_splits = int(attn_splits)      # kv splits of the decoder attention (combined through scratch)
         self.valid_prefix_len = prefix_len
         if batch < 1 or batch * ((chunk_size * DEC_NH + 127) // 128) * 8 > self.sm_count:
             raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")

@@ -69,7 +69,7 @@ class Pi05DecoderNvfp4Pipeline(StepIO):
         self.ctx4, self.ctx4_sf = z(M, DEC_NH * DEC_HD // 2, dtype=torch.uint8), sfb(DEC_NH * DEC_HD)
         self.hid4, self.hid4_sf = z(M, DEC_H // 2, dtype=torch.uint8), sfb(DEC_H)
         self.ones = torch.ones(DEC_D, dtype=BF16, device=dev)
-        self.attn_splits = 8
+        self.attn_splits = fe.attn_splits
         self.o_accum = z(self.attn_splits, B, S, DEC_NH, DEC_HD, dtype=torch.float32)
         self.lse_accum = z(self.attn_splits, B, DEC_NH, S, dtype=torch.float32)
         self.attn_counters = z(2 * B * ((S * DEC_NH + 127) // 128), dtype=torch.int32)
