@@ -311,7 +311,7 @@ def run_wan(args):
     state = synthetic_wan_state(0, layers=1)
     grid, B, T = (13, 30, 52), 2, 512
     model = WanDiTB200(state, grid=grid, batch=B, text_len=T, device=local, tp_rank=rank, tp_size=world,
-                       repeat_blocks=layers)
+                       repeat_blocks=layers, overlap_chunks=args.wan_overlap_chunks)
     L, D = model.L, model.dim
     g = torch.Generator().manual_seed(1)
     x_host = torch.randn(B, L, D, generator=g).to(torch.bfloat16).pin_memory()
@@ -572,6 +572,8 @@ def main():
                     help="pi05 workload: fp8 = configs[2] (default, the headline), nvfp4 = configs[3]")
     ap.add_argument("--batch", type=int, default=1, help="pi05 workload with --precision nvfp4: chunks per loop (1 or 4)")
     ap.add_argument("--wan-layers", type=int, default=30)
+    ap.add_argument("--wan-overlap-chunks", type=int, default=int(os.environ.get("FRT_WAN_CHUNKS", "4")),
+                    help="wan workload under TP: pieces per row-parallel GEMM whose all-reduce overlaps the next piece")
     args = ap.parse_args()
     if args.workload == "wan" and args.impl != "reference":
         run_wan(args)

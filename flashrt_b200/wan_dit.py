@@ -98,7 +98,7 @@ SITES = ("qkv", "o", "cq", "co", "f1", "f2")
 class WanDiTB200:
     def __init__(self, state: dict, *, grid=(13, 30, 52), batch: int = 2, text_len: int = 512, device=0,
                  tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1,
-                 fuse_epilogues: bool = True):
+                 fuse_epilogues: bool = True, overlap_chunks: int = 4):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device)
@@ -166,6 +166,10 @@ class WanDiTB200:
         self.scratch = torch.zeros(1, dtype=torch.float32, device=dev)
         self.gemm = fvk.GemmRunner()
         self.fuse_epilogues = fuse_epilogues
+        # row-parallel GEMM + all-reduce: the rows are cut into this many pieces so that the all-reduce of piece c
+        # (NCCL, side stream) runs while the GEMM of piece c + 1 computes
+        self.overlap_chunks = max(1, int(overlap_chunks)) if tp_size > 1 else 1
+        self.comm_stream = torch.cuda.Stream(device=self.device) if tp_size > 1 else None
         self.calibrated = False
         self.launches_per_step = 0
 
@@ -181,6 +185,30 @@ class WanDiTB200:
         self.gemm.fp8_nt_dev(a8.data_ptr(), w8.data_ptr(), out.data_ptr(), M, N, K, scale_ptr, ws.data_ptr(), st,
                              bias=bias.data_ptr() if bias is not None else None)
         self.launches_per_step += 1
+
+    def _gemm_allreduce(self, a8, w8, ws, out, M, N, K, scale_ptr, st, bias=None):
+        """Row-parallel projection: out = sum over ranks of (a8 . w8^T [+ bias]).  With more than one rank the rows are
+        processed in pieces and each piece is all-reduced on the communication stream while the next one computes."""
+        C = self.overlap_chunks
+        if self.tp == 1 or C == 1 or M < getattr(self, "_min_chunk_rows", 256) * C:
+            self._gemm(a8, w8, ws, out, M, N, K, scale_ptr, st, bias=bias)
+            self._allreduce(out)
+            return
+        rows = ((M + C - 1) // C + 127) // 128 * 128
+        cur = torch.cuda.current_stream()
+        r0 = 0
+        while r0 < M:
+            r1 = min(M, r0 + rows)
+            self._gemm(a8[r0:r1], w8, ws, out[r0:r1], r1 - r0, N, K, scale_ptr, st, bias=bias)
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                torch.distributed.all_reduce(out[r0:r1], group=self.group)
+            r0 = r1
+        done = torch.cuda.Event()
+        done.record(self.comm_stream)
+        cur.wait_event(done)
 
     def _attn(self, q, k, v, out, out8, scale_ptr, Sq, Skv, kstr, vstr, st):
         hl, hd = self.hl, self.hd
@@ -261,8 +289,7 @@ class WanDiTB200:
                 self._quant(self.a, self.a8, i, "o", st, True)
             else:
                 self._attn(self.q, self.k, v_view, self.a, self.a8, self._sp(i, "o"), L, L, ks, kstr_self, st)
-            self._gemm(self.a8, b["o8"], b["o_s"], self.o, M, D, dl, self._sp(i, "o"), st, bias=b["o_b"])
-            self._allreduce(self.o)
+            self._gemm_allreduce(self.a8, b["o8"], b["o_s"], self.o, M, D, dl, self._sp(i, "o"), st, bias=b["o_b"])
             self._gated_residual(self.o, e_out[2], st)
             # ---- cross-attention to the text tokens
             if calibrate:
@@ -284,8 +311,8 @@ class WanDiTB200:
             else:
                 self._attn(self.cqn, self.ctx_k[i], self.ctx_v[i], self.a, self.a8, self._sp(i, "co"), L, self.T, kc,
                            kc, st)
-            self._gemm(self.a8, b["co8"], b["co_s"], self.o, M, D, dl, self._sp(i, "co"), st, bias=b["co_b"])
-            self._allreduce(self.o)
+            self._gemm_allreduce(self.a8, b["co8"], b["co_s"], self.o, M, D, dl, self._sp(i, "co"), st,
+                                 bias=b["co_b"])
             fvk.residual_add(self.x.data_ptr(), self.o.data_ptr(), M * D, st)
             # ---- FFN
             self._adaln(i, "f1", e_out[4], e_out[3], st, calibrate)
@@ -305,8 +332,7 @@ class WanDiTB200:
                                                    D, self._sp(i, "f1"), b["f1_s"].data_ptr(), b["f1_b"].data_ptr(),
                                                    self._sp(i, "f2"), st)
                 self.launches_per_step += 1
-            self._gemm(self.f8, b["f28"], b["f2_s"], self.o, M, D, fl, self._sp(i, "f2"), st, bias=b["f2_b"])
-            self._allreduce(self.o)
+            self._gemm_allreduce(self.f8, b["f28"], b["f2_s"], self.o, M, D, fl, self._sp(i, "f2"), st, bias=b["f2_b"])
             self._gated_residual(self.o, e_out[5], st)
         return self.x.reshape(B, L, D).clone()
 

@@ -23,7 +23,16 @@ def main():
     m.set_context(ctx)
     m.calibrate(x, tproj)
     got = m.step(x, tproj).float().cpu()
-    ok = True
+    # the chunked form (all-reduce of one row piece overlapping the GEMM of the next, on a side stream) must give
+    # the same bytes as the plain GEMM -> all-reduce: force pieces small enough for this reduced shape
+    m.overlap_chunks = 3
+    m._min_chunk_rows = 128
+    got_chunked = m.step(x, tproj).float().cpu()
+    m.overlap_chunks = 1
+    got_plain = m.step(x, tproj).float().cpu()
+    ok = bool(torch.equal(got_chunked, got_plain))
+    if not ok:
+        print(f"rank {rank}: chunked all-reduce differs from the plain one", flush=True)
     if rank == 0:
         ref = wan_ref.step(x, state, tproj, ctx, cos, sin)
         rms = float(ref.pow(2).mean().sqrt())
@@ -31,7 +40,7 @@ def main():
         cosv = float((got.double().flatten() @ ref.double().flatten()) / (got.double().norm() * ref.double().norm()))
         print(f"TP={world} cos={cosv:.6f} err_rms={float(err.pow(2).mean().sqrt()):.5f} max={float(err.max()):.4f}",
               flush=True)
-        ok = cosv >= 0.999 and float(err.pow(2).mean().sqrt()) <= 1e-2 * rms and float(err.max()) <= 0.1 * rms
+        ok = ok and cosv >= 0.999 and float(err.pow(2).mean().sqrt()) <= 1e-2 * rms and float(err.max()) <= 0.1 * rms
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
