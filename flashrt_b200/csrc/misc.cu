@@ -11,9 +11,9 @@
 namespace frt {
 
 // D(M,N) bf16 = A(M,K) . B(K,N) (+ bias(N)) (+ D when accumulate), bf16 operands, fp32 accumulate.
-// Block: 32 output columns x 8 K-slices, 4 output rows.  The projections this
+// Block: 32 output columns x 16 K-slices, 2 output rows.  The projections this
 // serves move < 100 KB; the shape of the grid only has to cover the machine.
-constexpr int SG_COLS = 32, SG_KS = 8, SG_ROWS = 4, SG_KCHUNK = 1024;
+constexpr int SG_COLS = 32, SG_KS = 16, SG_ROWS = 2, SG_KCHUNK = 1024;
 
 template <bool A_F32, bool D_F32>
 __global__ void __launch_bounds__(SG_COLS * SG_KS)
@@ -31,7 +31,7 @@ small_gemm_bf16_kernel(const void* __restrict__ Av, const __nv_bfloat16* __restr
     const int n = blockIdx.x * SG_COLS + tx;
     const int m0 = blockIdx.y * SG_ROWS;
     pdl_wait();
-    float acc[SG_ROWS] = {0.f, 0.f, 0.f, 0.f};
+    float acc[SG_ROWS] = {};
     for (int k0 = 0; k0 < K; k0 += SG_KCHUNK) {
         const int kc = K - k0 < SG_KCHUNK ? K - k0 : SG_KCHUNK;
         __syncthreads();
@@ -44,6 +44,8 @@ small_gemm_bf16_kernel(const void* __restrict__ Av, const __nv_bfloat16* __restr
         }
         __syncthreads();
         if (n < N) {
+            // the loads of B do not depend on one another: keep 16 of them in flight per thread
+#pragma unroll 16
             for (int k = ks; k < kc; k += SG_KS) {
                 const float b = __bfloat162float(B[(size_t)(k0 + k) * N + n]);
 #pragma unroll
