@@ -503,6 +503,9 @@ void orc_adaln_modulation6(const float* params, const float* layer_mod, uint16_t
  *             scale = RN-even E4M3 of max(amax / 6, 1e-12), inv = 1 / scale (IEEE: a zero scale gives inf and
  *             0 * inf = NaN, which falls through every '<=' test to code 7), thresholds compared with '<='
  *             (a tie goes to the smaller magnitude).
+ * Family 1 is pinned bit for bit against the reference's own torch NVFP4 reference (golden vectors generated by
+ * tests/golden/make_nvfp4_golden.py from its tests/test_fp4_integration_meta.py:31-57); family 0 has no CPU statement
+ * in the reference and is restated from the source text only.
  * Low nibble = even element.  An optional FP32 global scale g divides the input first (x * (1 / g)); the
  * reference's quantisers carry none (g = 1).  Divisions are IEEE here; the reference builds with fast-math. */
 

@@ -300,3 +300,20 @@ def test_nvfp4_gemm_oracle_shapes():
     assert D.shape == (5, 7)
     from_cos = float((D.ravel() @ ref.ravel()) / (np.linalg.norm(D) * np.linalg.norm(ref)))
     assert from_cos > 0.98
+
+
+def test_nvfp4_family1_matches_the_references_torch_reference():
+    """Golden vectors produced by the reference's own ``fake_nvfp4`` (tests/test_fp4_integration_meta.py, executed
+    unchanged by tests/golden/make_nvfp4_golden.py): quantise + dequantise of the family-1 restatement must equal
+    them bit for bit, including an all-zero block, ties on every e2m1 threshold and a block whose scale rounds to 0."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "nvfp4_fake_quant.npz"))
+    names = [k[3:] for k in z.files if k.startswith("in_")]
+    assert len(names) >= 4
+    for n in names:
+        x = np.ascontiguousarray(z["in_" + n], np.float32)
+        packed, sf = O.quantize_nvfp4(x, 1)
+        assert np.array_equal(O.dequantize_nvfp4(packed, sf), z["out_" + n]), n
+        # the same inputs as bf16 bit patterns (the device kernels' input type) give the same codes
+        p2, s2 = O.quantize_nvfp4(O.f32_to_bf16_bits(x), 1)
+        assert np.array_equal(p2, packed) and np.array_equal(s2, sf), n
