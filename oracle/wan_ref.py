@@ -1,9 +1,15 @@
 """TEST INFRASTRUCTURE ONLY — fp32 torch restatement (CPU) of a Wan2.2-shape video-DiT block.
 
-PARITY UNPINNED: the block arithmetic of the reference's Wan path lives in the external ``wan`` package
-(``wan.modules.model``, imported at flash_rt/frontends/torch/wan22_rtx.py:78-113), which is not vendored in the
-reference tree, carries no pinned version there and is not installed here; the reference's tests at that boundary
-are structural only.  This file restates the block from BASELINE configuration 4 and from the kernel call sites
+PINNING.  Building blocks: pinned against the reference's own catalog ground truth -- ``_rms`` + ``_rope``
+(full-width q/k RMSNorm, complex-pair RoPE) against ``qk_norm_rope_ref``, affine LayerNorm against
+``norm_fused_ref``, modulated affine-free LayerNorm -> projections against ``modnorm_qkv_chain_ref``, LN -> fc1 ->
+GELU(tanh) -> fc2 + x against ``vision_ffn_ref``, attention against ``attention_core_ref``
+(``flash_rt/structures/catalog/*/reference.py``; fixtures ``tests/golden/wan_parts.npz`` by
+``tests/golden/make_wan_golden.py``, checked in ``tests/test_oracle_cpu.py``).  Composition of the block (order of
+the sub-layers, which of the six modulation vectors goes where): PARITY UNPINNED -- that arithmetic lives in the
+external ``wan`` package (``wan.modules.model``, imported at flash_rt/frontends/torch/wan22_rtx.py:78-113), which
+is not vendored in the reference tree, carries no pinned version there and is not installed here; the reference's
+tests at that boundary are structural only.  The composition is restated from BASELINE configuration 4 and from the kernel call sites
 the reference does contain: the six-way modulation and its use (flash_rt/models/motus/_modulate_fuse_swap.py:1-33,
 csrc/kernels/elementwise.cu:603-645), the q/k RMSNorm over the full model width and the complex-pair 3-D RoPE
 (csrc/quantize/qkv_split_norm_rope_bf16.cuh:22-41), affine-free LayerNorm with eps 1e-6

@@ -317,3 +317,34 @@ def test_nvfp4_family1_matches_the_references_torch_reference():
         # the same inputs as bf16 bit patterns (the device kernels' input type) give the same codes
         p2, s2 = O.quantize_nvfp4(O.f32_to_bf16_bits(x), 1)
         assert np.array_equal(p2, packed) and np.array_equal(s2, sf), n
+
+
+def test_wan_ref_building_blocks_match_reference_catalog():
+    """The helpers the video-DiT restatement is made of agree with the reference's own catalog ground truth
+    (tests/golden/wan_parts.npz, generated by tests/golden/make_wan_golden.py): full-width q/k RMSNorm + complex-pair
+    RoPE (qk_norm_rope_ref, projection scope, interleaved layout), affine LayerNorm (norm_fused_ref), modulated
+    affine-free LayerNorm -> projections (modnorm_qkv_chain_ref), LN -> fc1 -> GELU(tanh) -> fc2 + x (vision_ffn_ref)."""
+    import importlib.util
+    import os
+    import torch
+    from oracle import wan_ref as W
+    here = os.path.dirname(__file__)
+    spec = importlib.util.spec_from_file_location("make_wan_golden", os.path.join(here, "golden", "make_wan_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    i = gen.inputs()
+    z = np.load(os.path.join(here, "golden", "wan_parts.npz"))
+    B, L, D, H, HD = gen.B, gen.L, gen.D, gen.H, gen.HD
+    close = lambda a, name: np.testing.assert_allclose(a.numpy(), z[name], rtol=2e-5, atol=2e-5, err_msg=name)  # noqa: E731
+    q = W._rope(W._rms(i["q"].reshape(B, L, D), i["wq_norm"]).reshape(B, L, H, HD), i["cos"], i["sin"])
+    k = W._rope(W._rms(i["k"].reshape(B, L, D), i["wk_norm"]).reshape(B, L, H, HD), i["cos"], i["sin"])
+    close(q, "qk_norm_rope_q")
+    close(k, "qk_norm_rope_k")
+    close(W._ln(i["x"]) * i["ln_w"] + i["ln_b"], "norm_fused")
+    scale, shift = torch.from_numpy(z["silu_cond_affine"]).chunk(2, dim=-1)
+    h = W._ln(i["x"]) * (1 + scale[:, None]) + shift[:, None]
+    close(h @ i["w_q"].t() + i["b_q"], "modnorm_q")
+    close(h @ i["w_k"].t() + i["b_k"], "modnorm_k")
+    close(h @ i["w_v"].t() + i["b_v"], "modnorm_v")
+    ff = torch.nn.functional.gelu(W._ln(i["x"]) @ i["w_fc1"].t() + i["b_fc1"], approximate="tanh")
+    close(i["x"] + (ff @ i["w_fc2"].t() + i["b_fc2"]), "vision_ffn")
