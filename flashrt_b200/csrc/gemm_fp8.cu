@@ -109,9 +109,16 @@ struct GemmParams {
     const uint8_t* sf_col;
     int sf_katoms;             //   atoms along K = K / 64
     int sf_col_rblocks;        //   128-row atom rows of the column operand's scale buffer
+    // EPI_GATE_RES_NORM_FP8: residual (M, N) bf16 in/out, gate (N,), style rows [scale (N) | shift (N)], next site's
+    // FP8 activations out8 (M, N) with out_scale; the cluster spans all N / 128 tiles so that the row statistics
+    // can be exchanged through distributed shared memory
+    __nv_bfloat16* resid;
+    const __nv_bfloat16* gate;
+    const __nv_bfloat16* style;
+    float eps;
 };
 
-enum { EPI_BF16 = 0, EPI_ROPE_SPLIT = 1, EPI_GEGLU_FP8 = 2 };
+enum { EPI_BF16 = 0, EPI_ROPE_SPLIT = 1, EPI_GEGLU_FP8 = 2, EPI_GATE_RES_NORM_FP8 = 3 };
 
 template <int BN, bool FP4 = false>
 struct GemmCfg {
@@ -197,8 +204,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     // first row of the lane operand; with the GeGLU epilogue a tile is 64 gate rows + the 64 matching up rows
     const int lane0 = (EPI == EPI_GEGLU_FP8) ? blockIdx.x * 64 : blockIdx.x * 128;
     const int col0 = blockIdx.y * BN;                // first row of the column operand
-    const uint32_t S = tc::cluster_nctarank();
-    const uint32_t rank = tc::cluster_ctarank();
+    // split-K ranks: the CTAs of a (1, 1, S) cluster, or -- with the fused norm -- the z extent of a (tiles, 1, S) one
+    const uint32_t S = (EPI == EPI_GATE_RES_NORM_FP8) ? gridDim.z : tc::cluster_nctarank();
+    const uint32_t rank = (EPI == EPI_GATE_RES_NORM_FP8) ? blockIdx.z : tc::cluster_ctarank();
     const int kb_begin = (int)((long long)p.kb_total * rank / S);
     const int kb_end = (int)((long long)p.kb_total * (rank + 1) / S);
     const int nkb = kb_end - kb_begin;
@@ -440,9 +448,118 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
             }
         }
         TRACE(5);
-        if (S > 1) tc::cluster_sync_all(); else __syncthreads();
+        if (S > 1 || EPI == EPI_GATE_RES_NORM_FP8) tc::cluster_sync_all(); else __syncthreads();
         TRACE(6);
-        if (!*abort_flag && SWAP) {
+        if constexpr (EPI == EPI_GATE_RES_NORM_FP8) {
+            // ---- split-K sum, gated residual update, RMS statistics over the whole row (all tiles of the cluster),
+            // adaRMS modulation and FP8 quantisation of the next GEMM's input.  Every thread reaches both barriers.
+            // Cluster rank of CTA (tile x, split z) = x + gridDim.x * z.  S is 1 or 2.
+            const uint32_t T = gridDim.x;                                  // tiles across the row = CTAs per split
+            const uint32_t red_addr = tc::smem_u32(red);
+            float* part = red + BN * 128;                                   // [token][16 groups] partial sums of squares
+            float* tok_ssq = part + BN * 16;                                // [token] this tile's sum of squares
+            const int cols_per = (BN + (int)S - 1) / (int)S;
+            const int cbeg = (int)rank * cols_per;
+            int cend = cbeg + cols_per < BN ? cbeg + cols_per : BN;
+            if (col0 + cend > p.M) cend = p.M - col0;
+            const int ntok = cend > cbeg ? cend - cbeg : 0;
+            const int items = ntok * 16;
+            const bool live = !*abort_flag;
+            if (live) {
+                const uint32_t other = S == 2 ? tc::dsmem_map(red_addr, blockIdx.x + T * (rank ^ 1u)) : red_addr;
+#pragma unroll 2
+                for (int it = threadIdx.x; it < items; it += 128) {
+                    const int c = cbeg + it / 16, g = it % 16;
+                    const int m = col0 + c, n = lane0 + g * 8;
+                    float* mine = &red[c * 128 + g * 8];
+                    float4 x0 = reinterpret_cast<const float4*>(mine)[0], x1 = reinterpret_cast<const float4*>(mine)[1];
+                    if (S == 2) {
+                        const float4 y0 = tc::dsmem_ld_f32x4(other + (uint32_t)(c * 128 + g * 8) * 4u);
+                        const float4 y1 = tc::dsmem_ld_f32x4(other + (uint32_t)(c * 128 + g * 8) * 4u + 16u);
+                        x0.x += y0.x; x0.y += y0.y; x0.z += y0.z; x0.w += y0.w;
+                        x1.x += y1.x; x1.y += y1.y; x1.z += y1.z; x1.w += y1.w;
+                    }
+                    const float a[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    const uint4 rv = ld_global_v4(p.resid + (size_t)m * p.N + n);
+                    const uint4 gv = ld_global_v4(p.gate + n);
+                    const uint32_t* rw = &rv.x;
+                    const uint32_t* gw = &gv.x;
+                    uint4 ob;
+                    uint32_t* ow = &ob.x;
+                    float ssq = 0.0f, rr[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float r0, r1, g0, g1;
+                        unpack_bf16x2(rw[k], r0, r1);
+                        unpack_bf16x2(gw[k], g0, g1);
+                        // the GEMM result is rounded to bf16 as the separate kernel stores it, then x += o * gate
+                        const float o0 = __bfloat162float(__float2bfloat16_rn(a[2 * k] * alpha));
+                        const float o1 = __bfloat162float(__float2bfloat16_rn(a[2 * k + 1] * alpha));
+                        r0 = __fmaf_rn(o0, g0, r0);
+                        r1 = __fmaf_rn(o1, g1, r1);
+                        ssq = __fmaf_rn(r0, r0, ssq);
+                        ssq = __fmaf_rn(r1, r1, ssq);
+                        ow[k] = pack_bf16x2(r0, r1);
+                        unpack_bf16x2(ow[k], rr[2 * k], rr[2 * k + 1]);          // the rounded value feeds the norm
+                    }
+                    st_global_v4(p.resid + (size_t)m * p.N + n, ob);
+                    reinterpret_cast<float4*>(mine)[0] = make_float4(rr[0], rr[1], rr[2], rr[3]);
+                    reinterpret_cast<float4*>(mine)[1] = make_float4(rr[4], rr[5], rr[6], rr[7]);
+                    part[(c - cbeg) * 16 + g] = ssq;
+                }
+            }
+            __syncthreads();
+            if (live && (int)threadIdx.x < ntok) {
+                float t = 0.0f;
+#pragma unroll
+                for (int g = 0; g < 16; ++g) t = __fadd_rn(t, part[threadIdx.x * 16 + g]);
+                tok_ssq[threadIdx.x] = t;
+            }
+            tc::cluster_sync_all();
+            // one thread per token gathers the row total from the tiles (all remote loads in flight together; a
+            // remote scalar round trip per work item would cost more than the separate norm kernel)
+            float* tok_rms = tok_ssq + BN;
+            if (live && (int)threadIdx.x < ntok) {
+                const uint32_t ssq_addr = tc::smem_u32(tok_ssq) + 4u * threadIdx.x;
+                float v[8];
+#pragma unroll
+                for (uint32_t x = 0; x < 8; ++x) v[x] = x < T ? tc::dsmem_ld_f32(tc::dsmem_map(ssq_addr, x + T * rank)) : 0.0f;
+                float tot = 0.0f;
+#pragma unroll
+                for (uint32_t x = 0; x < 8; ++x) tot = __fadd_rn(tot, v[x]);          // tiles of the row in fixed order
+                const float var = __fadd_rn(__fdiv_rn(tot, (float)p.N), p.eps);
+                tok_rms[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(var));
+            }
+            __syncthreads();
+            if (live) {
+                const float inv_os = __fdiv_rn(1.0f, *p.out_scale);
+#pragma unroll 2
+                for (int it = threadIdx.x; it < items; it += 128) {
+                    const int c = cbeg + it / 16, g = it % 16;
+                    const int m = col0 + c, n = lane0 + g * 8;
+                    const float rms = tok_rms[c - cbeg];
+                    const float* mine = &red[c * 128 + g * 8];
+                    const uint4 sc = ld_global_v4(p.style + n), sh = ld_global_v4(p.style + p.N + n);
+                    const uint32_t* scw = &sc.x;
+                    const uint32_t* shw = &sh.x;
+                    float q[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float s0, s1, h0, h1;
+                        unpack_bf16x2(scw[k], s0, s1);
+                        unpack_bf16x2(shw[k], h0, h1);
+                        const float n0 = __fmaf_rn(__fmul_rn(mine[2 * k], rms), __fadd_rn(1.0f, s0), h0);
+                        const float n1 = __fmaf_rn(__fmul_rn(mine[2 * k + 1], rms), __fadd_rn(1.0f, s1), h1);
+                        q[2 * k] = clamp448(__fmul_rn(n0, inv_os));
+                        q[2 * k + 1] = clamp448(__fmul_rn(n1, inv_os));
+                    }
+                    uint2 o8;
+                    o8.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+                    o8.y = f32x4_to_e4m3x4(q[4], q[5], q[6], q[7]);
+                    st_global_v2(p.out8 + (size_t)m * p.N + n, o8);
+                }
+            }
+        } else if (!*abort_flag && SWAP) {
             // Work item = (column c of this rank's slice, group of 8 consecutive lanes): every remote read is a
             // 16-byte load, every global store a full 16-byte (bf16) or 8-byte (fp8) vector, and all loads of an
             // item are in flight together.  Ranks are summed in fixed order 0, 1, ...
@@ -609,7 +726,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
             }
         }
         TRACE(7);
-        if (S > 1) tc::cluster_sync_all();
+        if (S > 1 || EPI == EPI_GATE_RES_NORM_FP8) tc::cluster_sync_all();
         TRACE(8);
     }
 
@@ -731,6 +848,52 @@ static int pick_splits(int tiles, int kb_total, int requested) {
     int s = 1;
     while (s < 4 && tiles * s * 2 <= 120 && s * 2 <= kb_total) s *= 2;
     return s;
+}
+
+// fused projection + gated residual + adaRMS + FP8: one cluster of (N / 128 tiles) x S CTAs
+static int launch_gemm_gate_res_norm(const void* A, const void* W, GemmParams p, int K, int splits, bool pdl,
+                                     cudaStream_t stream) {
+    constexpr int BN = 64;
+    using Cfg = GemmCfg<BN>;
+    auto kern = gemm_fp8_kernel<BN, true, EPI_GATE_RES_NORM_FP8>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        attr_done = true;
+    }
+    p.lane_rows = p.N;
+    p.col_rows = p.M;
+    p.w_is_lane = 1;
+    CUtensorMap tmL, tmC;
+    int rc = get_tmap_2d_u8(&tmL, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, 128);
+    if (rc) return rc;
+    rc = get_tmap_2d_u8(&tmC, A, (uint64_t)p.M, (uint64_t)K, (uint64_t)K, BN);
+    if (rc) return rc;
+    const int tiles = p.N / 128;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, 1, splits);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = tiles;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = splits;
+    ++na;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmL, tmC, p);
+    return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
 
 template <int EPI>
@@ -915,6 +1078,42 @@ int frt_b200_gemm_nvfp4_nt_rope_split(const void* A, const void* SFA, const void
     p.head_dim = head_dim;
     return dispatch_small_m_nvfp4<EPI_ROPE_SPLIT>(A, W, p, K, M, (p.N + 127) / 128, splits, flags & 1,
                                                   (cudaStream_t)stream);
+}
+
+// Row-parallel projection of the action expert with the following norm kernel fused (M <= 64, N = 128 .. 1024):
+//   o = bf16(sa * sb * A . W^T); residual <- bf16(residual + o * gate); rms over the N features of each row;
+//   out8 = e4m3(clamp(((residual * rms) * (1 + scale) + shift) * (1 / *d_out_scale), +-448)),
+//   gate (N,) and style = [scale (N) | shift (N)] shared by all rows.  Stands for frt_b200_gemm_fp8_nt followed by
+//   frt_b200_norm_fp8 (gate_residual_ada_norm_fp8) with unit norm weight: same rounding points; the row sum of
+//   squares is accumulated in a different (fixed) order, so FP8 codes may differ in the last place on rare rows.
+// splits: 1 or 2 (0 = 2 when K >= 2048).
+int frt_b200_gemm_fp8_nt_gate_res_norm_fp8(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                           const float* d_scale_b, void* residual, const void* gate, const void* style,
+                                           void* out8, const float* d_out_scale, float eps, int splits, int flags,
+                                           void* stream) {
+    if (!A || !W || !residual || !gate || !style || !out8 || !d_out_scale || M < 0 || N <= 0 || K <= 0)
+        return FRT_ERR_INVALID;
+    if ((K % 16) || M > 64 || (N % 128) || N > 1024) return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(residual) & 15) || (reinterpret_cast<uintptr_t>(gate) & 15) ||
+        (reinterpret_cast<uintptr_t>(style) & 15) || (reinterpret_cast<uintptr_t>(out8) & 7))
+        return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    GemmParams p = {};
+    p.sa = d_scale_a;
+    p.sb = d_scale_b;
+    p.alpha_host = 1.0f;
+    p.M = M;
+    p.N = N;
+    p.kb_total = (K + 127) / 128;
+    p.resid = (__nv_bfloat16*)residual;
+    p.gate = (const __nv_bfloat16*)gate;
+    p.style = (const __nv_bfloat16*)style;
+    p.out8 = (uint8_t*)out8;
+    p.out_scale = d_out_scale;
+    p.eps = eps;
+    int sp = splits > 0 ? (splits > 2 ? 2 : splits) : (K >= 2048 ? 2 : 1);
+    if (sp > p.kb_total) sp = p.kb_total;
+    return launch_gemm_gate_res_norm(A, W, p, K, sp, flags & 1, (cudaStream_t)stream);
 }
 
 // FFN-up projection with bias + GELU(tanh) + FP8 quantise in the epilogue (M > 256):

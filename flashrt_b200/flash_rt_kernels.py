@@ -240,6 +240,13 @@ class GemmRunner:
         call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits,
              _f(pdl) | (2 if one_tile_per_cta else 0), stream)
 
+    def fp8_nt_dev_gate_res_norm_fp8(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, style, out, d_scale_out,
+                                     stream=0, *, eps=1e-6, pdl=False, splits=0):
+        """``fp8_nt_dev`` followed by ``gate_residual_ada_norm_fp8`` (unit norm weight, shared gate / style rows) in
+        one launch: the projection's result never leaves the chip before the next GEMM's FP8 input is written."""
+        call("frt_b200_gemm_fp8_nt_gate_res_norm_fp8", A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, style, out,
+             d_scale_out, eps, splits, _f(pdl), stream)
+
     def fp8_nt_dev_bias_gelu_fp8(self, A, B, out, M, N, K, d_scale_a, d_scale_b, bias, d_scale_out, stream=0, *,
                                  pdl=False):
         """``fp8_nt_dev`` followed by ``bias_gelu_quantize_fp8_static_bf16`` (csrc/bindings.cpp:3427-3440) in one

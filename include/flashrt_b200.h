@@ -221,6 +221,17 @@ int frt_b200_adaln_modulation6(const float* adaln_params, const float* layer_mod
                                void* out2, void* out3, void* out4, void* out5, int B, int S, int D, int flags,
                                void* stream);
 
+/* fp8 GEMM (GemmRunner::fp8_nt_dev, csrc/bindings.cpp:717-727) + gate_residual_ada_norm_fp8
+ * (csrc/bindings.cpp:1144-1162 -> csrc/kernels/fusion.cu:15-81) in one launch, M <= 64, N = 128 .. 1024 (N % 128 == 0):
+ *   o = bf16(sa * sb * A . W^T); residual <- bf16(residual + o * gate); out8 = e4m3 of the adaRMS-modulated row
+ *   (unit norm weight; gate (N,), style = [scale (N) | shift (N)] shared by all rows) with scale *d_out_scale.
+ * One thread-block cluster holds every 128-column tile of the row (x its split-K halves), so the row's sum of
+ * squares is exchanged through distributed shared memory.  Same rounding points as the two separate calls; the sum of
+ * squares is accumulated in a different fixed order, so single FP8 codes may differ in the last place. */
+int frt_b200_gemm_fp8_nt_gate_res_norm_fp8(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                           const float* d_scale_b, void* residual, const void* gate, const void* style,
+                                           void* out8, const float* d_out_scale, float eps, int splits, int flags,
+                                           void* stream);
 /* fp8 GEMM (GemmRunner::fp8_nt_dev, csrc/bindings.cpp:717-727) + bias_gelu_quantize_fp8_static_bf16
  * (csrc/bindings.cpp:3427-3440 -> csrc/quantize/bias_gelu_quantize_fp8.cu:24-49) in one launch, M > 256, N >= 128:
  *   out8 (M, N) e4m3 = clamp(gelu_tanh(bf16(sa * sb * A . W^T) + bias) * (1 / *d_out_scale), +-448)

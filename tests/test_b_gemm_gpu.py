@@ -243,3 +243,44 @@ def test_gemm_fp8_bias_gelu_epilogue_equals_pair(M, N, K):
     # and against the oracle
     ref = O.bias_gelu_quantize_fp8(d_mid.get(), bias, 0.013)
     assert np.array_equal(d_fused.get(), ref)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(50, 1024, 2048, 0), (50, 1024, 4096, 2), (10, 512, 1024, 1), (64, 1024, 256, 1),
+                                          (33, 1024, 1024, 2), (1, 128, 128, 1)])
+def test_gemm_fp8_gate_res_norm_epilogue_vs_pair(M, N, K, splits):
+    """Projection + gated residual + adaRMS + FP8 in one launch (one cluster across the row) against the two
+    separate kernels: the updated residual is identical (same operations); the FP8 codes use a row sum of squares
+    accumulated in a different fixed order, so they are identical except where the pre-rounding value sits within a
+    last-bit distance of a rounding boundary -- at most one code step apart, on a tiny fraction of the elements."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from flashrt_b200 import _lib
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M * 7 + N + K + splits)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    resid = rand_bf16(rng, (M, N), 1.5)
+    style = rand_bf16(rng, (3 * N,), 0.3)            # [scale | shift | gate] of the next norm (gate unused here)
+    gate = rand_bf16(rng, (N,), 0.7)                 # gate of this residual
+    d_A, d_W, d_sa, d_sb, d_so = Dev(A), Dev(W), f32(sa), f32(sb), f32(0.011)
+    d_style, d_gate = Dev(style), Dev(gate)
+    g = fvk.GemmRunner()
+    # pair
+    d_o, d_r1, d_a1 = zeros((M, N), np.uint16), Dev(resid), zeros((M, N), np.uint8)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_o.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0)
+    _lib.call("frt_b200_norm_fp8", d_r1.ptr, d_o.ptr, d_gate.ptr, 0, None, d_style.ptr, 0, d_a1.ptr, None, M, N, 1e-6,
+              d_so.ptr, 0, 0)
+    # fused
+    d_r2, d_a2 = Dev(resid), zeros((M, N), np.uint8)
+    g.fp8_nt_dev_gate_res_norm_fp8(d_A.ptr, d_W.ptr, M, N, K, d_sa.ptr, d_sb.ptr, d_r2.ptr, d_gate.ptr, d_style.ptr,
+                                   d_a2.ptr, d_so.ptr, 0, splits=splits)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_r1.get(), d_r2.get())
+    c1, c2 = d_a1.get(), d_a2.get()
+    same = (c1 == c2).mean()
+    assert same >= 0.995, same
+    v1, v2 = O.e4m3_to_f32(c1), O.e4m3_to_f32(c2)
+    assert (np.abs(v1 - v2) <= np.maximum(np.abs(v1), np.abs(v2)) * 0.13 + 2.0 ** -9).all()   # one code step at most
+    # and the oracle's norm on the oracle-exact residual agrees to the same degree
+    _, ref8, _ = O.norm(resid, x=d_o.get(), gate_in=gate[None, :], gate_in_stride=0, style=style[None, :],
+                        style_stride=0, out="fp8", scale=0.011)
+    assert (ref8 == c2).mean() >= 0.995

@@ -75,6 +75,7 @@ def test_full_depth_loop_runs_and_is_finite():
     assert a.shape == (50, 32) and np.isfinite(a).all()
     assert np.array_equal(a, b)
     assert 0.05 < float(np.abs(a).mean()) < 50
+    # per step: in-projection, first norm, 18 x (qkv, attention, o, norm, gate|up, down, norm), final norm, out-projection
     assert model.frontend.kernels_per_loop() == 10 * (2 + 7 * 18 + 2)
 
 
@@ -150,3 +151,25 @@ def test_fixed_shape_graph_serves_every_prefix_length(precision):
     assert all(g is graphs[0] for g in graphs)          # never re-captured
     from flashrt_b200 import flash_rt_fa2 as fa2
     assert fa2.attention_status() == 0
+
+
+def test_fused_norm_variant_matches_the_default_loop():
+    """fuse_norm=True (projection + gated residual + adaRMS in one 16-CTA-cluster launch, 950 launches per loop):
+    same actions as the default composition to within the FP8 code flips of the differently ordered row statistics."""
+    from flashrt_b200 import load_model
+    from flashrt_b200.pi05_decoder import synthetic_state_dict
+    L = 3
+    sd = synthetic_state_dict(seed=0, layers=L)
+    pk, pv = R.synthetic_prefix_kv(seed=1, layers=L, prefix_len=768)
+    cal = [R.synthetic_noise(100 + j) for j in range(3)]
+    noise = R.synthetic_noise(1).numpy()
+    outs = []
+    for fn in (False, True):
+        m = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768, fuse_norm=fn)
+        m.set_prefix(pk, pv)
+        m.calibrate(cal)
+        outs.append(m.predict(noise=noise))
+        assert m.frontend.kernels_per_loop() == (10 * (2 + 5 * L + 1 + 2) if fn else 10 * (2 + 7 * L + 2))
+    a, b = torch.from_numpy(outs[0]), torch.from_numpy(outs[1])
+    assert _cos(a, b) >= 0.9999
+    assert float((a - b).abs().max()) <= 2e-2 * float(a.pow(2).mean().sqrt())
