@@ -30,6 +30,7 @@ small_gemm_bf16_kernel(const void* __restrict__ Av, const __nv_bfloat16* __restr
     const int ks = threadIdx.x / SG_COLS;
     const int n = blockIdx.x * SG_COLS + tx;
     const int m0 = blockIdx.y * SG_ROWS;
+    pdl_launch_dependents();     // the dependent kernel still waits for this grid to complete
     pdl_wait();
     float acc[SG_ROWS] = {};
     for (int k0 = 0; k0 < K; k0 += SG_KCHUNK) {
@@ -56,7 +57,6 @@ small_gemm_bf16_kernel(const void* __restrict__ Av, const __nv_bfloat16* __restr
 #pragma unroll
     for (int r = 0; r < SG_ROWS; ++r) part[ks][r][tx] = acc[r];
     __syncthreads();
-    pdl_launch_dependents();
     if (ks < SG_ROWS && n < N && m0 + ks < M) {
         const int r = ks;
         float s = 0.0f;

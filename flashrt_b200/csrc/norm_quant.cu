@@ -65,6 +65,9 @@ norm_row_kernel(NormArgs a) {
     uint4 wv = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
     uint4 sc = make_uint4(0, 0, 0, 0), sh = sc, gt = sc;
 
+    // The next kernel in the stream may start its own input-independent prologue right away (it still waits for
+    // this grid to finish before it touches anything this grid writes).
+    pdl_launch_dependents();
     // Everything that does not depend on the producer kernel is fetched first.
     if (active) {
         if (a.weight) wv = ld_global_v4(a.weight + col);
@@ -121,8 +124,6 @@ norm_row_kernel(NormArgs a) {
             }
         }
     }
-    pdl_launch_dependents();
-
     ssq = warp_sum_butterfly(ssq);
     const int nwarps = blockDim.x >> 5;
     if ((tid & 31) == 0) warp_tot[tid >> 5] = ssq;

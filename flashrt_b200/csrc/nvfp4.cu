@@ -25,6 +25,7 @@ quantize_nvfp4_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restrict_
     float inv_g = 1.0f;
     const bool has_g = d_global != nullptr;
     if (has_g) inv_g = __fdiv_rn(1.0f, *d_global);
+    pdl_launch_dependents();
     pdl_wait();
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -55,7 +56,6 @@ quantize_nvfp4_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restrict_
         st_global_v2(packed + row * (D >> 1) + blk * 8, o);
         sf[nvfp4::sf_offset(row, blk, katoms)] = (uint8_t)sb;
     }
-    pdl_launch_dependents();
 }
 
 template <int FAMILY>
@@ -65,6 +65,7 @@ geglu_nvfp4_kernel(const __nv_bfloat16* __restrict__ merged, uint8_t* __restrict
     const int nblk = H >> 4;
     const int katoms = (H + 63) >> 6;
     const long long total = (long long)rows * nblk;
+    pdl_launch_dependents();
     pdl_wait();
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -94,7 +95,6 @@ geglu_nvfp4_kernel(const __nv_bfloat16* __restrict__ merged, uint8_t* __restrict
         st_global_v2(packed + row * (H >> 1) + blk * 8, o);
         sf[nvfp4::sf_offset(row, blk, katoms)] = (uint8_t)sb;
     }
-    pdl_launch_dependents();
 }
 
 template <typename K, typename... Args>

@@ -439,7 +439,7 @@ class Pi05DecoderB200:
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
                  cfg_beta: float | None = None, fixed_shape: bool = False, attn_splits: int = 8,
-                 fuse_norm: bool = False, **_ignored):
+                 fuse_norm: bool = False, gu_splits: int = 0, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -461,6 +461,7 @@ class Pi05DecoderB200:
         # fixed-shape mode: prefix_len is the LARGEST prefix; the valid length is a device-side value
         self.fixed_shape = bool(fixed_shape)
         self.attn_splits = int(attn_splits)      # kv splits of the decoder attention (combined through scratch)
+        self.gu_splits = int(gu_splits)          # split-K of the gate|up projection (0 = the library's choice)
         self.valid_prefix_len = prefix_len
         if batch < 1 or batch * ((chunk_size * DEC_NH + 127) // 128) * 8 > self.sm_count:
             raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")
