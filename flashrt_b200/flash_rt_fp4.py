@@ -89,12 +89,14 @@ pi05_gate_res_adarms_fp4_sfa_fp16 = pi05_gate_res_adarms_fp4_sfa_bf16           
 pi05_gate_res_adarms_fp4_sfa_native_fp16 = pi05_gate_res_adarms_fp4_sfa_bf16     # :627-657
 
 
-def rms_norm_fp4_sfa_fp16(x, weight, packed, sfa, seq_len, dim, stream=0, *, pdl=False, eps=1e-6):   # :501-513
+def rms_norm_fp4_sfa_fp16(x, packed, sfa, seq_len, dim, stream=0, *, weight=0, pdl=False, eps=1e-6):   # :501-513
+    # the reference's kernel has no weight operand (the norm weight is folded into the next projection); `weight`
+    # is an extension of this library
     call("frt_b200_norm_nvfp4", x, None, None, 0, weight or None, None, 0, packed, sfa, None, seq_len, dim, eps,
          FAMILY, _f(pdl), stream)
 
 
-def residual_add_rms_norm_fp4_sfa_fp16(residual, x, weight, packed, sfa, seq_len, dim, stream=0, *, pdl=False,
+def residual_add_rms_norm_fp4_sfa_fp16(residual, x, packed, sfa, seq_len, dim, stream=0, *, weight=0, pdl=False,
                                        eps=1e-6):                                                    # :531-545
     call("frt_b200_norm_nvfp4", residual, x, None, 0, weight or None, None, 0, packed, sfa, None, seq_len, dim,
          eps, FAMILY, _f(pdl), stream)

@@ -57,3 +57,31 @@ def test_shim_mirrors_reference_binding_names():
     import pytest
     with pytest.raises(fvk.NotBuilt):
         fvk.GemmRunner().fp8_nn_dev(0, 0, 0, 1, 1, 16, 0, 0)
+
+
+def test_stand_in_modules_accept_the_reference_binding_signatures():
+    """Every reference entry point of the path (names and keyword order read from the reference's pybind sources into
+    tests/golden/reference_surface.json) exists in the stand-in modules with the same parameter names in the same
+    order, so that positional and keyword call sites of the reference bind unchanged.  Extra parameters of the
+    stand-ins are keyword-only."""
+    import inspect
+    import json
+    import os
+    from flashrt_b200 import flash_rt_fa2, flash_rt_fp4, flash_rt_kernels
+    surface = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_surface.json")))
+    mods = {"flash_rt_kernels": flash_rt_kernels, "flash_rt_fa2": flash_rt_fa2, "flash_rt_fp4": flash_rt_fp4,
+            "GemmRunner": flash_rt_kernels.GemmRunner}
+    problems = []
+    for mod_name, entries in surface.items():
+        for name, ref_args in entries.items():
+            fn = getattr(mods[mod_name], name, None)
+            if fn is None:
+                problems.append(f"{mod_name}.{name}: missing")
+                continue
+            params = list(inspect.signature(fn).parameters.values())
+            if params and params[0].name == "self":
+                params = params[1:]
+            positional = [p.name for p in params if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
+            if positional != ref_args:
+                problems.append(f"{mod_name}.{name}: {positional} != reference {ref_args}")
+    assert not problems, "\n".join(problems)
