@@ -185,7 +185,7 @@ def run_ours(args):
     gsd = torch.Generator().manual_seed(1)
     nv = args.precision == "nvfp4"
     model = load_model("synthetic:0", config="pi05", device=local, use_pdl=not args.no_pdl,
-                       precision=args.precision, batch=args.batch)
+                       precision=args.precision, batch=args.batch, persistent_loop=args.persistent_loop)
     fe = model.frontend
     L, P = fe.layers, fe.prefix_len
     model.set_prefix(torch.randn(L, P, 256, generator=gsd), torch.randn(L, P, 256, generator=gsd))
@@ -563,6 +563,8 @@ def main():
     ap.add_argument("--no-pdl", action="store_true",
                     help="chain kernels with plain stream order instead of programmatic dependent launch "
                          "(Nsight Compute cannot profile programmatically dependent launches)")
+    ap.add_argument("--persistent-loop", action="store_true",
+                    help="pi05 / fp8: run the whole denoise loop as one persistent cooperative kernel")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
     ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops", "prefix"],

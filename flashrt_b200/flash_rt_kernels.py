@@ -15,7 +15,7 @@ dependent launch; the B200 pipeline uses it, reference call sites never pass it.
 from __future__ import annotations
 
 from . import _lib
-from ._lib import KernelError, call  # noqa: F401  (re-exported)
+from ._lib import KernelError, call, call_status  # noqa: F401  (re-exported)
 
 
 class NotBuilt(RuntimeError):
@@ -311,7 +311,8 @@ def get_sm_version() -> int:
 def tensor_core_status(reset: bool = True) -> int:
     """0 unless a bounded wait inside a tensor-core kernel gave up (see ``frt_b200_gemm_status``)."""
     r = 1 if reset else 0
-    return _lib.call_status("frt_b200_gemm_status", r) or _lib.call_status("frt_b200_attention_status", r)
+    return (_lib.call_status("frt_b200_gemm_status", r) or _lib.call_status("frt_b200_attention_status", r)
+            or _lib.call_status("frt_b200_expert_loop_status", r))
 
 
 def __getattr__(name: str):

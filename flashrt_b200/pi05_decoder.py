@@ -23,6 +23,7 @@ PyTorch only provides device memory, streams and graph capture here.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 
 import numpy as np
@@ -256,6 +257,15 @@ class StepIO:
                          kv_static_rows=fe.prefix_len, **kw)
 
 
+class ExpertLoopArgs(ctypes.Structure):
+    """``frt_b200_expert_loop_args`` of the C header (same member order)."""
+    _fields_ = ([(n, ctypes.c_void_p) for n in (
+        "w_qkv", "w_o", "w_gu", "w_d", "ws_qkv", "ws_o", "ws_gu", "ws_d", "act_scale", "style_attn", "style_ffn",
+        "style_final", "rope", "in_w", "in_b", "out_w", "out_b", "k_cache", "v_cache", "noise", "workspace")]
+        + [("workspace_bytes", ctypes.c_longlong)]
+        + [(n, ctypes.c_int) for n in ("steps", "layers", "S", "prefix_len", "kv_rows")])
+
+
 class Pi05DecoderPipeline(StepIO):
     """Pointer-only composition of the denoise loop (what gets captured in the graph)."""
 
@@ -288,6 +298,37 @@ class Pi05DecoderPipeline(StepIO):
         self.act_scale = torch.ones(N, L, len(SITES), dtype=torch.float32, device=dev)
         self.scratch_scale = torch.zeros(1, dtype=torch.float32, device=dev)
         self.calibrated = False
+        self.loop_args = None
+        if fe.persistent_loop:
+            self._init_persistent_loop()
+
+    # ---- the loop as one persistent kernel ---------------------------------
+    def _init_persistent_loop(self):
+        """Scratch and argument block of ``frt_b200_expert_loop_fp8``: the whole N-step loop in one cooperative
+        launch (same weights, scales, styles and caches as the operator-by-operator composition below, which stays
+        the calibration pass)."""
+        fe = self.fe
+        if fe.batch != 1 or fe.cfg_beta is not None or fe.fixed_shape or fe.chunk_size > 64:
+            raise ValueError("persistent_loop serves batch 1, no guidance pair, no fixed-shape mode, chunk <= 64")
+        nbytes = ctypes.c_longlong(0)
+        fvk.call("frt_b200_expert_loop_workspace_bytes", fe.chunk_size, fe.prefix_len, ctypes.addressof(nbytes))
+        self.loop_ws = torch.zeros(nbytes.value, dtype=torch.uint8, device=fe.device)
+        a = ExpertLoopArgs()
+        for name, t in (("w_qkv", fe.w_qkv), ("w_o", fe.w_o), ("w_gu", fe.w_gu), ("w_d", fe.w_d),
+                        ("ws_qkv", fe.ws_qkv_t), ("ws_o", fe.ws_o_t), ("ws_gu", fe.ws_gu_t), ("ws_d", fe.ws_d_t),
+                        ("act_scale", self.act_scale), ("style_attn", fe.style_attn), ("style_ffn", fe.style_ffn),
+                        ("style_final", fe.style_final), ("rope", fe.rope), ("in_w", fe.action_in_w),
+                        ("in_b", fe.action_in_b), ("out_w", fe.action_out_w), ("out_b", fe.action_out_b),
+                        ("k_cache", fe.k_cache), ("v_cache", fe.v_cache), ("noise", self.noise),
+                        ("workspace", self.loop_ws)):
+            assert t.is_contiguous(), name
+            setattr(a, name, t.data_ptr())
+        a.workspace_bytes = nbytes.value
+        a.steps, a.layers, a.S, a.prefix_len, a.kv_rows = fe.num_steps, fe.layers, fe.chunk_size, fe.prefix_len, fe.kv_rows
+        self.loop_args = a
+
+    def _run_persistent(self, stream: int) -> None:
+        fvk.call("frt_b200_expert_loop_fp8", ctypes.addressof(self.loop_args), ctypes.sizeof(self.loop_args), stream)
 
     # ---- small helpers -------------------------------------------------
     def _scale_ptr(self, step, layer, site):
@@ -315,6 +356,9 @@ class Pi05DecoderPipeline(StepIO):
         amax / 448 is measured on the device and folded (max) into the per-site per-step scale table.
         ``step_hook(step)`` (eager runs only) is called after each Euler step, e.g. to snapshot the state."""
         fe, g = self.fe, self.gemm
+        if self.loop_args is not None and not calibrate and step_hook is None:
+            self._run_persistent(stream)
+            return
         S, L, B, CS = self.M, fe.layers, fe.batch, fe.chunk_size    # S = batch * chunk rows
         pdl = fe.use_pdl and not calibrate
         for step in range(fe.num_steps):
@@ -439,7 +483,7 @@ class Pi05DecoderB200:
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
                  cfg_beta: float | None = None, fixed_shape: bool = False, attn_splits: int = 8,
-                 fuse_norm: bool = False, gu_splits: int = 0, **_ignored):
+                 fuse_norm: bool = False, gu_splits: int = 0, persistent_loop: bool = False, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -451,6 +495,10 @@ class Pi05DecoderB200:
         # projection + gated residual + adaRMS as one 16-CTA-cluster launch: measured slower than the two kernels
         # (10.17 ms vs 9.75 ms per loop, 950 vs 1300 launches), so off unless asked for
         self.fuse_norm = bool(fuse_norm) and fuse_epilogues
+        # the whole loop as one cooperative kernel (phases separated by grid barriers) instead of 1300 launches
+        self.persistent_loop = bool(persistent_loop)
+        if self.persistent_loop and precision != "fp8":
+            raise ValueError("persistent_loop is built for the FP8 loop")
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.kv_rows = prefix_len + chunk_size
         if precision not in ("fp8", "nvfp4"):
@@ -665,5 +713,7 @@ class Pi05DecoderB200:
         """Launches of this library's kernels inside one replay (for reporting)."""
         L, N = self.layers, self.num_steps
         p = self.pipeline
+        if getattr(p, "loop_args", None) is not None:
+            return 1
         # in-projection(s), first norm, the blocks, final residual + final norm, out-projection (+ guidance combine)
         return int(round(N * (p.step_io_launches() + 1 + p.launches_per_layer() * L + 1)))

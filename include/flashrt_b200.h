@@ -309,6 +309,45 @@ int frt_b200_sm_version(void);
 int frt_b200_cfg_combine_into_residual(void* residual, const void* v_cond, const void* v_uncond, float beta,
                                        long long n, int f32, int flags, void* stream);
 
+/* ---------------------------------------------------------------- the whole denoise loop as one persistent kernel
+ * Pi05Pipeline.transformer_decoder / _decoder_layer   flash_rt/models/pi05/pipeline_rtx.py:1451-1749
+ * (the reference runs this loop as ~2000 launches inside one CUDA graph; its kernel library has no counterpart in the
+ * reference for a single-launch form: no counterpart in the reference).  Same arithmetic as the operator-by-operator
+ * composition of this library (FP8 E4M3 projections with static per-site activation scales, bf16 residual stream and
+ * attention, fp32 Euler state), batch 1, S <= 64 action tokens, decoder width 1024 / hidden 4096 / 8 x 256 query
+ * heads over one KV head.  One cooperative launch of one CTA per SM; phases are separated by grid-wide barriers with
+ * bounded waits (see frt_b200_expert_loop_status).
+ *
+ * All members are device pointers except `workspace_bytes` and the ints.  Weights are E4M3 bytes, (layers, N, K) with
+ * K contiguous: w_qkv N = 2560 (Q rows and K rows interleaved for adjacent-pair RoPE), w_o N = 1024 K = 2048,
+ * w_gu N = 8192 (gate rows, then up rows), w_d N = 1024 K = 4096; ws_* (layers,) fp32 weight scales;
+ * act_scale (steps, layers, 4) fp32, sites qkv / o / gate-up / down; style_attn, style_ffn (steps, layers, 3072) and
+ * style_final (steps, 3072) bf16 rows [scale | shift | gate]; rope (S, 256) bf16 [cos0, sin0, cos1, sin1, ...];
+ * in_w (32, 1024), in_b (1024), out_w (1024, 32) and out_b (32) bf16, the out-projection pre-scaled by -1 / steps;
+ * k_cache / v_cache (layers, kv_rows, 256) bf16 holding the prefix in rows [0, prefix_len) -- rows
+ * [prefix_len, prefix_len + S) are overwritten; noise (S, 32) fp32 in/out.  workspace: frt_b200_expert_loop_workspace_bytes
+ * bytes, 256-byte aligned, contents arbitrary. */
+typedef struct frt_b200_expert_loop_args {
+    const void *w_qkv, *w_o, *w_gu, *w_d;
+    const void *ws_qkv, *ws_o, *ws_gu, *ws_d;
+    const void *act_scale;
+    const void *style_attn, *style_ffn, *style_final;
+    const void *rope;
+    const void *in_w, *in_b, *out_w, *out_b;
+    void *k_cache, *v_cache;
+    void *noise;
+    void *workspace;
+    long long workspace_bytes;
+    int steps, layers, S, prefix_len, kv_rows;
+} frt_b200_expert_loop_args;
+/* host_args: HOST pointer to a frt_b200_expert_loop_args, args_bytes = sizeof of it (checked). */
+int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream);
+/* no counterpart in the reference: size of the loop kernel's scratch for S action tokens behind prefix_len keys */
+int frt_b200_expert_loop_workspace_bytes(int S, int prefix_len, long long* out_bytes);
+/* Status word of the loop kernel (0 = no bounded wait gave up; else code | CTA << 8, code 1 weight producer, 2 MMA
+ * issuer, 3 worker, 4 grid barrier); synchronises the device. */
+int frt_b200_expert_loop_status(int reset);
+
 /* number of SMs of the current device (grid sizing) */
 int frt_b200_device_sm_count(void);
 

