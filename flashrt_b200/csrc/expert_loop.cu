@@ -46,8 +46,13 @@ __device__ unsigned long long g_loop_trace[160][128];
     do {                                                                                                    \
         if (wtid == 0 && gl >= L && gl < L + 2) g_loop_trace[cta][(gl - L) * 64 + (ev)] = tc::global_timer_ns(); \
     } while (0)
+#define LTM(ev)                                                                                             \
+    do {                                                                                                    \
+        if ((ev) >= 0 && gl >= L && gl < L + 2) g_loop_trace[cta][(gl - L) * 64 + (ev)] = tc::global_timer_ns(); \
+    } while (0)
 #else
 #define LT(ev)
+#define LTM(ev)
 #endif
 
 namespace el {
@@ -80,7 +85,7 @@ struct LoopParams {
     uint8_t* attn8;        // (64, 2048)
     uint8_t* hid8;         // (64, 4096)
     float* part;           // (4, 64, 1024) split-K partials
-    float* po;             // (attention units, 128, 256)
+    __nv_bfloat16* po;     // (attention units, 128, 256) normalised partial outputs
     float* plse;           // (attention units, 128)
     int steps, layers, S, prefix_len, kv_rows, T, chunks_total, nsplit, att_units, att_tiles;
     float scale_log2;
@@ -103,7 +108,7 @@ __device__ __forceinline__ int gemm_unit(int G, int cta, int gl, int ph) {
     return u < n ? u : -1;
 }
 __device__ __forceinline__ int att_unit(int G, int cta, int gl, int units) {
-    const long long g0 = (long long)gl * units + 64;
+    const long long g0 = (long long)gl * U_LAYER + U_QKV;     // right behind the block's QKV units
     const int u = (int)((((long long)cta - g0) % G + G) % G);
     return u < units ? u : -1;
 }
@@ -133,7 +138,8 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, int nrows, int wtid, Src
 
 __global__ void __launch_bounds__(320, 1)
 expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmO,
-                   const __grid_constant__ CUtensorMap tmGU, const __grid_constant__ CUtensorMap tmD, LoopParams p) {
+                   const __grid_constant__ CUtensorMap tmGU, const __grid_constant__ CUtensorMap tmD,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, LoopParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* ring = smem;
@@ -145,7 +151,8 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
     uint64_t* acc_bar = b_ready + 1;          // accumulator (or S = Q.K^T) complete
     uint64_t* p_ready = b_ready + 2;          // 128 arrivals: P is in tensor memory
     uint64_t* o_full = b_ready + 3;           // P.V complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 4);
+    uint64_t* kv_full = b_ready + 4;          // prefix K / V chunk fetched ahead of the attention phase has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* issued = abort_flag + 1;
     volatile int* consumed = abort_flag + 2;
@@ -171,6 +178,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
         tc::mbar_init(acc_bar, 1);
         tc::mbar_init(p_ready, 128);
         tc::mbar_init(o_full, 1);
+        tc::mbar_init(kv_full, 1);
         *abort_flag = 0;
         *issued = 0;
         *consumed = 0;
@@ -180,6 +188,8 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
         tc::tma_prefetch_desc(&tmO);
         tc::tma_prefetch_desc(&tmGU);
         tc::tma_prefetch_desc(&tmD);
+        tc::tma_prefetch_desc(&tmK);
+        tc::tma_prefetch_desc(&tmV);
     }
     if (warp == 1) {
         tc::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -253,9 +263,11 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                 }
                 return true;
             };
-            auto run_gemm = [&](int u) {
+            auto run_gemm = [&](int u, int gl, int tr) {
+                (void)gl; (void)tr;
                 if (u < 0 || dead) return;
                 if (!wait(b_ready, nb & 1)) return;
+                LTM(tr);
                 ++nb;
                 tc::tc_fence_after_sync();
                 for (int kb = 0; kb < KB_PER_UNIT; ++kb) {
@@ -271,10 +283,11 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                     ++cc;
                     *consumed = (int)cc;
                 }
+                LTM(tr + 1);
                 tc::mma_commit(acc_bar);
             };
             for (int gl = 0; gl < p.steps * L && !dead; ++gl) {
-                run_gemm(gemm_unit(G, cta, gl, 0));
+                run_gemm(gemm_unit(G, cta, gl, 0), gl, 40);
                 const int au = att_unit(G, cta, gl, p.att_units);
                 if (au >= 0 && wait(b_ready, nb & 1)) {
                     ++nb;
@@ -295,9 +308,9 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         tc::mma_commit(o_full);
                     }
                 }
-                run_gemm(gemm_unit(G, cta, gl, 1));
-                run_gemm(gemm_unit(G, cta, gl, 2));
-                run_gemm(gemm_unit(G, cta, gl, 3));
+                run_gemm(gemm_unit(G, cta, gl, 1), gl, 42);
+                run_gemm(gemm_unit(G, cta, gl, 2), gl, 44);
+                run_gemm(gemm_unit(G, cta, gl, 3), gl, 46);
             }
         }
     } else {
@@ -311,7 +324,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
         const bool row_cta = cta < S;
         const int row = cta;
         const int n0 = wtid * 4;
-        uint32_t n_acc = 0, n_o = 0, epoch = 0;
+        uint32_t n_acc = 0, n_o = 0, n_kv = 0, epoch = 0;
         // `dead` is the same for all 256 workers (it is taken from one thread's sample inside the grid barrier), so
         // it may guard code that contains worker barriers; `bad` is per warp and only short-circuits later waits
         bool dead = false, bad = false;
@@ -326,6 +339,28 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                 bad = true;
             }
             return ok;
+        };
+        // this thread's 32 accumulator columns.  (Four independent accumulation chains, one per K = 32 slice, were
+        // measured: the MMA issue time of a unit stayed at 2.2 us, so the chain is not what bounds it.)
+        auto ld_acc = [&](uint32_t* v) {
+            tc::tmem_ld32(tmem + lane_off + half * 32, v);
+            tc::tmem_ld_wait();
+        };
+        // split-K partial of a projection: accumulator -> shared memory [token][128 features] -> rows of 512 bytes
+        auto store_partial = [&](bool ok, int ks, int tile) {
+            float* stage = reinterpret_cast<float*>(sh);
+            if (ok) {
+                tc::tc_fence_after_sync();
+                uint32_t v[32];
+                ld_acc(v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stage[(half * 32 + j) * 128 + quad * 32 + lane] = __uint_as_float(v[j]);
+                tc::tc_fence_before_sync();
+            }
+            work_sync();
+            for (int m = ww; m < S; m += 8)
+                __stcg(reinterpret_cast<float4*>(p.part + ((size_t)ks * MAXS + m) * D + tile * 128) + lane,
+                       *reinterpret_cast<const float4*>(stage + m * 128 + lane * 4));
         };
         auto grid_barrier = [&]() {
             ++epoch;
@@ -455,6 +490,20 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                 const int gl = step * L + layer;
                 const float* asc = p.act_scale + (size_t)gl * 4;
                 LT(0);
+                // The keys / values of the prefix do not change during the loop: the chunk of this CTA's attention unit
+                // is fetched by TMA now and lands during phases A and B (an attention CTA owns no QKV unit of the same
+                // block, so nothing else uses the operand region until phase C).
+                const int au = dead ? -1 : att_unit(G, cta, gl, p.att_units);
+                const bool kv_ahead = au >= 0 && (au / p.att_tiles + 1) * BKV <= p.prefix_len;
+                if (kv_ahead && wtid == 0) {
+                    const int y = layer * p.kv_rows + (au / p.att_tiles) * BKV;
+                    tc::mbar_arrive_expect_tx(kv_full, 2 * BKV * HD * 2);
+#pragma unroll
+                    for (int db = 0; db < 4; ++db) {
+                        tc::tma_load_2d(smem + OFF_K + db * (BKV * 128), &tmK, kv_full, db * 128, y);
+                        tc::tma_load_2d(smem + OFF_V + db * (BKV * 128), &tmV, kv_full, db * 128, y);
+                    }
+                }
                 // ---------------------------------------------------------------- A: rows
                 if (row_cta && !dead) {
                     float ssq = 0.0f;
@@ -521,8 +570,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         if (ok) {
                             tc::tc_fence_after_sync();
                             uint32_t v[32];
-                            tc::tmem_ld32(tmem + lane_off + half * 32, v);
-                            tc::tmem_ld_wait();
+                            ld_acc(v);
                             __nv_bfloat16* dst = is_q ? p.q + n
                                                       : (is_k ? p.k_cache : p.v_cache) +
                                                             ((size_t)layer * p.kv_rows + p.prefix_len) * HD + nr;
@@ -556,7 +604,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                 // = one (token, head) row, bf16 pairs per column) and feeds the MMA as the A operand, K and V sit in
                 // the 64 KB operand region, P overlays S.
                 {
-                    const int au = att_unit(G, cta, gl, p.att_units);
                     if (au >= 0 && !dead) {
                         const int tile = au % p.att_tiles, c = au / p.att_tiles;
                         const int tok0 = tile * 16, key0 = c * BKV;
@@ -569,18 +616,24 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                             uint4 qv[16];
 #pragma unroll
                             for (int i = 0; i < 16; ++i) qv[i] = tok < S ? __ldcg(src + i) : make_uint4(0, 0, 0, 0);
-                            load_tile<HD * 2, 8>(smem + OFF_K, BKV, wtid, [&](int r) -> const uint8_t* {
-                                return key0 + r < p.T ? reinterpret_cast<const uint8_t*>(kc + (size_t)(key0 + r) * HD)
-                                                      : nullptr;
-                            });
-                            load_tile<HD * 2, 8>(smem + OFF_V, BKV, wtid, [&](int r) -> const uint8_t* {
-                                return key0 + r < p.T ? reinterpret_cast<const uint8_t*>(vc + (size_t)(key0 + r) * HD)
-                                                      : nullptr;
-                            });
+                            if (!kv_ahead) {       // the chunk holds rows appended in phase B: plain loads
+                                load_tile<HD * 2, 8>(smem + OFF_K, BKV, wtid, [&](int r) -> const uint8_t* {
+                                    return key0 + r < p.T ? reinterpret_cast<const uint8_t*>(kc + (size_t)(key0 + r) * HD)
+                                                          : nullptr;
+                                });
+                                load_tile<HD * 2, 8>(smem + OFF_V, BKV, wtid, [&](int r) -> const uint8_t* {
+                                    return key0 + r < p.T ? reinterpret_cast<const uint8_t*>(vc + (size_t)(key0 + r) * HD)
+                                                          : nullptr;
+                                });
+                            }
                             const uint32_t tq = tmem + Q_COL + lane_off + half * 64;
                             tc::tmem_st32(tq, &qv[0].x);
                             tc::tmem_st32(tq + 32, &qv[8].x);
                             tc::tmem_st_wait();
+                        }
+                        if (kv_ahead) {
+                            (void)wait(kv_full, n_kv & 1);
+                            ++n_kv;
                         }
                         tc::fence_proxy_async_smem();
                         tc::tc_fence_before_sync();
@@ -635,40 +688,38 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         ok = wait(o_full, n_o & 1);
                         ++n_o;
                         LT(13);
-                        // ---- normalised partial -> shared memory (xor-swizzled 16-byte chunks) -> global scratch, 128
-                        // columns at a time (runs even after a failed wait: everyone must reach the worker barriers)
+                        // ---- normalised partial as bf16 -> shared memory (rows of 512 bytes, 16-byte chunks xor-swizzled)
+                        // -> global scratch with full-row stores (runs even after a failed wait: everyone must reach
+                        // the worker barriers)
                         work_sync();
                         tc::tc_fence_after_sync();
-                        float* red = reinterpret_cast<float*>(sh);             // [128 rows][128 columns]
                         const float invl = s_l[arow];
-                        float* dst_unit = p.po + (size_t)au * 128 * HD;
+                        {
+                            const uint32_t tmem_O = tmem + O_COL + lane_off + half * 128;
 #pragma unroll 1
-                        for (int hp = 0; hp < 2; ++hp) {
-                            if (half == hp) {
-                                const uint32_t tmem_O = tmem + O_COL + lane_off + hp * 128;
-#pragma unroll 1
-                                for (int cb = 0; cb < 128; cb += 32) {
-                                    uint32_t ov[32];
-                                    tc::tmem_ld32(tmem_O + cb, ov);
-                                    tc::tmem_ld_wait();
+                            for (int cb = 0; cb < 128; cb += 32) {
+                                uint32_t ov[32];
+                                tc::tmem_ld32(tmem_O + cb, ov);
+                                tc::tmem_ld_wait();
 #pragma unroll
-                                    for (int j4 = 0; j4 < 8; ++j4) {
-                                        const int ch = (cb >> 2) + j4;
-                                        *reinterpret_cast<float4*>(&red[(size_t)arow * 128 + ((ch ^ (arow & 7)) << 2)]) =
-                                            make_float4(__uint_as_float(ov[j4 * 4]) * invl, __uint_as_float(ov[j4 * 4 + 1]) * invl,
-                                                        __uint_as_float(ov[j4 * 4 + 2]) * invl, __uint_as_float(ov[j4 * 4 + 3]) * invl);
-                                    }
+                                for (int j8 = 0; j8 < 4; ++j8) {
+                                    uint4 o;
+                                    o.x = pack_bf16x2(__uint_as_float(ov[j8 * 8 + 0]) * invl, __uint_as_float(ov[j8 * 8 + 1]) * invl);
+                                    o.y = pack_bf16x2(__uint_as_float(ov[j8 * 8 + 2]) * invl, __uint_as_float(ov[j8 * 8 + 3]) * invl);
+                                    o.z = pack_bf16x2(__uint_as_float(ov[j8 * 8 + 4]) * invl, __uint_as_float(ov[j8 * 8 + 5]) * invl);
+                                    o.w = pack_bf16x2(__uint_as_float(ov[j8 * 8 + 6]) * invl, __uint_as_float(ov[j8 * 8 + 7]) * invl);
+                                    const int ch = ((half * 128 + cb) >> 3) + j8;             // 16-byte chunk of the row, 0..31
+                                    *reinterpret_cast<uint4*>(sh + arow * 512 + ((ch ^ (arow & 7)) << 4)) = o;
                                 }
                             }
-                            work_sync();
-#pragma unroll 4
-                            for (int r = ww; r < 128; r += 8)
-                                __stcg(reinterpret_cast<float4*>(dst_unit + (size_t)r * HD + hp * 128) + lane,
-                                       *reinterpret_cast<const float4*>(&red[(size_t)r * 128 + ((lane ^ (r & 7)) << 2)]));
-                            work_sync();
                         }
-                        if (wtid < 128) __stcg(p.plse + (size_t)au * 128 + wtid, s_lse[wtid]);
                         tc::tc_fence_before_sync();
+                        work_sync();
+                        uint4* dst_unit = reinterpret_cast<uint4*>(p.po + (size_t)au * 128 * HD);
+#pragma unroll 4
+                        for (int r = ww; r < 128; r += 8)
+                            __stcg(dst_unit + r * 32 + lane, *reinterpret_cast<const uint4*>(sh + r * 512 + ((lane ^ (r & 7)) << 4)));
+                        if (wtid < 128) __stcg(p.plse + (size_t)au * 128 + wtid, s_lse[wtid]);
                     }
                 }
                 LT(11);
@@ -678,41 +729,53 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                 // ---------------------------------------------------------------- D: combine the chunks -> FP8
                 if (!dead) {
                     const float inv_os = __fdiv_rn(1.0f, asc[1]);
-                    const int items = S * NH * (HD / 4);
+                    const int items = S * NH * (HD / 8);
                     for (int it = cta * NWORK + wtid; it < items; it += G * NWORK) {
-                        const int ch = it & 63, head = (it >> 6) & 7, tok = it >> 9;
+                        const int ch = it & 31, head = (it >> 5) & 7, tok = it >> 8;
                         const int tile = tok >> 4, r = ((tok & 15) << 3) + head;
-                        float M = -INFINITY, Lw = 0.0f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                        float M = -INFINITY, Lw = 0.0f, a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                         for (int s0 = 0; s0 < p.nsplit; s0 += 8) {
                             // eight partials in flight together, then folded into the running (max, sum, value)
                             float lse[8];
-                            float4 x[8];
+                            uint4 x[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const bool in = s0 + j < p.nsplit;
                                 const size_t ub = (size_t)((in ? s0 + j : 0) * p.att_tiles + tile) * 128 + r;
                                 lse[j] = in ? __ldcg(p.plse + ub) : -INFINITY;
-                                x[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.po + ub * HD) + ch)
-                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                                x[j] = in ? __ldcg(reinterpret_cast<const uint4*>(p.po + ub * HD) + ch) : make_uint4(0, 0, 0, 0);
                             }
                             float Mg = M;
 #pragma unroll
                             for (int j = 0; j < 8; ++j) Mg = fmaxf(Mg, lse[j]);
                             const float resc = (M == -INFINITY) ? 0.0f : ex2(M - Mg);
-                            Lw *= resc; a0 *= resc; a1 *= resc; a2 *= resc; a3 *= resc;
+                            Lw *= resc;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) a[e] *= resc;
                             M = Mg;
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const float w = (lse[j] == -INFINITY) ? 0.0f : ex2(lse[j] - M);
                                 Lw += w;
-                                a0 += w * x[j].x; a1 += w * x[j].y; a2 += w * x[j].z; a3 += w * x[j].w;
+                                const uint32_t* xw = &x[j].x;
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float lo, hi;
+                                    unpack_bf16x2(xw[e], lo, hi);
+                                    a[2 * e] += w * lo;
+                                    a[2 * e + 1] += w * hi;
+                                }
                             }
                         }
                         const float invL = Lw > 0.0f ? 1.0f / Lw : 0.0f;
                         // the attention output is a bf16 tensor in the operator composition: keep that rounding point
-                        *reinterpret_cast<uint32_t*>(p.attn8 + (size_t)tok * QD + head * HD + ch * 4) =
-                            f32x4_to_e4m3x4(clamp448(__fmul_rn(bf16r(a0 * invL), inv_os)), clamp448(__fmul_rn(bf16r(a1 * invL), inv_os)),
-                                            clamp448(__fmul_rn(bf16r(a2 * invL), inv_os)), clamp448(__fmul_rn(bf16r(a3 * invL), inv_os)));
+                        float q8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) q8[e] = clamp448(__fmul_rn(bf16r(a[e] * invL), inv_os));
+                        uint2 o8;
+                        o8.x = f32x4_to_e4m3x4(q8[0], q8[1], q8[2], q8[3]);
+                        o8.y = f32x4_to_e4m3x4(q8[4], q8[5], q8[6], q8[7]);
+                        *reinterpret_cast<uint2*>(p.attn8 + (size_t)tok * QD + head * HD + ch * 8) = o8;
                     }
                 }
                 LT(15);
@@ -733,19 +796,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         const bool ok = wait(acc_bar, n_acc & 1);
                         LT(18);
                         ++n_acc;
-                        if (ok) {
-                            tc::tc_fence_after_sync();
-                            uint32_t v[32];
-                            tc::tmem_ld32(tmem + lane_off + half * 32, v);
-                            tc::tmem_ld_wait();
-                            const int n = tile * 128 + quad * 32 + lane;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int m = half * 32 + j;
-                                if (m < S) __stcg(p.part + ((size_t)ks * MAXS + m) * D + n, __uint_as_float(v[j]));
-                            }
-                            tc::tc_fence_before_sync();
-                        }
+                        store_partial(ok, ks, tile);
                     }
                 }
                 LT(19);
@@ -782,14 +833,14 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         if (ok) {
                             tc::tc_fence_after_sync();
                             uint32_t v[32];
-                            tc::tmem_ld32(tmem + lane_off + half * 32, v);
-                            tc::tmem_ld_wait();
+                            ld_acc(v);
                             float* exr = ex + (rr >> 6) * (MAXS * 64) + (rr & 63);
 #pragma unroll
                             for (int j = 0; j < 32; ++j) exr[(half * 32 + j) * 64] = bf16r(__uint_as_float(v[j]) * alpha);
                             tc::tc_fence_before_sync();
                         }
                         work_sync();
+                        LT(34);
                         {
                             // thread = hidden unit h of this tile for tokens tg, tg + 4, ...: all operands first, then
                             // the arithmetic, then the stores (32 consecutive bytes per warp and token)
@@ -830,19 +881,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         const bool ok = wait(acc_bar, n_acc & 1);
                         LT(30);
                         ++n_acc;
-                        if (ok) {
-                            tc::tc_fence_after_sync();
-                            uint32_t v[32];
-                            tc::tmem_ld32(tmem + lane_off + half * 32, v);
-                            tc::tmem_ld_wait();
-                            const int n = tile * 128 + quad * 32 + lane;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int m = half * 32 + j;
-                                if (m < S) __stcg(p.part + ((size_t)ks * MAXS + m) * D + n, __uint_as_float(v[j]));
-                            }
-                            tc::tc_fence_before_sync();
-                        }
+                        store_partial(ok, ks, tile);
                     }
                 }
                 LT(31);
@@ -896,7 +935,7 @@ static int loop_layout(int S, int prefix_len, LoopLayout* o) {
     o->attn8 = off; off += (long long)el::MAXS * el::QD;
     o->hid8 = off; off += (long long)el::MAXS * el::HID;
     o->part = off; off += 4LL * el::MAXS * el::D * 4;
-    o->po = off; off += (long long)o->units * 128 * el::HD * 4;
+    o->po = off; off += (long long)o->units * 128 * el::HD * 2;
     o->plse = off; off += align_up((long long)o->units * 128 * 4, 256);
     o->total = off;
     return FRT_OK;
@@ -949,7 +988,7 @@ int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream
     if (per_sm < 1) return FRT_ERR_UNSUPPORTED;
     const int G = sms;
     // every CTA owns at most one unit per phase and one token row
-    if (G < el::U_GU || G < a.S || G < lay.units) return FRT_ERR_UNSUPPORTED;
+    if (G < el::U_GU || G < a.S || G < el::U_QKV + lay.units) return FRT_ERR_UNSUPPORTED;
 
     CUtensorMap tmQKV, tmO, tmGU, tmD;
     rc = get_tmap_2d_u8(&tmQKV, a.w_qkv, (uint64_t)a.layers * el::NQKV, el::D, el::D, 128);
@@ -959,6 +998,11 @@ int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream
     rc = get_tmap_2d_u8(&tmGU, a.w_gu, (uint64_t)a.layers * 2 * el::HID, el::D, el::D, 64);
     if (rc) return rc;
     rc = get_tmap_2d_u8(&tmD, a.w_d, (uint64_t)a.layers * el::D, el::HID, el::HID, 128);
+    if (rc) return rc;
+    CUtensorMap tmK, tmV;      // caches as byte matrices: one row of 512 bytes per key
+    rc = get_tmap_2d_u8(&tmK, a.k_cache, (uint64_t)a.layers * a.kv_rows, el::HD * 2, el::HD * 2, el::BKV);
+    if (rc) return rc;
+    rc = get_tmap_2d_u8(&tmV, a.v_cache, (uint64_t)a.layers * a.kv_rows, el::HD * 2, el::HD * 2, el::BKV);
     if (rc) return rc;
 
     uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
@@ -977,7 +1021,7 @@ int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream
     p.attn8 = ws + lay.attn8;
     p.hid8 = ws + lay.hid8;
     p.part = reinterpret_cast<float*>(ws + lay.part);
-    p.po = reinterpret_cast<float*>(ws + lay.po);
+    p.po = reinterpret_cast<__nv_bfloat16*>(ws + lay.po);
     p.plse = reinterpret_cast<float*>(ws + lay.plse);
     p.steps = a.steps; p.layers = a.layers; p.S = a.S; p.prefix_len = a.prefix_len; p.kv_rows = a.kv_rows;
     p.T = lay.T; p.chunks_total = lay.chunks; p.nsplit = lay.nsplit; p.att_units = lay.units; p.att_tiles = lay.tiles;
@@ -995,7 +1039,7 @@ int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, el::expert_loop_kernel, tmQKV, tmO, tmGU, tmD, p);
+    e = cudaLaunchKernelEx(&cfg, el::expert_loop_kernel, tmQKV, tmO, tmGU, tmD, tmK, tmV, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }
 
