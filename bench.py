@@ -237,6 +237,8 @@ def run_ours(args):
         from flashrt_b200 import flash_rt_kernels as fvk
         status = fvk.tensor_core_status()
         peak, peak_src = _peaks()
+        if args.loop_trace:
+            loop_trace_report(ms)
         if args.lean:
             print(json.dumps({"metric": METRIC, "value": round(ms, 4), "unit": "ms", "lean": True,
                               "e2e_ms": round(e2e_ms, 4), "tensor_core_status": status}), flush=True)
@@ -553,6 +555,43 @@ def run_prefix(args):
     print(json.dumps(line), flush=True)
 
 
+def loop_trace_report(ms: float) -> None:
+    """Phase timing of the persistent loop kernel from its device-side stamps (library built with
+    ``FRT_NVCC_EXTRA=-DFRT_LOOP_TRACE``): worker thread 0 of every CTA stamps %globaltimer at the start and end of each
+    phase of two decoder blocks of the second Euler step, the MMA thread when it sees its operands and when it has
+    issued its last MMA.  Printed to stderr; the JSON line on stdout is unchanged."""
+    import ctypes
+    import numpy as np
+    from flashrt_b200 import _lib
+    lib = _lib.load()
+    if not hasattr(lib, "frt_loop_trace_read"):
+        print("loop trace: the library was built without -DFRT_LOOP_TRACE", file=sys.stderr)
+        return
+    buf = (ctypes.c_ulonglong * (160 * 128))()
+    lib.frt_loop_trace_read.argtypes = [ctypes.c_void_p]
+    lib.frt_loop_trace_read(ctypes.addressof(buf))
+    t = np.frombuffer(buf, dtype=np.uint64).reshape(160, 128).astype(np.int64)
+    names = ["A rows", "B qkv", "C attention", "D combine", "E o-proj", "F rows", "G gate|up", "H down"]
+    tr = {1: 40, 4: 42, 6: 44, 7: 46}
+    out = [f"persistent loop: {ms:.3f} ms per loop; phase times in us (second Euler step, blocks 0 and 1)"]
+    for blk in range(2):
+        tt = t[:148, blk * 64: blk * 64 + 64]
+        out.append(f"block {blk}: {(tt[:, 32].max() - tt[:, 0].min()) / 1e3:.2f} us")
+        out.append("  phase         whole  slowest-CTA work  barrier (last arrival -> first release)  owners: operands in smem | MMA issue | epilogue")
+        for k, nm in enumerate(names):
+            st, en, nx = tt[:, 4 * k], tt[:, 4 * k + 3], tt[:, 4 * k + 4]
+            line = (f"  {nm:12s} {(nx.max() - st.min()) / 1e3:6.2f} {(en - st).max() / 1e3:10.2f} "
+                    f"{(nx.min() - en.max()) / 1e3:18.2f}")
+            if k in tr:
+                own = (tt[:, tr[k]] > st) & (tt[:, tr[k]] < st + 100000)
+                if own.any():
+                    med = lambda a, b: float(np.median((tt[:, a] - tt[:, b])[own])) / 1e3  # noqa: E731
+                    line += (f"{'':22s}{int(own.sum()):3d}: {med(tr[k], 4 * k):.2f} | {med(tr[k] + 1, tr[k]):.2f} | "
+                             f"{med(4 * k + 3, 4 * k + 2):.2f}")
+            out.append(line)
+    print("\n".join(out), file=sys.stderr, flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -565,6 +604,9 @@ def main():
                          "(Nsight Compute cannot profile programmatically dependent launches)")
     ap.add_argument("--persistent-loop", action="store_true",
                     help="pi05 / fp8: run the whole denoise loop as one persistent cooperative kernel")
+    ap.add_argument("--loop-trace", action="store_true",
+                    help="with --persistent-loop and a library built with FRT_NVCC_EXTRA=-DFRT_LOOP_TRACE: print the "
+                         "kernel's phase timing to stderr")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
     ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops", "prefix"],

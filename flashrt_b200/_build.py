@@ -40,9 +40,14 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 
 def build_native(force: bool = False, verbose: bool = False) -> str:
-    """Compile every ``csrc/*.cu`` and link ``libflashrt_b200.so``.  Returns its path."""
+    """Compile every ``csrc/*.cu`` and link ``libflashrt_b200.so``.  Returns its path.
+
+    ``FRT_NVCC_EXTRA`` (environment, space separated) appends compiler flags, e.g. ``-DFRT_LOOP_TRACE`` for the
+    phase stamps of the persistent loop kernel that ``bench.py --persistent-loop --loop-trace`` reads (use
+    ``--force`` when switching it on or off: the objects do not depend on the environment)."""
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
+    extra = os.environ.get("FRT_NVCC_EXTRA", "").split()
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "flashrt_b200.h"))
     headers = [h for h in headers if os.path.exists(h)]
@@ -53,7 +58,7 @@ def build_native(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ, s[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + ["-I", os.path.join(os.path.dirname(HERE), "include"), "-c", src, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + extra + ["-I", os.path.join(os.path.dirname(HERE), "include"), "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")
