@@ -100,14 +100,14 @@ __device__ __forceinline__ float bf16r(float f) { return __bfloat162float(__floa
 __device__ __forceinline__ void work_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // unit of GEMM phase `ph` (0 QKV, 1 O, 2 gate|up, 3 down) of global layer `gl` that CTA `cta` owns, or -1
-__device__ __forceinline__ int gemm_unit(int G, int cta, int gl, int ph) {
+__host__ __device__ __forceinline__ int gemm_unit(int G, int cta, int gl, int ph) {
     const int off = ph == 0 ? 0 : ph == 1 ? U_QKV : ph == 2 ? U_QKV + U_O : U_QKV + U_O + U_GU;
     const int n = ph == 0 ? U_QKV : ph == 1 ? U_O : ph == 2 ? U_GU : U_D;
     const long long g0 = (long long)gl * U_LAYER + off;
     const int u = (int)((((long long)cta - g0) % G + G) % G);
     return u < n ? u : -1;
 }
-__device__ __forceinline__ int att_unit(int G, int cta, int gl, int units) {
+__host__ __device__ __forceinline__ int att_unit(int G, int cta, int gl, int units) {
     const long long g0 = (long long)gl * U_LAYER + U_QKV;     // right behind the block's QKV units
     const int u = (int)((((long long)cta - g0) % G + G) % G);
     return u < units ? u : -1;
@@ -1041,6 +1041,15 @@ int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, el::expert_loop_kernel, tmQKV, tmO, tmGU, tmD, tmK, tmV, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
+}
+
+// The static schedule of the loop kernel, evaluated on the host (no GPU needed): which unit of `phase` (0 QKV, 1 output
+// projection, 2 gate|up, 3 down, 4 attention with `att_units` units) of global block `gl` = step * layers + layer
+// the CTA `cta` of a grid of G owns; *unit_out = -1 when it owns none.
+int frt_b200_expert_loop_schedule(int G, int cta, int gl, int phase, int att_units, int* unit_out) {
+    if (!unit_out || G < 1 || cta < 0 || cta >= G || gl < 0 || phase < 0 || phase > 4) return FRT_ERR_INVALID;
+    *unit_out = phase < 4 ? el::gemm_unit(G, cta, gl, phase) : el::att_unit(G, cta, gl, att_units);
+    return FRT_OK;
 }
 
 // device status word of the persistent loop kernel (0 = no bounded wait ever gave up); code 1 weight producer,

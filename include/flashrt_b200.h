@@ -344,6 +344,12 @@ typedef struct frt_b200_expert_loop_args {
 int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream);
 /* no counterpart in the reference: size of the loop kernel's scratch for S action tokens behind prefix_len keys */
 int frt_b200_expert_loop_workspace_bytes(int S, int prefix_len, long long* out_bytes);
+/* no counterpart in the reference: the loop kernel's static work assignment, evaluated on the HOST (no GPU needed).
+ * Every unit of a phase (0 QKV: 20 units, 1 output projection: 16, 2 gate|up: 64, 3 down: 32, 4 attention:
+ * att_units) of block gl = step * layers + layer belongs to exactly one CTA of the grid of G; *unit_out (host) = the
+ * unit of CTA `cta`, or -1.  The CTAs of a block's attention units own none of its QKV units (their operand space
+ * receives the prefetched K/V chunk while the QKV phase runs). */
+int frt_b200_expert_loop_schedule(int G, int cta, int gl, int phase, int att_units, int* unit_out);
 /* Status word of the loop kernel (0 = no bounded wait gave up; else code | CTA << 8, code 1 weight producer, 2 MMA
  * issuer, 3 worker, 4 grid barrier); synchronises the device. */
 int frt_b200_expert_loop_status(int reset);

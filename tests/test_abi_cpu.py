@@ -85,3 +85,56 @@ def test_stand_in_modules_accept_the_reference_binding_signatures():
             if positional != ref_args:
                 problems.append(f"{mod_name}.{name}: {positional} != reference {ref_args}")
     assert not problems, "\n".join(problems)
+
+
+def test_expert_loop_args_struct_matches_the_header():
+    """The ctypes mirror of ``frt_b200_expert_loop_args`` has the header's members in the header's order, and the
+    size a C compiler gives the struct."""
+    import subprocess
+    import tempfile
+    from flashrt_b200.pi05_decoder import ExpertLoopArgs
+    text = open(_lib.HEADER_PATH).read()
+    body = re.search(r"typedef struct frt_b200_expert_loop_args \{(.*?)\} frt_b200_expert_loop_args;", text, re.S).group(1)
+    names = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if decl:
+            names += [n.strip().lstrip("*") for n in re.sub(r"^(const\s+)?(void|long long|int)\s*", "", decl).split(",")]
+    assert names == [f[0] for f in ExpertLoopArgs._fields_]
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "s.c")
+        open(src, "w").write('#include <stdio.h>\n#include "flashrt_b200.h"\n'
+                             'int main(void){printf("%zu", sizeof(frt_b200_expert_loop_args));return 0;}\n')
+        exe = os.path.join(d, "s")
+        subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), src, "-o", exe], check=True)
+        size = int(subprocess.run([exe], capture_output=True, text=True, check=True).stdout)
+    assert size == ctypes.sizeof(ExpertLoopArgs)
+
+
+def test_expert_loop_schedule_covers_every_unit_once():
+    """Host evaluation of the persistent kernel's static schedule: in every phase of every block each unit has exactly
+    one owner, no CTA owns two units of a phase, attention CTAs own no QKV unit of the same block, and over the whole
+    loop every CTA streams the same number of weight units to within one."""
+    lib = _lib.load()
+    G, att_units, blocks = 148, 52, 180
+    counts = {0: 20, 1: 16, 2: 64, 3: 32, 4: att_units}
+    out = ctypes.c_int(0)
+    per_cta = [0] * G
+    for gl in list(range(0, 40)) + [blocks - 1]:
+        owners = {}
+        for ph, n in counts.items():
+            seen = {}
+            for cta in range(G):
+                assert lib.frt_b200_expert_loop_schedule(G, cta, gl, ph, att_units, ctypes.addressof(out)) == 0
+                u = out.value
+                assert -1 <= u < n
+                if u >= 0:
+                    assert u not in seen
+                    seen[u] = cta
+                    if ph < 4 and gl < 37:           # 37 blocks x 132 units = 33 full rounds of 148
+                        per_cta[cta] += 1
+            assert sorted(seen) == list(range(n)), (gl, ph)
+            owners[ph] = set(seen.values())
+        assert not (owners[0] & owners[4])
+    assert max(per_cta) - min(per_cta) <= 1
+    assert lib.frt_b200_expert_loop_schedule(G, G, 0, 0, att_units, ctypes.addressof(out)) == -1
