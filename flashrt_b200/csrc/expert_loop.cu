@@ -23,7 +23,15 @@
 // the same share of the weights.  Weights do not depend on activations: a dedicated warp per CTA walks the CTA's
 // static unit list and keeps a ring of TMA stages full ACROSS phase boundaries, so the HBM stream of the next
 // phases runs while the CTA waits at a barrier.  Activations (a few hundred KB, L2 resident) are fetched with plain
-// loads after each barrier and written into the swizzled operand layout by the worker warps.
+// loads after each barrier and written into the swizzled operand layout by the worker warps; Q goes to tensor memory
+// and is the attention MMA's A operand; the key / value chunks that lie inside the prefix are fetched by TMA at the
+// start of phase A (attention CTAs own no QKV unit of the same block, so their operand space is free until phase C).
+// Partials (split-K fp32, attention bf16 + log-sum-exp) cross CTAs through L2 scratch and are summed in fixed order:
+// replays are bit-reproducible.  The residual row of token r never leaves the registers of CTA r.
+//
+// Measured (18 blocks x 10 steps, 50 tokens, 768 prefix keys): 10.5 ms per loop against 9.75 ms for the graph of 1300
+// operator launches, i.e. a phase costs what a launch costs (barrier 1.1-1.4 us + one L2 round trip for the operand
+// 1.5 us + 32 MMAs 2 us + epilogue); build with -DFRT_LOOP_TRACE for the per-phase stamps.
 //
 // Warps: 0 = weight TMA producer, 1 = MMA issuer (one thread), 2-9 = workers (operand loads, softmax, epilogues,
 // row phases, grid barrier).  Every wait is bounded by one wall-clock deadline taken at kernel start; a wait that
