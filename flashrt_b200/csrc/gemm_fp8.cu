@@ -908,6 +908,7 @@ static int dispatch_small_m(const void* A, const void* W, GemmParams p, int K, i
 }
 
 #include "gemm_persistent.cuh"
+#include "gemm_pair.cuh"
 
 template <int EPI>
 static int dispatch_small_m_nvfp4(const void* A, const void* W, GemmParams p, int K, int M, int tiles, int splits,
@@ -928,7 +929,8 @@ extern "C" {
 // D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . W(N,K)^T + bias
 // A, W: FP8 E4M3 row-major, K contiguous.  K % 16 == 0; A, W 16-byte aligned.
 // splits: 0 = choose, otherwise the split-K factor (clamped to [1, 8]).
-// flags: bit0 = programmatic dependent launch.
+// flags: bit0 = programmatic dependent launch; bit1 = one-tile-per-CTA kernel for M > 256; bit3 = CTA-pair kernel
+// (256 x 256 tiles, M > 256, N >= 256, no split-K).
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream) {
@@ -948,6 +950,8 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     bool pdl = flags & 1;
     if (M <= 256) return dispatch_small_m<EPI_BF16>(A, W, p, K, M, (N + 127) / 128, splits, pdl, s);
     int sp = splits > 0 ? pick_splits(1, p.kb_total, splits > 8 ? 8 : splits) : 1;
+    // flags bit3: one 256 x 256 tile per CTA pair (cta_group::2); opt-in until it has been measured on a GPU
+    if (sp == 1 && (flags & 8) && N >= 256) return launch_gemm_pair(A, W, p, K, pdl, s);
     if (sp == 1 && !(flags & 2)) {      // flags bit1 keeps the one-tile-per-CTA kernel (for comparison runs)
         if (N >= 256) return launch_gemm_persistent<256, EPI_P_BF16>(A, W, p, K, pdl, s);
         if (N > 64) return launch_gemm_persistent<128, EPI_P_BF16>(A, W, p, K, pdl, s);

@@ -234,11 +234,12 @@ class GemmRunner:
     """
 
     def fp8_nt_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
-                   one_tile_per_cta=False):
+                   one_tile_per_cta=False, cta_pair=False):
         """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form.
-        ``one_tile_per_cta`` selects the non-persistent large-M kernel (same result; kept for comparison runs)."""
+        ``one_tile_per_cta`` selects the non-persistent large-M kernel (same result; kept for comparison runs);
+        ``cta_pair`` the 256 x 256-tile kernel on CTA pairs (M > 256, N >= 256; opt-in)."""
         call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits,
-             _f(pdl) | (2 if one_tile_per_cta else 0), stream)
+             _f(pdl) | (2 if one_tile_per_cta else 0) | (8 if cta_pair else 0), stream)
 
     def fp8_nt_dev_gate_res_norm_fp8(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, style, out, d_scale_out,
                                      stream=0, *, eps=1e-6, pdl=False, splits=0):

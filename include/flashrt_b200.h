@@ -105,7 +105,9 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
  *   A, W: E4M3, row-major, K contiguous, 16-byte aligned, K % 16 == 0.  d_scale_* and bias may be NULL.
  *   splits: 0 = choose; else split-K factor in [1, 16] (reduced inside a thread-block cluster).
  *   M > 256 runs as a persistent kernel (one CTA per SM walking the tile list, two accumulators in tensor memory so
- *   that the epilogue overlaps the next tile's MMAs); flags bit 1 selects the one-tile-per-CTA kernel instead. */
+ *   that the epilogue overlaps the next tile's MMAs); flags bit 1 selects the one-tile-per-CTA kernel instead;
+ *   flags bit 3 (M > 256, N >= 256, no split-K) a kernel with one 256 x 256 tile per CTA pair (tcgen05 cta_group::2:
+ *   each CTA stages its 128 rows of A and 128 of the 256 weight rows, the leader issues the MMAs for both). */
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream);

@@ -1,6 +1,8 @@
 """GPU parity: tcgen05 FP8 GEMM vs the oracle (fp64-accumulated C loop for small cases, fp32 BLAS on the
 decoded operands for large ones).  Floating-point bar: cosine >= 0.999 and max-abs <= 2e-2 x RMS(ref);
 the tighter bound asserted here is one bf16 ulp of the value plus a small RMS-relative slack."""
+import os
+
 import numpy as np
 import pytest
 
@@ -221,6 +223,30 @@ def test_gemm_fp8_persistent_equals_one_tile_per_cta(M, N, K):
     assert fvk.tensor_core_status() == 0
     assert np.array_equal(d_1.get(), d_2.get())
     _check(d_1.get(), _ref(A, W, sa, sb, bias))
+
+
+@pytest.mark.skipif(os.environ.get("FRT_TEST_CTA_PAIR") != "1",
+                    reason="the CTA-pair GEMM was written after this build's GPU time was spent and has not run on a "
+                           "GPU yet; set FRT_TEST_CTA_PAIR=1 to run it")
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (512, 256, 128), (1000, 700, 512), (8192, 3072, 3072)])
+def test_gemm_fp8_cta_pair_kernel(M, N, K):
+    """256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) against the torch reference, and against the persistent
+    one-CTA kernel (same K order per output: expected identical, asserted to within the bf16 rounding of the result)."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M + 7 * N + K)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    bias = rand_bf16(rng, (N,), 0.3)
+    d_A, d_W, d_b, d_sa, d_sb = Dev(A), Dev(W), Dev(bias), f32(sa), f32(sb)
+    d_1, d_2 = zeros((M, N), np.uint16), zeros((M, N), np.uint16)
+    g = fvk.GemmRunner()
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_1.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_2.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr, cta_pair=True)
+    assert fvk.tensor_core_status() == 0
+    _check(d_2.get(), _ref(A, W, sa, sb, bias))
+    a, b = d_1.get().astype(np.int64), d_2.get().astype(np.int64)
+    assert np.abs(a - b).max() <= 1          # bf16 bit patterns at most one step apart
 
 
 @pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (1000, 200, 512), (3000, 14336 // 8, 3072)])
