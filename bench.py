@@ -449,6 +449,7 @@ def run_ops(args):
         del res, x, out
     # ---- GEMMs
     NK = [(1024, 1024), (4096, 1024), (1024, 4096), (3072, 3072), (14336, 3072), (3072, 14336)]
+    gemm_flags = 8 if args.cta_pair else 0       # bit 3: the 256 x 256-tile kernel on CTA pairs for M > 256
     for kind in ("fp8", "nvfp4"):
         for M in (16, 50, 256, 2048, 8192, 20480):
             for N, K in NK:
@@ -463,7 +464,8 @@ def run_ops(args):
                     def enq():
                         for w in Ws:
                             _lib.call("frt_b200_gemm_fp8_nt", A.data_ptr(), w.data_ptr(), D.data_ptr(), M, N, K,
-                                      one.data_ptr(), one.data_ptr(), 1.0, None, 0, 0, s.cuda_stream)
+                                      one.data_ptr(), one.data_ptr(), 1.0, None, 0, gemm_flags if M > 256 else 0,
+                                      s.cuda_stream)
                 else:
                     sfa = torch.full((fp4.sfa_size_bytes(M, K),), 0x38, dtype=torch.uint8, device="cuda")
                     sfw = torch.full((fp4.sfa_size_bytes(N, K),), 0x30, dtype=torch.uint8, device="cuda")
@@ -490,6 +492,7 @@ def run_ops(args):
                                                                            "note": "tensor peaks = 2x / 4x the measured cuBLAS bf16 burst"},
                        "l2": ("norm and M <= 256 GEMM cases cycle through distinct row / weight buffers totalling more than "
                               "L2; M >= 2048 GEMM cases alternate two weight buffers (tensor-bound)"),
+                       "large_m_fp8_kernel": "cta pair (256 x 256 tiles)" if args.cta_pair else "persistent, one CTA per tile",
                        "tensor_core_status": fvk.tensor_core_status(), "table": table},
             "gpu_launches": launches}
     print(json.dumps(line), flush=True)
@@ -626,6 +629,8 @@ def main():
                          "(Nsight Compute cannot profile programmatically dependent launches)")
     ap.add_argument("--persistent-loop", action="store_true",
                     help="pi05 / fp8: run the whole denoise loop as one persistent cooperative kernel")
+    ap.add_argument("--cta-pair", action="store_true",
+                    help="--workload ops: run the FP8 GEMMs with M > 256 through the CTA-pair kernel")
     ap.add_argument("--loop-trace", action="store_true",
                     help="with --persistent-loop and a library built with FRT_NVCC_EXTRA=-DFRT_LOOP_TRACE: print the "
                          "kernel's phase timing to stderr")
