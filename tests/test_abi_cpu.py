@@ -138,3 +138,20 @@ def test_expert_loop_schedule_covers_every_unit_once():
         assert not (owners[0] & owners[4])
     assert max(per_cta) - min(per_cta) <= 1
     assert lib.frt_b200_expert_loop_schedule(G, G, 0, 0, att_units, ctypes.addressof(out)) == -1
+
+
+def test_expert_loop_entry_points_validate_before_touching_the_device():
+    """Argument checks of the single-launch loop run on the host: no GPU is needed to be refused."""
+    from flashrt_b200.pi05_decoder import ExpertLoopArgs
+    lib = _lib.load()
+    n = ctypes.c_longlong(0)
+    assert lib.frt_b200_expert_loop_workspace_bytes(50, 768, ctypes.addressof(n)) == 0
+    # sync words + FP8 / bf16 activations + split-K partials + 4 x 13 attention units of 128 x 256 bf16 + their lse
+    assert n.value == 256 + 64 * 1024 + 64 * 2048 * 2 + 64 * 2048 + 64 * 4096 + 4 * 64 * 1024 * 4 + 52 * 128 * 256 * 2 \
+        + 52 * 128 * 4
+    assert lib.frt_b200_expert_loop_workspace_bytes(65, 768, ctypes.addressof(n)) == -2      # more than 64 tokens
+    assert lib.frt_b200_expert_loop_workspace_bytes(50, 768, None) == -1
+    a = ExpertLoopArgs()
+    assert lib.frt_b200_expert_loop_fp8(None, ctypes.sizeof(a), None) == -1
+    assert lib.frt_b200_expert_loop_fp8(ctypes.addressof(a), ctypes.sizeof(a) - 8, None) == -1   # struct size mismatch
+    assert lib.frt_b200_expert_loop_fp8(ctypes.addressof(a), ctypes.sizeof(a), None) == -1       # null pointers
