@@ -29,6 +29,7 @@
 #include "common.cuh"
 #include "tc05.cuh"
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -909,6 +910,7 @@ static int dispatch_small_m(const void* A, const void* W, GemmParams p, int K, i
 
 #include "gemm_persistent.cuh"
 #include "gemm_pair.cuh"
+#include "gemm_tok.cuh"
 
 template <int EPI>
 static int dispatch_small_m_nvfp4(const void* A, const void* W, GemmParams p, int K, int M, int tiles, int splits,
@@ -923,6 +925,20 @@ static int dispatch_small_m_nvfp4(const void* A, const void* W, GemmParams p, in
 }  // namespace frt
 
 using namespace frt;
+
+// flags bits 8-9: tile-width hint of the token-major small-M kernel (1 = 64, 2 = 128, 3 = 256 weight rows)
+static inline int tok_bn_hint(int flags) {
+    const int h = (flags >> 8) & 3;
+    return h == 1 ? 64 : h == 2 ? 128 : h == 3 ? 256 : 0;
+}
+static inline int tok_split_hint(int splits) {
+    return (splits == 1 || splits == 2 || splits == 4 || splits == 8) ? splits : 0;
+}
+// the token-major kernel serves M <= 256 rows, K in whole 128-byte k-blocks, 16-byte output rows; flags bit 4 keeps
+// the swapped (weights-on-lanes) kernel
+static inline bool tok_eligible(int M, int N, int K, int flags) {
+    return M <= 256 && (K % 128) == 0 && (N % 8) == 0 && !(flags & 16);
+}
 
 extern "C" {
 
@@ -948,6 +964,13 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     p.kb_total = (K + 127) / 128;
     cudaStream_t s = (cudaStream_t)stream;
     bool pdl = flags & 1;
+    if (tok_eligible(M, N, K, flags)) {
+        TokParams t = {};
+        t.M = M; t.N = N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = alpha_host;
+        t.out = (__nv_bfloat16*)D; t.bias = (const __nv_bfloat16*)bias;
+        int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_BF16>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits), pdl, s);
+        if (rc != FRT_ERR_UNSUPPORTED) return rc;
+    }
     if (M <= 256) return dispatch_small_m<EPI_BF16>(A, W, p, K, M, (N + 127) / 128, splits, pdl, s);
     int sp = splits > 0 ? pick_splits(1, p.kb_total, splits > 8 ? 8 : splits) : 1;
     // flags bit3: one 256 x 256 tile per CTA pair (cta_group::2); opt-in until it has been measured on a GPU
@@ -991,6 +1014,15 @@ int frt_b200_gemm_fp8_nt_rope_split(const void* A, const void* W, int M, int K, 
     p.k_dim = k_dim;
     p.v_dim = v_dim;
     p.head_dim = head_dim;
+    if (tok_eligible(M, p.N, K, flags) && M <= 128 && (head_dim % 8) == 0) {
+        TokParams t = {};
+        t.M = M; t.N = p.N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+        t.rope = p.rope; t.outQ = p.outQ; t.outK = p.outK; t.outV = p.outV; t.devpos = devpos;
+        t.q_dim = q_dim; t.k_dim = k_dim; t.v_dim = v_dim; t.head_dim = head_dim;
+        int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_ROPE>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
+                                                             flags & 1, (cudaStream_t)stream);
+        if (rc != FRT_ERR_UNSUPPORTED) return rc;
+    }
     return dispatch_small_m<EPI_ROPE_SPLIT>(A, W, p, K, M, (p.N + 127) / 128, splits, flags & 1, (cudaStream_t)stream);
 }
 
@@ -1014,6 +1046,14 @@ int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int
     p.out8 = (uint8_t*)out8;
     p.out_scale = d_out_scale;
     p.half = half;
+    if (tok_eligible(M, p.N, K, flags) && M <= 128 && (half % 128) == 0) {
+        TokParams t = {};
+        t.M = M; t.N = p.N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+        t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
+        int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, 256, tok_split_hint(splits), flags & 1,
+                                                              (cudaStream_t)stream);
+        if (rc != FRT_ERR_UNSUPPORTED) return rc;
+    }
     return dispatch_small_m<EPI_GEGLU_FP8>(A, W, p, K, M, half / 64, splits, flags & 1, (cudaStream_t)stream);
 }
 
@@ -1141,6 +1181,83 @@ int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8,
     p.out_scale = d_out_scale;
     if (N >= 256) return launch_gemm_persistent<256, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
     return launch_gemm_persistent<128, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
+}
+
+// Row-parallel projection with the gated residual update fused (M <= 128, N % 64 == 0, K % 128 == 0):
+//   o = bf16(sa * sb * A . W^T);  residual(M, N) <- bf16(residual + o * gate),  gate (N,) shared by all rows;
+//   stats_out[tile][m] (row pitch 128 floats, N / tile_width rows; may be NULL) = sum over the tile's features of the
+//   squares of the UNROUNDED updated residual -- the first pass of gate_residual_ada_norm_fp8
+//   (csrc/kernels/fusion.cu:41-47); frt_b200_norm_gemm_fp8_nt_* finishes the norm inside the next projection.
+// *stat_tiles (host int, may be NULL) receives the number of statistics rows written.
+int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                       const float* d_scale_b, void* residual, const void* gate, float* stats_out,
+                                       int* stat_tiles, int splits, int flags, void* stream) {
+    if (!A || !W || !residual || !gate || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if ((K % 128) || M > 128 || (N % 64)) return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(residual) & 15) || (reinterpret_cast<uintptr_t>(gate) & 15)) return FRT_ERR_INVALID;
+    TokParams t = {};
+    t.M = M; t.N = N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+    t.resid = (__nv_bfloat16*)residual; t.gate = (const __nv_bfloat16*)gate; t.stats_out = stats_out;
+    TokPlan pl;
+    int bn = tok_bn_hint(flags);
+    if (bn == 0 && (N % 128)) bn = 64;
+    if (!tok_plan(N, K, 1, TOK_EPI_RESID, TOK_PRO_TMA, tok_sm_count(), bn, tok_split_hint(splits), &pl))
+        return FRT_ERR_UNSUPPORTED;
+    if (stat_tiles) *stat_tiles = N / pl.BN;
+    if (M == 0) return FRT_OK;
+    if (pl.BN == 128)
+        return launch_gemm_tok<128, TOK_PRO_TMA, TOK_EPI_RESID>(A, W, t, K, pl, flags & 1, (cudaStream_t)stream);
+    return launch_gemm_tok<64, TOK_PRO_TMA, TOK_EPI_RESID>(A, W, t, K, pl, flags & 1, (cudaStream_t)stream);
+}
+
+// QKV projection whose FP8 input is produced inside the kernel from the residual stream (M <= 128, K = 128, 256, 512
+// per split): a = e4m3(clamp(((x * rms) * (1 + scale) + shift) / *d_scale_a, +-448)) with
+//   rms[m] = 1 / sqrt(sum_t stats_in[t][m] / K + eps)  (stats_in: n_stat rows of 128 floats, summed in order),
+//   style = [scale (K) | shift (K)] one bf16 row shared by all tokens (unit norm weight),
+// followed by the projection and the RoPE + split + KV-append epilogue of frt_b200_gemm_fp8_nt_rope_split.
+// Stands for gate_residual_ada_norm_fp8 (second pass, csrc/kernels/fusion.cu:48-81) + fp8_nn_dev + qkv_split_rope.
+int frt_b200_norm_gemm_fp8_nt_rope_split(const void* x, const float* stats_in, int n_stat, const void* style, float eps,
+                                         const void* W, int M, int K, const float* d_scale_a, const float* d_scale_b,
+                                         const void* rope, void* Q, void* Kout, void* Vout, const int* devpos,
+                                         int q_dim, int k_dim, int v_dim, int head_dim, int splits, int flags,
+                                         void* stream) {
+    if (!x || !stats_in || !style || !W || !rope || !Q || !Kout || !Vout || !d_scale_a || M < 0 || K <= 0 || n_stat <= 0)
+        return FRT_ERR_INVALID;
+    if (q_dim <= 0 || k_dim <= 0 || v_dim <= 0 || head_dim <= 0) return FRT_ERR_INVALID;
+    if ((K % 128) || M > 128 || (head_dim % 8) || (q_dim % head_dim) || (k_dim % head_dim) || (v_dim % 8))
+        return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(style) & 15)) return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    TokParams t = {};
+    t.M = M; t.N = q_dim + k_dim + v_dim; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+    t.rope = (const __nv_bfloat16*)rope; t.outQ = (__nv_bfloat16*)Q; t.outK = (__nv_bfloat16*)Kout;
+    t.outV = (__nv_bfloat16*)Vout; t.devpos = devpos;
+    t.q_dim = q_dim; t.k_dim = k_dim; t.v_dim = v_dim; t.head_dim = head_dim;
+    t.x = (const __nv_bfloat16*)x; t.stats_in = stats_in; t.n_stat = n_stat; t.style = (const __nv_bfloat16*)style;
+    t.eps = eps;
+    return dispatch_gemm_tok<TOK_PRO_NORM, TOK_EPI_ROPE>(nullptr, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
+                                                        flags & 1, (cudaStream_t)stream);
+}
+
+// gate|up projection with the same in-kernel adaRMS -> FP8 producer in front and the GeGLU -> FP8 epilogue of
+// frt_b200_gemm_fp8_nt_geglu_fp8 behind (M <= 128, half % 128 == 0).
+int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, int n_stat, const void* style, float eps,
+                                        const void* W, void* out8, int M, int half, int K, const float* d_scale_a,
+                                        const float* d_scale_b, const float* d_out_scale, int splits, int flags,
+                                        void* stream) {
+    if (!x || !stats_in || !style || !W || !out8 || !d_scale_a || !d_out_scale || M < 0 || half <= 0 || K <= 0 ||
+        n_stat <= 0)
+        return FRT_ERR_INVALID;
+    if ((K % 128) || M > 128 || (half % 128)) return FRT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(style) & 15)) return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    TokParams t = {};
+    t.M = M; t.N = 2 * half; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+    t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
+    t.x = (const __nv_bfloat16*)x; t.stats_in = stats_in; t.n_stat = n_stat; t.style = (const __nv_bfloat16*)style;
+    t.eps = eps;
+    return dispatch_gemm_tok<TOK_PRO_NORM, TOK_EPI_GEGLU>(nullptr, W, t, K, 256, tok_split_hint(splits), flags & 1,
+                                                         (cudaStream_t)stream);
 }
 
 // returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)

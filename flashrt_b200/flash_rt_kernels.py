@@ -225,6 +225,11 @@ def fp8_gemm_descale_bf16out(A, B, C, M, N, K, act_descale, w_descale, stream=0,
     call("frt_b200_gemm_fp8_nt", A, B, C, M, N, K, act_descale, w_descale, 1.0, None, splits, _f(pdl), stream)
 
 
+def _tile_hint(tile_n: int) -> int:
+    """flags bits 8-9 of the small-M FP8 GEMM entry points: pinned tile width of the token-major kernel."""
+    return {0: 0, 64: 1, 128: 2, 256: 3}[int(tile_n)] << 8
+
+
 class GemmRunner:
     """Stand-in for the reference's cuBLASLt ``GemmRunner`` (``csrc/gemm/gemm_runner.h``).
 
@@ -234,12 +239,42 @@ class GemmRunner:
     """
 
     def fp8_nt_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
-                   one_tile_per_cta=False, cta_pair=False):
+                   one_tile_per_cta=False, cta_pair=False, swapped=False, tile_n=0):
         """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form.
         ``one_tile_per_cta`` selects the non-persistent large-M kernel (same result; kept for comparison runs);
-        ``cta_pair`` the 256 x 256-tile kernel on CTA pairs (M > 256, N >= 256; opt-in)."""
+        ``cta_pair`` the 256 x 256-tile kernel on CTA pairs (M > 256, N >= 256; opt-in).  M <= 256: ``swapped``
+        keeps the weights-on-lanes kernel instead of the token-major one, ``tile_n`` (64 / 128 / 256) pins the
+        token-major kernel's tile width."""
         call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits,
-             _f(pdl) | (2 if one_tile_per_cta else 0) | (8 if cta_pair else 0), stream)
+             _f(pdl) | (2 if one_tile_per_cta else 0) | (8 if cta_pair else 0) | (16 if swapped else 0)
+             | _tile_hint(tile_n), stream)
+
+    # -- the decoder's projections with the norm kernel between them folded in ------------------------------
+    def fp8_nt_dev_gate_residual(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, stats_out, stream=0, *,
+                                 pdl=False, splits=0, tile_n=0) -> int:
+        """``fp8_nt_dev`` + the first pass of ``gate_residual_ada_norm_fp8``: residual <- residual + o * gate and
+        the per-tile row sums of squares into ``stats_out`` (rows of 128 floats).  Returns the number of rows
+        written, which the consuming ``norm_fp8_nt_dev_*`` call takes as ``n_stat``."""
+        import ctypes
+        n = ctypes.c_int(0)
+        call("frt_b200_gemm_fp8_nt_gate_residual", A, B, M, N, K, d_scale_a, d_scale_b, residual, gate,
+             stats_out or None, ctypes.addressof(n), splits, _f(pdl) | _tile_hint(tile_n), stream)
+        return n.value
+
+    def norm_fp8_nt_dev_rope_split(self, x, stats, n_stat, style, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc,
+                                   Vc, q_dim, k_dim, v_dim, head_dim, stream=0, *, eps=1e-6, devpos=0, pdl=False,
+                                   splits=0, tile_n=0):
+        """Second pass of ``gate_residual_ada_norm_fp8`` (adaRMS -> FP8 from the residual rows and the sums of
+        squares in ``stats``) produced inside the QKV projection, then ``qkv_split_rope[_devpos]``."""
+        call("frt_b200_norm_gemm_fp8_nt_rope_split", x, stats, n_stat, style, eps, B, M, K, d_scale_a, d_scale_b,
+             rope_weights, Q, Kc, Vc, devpos or None, q_dim, k_dim, v_dim, head_dim, splits,
+             _f(pdl) | _tile_hint(tile_n), stream)
+
+    def norm_fp8_nt_dev_geglu_fp8(self, x, stats, n_stat, style, B, out, M, half_dim, K, d_scale_a, d_scale_b,
+                                  d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0):
+        """The same producer in front of the gate|up projection, ``gate_geglu_merged_fp8`` behind it."""
+        call("frt_b200_norm_gemm_fp8_nt_geglu_fp8", x, stats, n_stat, style, eps, B, out, M, half_dim, K, d_scale_a,
+             d_scale_b, d_scale_out, splits, _f(pdl), stream)
 
     def fp8_nt_dev_gate_res_norm_fp8(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, style, out, d_scale_out,
                                      stream=0, *, eps=1e-6, pdl=False, splits=0):
@@ -257,16 +292,17 @@ class GemmRunner:
 
     # -- fused forms (no reference counterpart as single calls; each equals two reference calls) ------------
     def fp8_nt_dev_rope_split(self, A, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc, Vc, q_dim, k_dim, v_dim,
-                              head_dim, stream=0, *, devpos=0, pdl=False, splits=0):
+                              head_dim, stream=0, *, devpos=0, pdl=False, splits=0, swapped=False, tile_n=0):
         """``fp8_nt_dev`` into a (M, q+k+v) buffer followed by ``qkv_split_rope[_devpos]``, in one launch."""
         call("frt_b200_gemm_fp8_nt_rope_split", A, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc, Vc,
-             devpos or None, q_dim, k_dim, v_dim, head_dim, splits, _f(pdl), stream)
+             devpos or None, q_dim, k_dim, v_dim, head_dim, splits,
+             _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_geglu_fp8(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, stream=0, *,
-                             pdl=False, splits=0):
+                             pdl=False, splits=0, swapped=False):
         """``fp8_nt_dev`` into a merged (M, 2*half) buffer followed by ``gate_geglu_merged_fp8``, in one launch."""
         call("frt_b200_gemm_fp8_nt_geglu_fp8", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, splits,
-             _f(pdl), stream)
+             _f(pdl) | (16 if swapped else 0), stream)
 
     def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, **kw):
         raise NotBuilt(

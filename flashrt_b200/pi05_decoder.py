@@ -296,6 +296,8 @@ class Pi05DecoderPipeline(StepIO):
         self.attn_counters = z(2 * fe.batch * ((fe.chunk_size * DEC_NH + 127) // 128), dtype=torch.int32)
         # activation scales: one per GEMM input site, per layer, per denoise step (pipeline_rtx.py:649-660)
         self.act_scale = torch.ones(N, L, len(SITES), dtype=torch.float32, device=dev)
+        # per-tile row sums of squares handed from a row-parallel projection to the next column-parallel one
+        self.row_stats = torch.zeros(16, 128, dtype=torch.float32, device=dev)
         self.scratch_scale = torch.zeros(1, dtype=torch.float32, device=dev)
         self.calibrated = False
         self.loop_args = None
@@ -361,9 +363,18 @@ class Pi05DecoderPipeline(StepIO):
             return
         S, L, B, CS = self.M, fe.layers, fe.batch, fe.chunk_size    # S = batch * chunk rows
         pdl = fe.use_pdl and not calibrate
+        fold = self._folds_norms() and not calibrate
         for step in range(fe.num_steps):
             # C0: action tokens -> width D, + bias
             self._step_in(stream, pdl)
+            if fold:
+                self._folded_layers(step, stream, pdl)
+                fvk.ada_rms_norm_style(self.x.data_ptr(), self.ones.data_ptr(), self._style("final", step),
+                                       self.xn.data_ptr(), 0, S, DEC_D, 1e-6, stream, pdl=pdl, style_stride=0)
+                self._step_out(stream, pdl)
+                if step_hook is not None:
+                    step_hook(step)
+                continue
             for i in range(L):
                 # C1: adaRMS(style_attn) -> FP8 (layer 0 only; later layers get it from C7 of the previous one)
                 if i == 0:
@@ -438,9 +449,50 @@ class Pi05DecoderPipeline(StepIO):
             if step_hook is not None:
                 step_hook(step)
 
+    def _folds_norms(self) -> bool:
+        fe = self.fe
+        return fe.fold_norms and fe.batch == 1 and self.M <= 128
+
+    def _folded_layers(self, step, stream, pdl) -> None:
+        """The 18 blocks of one Euler step with five launches each: QKV (adaRMS producer in front, RoPE + split + KV
+        append behind), attention (+ FP8 copy), attention-out (+ gated residual + row statistics), gate|up (adaRMS
+        producer, GeGLU -> FP8), FFN-down (+ gated residual + row statistics).  Layer 0 takes its FP8 input from
+        the norm kernel that follows the in-projection."""
+        fe, g = self.fe, self.gemm
+        S, L = self.M, fe.layers
+        x, stats = self.x.data_ptr(), self.row_stats.data_ptr()
+        qd, kd = DEC_NH * DEC_HD, DEC_NKV * DEC_HD
+        gate_off = 2 * DEC_D * 2
+        n_stat = 0
+        for i in range(L):
+            kp, vp, dp = self._kv_dst(i, 0)
+            if i == 0:
+                self._norm(None, None, "attn", step, 0, "qkv", stream, pdl, False)
+                g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
+                                        self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
+                                        fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, stream,
+                                        devpos=dp, pdl=pdl)
+            else:
+                g.norm_fp8_nt_dev_rope_split(x, stats, n_stat, self._style("attn", step, i), fe.w_qkv[i].data_ptr(),
+                                             S, DEC_D, self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
+                                             fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD,
+                                             stream, devpos=dp, pdl=pdl)
+            self._attention(i, stream, pdl, self._scale_ptr(step, i, "o"))
+            n_stat = g.fp8_nt_dev_gate_residual(self.attn8.data_ptr(), fe.w_o[i].data_ptr(), S, DEC_D, qd,
+                                                self._scale_ptr(step, i, "o"), fe.ws_o_t[i].data_ptr(), x,
+                                                self._style("attn", step, i) + gate_off, stats, stream, pdl=pdl)
+            g.norm_fp8_nt_dev_geglu_fp8(x, stats, n_stat, self._style("ffn", step, i), fe.w_gu[i].data_ptr(),
+                                        self.hid8.data_ptr(), S, DEC_H, DEC_D, self._scale_ptr(step, i, "gu"),
+                                        fe.ws_gu_t[i].data_ptr(), self._scale_ptr(step, i, "d"), stream, pdl=pdl)
+            n_stat = g.fp8_nt_dev_gate_residual(self.hid8.data_ptr(), fe.w_d[i].data_ptr(), S, DEC_D, DEC_H,
+                                                self._scale_ptr(step, i, "d"), fe.ws_d_t[i].data_ptr(), x,
+                                                self._style("ffn", step, i) + gate_off, stats, stream, pdl=pdl)
+
     def launches_per_layer(self) -> float:
         """Average over the layers (the last layer keeps its separate residual kernel when the norms are fused)."""
         fe = self.fe
+        if self._folds_norms():
+            return 5.0
         qkv = 1 if fe.batch == 1 and fe.fuse_epilogues else 1 + fe.batch
         gu = 1 if fe.fuse_epilogues else 2
         if fe.fuse_norm and self.M <= 64:
@@ -483,7 +535,7 @@ class Pi05DecoderB200:
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
                  cfg_beta: float | None = None, fixed_shape: bool = False, attn_splits: int = 8,
-                 fuse_norm: bool = False, gu_splits: int = 0, persistent_loop: bool = False, **_ignored):
+                 fuse_norm: bool = False, fold_norms: bool = True, persistent_loop: bool = False, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -495,6 +547,10 @@ class Pi05DecoderB200:
         # projection + gated residual + adaRMS as one 16-CTA-cluster launch: measured slower than the two kernels
         # (10.17 ms vs 9.75 ms per loop, 950 vs 1300 launches), so off unless asked for
         self.fuse_norm = bool(fuse_norm) and fuse_epilogues
+        # the two norm launches of a block folded into the projections around them: the row-parallel projections
+        # (attention-out, FFN-down) update the residual and leave per-tile sums of squares, the column-parallel ones
+        # (QKV, gate|up) produce their own FP8 input from them: 5 launches per block instead of 7
+        self.fold_norms = bool(fold_norms) and fuse_epilogues and not self.fuse_norm
         # the whole loop as one cooperative kernel (phases separated by grid barriers) instead of 1300 launches
         self.persistent_loop = bool(persistent_loop)
         if self.persistent_loop and precision != "fp8":
@@ -509,7 +565,6 @@ class Pi05DecoderB200:
         # fixed-shape mode: prefix_len is the LARGEST prefix; the valid length is a device-side value
         self.fixed_shape = bool(fixed_shape)
         self.attn_splits = int(attn_splits)      # kv splits of the decoder attention (combined through scratch)
-        self.gu_splits = int(gu_splits)          # split-K of the gate|up projection (0 = the library's choice)
         self.valid_prefix_len = prefix_len
         if batch < 1 or batch * ((chunk_size * DEC_NH + 127) // 128) * 8 > self.sm_count:
             raise ValueError(f"batch {batch} x chunk {chunk_size} does not fit the one-wave split-KV attention")

@@ -107,7 +107,10 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
  *   M > 256 runs as a persistent kernel (one CTA per SM walking the tile list, two accumulators in tensor memory so
  *   that the epilogue overlaps the next tile's MMAs); flags bit 1 selects the one-tile-per-CTA kernel instead;
  *   flags bit 3 (M > 256, N >= 256, no split-K) a kernel with one 256 x 256 tile per CTA pair (tcgen05 cta_group::2:
- *   each CTA stages its 128 rows of A and 128 of the 256 weight rows, the leader issues the MMAs for both). */
+ *   each CTA stages its 128 rows of A and 128 of the 256 weight rows, the leader issues the MMAs for both).
+ *   M <= 256 with K % 128 == 0 and N % 8 == 0 runs the token-major kernel (activation rows on the 128 accumulator
+ *   lanes, up to 256 weight rows on the columns, split-K in {1, 2, 4, 8} over a cluster); flags bit 4 keeps the
+ *   swapped kernel (weights on the lanes) instead; flags bits 8-9 pin the tile width (1 = 64, 2 = 128, 3 = 256). */
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream);
@@ -234,6 +237,33 @@ int frt_b200_gemm_fp8_nt_gate_res_norm_fp8(const void* A, const void* W, int M, 
                                            const float* d_scale_b, void* residual, const void* gate, const void* style,
                                            void* out8, const float* d_out_scale, float eps, int splits, int flags,
                                            void* stream);
+/* The decoder's projections with the norm kernel between them folded in (token-major kernel, M <= 128, K % 128 == 0).
+ *
+ * Row-parallel projection + first pass of gate_residual_ada_norm_fp8 (csrc/bindings.cpp:1144-1162 ->
+ * csrc/kernels/fusion.cu:41-47):  o = bf16(sa * sb * A . W^T); residual (M, N) <- bf16(residual + o * gate), gate (N,)
+ * shared by all rows; stats_out[tile][m] (row pitch 128 floats; may be NULL) = sum over the tile's features of the
+ * squares of the unrounded updated residual.  *stat_tiles (host, may be NULL) = rows of stats_out written.
+ * N % 64 == 0. */
+int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                       const float* d_scale_b, void* residual, const void* gate, float* stats_out,
+                                       int* stat_tiles, int splits, int flags, void* stream);
+/* Second pass of gate_residual_ada_norm_fp8 (csrc/kernels/fusion.cu:48-81) produced inside the next projection:
+ *   rms[m] = 1 / sqrt(sum_t stats_in[t][m] / K + eps), t = 0 .. n_stat-1 in order;
+ *   a = e4m3(clamp(((x * rms) * (1 + scale) + shift) / *d_scale_a, +-448)), style = [scale (K) | shift (K)] one bf16 row
+ *   (unit norm weight), x (M, K) bf16;
+ * then GemmRunner::fp8_nt_dev and the epilogue of frt_b200_gemm_fp8_nt_rope_split / _geglu_fp8.  K / splits must
+ * be 128, 256 or 512 bytes (the K-slice stays resident in shared memory). */
+int frt_b200_norm_gemm_fp8_nt_rope_split(const void* x, const float* stats_in, int n_stat, const void* style, float eps,
+                                         const void* W, int M, int K, const float* d_scale_a, const float* d_scale_b,
+                                         const void* rope, void* Q, void* Kout, void* Vout, const int* devpos,
+                                         int q_dim, int k_dim, int v_dim, int head_dim, int splits, int flags,
+                                         void* stream);
+/* The same producer (csrc/kernels/fusion.cu:48-81) in front of the gate|up projection, gate_geglu_merged_fp8
+ * (csrc/kernels/activation.cu:249-279) behind it; half % 128 == 0. */
+int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, int n_stat, const void* style, float eps,
+                                        const void* W, void* out8, int M, int half, int K, const float* d_scale_a,
+                                        const float* d_scale_b, const float* d_out_scale, int splits, int flags,
+                                        void* stream);
 /* fp8 GEMM (GemmRunner::fp8_nt_dev, csrc/bindings.cpp:717-727) + bias_gelu_quantize_fp8_static_bf16
  * (csrc/bindings.cpp:3427-3440 -> csrc/quantize/bias_gelu_quantize_fp8.cu:24-49) in one launch, M > 256, N >= 128:
  *   out8 (M, N) e4m3 = clamp(gelu_tanh(bf16(sa * sb * A . W^T) + bias) * (1 / *d_out_scale), +-448)

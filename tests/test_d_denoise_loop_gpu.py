@@ -16,12 +16,9 @@ def _cos(a, b):
     return float(a @ b / (a.norm() * b.norm()))
 
 
-@pytest.fixture(scope="module")
-def small_model():
-    """4 layers keep the CPU oracle to a few seconds; the 18-layer shape is covered below."""
+def _build(L):
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import synthetic_state_dict
-    L = 4
     sd = synthetic_state_dict(seed=0, layers=L)
     model = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768)
     pk, pv = R.synthetic_prefix_kv(seed=1, layers=L, prefix_len=768)
@@ -32,8 +29,28 @@ def small_model():
     return dict(model=model, ck=ck, pk=pk_b.float(), pv=pv_b.float(), L=L)
 
 
+@pytest.fixture(scope="module")
+def small_model():
+    """4 layers: the depth the other loop tests in this file reuse."""
+    return _build(4)
+
+
+@pytest.fixture(scope="module")
+def full_model():
+    """18 layers, 10 steps, 768 prefix keys, 8 calibration noises: the configuration ``bench.py`` times."""
+    return _build(18)
+
+
 def test_loop_matches_fp32_oracle_per_step_and_final(small_model):
-    m = small_model
+    _loop_parity(small_model)
+
+
+def test_full_depth_loop_matches_fp32_oracle_per_step_and_final(full_model):
+    """The benchmarked configuration itself (18 blocks) against the fp32 oracle, same bar, every Euler step."""
+    _loop_parity(full_model)
+
+
+def _loop_parity(m):
     fe = m["model"].frontend
     noise = R.synthetic_noise(1)
     noise_b = noise.to(torch.bfloat16).float()
@@ -75,8 +92,8 @@ def test_full_depth_loop_runs_and_is_finite():
     assert a.shape == (50, 32) and np.isfinite(a).all()
     assert np.array_equal(a, b)
     assert 0.05 < float(np.abs(a).mean()) < 50
-    # per step: in-projection, first norm, 18 x (qkv, attention, o, norm, gate|up, down, norm), final norm, out-projection
-    assert model.frontend.kernels_per_loop() == 10 * (2 + 7 * 18 + 2)
+    # per step: in-projection, first norm, 18 x (qkv, attention, o, gate|up, down), final norm, out-projection
+    assert model.frontend.kernels_per_loop() == 10 * (2 + 5 * 18 + 2)
 
 
 def test_refuses_wrong_inputs():
@@ -153,9 +170,10 @@ def test_fixed_shape_graph_serves_every_prefix_length(precision):
     assert fa2.attention_status() == 0
 
 
-def test_fused_norm_variant_matches_the_default_loop():
-    """fuse_norm=True (projection + gated residual + adaRMS in one 16-CTA-cluster launch, 950 launches per loop):
-    same actions as the default composition to within the FP8 code flips of the differently ordered row statistics."""
+def test_compositions_of_the_norms_agree():
+    """Three compositions of the same block: norm kernels on their own (7 launches per block), folded into the
+    projections around them (the default, 5), and fuse_norm=True (projection + gated residual + adaRMS in one
+    16-CTA-cluster launch).  Same actions to within the FP8 code flips of the differently ordered row statistics."""
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import synthetic_state_dict
     L = 3
@@ -164,12 +182,15 @@ def test_fused_norm_variant_matches_the_default_loop():
     cal = [R.synthetic_noise(100 + j) for j in range(3)]
     noise = R.synthetic_noise(1).numpy()
     outs = []
-    for fn in (False, True):
-        m = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768, fuse_norm=fn)
+    for kw, per_step in ((dict(fold_norms=False), 2 + 7 * L + 2), (dict(), 2 + 5 * L + 2),
+                         (dict(fuse_norm=True), 2 + 5 * L + 1 + 2)):
+        m = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768, **kw)
         m.set_prefix(pk, pv)
         m.calibrate(cal)
         outs.append(m.predict(noise=noise))
-        assert m.frontend.kernels_per_loop() == (10 * (2 + 5 * L + 1 + 2) if fn else 10 * (2 + 7 * L + 2))
-    a, b = torch.from_numpy(outs[0]), torch.from_numpy(outs[1])
-    assert _cos(a, b) >= 0.9999
-    assert float((a - b).abs().max()) <= 2e-2 * float(a.pow(2).mean().sqrt())
+        assert m.frontend.kernels_per_loop() == 10 * per_step
+    a = torch.from_numpy(outs[0])
+    for o in outs[1:]:
+        b = torch.from_numpy(o)
+        assert _cos(a, b) >= 0.9999
+        assert float((a - b).abs().max()) <= 2e-2 * float(a.pow(2).mean().sqrt())

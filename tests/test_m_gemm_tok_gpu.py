@@ -1,0 +1,219 @@
+"""GPU parity of the token-major small-M FP8 GEMM (activation rows on the accumulator lanes, weights on the columns,
+split-K over a cluster) and of the decoder projections that fold the norm kernel between them:
+  * plain GEMM over tile widths x split factors x row counts against the fp64 oracle, and bit for bit on exact products;
+  * gated-residual epilogue: residual bits exact against the restated arithmetic, row statistics to fp32 accuracy;
+  * in-kernel adaRMS -> FP8 producer: every produced E4M3 code exact (read back through identity weights), and the
+    fused launches byte-identical to the same GEMM fed with the restated codes."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from oracle import oracle as O  # noqa: E402
+from test_b_gemm_gpu import _check, _fp8_operand, _ref  # noqa: E402
+
+
+def _fma32(a, b, c):
+    """fp32 fused multiply-add of arrays (products of <= 24-bit significands are exact in fp64; one rounding)."""
+    return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+@pytest.mark.parametrize("M,N,K", [(50, 1024, 1024), (1, 256, 2048), (128, 512, 1024), (200, 1024, 1024),
+                                   (50, 2560, 1024), (16, 1000, 4096), (50, 1024, 8192)])
+def test_token_major_gemm(M, N, K, splits, tile_n):
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M * 7919 + N * 31 + K + splits * 3 + tile_n)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    bias = rand_bf16(rng, (N,), 0.2)
+    d_A, d_W, d_D, d_b = Dev(A), Dev(W), zeros((M, N), np.uint16), Dev(bias)
+    d_sa, d_sb = f32(sa), f32(sb)
+    fvk.GemmRunner().fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits,
+                                tile_n=tile_n, bias=d_b.ptr)
+    got = d_D.get()
+    assert fvk.tensor_core_status() == 0
+    _check(got, _ref(A, W, sa, sb, bias))
+
+
+@pytest.mark.parametrize("splits,tile_n", [(1, 256), (4, 128), (8, 64), (2, 256)])
+def test_token_major_gemm_exact_products(splits, tile_n):
+    """Small integers in E4M3 make every product and partial sum exact: equal to the fp64 oracle bit for bit, and to
+    the swapped kernel."""
+    import torch
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(5 + splits)
+    M, N, K = 50, 512, 1024
+    vals = np.array([-4, -3, -2, -1, 0, 1, 2, 3, 4], np.float32)
+    A = torch.from_numpy(rng.choice(vals, (M, K))).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    W = torch.from_numpy(rng.choice(vals, (N, K))).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    ref = O.gemm_fp8(A, W, 0.5, 0.25, b_is_nk=True)
+    d_sa, d_sb = f32(0.5), f32(0.25)
+    d_A, d_W, d_D, d_S = Dev(A), Dev(W), zeros((M, N), np.uint16), zeros((M, N), np.uint16)
+    g = fvk.GemmRunner()
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_D.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits, tile_n=tile_n)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_S.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits, swapped=True)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_D.get(), ref)
+    assert np.array_equal(d_S.get(), ref)
+
+
+@pytest.mark.parametrize("M,N,K,splits,tile_n", [(50, 1024, 2048, 8, 64), (50, 1024, 4096, 8, 64), (50, 1024, 2048, 4, 128),
+                                                 (128, 512, 1024, 2, 64), (7, 1024, 4096, 0, 0), (50, 1024, 1024, 1, 128)])
+def test_gated_residual_epilogue(M, N, K, splits, tile_n):
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M + N + K + splits)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    res0 = rand_bf16(rng, (M, N), 1.0)
+    gate = rand_bf16(rng, (N,), 0.5)
+    d_A, d_W, d_sa, d_sb = Dev(A), Dev(W), f32(sa), f32(sb)
+    d_o, d_res, d_gate = zeros((M, N), np.uint16), Dev(res0), Dev(gate)
+    d_stats = Dev(np.full((16, 128), -1.0, np.float32))
+    g = fvk.GemmRunner()
+    n_stat = g.fp8_nt_dev_gate_residual(d_A.ptr, d_W.ptr, M, N, K, d_sa.ptr, d_sb.ptr, d_res.ptr, d_gate.ptr,
+                                        d_stats.ptr, 0, splits=splits, tile_n=tile_n)
+    # the projection on its own with the same K split: its bf16 result is what the epilogue rounds to
+    sp = splits if splits else 8
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_o.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=sp, tile_n=tile_n or 64)
+    assert fvk.tensor_core_status() == 0
+    _check(d_o.get(), _ref(A, W, sa, sb))
+    o = O.bf16_bits_to_f32(d_o.get())
+    r_new = _fma32(o, np.broadcast_to(O.bf16_bits_to_f32(gate), (M, N)), O.bf16_bits_to_f32(res0))
+    if splits:
+        assert np.array_equal(d_res.get(), O.f32_to_bf16_bits(r_new))
+    else:   # the library chose the split: compare to within one bf16 step of the projection
+        assert np.abs(O.bf16_bits_to_f32(d_res.get()) - r_new).max() <= 0.05
+        r_new = None
+    stats = d_stats.get()
+    assert n_stat in (N // 64, N // 128)
+    bn = N // n_stat
+    assert (stats[n_stat:] == -1.0).all() and (stats[:n_stat, M:] == -1.0).all()
+    if r_new is not None:
+        want = (r_new.astype(np.float64) ** 2).reshape(M, n_stat, bn).sum(-1).T     # [tile][token]
+        assert np.allclose(stats[:n_stat, :M], want, rtol=2e-6, atol=1e-6)
+
+
+def _expected_codes(x_bits, stats, style_bits, K, eps, sa):
+    """Restatement of the in-kernel adaRMS -> FP8 producer (same operations, same order)."""
+    M = x_bits.shape[0]
+    tot = np.zeros(M, np.float32)
+    for t in range(stats.shape[0]):
+        tot = (tot + stats[t, :M]).astype(np.float32)
+    var = (tot / np.float32(K)).astype(np.float32) + np.float32(eps)
+    rms = (np.float32(1.0) / np.sqrt(var.astype(np.float32)).astype(np.float32)).astype(np.float32)
+    x = O.bf16_bits_to_f32(x_bits)
+    sc = O.bf16_bits_to_f32(style_bits[:K])[None, :]
+    sh = O.bf16_bits_to_f32(style_bits[K:2 * K])[None, :]
+    t = (x * rms[:, None]).astype(np.float32)
+    n = _fma32(t, (np.float32(1.0) + sc).astype(np.float32), np.broadcast_to(sh, t.shape))
+    inv = np.float32(1.0) / np.float32(sa)
+    q = np.clip((n * inv).astype(np.float32), -448.0, 448.0)
+    return O.f32_to_e4m3(q)
+
+
+def _producer_inputs(rng, M, K, n_stat):
+    from gpu_util import rand_bf16
+    x = rand_bf16(rng, (M, K), 1.5)
+    style = rand_bf16(rng, (3 * K,), 0.3)
+    xf = O.bf16_bits_to_f32(x).astype(np.float64)
+    ssq = (xf ** 2).sum(-1)
+    w = rng.random((n_stat, M)) + 0.1
+    stats = np.zeros((n_stat, 128), np.float32)
+    stats[:, :M] = (w / w.sum(0) * ssq[None, :]).astype(np.float32)
+    return x, style, stats
+
+
+@pytest.mark.parametrize("M,splits", [(50, 4), (50, 8), (50, 2), (128, 4), (3, 4)])
+def test_norm_producer_codes_are_exact(M, splits):
+    """Identity weights and a RoPE table of (cos, sin) = (1, 0) return the producer's E4M3 codes themselves: each must
+    equal the restated arithmetic."""
+    import torch
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(M * 11 + splits)
+    K, n_stat = 1024, 16
+    x, style, stats = _producer_inputs(rng, M, K, n_stat)
+    W = np.zeros((K, K), np.uint8)
+    W[np.arange(K), np.arange(K)] = 0x38                     # 1.0 in E4M3
+    sa = 0.125                                               # a power of two: alpha * code value is exact in bf16
+    rope = O.f32_to_bf16_bits(np.tile(np.array([1.0, 0.0], np.float32), (M, 128)))
+    q_dim, k_dim, v_dim, hd = 512, 256, 256, 256
+    d_x, d_st, d_sty, d_W, d_rope = Dev(x), Dev(stats), Dev(style), Dev(W), Dev(rope)
+    d_sa, d_sb = f32(sa), f32(1.0)
+    d_Q, d_K, d_V = zeros((M, q_dim), np.uint16), zeros((M, k_dim), np.uint16), zeros((M, v_dim), np.uint16)
+    fvk.GemmRunner().norm_fp8_nt_dev_rope_split(d_x.ptr, d_st.ptr, n_stat, d_sty.ptr, d_W.ptr, M, K, d_sa.ptr, d_sb.ptr,
+                                                d_rope.ptr, d_Q.ptr, d_K.ptr, d_V.ptr, q_dim, k_dim, v_dim, hd, 0,
+                                                splits=splits)
+    assert fvk.tensor_core_status() == 0
+    got = O.bf16_bits_to_f32(np.concatenate([d_Q.get(), d_K.get(), d_V.get()], axis=1))
+    want = O.e4m3_to_f32(_expected_codes(x, stats, style, K, 1e-6, sa)) * np.float32(sa)
+    bad = got != want
+    assert bad.mean() <= 2e-5, f"{int(bad.sum())} of {bad.size} codes differ"       # fp64-emulated fma: rare halfway cases
+    assert (np.abs(want) > 0).mean() > 0.9
+
+
+@pytest.mark.parametrize("M,splits", [(50, 4), (50, 0), (100, 2)])
+def test_norm_producer_in_front_of_qkv_and_gate_up(M, splits):
+    """The fused launches equal the same GEMM (same tile width and split) fed with the restated FP8 codes."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M * 13 + splits)
+    K, n_stat, H = 1024, 8, 4096
+    x, style, stats = _producer_inputs(rng, M, K, n_stat)
+    xs = O.bf16_bits_to_f32(x)
+    sa = float(np.abs(xs).max()) * 4.0 / 448.0
+    codes = _expected_codes(x, stats, style, K, 1e-6, sa)
+    g = fvk.GemmRunner()
+    d_x, d_st, d_sty, d_A = Dev(x), Dev(stats), Dev(style), Dev(codes)
+    d_sa = f32(sa)
+    # ---- QKV
+    q_dim, k_dim, v_dim, hd, pos = 2048, 256, 256, 256, 5
+    Wq, sb = _fp8_operand(rng, q_dim + k_dim + v_dim, K, 0.02)
+    inv_freq = 1.0 / (10000 ** (np.arange(0, hd, 2, dtype=np.float64) / hd))
+    ph = np.arange(pos, pos + M, dtype=np.float64)[:, None] * inv_freq[None, :]
+    rope = O.f32_to_bf16_bits(np.stack([np.cos(ph), np.sin(ph)], -1).reshape(M, hd).astype(np.float32))
+    d_W, d_sb, d_rope = Dev(Wq), f32(sb), Dev(rope)
+    outs = []
+    for fused in (False, True):
+        d_Q, d_K, d_V = zeros((M, q_dim), np.uint16), zeros((M + pos, k_dim), np.uint16), zeros((M + pos, v_dim), np.uint16)
+        tail = (d_rope.ptr, d_Q.ptr, d_K.ptr + pos * k_dim * 2, d_V.ptr + pos * v_dim * 2, q_dim, k_dim, v_dim, hd, 0)
+        if fused:
+            g.norm_fp8_nt_dev_rope_split(d_x.ptr, d_st.ptr, n_stat, d_sty.ptr, d_W.ptr, M, K, d_sa.ptr, d_sb.ptr, *tail,
+                                         splits=splits)
+        else:
+            g.fp8_nt_dev_rope_split(d_A.ptr, d_W.ptr, M, K, d_sa.ptr, d_sb.ptr, *tail, splits=splits)
+        outs.append((d_Q.get(), d_K.get(), d_V.get()))
+    assert fvk.tensor_core_status() == 0
+    mism = sum(int((a != b).sum()) for a, b in zip(*outs))
+    assert mism <= 40, mism            # a code that differs from the restatement (fma emulation) touches one output row
+    assert (outs[1][0] != 0).mean() > 0.9
+    # ---- gate|up
+    Wg, sbg = _fp8_operand(rng, 2 * H, K, 0.03)
+    d_Wg, d_sbg, d_so = Dev(Wg), f32(sbg), f32(0.004)
+    d_o1, d_o2 = zeros((M, H), np.uint8), zeros((M, H), np.uint8)
+    g.fp8_nt_dev_geglu_fp8(d_A.ptr, d_Wg.ptr, d_o1.ptr, M, H, K, d_sa.ptr, d_sbg.ptr, d_so.ptr, 0, splits=splits)
+    g.norm_fp8_nt_dev_geglu_fp8(d_x.ptr, d_st.ptr, n_stat, d_sty.ptr, d_Wg.ptr, d_o2.ptr, M, H, K, d_sa.ptr, d_sbg.ptr,
+                                d_so.ptr, 0, splits=splits)
+    assert fvk.tensor_core_status() == 0
+    assert int((d_o1.get() != d_o2.get()).sum()) <= 40
+    assert (d_o2.get() != 0).mean() > 0.5
+
+
+def test_refusals():
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from flashrt_b200._lib import KernelError
+    from gpu_util import zeros
+    g = fvk.GemmRunner()
+    z = zeros((256, 1024), np.uint16)
+    with pytest.raises(KernelError):       # more rows than one accumulator tile
+        g.fp8_nt_dev_gate_residual(z.ptr, z.ptr, 129, 1024, 1024, 0, 0, z.ptr, z.ptr, z.ptr, 0)
+    with pytest.raises(KernelError):       # K not in whole 128-byte blocks
+        g.fp8_nt_dev_gate_residual(z.ptr, z.ptr, 50, 1024, 1000, 0, 0, z.ptr, z.ptr, z.ptr, 0)
+    with pytest.raises(KernelError):       # K-slice that cannot stay resident
+        g.norm_fp8_nt_dev_geglu_fp8(z.ptr, z.ptr, 4, z.ptr, z.ptr, z.ptr, 50, 4096, 4096, z.ptr, z.ptr, z.ptr, 0,
+                                    splits=2)
