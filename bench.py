@@ -84,25 +84,30 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------------------
-def cpu_reference_loop(steps: int, warmup: int, layers: int = 18):
-    """The reference's torch math for this path (fp32, CPU): oracle.block_ref.denoise_loop on all host cores."""
+def cpu_reference_loop(steps: int, warmup: int, layers: int = 18, inputs=None):
+    """The reference's torch math for this path (fp32, CPU): oracle.block_ref.denoise_loop on all host cores.
+    ``inputs`` = (prefix_k, prefix_v, noise) of the device arm (so that the two outputs can be compared); seeded
+    stand-ins otherwise.  Returns (median ms, cores, actions of the last run)."""
     import torch
     from oracle import block_ref as R
     from flashrt_b200.pi05_decoder import synthetic_state_dict
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     sd = synthetic_state_dict(0, layers)
-    ck = R.from_hf_state_dict(sd, layers)
-    pk, pv = R.synthetic_prefix_kv(1, layers)
-    noise = R.synthetic_noise(1)
+    ck = R.from_hf_state_dict({k: v.to(torch.bfloat16).float() for k, v in sd.items()}, layers)
+    if inputs is None:
+        pk, pv = R.synthetic_prefix_kv(1, layers)
+        noise = R.synthetic_noise(1)
+    else:
+        pk, pv, noise = (t.to(torch.bfloat16).float() for t in inputs)
     for _ in range(warmup):
         R.denoise_loop(noise, ck, pk, pv, layers=layers)
-    ts = []
+    ts, out = [], None
     for _ in range(steps):
         t0 = time.perf_counter()
-        R.denoise_loop(noise, ck, pk, pv, layers=layers)
+        out = R.denoise_loop(noise, ck, pk, pv, layers=layers)
         ts.append((time.perf_counter() - t0) * 1e3)
-    return statistics.median(ts), cores
+    return statistics.median(ts), cores, out
 
 
 def run_reference(args):
@@ -110,7 +115,7 @@ def run_reference(args):
     if rank != 0:
         return
     steps = max(1, min(args.steps, 5))
-    ms, cores = cpu_reference_loop(steps, min(args.warmup, 1))
+    ms, cores, _ = cpu_reference_loop(steps, min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": METRIC, "value": round(ms, 3), "unit": "ms", "n_gpus": args.gpus,
         "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": round(ms, 3), "higher_is_better": False,
@@ -126,30 +131,57 @@ def run_reference(args):
 
 # ---------------------------------------------------------------------------------------------------------------
 def gemm_roofline(fe, reps: int = 20):
-    """Average duration of the dominant kernel (the small-M FP8 GEMM that streams the weights): a graph holding
-    exactly the 4 x 18 GEMM launches of one Euler step, each on its own layer's weights (311 MB > L2), timed with
-    CUDA events on the launching stream."""
+    """Average duration of the dominant kernel family (the small-M FP8 projections that stream the weights): a graph
+    holding exactly the 4 x 18 projection launches of one Euler step in the form the loop uses them (norm producer /
+    fused epilogues included), each on its own layer's weights (311 MB > L2), timed with CUDA events on the
+    launching stream.  Returns (us per launch, algorithmic bytes per launch, launches)."""
     import torch
+    from flashrt_b200.pi05_decoder import DEC_D, DEC_H, DEC_HD, DEC_NH, DEC_NKV
     p, s = fe.pipeline, fe.stream
     S, L = fe.chunk_size * fe.batch, fe.layers
     nv = fe.precision == "nvfp4"
+    st = s.cuda_stream
     if nv:
         shapes = [("qkv", None, (p.act4, p.act4_sf), p.qkv, 2560, 1024), ("o", None, (p.ctx4, p.ctx4_sf), p.xn, 1024, 2048),
                   ("gu", None, (p.act4, p.act4_sf), p.merged, 8192, 1024), ("d", None, (p.hid4, p.hid4_sf), p.xn, 1024, 4096)]
     else:
         shapes = [("w_qkv", "ws_qkv_t", p.act8, p.qkv, 2560, 1024), ("w_o", "ws_o_t", p.attn8, p.xn, 1024, 2048),
                   ("w_gu", "ws_gu_t", p.act8, p.merged, 8192, 1024), ("w_d", "ws_d_t", p.hid8, p.xn, 1024, 4096)]
+    folded = (not nv) and p._folds_norms()
 
     def enqueue():
+        if folded:
+            g, pdl = p.gemm, fe.use_pdl
+            x, stats = p.x.data_ptr(), p.row_stats.data_ptr()
+            qd, kd = DEC_NH * DEC_HD, DEC_NKV * DEC_HD
+            for i in range(L):
+                kp, vp, dp = p._kv_dst(i, 0)
+                g.norm_fp8_nt_dev_rope_split(x, stats, 16, p._style("attn", 0, i), fe.w_qkv[i].data_ptr(), S, DEC_D,
+                                             p._scale_ptr(0, i, "qkv"), fe.ws_qkv_t[i].data_ptr(), fe.rope.data_ptr(),
+                                             p.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, st, devpos=dp, pdl=pdl,
+                                             splits=4, tile_n=64)
+                g.fp8_nt_dev_gate_residual(p.attn8.data_ptr(), fe.w_o[i].data_ptr(), S, DEC_D, qd, p._scale_ptr(0, i, "o"),
+                                           fe.ws_o_t[i].data_ptr(), x, p._style("attn", 0, i) + 4 * DEC_D, stats, st,
+                                           pdl=pdl, splits=4, tile_n=64)
+                g.norm_fp8_nt_dev_geglu_fp8(x, stats, 16, p._style("ffn", 0, i), fe.w_gu[i].data_ptr(), p.hid8.data_ptr(),
+                                            S, DEC_H, DEC_D, p._scale_ptr(0, i, "gu"), fe.ws_gu_t[i].data_ptr(),
+                                            p._scale_ptr(0, i, "d"), st, pdl=pdl, splits=2, tile_n=128)
+                g.fp8_nt_dev_gate_residual(p.hid8.data_ptr(), fe.w_d[i].data_ptr(), S, DEC_D, DEC_H, p._scale_ptr(0, i, "d"),
+                                           fe.ws_d_t[i].data_ptr(), x, p._style("ffn", 0, i) + 4 * DEC_D, stats, st,
+                                           pdl=pdl, splits=8, tile_n=64)
+            return
         for i in range(L):
             for wn, sn, a8, out, N, K in shapes:
                 if nv:
-                    p._gemm(a8[0], a8[1], fe.w4[i][wn], out, s.cuda_stream, fe.use_pdl)
+                    p._gemm(a8[0], a8[1], fe.w4[i][wn], out, st, fe.use_pdl)
                 else:
                     p._gemm(a8, getattr(fe, wn)[i], getattr(fe, sn)[i], out, S, N, K, p._scale_ptr(0, i, "qkv"),
-                            s.cuda_stream, fe.use_pdl)
+                            st, fe.use_pdl)
 
     with torch.cuda.stream(s):
+        if folded:
+            keep = p.x.clone()
+            p.row_stats.fill_(64.0)
         enqueue()
         s.synchronize()
         g = torch.cuda.CUDAGraph()
@@ -163,6 +195,8 @@ def gemm_roofline(fe, reps: int = 20):
             g.replay()
         e1.record(s)
         s.synchronize()
+        if folded:
+            p.x.copy_(keep)
     launches = len(shapes) * L
     us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
     eb = 0.5625 if nv else 1.0          # bytes per operand element (NVFP4: 4 bits + one scale byte per 16)
@@ -170,9 +204,15 @@ def gemm_roofline(fe, reps: int = 20):
     return us, bytes_per_launch, launches
 
 
+def _pctl(xs, q):
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(round(q * (len(xs) - 1))))]
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
+    t_start = time.perf_counter()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -188,11 +228,13 @@ def run_ours(args):
                        precision=args.precision, batch=args.batch, persistent_loop=args.persistent_loop)
     fe = model.frontend
     L, P = fe.layers, fe.prefix_len
-    model.set_prefix(torch.randn(L, P, 256, generator=gsd), torch.randn(L, P, 256, generator=gsd))
+    prefix_k, prefix_v = torch.randn(L, P, 256, generator=gsd), torch.randn(L, P, 256, generator=gsd)
+    model.set_prefix(prefix_k, prefix_v)
     cal = [torch.randn(fe.chunk_size, ACTION_DIM, generator=torch.Generator().manual_seed(100 + j)) for j in range(args.calib_samples)]
     model.calibrate(cal)                  # no-op for NVFP4 (block scales are computed at run time)
     nshape = (fe.chunk_size, ACTION_DIM) if fe.batch == 1 else (fe.batch, fe.chunk_size, ACTION_DIM)
-    noise = torch.randn(*nshape, generator=torch.Generator().manual_seed(7)).numpy()
+    noise_t = torch.randn(*nshape, generator=torch.Generator().manual_seed(7))
+    noise = noise_t.numpy()
     model.predict(noise=noise)            # captures the graph
 
     def barrier():
@@ -216,6 +258,14 @@ def run_ours(args):
     barrier()
     torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / args.steps
+    # ---- distribution of single replays (events around every replay; the mean above stays the value)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in evs:
+        a.record(s)
+        fe.forward_decode_only()
+        b.record(s)
+    s.synchronize()
+    per = [a.elapsed_time(b) for a, b in evs]
     # ---- end to end through the public API: host noise in, host actions out
     for _ in range(3):
         model.predict(noise=noise)
@@ -233,21 +283,15 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
 
-    if rank == 0:
-        from flashrt_b200 import flash_rt_kernels as fvk
-        status = fvk.tensor_core_status()
+    from flashrt_b200 import flash_rt_kernels as fvk
+    status = fvk.tensor_core_status()
+    line = None
+    if rank == 0 and args.lean:
+        print(json.dumps({"metric": METRIC, "value": round(ms, 4), "unit": "ms", "lean": True,
+                          "e2e_ms": round(e2e_ms, 4), "tensor_core_status": status}), flush=True)
+    elif rank == 0:
         peak, peak_src = _peaks()
-        if args.loop_trace:
-            loop_trace_report(ms)
-        if args.lean:
-            print(json.dumps({"metric": METRIC, "value": round(ms, 4), "unit": "ms", "lean": True,
-                              "e2e_ms": round(e2e_ms, 4), "tensor_core_status": status}), flush=True)
-            if world > 1:
-                dist.destroy_process_group()
-            return
         gemm_us, gemm_bytes, _ = gemm_roofline(fe)
-        alt = (persistent_loop_ms(local, args.calib_samples)
-               if (not nv and fe.batch == 1 and not args.persistent_loop) else None)
         M = fe.batch * fe.chunk_size
         gemm_out_bytes = 2 * M * (2560 + 1024 + 8192 + 1024) / 4
         achieved = gemm_bytes / (gemm_us * 1e-6) / 1e9
@@ -255,7 +299,17 @@ def run_ours(args):
         # block scales) + prefix/fresh KV per layer per step (per batch element)
         wbytes = 17301504 * (0.5625 if nv else 1.0)
         loop_bytes = int(fe.num_steps * L * (wbytes + fe.batch * 2 * (P + fe.chunk_size) * 256 * 2))
-        cpu_ms, cores = cpu_reference_loop(3, 1, L)
+        # the CPU port of the reference math on the SAME prefix and noise: the baseline time, and the check that the
+        # timed output is right
+        cpu_ms, cores, ref = cpu_reference_loop(3, 1, L, inputs=(prefix_k, prefix_v, noise_t if fe.batch == 1 else noise_t[0]))
+        got = torch.from_numpy(out if fe.batch == 1 else out[0]).double().flatten()
+        refd = ref.double().flatten()
+        rms = float(refd.pow(2).mean().sqrt())
+        parity = {"cosine": round(float(got @ refd / (got.norm() * refd.norm())), 6),
+                  "max_abs_over_rms": round(float((got - refd).abs().max()) / rms, 4),
+                  "rms_err_over_rms": round(float((got - refd).pow(2).mean().sqrt()) / rms, 4),
+                  "layers": L, "steps": fe.num_steps,
+                  "against": "fp32 torch oracle (oracle.block_ref.denoise_loop) on the same weights, prefix and noise"}
         line = {
             "metric": METRIC, "value": round(ms, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False,
@@ -274,25 +328,86 @@ def run_ours(args):
                     "d2h_bytes_per_step": int(out.nbytes)},
             "gpu_launches": fe.kernels_per_loop() * args.steps,
             "aggregate_loops_per_s": round(world * 1e3 / ms, 2),
-            # the same loop as ONE persistent cooperative kernel (opt-in composition, reported beside the default)
-            "persistent_loop": alt,
+            "p50_ms": round(_pctl(per, 0.5), 4), "p95_ms": round(_pctl(per, 0.95), 4),
+            "parity": parity,
             "loop_hbm_floor": {"algorithmic_bytes": loop_bytes, "floor_ms": round(loop_bytes / (peak * 1e9) * 1e3, 4),
                                "frac": round(loop_bytes / (peak * 1e9) * 1e3 / ms, 4)},
-            "roofline": {"bound": "hbm", "kernel": ("gemm_fp8_kernel<..,true,..,NVFP4> (M=%d weight streaming)" % M
-                                                    if nv else "gemm_fp8_kernel<64,true> (M=50 weight streaming)"),
+            "roofline": {"bound": "hbm",
+                         "kernel": ("gemm_fp8_kernel<..,true,..,NVFP4> (M=%d weight streaming)" % M if nv else
+                                    "gemm_tok_kernel (M=%d projections of the loop: weight streaming)" % M),
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
-                         # dram read+write of one launch from the ncu capture in profiles/ (1.005 x the algorithmic
-                         # read bytes; the bf16 result stays in L2), scaled to the average launch by bytes
-                         "traffic": int(1.005 * (gemm_bytes - gemm_out_bytes)), "peak_source": peak_src,
+                         # not measured in this run: dram read + write of one launch from the ncu capture under
+                         # profiles/ (1.005 x the algorithmic read bytes; the result stays in L2), scaled by bytes
+                         "traffic": int(1.005 * (gemm_bytes - gemm_out_bytes)),
+                         "traffic_source": "carried over from the ncu capture in profiles/, scaled by bytes",
+                         "peak_source": peak_src,
                          "avg_launch_us": round(gemm_us, 3), "algorithmic_bytes_per_launch": int(gemm_bytes)},
             "cpu_baseline": {"value": round(cpu_ms, 2), "unit": "ms", "cores": cores, "kind": "port",
                              "sample": "3 full 10-step loops of the fp32 torch oracle, median"},
             "clocks": clocks,
         }
+    # ---- the other configurations of the benchmark definition, measured after the headline (never inside it)
+    if not args.lean and not args.no_extras:
+        del model, fe
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        budget = args.extras_budget_s
+        extras = {}
+        if time.perf_counter() - t_start < budget:
+            try:
+                w = measure_wan(args, rank, world, local, steps=3, warm=1)
+                extras["video_dit"] = {"ms": w["ms"], "e2e_ms": w["e2e_ms"], "tp": world, "layers": w["layers"],
+                                       "frac_weighted": w["frac_weighted"], "finite": w["finite"],
+                                       "tensor_core_status": w["status"], "launches_per_step": w["launches"]}
+            except Exception as e:  # noqa: BLE001
+                extras["video_dit"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+        if world == 1 and rank == 0:
+            for name, fn in (("ops", lambda: ops_summary(args)), ("nvfp4", lambda: nvfp4_summary(args, local))):
+                if time.perf_counter() - t_start > budget:
+                    extras[name] = {"skipped": "time budget of the default run"}
+                    continue
+                try:
+                    extras[name] = fn()
+                except Exception as e:  # noqa: BLE001
+                    extras[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
+        if line is not None:
+            line.update(extras)
+    if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def nvfp4_summary(args, local: int) -> dict:
+    """configs[3] in short: the NVFP4 loop at batch 1 and batch 4, graph replay only (ms per loop)."""
+    import torch
+    from flashrt_b200 import load_model
+    from flashrt_b200.pi05_decoder import ACTION_DIM
+    res = {}
+    for batch in (1, 4):
+        model = load_model("synthetic:0", config="pi05", device=local, precision="nvfp4", batch=batch)
+        fe = model.frontend
+        g = torch.Generator().manual_seed(1)
+        model.set_prefix(torch.randn(fe.layers, fe.prefix_len, 256, generator=g),
+                         torch.randn(fe.layers, fe.prefix_len, 256, generator=g))
+        shape = (fe.chunk_size, ACTION_DIM) if batch == 1 else (batch, fe.chunk_size, ACTION_DIM)
+        out = model.predict(noise=torch.randn(*shape, generator=g).numpy())
+        s = fe.stream
+        for _ in range(3):
+            fe.forward_decode_only()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(20):
+            fe.forward_decode_only()
+        e1.record(s)
+        s.synchronize()
+        res[f"b{batch}_ms"] = round(e0.elapsed_time(e1) / 20, 4)
+        res[f"b{batch}_finite"] = bool((out == out).all())
+        del model, fe
+        torch.cuda.empty_cache()
+    return res
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -302,17 +417,13 @@ WAN_WORKLOAD = ("wan2.2-5B-shape DiT step: 30 blocks, width 3072, 24 heads x 128
                 "FP8 E4M3 GEMMs + bf16 attention")
 
 
-def run_wan(args):
-    """Benchmark configuration 4: one denoise step of the video DiT, tensor-parallel over the N GPUs (strong scaling)."""
+def measure_wan(args, rank, world, local, steps, warm):
+    """One denoise step of the video DiT, tensor-parallel over the ``world`` ranks of the already initialised process
+    group (strong scaling).  Returns the timings (max over ranks) and the roofline inputs on every rank."""
     import torch
     import torch.distributed as dist
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     from flashrt_b200.wan_dit import WanDiTB200, synthetic_wan_state
+    from flashrt_b200 import flash_rt_kernels as fvk
     layers = args.wan_layers
     state = synthetic_wan_state(0, layers=1)
     grid, B, T = (13, 30, 52), 2, 512
@@ -326,7 +437,6 @@ def run_wan(args):
     x_dev = x_host.to(f"cuda:{local}")
     model.set_context(ctx)
     model.calibrate(x_dev, tproj)
-    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
 
     def barrier():
         if world > 1:
@@ -357,31 +467,90 @@ def run_wan(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops_sustained": 1400.0}
+    bf16_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    gemm_flop = 2.0 * B * L * (3072 * 9216 + 3 * 3072 * 3072 + 2 * 3072 * 14336) * layers      # FP8 projections
+    attn_flop = 4.0 * L * L * 3072 * B * layers + 4.0 * L * T * 3072 * B * layers              # bf16 attention
+    # time-weighted floor per GPU: the FP8 part against 2 x the measured bf16 rate, the attention against 1 x
+    floor_ms = (gemm_flop / (2 * bf16_peak) + attn_flop / bf16_peak) / world / 1e12 * 1e3
+    res = {"ms": round(ms, 2), "e2e_ms": round(e2e_ms, 2), "layers": layers, "clocks": clocks,
+           "finite": bool(torch.isfinite(out.float()).all()), "status": fvk.tensor_core_status(),
+           "launches": model.launches_per_step, "gemm_flop": gemm_flop, "attn_flop": attn_flop,
+           "bf16_peak": bf16_peak, "floor_ms": round(floor_ms, 2), "frac_weighted": round(floor_ms / ms, 4),
+           "h2d": int(x_host.numel() * 2), "d2h": int(out_host.numel() * 2), "steps": steps, "warm": warm}
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
+def wan_cpu_baseline(tokens: int = 512, text: int = 128):
+    """One block of the fp32 torch restatement of the video-DiT block (oracle.wan_ref.block) on the host cores at a
+    reduced token count, scaled to the 30-block step at 2 x 20280 tokens by FLOPs (projections linear, attention
+    quadratic in the tokens): an extrapolation, flagged as such."""
+    import torch
+    from oracle import wan_ref
+    from flashrt_b200.wan_dit import synthetic_wan_state
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    st = synthetic_wan_state(0, layers=1)
+    bw = st["blocks"][0]
+    D, hd, B = 3072, 128, 2
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(B, tokens, D, generator=g)
+    ctx = torch.randn(B, text, 4096, generator=g)
+    tp = torch.randn(B, 6, D, generator=g) * 0.3
+    cos, sin = (torch.ones(tokens, hd // 2), torch.zeros(tokens, hd // 2))
+    t0 = time.perf_counter()
+    wan_ref.block(x, bw, tp, ctx, cos, sin, hd)
+    sec = time.perf_counter() - t0
+    Lf, Tf = 20280, 512
+    small = 2.0 * B * tokens * (3072 * 9216 + 3 * 3072 * 3072 + 2 * 3072 * 14336) + 4.0 * tokens * tokens * 3072 * B \
+        + 4.0 * tokens * text * 3072 * B
+    full = 2.0 * B * Lf * (3072 * 9216 + 3 * 3072 * 3072 + 2 * 3072 * 14336) + 4.0 * Lf * Lf * 3072 * B \
+        + 4.0 * Lf * Tf * 3072 * B
+    return {"value": round(sec * full / small * 30 * 1e3, 1), "unit": "ms", "cores": cores, "kind": "port",
+            "sample": (f"one block of the fp32 torch restatement at {tokens} latent + {text} text tokens "
+                       f"({sec:.2f} s), EXTRAPOLATED by FLOPs to 30 blocks at 20280 + 512 tokens")}
+
+
+def run_wan(args):
+    """Benchmark configuration 4: one denoise step of the video DiT, tensor-parallel over the N GPUs (strong scaling)."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    w = measure_wan(args, rank, world, local, steps, warm)
     if rank == 0:
-        from flashrt_b200 import flash_rt_kernels as fvk
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
-            os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops_sustained": 1400.0}
-        gemm_flop = 2.0 * B * L * (3072 * 9216 + 3 * 3072 * 3072 + 2 * 3072 * 14336) * layers
-        attn_flop = 4.0 * L * L * 3072 * B * layers + 4.0 * L * T * 3072 * B * layers
-        achieved = (gemm_flop + attn_flop) / world / (ms * 1e-3) / 1e12
-        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        try:
+            cpu = wan_cpu_baseline()
+        except Exception as e:  # noqa: BLE001
+            cpu = {"error": f"{type(e).__name__}: {e}"[:200]}
+        achieved = (w["gemm_flop"] + w["attn_flop"]) / world / (w["ms"] * 1e-3) / 1e12
         line = {
-            "metric": WAN_METRIC, "value": round(ms, 2), "unit": "ms", "n_gpus": world, "steps": steps, "warmup": warm,
-            "ms_per_step": round(ms, 2), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "metric": WAN_METRIC, "value": w["ms"], "unit": "ms", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": w["ms"], "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 GEMMs (fp32 accumulate), bf16 attention", "data": "synthetic",
-            "config": {"workload": WAN_WORKLOAD, "layers": layers, "parallelism": f"tp{world} (heads + FFN columns, "
+            "config": {"workload": WAN_WORKLOAD, "layers": w["layers"], "parallelism": f"tp{world} (heads + FFN columns, "
                        "NCCL all-reduce after attention-out, cross-attention-out and FFN-down)",
                        "l2": "activations of one step (> 1 GB) exceed the 126 MB L2; no explicit flush",
-                       "tensor_core_status": fvk.tensor_core_status(), "finite": bool(torch.isfinite(out.float()).all())},
-            "e2e": {"value": round(e2e_ms, 2), "unit": "ms", "h2d_bytes_per_step": int(x_host.numel() * 2),
-                    "d2h_bytes_per_step": int(out_host.numel() * 2)},
-            "gpu_launches": model.launches_per_step * steps,
+                       "tensor_core_status": w["status"], "finite": w["finite"]},
+            "e2e": {"value": w["e2e_ms"], "unit": "ms", "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"]},
+            "gpu_launches": w["launches"] * steps,
             "roofline": {"bound": "tensor", "kernel": "whole step (FP8 GEMMs + bf16 attention), per GPU",
-                         "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
-                         "frac": round(achieved / peak, 4), "traffic": None,
-                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (bf16 peak; FP8 GEMMs can exceed it)",
-                         "flop_per_step": gemm_flop + attn_flop},
-            "cpu_baseline": None, "clocks": clocks,
+                         # time-weighted: FP8 FLOPs against 2 x the measured bf16 rate, attention FLOPs against 1 x
+                         "achieved": round(achieved, 1), "peak": round((w["gemm_flop"] + w["attn_flop"]) / world /
+                                                                       (w["floor_ms"] * 1e-3) / 1e12, 1),
+                         "unit": "TFLOP/s", "frac": w["frac_weighted"], "traffic": None,
+                         "peak_source": ("time-weighted from MEASURED_PEAKS.json bf16_tflops_sustained: FP8 projections "
+                                         "at 2 x, bf16 attention at 1 x"),
+                         "floor_ms": w["floor_ms"], "flop_per_step": w["gemm_flop"] + w["attn_flop"]},
+            "cpu_baseline": cpu, "clocks": w["clocks"],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -389,15 +558,17 @@ def run_wan(args):
 
 
 # ---------------------------------------------------------------------------------------------------------------
-def run_ops(args):
+def ops_table(args, quick: bool):
     """Operator sweep (benchmark configuration 1) on one GPU: fused residual + RMSNorm + FP8 quantise over row widths,
     FP8 and NVFP4 GEMMs over M x (N, K).  Every case is timed as a CUDA graph of launches that cycle through
-    enough distinct buffers to exceed L2, with CUDA events around the replays.  One JSON line; the table is in
-    ``config.table`` (GB/s for the norm, TFLOP/s for the GEMMs, with the fraction of the measured peak)."""
+    enough distinct buffers to exceed L2, with CUDA events around the replays.  ``quick``: the norm rows and the FP8
+    GEMMs with M >= 2048 only.  The FP8 GEMMs with M >= 2048 carry a LIBRARY column beside them: the same product
+    through ``torch._scaled_mm`` (cuBLASLt FP8, per-tensor scales) on the same tensors -- the stated baseline, since
+    the reference's own sm_100 CUTLASS kernels cannot be built here; never on the hot path.
+    Returns (table, launches, peaks)."""
     import torch
     from flashrt_b200 import _lib
     from flashrt_b200 import flash_rt_fp4 as fp4
-    torch.cuda.set_device(0)
     peak_hbm, _ = _peaks()
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -409,7 +580,7 @@ def run_ops(args):
     L2 = 160e6
     launches = 0
 
-    def timed(enqueue, n_launch, reps=5):
+    def timed(enqueue, n_launch, reps=5, count=True):
         with torch.cuda.stream(s):
             enqueue()
             s.synchronize()
@@ -425,7 +596,8 @@ def run_ops(args):
             e1.record(s)
             s.synchronize()
         nonlocal launches
-        launches += n_launch * (1 + 3 + reps)
+        if count:
+            launches += n_launch * (1 + 3 + reps)
         return e0.elapsed_time(e1) * 1e-3 / (reps * n_launch)
 
     table = []
@@ -450,8 +622,8 @@ def run_ops(args):
     # ---- GEMMs
     NK = [(1024, 1024), (4096, 1024), (1024, 4096), (3072, 3072), (14336, 3072), (3072, 14336)]
     gemm_flags = 8 if args.cta_pair else 0       # bit 3: the 256 x 256-tile kernel on CTA pairs for M > 256
-    for kind in ("fp8", "nvfp4"):
-        for M in (16, 50, 256, 2048, 8192, 20480):
+    for kind in (("fp8",) if quick else ("fp8", "nvfp4")):
+        for M in ((2048, 8192, 20480) if quick else (16, 50, 256, 2048, 8192, 20480)):
             for N, K in NK:
                 eb = 1.0 if kind == "fp8" else 0.5
                 wbytes = N * K * eb
@@ -459,6 +631,7 @@ def run_ops(args):
                 A = torch.randint(0, 256, (M, int(K * eb)), dtype=torch.uint8, device="cuda")
                 Ws = [torch.randint(0, 120, (N, int(K * eb)), dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
                 D = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+                lib_us = None
                 if kind == "fp8":
                     A &= 0x77                      # finite E4M3 codes
                     def enq():
@@ -466,6 +639,16 @@ def run_ops(args):
                             _lib.call("frt_b200_gemm_fp8_nt", A.data_ptr(), w.data_ptr(), D.data_ptr(), M, N, K,
                                       one.data_ptr(), one.data_ptr(), 1.0, None, 0, gemm_flags if M > 256 else 0,
                                       s.cuda_stream)
+                    if M >= 2048:
+                        a8 = A.view(torch.float8_e4m3fn)
+                        w8 = [w.view(torch.float8_e4m3fn).t() for w in Ws]
+                        def enq_lib():
+                            for w in w8:
+                                torch._scaled_mm(a8, w, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                        try:
+                            lib_us = timed(enq_lib, nbuf, reps=3, count=False) * 1e6
+                        except Exception:  # noqa: BLE001
+                            lib_us = None
                 else:
                     sfa = torch.full((fp4.sfa_size_bytes(M, K),), 0x38, dtype=torch.uint8, device="cuda")
                     sfw = torch.full((fp4.sfa_size_bytes(N, K),), 0x30, dtype=torch.uint8, device="cuda")
@@ -477,22 +660,74 @@ def run_ops(args):
                 tf = 2.0 * M * N * K / t / 1e12
                 ob = 0.5625 if kind == "nvfp4" else 1.0
                 gbs = (ob * (N * K + M * K) + 2 * M * N) / t / 1e9
-                table.append({"op": "gemm_" + kind, "M": M, "N": N, "K": K, "us": round(t * 1e6, 2),
-                              "TFLOP/s": round(tf, 1),
-                              "frac_tensor": round(tf / (fp8_peak if kind == "fp8" else fp4_peak), 3),
-                              "GB/s": round(gbs, 1), "frac_hbm": round(gbs / peak_hbm, 3)})
+                row = {"op": "gemm_" + kind, "M": M, "N": N, "K": K, "us": round(t * 1e6, 2),
+                       "TFLOP/s": round(tf, 1),
+                       "frac_tensor": round(tf / (fp8_peak if kind == "fp8" else fp4_peak), 3),
+                       "frac_datasheet": round(tf / (4500.0 if kind == "fp8" else 9000.0), 3),
+                       "GB/s": round(gbs, 1), "frac_hbm": round(gbs / peak_hbm, 3)}
+                if lib_us is not None:
+                    row["cublaslt_us"] = round(lib_us, 2)
+                    row["vs_cublaslt"] = round(lib_us / (t * 1e6), 3)      # > 1: this library is faster
+                table.append(row)
                 del A, Ws, D
+    # ---- long-sequence bidirectional attention (the video-DiT shape) beside torch's fused SDPA, full sweep only
+    if not quick:
+        from flashrt_b200 import flash_rt_fa2 as fa2
+        B, Sq, H, Dh = 2, 20280, 24, 128
+        q = torch.randn(B, Sq, H, Dh, device="cuda").bfloat16()
+        k, v, o = torch.randn_like(q), torch.randn_like(q), torch.empty_like(q)
+        st3 = (Sq * H * Dh, H * Dh, Dh)
+        def enq_a():
+            fa2.fwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 0, 0, 0, B, Sq, Sq, H, H, Dh, st3, st3,
+                         st3, st3, Dh ** -0.5, 148, s.cuda_stream)
+        t = timed(enq_a, 1, reps=3)
+        qt, kt, vt = (z.transpose(1, 2) for z in (q, k, v))
+        def enq_s():
+            torch.nn.functional.scaled_dot_product_attention(qt, kt, vt)
+        try:
+            tl = timed(enq_s, 1, reps=3, count=False)
+        except Exception:  # noqa: BLE001
+            tl = None
+        fl = 4.0 * B * H * Sq * Sq * Dh
+        row = {"op": "attention_bf16", "B": B, "S": Sq, "H": H, "D": Dh, "us": round(t * 1e6, 1),
+               "TFLOP/s": round(fl / t / 1e12, 1), "frac_tensor": round(fl / t / 1e12 / bf16_tf, 3)}
+        if tl:
+            row["torch_sdpa_us"] = round(tl * 1e6, 1)
+            row["vs_torch_sdpa"] = round(tl / t, 3)
+        table.append(row)
+    return table, launches, {"hbm_gbs": peak_hbm, "fp8_tflops": fp8_peak, "nvfp4_tflops": fp4_peak,
+                             "fp8_datasheet_tflops": 4500.0,
+                             "note": "tensor peaks = 2x / 4x the measured cuBLAS bf16 burst; the 4.5 PF dense "
+                                     "FP8 datasheet figure beside it"}
+
+
+def ops_summary(args) -> dict:
+    """configs[1] in short for the default line: worst norm fraction of HBM peak, the FP8 GEMM fractions at M >= 2048
+    (of 2 x the measured bf16 burst), how many of the 18 reach 0.60, and the ratio to cuBLASLt per shape."""
+    table, _, _ = ops_table(args, quick=True)
+    norm = [r for r in table if r["op"] == "residual_add_rms_norm_fp8"]
+    big = [r for r in table if r["op"] == "gemm_fp8"]
+    key = lambda r: f"{r['M']}x{r['N']}x{r['K']}"  # noqa: E731
+    return {"norm_frac_min": min(r["frac_hbm"] for r in norm),
+            "gemm_fp8_frac": {key(r): r["frac_tensor"] for r in big},
+            "n_at_target": sum(1 for r in big if r["frac_tensor"] >= 0.60), "n_shapes": len(big),
+            "vs_cublaslt": {key(r): r.get("vs_cublaslt") for r in big}}
+
+
+def run_ops(args):
+    import torch
+    torch.cuda.set_device(0)
+    table, launches, peaks = ops_table(args, quick=False)
     from flashrt_b200 import flash_rt_kernels as fvk
     big = [r for r in table if r["op"] == "gemm_fp8" and r["M"] >= 2048]
     line = {"metric": "operator sweep (configs[1])", "value": round(statistics.mean(r["frac_tensor"] for r in big), 4),
             "unit": "mean fraction of 2 x measured bf16 peak over the FP8 GEMMs with M >= 2048", "n_gpus": 1,
             "steps": 1, "warmup": 3, "higher_is_better": True, "data": "synthetic", "dtype": "fp8_e4m3 / nvfp4 / bf16",
-            "config": {"workload": "configs[1] operator sweep", "peaks": {"hbm_gbs": peak_hbm, "fp8_tflops": fp8_peak,
-                                                                           "nvfp4_tflops": fp4_peak,
-                                                                           "note": "tensor peaks = 2x / 4x the measured cuBLAS bf16 burst"},
+            "config": {"workload": "configs[1] operator sweep", "peaks": peaks,
                        "l2": ("norm and M <= 256 GEMM cases cycle through distinct row / weight buffers totalling more than "
                               "L2; M >= 2048 GEMM cases alternate two weight buffers (tensor-bound)"),
                        "large_m_fp8_kernel": "cta pair (256 x 256 tiles)" if args.cta_pair else "persistent, one CTA per tile",
+                       "library_baseline": "torch._scaled_mm (cuBLASLt FP8) and torch SDPA on the same tensors",
                        "tensor_core_status": fvk.tensor_core_status(), "table": table},
             "gpu_launches": launches}
     print(json.dumps(line), flush=True)
@@ -562,61 +797,6 @@ def run_prefix(args):
     print(json.dumps(line), flush=True)
 
 
-def persistent_loop_ms(local: int, calib_samples: int):
-    """The same workload through ``persistent_loop=True`` (one cooperative launch per loop), timed by a child process
-    (``bench.py --persistent-loop --lean``) on the same GPU so that nothing it does can disturb this process's
-    measurement.  Never fails the bench: errors are reported in the value."""
-    env = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK=str(local))
-    for k in ("MASTER_ADDR", "MASTER_PORT", "GROUP_RANK", "LOCAL_WORLD_SIZE", "TORCHELASTIC_RUN_ID"):
-        env.pop(k, None)
-    cmd = [sys.executable, os.path.abspath(__file__), "--persistent-loop", "--lean", "--steps", "50", "--warmup", "5",
-           "--calib-samples", str(calib_samples)]
-    try:
-        r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
-        rec = json.loads(r.stdout.strip().splitlines()[-1])
-        return {"ms": rec["value"], "e2e_ms": rec["e2e_ms"], "launches_per_loop": 1,
-                "tensor_core_status": rec["tensor_core_status"]}
-    except Exception as e:  # noqa: BLE001
-        return {"error": f"{type(e).__name__}: {e}"[:200]}
-
-
-def loop_trace_report(ms: float) -> None:
-    """Phase timing of the persistent loop kernel from its device-side stamps (library built with
-    ``FRT_NVCC_EXTRA=-DFRT_LOOP_TRACE``): worker thread 0 of every CTA stamps %globaltimer at the start and end of each
-    phase of two decoder blocks of the second Euler step, the MMA thread when it sees its operands and when it has
-    issued its last MMA.  Printed to stderr; the JSON line on stdout is unchanged."""
-    import ctypes
-    import numpy as np
-    from flashrt_b200 import _lib
-    lib = _lib.load()
-    if not hasattr(lib, "frt_loop_trace_read"):
-        print("loop trace: the library was built without -DFRT_LOOP_TRACE", file=sys.stderr)
-        return
-    buf = (ctypes.c_ulonglong * (160 * 128))()
-    lib.frt_loop_trace_read.argtypes = [ctypes.c_void_p]
-    lib.frt_loop_trace_read(ctypes.addressof(buf))
-    t = np.frombuffer(buf, dtype=np.uint64).reshape(160, 128).astype(np.int64)
-    names = ["A rows", "B qkv", "C attention", "D combine", "E o-proj", "F rows", "G gate|up", "H down"]
-    tr = {1: 40, 4: 42, 6: 44, 7: 46}
-    out = [f"persistent loop: {ms:.3f} ms per loop; phase times in us (second Euler step, blocks 0 and 1)"]
-    for blk in range(2):
-        tt = t[:148, blk * 64: blk * 64 + 64]
-        out.append(f"block {blk}: {(tt[:, 32].max() - tt[:, 0].min()) / 1e3:.2f} us")
-        out.append("  phase         whole  slowest-CTA work  barrier (last arrival -> first release)  owners: operands in smem | MMA issue | epilogue")
-        for k, nm in enumerate(names):
-            st, en, nx = tt[:, 4 * k], tt[:, 4 * k + 3], tt[:, 4 * k + 4]
-            line = (f"  {nm:12s} {(nx.max() - st.min()) / 1e3:6.2f} {(en - st).max() / 1e3:10.2f} "
-                    f"{(nx.min() - en.max()) / 1e3:18.2f}")
-            if k in tr:
-                own = (tt[:, tr[k]] > st) & (tt[:, tr[k]] < st + 100000)
-                if own.any():
-                    med = lambda a, b: float(np.median((tt[:, a] - tt[:, b])[own])) / 1e3  # noqa: E731
-                    line += (f"{'':22s}{int(own.sum()):3d}: {med(tr[k], 4 * k):.2f} | {med(tr[k] + 1, tr[k]):.2f} | "
-                             f"{med(4 * k + 3, 4 * k + 2):.2f}")
-            out.append(line)
-    print("\n".join(out), file=sys.stderr, flush=True)
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -631,9 +811,11 @@ def main():
                     help="pi05 / fp8: run the whole denoise loop as one persistent cooperative kernel")
     ap.add_argument("--cta-pair", action="store_true",
                     help="--workload ops: run the FP8 GEMMs with M > 256 through the CTA-pair kernel")
-    ap.add_argument("--loop-trace", action="store_true",
-                    help="with --persistent-loop and a library built with FRT_NVCC_EXTRA=-DFRT_LOOP_TRACE: print the "
-                         "kernel's phase timing to stderr")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="pi05 workload: skip the short runs of the other configurations (video-DiT step, operator "
+                         "sweep, NVFP4 loop) that the default line carries as extra keys")
+    ap.add_argument("--extras-budget-s", type=float, default=150.0,
+                    help="an extra is started only while the whole run has taken less than this many seconds")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
     ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops", "prefix"],

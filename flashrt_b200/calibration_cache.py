@@ -3,9 +3,11 @@
 Calibration cache -- mirror of the reference's ``flash_rt/core/quant/calibrator.py:28-145``: static activation
 scales are specific to a checkpoint and to the prefix length, so they are stored as JSON under a key made of a
 fast checkpoint hash (SHA-256 of the first 64 KB of the file plus its size, 16 hex digits) and ``Se``, and
-validated on load (version, hash, Se, count).  Same file naming (``{hash}_Se{Se}.json``), same JSON keys for the
-part this path owns (``ae_scales`` = decoder scales, here one per (denoise step, layer, GEMM site), flattened in
-that order); the encoder fields of the reference's file are absent because the encoder is not part of this path.
+validated on load (version, hash, Se, count).  The record is NOT the reference's: it holds only the decoder table
+(``ae_scales``, here one scale per (denoise step, layer, GEMM site), flattened in that order) and none of the
+encoder fields, so a file of one implementation must never be taken for the other's.  The files therefore carry
+their own suffix (``{hash}_Se{Se}.b200dec.json`` next to the reference's ``{hash}_Se{Se}.json``) and their own
+``format`` tag; the reference neither finds nor overwrites them, and its files are left alone here.
 Default location ``~/.flash_rt/calibration`` as in the reference; ``cache_dir`` overrides it.
 
 Synthetic checkpoint -- a ``.safetensors`` file with the HF key names and shapes of the Pi0.5 action expert and
@@ -21,6 +23,8 @@ from pathlib import Path
 from typing import Optional
 
 CACHE_VERSION = 1
+CACHE_FORMAT = "flashrt_b200.decoder_scales"      # distinguishes the record from the reference's calibration files
+CACHE_SUFFIX = ".b200dec.json"
 DEFAULT_CACHE_DIR = Path.home() / ".flash_rt" / "calibration"
 
 
@@ -41,7 +45,7 @@ def checkpoint_hash(checkpoint_path: str, read_bytes: int = 65536) -> str:
 
 
 def cache_path(ckpt_hash: str, Se: int, cache_dir=None) -> Path:
-    return Path(cache_dir or DEFAULT_CACHE_DIR) / f"{ckpt_hash}_Se{Se}.json"
+    return Path(cache_dir or DEFAULT_CACHE_DIR) / f"{ckpt_hash}_Se{Se}{CACHE_SUFFIX}"
 
 
 def save_calibration(checkpoint_path: str, Se: int, ae_scales: list, metadata: Optional[dict] = None,
@@ -49,11 +53,11 @@ def save_calibration(checkpoint_path: str, Se: int, ae_scales: list, metadata: O
     ckpt = checkpoint_hash(checkpoint_path)
     path = cache_path(ckpt, Se, cache_dir)
     path.parent.mkdir(parents=True, exist_ok=True)
-    data = {"version": CACHE_VERSION, "ckpt_hash": ckpt, "Se": int(Se), "num_ae_scales": len(ae_scales),
+    data = {"format": CACHE_FORMAT, "version": CACHE_VERSION, "ckpt_hash": ckpt, "Se": int(Se), "num_ae_scales": len(ae_scales),
             "ae_scales": [float(v) for v in ae_scales]}
     if metadata is not None:
         data["metadata"] = metadata
-    tmp = path.with_suffix(".json.tmp")
+    tmp = path.with_name(path.name + ".tmp")
     with open(tmp, "w") as f:
         json.dump(data, f, indent=2)
     os.replace(tmp, path)
@@ -75,7 +79,8 @@ def load_calibration(checkpoint_path: str, Se: int, expected_count: Optional[int
             data = json.load(f)
     except (OSError, ValueError):
         return None
-    if data.get("version") != CACHE_VERSION or data.get("ckpt_hash") != ckpt or data.get("Se") != Se:
+    if (data.get("format") != CACHE_FORMAT or data.get("version") != CACHE_VERSION or data.get("ckpt_hash") != ckpt
+            or data.get("Se") != Se):
         return None
     scales = data.get("ae_scales")
     if not isinstance(scales, list) or data.get("num_ae_scales") != len(scales):

@@ -120,6 +120,9 @@ struct AttnParams {
     float* lse_accum;            // (splits, B, Hq, Sq) fp32, log2-domain log-sum-exp of the split (-inf if empty)
     unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals, readers; zero before first use
     float scale_log2;            // softmax_scale * log2(e)
+#ifdef FRT_TOK_TRACE
+    int trace_slot;
+#endif
 };
 
 template <int D, int BKV>
@@ -792,17 +795,19 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
 #define FRT_STATIC_CNT_BYTES ((size_t)FRT_STATIC_ATTN_MAX_TILES * 2 * 4)
 static __device__ __align__(256) unsigned char g_attn_static_scratch[FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES +
                                                                      FRT_STATIC_CNT_BYTES];
-// In host code the array's name is only a handle; the device address is asked for once per device.
+// In host code the array's name is only a handle; the device address is asked for once per device (under g_attn_mu).
 static void* g_attn_static_ptr[64] = {nullptr};
 
 // Same operation and arguments as frt_b200_attention_fwd_bf16 without the three scratch pointers: the split-KV
 // partials go to the module's own fixed device array (about 4.2 MB per GPU).  Limits: kv_splits <= 8,
 // batch * num_heads_q * seqlen_q <= 512, head_dim <= 256, at most 64 (row tile, kv head, batch) triples; anything
 // larger returns -4.  Nothing is allocated or freed by this call.  The first call on each device looks up the
-// array's device address (cudaGetSymbolAddress) and zeroes the arrival counters with a blocking memset: make that
-// first call before any stream capture.  Every call uses the same array, which keeps whatever the previous call
-// left in it (the kernel overwrites the partials it reads and re-arms the counters itself), so two calls whose
-// kernels can overlap on the GPU -- different streams, or graph branches -- would corrupt each other.
+// array's device address (cudaGetSymbolAddress) and clears the arrival counters with a memset enqueued on the
+// caller's stream in front of the kernel: make that first call before any stream capture (inside a capture it is
+// refused with -1).  Every call uses the same array, which keeps whatever the previous call left in it (the kernel
+// overwrites the partials it reads and re-arms the counters itself), so two calls whose kernels can overlap on the
+// GPU -- different streams, or graph branches -- would corrupt each other.  After a call whose bounded wait gave up
+// (frt_b200_attention_status != 0) the counters are stale: frt_b200_attention_status(1) clears them as well.
 int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                                const float* out_scale, float* lse, const int* seqused_k, int batch,
                                                int seqlen_q, int seqlen_k, int num_heads_q, int num_heads_kv,
@@ -810,8 +815,11 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
                                                const long long* v_strides, const long long* o_strides,
                                                float softmax_scale, int kv_splits, int kv_static_rows, int flags,
                                                void* stream) {
-    if (batch <= 0 || seqlen_q < 0 || num_heads_q <= 0 || num_heads_kv <= 0 || (num_heads_q % num_heads_kv))
+    if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return FRT_ERR_INVALID;
+    if (batch <= 0 || seqlen_q < 0 || seqlen_k <= 0 || num_heads_q <= 0 || num_heads_kv <= 0 ||
+        (num_heads_q % num_heads_kv))
         return FRT_ERR_INVALID;
+    if (O_fp8 && !out_scale) return FRT_ERR_INVALID;
     const long long rows = (long long)batch * num_heads_q * seqlen_q;
     const int G = num_heads_q / num_heads_kv;
     const long long tiles = (((long long)seqlen_q * G + 127) / 128) * num_heads_kv * batch;
@@ -822,16 +830,24 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return FRT_CUDA_ERR(e);
     if (dev < 0 || dev >= 64) return FRT_ERR_UNSUPPORTED;
-    if (!g_attn_static_ptr[dev]) {
-        void* ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_attn_static_scratch);
-        if (e != cudaSuccess || !ptr) return FRT_CUDA_ERR(e);
-        e = cudaMemset(static_cast<unsigned char*>(ptr) + FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES, 0,
-                       FRT_STATIC_CNT_BYTES);
-        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        g_attn_static_ptr[dev] = ptr;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_attn_mu);
+        if (!g_attn_static_ptr[dev]) {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            e = cudaStreamIsCapturing((cudaStream_t)stream, &cap);
+            if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+            if (cap != cudaStreamCaptureStatusNone) return FRT_ERR_INVALID;   // set-up call must precede any capture
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_attn_static_scratch);
+            if (e != cudaSuccess || !ptr) return e != cudaSuccess ? FRT_CUDA_ERR(e) : FRT_ERR_INVALID;
+            e = cudaMemsetAsync(static_cast<unsigned char*>(ptr) + FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES, 0,
+                                FRT_STATIC_CNT_BYTES, (cudaStream_t)stream);
+            if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+            g_attn_static_ptr[dev] = ptr;
+        }
+        base = static_cast<unsigned char*>(g_attn_static_ptr[dev]);
     }
-    unsigned char* base = static_cast<unsigned char*>(g_attn_static_ptr[dev]);
     return frt_b200_attention_fwd_bf16(Q, K, V, O, O_fp8, out_scale, lse, seqused_k, batch, seqlen_q, seqlen_k,
                                        num_heads_q, num_heads_kv, head_dim, q_strides, k_strides, v_strides, o_strides,
                                        softmax_scale, kv_splits, kv_static_rows, reinterpret_cast<float*>(base),
@@ -840,17 +856,38 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
 }
 
 // returns (and optionally clears) the attention kernels' device status word; 0 = no bounded wait gave up.
-// code 0x11 = TMA producer, 0x12 = MMA issuer, 0x13 = softmax warps.  Synchronises the device.
+// code 0x11 = TMA producer, 0x12 = MMA issuer, 0x13 = softmax warps.  Synchronises the device.  Clearing a
+// non-zero status also clears the arrival counters of the built-in scratch on the current device (a kernel that
+// gave up leaves them mid-count, and the static-scratch caller has no buffer of its own to re-zero).
 int frt_b200_attention_status(int reset) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return FRT_CUDA_ERR(e);
     int v = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int));
+    e = cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int));
     if (e != cudaSuccess) return FRT_CUDA_ERR(e);
     if (reset && v) {
         int z = 0;
         cudaMemcpyToSymbol(g_attn_status, &z, sizeof(int));
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+            std::lock_guard<std::mutex> lk(g_attn_mu);
+            if (g_attn_static_ptr[dev]) {
+                cudaMemset(static_cast<unsigned char*>(g_attn_static_ptr[dev]) + FRT_STATIC_O_BYTES +
+                               FRT_STATIC_LSE_BYTES, 0, FRT_STATIC_CNT_BYTES);
+                cudaDeviceSynchronize();
+            }
+        }
     }
     return v;
 }
+
+#ifdef FRT_TOK_TRACE
+int frt_attn_trace_read(unsigned long long* host, int reset_slot) {
+    cudaDeviceSynchronize();
+    if (reset_slot) g_attn_trace_slot = 0;
+    return (int)cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(unsigned long long) * 8 * 64 * 16);
+}
+#endif
 
 #ifdef FRT_TRACE
 int frt_atrace_read(long long* host64) {

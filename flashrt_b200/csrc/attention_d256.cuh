@@ -9,9 +9,24 @@
 //   * P (bf16) overlays its S buffer and feeds the PV MMA as the A operand from TMEM -- no shared-memory round trip;
 //   * the row of S lives in registers (one tcgen05.wait per chunk); O is rescaled only when a row maximum grows by
 //     more than 2^8.
-// KV splits: none (gridDim.z = 1, result written directly) or through the caller's scratch (same layout, arrival
-// counters and combine as the single-tile kernel's scratch path).  Warps: 0-3 softmax (thread = row), 4 TMA, 5 MMA.
+// KV splits: none (gridDim.z = 1, result written directly) or through the caller's scratch.  The scratch path is
+// built around bulk copies: a split's normalised O leaves as bf16 in column slices [slice][row][D / C] -- one
+// contiguous block per (row tile, split), written by ONE cp.async.bulk from shared memory -- then the arrival
+// counter, and every split fetches its own column slice of all C partials with C bulk loads and combines them out
+// of shared memory.  (Measured at the action-expert shape with per-thread fp32 stores and loads instead: 2.4 us to
+// publish, 4.9 us to combine -- five dependent L2 round trips per thread -- out of 14.5 us per launch.)
+// Warps: 0-3 softmax (thread = row), 4 TMA, 5 MMA.
 #pragma once
+
+#ifdef FRT_TOK_TRACE
+__device__ unsigned long long g_attn_trace[8][64][16];
+static int g_attn_trace_slot = 0;
+#define ATT_STAMP(i) do { if (threadIdx.x == 0) g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 64][i] = tc::global_timer_ns(); } while (0)
+#define ATT_STAMP_ANY(i) do { g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 64][i] = tc::global_timer_ns(); } while (0)
+#else
+#define ATT_STAMP(i)
+#define ATT_STAMP_ANY(i)
+#endif
 
 struct D256Cfg {
     static constexpr int D = 256, BKV = 64;
@@ -38,7 +53,6 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* sQ = smem;
     uint8_t* sK = smem + Cfg::OFF_K;
     uint8_t* sV = smem + Cfg::OFF_V;
-    float* red = reinterpret_cast<float*>(smem);                       // aliases the operand tiles after the last MMA
     float* s_lse = reinterpret_cast<float*>(smem + Cfg::DATA_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::DATA_BYTES + Cfg::ML_BYTES);
     uint64_t* q_full = bars + 0;
@@ -49,12 +63,14 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t* p_ready = bars + 9;     // [2] 128 arrivals per chunk, one barrier per S / P buffer
     uint64_t* o_full = bars + 11;     // PV of a chunk has completed (read only where the count is known to within one)
     uint64_t* o_done = bars + 12;     // every PV of this CTA has completed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* c_full = bars + 13;     // the C column slices of the combine have landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    ATT_STAMP(0);
     const bool via_scratch = p.o_accum != nullptr;
     const uint32_t C = gridDim.z;
     const uint32_t rank = blockIdx.z;
@@ -62,6 +78,10 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int hk = blockIdx.y % p.Hkv;
     const int b = blockIdx.y / p.Hkv;
     const int tok0 = tile * (128 / p.G);
+    const int gshift = 31 - __clz(p.G);
+    int rows_valid = (p.Sq - tok0) << gshift;                       // query rows (token x head-in-group) of this tile
+    rows_valid = rows_valid > 128 ? 128 : rows_valid;
+    uint8_t* cbuf = smem;                                           // the C column slices of the combine, up to 64 KB
     const int c_begin = (int)((long long)p.chunks_total * rank / C);
     const int c_end = (int)((long long)p.chunks_total * (rank + 1) / C);
     const int nchunks = c_end - c_begin;
@@ -78,6 +98,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc::mbar_init(&p_ready[1], 128);
         tc::mbar_init(o_full, 1);
         tc::mbar_init(o_done, 1);
+        tc::mbar_init(c_full, 1);
         *abort_flag = 0;
         tc::mbar_fence_init();
         tc::tma_prefetch_desc(&tmQ);
@@ -114,6 +135,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             ++early;
         }
         pdl_wait();
+        ATT_STAMP_ANY(1);
         tc::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
         for (int db = 0; db < 4; ++db)
             tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, q_full, db * 64, 0, hk, tok0, b);
@@ -139,6 +161,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc::mma_commit(&s_full[j & 1]);
         };
         ATTN_WAIT(q_full, 0u, AERR_MMA);
+        ATT_STAMP_ANY(2);
         if (nchunks > 0 && !*abort_flag) {
             ATTN_WAIT(&k_full[0], 0u, AERR_MMA);
             if (!*abort_flag) {
@@ -167,6 +190,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc::mma_commit(o_full);
         }
         if (!*abort_flag) tc::mma_commit(o_done);
+        ATT_STAMP_ANY(3);
     } else if (warp < 4) {
         // ---------------- softmax: thread = row
         pdl_wait();
@@ -182,6 +206,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             __syncwarp();
             if (__any_sync(0xffffffffu, *abort_flag != 0)) { alive = false; break; }
             tc::tc_fence_after_sync();
+            if (j == 0) ATT_STAMP(4);
             const uint32_t tmem_S = tmem + Cfg::S_COL + (j & 1) * 64 + lane_off;
             const int valid = kv_len - (c_begin + j) * BKV;
             uint32_t sv[BKV];
@@ -240,37 +265,73 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             tc::tc_fence_before_sync();
             tc::mbar_arrive(&p_ready[j & 1]);
+            if (j == 0) ATT_STAMP(5);
         }
+        ATT_STAMP(6);
         // ---------------- the accumulated O of this split (o_full may be two completions behind here: use o_done)
         if (alive) {
             if (nchunks > 0) ATTN_WAIT(o_done, 0u, AERR_SOFTMAX);
             __syncwarp();
             alive = !__any_sync(0xffffffffu, *abort_flag != 0);
         }
+        ATT_STAMP(7);
         if (alive) {
             tc::tc_fence_after_sync();
             const float invl = l_run > 0.0f ? 1.0f / l_run : 0.0f;
             if (via_scratch) {
-                // O / l (log2-domain lse alongside) -> shared memory, rows with xor-swizzled 16-byte chunks; the whole
-                // CTA then copies full rows to the global scratch with coalesced stores
-                s_lse[row] = l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t v[32];
-                    if (nchunks > 0) {
-                        tc::tmem_ld32(tmem_O + c, v);
+                // O / l as bf16 straight from registers to the scratch in column slices [slice][row][D / C]: the 64
+                // bytes a thread writes per 32 columns are adjacent to its neighbours' (the rows of a slice are
+                // contiguous), so a warp's store covers 2 KB without gaps.  Log2-domain lse alongside.
+                const int dper = D / (int)C;                   // columns per slice: 32 .. 256, a multiple of 32
+                const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;
+                const size_t row0 = ((size_t)(b * p.Hkv + hk) * p.Sq << gshift) + (size_t)tile * 128;
+                uint8_t* blk = reinterpret_cast<uint8_t*>(p.o_accum) + (rank * split_stride + row0) * (size_t)(D * 2);
+                if (row < rows_valid)
+                    __stcg(p.lse_accum + rank * split_stride + row0 + row,
+                           l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY);
+                // 64 columns per step, the next step's tensor-memory load in flight while this one is converted
+                auto emit = [&](const uint32_t* v, int c) {
+                    if (row < rows_valid) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int cc = c + 32 * h;
+                            uint4* dst = reinterpret_cast<uint4*>(blk + ((size_t)(cc / dper) * rows_valid + row) * (dper * 2) +
+                                                                  (cc % dper) * 2);
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; ++j4) {
+                                const uint32_t* w = v + 32 * h + 8 * j4;
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(w[0]) * invl, __uint_as_float(w[1]) * invl);
+                                o.y = pack_bf16x2(__uint_as_float(w[2]) * invl, __uint_as_float(w[3]) * invl);
+                                o.z = pack_bf16x2(__uint_as_float(w[4]) * invl, __uint_as_float(w[5]) * invl);
+                                o.w = pack_bf16x2(__uint_as_float(w[6]) * invl, __uint_as_float(w[7]) * invl);
+                                __stcg(dst + j4, o);
+                            }
+                        }
+                    }
+                };
+                uint32_t va[64], vb[64];
+                if (nchunks > 0) {                              // warp-uniform: the loads are warp-collective
+                    tc::tmem_ld32(tmem_O + 0, va);
+                    tc::tmem_ld32(tmem_O + 32, va + 32);
+#pragma unroll
+                    for (int c = 0; c < D; c += 128) {
                         tc::tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = 0u;
+                        tc::tmem_ld32(tmem_O + c + 64, vb);
+                        tc::tmem_ld32(tmem_O + c + 96, vb + 32);
+                        emit(va, c);
+                        tc::tmem_ld_wait();
+                        if (c + 128 < D) {
+                            tc::tmem_ld32(tmem_O + c + 128, va);
+                            tc::tmem_ld32(tmem_O + c + 160, va + 32);
+                        }
+                        emit(vb, c + 64);
                     }
+                } else {
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
-                        const int ch = (c >> 2) + j4;
-                        *reinterpret_cast<float4*>(&red[(size_t)row * D + ((ch ^ (row & 7)) << 2)]) =
-                            make_float4(__uint_as_float(v[j4 * 4]) * invl, __uint_as_float(v[j4 * 4 + 1]) * invl,
-                                        __uint_as_float(v[j4 * 4 + 2]) * invl, __uint_as_float(v[j4 * 4 + 3]) * invl);
-                    }
+                    for (int i = 0; i < 64; ++i) va[i] = 0u;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 64) emit(va, c);
                 }
             } else {
                 // single split: the result leaves directly, one row per thread
@@ -323,31 +384,25 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     __syncwarp();
     if (via_scratch) {
-        // ---------------- combine through global scratch: every CTA of the tile publishes its partial, waits
-        // (bounded) for all C of them and finishes D / C columns of every row; all global accesses coalesced
+        // ---------------- combine through global scratch.  Block of (batch, kv head, tile, split) in o_accum, as bf16:
+        // rows_valid x D, stored [slice][row][D / C]; the rows of all tiles of one (split, batch, kv head) are packed
+        // back to back, so the caller's (splits, batch, heads, seqlen_q, D) fp32 buffer is always large enough.
         const unsigned tile_id = (unsigned)((b * p.Hkv + hk) * gridDim.x + tile);
         unsigned* cnt = p.counters + 2 * tile_id;
-        const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;
+        const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;            // rows per split in the scratch
+        const size_t row0 = ((size_t)(b * p.Hkv + hk) * p.Sq << gshift) + (size_t)tile * 128;
         const int dper = D / (int)C;
-        __syncthreads();
-        const int gshift = 31 - __clz(p.G);
-        int rows_valid = (p.Sq - tok0) << gshift;
-        rows_valid = rows_valid > 128 ? 128 : rows_valid;
-        if (!*abort_flag) {
-#pragma unroll 4
-            for (int r = warp; r < rows_valid; r += 6) {
-                const int t = tok0 + (r >> gshift);
-                const int hq = hk * p.G + (r & (p.G - 1));
-                const size_t ridx = rank * split_stride + ((size_t)b * p.Hq + hq) * p.Sq + t;
-                float4* dst = reinterpret_cast<float4*>(p.o_accum + ridx * D);
-#pragma unroll
-                for (int ch = lane; ch < D / 4; ch += 32)
-                    __stcg(dst + ch, *reinterpret_cast<const float4*>(&red[(size_t)r * D + ((ch ^ (r & 7)) << 2)]));
-                if (lane == 0) __stcg(p.lse_accum + ridx, s_lse[r]);
-            }
-        }
+        const uint32_t slice_bytes = (uint32_t)rows_valid * dper * 2;
+        uint8_t* gbase = reinterpret_cast<uint8_t*>(p.o_accum);
+        float* s_w = reinterpret_cast<float*>(smem + 65536);        // [row][8] combine weights
+        float* s_l = s_w + 128 * 8;                                  // [split][row] log-sum-exps of the partials
+        // the log-sum-exps of a tile are rows_valid consecutive floats per split: fetched with the slices when aligned
+        const bool lse_bulk = ((split_stride | row0 | (size_t)rows_valid) & 3) == 0 &&
+                              (reinterpret_cast<uintptr_t>(p.lse_accum) & 15) == 0;
+        ATT_STAMP(8);
         __threadfence();
         __syncthreads();
+        ATT_STAMP(9);
         if (threadIdx.x == 0) {
             atomicAdd(cnt, 1u);
             bool ok = false;
@@ -362,32 +417,36 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (!ok) {
                 if (!*abort_flag) atomicCAS(&g_attn_status, 0, AERR_SOFTMAX | (blockIdx.x << 8));
                 *abort_flag = 1;
+            } else {
+                // this split's column slice of all C partials: C bulk loads of rows_valid x dper bf16
+                asm volatile("fence.proxy.async;" ::: "memory");
+                tc::mbar_arrive_expect_tx(c_full, C * slice_bytes + (lse_bulk ? C * (uint32_t)rows_valid * 4u : 0u));
+                for (uint32_t sidx = 0; sidx < C; ++sidx) {
+                    tc::bulk_load(cbuf + sidx * slice_bytes,
+                                  gbase + (sidx * split_stride + row0) * (size_t)(D * 2) + (size_t)rank * slice_bytes,
+                                  slice_bytes, c_full);
+                    if (lse_bulk)
+                        tc::bulk_load(s_l + sidx * 128, p.lse_accum + sidx * split_stride + row0,
+                                      (uint32_t)rows_valid * 4u, c_full);
+                }
             }
         }
         __syncthreads();
+        ATT_STAMP(10);
         if (!*abort_flag) {
-            const int cpr = dper >> 2;
-            const int d0 = (int)rank * dper;
-            const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
-            const int cshift = 31 - __clz(cpr);
-#pragma unroll 2
-            for (int idx = threadIdx.x; idx < rows_valid * cpr; idx += 192) {
-                const int r = idx >> cshift, ch = idx & (cpr - 1);
+            // weights of the C partials of a row from their log-sum-exps
+            if (lse_bulk) ATTN_WAIT(c_full, 0u, AERR_SOFTMAX);
+            if ((int)threadIdx.x < rows_valid && !*abort_flag) {
+                const int r = threadIdx.x;
                 const int t = tok0 + (r >> gshift);
                 const int hq = hk * p.G + (r & (p.G - 1));
                 const size_t r0 = ((size_t)b * p.Hq + hq) * p.Sq + t;
                 float w[8];
-                float4 x[8];
 #pragma unroll
-                for (int sidx = 0; sidx < 8; ++sidx) {
-                    if ((uint32_t)sidx < C) {
-                        w[sidx] = __ldcg(p.lse_accum + sidx * split_stride + r0);
-                        x[sidx] = __ldcg(reinterpret_cast<const float4*>(p.o_accum + (sidx * split_stride + r0) * D + d0) + ch);
-                    } else {
-                        w[sidx] = -INFINITY;
-                        x[sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                }
+                for (int sidx = 0; sidx < 8; ++sidx)
+                    w[sidx] = (uint32_t)sidx < C
+                                  ? (lse_bulk ? s_l[sidx * 128 + r] : __ldcg(p.lse_accum + sidx * split_stride + row0 + r))
+                                  : -INFINITY;
                 float M = -INFINITY;
 #pragma unroll
                 for (int sidx = 0; sidx < 8; ++sidx) M = fmaxf(M, w[sidx]);
@@ -398,30 +457,58 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     Lw += w[sidx];
                 }
                 const float invL = Lw > 0.0f ? 1.0f / Lw : 0.0f;
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-                for (int sidx = 0; sidx < 8; ++sidx) {
-                    const float ws = w[sidx] * invL;
-                    a0 += ws * x[sidx].x; a1 += ws * x[sidx].y; a2 += ws * x[sidx].z; a3 += ws * x[sidx].w;
+                for (int sidx = 0; sidx < 8; ++sidx) s_w[r * 8 + sidx] = w[sidx] * invL;
+                if (p.lse && rank == 0) p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
+            }
+            if (!lse_bulk) ATTN_WAIT(c_full, 0u, AERR_SOFTMAX);
+        }
+        __syncthreads();
+        if (!*abort_flag) {
+            const int cpr = dper >> 3;                       // 16-byte chunks (8 columns) per slice row
+            const int d0 = (int)rank * dper;
+            const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+            const int cshift = 31 - __clz(cpr);
+            for (int idx = threadIdx.x; idx < rows_valid * cpr; idx += 192) {
+                const int r = idx >> cshift, ch = idx & (cpr - 1);
+                const int t = tok0 + (r >> gshift);
+                const int hq = hk * p.G + (r & (p.G - 1));
+                float a[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a[i] = 0.0f;
+                for (uint32_t sidx = 0; sidx < C; ++sidx) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(cbuf + sidx * slice_bytes + ((size_t)r * cpr + ch) * 16);
+                    const float ws = s_w[r * 8 + sidx];
+                    float f0, f1;
+                    unpack_bf16x2(x.x, f0, f1); a[0] += ws * f0; a[1] += ws * f1;
+                    unpack_bf16x2(x.y, f0, f1); a[2] += ws * f0; a[3] += ws * f1;
+                    unpack_bf16x2(x.z, f0, f1); a[4] += ws * f0; a[5] += ws * f1;
+                    unpack_bf16x2(x.w, f0, f1); a[6] += ws * f0; a[7] += ws * f1;
                 }
-                const size_t o = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs + d0 + ch * 4;
-                uint2 ob;
-                ob.x = pack_bf16x2(a0, a1);
-                ob.y = pack_bf16x2(a2, a3);
-                st_global_v2(p.O + o, ob);
+                const size_t o = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs + d0 + ch * 8;
+                uint4 ob;
+                ob.x = pack_bf16x2(a[0], a[1]);
+                ob.y = pack_bf16x2(a[2], a[3]);
+                ob.z = pack_bf16x2(a[4], a[5]);
+                ob.w = pack_bf16x2(a[6], a[7]);
+                st_global_v4(p.O + o, ob);
                 if (p.O_fp8) {
-                    float q0, q1, q2, q3;
-                    unpack_bf16x2(ob.x, q0, q1);
-                    unpack_bf16x2(ob.y, q2, q3);
-                    *reinterpret_cast<uint32_t*>(p.O_fp8 + o) =
-                        f32x4_to_e4m3x4(clamp448(__fmul_rn(q0, inv_os)), clamp448(__fmul_rn(q1, inv_os)),
-                                        clamp448(__fmul_rn(q2, inv_os)), clamp448(__fmul_rn(q3, inv_os)));
+                    float q[8];
+                    unpack_bf16x2(ob.x, q[0], q[1]);
+                    unpack_bf16x2(ob.y, q[2], q[3]);
+                    unpack_bf16x2(ob.z, q[4], q[5]);
+                    unpack_bf16x2(ob.w, q[6], q[7]);
+                    uint2 o8;
+                    o8.x = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[0], inv_os)), clamp448(__fmul_rn(q[1], inv_os)),
+                                           clamp448(__fmul_rn(q[2], inv_os)), clamp448(__fmul_rn(q[3], inv_os)));
+                    o8.y = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[4], inv_os)), clamp448(__fmul_rn(q[5], inv_os)),
+                                           clamp448(__fmul_rn(q[6], inv_os)), clamp448(__fmul_rn(q[7], inv_os)));
+                    st_global_v2(p.O_fp8 + o, o8);
                 }
-                if (p.lse && rank == 0 && ch == 0)
-                    p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
             }
         }
         __syncthreads();
+        ATT_STAMP(11);
         if (threadIdx.x == 0) {
             const unsigned done = atomicAdd(cnt + 1, 1u);
             if (done == C - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
@@ -430,6 +517,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc::tc_fence_before_sync();
     __syncthreads();
     if (warp == 5) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+    ATT_STAMP(12);
 }
 
 static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
@@ -460,6 +548,10 @@ static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnPar
         rc = make_tmap_bf16(&tmV, V, 4, dims, strv, box);
         if (rc) return rc;
     }
+#ifdef FRT_TOK_TRACE
+    p.trace_slot = g_attn_trace_slot;
+    g_attn_trace_slot = (g_attn_trace_slot + 1) % 8;
+#endif
     p.chunks_total = (p.Skv + Cfg::BKV - 1) / Cfg::BKV;
     if (splits > p.chunks_total) splits = p.chunks_total;
     if (splits < 1) splits = 1;

@@ -1046,12 +1046,12 @@ int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int
     p.out8 = (uint8_t*)out8;
     p.out_scale = d_out_scale;
     p.half = half;
-    if (tok_eligible(M, p.N, K, flags) && M <= 128 && (half % 128) == 0) {
+    if (tok_eligible(M, p.N, K, flags) && M <= 128 && (half % 64) == 0) {
         TokParams t = {};
         t.M = M; t.N = p.N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
         t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
-        int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, 256, tok_split_hint(splits), flags & 1,
-                                                              (cudaStream_t)stream);
+        int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
+                                                              flags & 1, (cudaStream_t)stream);
         if (rc != FRT_ERR_UNSUPPORTED) return rc;
     }
     return dispatch_small_m<EPI_GEGLU_FP8>(A, W, p, K, M, half / 64, splits, flags & 1, (cudaStream_t)stream);
@@ -1201,7 +1201,8 @@ int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int 
     TokPlan pl;
     int bn = tok_bn_hint(flags);
     if (bn == 0 && (N % 128)) bn = 64;
-    if (!tok_plan(N, K, 1, TOK_EPI_RESID, TOK_PRO_TMA, tok_sm_count(), bn, tok_split_hint(splits), &pl))
+    if (!tok_plan(N, K, 1, M < 128 ? (M > 0 ? M : 1) : 128, TOK_EPI_RESID, TOK_PRO_TMA, tok_sm_count(), bn,
+                  tok_split_hint(splits), &pl))
         return FRT_ERR_UNSUPPORTED;
     if (stat_tiles) *stat_tiles = N / pl.BN;
     if (M == 0) return FRT_OK;
@@ -1248,7 +1249,7 @@ int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, in
     if (!x || !stats_in || !style || !W || !out8 || !d_scale_a || !d_out_scale || M < 0 || half <= 0 || K <= 0 ||
         n_stat <= 0)
         return FRT_ERR_INVALID;
-    if ((K % 128) || M > 128 || (half % 128)) return FRT_ERR_UNSUPPORTED;
+    if ((K % 128) || M > 128 || (half % 64)) return FRT_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(style) & 15)) return FRT_ERR_INVALID;
     if (M == 0) return FRT_OK;
     TokParams t = {};
@@ -1256,8 +1257,8 @@ int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, in
     t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
     t.x = (const __nv_bfloat16*)x; t.stats_in = stats_in; t.n_stat = n_stat; t.style = (const __nv_bfloat16*)style;
     t.eps = eps;
-    return dispatch_gemm_tok<TOK_PRO_NORM, TOK_EPI_GEGLU>(nullptr, W, t, K, 256, tok_split_hint(splits), flags & 1,
-                                                         (cudaStream_t)stream);
+    return dispatch_gemm_tok<TOK_PRO_NORM, TOK_EPI_GEGLU>(nullptr, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
+                                                         flags & 1, (cudaStream_t)stream);
 }
 
 // returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)
@@ -1271,6 +1272,14 @@ int frt_b200_gemm_status(int reset) {
     }
     return v;
 }
+
+#ifdef FRT_TOK_TRACE
+int frt_tok_trace_read(unsigned long long* host, int reset_slot) {
+    cudaDeviceSynchronize();
+    if (reset_slot) g_tok_trace_slot = 0;
+    return (int)cudaMemcpyFromSymbol(host, g_tok_trace, sizeof(unsigned long long) * 8 * 160 * 16);
+}
+#endif
 
 #ifdef FRT_TRACE
 int frt_trace_read(long long* host64) {

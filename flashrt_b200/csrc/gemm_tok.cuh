@@ -12,9 +12,15 @@
 //   * an accumulator row is one token: a thread that finishes (token, 8 features) holds 8 CONSECUTIVE output
 //     features, so RoPE pairs, GeGLU (gate column j and up column 128 + j of the same tile), the gated residual
 //     update and the row sum of squares all stay inside a thread or a group of 8-16 neighbouring lanes.
-// Split-K partials are staged in shared memory as rows of fp32 (16-byte chunks xor-swizzled by the row) and summed
-// in fixed order 0, 1, ... through distributed shared memory; rank r of the cluster finishes a contiguous range of
-// tokens.  No global workspace; results are deterministic.
+// Split-K: rank r of the cluster finishes a contiguous range of tokens.  Every rank PUSHES the accumulator rows of a
+// token straight from registers into the owner's shared memory (st.async, 16 bytes each, completing bytes on the
+// owner's mbarrier); the owner waits for S x tokens x BN x 4 bytes and sums the S slots in fixed order 0, 1, ...
+// No cluster barrier and no remote load sits between the last MMA and the result.  Measured on B200: a cluster
+// barrier costs 0.75 us and a pull-based exchange needs two of them plus two remote round trips (6.2 us per launch
+// of the attention-out projection against 4.3 us with the push); staging the rows and pushing them with
+// cp.async.bulk (shared::cta -> shared::cluster) was no faster: either way the cluster network moves about
+// 2.2 TB/s over the whole chip (~17 GB/s per SM), so the tile width and the split are chosen to keep the exchanged
+// bytes per CTA ((S - 1) / S x tokens x BN x 4) near 10 KB.  No global workspace; deterministic.
 //
 // A operand: FP8 activations by TMA (PRO_TMA), or produced inside the kernel (PRO_NORM): every CTA reads the bf16
 // residual rows of its K-slice, the per-tile partial sums of squares left by the previous projection's epilogue
@@ -31,6 +37,14 @@
 // thread still reaches the cluster barriers and the TMEM release.
 #pragma once
 
+#ifdef FRT_TOK_TRACE
+__device__ unsigned long long g_tok_trace[8][160][16];
+static int g_tok_trace_slot = 0;
+#define TOK_STAMP(i) do { if (threadIdx.x == tstamp_thread) g_tok_trace[p.trace_slot][ (blockIdx.z * gridDim.x + blockIdx.x) % 160][i] = tc::global_timer_ns(); } while (0)
+#else
+#define TOK_STAMP(i)
+#endif
+
 enum { TOK_EPI_BF16 = 0, TOK_EPI_ROPE = 1, TOK_EPI_GEGLU = 2, TOK_EPI_RESID = 3 };
 enum { TOK_PRO_TMA = 0, TOK_PRO_NORM = 1 };
 enum { TOK_STAT_STRIDE = 128 };          // floats between the per-tile rows of a statistics buffer
@@ -39,7 +53,8 @@ struct TokParams {
     int M, N;                  // activation rows (all m-tiles), output features
     int nkb;                   // 128-byte k-blocks per split
     int stages;                // shared-memory ring depth (>= nkb when the A operand is produced in the kernel)
-    int stage_rows;            // rows of the fp32 staging area = tokens of an m-tile rounded up to 32
+    int per;                   // tokens finished by one rank of the cluster = ceil(tokens of an m-tile / S)
+    int ring_bytes;            // bytes of the operand ring / staging area in front of the receive slots
     const float* sa;           // device scalars (may be null = 1): activation / weight scale
     const float* sb;
     float alpha_host;
@@ -68,6 +83,9 @@ struct TokParams {
     int K;
     const __nv_bfloat16* style;
     float eps;
+#ifdef FRT_TOK_TRACE
+    int trace_slot;
+#endif
 };
 
 template <int BN>
@@ -78,56 +96,49 @@ struct TokCfg {
     static constexpr int MAX_STAGES = BN == 256 ? 4 : BN == 128 ? 6 : 8;
     static constexpr int AUX_BYTES = 2048;                    // barriers, flags, per-token 1 / rms
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static int smem_bytes(int stages, int stage_rows) {
-        const int ops = stages * STAGE_BYTES, red = stage_rows * BN * 4;
-        return AUX_BYTES + 1024 + (ops > red ? ops : red);
+    // operand ring, then the receive slots [S][per][BN] fp32 of the split-K exchange (never aliased: a fast rank
+    // pushes while a slow rank's MMAs still read its operands)
+    static int ring_bytes(int stages, int S, int per) { return stages * STAGE_BYTES; }
+    static int smem_bytes(int stages, int S, int per) {
+        return AUX_BYTES + 1024 + ring_bytes(stages, S, per) + S * per * BN * 4;
     }
 };
 
-__device__ __forceinline__ float4 dsmem_ld_v4(uint32_t cluster_addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "r"(cluster_addr)
+// 16 bytes from registers into a cluster peer's shared memory; the bytes are counted on the peer's mbarrier
+__device__ __forceinline__ void st_async_v4(uint32_t peer_addr, uint32_t peer_bar, uint32_t a, uint32_t b, uint32_t c,
+                                            uint32_t d) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(peer_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(peer_bar)
                  : "memory");
-    return v;
+}
+__device__ __forceinline__ void cluster_arrive_release() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Sum over the S ranks (fixed order) of the 8 staged fp32 values of (row, 8-column group starting at column c8*8).
+// Sum over the S slots (fixed order) of the 8 received fp32 values of (token t of this rank, columns c8*8 .. +7).
 template <int BN>
-__device__ __forceinline__ void tok_reduce8(const uint32_t* rank_base, uint32_t S, int row, int c8, float* a) {
-    const uint32_t sw = (uint32_t)(row & 7);
-    const uint32_t o0 = (uint32_t)row * (BN * 4) + ((((uint32_t)(2 * c8)) ^ sw) << 4);
-    const uint32_t o1 = (uint32_t)row * (BN * 4) + ((((uint32_t)(2 * c8 + 1)) ^ sw) << 4);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = 0.0f;
-    // four ranks (eight 16-byte loads) in flight per round trip
-#pragma unroll
-    for (uint32_t s0 = 0; s0 < 8; s0 += 4) {
-        if (s0 < S) {
-            float4 x[4], y[4];
-#pragma unroll
-            for (uint32_t s = 0; s < 4; ++s) {
-                if (s0 + s < S) {
-                    x[s] = dsmem_ld_v4(rank_base[s0 + s] + o0);
-                    y[s] = dsmem_ld_v4(rank_base[s0 + s] + o1);
-                }
-            }
-#pragma unroll
-            for (uint32_t s = 0; s < 4; ++s) {
-                if (s0 + s < S) {
-                    a[0] += x[s].x; a[1] += x[s].y; a[2] += x[s].z; a[3] += x[s].w;
-                    a[4] += y[s].x; a[5] += y[s].y; a[6] += y[s].z; a[7] += y[s].w;
-                }
-            }
-        }
+__device__ __forceinline__ void tok_sum8(const float* recv, int S, int per, int t, int c8, float* a) {
+    const float4* row = reinterpret_cast<const float4*>(recv + (size_t)t * BN);
+    const int c0 = 2 * c8, c1 = 2 * c8 + 1;
+    const size_t slot = (size_t)per * BN / 4;
+    float4 x = row[c0], y = row[c1];
+    a[0] = x.x; a[1] = x.y; a[2] = x.z; a[3] = x.w;
+    a[4] = y.x; a[5] = y.y; a[6] = y.z; a[7] = y.w;
+    for (int s = 1; s < S; ++s) {
+        x = row[s * slot + c0];
+        y = row[s * slot + c1];
+        a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
+        a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
     }
 }
 
 template <int BN, int PRO, int EPI>
 __global__ void __launch_bounds__(256, 2)
 gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, TokParams p) {
-    static_assert(EPI != TOK_EPI_GEGLU || BN == 256, "GeGLU tiles are 128 gate rows + the 128 matching up rows");
+    static_assert(EPI != TOK_EPI_GEGLU || BN >= 128, "GeGLU tiles are BN / 2 gate rows + the matching up rows");
     using Cfg = TokCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* aux = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -136,26 +147,36 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint64_t* empty = full + 8;                                  // [8]
     uint64_t* accum_bar = empty + 8;
     uint64_t* a_ready = accum_bar + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(a_ready + 1);
+    uint64_t* recv_bar = a_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* issued = abort_flag + 1;
     volatile int* consumed = abort_flag + 2;
     float* s_rms = reinterpret_cast<float*>(aux + 512);          // [128]
-    float* red = reinterpret_cast<float*>(tiles);                // aliases the operand ring after the last MMA
+    float* recv = reinterpret_cast<float*>(tiles + p.ring_bytes);   // [S][per][BN]
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef FRT_TOK_TRACE
+    int tstamp_thread = 0;
+#endif
+    TOK_STAMP(0);
     const int tile = blockIdx.x;
-    // first weight row of the tile; with GeGLU a tile is 128 gate rows + the 128 matching up rows
-    const int n0 = (EPI == TOK_EPI_GEGLU) ? tile * 128 : tile * BN;
+    // first weight row of the tile; with GeGLU a tile is BN / 2 gate rows + the BN / 2 matching up rows
+    const int n0 = (EPI == TOK_EPI_GEGLU) ? tile * (BN / 2) : tile * BN;
     const int m0 = blockIdx.y * 128;
     const int Mt = (p.M - m0) < 128 ? (p.M - m0) : 128;         // tokens of this m-tile
-    const uint32_t S = tc::cluster_nctarank();
-    const uint32_t rank = tc::cluster_ctarank();
+    const int S = (int)tc::cluster_nctarank();
+    const int rank = (int)tc::cluster_ctarank();
     const int nkb = p.nkb;
-    const int kb0 = (int)rank * nkb;
+    const int kb0 = rank * nkb;
     const int STG = p.stages;
+    const int per = p.per;
+    // tokens this rank finishes: [tb, te) inside the m-tile
+    const int tb = rank * per < Mt ? rank * per : Mt;
+    const int te = tb + per < Mt ? tb + per : Mt;
+    const int ntok = te - tb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 8; ++s) {
@@ -164,10 +185,13 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         tc::mbar_init(accum_bar, 1);
         tc::mbar_init(a_ready, 256);
+        tc::mbar_init(recv_bar, 1);
         *abort_flag = 0;
         *issued = 0;
         *consumed = 0;
         tc::mbar_fence_init();
+        // every rank (this one included) sends this rank's tokens: S slots of ntok rows
+        tc::mbar_arrive_expect_tx(recv_bar, (uint32_t)(S * ntok * BN * 4));
         if (PRO == TOK_PRO_TMA) tc::tma_prefetch_desc(&tmA);
         tc::tma_prefetch_desc(&tmW);
     }
@@ -179,6 +203,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_d = *tmem_slot;
+    // the peers may push into this CTA once they have seen this arrival (they wait for it just before their first push)
+    cluster_arrive_release();
+    TOK_STAMP(1);
 
     pdl_launch_dependents();
 
@@ -187,9 +214,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t tx = (PRO == TOK_PRO_TMA) ? Cfg::STAGE_BYTES : Cfg::W_BYTES;
         auto load_w = [&](int stage, int kb) {
             uint8_t* dst = tiles + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES;
-            if (EPI == TOK_EPI_GEGLU) {      // tmW has a 128-row box here
+            if (EPI == TOK_EPI_GEGLU) {      // tmW has a box of BN / 2 rows here
                 tc::tma_load_2d(dst, &tmW, &full[stage], kb * 128, n0);
-                tc::tma_load_2d(dst + 128 * 128, &tmW, &full[stage], kb * 128, p.half + n0);
+                tc::tma_load_2d(dst + (BN / 2) * 128, &tmW, &full[stage], kb * 128, p.half + n0);
             } else {
                 tc::tma_load_2d(dst, &tmW, &full[stage], kb * 128, n0);
             }
@@ -229,20 +256,26 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int r_first = threadIdx.x / CH;
         const int kcol = (kb0 * 128) + c16 * 16;      // first feature of this thread's chunk
         // style row and scale do not depend on the producer grid
-        const uint4 sc0 = ld_global_v4(p.style + kcol), sc1 = ld_global_v4(p.style + kcol + 8);
-        const uint4 sh0 = ld_global_v4(p.style + p.K + kcol), sh1 = ld_global_v4(p.style + p.K + kcol + 8);
+        float one_sc[16], shf[16];                    // 1 + scale and shift of this thread's 16 features
+        {
+            const uint4 sc0 = ld_global_v4(p.style + kcol), sc1 = ld_global_v4(p.style + kcol + 8);
+            const uint4 sh0 = ld_global_v4(p.style + p.K + kcol), sh1 = ld_global_v4(p.style + p.K + kcol + 8);
+            const uint32_t scw[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
+            const uint32_t shw[8] = {sh0.x, sh0.y, sh0.z, sh0.w, sh1.x, sh1.y, sh1.z, sh1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float s0, s1;
+                unpack_bf16x2(scw[i], s0, s1);
+                one_sc[2 * i] = __fadd_rn(1.0f, s0);
+                one_sc[2 * i + 1] = __fadd_rn(1.0f, s1);
+                unpack_bf16x2(shw[i], shf[2 * i], shf[2 * i + 1]);
+            }
+        }
         const float inv_scale = __fdiv_rn(1.0f, p.sa ? *p.sa : 1.0f);
         pdl_wait();
-        // per-token 1 / rms from the per-tile partial sums of squares (fixed order)
-        if ((int)threadIdx.x < Mt) {
-            float tot = 0.0f;
-            for (int t = 0; t < p.n_stat; ++t) tot = __fadd_rn(tot, __ldcg(p.stats_in + t * TOK_STAT_STRIDE + m0 + threadIdx.x));
-            const float var = __fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps);
-            s_rms[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(var));
-        }
-        // residual chunks of up to four tokens per pass in flight
         const int passes = (Mt + rstep - 1) / rstep;
         for (int pb = 0; pb < passes; pb += 4) {
+            // residual chunks of up to four tokens in flight, and (first batch) the row statistics behind them
             uint4 xa[4], xb[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -253,27 +286,43 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     xb[j] = __ldcg(reinterpret_cast<const uint4*>(src + 8));
                 }
             }
-            if (pb == 0) __syncthreads();             // s_rms visible (every thread passes here exactly once)
+            if (pb == 0) {
+                // per-token 1 / rms from the per-tile partial sums of squares: all partials of a token in flight,
+                // summed in order
+                if ((int)threadIdx.x < Mt) {
+                    float tot = 0.0f;
+                    for (int t0 = 0; t0 < p.n_stat; t0 += 16) {
+                        float v[16];
+#pragma unroll
+                        for (int t = 0; t < 16; ++t)
+                            v[t] = (t0 + t < p.n_stat)
+                                       ? __ldcg(p.stats_in + (t0 + t) * TOK_STAT_STRIDE + m0 + threadIdx.x) : 0.0f;
+#pragma unroll
+                        for (int t = 0; t < 16; ++t)
+                            if (t0 + t < p.n_stat) tot = __fadd_rn(tot, v[t]);
+                    }
+                    const float var = __fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps);
+                    s_rms[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(var));
+                }
+                __syncthreads();                      // every thread passes here exactly once (passes >= 1)
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int r = r_first + (pb + j) * rstep;
                 if (pb + j < passes && r < Mt) {
                     const float rms = s_rms[r];
                     const uint32_t xw[8] = {xa[j].x, xa[j].y, xa[j].z, xa[j].w, xb[j].x, xb[j].y, xb[j].z, xb[j].w};
-                    const uint32_t scw[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
-                    const uint32_t shw[8] = {sh0.x, sh0.y, sh0.z, sh0.w, sh1.x, sh1.y, sh1.z, sh1.w};
                     uint32_t q[4];
 #pragma unroll
                     for (int i = 0; i < 8; i += 2) {
                         float v[4];
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            float r0, r1, s0, s1, h0, h1;
+                            float r0, r1;
                             unpack_bf16x2(xw[i + h], r0, r1);
-                            unpack_bf16x2(scw[i + h], s0, s1);
-                            unpack_bf16x2(shw[i + h], h0, h1);
-                            const float n0v = __fmaf_rn(__fmul_rn(r0, rms), __fadd_rn(1.0f, s0), h0);
-                            const float n1v = __fmaf_rn(__fmul_rn(r1, rms), __fadd_rn(1.0f, s1), h1);
+                            const int e = 2 * (i + h);
+                            const float n0v = __fmaf_rn(__fmul_rn(r0, rms), one_sc[e], shf[e]);
+                            const float n1v = __fmaf_rn(__fmul_rn(r1, rms), one_sc[e + 1], shf[e + 1]);
                             v[2 * h] = clamp448(__fmul_rn(n0v, inv_scale));
                             v[2 * h + 1] = clamp448(__fmul_rn(n1v, inv_scale));
                         }
@@ -285,10 +334,11 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
-        if (passes == 0) __syncthreads();
         tc::fence_proxy_async_smem();
         tc::mbar_arrive(a_ready);
+        TOK_STAMP(12);
     }
+
     if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
         constexpr uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN);
@@ -312,6 +362,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 break;
             }
             tc::tc_fence_after_sync();
+#ifdef FRT_TOK_TRACE
+            if (i == 0) g_tok_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 160][10] = tc::global_timer_ns();
+#endif
             const uint64_t so = (uint64_t)((s * Cfg::STAGE_BYTES) >> 4);
 #pragma unroll
             for (int k = 0; k < 4; ++k)   // 4 x (K = 32) per 128-byte k-block; +32 bytes = +2 in the address field
@@ -320,11 +373,44 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             *consumed = i + 1;
         }
         if (!failed) tc::mma_commit(accum_bar);
+#ifdef FRT_TOK_TRACE
+        g_tok_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 160][11] = tc::global_timer_ns();
+#endif
     }
     __syncwarp();
 
-    // ---------------- accumulator -> fp32 staging rows (16-byte chunks xor-swizzled by the row)
+    // ---------------- work items of the finish: (token of this rank, group of 8 output features); what an item needs
+    // from global memory besides the accumulator is fetched now, behind the MMAs
+    TOK_STAMP(2);
     pdl_wait();
+    TOK_STAMP(3);
+    constexpr int G = (EPI == TOK_EPI_GEGLU) ? BN / 16 : BN / 8;      // 8-feature groups per token that carry output
+    const int items = ntok * G;
+    const int items_pad = (items + 31) & ~31;                         // whole warps iterate together (shuffles below)
+    float alpha = p.alpha_host;
+    if (p.sa) alpha *= *p.sa;
+    if (p.sb) alpha *= *p.sb;
+    const float inv_os = (EPI == TOK_EPI_GEGLU) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+    const int pos = (EPI == TOK_EPI_ROPE && p.devpos) ? *p.devpos : 0;
+    uint4 pre0 = make_uint4(0, 0, 0, 0), pre1 = make_uint4(0, 0, 0, 0);   // first item's operands
+    {
+        const int it = threadIdx.x;
+        if (it < items) {
+            const int m = m0 + tb + it / G, n = n0 + (it % G) * 8;
+            if (EPI == TOK_EPI_RESID && n < p.N) {
+                pre0 = ld_global_v4(p.resid + (size_t)m * p.N + n);
+                pre1 = ld_global_v4(p.gate + n);
+            } else if (EPI == TOK_EPI_ROPE && n < p.q_dim + p.k_dim) {
+                const int nr = n < p.q_dim ? n : n - p.q_dim;
+                pre0 = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
+            } else if (EPI == TOK_EPI_BF16 && p.bias && n + 8 <= p.N &&
+                       (reinterpret_cast<uintptr_t>(p.bias + n) & 15) == 0) {
+                pre0 = ld_global_v4(p.bias + n);
+            }
+        }
+    }
+
+    // ---------------- accumulator rows -> the owning rank's receive slot [this rank][token][BN]
     const bool acc_seen = tc::mbar_wait_until(accum_bar, 0, deadline, abort_flag);
     const bool have_acc = __all_sync(0xffffffffu, acc_seen);   // tcgen05.ld below is warp-collective
     if (!have_acc && !*abort_flag) {
@@ -333,55 +419,52 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     __syncwarp();
     tc::tc_fence_after_sync();
+    TOK_STAMP(4);
+    cluster_wait_acquire();          // every peer has initialised its receive barrier (arrived during its set-up)
     {
         const int quad = warp & 3, chalf = warp >> 2;
-        const int row = quad * 32 + lane;
-        if (have_acc && quad * 32 < p.stage_rows) {
+        const int row = quad * 32 + lane;                      // token inside the m-tile
+        if (have_acc && quad * 32 < Mt) {
             const uint32_t trow = tmem_d + ((uint32_t)(quad * 32) << 16);
-            const uint32_t sw = (uint32_t)(row & 7);
+            const int owner = row / per < S ? row / per : 0;
+            const uint32_t dst_local = tc::smem_u32(recv) + (uint32_t)(((rank * per + (row % per)) * BN) * 4);
+            const uint32_t dst = tc::dsmem_map(dst_local, (uint32_t)owner);
+            const uint32_t bar = tc::dsmem_map(tc::smem_u32(recv_bar), (uint32_t)owner);
 #pragma unroll 1
             for (int c = chalf * (BN / 2); c < (chalf + 1) * (BN / 2); c += 32) {
                 uint32_t v[32];
                 tc::tmem_ld32(trow + c, v);
                 tc::tmem_ld_wait();
-                float4* rrow = reinterpret_cast<float4*>(red + (size_t)row * BN);
+                if (row < Mt) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    rrow[((uint32_t)((c >> 2) + j)) ^ sw] =
-                        make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    for (int j = 0; j < 8; ++j)
+                        st_async_v4(dst + (uint32_t)(c + 4 * j) * 4u, bar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
             }
         }
     }
-    tc::tc_fence_before_sync();
-    if (S > 1) tc::cluster_sync_all(); else __syncthreads();
+    TOK_STAMP(5);
+    // ---------------- all S slots of this rank's tokens have landed
+    const bool got = tc::mbar_wait_until(recv_bar, 0, deadline, abort_flag);
+    if (!got && !*abort_flag) {
+        *abort_flag = 1;
+        atomicCAS(&g_gemm_status, 0, ERR_EPILOGUE | (blockIdx.x << 8));
+    }
+    __syncwarp();
+    TOK_STAMP(6);
 
-    // ---------------- finish: rank r sums the S partials of its token range and applies the epilogue
+    // ---------------- finish: sum the S slots in order and apply the epilogue
     {
-        const uint32_t red_addr = tc::smem_u32(red);
-        uint32_t rank_base[8];
-#pragma unroll
-        for (uint32_t r = 0; r < 8; ++r) rank_base[r] = tc::dsmem_map(red_addr, r < S ? r : 0);
-        const int per = (Mt + (int)S - 1) / (int)S;
-        const int tb = (int)rank * per;
-        const int te = tb + per < Mt ? tb + per : Mt;
-        constexpr int G = (EPI == TOK_EPI_GEGLU) ? 16 : BN / 8;       // 8-feature groups per token that carry output
-        const int items = (te > tb ? te - tb : 0) * G;
-        const int items_pad = (items + 31) & ~31;                     // whole warps iterate together (shuffles below)
         const bool live = !*abort_flag;
-        float alpha = p.alpha_host;
-        if (p.sa) alpha *= *p.sa;
-        if (p.sb) alpha *= *p.sb;
-        const float inv_os = (EPI == TOK_EPI_GEGLU) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
-        const int pos = (EPI == TOK_EPI_ROPE && p.devpos) ? *p.devpos : 0;
         for (int it = threadIdx.x; it < items_pad; it += 256) {
             const bool act = live && it < items;
-            const int row = tb + it / G;          // token inside the m-tile
+            const int t = it / G;                 // token of this rank
             const int g = it % G;
-            const int m = m0 + row;
+            const int m = m0 + tb + t;
+            const bool first = it < 256;
             float a[8];
             if (act) {
-                tok_reduce8<BN>(rank_base, S, row, g, a);
+                tok_sum8<BN>(recv, S, per, t, g, a);
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) a[j] = 0.0f;
@@ -390,13 +473,21 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int n = n0 + g * 8;
                 if (act && n < p.N) {
                     float f[8];
+                    const bool vec = n + 8 <= p.N && (reinterpret_cast<uintptr_t>(p.out + (size_t)m * p.N + n) & 15) == 0;
+                    const bool bvec = p.bias && n + 8 <= p.N && (reinterpret_cast<uintptr_t>(p.bias + n) & 15) == 0;
+                    uint4 bv = pre0;
+                    if (bvec && !first) bv = ld_global_v4(p.bias + n);
+                    const uint32_t* bw = &bv.x;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         f[j] = a[j] * alpha;
-                        if (p.bias && n + j < p.N) f[j] += __bfloat162float(p.bias[n + j]);
+                        if (p.bias) {
+                            if (bvec) f[j] += bf16_bits_to_f32((bw[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+                            else if (n + j < p.N) f[j] += __bfloat162float(p.bias[n + j]);
+                        }
                     }
                     __nv_bfloat16* dst = p.out + (size_t)m * p.N + n;
-                    if (n + 8 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    if (vec) {
                         uint4 o;
                         o.x = pack_bf16x2(f[0], f[1]);
                         o.y = pack_bf16x2(f[2], f[3]);
@@ -420,8 +511,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const int nr = is_q ? n : (is_k ? n - p.q_dim : n - p.q_dim - p.k_dim);
                     uint4 o;
                     if (is_q || is_k) {
-                        const uint4 t = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
-                        const uint32_t* tw = &t.x;
+                        uint4 tq = pre0;
+                        if (!first) tq = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
+                        const uint32_t* tw = &tq.x;
                         uint32_t* ow = &o.x;
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
@@ -442,11 +534,11 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     st_global_v4(dst, o);
                 }
             } else if (EPI == TOK_EPI_GEGLU) {
-                // a = gate columns g*8.. of the tile, b = the matching up columns 128 + g*8..
+                // a = gate columns g*8.. of the tile, b = the matching up columns BN / 2 + g*8..
                 const int h = n0 + g * 8;
                 if (act && h < p.half) {
                     float b[8];
-                    tok_reduce8<BN>(rank_base, S, row, 16 + g, b);
+                    tok_sum8<BN>(recv, S, per, t, G + g, b);
                     float q[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -465,8 +557,11 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 float ssq = 0.0f;
                 if (act && n < p.N) {
                     __nv_bfloat16* rp = p.resid + (size_t)m * p.N + n;
-                    const uint4 rv = ld_global_v4(rp);
-                    const uint4 gv = ld_global_v4(p.gate + n);
+                    uint4 rv = pre0, gv = pre1;
+                    if (!first) {
+                        rv = ld_global_v4(rp);
+                        gv = ld_global_v4(p.gate + n);
+                    }
                     const uint32_t* rw = &rv.x;
                     const uint32_t* gw = &gv.x;
                     uint4 ob;
@@ -493,9 +588,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
         }
     }
-    if (S > 1) tc::cluster_sync_all();     // no rank leaves while its staging rows may still be read
+    TOK_STAMP(7);
 
-    // ---------------- teardown
+    // ---------------- teardown (nothing of this CTA is read by a peer: no cluster barrier before leaving)
     tc::tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
@@ -510,14 +605,20 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     __syncthreads();
     if (warp == 2) tc::tmem_dealloc(tmem_d, Cfg::TMEM_COLS);
+    TOK_STAMP(9);
 }
 
 // ------------------------------------------------------------------ host side
 struct TokPlan { int BN, S, nkb, stages; };
 
-// Tile width and split-K factor for (M, N, K): as many CTAs as fit one wave of `sms` SMs, at most 4 resident
-// k-blocks per CTA where the shape allows it, the smaller cluster on ties.  want_bn / want_s (> 0) pin a choice.
-static bool tok_plan(int N, int K, int m_tiles, int epi, int pro, int sms, int want_bn, int want_s, TokPlan* out) {
+// Tile width and split-K factor for (M, N, K) from a serial cost model in microseconds, fitted to device-timer
+// traces of the four decoder projections at 50 tokens: 0.33 per resident k-block (four MMA issues), 0.06 per KB a
+// CTA pushes to its cluster peers, 0.05 per rank for the receive wait, 0.6 per k-block of in-kernel norm work, a
+// charge for SMs that have to carry two CTAs, and a second wave only when the CTAs cannot all be resident (two per
+// SM fit while a CTA stays under ~110 KB of shared memory).  want_bn / want_s (> 0) pin a choice; callers that
+// have measured their shapes do so.
+static bool tok_plan(int N, int K, int m_tiles, int mt, int epi, int pro, int sms, int want_bn, int want_s,
+                     TokPlan* out) {
     if (K % 128) return false;
     const int kbt = K / 128;
     const int bns[3] = {256, 128, 64};
@@ -526,22 +627,30 @@ static bool tok_plan(int N, int K, int m_tiles, int epi, int pro, int sms, int w
     for (int bi = 0; bi < 3; ++bi) {
         const int BN = bns[bi];
         if (want_bn > 0 && BN != want_bn) continue;
-        if (epi == TOK_EPI_GEGLU && BN != 256) continue;
+        if (epi == TOK_EPI_GEGLU && (BN == 64 || ((N / 2) % (BN / 2)))) continue;
         if (epi == TOK_EPI_RESID && BN == 256) continue;    // the 8-lane / 16-lane row-sum groups
-        const int tiles = (epi == TOK_EPI_GEGLU ? (N / 2 + 127) / 128 : (N + BN - 1) / BN) * m_tiles;
+        const int tiles = (epi == TOK_EPI_GEGLU ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN) * m_tiles;
         const int max_st = BN == 256 ? 4 : BN == 128 ? 6 : 8;
+        const int stage_bytes = 16384 + BN * 128;
         for (int S = 1; S <= 8; S *= 2) {
             if (want_s > 0 && S != want_s) continue;
             if (kbt % S) continue;
             const int nkb = kbt / S;
             if (pro == TOK_PRO_NORM && (nkb > max_st || nkb > 4 || (nkb != 1 && nkb != 2 && nkb != 4))) continue;
             const int ctas = tiles * S;
-            // serial cost model in us: instruction issue of the K-slice, the cluster exchange, waves beyond the first
-            double cost = nkb * 0.33 + (S > 1 ? 0.25 + 0.06 * S : 0.0) + 0.004 * BN;
-            if (ctas > sms) cost += 3.0 * ((ctas + sms - 1) / sms - 1);
+            const int stages = nkb < max_st ? nkb : max_st;
+            const int per = (mt + S - 1) / S;
+            const int smem = 3072 + stages * stage_bytes + S * per * BN * 4;
+            if (pro == TOK_PRO_NORM && smem > 227 * 1024) continue;
+            const double pushed_kb = (double)(S - 1) / S * mt * BN * 4 / 1024.0;
+            double cost = nkb * 0.33 + pushed_kb * 0.06 + (S > 1 ? 0.05 * S : 0.0);
+            if (pro == TOK_PRO_NORM) cost += 0.6 * nkb;
+            const int resident = smem <= 110 * 1024 ? 2 * sms : sms;
+            if (ctas > resident) cost += 3.0 * ((ctas + resident - 1) / resident - 1);
+            else if (ctas > sms) cost += 1.0 * (ctas - sms) / sms;   // SMs that carry two CTAs run both slower
             if (cost < best) {
                 best = cost;
-                out->BN = BN; out->S = S; out->nkb = nkb; out->stages = nkb < max_st ? nkb : max_st;
+                out->BN = BN; out->S = S; out->nkb = nkb; out->stages = stages;
                 found = true;
             }
         }
@@ -558,9 +667,18 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     const int mt = p.M < 128 ? p.M : 128;
     p.nkb = pl.nkb;
     p.stages = pl.stages;
-    p.stage_rows = (mt + 31) & ~31;
+    p.per = (mt + pl.S - 1) / pl.S;
+    // the operand ring shrinks until it fits beside the receive slots
+    while (p.stages > 2 && Cfg::smem_bytes(p.stages, pl.S, p.per) > 227 * 1024) --p.stages;
+    if (PRO == TOK_PRO_NORM && p.stages < pl.nkb) return FRT_ERR_UNSUPPORTED;
     p.K = K;
-    const int smem = Cfg::smem_bytes(pl.stages, p.stage_rows);
+#ifdef FRT_TOK_TRACE
+    p.trace_slot = g_tok_trace_slot;
+    g_tok_trace_slot = (g_tok_trace_slot + 1) % 8;
+#endif
+    const int smem = Cfg::smem_bytes(p.stages, pl.S, p.per);
+    p.ring_bytes = Cfg::ring_bytes(p.stages, pl.S, p.per);
+    if (smem > 227 * 1024) return FRT_ERR_UNSUPPORTED;
     int dev = 0;
     cudaGetDevice(&dev);
     static int attr_smem[64] = {0};
@@ -578,9 +696,9 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     } else {
         memset(&tmA, 0, sizeof(tmA));
     }
-    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, EPI == TOK_EPI_GEGLU ? 128 : BN);
+    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, EPI == TOK_EPI_GEGLU ? BN / 2 : BN);
     if (rc) return rc;
-    const int tiles = EPI == TOK_EPI_GEGLU ? (p.half + 127) / 128 : (p.N + BN - 1) / BN;
+    const int tiles = EPI == TOK_EPI_GEGLU ? (p.half + BN / 2 - 1) / (BN / 2) : (p.N + BN - 1) / BN;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, m_tiles, pl.S);
     cfg.blockDim = dim3(256);
@@ -617,13 +735,11 @@ template <int PRO, int EPI>
 static int dispatch_gemm_tok(const void* A, const void* W, TokParams p, int K, int want_bn, int want_s, bool pdl,
                              cudaStream_t s) {
     TokPlan pl;
-    if (!tok_plan(EPI == TOK_EPI_GEGLU ? 2 * p.half : p.N, K, (p.M + 127) / 128, EPI, PRO, tok_sm_count(), want_bn,
-                  want_s, &pl))
+    if (!tok_plan(EPI == TOK_EPI_GEGLU ? 2 * p.half : p.N, K, (p.M + 127) / 128, p.M < 128 ? p.M : 128, EPI, PRO,
+                  tok_sm_count(), want_bn, want_s, &pl))
         return FRT_ERR_UNSUPPORTED;
     if (pl.BN == 256) return launch_gemm_tok<256, PRO, EPI>(A, W, p, K, pl, pdl, s);
-    if constexpr (EPI != TOK_EPI_GEGLU) {
-        if (pl.BN == 128) return launch_gemm_tok<128, PRO, EPI>(A, W, p, K, pl, pdl, s);
-        return launch_gemm_tok<64, PRO, EPI>(A, W, p, K, pl, pdl, s);
-    }
+    if (pl.BN == 128) return launch_gemm_tok<128, PRO, EPI>(A, W, p, K, pl, pdl, s);
+    if constexpr (EPI != TOK_EPI_GEGLU) return launch_gemm_tok<64, PRO, EPI>(A, W, p, K, pl, pdl, s);
     return FRT_ERR_UNSUPPORTED;
 }

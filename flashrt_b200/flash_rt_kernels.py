@@ -271,10 +271,10 @@ class GemmRunner:
              _f(pdl) | _tile_hint(tile_n), stream)
 
     def norm_fp8_nt_dev_geglu_fp8(self, x, stats, n_stat, style, B, out, M, half_dim, K, d_scale_a, d_scale_b,
-                                  d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0):
+                                  d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0, tile_n=0):
         """The same producer in front of the gate|up projection, ``gate_geglu_merged_fp8`` behind it."""
         call("frt_b200_norm_gemm_fp8_nt_geglu_fp8", x, stats, n_stat, style, eps, B, out, M, half_dim, K, d_scale_a,
-             d_scale_b, d_scale_out, splits, _f(pdl), stream)
+             d_scale_b, d_scale_out, splits, _f(pdl) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_gate_res_norm_fp8(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, style, out, d_scale_out,
                                      stream=0, *, eps=1e-6, pdl=False, splits=0):
@@ -299,10 +299,10 @@ class GemmRunner:
              _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_geglu_fp8(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, stream=0, *,
-                             pdl=False, splits=0, swapped=False):
+                             pdl=False, splits=0, swapped=False, tile_n=0):
         """``fp8_nt_dev`` into a merged (M, 2*half) buffer followed by ``gate_geglu_merged_fp8``, in one launch."""
         call("frt_b200_gemm_fp8_nt_geglu_fp8", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, splits,
-             _f(pdl) | (16 if swapped else 0), stream)
+             _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, **kw):
         raise NotBuilt(

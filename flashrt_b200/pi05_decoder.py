@@ -464,6 +464,14 @@ class Pi05DecoderPipeline(StepIO):
         qd, kd = DEC_NH * DEC_HD, DEC_NKV * DEC_HD
         gate_off = 2 * DEC_D * 2
         n_stat = 0
+        # tile width / split-K of the four projections at <= 64 tokens, from per-launch timings of the captured chain
+        # (QKV 64 x 4, attention-out 64 x 4, gate|up 64 + 64 x 2, FFN-down 64 x 8); larger row counts use the
+        # library's own choice
+        tuned = S <= 64
+        t_qkv = dict(splits=4, tile_n=64) if tuned else {}
+        t_o = dict(splits=4, tile_n=64) if tuned else {}
+        t_gu = dict(splits=2, tile_n=128) if tuned else {}
+        t_d = dict(splits=8, tile_n=64) if tuned else {}
         for i in range(L):
             kp, vp, dp = self._kv_dst(i, 0)
             if i == 0:
@@ -471,22 +479,25 @@ class Pi05DecoderPipeline(StepIO):
                 g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
                                         self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                         fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, stream,
-                                        devpos=dp, pdl=pdl)
+                                        devpos=dp, pdl=pdl, **t_qkv)
             else:
                 g.norm_fp8_nt_dev_rope_split(x, stats, n_stat, self._style("attn", step, i), fe.w_qkv[i].data_ptr(),
                                              S, DEC_D, self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                              fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD,
-                                             stream, devpos=dp, pdl=pdl)
+                                             stream, devpos=dp, pdl=pdl, **t_qkv)
             self._attention(i, stream, pdl, self._scale_ptr(step, i, "o"))
             n_stat = g.fp8_nt_dev_gate_residual(self.attn8.data_ptr(), fe.w_o[i].data_ptr(), S, DEC_D, qd,
                                                 self._scale_ptr(step, i, "o"), fe.ws_o_t[i].data_ptr(), x,
-                                                self._style("attn", step, i) + gate_off, stats, stream, pdl=pdl)
+                                                self._style("attn", step, i) + gate_off, stats, stream, pdl=pdl,
+                                                **t_o)
             g.norm_fp8_nt_dev_geglu_fp8(x, stats, n_stat, self._style("ffn", step, i), fe.w_gu[i].data_ptr(),
                                         self.hid8.data_ptr(), S, DEC_H, DEC_D, self._scale_ptr(step, i, "gu"),
-                                        fe.ws_gu_t[i].data_ptr(), self._scale_ptr(step, i, "d"), stream, pdl=pdl)
+                                        fe.ws_gu_t[i].data_ptr(), self._scale_ptr(step, i, "d"), stream, pdl=pdl,
+                                        **t_gu)
             n_stat = g.fp8_nt_dev_gate_residual(self.hid8.data_ptr(), fe.w_d[i].data_ptr(), S, DEC_D, DEC_H,
                                                 self._scale_ptr(step, i, "d"), fe.ws_d_t[i].data_ptr(), x,
-                                                self._style("ffn", step, i) + gate_off, stats, stream, pdl=pdl)
+                                                self._style("ffn", step, i) + gate_off, stats, stream, pdl=pdl,
+                                                **t_d)
 
     def launches_per_layer(self) -> float:
         """Average over the layers (the last layer keeps its separate residual kernel when the norms are fused)."""

@@ -259,7 +259,7 @@ int frt_b200_norm_gemm_fp8_nt_rope_split(const void* x, const float* stats_in, i
                                          int q_dim, int k_dim, int v_dim, int head_dim, int splits, int flags,
                                          void* stream);
 /* The same producer (csrc/kernels/fusion.cu:48-81) in front of the gate|up projection, gate_geglu_merged_fp8
- * (csrc/kernels/activation.cu:249-279) behind it; half % 128 == 0. */
+ * (csrc/kernels/activation.cu:249-279) behind it; half % 64 == 0. */
 int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, int n_stat, const void* style, float eps,
                                         const void* W, void* out8, int M, int half, int K, const float* d_scale_a,
                                         const float* d_scale_b, const float* d_out_scale, int splits, int flags,

@@ -230,6 +230,69 @@ class Nvfp4Linears:
         return (h_q @ self.w[(name, i)]).to(torch.bfloat16).float()
 
 
+class Fp8Linears:
+    """Per-tensor FP8 E4M3 stand-in for the four projections of every layer, restating the arithmetic of the
+    reference's FP8 decoder (weights: flash_rt/frontends/torch/pi05_rtx.py:344-350, scale = max(amax / 448, 1e-12);
+    activations: static per-site per-step scales, x * (1 / s) clamped to +-448 and rounded to E4M3,
+    csrc/kernels/quantize.cu:61-75; product on the dequantised values in fp32, result rounded to bf16,
+    csrc/gemm/gemm_runner.cu:263-272).  ``act_scale``: the (steps, layers, 4) table of the device model, sites in
+    the order qkv, o, gate|up, down."""
+    SITES = ("qkv", "o", "gu", "d")
+
+    def __init__(self, W: dict, layers: int, act_scale):
+        self.scale = torch.as_tensor(act_scale, dtype=torch.float32).cpu()
+        self.w = {}
+        gate_up = {}
+        for name in ("decoder_attn_qkv_w", "decoder_attn_o_w", "decoder_ffn_gate_w", "decoder_ffn_up_w",
+                     "decoder_ffn_down_w"):
+            for i in range(layers):
+                gate_up[(name, i)] = W[name][i].to(torch.bfloat16).float()           # (K, N)
+        for (name, i), w in gate_up.items():
+            # gate and up are one fused tensor on the device: one scale for both
+            if name in ("decoder_ffn_gate_w", "decoder_ffn_up_w"):
+                amax = max(float(gate_up[("decoder_ffn_gate_w", i)].abs().max()),
+                           float(gate_up[("decoder_ffn_up_w", i)].abs().max()))
+            else:
+                amax = float(w.abs().max())
+            s = max(np.float32(amax) / np.float32(448.0), np.float32(1e-12))
+            q = (w / torch.tensor(s)).clamp(-448, 448).to(torch.float8_e4m3fn).float()
+            self.w[(name, i)] = q * torch.tensor(s)
+
+    def act(self, h: torch.Tensor, step: int, i: int, site: str) -> torch.Tensor:
+        s = self.scale[step, i, self.SITES.index(site)]
+        inv = torch.tensor(1.0, dtype=torch.float32) / s
+        return (h.float() * inv).clamp(-448, 448).to(torch.float8_e4m3fn).float() * s
+
+    def __call__(self, h_q: torch.Tensor, name: str, i: int) -> torch.Tensor:
+        return (h_q @ self.w[(name, i)]).to(torch.bfloat16).float()
+
+
+def decoder_block_fp8(x, lin: "Fp8Linears", step: int, i: int, style_attn_row, style_ffn_row, prefix_k, prefix_v,
+                      rope_tab):
+    """The layer of ``decoder_block`` with FP8 projections and the device path's 16-bit rounding points (bf16
+    residual stream, bf16 GEMM outputs, bf16 attention output quantised to FP8, GeGLU product quantised straight from
+    fp32)."""
+    S = x.shape[0]
+    bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    h, gate_a = ada_rms(x, style_attn_row)
+    qkv = lin(lin.act(h, step, i, "qkv"), "decoder_attn_qkv_w", i)
+    q = qkv[:, :DEC_NH * DEC_HD].reshape(S, DEC_NH, DEC_HD)
+    k = qkv[:, DEC_NH * DEC_HD:(DEC_NH + DEC_NKV) * DEC_HD].reshape(S, DEC_NKV, DEC_HD)
+    v = qkv[:, (DEC_NH + DEC_NKV) * DEC_HD:].reshape(S, DEC_NKV, DEC_HD)
+    q = bf(rope_adjacent_pairs(q, rope_tab))
+    k = bf(rope_adjacent_pairs(k, rope_tab))
+    keys = torch.cat([prefix_k.reshape(-1, DEC_NKV, DEC_HD).float(), k], dim=0)
+    vals = torch.cat([prefix_v.reshape(-1, DEC_NKV, DEC_HD).float(), v], dim=0)
+    a = bf(attention(q, keys, vals, DEC_HD ** -0.5).reshape(S, DEC_NH * DEC_HD))
+    o = lin(lin.act(a, step, i, "o"), "decoder_attn_o_w", i)
+    x1 = bf(x + o * gate_a)
+    h2, gate_f = ada_rms(x1, style_ffn_row)
+    h2q = lin.act(h2, step, i, "gu")
+    hidden = gelu_tanh(lin(h2q, "decoder_ffn_gate_w", i)) * lin(h2q, "decoder_ffn_up_w", i)
+    f = lin(lin.act(hidden, step, i, "d"), "decoder_ffn_down_w", i)
+    return bf(x1 + f * gate_f)
+
+
 def decoder_block_nvfp4(x, lin: "Nvfp4Linears", i: int, style_attn_row, style_ffn_row, prefix_k, prefix_v,
                         rope_tab):
     """The layer of ``decoder_block`` with NVFP4 projections and the device path's 16-bit rounding points
@@ -282,12 +345,13 @@ def decoder_block(x, W: dict, i: int, style_attn_row, style_ffn_row, prefix_k, p
 
 def denoise_loop(noise, ckpt: dict, prefix_k, prefix_v, num_steps: int = 10, layers: int = DEC_L,
                  prefix_len: int | None = None, styles_bf16: bool = True, return_trajectory: bool = False,
-                 nvfp4: "Nvfp4Linears | None" = None):
+                 nvfp4: "Nvfp4Linears | None" = None, fp8: "Fp8Linears | None" = None):
     """10-step Euler flow matching in fp32: x <- x + dt * v(x, t), dt = -1/N, t from 1 down.
 
     ``styles_bf16``: the conditioning tables are data the device path reads from a bf16 precompute
     (pi05_rtx.py:369-448), so by default they are rounded the same way here and the comparison isolates the
-    loop itself.  ``nvfp4``: run the four projections of every layer through :class:`Nvfp4Linears`.
+    loop itself.  ``nvfp4`` / ``fp8``: run the four projections of every layer through :class:`Nvfp4Linears` /
+    :class:`Fp8Linears` (the like-for-like restatement of the quantised device path).
     Returns the final actions (S, 32) and, optionally, the list of states after each step.
     """
     W = ckpt
@@ -305,6 +369,8 @@ def denoise_loop(noise, ckpt: dict, prefix_k, prefix_v, num_steps: int = 10, lay
         for i in range(layers):
             if nvfp4 is not None:
                 x = decoder_block_nvfp4(x, nvfp4, i, sa[s, i], sf[s, i], prefix_k[i, :P], prefix_v[i, :P], tab)
+            elif fp8 is not None:
+                x = decoder_block_fp8(x, fp8, s, i, sa[s, i], sf[s, i], prefix_k[i, :P], prefix_v[i, :P], tab)
             else:
                 x = decoder_block(x, W, i, sa[s, i], sf[s, i], prefix_k[i, :P], prefix_v[i, :P], tab)
         h, _ = ada_rms(x, fin[s])

@@ -14,7 +14,7 @@ def test_calibration_cache_roundtrip_and_validation(tmp_path):
     scales = [0.5 + i * 1e-3 for i in range(10 * 18 * 4)]
     meta = {"layers": 18, "samples": 8}
     f = cc.save_calibration(str(ck), 768, scales, metadata=meta, cache_dir=tmp_path / "cache")
-    assert f.name == f"{cc.checkpoint_hash(str(ck))}_Se768.json"
+    assert f.name == f"{cc.checkpoint_hash(str(ck))}_Se768.b200dec.json"
     rec = cc.load_calibration(str(ck), 768, expected_count=720, cache_dir=tmp_path / "cache", metadata=meta)
     assert rec is not None and rec["ae_scales"] == scales and rec["version"] == 1 and rec["num_ae_scales"] == 720
     # every mismatch is a miss, never an exception
@@ -36,6 +36,16 @@ def test_calibration_cache_roundtrip_and_validation(tmp_path):
     assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache") is None
     f.write_text("{not json")
     assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache") is None
+    # a file in the reference's own format under the reference's own name is neither read nor overwritten
+    # (flash_rt/core/quant/calibrator.py:28-145: {hash}_Se{Se}.json with enc_* fields and layers * 4 decoder scales)
+    theirs = tmp_path / "cache" / f"{cc.checkpoint_hash(str(ck))}_Se768.json"
+    theirs.write_text(json.dumps({"version": 1, "ckpt_hash": cc.checkpoint_hash(str(ck)), "Se": 768,
+                                  "enc_scales": [1.0], "ae_scales": [1.0] * 72, "num_ae_scales": 72}))
+    before = theirs.read_text()
+    assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache") is None
+    cc.save_calibration(str(ck), 768, scales, cache_dir=tmp_path / "cache")
+    assert theirs.read_text() == before
+    assert cc.load_calibration(str(ck), 768, cache_dir=tmp_path / "cache")["format"] == cc.CACHE_FORMAT
     # directory form of the checkpoint path
     d = tmp_path / "ckpt_dir"
     d.mkdir()
