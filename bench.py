@@ -726,7 +726,9 @@ def run_ops(args):
             "config": {"workload": "configs[1] operator sweep", "peaks": peaks,
                        "l2": ("norm and M <= 256 GEMM cases cycle through distinct row / weight buffers totalling more than "
                               "L2; M >= 2048 GEMM cases alternate two weight buffers (tensor-bound)"),
-                       "large_m_fp8_kernel": "cta pair (256 x 256 tiles)" if args.cta_pair else "persistent, one CTA per tile",
+                       "large_m_fp8_kernel": ("cta pair (256 x 256 tiles) forced" if args.cta_pair else
+                                              "library's choice: cta pair for >= 2 waves of 256 x 256 tiles at "
+                                              "K >= 2048, else persistent one-CTA tiles"),
                        "library_baseline": "torch._scaled_mm (cuBLASLt FP8) and torch SDPA on the same tensors",
                        "tensor_core_status": fvk.tensor_core_status(), "table": table},
             "gpu_launches": launches}

@@ -120,6 +120,7 @@ struct AttnParams {
     float* lse_accum;            // (splits, B, Hq, Sq) fp32, log2-domain log-sum-exp of the split (-inf if empty)
     unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals, readers; zero before first use
     float scale_log2;            // softmax_scale * log2(e)
+    int flags;                   // the entry point's flags (bit 2: keep one CTA per (tile, split) in the head_dim-256 kernel)
 #ifdef FRT_TOK_TRACE
     int trace_slot;
 #endif
@@ -746,6 +747,7 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
     p.G = G;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.kv_static_rows = kv_static_rows;
+    p.flags = flags;
     if (o_accum && lse_accum && counters) {
         p.o_accum = o_accum;
         p.lse_accum = lse_accum;

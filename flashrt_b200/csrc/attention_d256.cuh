@@ -34,27 +34,35 @@ struct D256Cfg {
     static constexpr int KV_BYTES = BKV * D * 2;           // 32 KB, one of K or V, one stage
     static constexpr int OFF_K = Q_BYTES;
     static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
-    static constexpr int DATA_BYTES = OFF_V + 2 * KV_BYTES;   // 192 KB >= the 128 KB partial staged for the combine
+    // operand tiles of a CTA that owns D / dq columns of V: Q, two stages of K, two stages of its part of V (192 KB for
+    // dq = 1, 144 KB for dq = 4; the combine re-uses the first 74 KB after the last MMA)
+    static constexpr int data_bytes(int dq) { return OFF_V + 2 * (KV_BYTES / dq); }
     static constexpr int ML_BYTES = 128 * 4;
-    static constexpr int SMEM_BYTES = DATA_BYTES + ML_BYTES + 256 + 1024;
+    static constexpr int smem_bytes(int dq) { return data_bytes(dq) + ML_BYTES + 256 + 1024; }
     static constexpr int S_COL = 0;                        // two S buffers of 64 columns
     static constexpr int O_COL = 128;
     static constexpr int TMEM_COLS = 512;
     static constexpr float RESCALE_THRESHOLD = 8.0f;
 };
 
+// DQ: the head dim of V / O is cut into DQ parts, one CTA each (scratch path only).  Every part repeats Q.K^T and the
+// softmax of its (row tile, kv split) and computes P.V for D / DQ columns, so that the accumulator a CTA has to move
+// out of tensor memory -- the longest single step of the scratch path: 3 us for 128 x 256 fp32 -- shrinks by DQ and
+// the grid covers 4 x more SMs.
+template <int DQ>
 __global__ void __launch_bounds__(192, 1)
 attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, AttnParams p) {
     using Cfg = D256Cfg;
     constexpr int D = Cfg::D, BKV = Cfg::BKV;
+    constexpr int DV = D / DQ;                             // columns of V / O of this CTA
+    constexpr int V_BYTES = BKV * DV * 2;                  // one V stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;
     uint8_t* sK = smem + Cfg::OFF_K;
     uint8_t* sV = smem + Cfg::OFF_V;
-    float* s_lse = reinterpret_cast<float*>(smem + Cfg::DATA_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::DATA_BYTES + Cfg::ML_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::data_bytes(DQ) + Cfg::ML_BYTES);
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;      // [2]
     uint64_t* v_full = bars + 3;      // [2]
@@ -74,7 +82,9 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool via_scratch = p.o_accum != nullptr;
     const uint32_t C = gridDim.z;
     const uint32_t rank = blockIdx.z;
-    const int tile = blockIdx.x;
+    const int tile = blockIdx.x / DQ;
+    const int dq = blockIdx.x % DQ;
+    const int ntiles = gridDim.x / DQ;
     const int hk = blockIdx.y % p.Hkv;
     const int b = blockIdx.y / p.Hkv;
     const int tok0 = tile * (128 / p.G);
@@ -106,7 +116,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc::tma_prefetch_desc(&tmV);
     }
     if (warp == 5) {
-        tc::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tc::tmem_alloc(tmem_slot, (DQ == 1 ? 512 : 256));
         tc::tmem_relinquish();
     }
     tc::tc_fence_before_sync();
@@ -124,9 +134,9 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc::mbar_arrive_expect_tx(&k_full[st], Cfg::KV_BYTES);
             for (int db = 0; db < 4; ++db)
                 tc::tma_load_4d(sK + st * Cfg::KV_BYTES + db * (BKV * 128), &tmK, &k_full[st], db * 64, hk, key0, b);
-            tc::mbar_arrive_expect_tx(&v_full[st], Cfg::KV_BYTES);
-            for (int db = 0; db < 4; ++db)
-                tc::tma_load_4d(sV + st * Cfg::KV_BYTES + db * (BKV * 128), &tmV, &v_full[st], db * 64, hk, key0, b);
+            tc::mbar_arrive_expect_tx(&v_full[st], V_BYTES);
+            for (int db = 0; db < DV / 64; ++db)
+                tc::tma_load_4d(sV + st * V_BYTES + db * (BKV * 128), &tmV, &v_full[st], dq * DV + db * 64, hk, key0, b);
         };
         // chunks that lie inside the rows the previous kernel does not write may be fetched while it still runs
         int early = 0;
@@ -147,7 +157,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     } else if (warp == 5 && lane == 0) {
         // ---------------- MMA issuer
         constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);
-        constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, D);     // A = P from TMEM, B = V MN-major
+        constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, DV);    // A = P from TMEM, B = V MN-major
         const uint64_t dq_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ));
         const uint64_t dk_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sK));
         const uint64_t dv_base = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV), BKV * 128);
@@ -180,7 +190,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             ATTN_WAIT(&v_full[j & 1], (uint32_t)((j >> 1) & 1), AERR_MMA);
             if (*abort_flag) break;
             tc::tc_fence_after_sync();
-            const uint64_t dv = dv_base + (uint64_t)((j & 1) * (Cfg::KV_BYTES >> 4));
+            const uint64_t dv = dv_base + (uint64_t)((j & 1) * (V_BYTES >> 4));
             const uint32_t a_tm = tmem + Cfg::S_COL + (j & 1) * 64;
 #pragma unroll
             for (int k = 0; k < BKV / 16; ++k)
@@ -236,7 +246,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const float alpha = grow ? tc::ex2_approx(m_run - m_new) : 1.0f;
                 l_run *= alpha;
 #pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
+                for (int c = 0; c < DV; c += 32) {
                     uint32_t v[32];
                     tc::tmem_ld32(tmem_O + c, v);
                     tc::tmem_ld_wait();
@@ -282,31 +292,30 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 // O / l as bf16 straight from registers to the scratch in column slices [slice][row][D / C]: the 64
                 // bytes a thread writes per 32 columns are adjacent to its neighbours' (the rows of a slice are
                 // contiguous), so a warp's store covers 2 KB without gaps.  Log2-domain lse alongside.
-                const int dper = D / (int)C;                   // columns per slice: 32 .. 256, a multiple of 32
+                const int dper = DV / (int)C;                  // columns per slice: a multiple of 8
                 const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;
                 const size_t row0 = ((size_t)(b * p.Hkv + hk) * p.Sq << gshift) + (size_t)tile * 128;
-                uint8_t* blk = reinterpret_cast<uint8_t*>(p.o_accum) + (rank * split_stride + row0) * (size_t)(D * 2);
-                if (row < rows_valid)
+                // block of (tile, split): rows_valid x D bf16; inside it the part of this dq: rows_valid x DV
+                uint8_t* blk = reinterpret_cast<uint8_t*>(p.o_accum) + (rank * split_stride + row0) * (size_t)(D * 2) +
+                               (size_t)dq * rows_valid * (DV * 2);
+                if (row < rows_valid && dq == 0)
                     __stcg(p.lse_accum + rank * split_stride + row0 + row,
                            l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY);
                 // 64 columns per step, the next step's tensor-memory load in flight while this one is converted
                 auto emit = [&](const uint32_t* v, int c) {
                     if (row < rows_valid) {
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int cc = c + 32 * h;
+                        for (int j8 = 0; j8 < 8; ++j8) {                // 8 columns = 16 bytes at a time
+                            const int cc = c + 8 * j8;
                             uint4* dst = reinterpret_cast<uint4*>(blk + ((size_t)(cc / dper) * rows_valid + row) * (dper * 2) +
                                                                   (cc % dper) * 2);
-#pragma unroll
-                            for (int j4 = 0; j4 < 4; ++j4) {
-                                const uint32_t* w = v + 32 * h + 8 * j4;
-                                uint4 o;
-                                o.x = pack_bf16x2(__uint_as_float(w[0]) * invl, __uint_as_float(w[1]) * invl);
-                                o.y = pack_bf16x2(__uint_as_float(w[2]) * invl, __uint_as_float(w[3]) * invl);
-                                o.z = pack_bf16x2(__uint_as_float(w[4]) * invl, __uint_as_float(w[5]) * invl);
-                                o.w = pack_bf16x2(__uint_as_float(w[6]) * invl, __uint_as_float(w[7]) * invl);
-                                __stcg(dst + j4, o);
-                            }
+                            const uint32_t* w = v + 8 * j8;
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(w[0]) * invl, __uint_as_float(w[1]) * invl);
+                            o.y = pack_bf16x2(__uint_as_float(w[2]) * invl, __uint_as_float(w[3]) * invl);
+                            o.z = pack_bf16x2(__uint_as_float(w[4]) * invl, __uint_as_float(w[5]) * invl);
+                            o.w = pack_bf16x2(__uint_as_float(w[6]) * invl, __uint_as_float(w[7]) * invl);
+                            __stcg(dst, o);
                         }
                     }
                 };
@@ -314,24 +323,29 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (nchunks > 0) {                              // warp-uniform: the loads are warp-collective
                     tc::tmem_ld32(tmem_O + 0, va);
                     tc::tmem_ld32(tmem_O + 32, va + 32);
+                    if constexpr (DV >= 128) {
 #pragma unroll
-                    for (int c = 0; c < D; c += 128) {
-                        tc::tmem_ld_wait();
-                        tc::tmem_ld32(tmem_O + c + 64, vb);
-                        tc::tmem_ld32(tmem_O + c + 96, vb + 32);
-                        emit(va, c);
-                        tc::tmem_ld_wait();
-                        if (c + 128 < D) {
-                            tc::tmem_ld32(tmem_O + c + 128, va);
-                            tc::tmem_ld32(tmem_O + c + 160, va + 32);
+                        for (int c = 0; c < DV; c += 128) {
+                            tc::tmem_ld_wait();
+                            tc::tmem_ld32(tmem_O + c + 64, vb);
+                            tc::tmem_ld32(tmem_O + c + 96, vb + 32);
+                            emit(va, c);
+                            tc::tmem_ld_wait();
+                            if (c + 128 < DV) {
+                                tc::tmem_ld32(tmem_O + c + 128, va);
+                                tc::tmem_ld32(tmem_O + c + 160, va + 32);
+                            }
+                            emit(vb, c + 64);
                         }
-                        emit(vb, c + 64);
+                    } else {
+                        tc::tmem_ld_wait();
+                        emit(va, 0);
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) va[i] = 0u;
 #pragma unroll 1
-                    for (int c = 0; c < D; c += 64) emit(va, c);
+                    for (int c = 0; c < DV; c += 64) emit(va, c);
                 }
             } else {
                 // single split: the result leaves directly, one row per thread
@@ -387,12 +401,14 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // ---------------- combine through global scratch.  Block of (batch, kv head, tile, split) in o_accum, as bf16:
         // rows_valid x D, stored [slice][row][D / C]; the rows of all tiles of one (split, batch, kv head) are packed
         // back to back, so the caller's (splits, batch, heads, seqlen_q, D) fp32 buffer is always large enough.
-        const unsigned tile_id = (unsigned)((b * p.Hkv + hk) * gridDim.x + tile);
+        const unsigned tile_id = (unsigned)((b * p.Hkv + hk) * ntiles + tile);
+        const unsigned arrivals = C * DQ;        // one counter per tile: all kv splits of all DQ parts
         unsigned* cnt = p.counters + 2 * tile_id;
         const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;            // rows per split in the scratch
         const size_t row0 = ((size_t)(b * p.Hkv + hk) * p.Sq << gshift) + (size_t)tile * 128;
-        const int dper = D / (int)C;
+        const int dper = DV / (int)C;
         const uint32_t slice_bytes = (uint32_t)rows_valid * dper * 2;
+        const size_t part_off = (size_t)dq * rows_valid * (DV * 2);
         uint8_t* gbase = reinterpret_cast<uint8_t*>(p.o_accum);
         float* s_w = reinterpret_cast<float*>(smem + 65536);        // [row][8] combine weights
         float* s_l = s_w + 128 * 8;                                  // [split][row] log-sum-exps of the partials
@@ -409,7 +425,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (uint32_t it = 0;; ++it) {
                 unsigned seen;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
-                if (seen >= C) { ok = true; break; }
+                if (seen >= arrivals) { ok = true; break; }
                 if (*abort_flag) break;
                 if ((it & 15) == 15 && tc::global_timer_ns() > deadline) break;
                 __nanosleep(20);
@@ -423,7 +439,8 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tc::mbar_arrive_expect_tx(c_full, C * slice_bytes + (lse_bulk ? C * (uint32_t)rows_valid * 4u : 0u));
                 for (uint32_t sidx = 0; sidx < C; ++sidx) {
                     tc::bulk_load(cbuf + sidx * slice_bytes,
-                                  gbase + (sidx * split_stride + row0) * (size_t)(D * 2) + (size_t)rank * slice_bytes,
+                                  gbase + (sidx * split_stride + row0) * (size_t)(D * 2) + part_off +
+                                      (size_t)rank * slice_bytes,
                                   slice_bytes, c_full);
                     if (lse_bulk)
                         tc::bulk_load(s_l + sidx * 128, p.lse_accum + sidx * split_stride + row0,
@@ -459,14 +476,14 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const float invL = Lw > 0.0f ? 1.0f / Lw : 0.0f;
 #pragma unroll
                 for (int sidx = 0; sidx < 8; ++sidx) s_w[r * 8 + sidx] = w[sidx] * invL;
-                if (p.lse && rank == 0) p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
+                if (p.lse && rank == 0 && dq == 0) p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
             }
             if (!lse_bulk) ATTN_WAIT(c_full, 0u, AERR_SOFTMAX);
         }
         __syncthreads();
         if (!*abort_flag) {
             const int cpr = dper >> 3;                       // 16-byte chunks (8 columns) per slice row
-            const int d0 = (int)rank * dper;
+            const int d0 = dq * DV + (int)rank * dper;
             const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
             const int cshift = 31 - __clz(cpr);
             for (int idx = threadIdx.x; idx < rows_valid * cpr; idx += 192) {
@@ -511,25 +528,31 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ATT_STAMP(11);
         if (threadIdx.x == 0) {
             const unsigned done = atomicAdd(cnt + 1, 1u);
-            if (done == C - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
+            if (done == arrivals - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
         }
     }
     tc::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) tc::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+    if (warp == 5) tc::tmem_dealloc(tmem, (DQ == 1 ? 512 : 256));
     ATT_STAMP(12);
 }
 
 static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
                             const long long* ks, const long long* vs, int splits, bool pdl, cudaStream_t stream) {
     using Cfg = D256Cfg;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Cfg::SMEM_BYTES);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return FRT_ERR_UNSUPPORTED;
+    static bool attr_done[64] = {false};                 // the attribute is per device
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_d256_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::smem_bytes(1));
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        attr_done = true;
+        e = cudaFuncSetAttribute(attn_d256_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes(4));
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        attr_done[dev] = true;
     }
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     CUtensorMap tmQ, tmK, tmV;
     {
         uint64_t dims[5] = {(uint64_t)Cfg::D, (uint64_t)p.G, (uint64_t)p.Hkv, (uint64_t)p.Sq, (uint64_t)p.B};
@@ -558,22 +581,24 @@ static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnPar
     while (splits & (splits - 1)) --splits;            // power of two: each split finishes D / splits columns
     if (splits == 1) p.o_accum = nullptr;
     const int tiles = (p.Sq * p.G + 127) / 128;
+    int dq = 1;
     if (p.o_accum) {
-        int sms = 0, dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if ((long long)tiles * p.Hkv * p.B * splits > sms) return FRT_ERR_UNSUPPORTED;   // the CTAs of a tile wait for one another
+        const long long ctas = (long long)tiles * p.Hkv * p.B * splits;
+        if (ctas > sms) return FRT_ERR_UNSUPPORTED;    // the CTAs of a tile wait for one another
+        // four head-dim parts per (tile, split) while the whole grid still fits one wave and a slice keeps 8 columns
+        if (ctas * 4 <= sms && 64 / splits >= 8 && !(p.flags & 4)) dq = 4;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles, p.Hkv * p.B, splits);
+    cfg.gridDim = dim3(tiles * dq, p.Hkv * p.B, splits);
     cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.dynamicSmemBytes = Cfg::smem_bytes(dq);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_d256_kernel, tmQ, tmK, tmV, p);
+    cudaError_t e = dq == 4 ? cudaLaunchKernelEx(&cfg, attn_d256_kernel<4>, tmQ, tmK, tmV, p)
+                            : cudaLaunchKernelEx(&cfg, attn_d256_kernel<1>, tmQ, tmK, tmV, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }

@@ -945,8 +945,8 @@ extern "C" {
 // D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . W(N,K)^T + bias
 // A, W: FP8 E4M3 row-major, K contiguous.  K % 16 == 0; A, W 16-byte aligned.
 // splits: 0 = choose, otherwise the split-K factor (clamped to [1, 8]).
-// flags: bit0 = programmatic dependent launch; bit1 = one-tile-per-CTA kernel for M > 256; bit3 = CTA-pair kernel
-// (256 x 256 tiles, M > 256, N >= 256, no split-K).
+// flags: bit0 = programmatic dependent launch; bit1 = one-tile-per-CTA kernel for M > 256; bit3 = force the CTA-pair
+// kernel (256 x 256 tiles, M > 256, N >= 256, no split-K; chosen by itself for long tile lists), bit5 = never use it.
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream) {
@@ -973,8 +973,12 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     }
     if (M <= 256) return dispatch_small_m<EPI_BF16>(A, W, p, K, M, (N + 127) / 128, splits, pdl, s);
     int sp = splits > 0 ? pick_splits(1, p.kb_total, splits > 8 ? 8 : splits) : 1;
-    // flags bit3: one 256 x 256 tile per CTA pair (cta_group::2); opt-in until it has been measured on a GPU
-    if (sp == 1 && (flags & 8) && N >= 256) return launch_gemm_pair(A, W, p, K, pdl, s);
+    // One 256 x 256 tile per CTA pair (cta_group::2): measured 3-10 % faster than the one-CTA persistent kernel once
+    // the tile list fills at least two waves of pairs and K >= 2048 (e.g. 20480 x 14336 x 3072: 698 vs 744 us), a few
+    // percent slower on short lists and at K = 1024.  flags bit 3 forces it, flags bit 5 keeps the one-CTA kernel.
+    const long long tiles256 = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    const bool pair_pays = tiles256 >= 148 && K >= 2048 && !(flags & 32) && !(flags & 2);
+    if (sp == 1 && ((flags & 8) || pair_pays) && N >= 256) return launch_gemm_pair(A, W, p, K, pdl, s);
     if (sp == 1 && !(flags & 2)) {      // flags bit1 keeps the one-tile-per-CTA kernel (for comparison runs)
         if (N >= 256) return launch_gemm_persistent<256, EPI_P_BF16>(A, W, p, K, pdl, s);
         if (N > 64) return launch_gemm_persistent<128, EPI_P_BF16>(A, W, p, K, pdl, s);

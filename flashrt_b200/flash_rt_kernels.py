@@ -239,14 +239,16 @@ class GemmRunner:
     """
 
     def fp8_nt_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
-                   one_tile_per_cta=False, cta_pair=False, swapped=False, tile_n=0):
+                   one_tile_per_cta=False, cta_pair=None, swapped=False, tile_n=0):
         """D(M,N) bf16 = sa*sb * A(M,K) . B(N,K)^T — weights stored (N,K), the ``fp8_layout == "nk"`` form.
         ``one_tile_per_cta`` selects the non-persistent large-M kernel (same result; kept for comparison runs);
-        ``cta_pair`` the 256 x 256-tile kernel on CTA pairs (M > 256, N >= 256; opt-in).  M <= 256: ``swapped``
+        ``cta_pair`` True / False forces / forbids the 256 x 256-tile kernel on CTA pairs (M > 256, N >= 256; by
+        default the library uses it for tile lists of at least two waves at K >= 2048).  M <= 256: ``swapped``
         keeps the weights-on-lanes kernel instead of the token-major one, ``tile_n`` (64 / 128 / 256) pins the
         token-major kernel's tile width."""
         call("frt_b200_gemm_fp8_nt", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits,
-             _f(pdl) | (2 if one_tile_per_cta else 0) | (8 if cta_pair else 0) | (16 if swapped else 0)
+             _f(pdl) | (2 if one_tile_per_cta else 0) | (8 if cta_pair else 0) | (32 if cta_pair is False else 0)
+             | (16 if swapped else 0)
              | _tile_hint(tile_n), stream)
 
     # -- the decoder's projections with the norm kernel between them folded in ------------------------------

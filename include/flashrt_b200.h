@@ -106,8 +106,9 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
  *   splits: 0 = choose; else split-K factor in [1, 16] (reduced inside a thread-block cluster).
  *   M > 256 runs as a persistent kernel (one CTA per SM walking the tile list, two accumulators in tensor memory so
  *   that the epilogue overlaps the next tile's MMAs); flags bit 1 selects the one-tile-per-CTA kernel instead;
- *   flags bit 3 (M > 256, N >= 256, no split-K) a kernel with one 256 x 256 tile per CTA pair (tcgen05 cta_group::2:
- *   each CTA stages its 128 rows of A and 128 of the 256 weight rows, the leader issues the MMAs for both).
+ *   tile lists of at least two waves with K >= 2048 (or flags bit 3; M > 256, N >= 256, no split-K) run a kernel with
+ *   one 256 x 256 tile per CTA pair (tcgen05 cta_group::2: each CTA stages its 128 rows of A and 128 of the 256 weight
+ *   rows, the leader issues the MMAs for both); flags bit 5 keeps the one-CTA persistent kernel.
  *   M <= 256 with K % 128 == 0 and N % 8 == 0 runs the token-major kernel (activation rows on the 128 accumulator
  *   lanes, up to 256 weight rows on the columns, split-K in {1, 2, 4, 8} over a cluster); flags bit 4 keeps the
  *   swapped kernel (weights on the lanes) instead; flags bits 8-9 pin the tile width (1 = 64, 2 = 128, 3 = 256). */

@@ -225,9 +225,6 @@ def test_gemm_fp8_persistent_equals_one_tile_per_cta(M, N, K):
     _check(d_1.get(), _ref(A, W, sa, sb, bias))
 
 
-@pytest.mark.skipif(os.environ.get("FRT_TEST_CTA_PAIR") != "1",
-                    reason="the CTA-pair GEMM was written after this build's GPU time was spent and has not run on a "
-                           "GPU yet; set FRT_TEST_CTA_PAIR=1 to run it")
 @pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (512, 256, 128), (1000, 700, 512), (8192, 3072, 3072)])
 def test_gemm_fp8_cta_pair_kernel(M, N, K):
     """256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) against the torch reference, and against the persistent
@@ -241,7 +238,7 @@ def test_gemm_fp8_cta_pair_kernel(M, N, K):
     d_A, d_W, d_b, d_sa, d_sb = Dev(A), Dev(W), Dev(bias), f32(sa), f32(sb)
     d_1, d_2 = zeros((M, N), np.uint16), zeros((M, N), np.uint16)
     g = fvk.GemmRunner()
-    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_1.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_1.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr, cta_pair=False)
     g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_2.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr, cta_pair=True)
     assert fvk.tensor_core_status() == 0
     _check(d_2.get(), _ref(A, W, sa, sb, bias))
