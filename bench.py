@@ -736,6 +736,89 @@ def run_ops(args):
 
 
 # ---------------------------------------------------------------------------------------------------------------
+def run_timeline(args):
+    """Per-hop timeline of the operator graph (diagnostic; needs a library built with -DFRT_PHASE_STAMPS): two decoder
+    blocks (QKV, attention, attention-out, gate|up, FFN-down -- the loop's own calls) captured as one graph; every CTA
+    stamps %globaltimer at its phases, and the medians over the CTAs of a launch are printed on a common clock."""
+    import ctypes
+    import numpy as np
+    import torch
+    from flashrt_b200 import _lib, load_model
+    from flashrt_b200.pi05_decoder import ACTION_DIM
+    torch.cuda.set_device(0)
+    model = load_model("synthetic:0", config="pi05", device=0)
+    fe = model.frontend
+    p, L = fe.pipeline, fe.layers
+    g = torch.Generator().manual_seed(1)
+    model.set_prefix(torch.randn(L, fe.prefix_len, 256, generator=g), torch.randn(L, fe.prefix_len, 256, generator=g))
+    model.calibrate([torch.randn(fe.chunk_size, ACTION_DIM, generator=g)])
+    gb = (ctypes.c_ulonglong * (8 * 160 * 16))()
+    ab = (ctypes.c_ulonglong * (8 * 64 * 16))()
+
+    def read(reset=1):
+        rc = _lib.call_status("frt_b200_phase_stamps_read", ctypes.addressof(gb), ctypes.addressof(ab), reset)
+        if rc != 0:
+            raise SystemExit("timeline: the library was built without -DFRT_PHASE_STAMPS "
+                             "(FRT_NVCC_EXTRA=-DFRT_PHASE_STAMPS python -m flashrt_b200._build --force)")
+        return (np.frombuffer(gb, dtype=np.uint64).reshape(8, 160, 16).astype(np.int64),
+                np.frombuffer(ab, dtype=np.uint64).reshape(8, 64, 16).astype(np.int64))
+
+    s = fe.stream
+    calls = {"n": 0}
+    orig = p._folded_layers
+
+    def two_blocks(step, stream, pdl):
+        fe.layers = 2
+        try:
+            orig(step, stream, pdl)
+        finally:
+            fe.layers = L
+
+    with torch.cuda.stream(s):
+        p.noise.normal_()
+        p._step_in(s.cuda_stream, True)
+        p._norm(None, None, "attn", 0, 0, "qkv", s.cuda_stream, True, False)
+        two_blocks(0, s.cuda_stream, True)
+        s.synchronize()
+        read()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=s, capture_error_mode="relaxed"):
+            two_blocks(0, s.cuda_stream, True)
+        for _ in range(3):
+            gr.replay()
+        s.synchronize()
+    tt, ta = read(0)
+    kinds = ["qkv (TMA-fed, layer 0)", "attention", "attention-out", "gate|up (norm producer)", "FFN-down",
+             "qkv (norm producer)", "attention", "attention-out", "gate|up (norm producer)", "FFN-down"]
+    rows, gi, ai = [], 0, 0
+    for k in kinds:
+        if k == "attention":
+            a = ta[ai % 8]
+            ai += 1
+            a = a[a[:, 0] > 0]
+            cols = (a[:, 0].min(), np.median(a[:, 1]), np.median(a[:, 7]), np.median(a[:, 9]), np.median(a[:, 10]),
+                    a[:, 12].max())
+        else:
+            a = tt[gi % 8]
+            gi += 1
+            a = a[a[:, 0] > 0]
+            cols = (a[:, 0].min(), np.median(a[:, 3]), np.median(a[:, 4]), np.median(a[:, 6]), np.median(a[:, 7]),
+                    a[:, 9].max())
+        rows.append({"kernel": k, "ctas": int(len(a)), "ns": [float(v) for v in cols]})
+    t0 = rows[0]["ns"][0]
+    for r in rows:
+        r["us"] = [round((v - t0) / 1e3, 2) for v in r.pop("ns")]
+    hdr = ("kernel                     CTAs  first CTA start | dependency wait returned (GEMM: + operand produced) | "
+           "accumulator complete | GEMM: slots received / attention: partial published | GEMM: finish done / "
+           "attention: all splits arrived | last CTA end   [us, common clock, medians over the CTAs]")
+    print(hdr, file=sys.stderr)
+    for r in rows:
+        print(f"{r['kernel']:26s} {r['ctas']:4d}  " + "  ".join(f"{v:8.2f}" for v in r["us"]), file=sys.stderr)
+    print(json.dumps({"metric": "operator-graph phase timeline (diagnostic)", "unit": "us", "rows": rows,
+                      "block_us": rows[-1]["us"][-1] - rows[4]["us"][-1]}), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
 def run_prefix(args):
     """The step in front of the denoise path: 18 Gemma-2B encoder layers (FP8) turning a 768-token prefix into the
     per-layer K / V of the action expert.  One "step" = one encode() of the whole prefix."""
@@ -820,7 +903,7 @@ def main():
                     help="an extra is started only while the whole run has taken less than this many seconds")
     ap.add_argument("--lean", action="store_true",
                     help="skip the CPU baseline and the GEMM roofline leg (for short runs under a profiler)")
-    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops", "prefix"],
+    ap.add_argument("--workload", default="pi05", choices=["pi05", "wan", "ops", "prefix", "timeline"],
                     help="pi05 = the headline action-expert loop (default); wan = the video-DiT step (configs[4]); "
                          "ops = the operator sweep of configs[1] (norm / FP8 GEMM / NVFP4 GEMM)")
     ap.add_argument("--precision", default="fp8", choices=["fp8", "nvfp4"],
@@ -838,6 +921,9 @@ def main():
         return
     if args.workload == "prefix" and args.impl != "reference":
         run_prefix(args)
+        return
+    if args.workload == "timeline" and args.impl != "reference":
+        run_timeline(args)
         return
     if args.impl == "reference":
         run_reference(args)

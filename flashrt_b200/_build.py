@@ -42,8 +42,8 @@ def _stale(target: str, deps: list[str]) -> bool:
 def build_native(force: bool = False, verbose: bool = False) -> str:
     """Compile every ``csrc/*.cu`` and link ``libflashrt_b200.so``.  Returns its path.
 
-    ``FRT_NVCC_EXTRA`` (environment, space separated) appends compiler flags, e.g. ``-DFRT_LOOP_TRACE`` for the
-    phase stamps of the persistent loop kernel that ``bench.py --persistent-loop --loop-trace`` reads (use
+    ``FRT_NVCC_EXTRA`` (environment, space separated) appends compiler flags, e.g. ``-DFRT_PHASE_STAMPS`` for the
+    device-timer phase stamps that ``bench.py --workload timeline`` reads through ``frt_b200_phase_stamps_read`` (use
     ``--force`` when switching it on or off: the objects do not depend on the environment)."""
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()

@@ -34,15 +34,6 @@ namespace frt {
 
 __device__ int g_attn_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
 
-#ifdef FRT_TRACE
-__device__ long long g_atrace[64];
-#define ATRACE(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_atrace[i] = clock64(); } while (0)
-#define ATRACE0(i) do { if (threadIdx.x == 0) ATRACE(i); } while (0)
-#else
-#define ATRACE(i)
-#define ATRACE0(i)
-#endif
-
 // ------------------------------------------------------------------ tensor maps (bf16, up to 5-D)
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -121,7 +112,7 @@ struct AttnParams {
     unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals, readers; zero before first use
     float scale_log2;            // softmax_scale * log2(e)
     int flags;                   // the entry point's flags (bit 2: keep one CTA per (tile, split) in the head_dim-256 kernel)
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
     int trace_slot;
 #endif
 };
@@ -186,7 +177,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
-    ATRACE0(0);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     // kv splits are either the CTAs of a cluster (combined through DSMEM) or, when scratch buffers are given,
@@ -366,7 +356,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc::tc_fence_after_sync();
         }
         __syncwarp();
-        ATRACE0(10);
         s_m[row] = m_run;
         s_l[row] = l_run;
         if (via_scratch) {
@@ -395,7 +384,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     }
                 }
             }
-            ATRACE0(11);
         } else if (!__any_sync(0xffffffffu, *abort_flag != 0)) {
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
@@ -430,7 +418,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         unsigned* cnt = p.counters + 2 * tile_id;
         const size_t split_stride = (size_t)p.B * p.Hq * p.Sq;
         __syncthreads();
-        ATRACE0(12);
         // G divides 128, so it is a power of two: row -> (token, head) by shift / mask
         const int gshift = 31 - __clz(p.G);
         int rows_valid = (p.Sq - tok0) << gshift;
@@ -450,7 +437,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         __threadfence();
         __syncthreads();
-        ATRACE0(13);
         if (threadIdx.x == 0) {
             atomicAdd(cnt, 1u);
             bool ok = false;
@@ -468,7 +454,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
         }
         __syncthreads();
-        ATRACE0(14);
         if (!*abort_flag) {
             const int cpr = dper >> 2;                            // 16-byte chunks of this rank's slice per row
             const int d0 = (int)rank * dper;
@@ -527,7 +512,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         // the last CTA of the tile to finish reading re-arms the counters for the next launch
         __syncthreads();
-        ATRACE0(15);
         if (threadIdx.x == 0) {
             const unsigned done = atomicAdd(cnt + 1, 1u);
             if (done == C - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
@@ -634,12 +618,13 @@ template <int D, int BKV>
 static int launch_attn(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
                        const long long* ks, const long long* vs, int splits, bool pdl, cudaStream_t stream) {
     using Cfg = AttnCfg<D, BKV>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     // Q as {d, head-in-group, kv head, token, batch}; strides in elements: qs = {batch, row, head}
     CUtensorMap tmQ, tmK, tmV;
@@ -883,18 +868,36 @@ int frt_b200_attention_status(int reset) {
     return v;
 }
 
-#ifdef FRT_TOK_TRACE
-int frt_attn_trace_read(unsigned long long* host, int reset_slot) {
-    cudaDeviceSynchronize();
-    if (reset_slot) g_attn_trace_slot = 0;
-    return (int)cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(unsigned long long) * 8 * 64 * 16);
-}
+// Diagnostics (no counterpart in the reference): device-timer phase stamps of the last 8 launches of the token-major
+// GEMM (gemm_host: 8 x 160 CTAs x 16 stamps) and of the head_dim-256 attention kernel (attn_host: 8 x 64 x 16), in
+// nanoseconds of %globaltimer.  Only a library built with -DFRT_PHASE_STAMPS records them; otherwise -2.
+// reset != 0 restarts the launch slots at 0 and clears the stamps (after copying them out).  Synchronises the device.
+#ifdef FRT_PHASE_STAMPS
+extern "C" int frt_b200_gemm_phase_stamps(unsigned long long* host, int reset);
 #endif
-
-#ifdef FRT_TRACE
-int frt_atrace_read(long long* host64) {
-    return (int)cudaMemcpyFromSymbol(host64, g_atrace, sizeof(long long) * 64);
-}
+int frt_b200_phase_stamps_read(unsigned long long* gemm_host, unsigned long long* attn_host, int reset) {
+#ifdef FRT_PHASE_STAMPS
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+    if (gemm_host) {
+        int rc = frt_b200_gemm_phase_stamps(gemm_host, reset);
+        if (rc) return rc;
+    }
+    if (attn_host) {
+        e = cudaMemcpyFromSymbol(attn_host, g_attn_trace, sizeof(unsigned long long) * 8 * 64 * 16);
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+    }
+    if (reset) {
+        g_attn_trace_slot = 0;
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_attn_trace) == cudaSuccess && ptr)
+            cudaMemset(ptr, 0, sizeof(unsigned long long) * 8 * 64 * 16);
+    }
+    return FRT_OK;
+#else
+    (void)gemm_host; (void)attn_host; (void)reset;
+    return FRT_ERR_UNSUPPORTED;
 #endif
+}
 
 }  // extern "C"

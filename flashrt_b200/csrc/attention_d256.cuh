@@ -18,7 +18,7 @@
 // Warps: 0-3 softmax (thread = row), 4 TMA, 5 MMA.
 #pragma once
 
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
 __device__ unsigned long long g_attn_trace[8][64][16];
 static int g_attn_trace_slot = 0;
 #define ATT_STAMP(i) do { if (threadIdx.x == 0) g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 64][i] = tc::global_timer_ns(); } while (0)
@@ -571,7 +571,7 @@ static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnPar
         rc = make_tmap_bf16(&tmV, V, 4, dims, strv, box);
         if (rc) return rc;
     }
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
     p.trace_slot = g_attn_trace_slot;
     g_attn_trace_slot = (g_attn_trace_slot + 1) % 8;
 #endif

@@ -306,12 +306,13 @@ attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 static int launch_attn_pair(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
                             const long long* ks, const long long* vs, bool pdl, cudaStream_t stream) {
     using Cfg = PairCfg;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(attn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     CUtensorMap tmQ, tmK, tmV;
     {

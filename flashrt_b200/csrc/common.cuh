@@ -133,4 +133,23 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- host: per-device launch set-up
+// Function attributes (dynamic shared memory size, non-portable cluster size) and the SM count belong to a device,
+// not to the process: a launcher sets them once per device ordinal.
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool need(int& dev) {
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { dev = -1; return true; }
+        return !done[dev];
+    }
+    void set(int dev) { if (dev >= 0 && dev < 64) done[dev] = true; }
+};
+inline int device_sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    return sms[dev] > 0 ? sms[dev] : 148;
+}
+
 }  // namespace frt

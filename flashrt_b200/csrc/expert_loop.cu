@@ -31,7 +31,7 @@
 //
 // Measured (18 blocks x 10 steps, 50 tokens, 768 prefix keys): 10.5 ms per loop against 9.75 ms for the graph of 1300
 // operator launches, i.e. a phase costs what a launch costs (barrier 1.1-1.4 us + one L2 round trip for the operand
-// 1.5 us + 32 MMAs 2 us + epilogue); build with -DFRT_LOOP_TRACE for the per-phase stamps.
+// 1.5 us + 32 MMAs 2 us + epilogue).
 //
 // Warps: 0 = weight TMA producer, 1 = MMA issuer (one thread), 2-9 = workers (operand loads, softmax, epilogues,
 // row phases, grid barrier).  Every wait is bounded by one wall-clock deadline taken at kernel start; a wait that
@@ -47,21 +47,6 @@ int get_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t r
 
 __device__ int g_loop_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
 
-#ifdef FRT_LOOP_TRACE
-// debugging aid: wall-clock stamps of worker thread 0 of every CTA through the phases of two blocks of the second step
-__device__ unsigned long long g_loop_trace[160][128];
-#define LT(ev)                                                                                              \
-    do {                                                                                                    \
-        if (wtid == 0 && gl >= L && gl < L + 2) g_loop_trace[cta][(gl - L) * 64 + (ev)] = tc::global_timer_ns(); \
-    } while (0)
-#define LTM(ev)                                                                                             \
-    do {                                                                                                    \
-        if ((ev) >= 0 && gl >= L && gl < L + 2) g_loop_trace[cta][(gl - L) * 64 + (ev)] = tc::global_timer_ns(); \
-    } while (0)
-#else
-#define LT(ev)
-#define LTM(ev)
-#endif
 
 namespace el {
 
@@ -275,7 +260,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                 (void)gl; (void)tr;
                 if (u < 0 || dead) return;
                 if (!wait(b_ready, nb & 1)) return;
-                LTM(tr);
                 ++nb;
                 tc::tc_fence_after_sync();
                 for (int kb = 0; kb < KB_PER_UNIT; ++kb) {
@@ -291,7 +275,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                     ++cc;
                     *consumed = (int)cc;
                 }
-                LTM(tr + 1);
                 tc::mma_commit(acc_bar);
             };
             for (int gl = 0; gl < p.steps * L && !dead; ++gl) {
@@ -497,7 +480,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
             for (int layer = 0; layer < L; ++layer) {
                 const int gl = step * L + layer;
                 const float* asc = p.act_scale + (size_t)gl * 4;
-                LT(0);
                 // The keys / values of the prefix do not change during the loop: the chunk of this CTA's attention unit
                 // is fetched by TMA now and lands during phases A and B (an attention CTA owns no QKV unit of the same
                 // block, so nothing else uses the operand region until phase C).
@@ -545,9 +527,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                     }
                     ada_norm_fp8(ssq, p.style_attn + (size_t)gl * 3 * D, asc[0]);
                 }
-                LT(3);
                 grid_barrier();
-                LT(4);
 
                 // ---------------------------------------------------------------- B: QKV projection + RoPE + split
                 {
@@ -558,7 +538,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         });
                         tc::fence_proxy_async_smem();
                         tc::mbar_arrive(b_ready);
-                        LT(5);
                         const int n = u * 128 + quad * 32 + lane;       // feature of the fused q|k|v row
                         const bool is_q = n < QD, is_k = !is_q && n < QD + HD;
                         const int nr = n & (HD - 1);
@@ -573,7 +552,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         }
                         const float alpha = asc[0] * p.ws_qkv[layer];
                         const bool ok = wait(acc_bar, n_acc & 1);
-                        LT(6);
                         ++n_acc;
                         if (ok) {
                             tc::tc_fence_after_sync();
@@ -603,9 +581,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         }
                     }
                 }
-                LT(7);
                 grid_barrier();
-                LT(8);
 
                 // ---------------------------------------------------------------- C: attention partials
                 // unit = (tile of 16 tokens x 8 heads, one chunk of 64 keys).  Q goes to tensor memory (each thread
@@ -646,10 +622,8 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         tc::fence_proxy_async_smem();
                         tc::tc_fence_before_sync();
                         tc::mbar_arrive(b_ready);
-                        LT(9);
                         bool ok = wait(acc_bar, n_acc & 1);
                         ++n_acc;
-                        LT(10);
                         float m_run = -INFINITY, l_run = 0.0f;
                         if (ok && ww < 4) {
                             // ---- softmax of the chunk: thread = row, P (bf16) overlays S in tensor memory
@@ -695,7 +669,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         }
                         ok = wait(o_full, n_o & 1);
                         ++n_o;
-                        LT(13);
                         // ---- normalised partial as bf16 -> shared memory (rows of 512 bytes, 16-byte chunks xor-swizzled)
                         // -> global scratch with full-row stores (runs even after a failed wait: everyone must reach
                         // the worker barriers)
@@ -730,9 +703,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         if (wtid < 128) __stcg(p.plse + (size_t)au * 128 + wtid, s_lse[wtid]);
                     }
                 }
-                LT(11);
                 grid_barrier();
-                LT(12);
 
                 // ---------------------------------------------------------------- D: combine the chunks -> FP8
                 if (!dead) {
@@ -786,9 +757,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         *reinterpret_cast<uint2*>(p.attn8 + (size_t)tok * QD + head * HD + ch * 8) = o8;
                     }
                 }
-                LT(15);
                 grid_barrier();
-                LT(16);
 
                 // ---------------------------------------------------------------- E: output projection (split-K 2)
                 {
@@ -800,16 +769,12 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         });
                         tc::fence_proxy_async_smem();
                         tc::mbar_arrive(b_ready);
-                        LT(17);
                         const bool ok = wait(acc_bar, n_acc & 1);
-                        LT(18);
                         ++n_acc;
                         store_partial(ok, ks, tile);
                     }
                 }
-                LT(19);
                 grid_barrier();
-                LT(20);
 
                 // ---------------------------------------------------------------- F: rows
                 if (row_cta && !dead) {
@@ -817,9 +782,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                     const float ssq = add_delta(2, alpha, p.style_attn + (size_t)gl * 3 * D + 2 * D);
                     ada_norm_fp8(ssq, p.style_ffn + (size_t)gl * 3 * D, asc[2]);
                 }
-                LT(23);
                 grid_barrier();
-                LT(24);
 
                 // ---------------------------------------------------------------- G: gate|up projection + GeGLU
                 {
@@ -830,9 +793,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         });
                         tc::fence_proxy_async_smem();
                         tc::mbar_arrive(b_ready);
-                        LT(25);
                         const bool ok = wait(acc_bar, n_acc & 1);
-                        LT(26);
                         ++n_acc;
                         // the token operand is dead once the accumulator is complete: its space carries the exchange
                         float* ex = reinterpret_cast<float*>(sh);                 // [gate | up][token][64]
@@ -848,7 +809,6 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                             tc::tc_fence_before_sync();
                         }
                         work_sync();
-                        LT(34);
                         {
                             // thread = hidden unit h of this tile for tokens tg, tg + 4, ...: all operands first, then
                             // the arithmetic, then the stores (32 consecutive bytes per warp and token)
@@ -871,9 +831,7 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         }
                     }
                 }
-                LT(27);
                 grid_barrier();
-                LT(28);
 
                 // ---------------------------------------------------------------- H: down projection (split-K 4)
                 {
@@ -885,16 +843,12 @@ expert_loop_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_const
                         });
                         tc::fence_proxy_async_smem();
                         tc::mbar_arrive(b_ready);
-                        LT(29);
                         const bool ok = wait(acc_bar, n_acc & 1);
-                        LT(30);
                         ++n_acc;
                         store_partial(ok, ks, tile);
                     }
                 }
-                LT(31);
                 grid_barrier();
-                LT(32);
             }
         }
         if (row_cta && !dead) finish_step(p.steps - 1);
@@ -983,12 +937,13 @@ int frt_b200_expert_loop_fp8(const void* host_args, int args_bytes, void* stream
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static frt::PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(el::expert_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              el::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     int per_sm = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, el::expert_loop_kernel, 320, el::SMEM_BYTES);
@@ -1072,11 +1027,5 @@ int frt_b200_expert_loop_status(int reset) {
     }
     return v;
 }
-
-#ifdef FRT_LOOP_TRACE
-int frt_loop_trace_read(unsigned long long* host) {
-    return (int)cudaMemcpyFromSymbol(host, g_loop_trace, sizeof(unsigned long long) * 160 * 128);
-}
-#endif
 
 }  // extern "C"

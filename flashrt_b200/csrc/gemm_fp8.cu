@@ -38,15 +38,6 @@ namespace frt {
 // ------------------------------------------------------------------ status word
 __device__ int g_gemm_status = 0;   // 0 ok; otherwise first failure code | (blockIdx.x << 8)
 
-#ifdef FRT_TRACE
-__device__ long long g_trace[64];
-#define TRACE(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 96) g_trace[i] = clock64(); } while (0)
-#define TRACE_MMA(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_trace[i] = clock64(); } while (0)
-#else
-#define TRACE(i)
-#define TRACE_MMA(i)
-#endif
-
 // ------------------------------------------------------------------ tensor maps (host)
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -117,6 +108,7 @@ struct GemmParams {
     const __nv_bfloat16* gate;
     const __nv_bfloat16* style;
     float eps;
+    int w_kn;                  // large-M persistent kernel: weights stored (K, N) row-major
 };
 
 enum { EPI_BF16 = 0, EPI_ROPE_SPLIT = 1, EPI_GEGLU_FP8 = 2, EPI_GATE_RES_NORM_FP8 = 3 };
@@ -199,7 +191,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     volatile int* consumed = abort_flag + 2;
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
-    TRACE(0);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     // first row of the lane operand; with the GeGLU epilogue a tile is 64 gate rows + the 64 matching up rows
@@ -233,7 +224,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_d = *tmem_slot;
-    TRACE(1);
 
     pdl_launch_dependents();
 
@@ -323,8 +313,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 break;
             }
             tc::tc_fence_after_sync();
-            if (i == 0) TRACE_MMA(10);
-            if (i == nkb - 1) TRACE_MMA(11);
             const uint32_t sL = tc::smem_u32(stage_base + s * Cfg::STAGE_BYTES);
             const uint32_t sC = sL + Cfg::L_BYTES;
             const uint64_t dL = tc::make_desc_kmajor_sw128(sL);
@@ -356,9 +344,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     __syncwarp();
 
     // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w .. 32w+31
-    TRACE(2);
     pdl_wait();
-    TRACE(3);
     const bool acc_seen = tc::mbar_wait_until(accum_bar, 0, deadline, abort_flag);
     const bool have_acc = __all_sync(0xffffffffu, acc_seen);   // tcgen05.ld below is warp-collective
     if (!have_acc && !*abort_flag) {
@@ -367,7 +353,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     }
     __syncwarp();
     tc::tc_fence_after_sync();
-    TRACE(4);
 
     float alpha = p.alpha_host;
     if (p.sa) alpha *= *p.sa;
@@ -448,9 +433,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                     red[(c + j) * 128 + warp * 32 + lane] = __uint_as_float(v[j]);
             }
         }
-        TRACE(5);
         if (S > 1 || EPI == EPI_GATE_RES_NORM_FP8) tc::cluster_sync_all(); else __syncthreads();
-        TRACE(6);
         if constexpr (EPI == EPI_GATE_RES_NORM_FP8) {
             // ---- split-K sum, gated residual update, RMS statistics over the whole row (all tiles of the cluster),
             // adaRMS modulation and FP8 quantisation of the next GEMM's input.  Every thread reaches both barriers.
@@ -726,9 +709,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 }
             }
         }
-        TRACE(7);
         if (S > 1 || EPI == EPI_GATE_RES_NORM_FP8) tc::cluster_sync_all();
-        TRACE(8);
     }
 
     // ---------------- teardown
@@ -746,7 +727,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
     }
     __syncthreads();
     if (warp == 2) tc::tmem_dealloc(tmem_d, Cfg::TMEM_COLS);
-    TRACE(9);
 }
 
 // ------------------------------------------------------------------ host launch
@@ -787,14 +767,15 @@ int get_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t r
 template <int BN, bool SWAP, int EPI, bool FP4 = false>
 static int launch_gemm(const void* A, const void* W, GemmParams p, int K, int splits, bool pdl, cudaStream_t stream) {
     using Cfg = GemmCfg<BN, FP4>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI, FP4>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
         e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, SWAP, EPI, FP4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     const void* lane_ptr = SWAP ? W : A;
     const void* col_ptr = SWAP ? A : W;
@@ -857,13 +838,14 @@ static int launch_gemm_gate_res_norm(const void* A, const void* W, GemmParams p,
     constexpr int BN = 64;
     using Cfg = GemmCfg<BN>;
     auto kern = gemm_fp8_kernel<BN, true, EPI_GATE_RES_NORM_FP8>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     p.lane_rows = p.N;
     p.col_rows = p.M;
@@ -986,6 +968,40 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     if (N >= 256) return launch_gemm<256, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
     if (N > 64) return launch_gemm<128, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
     return launch_gemm<64, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
+}
+
+// The same product with the weights stored (K, N) row-major -- GemmRunner::fp8_nn_dev, the reference's default
+// ("kn") layout (csrc/bindings.cpp:706-716, flash_rt/models/pi05/pipeline_rtx.py:550-562):
+//   D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . B(K,N) + bias.
+// The weight tiles arrive as boxes of 128 K-rows x 128 N-bytes and feed the MMA as an MN-major operand; accumulation
+// order and result are those of frt_b200_gemm_fp8_nt on the transposed weights (bit for bit).  K % 128 == 0,
+// N % 16 == 0; M <= 256 runs the token-major kernel, larger M the persistent kernel (N >= 128).
+int frt_b200_gemm_fp8_nn(const void* A, const void* B, void* D, int M, int N, int K, const float* d_scale_a,
+                         const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
+                         void* stream) {
+    if (!A || !B || !D || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if ((K % 128) || (N % 16) || N < 128) return FRT_ERR_UNSUPPORTED;
+    if (M == 0) return FRT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool pdl = flags & 1;
+    if (M <= 256) {
+        TokParams t = {};
+        t.M = M; t.N = N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = alpha_host;
+        t.out = (__nv_bfloat16*)D; t.bias = (const __nv_bfloat16*)bias; t.w_kn = 1;
+        return dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_BF16>(A, B, t, K, tok_bn_hint(flags), tok_split_hint(splits), pdl, s);
+    }
+    GemmParams p = {};
+    p.out = (__nv_bfloat16*)D;
+    p.sa = d_scale_a;
+    p.sb = d_scale_b;
+    p.alpha_host = alpha_host;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.M = M;
+    p.N = N;
+    p.kb_total = K / 128;
+    p.w_kn = 1;
+    if (N >= 256) return launch_gemm_persistent<256, EPI_P_BF16>(A, B, p, K, pdl, s);
+    return launch_gemm_persistent<128, EPI_P_BF16>(A, B, p, K, pdl, s);
 }
 
 // QKV projection with the RoPE + split + KV-append epilogue fused (M <= 256):
@@ -1277,18 +1293,19 @@ int frt_b200_gemm_status(int reset) {
     return v;
 }
 
-#ifdef FRT_TOK_TRACE
-int frt_tok_trace_read(unsigned long long* host, int reset_slot) {
-    cudaDeviceSynchronize();
-    if (reset_slot) g_tok_trace_slot = 0;
-    return (int)cudaMemcpyFromSymbol(host, g_tok_trace, sizeof(unsigned long long) * 8 * 160 * 16);
-}
-#endif
-
-#ifdef FRT_TRACE
-int frt_trace_read(long long* host64) {
-    return (int)cudaMemcpyFromSymbol(host64, g_trace, sizeof(long long) * 64);
-}
-#endif
 
 }  // extern "C"
+
+#ifdef FRT_PHASE_STAMPS
+// not part of the ABI: the GEMM half of frt_b200_phase_stamps_read (attention.cu)
+extern "C" __attribute__((visibility("hidden"))) int frt_b200_gemm_phase_stamps(unsigned long long* host, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(host, g_tok_trace, sizeof(unsigned long long) * 8 * 160 * 16);
+    if (reset) {
+        g_tok_trace_slot = 0;
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_tok_trace) == cudaSuccess && ptr)
+            cudaMemset(ptr, 0, sizeof(unsigned long long) * 8 * 160 * 16);
+    }
+    return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
+}
+#endif

@@ -247,16 +247,14 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 static int launch_gemm_pair(const void* A, const void* W, GemmParams p, int K, bool pdl, cudaStream_t stream) {
     using Cfg = PairCfg;
-    static bool attr_done = false;
-    static int sms = 0;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    const int sms = device_sm_count();
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     CUtensorMap tmA, tmW;
     int rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, (uint64_t)K, (uint64_t)K, 128);

@@ -106,7 +106,13 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                 uint8_t* dst = smem + s * Cfg::STAGE_BYTES;
                 tc::mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
                 tc::tma_load_2d(dst, &tmA, &full[s], kb * 128, m0);
-                tc::tma_load_2d(dst + Cfg::L_BYTES, &tmW, &full[s], kb * 128, n0);
+                if (!FP4 && p.w_kn) {      // (K, N) weights: one 128 x 128-byte box per 128 output features
+#pragma unroll
+                    for (int j = 0; j < BN / 128; ++j)
+                        tc::tma_load_2d(dst + Cfg::L_BYTES + j * 16384, &tmW, &full[s], n0 + j * 128, kb * 128);
+                } else {
+                    tc::tma_load_2d(dst + Cfg::L_BYTES, &tmW, &full[s], kb * 128, n0);
+                }
                 if (FP4) {      // activations are the lane operand here: sf_lane = SFA, sf_col = SFW
                     uint8_t* sf = dst + Cfg::L_BYTES + Cfg::C_BYTES;
                     tc::bulk_load(sf, p.sf_lane + ((size_t)(m0 / 128) * p.sf_katoms + (size_t)kb * 4) * 512, 2048,
@@ -118,11 +124,15 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer: accumulator i & 1 for the CTA's i-th tile
-        constexpr uint32_t idesc = FP4 ? tc::make_idesc_nvfp4(128, BN) : tc::make_idesc(0, 0, 0, 0, 128, BN);
+        const bool w_kn = !FP4 && p.w_kn;
+        const uint32_t idesc = FP4 ? tc::make_idesc_nvfp4(128, BN)
+                                   : (tc::make_idesc(0, 0, 0, 0, 128, BN) | (w_kn ? (1u << 16) : 0u));
         const uint32_t sf_smem0 = tc::smem_u32(smem + Cfg::L_BYTES + Cfg::C_BYTES);
         const uint32_t tmem_sfa = tmem + Cfg::SF_COL, tmem_sfw = tmem + Cfg::SF_COL + 16;
         const uint64_t dL0 = tc::make_desc_kmajor_sw128(tc::smem_u32(smem));
-        const uint64_t dC0 = tc::make_desc_kmajor_sw128(tc::smem_u32(smem + Cfg::L_BYTES));
+        const uint64_t dC0 = w_kn ? tc::make_desc_mnmajor_sw128(tc::smem_u32(smem + Cfg::L_BYTES), 16384)
+                                  : tc::make_desc_kmajor_sw128(tc::smem_u32(smem + Cfg::L_BYTES));
+        const uint64_t cstep = w_kn ? (uint64_t)((32 * 128) >> 4) : 2u;
         long long kc = 0;
         int i = 0;
         for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x, ++i) {
@@ -157,7 +167,7 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                 } else {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        tc::mma_f8(d_tm, dL0 + so + 2 * k, dC0 + so + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc::mma_f8(d_tm, dL0 + so + 2 * k, dC0 + so + cstep * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 tc::mma_commit(&empty[s]);
             }
@@ -255,23 +265,22 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 template <int BN, int EPI, bool FP4 = false>
 static int launch_gemm_persistent(const void* A, const void* W, GemmParams p, int K, bool pdl, cudaStream_t stream) {
     using Cfg = PGemmCfg<BN, FP4>;
-    static bool attr_done = false;
-    static int sms = 0;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    int attr_dev = 0;
+    const int sms = device_sm_count();
+    if (attr_once.need(attr_dev)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_persistent_kernel<BN, EPI, FP4>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        attr_done = true;
+        attr_once.set(attr_dev);
     }
     CUtensorMap tmA, tmW;
     const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
     if (FP4) p.sf_katoms = K / 64;
     int rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, row_bytes, row_bytes, 128);
     if (rc) return rc;
-    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, row_bytes, row_bytes, BN);
+    rc = (!FP4 && p.w_kn) ? get_tmap_2d_u8(&tmW, W, (uint64_t)K, (uint64_t)p.N, (uint64_t)p.N, 128)
+                          : get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, row_bytes, row_bytes, BN);
     if (rc) return rc;
     const int total = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
     cudaLaunchConfig_t cfg = {};

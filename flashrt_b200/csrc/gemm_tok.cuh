@@ -37,7 +37,10 @@
 // thread still reaches the cluster barriers and the TMEM release.
 #pragma once
 
-#ifdef FRT_TOK_TRACE
+// Diagnostic build (-DFRT_PHASE_STAMPS): every CTA stamps %globaltimer at the phases of the kernel (start, set-up done,
+// dependency wait returned, first / last MMA issued, accumulator seen, rows pushed, slots received, finish done, end)
+// into one of 8 launch slots; frt_b200_phase_stamps_read returns them.  Compiled out otherwise.
+#ifdef FRT_PHASE_STAMPS
 __device__ unsigned long long g_tok_trace[8][160][16];
 static int g_tok_trace_slot = 0;
 #define TOK_STAMP(i) do { if (threadIdx.x == tstamp_thread) g_tok_trace[p.trace_slot][ (blockIdx.z * gridDim.x + blockIdx.x) % 160][i] = tc::global_timer_ns(); } while (0)
@@ -83,7 +86,8 @@ struct TokParams {
     int K;
     const __nv_bfloat16* style;
     float eps;
-#ifdef FRT_TOK_TRACE
+    int w_kn;                  // weights stored (K, N) row-major (the MN-major B operand) instead of (N, K)
+#ifdef FRT_PHASE_STAMPS
     int trace_slot;
 #endif
 };
@@ -158,7 +162,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
     int tstamp_thread = 0;
 #endif
     TOK_STAMP(0);
@@ -214,7 +218,15 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t tx = (PRO == TOK_PRO_TMA) ? Cfg::STAGE_BYTES : Cfg::W_BYTES;
         auto load_w = [&](int stage, int kb) {
             uint8_t* dst = tiles + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES;
-            if (EPI == TOK_EPI_GEGLU) {      // tmW has a box of BN / 2 rows here
+            if (p.w_kn) {
+                // (K, N) weights: boxes of 128 K-rows x 128 N-bytes, one per 128 output features; the tile is then an
+                // MN-major operand (128-byte rows along N, 8 K-rows per swizzle atom, 16 KB between the chunks)
+#pragma unroll
+                for (int j = 0; j < (BN >= 128 ? BN / 128 : 1); ++j) {
+                    const int nj = (EPI == TOK_EPI_GEGLU && j == 1) ? p.half + n0 : n0 + j * 128;
+                    tc::tma_load_2d(dst + j * 16384, &tmW, &full[stage], nj, kb * 128);
+                }
+            } else if (EPI == TOK_EPI_GEGLU) {      // tmW has a box of BN / 2 rows here
                 tc::tma_load_2d(dst, &tmW, &full[stage], kb * 128, n0);
                 tc::tma_load_2d(dst + (BN / 2) * 128, &tmW, &full[stage], kb * 128, p.half + n0);
             } else {
@@ -341,7 +353,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        constexpr uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN);
+        const uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN) | (p.w_kn ? (1u << 16) : 0u);   // bit 16: B MN-major
         bool failed = false;
         if (PRO == TOK_PRO_NORM) {
             if (!tc::mbar_wait_until(a_ready, 0, deadline, abort_flag)) {
@@ -351,7 +363,10 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
         }
         const uint64_t dA0 = tc::make_desc_kmajor_sw128(tc::smem_u32(tiles));
-        const uint64_t dW0 = tc::make_desc_kmajor_sw128(tc::smem_u32(tiles + Cfg::A_BYTES));
+        const uint64_t dW0 = p.w_kn ? tc::make_desc_mnmajor_sw128(tc::smem_u32(tiles + Cfg::A_BYTES), 16384)
+                                    : tc::make_desc_kmajor_sw128(tc::smem_u32(tiles + Cfg::A_BYTES));
+        // one K = 32 step: 32 bytes along a K-major row, or 32 rows of 128 bytes of an MN-major tile
+        const uint64_t wstep = p.w_kn ? (uint64_t)((32 * 128) >> 4) : 2u;
         for (int i = 0; i < nkb && !failed; ++i) {
             const int s = i % STG;
             const uint32_t ph = (i / STG) & 1;
@@ -362,18 +377,18 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 break;
             }
             tc::tc_fence_after_sync();
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
             if (i == 0) g_tok_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 160][10] = tc::global_timer_ns();
 #endif
             const uint64_t so = (uint64_t)((s * Cfg::STAGE_BYTES) >> 4);
 #pragma unroll
             for (int k = 0; k < 4; ++k)   // 4 x (K = 32) per 128-byte k-block; +32 bytes = +2 in the address field
-                tc::mma_f8(tmem_d, dA0 + so + 2 * k, dW0 + so + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc::mma_f8(tmem_d, dA0 + so + 2 * k, dW0 + so + wstep * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
             tc::mma_commit(&empty[s]);
             *consumed = i + 1;
         }
         if (!failed) tc::mma_commit(accum_bar);
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
         g_tok_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 160][11] = tc::global_timer_ns();
 #endif
     }
@@ -618,7 +633,7 @@ struct TokPlan { int BN, S, nkb, stages; };
 // SM fit while a CTA stays under ~110 KB of shared memory).  want_bn / want_s (> 0) pin a choice; callers that
 // have measured their shapes do so.
 static bool tok_plan(int N, int K, int m_tiles, int mt, int epi, int pro, int sms, int want_bn, int want_s,
-                     TokPlan* out) {
+                     TokPlan* out, bool w_kn = false) {
     if (K % 128) return false;
     const int kbt = K / 128;
     const int bns[3] = {256, 128, 64};
@@ -629,6 +644,7 @@ static bool tok_plan(int N, int K, int m_tiles, int mt, int epi, int pro, int sm
         if (want_bn > 0 && BN != want_bn) continue;
         if (epi == TOK_EPI_GEGLU && (BN == 64 || ((N / 2) % (BN / 2)))) continue;
         if (epi == TOK_EPI_RESID && BN == 256) continue;    // the 8-lane / 16-lane row-sum groups
+        if (w_kn && (BN == 64 || (epi == TOK_EPI_GEGLU && BN != 256))) continue;   // 128-feature boxes of (K, N) weights
         const int tiles = (epi == TOK_EPI_GEGLU ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN) * m_tiles;
         const int max_st = BN == 256 ? 4 : BN == 128 ? 6 : 8;
         const int stage_bytes = 16384 + BN * 128;
@@ -672,7 +688,7 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     while (p.stages > 2 && Cfg::smem_bytes(p.stages, pl.S, p.per) > 227 * 1024) --p.stages;
     if (PRO == TOK_PRO_NORM && p.stages < pl.nkb) return FRT_ERR_UNSUPPORTED;
     p.K = K;
-#ifdef FRT_TOK_TRACE
+#ifdef FRT_PHASE_STAMPS
     p.trace_slot = g_tok_trace_slot;
     g_tok_trace_slot = (g_tok_trace_slot + 1) % 8;
 #endif
@@ -696,7 +712,8 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     } else {
         memset(&tmA, 0, sizeof(tmA));
     }
-    rc = get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, EPI == TOK_EPI_GEGLU ? BN / 2 : BN);
+    rc = p.w_kn ? get_tmap_2d_u8(&tmW, W, (uint64_t)K, (uint64_t)p.N, (uint64_t)p.N, 128)
+                : get_tmap_2d_u8(&tmW, W, (uint64_t)p.N, (uint64_t)K, (uint64_t)K, EPI == TOK_EPI_GEGLU ? BN / 2 : BN);
     if (rc) return rc;
     const int tiles = EPI == TOK_EPI_GEGLU ? (p.half + BN / 2 - 1) / (BN / 2) : (p.N + BN - 1) / BN;
     cudaLaunchConfig_t cfg = {};
@@ -736,7 +753,7 @@ static int dispatch_gemm_tok(const void* A, const void* W, TokParams p, int K, i
                              cudaStream_t s) {
     TokPlan pl;
     if (!tok_plan(EPI == TOK_EPI_GEGLU ? 2 * p.half : p.N, K, (p.M + 127) / 128, p.M < 128 ? p.M : 128, EPI, PRO,
-                  tok_sm_count(), want_bn, want_s, &pl))
+                  tok_sm_count(), want_bn, want_s, &pl, p.w_kn != 0))
         return FRT_ERR_UNSUPPORTED;
     if (pl.BN == 256) return launch_gemm_tok<256, PRO, EPI>(A, W, p, K, pl, pdl, s);
     if (pl.BN == 128) return launch_gemm_tok<128, PRO, EPI>(A, W, p, K, pl, pdl, s);

@@ -3,9 +3,10 @@ denoise path, backed by the sm_100a C-ABI library.
 
 Same names and argument order; every pointer is a Python ``int`` holding a device address.  The 16-bit
 activation type of this library is **bf16** (the reference's Pi0.5 NVFP4 decoder keeps an fp16 residual
-stream, its GR00T path a bf16 one): the ``*_bf16`` names are the native ones, and the reference's ``*_fp16``
-names are provided as aliases that read / write bf16 buffers -- a caller that hands them fp16 data gets
-wrong results, which is why ``STREAM_DTYPE`` is exported for frontends to check.
+stream, its GR00T path a bf16 one): the ``*_bf16`` names are the native ones.  The reference's ``*_fp16`` names
+exist too, but pointers carry no type and an fp16 buffer read as bf16 gives silently wrong numbers, so every
+``*_fp16`` name REFUSES (:class:`NotBuilt`) unless the caller states ``io_dtype="bf16"`` -- i.e. that the buffers it
+passes hold bf16 -- and ``STREAM_DTYPE`` is exported for frontends to check before they allocate.
 
 Functions that return ``int`` in the reference return the C-ABI status (0 = success); ``void`` ones raise
 :class:`flashrt_b200._lib.KernelError`.  One GEMM kernel serves every ``variant`` index.
@@ -20,6 +21,26 @@ from .flash_rt_kernels import NotBuilt, _f
 
 STREAM_DTYPE = "bfloat16"
 FAMILY = 1      # flash_rt_fp4 convention: RN-even E4M3 block scale, '<=' thresholds
+
+
+def _fp16_name(fn, name: str):
+    """The reference binding ``name`` (fp16 buffers there) served by the bf16 kernel ``fn``: callable only with
+    ``io_dtype="bf16"``, the caller's statement that its 16-bit buffers hold bf16."""
+    def wrapper(*args, io_dtype=None, **kw):
+        if io_dtype != "bf16":
+            raise NotBuilt(f"flash_rt_fp4.{name}: this library's 16-bit activations are bf16; an fp16 buffer would be "
+                           f"mis-read.  Allocate bf16 buffers and call {fn.__name__}, or pass io_dtype=\"bf16\" to "
+                           f"state that the buffers hold bf16 (STREAM_DTYPE = {STREAM_DTYPE!r}).")
+        return fn(*args, **kw)
+    import inspect
+    sig = inspect.signature(fn)
+    params = [q for q in sig.parameters.values() if q.kind != q.VAR_KEYWORD]
+    params.append(inspect.Parameter("io_dtype", inspect.Parameter.KEYWORD_ONLY, default=None))
+    params += [q for q in sig.parameters.values() if q.kind == q.VAR_KEYWORD]
+    wrapper.__signature__ = sig.replace(parameters=params)     # same positional names and order as the reference binding
+    wrapper.__name__ = name
+    wrapper.__doc__ = f"``{name}`` of csrc/fp4_bindings.cpp on bf16 buffers (requires io_dtype=\"bf16\"); see {fn.__name__}."
+    return wrapper
 
 
 def has_nvfp4() -> bool:                                   # csrc/fp4_bindings.cpp:466
@@ -47,22 +68,25 @@ def quantize_fp4_dynamic_sfa_bf16_vec(src, packed, sfa, N, D, is_sfb=False, stre
                        _f(pdl), stream)
 
 
-quantize_fp4_dynamic_sfa_fp16 = quantize_fp4_dynamic_sfa_bf16_vec       # csrc/fp4_bindings.cpp:299-315
-quantize_fp4_dynamic_sfa_fp16_vec = quantize_fp4_dynamic_sfa_bf16_vec   # csrc/fp4_bindings.cpp:317-333
+quantize_fp4_dynamic_sfa_fp16 = _fp16_name(quantize_fp4_dynamic_sfa_bf16_vec, "quantize_fp4_dynamic_sfa_fp16")       # csrc/fp4_bindings.cpp:299-315
+quantize_fp4_dynamic_sfa_fp16_vec = _fp16_name(quantize_fp4_dynamic_sfa_bf16_vec, "quantize_fp4_dynamic_sfa_fp16_vec")   # csrc/fp4_bindings.cpp:317-333
 
 
 def gate_geglu_fp4_sfa_vec_bf16(merged, packed, sfa, seq_len, half_dim, stream=0, *, pdl=False) -> int:
     return call_status("frt_b200_geglu_nvfp4", merged, packed, sfa, seq_len, half_dim, FAMILY, _f(pdl), stream)
 
 
-gate_geglu_fp4_sfa_vec_fp16 = gate_geglu_fp4_sfa_vec_bf16               # csrc/fp4_bindings.cpp:739-753
+gate_geglu_fp4_sfa_vec_fp16 = _fp16_name(gate_geglu_fp4_sfa_vec_bf16, "gate_geglu_fp4_sfa_vec_fp16")               # csrc/fp4_bindings.cpp:739-753
 
 
-def gate_geglu_fp4_sfa_fp16(merged, packed, sfa, seq_len, half_dim, stream=0, *, pdl=False):   # :711-723
+def gate_geglu_fp4_sfa_bf16(merged, packed, sfa, seq_len, half_dim, stream=0, *, pdl=False):   # :711-723
     call("frt_b200_geglu_nvfp4", merged, packed, sfa, seq_len, half_dim, FAMILY, _f(pdl), stream)
 
 
-gate_geglu_fp4_sfa_v2_fp16 = gate_geglu_fp4_sfa_fp16                    # csrc/fp4_bindings.cpp:725-737
+gate_geglu_fp4_sfa_fp16 = _fp16_name(gate_geglu_fp4_sfa_bf16, "gate_geglu_fp4_sfa_fp16")
+
+
+gate_geglu_fp4_sfa_v2_fp16 = _fp16_name(gate_geglu_fp4_sfa_bf16, "gate_geglu_fp4_sfa_v2_fp16")                    # csrc/fp4_bindings.cpp:725-737
 
 
 # ------------------------------------------------------------------ fused norms -> NVFP4
@@ -83,26 +107,32 @@ def pi05_gate_res_adarms_fp4_sfa_bf16(x, prev_gate, residual, style, packed, sfa
          dim, eps, FAMILY, _f(pdl), stream)
 
 
-pi05_adarms_fp4_sfa_fp16 = pi05_adarms_fp4_sfa_bf16                              # :547-570
-pi05_adarms_fp4_sfa_native_fp16 = pi05_adarms_fp4_sfa_bf16                       # :602-625
-pi05_gate_res_adarms_fp4_sfa_fp16 = pi05_gate_res_adarms_fp4_sfa_bf16            # :572-600
-pi05_gate_res_adarms_fp4_sfa_native_fp16 = pi05_gate_res_adarms_fp4_sfa_bf16     # :627-657
+pi05_adarms_fp4_sfa_fp16 = _fp16_name(pi05_adarms_fp4_sfa_bf16, "pi05_adarms_fp4_sfa_fp16")                              # :547-570
+pi05_adarms_fp4_sfa_native_fp16 = _fp16_name(pi05_adarms_fp4_sfa_bf16, "pi05_adarms_fp4_sfa_native_fp16")                       # :602-625
+pi05_gate_res_adarms_fp4_sfa_fp16 = _fp16_name(pi05_gate_res_adarms_fp4_sfa_bf16, "pi05_gate_res_adarms_fp4_sfa_fp16")            # :572-600
+pi05_gate_res_adarms_fp4_sfa_native_fp16 = _fp16_name(pi05_gate_res_adarms_fp4_sfa_bf16, "pi05_gate_res_adarms_fp4_sfa_native_fp16")     # :627-657
 
 
-def rms_norm_fp4_sfa_fp16(x, packed, sfa, seq_len, dim, stream=0, *, weight=0, pdl=False, eps=1e-6):   # :501-513
+def rms_norm_fp4_sfa_bf16(x, packed, sfa, seq_len, dim, stream=0, *, weight=0, pdl=False, eps=1e-6):   # :501-513
     # the reference's kernel has no weight operand (the norm weight is folded into the next projection); `weight`
     # is an extension of this library
     call("frt_b200_norm_nvfp4", x, None, None, 0, weight or None, None, 0, packed, sfa, None, seq_len, dim, eps,
          FAMILY, _f(pdl), stream)
 
 
-def residual_add_rms_norm_fp4_sfa_fp16(residual, x, packed, sfa, seq_len, dim, stream=0, *, weight=0, pdl=False,
+rms_norm_fp4_sfa_fp16 = _fp16_name(rms_norm_fp4_sfa_bf16, "rms_norm_fp4_sfa_fp16")
+
+
+def residual_add_rms_norm_fp4_sfa_bf16(residual, x, packed, sfa, seq_len, dim, stream=0, *, weight=0, pdl=False,
                                        eps=1e-6):                                                    # :531-545
     call("frt_b200_norm_nvfp4", residual, x, None, 0, weight or None, None, 0, packed, sfa, None, seq_len, dim,
          eps, FAMILY, _f(pdl), stream)
 
 
-residual_add_rms_norm_fp4_sfa_v2_fp16 = residual_add_rms_norm_fp4_sfa_fp16                           # :515-529
+residual_add_rms_norm_fp4_sfa_fp16 = _fp16_name(residual_add_rms_norm_fp4_sfa_bf16, "residual_add_rms_norm_fp4_sfa_fp16")
+
+
+residual_add_rms_norm_fp4_sfa_v2_fp16 = _fp16_name(residual_add_rms_norm_fp4_sfa_bf16, "residual_add_rms_norm_fp4_sfa_v2_fp16")                           # :515-529
 
 
 # ------------------------------------------------------------------ GEMM
@@ -115,8 +145,11 @@ def cutlass_fp4_gemm_variant(idx, A, SFA, B, SFB, D, M, N, K, alpha=1.0, beta=0.
                        _f(pdl) | (2 if one_tile_per_cta else 0), stream)
 
 
-def cutlass_fp4_sq_fp16(A, SFA, B, SFB, D, M, N, K, alpha=1.0, beta=0.0, stream=0, **kw) -> int:   # :85-99
+def cutlass_fp4_sq_bf16(A, SFA, B, SFB, D, M, N, K, alpha=1.0, beta=0.0, stream=0, **kw) -> int:   # :85-99
     return cutlass_fp4_gemm_variant(0, A, SFA, B, SFB, D, M, N, K, alpha, beta, stream, **kw)
+
+
+cutlass_fp4_sq_fp16 = _fp16_name(cutlass_fp4_sq_bf16, "cutlass_fp4_sq_fp16")
 
 
 def cutlass_fp4_gemm_bias_bf16(A, SFA, B, SFB, bias, D, M, N, K, stream=0, *, pdl=False, splits=0) -> int:

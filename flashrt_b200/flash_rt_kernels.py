@@ -306,10 +306,13 @@ class GemmRunner:
         call("frt_b200_gemm_fp8_nt_geglu_fp8", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, splits,
              _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
 
-    def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, **kw):
-        raise NotBuilt(
-            "fp8_nn_dev (weights stored (K,N)) is not provided: this library keeps FP8 weights K-contiguous "
-            "(N,K); use fp8_nt_dev, the reference's own fp8_layout='nk' path (csrc/bindings.cpp:717-727)")
+    def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
+                   tile_n=0):
+        """D(M,N) bf16 = sa*sb * A(M,K) . B(K,N) — weights stored (K,N), the reference's default ``fp8_layout == "kn"``
+        form (csrc/bindings.cpp:706-716).  Same result as ``fp8_nt_dev`` on the transposed weights.  K % 128 == 0,
+        N % 16 == 0, N >= 128."""
+        call("frt_b200_gemm_fp8_nn", A, B, D, M, N, K, d_scale_a, d_scale_b, 1.0, bias, splits,
+             _f(pdl) | _tile_hint(tile_n), stream)
 
     def bf16_nn(self, A, B, D, M, N, K, stream=0, *, pdl=False, bias=None, accumulate=False, a_f32=False,
                 d_f32=False):

@@ -103,7 +103,7 @@ def _finish_spec(dec: LayerBlock, dp: str, layers: int, num_steps: int) -> Model
 
 def synthetic_state_dict(seed: int = 0, layers: int = DEC_L) -> dict:
     """Random-init checkpoint with the HF key names and shapes of the Pi0.5 action expert
-    (matrices ~ N(0, 0.02), biases zero) — stands in for a trained checkpoint, which this build cannot reach."""
+    (matrices ~ N(0, 0.02), biases zero) — the stand-in for a trained checkpoint in tests and benchmarks."""
     g = torch.Generator().manual_seed(seed)
 
     def w(*shape):
@@ -773,6 +773,11 @@ class Pi05DecoderB200:
         with torch.cuda.stream(self.stream):
             self._pinned_out.copy_(self._dev_out, non_blocking=True)
         self.stream.synchronize()
+        # a bounded device-side wait that gave up leaves a status word and garbage actions: never return those
+        status = fvk.tensor_core_status()
+        if status != 0:
+            raise fvk.KernelError(f"a tensor-core kernel of the denoise loop gave up a bounded wait (status {status:#x}); "
+                                  "the actions of this call are invalid")
         return {"actions": self._pinned_out.numpy().reshape(shape).copy()}
 
     def kernels_per_loop(self) -> int:

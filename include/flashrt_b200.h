@@ -115,6 +115,13 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
                          const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
                          void* stream);
+/* GemmRunner::fp8_nn_dev (csrc/bindings.cpp:706-716 -> csrc/gemm/gemm_runner.cu:67-76), the reference's default weight
+ * layout: B stored (K, N) row-major.  D(M,N) bf16 = alpha_host * (*d_scale_a) * (*d_scale_b) * A(M,K) . B(K,N) + bias.
+ * The weight tiles are loaded as 128 K-rows x 128 N-bytes and consumed as an MN-major MMA operand; the result equals
+ * frt_b200_gemm_fp8_nt on the transposed weights bit for bit.  K % 128 == 0, N % 16 == 0, N >= 128. */
+int frt_b200_gemm_fp8_nn(const void* A, const void* B, void* D, int M, int N, int K, const float* d_scale_a,
+                         const float* d_scale_b, float alpha_host, const void* bias, int splits, int flags,
+                         void* stream);
 /* The same GEMM (M <= 256) with the kernel that follows it in the decoder fused into its epilogue.
  *
  * QKV projection + qkv_split_rope[_devpos] (csrc/bindings.cpp:1071-1099 -> csrc/kernels/rope.cu:135-277):
@@ -179,6 +186,12 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
                                                void* stream);
 /* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
 int frt_b200_attention_status(int reset);
+/* Diagnostics, no counterpart in the reference: device-timer (%globaltimer, ns) phase stamps of the last 8 launches of
+ * the token-major small-M GEMM (gemm_host: 8 launches x 160 CTAs x 16 stamps) and of the head_dim-256 attention kernel
+ * (attn_host: 8 x 64 x 16); either pointer may be NULL.  Recorded only by a library built with -DFRT_PHASE_STAMPS
+ * (FRT_NVCC_EXTRA=-DFRT_PHASE_STAMPS python -m flashrt_b200._build --force); a regular build returns -2.
+ * reset != 0 restarts the launch slots and clears the stamps after copying them out.  Synchronises the device. */
+int frt_b200_phase_stamps_read(unsigned long long* gemm_host, unsigned long long* attn_host, int reset);
 
 /* ---------------------------------------------------------------- video-DiT (Wan-shape) fused producers
  * ada_layer_norm_fp8                 csrc/bindings.cpp:3482-3495 -> csrc/quantize/ada_layer_norm_fp8.cu:58-147

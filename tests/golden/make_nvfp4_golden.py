@@ -54,7 +54,9 @@ def inputs():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and "FLASHRT_REFERENCE" not in os.environ:
+        raise SystemExit("usage: make_nvfp4_golden.py <path to a FlashRT checkout>  (or FLASHRT_REFERENCE=<path>)")
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ["FLASHRT_REFERENCE"]
     fake_nvfp4 = load_reference(ref_root)
     out = {}
     for name, x in inputs().items():

@@ -46,7 +46,9 @@ def args_of(text: str, name: str):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and "FLASHRT_REFERENCE" not in os.environ:
+        raise SystemExit("usage: make_surface_golden.py <path to a FlashRT checkout>  (or FLASHRT_REFERENCE=<path>)")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["FLASHRT_REFERENCE"]
     out = {}
     for module, (path, names) in WANTED.items():
         text = open(os.path.join(ref, path)).read()

@@ -37,7 +37,9 @@ def inputs():
 
 
 def main():
-    sys.path.insert(0, os.environ.get("FLASHRT_REFERENCE", "/root/reference"))
+    if "FLASHRT_REFERENCE" not in os.environ:
+        raise SystemExit("set FLASHRT_REFERENCE=<path to a FlashRT checkout>")
+    sys.path.insert(0, os.environ["FLASHRT_REFERENCE"])
     from flash_rt.structures.catalog.modnorm_qkv_chain.reference import modnorm_qkv_chain_ref
     from flash_rt.structures.catalog.norm_fused.reference import norm_fused_ref
     from flash_rt.structures.catalog.qk_norm_rope.reference import qk_norm_rope_ref

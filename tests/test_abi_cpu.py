@@ -49,14 +49,14 @@ def test_shim_mirrors_reference_binding_names():
               "gpu_copy", "quantize_fp8_static", "quantize_fp8_device", "fp8_accumulate_scale_max",
               "fp8_gemm_descale_bf16out", "GemmRunner", "has_cutlass_sm100", "get_sm_version"):
         assert callable(getattr(fvk, n)), n
-    for n in ("fp8_nt_dev", "bf16_nn", "autotune_fp8_nn_dev", "autotune_bf16_nn"):
+    for n in ("fp8_nt_dev", "fp8_nn_dev", "bf16_nn", "autotune_fp8_nn_dev", "autotune_bf16_nn"):
         assert callable(getattr(fvk.GemmRunner, n)), n
     for n in ("fwd_bf16", "fwd_bf16_seqused", "fwd_bf16_seqused_splitkv"):
         assert callable(getattr(flash_rt_fa2, n)), n
     assert not hasattr(fvk, "silu_mul_split_fp8_fp16")        # outside the path: refused, not faked
     import pytest
     with pytest.raises(fvk.NotBuilt):
-        fvk.GemmRunner().fp8_nn_dev(0, 0, 0, 1, 1, 16, 0, 0)
+        fvk.GemmRunner().bf16_nn(0, 0, 0, 128, 128, 128)      # only the 32 <-> 1024 action projections are on the path
 
 
 def test_stand_in_modules_accept_the_reference_binding_signatures():
@@ -155,3 +155,16 @@ def test_expert_loop_entry_points_validate_before_touching_the_device():
     assert lib.frt_b200_expert_loop_fp8(None, ctypes.sizeof(a), None) == -1
     assert lib.frt_b200_expert_loop_fp8(ctypes.addressof(a), ctypes.sizeof(a) - 8, None) == -1   # struct size mismatch
     assert lib.frt_b200_expert_loop_fp8(ctypes.addressof(a), ctypes.sizeof(a), None) == -1       # null pointers
+
+
+def test_fp16_named_fp4_entries_refuse_without_a_stated_dtype():
+    """The reference's ``*_fp16`` bindings take fp16 buffers; here the 16-bit type is bf16 and a pointer carries no type,
+    so those names refuse unless the caller states that its buffers hold bf16."""
+    import pytest
+    from flashrt_b200 import flash_rt_fp4 as fp4
+    from flashrt_b200.flash_rt_kernels import NotBuilt
+    assert fp4.STREAM_DTYPE == "bfloat16"
+    for name in ("pi05_adarms_fp4_sfa_fp16", "quantize_fp4_dynamic_sfa_fp16", "rms_norm_fp4_sfa_fp16",
+                 "residual_add_rms_norm_fp4_sfa_v2_fp16", "gate_geglu_fp4_sfa_fp16", "cutlass_fp4_sq_fp16"):
+        with pytest.raises(NotBuilt, match="bf16"):
+            getattr(fp4, name)(0, 0, 0, 0, 0, 0, 0, 0, 0)

@@ -217,3 +217,32 @@ def test_refusals():
     with pytest.raises(KernelError):       # K-slice that cannot stay resident
         g.norm_fp8_nt_dev_geglu_fp8(z.ptr, z.ptr, 4, z.ptr, z.ptr, z.ptr, 50, 4096, 4096, z.ptr, z.ptr, z.ptr, 0,
                                     splits=2)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(50, 2560, 1024, 0), (50, 1024, 2048, 4), (16, 8192, 1024, 0), (128, 1024, 4096, 8),
+                                          (200, 3072, 3072, 0), (1, 256, 128, 1), (2048, 1024, 1024, 0),
+                                          (1000, 384, 512, 0), (8192, 3072, 3072, 0), (300, 14336, 3072, 0)])
+def test_fp8_nn_dev_kn_weights_equal_nt_on_the_transpose(M, N, K, splits):
+    """GemmRunner.fp8_nn_dev -- weights stored (K, N), the reference's default layout -- gives the bytes of fp8_nt_dev on
+    the transposed weights (same kernel, same accumulation order; only the operand descriptor differs), and both
+    agree with the fp64 oracle."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, rand_bf16, zeros
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, N, K, 0.02)
+    bias = rand_bf16(rng, (N,), 0.2)
+    d_A, d_W, d_Wt, d_b = Dev(A), Dev(W), Dev(np.ascontiguousarray(W.T)), Dev(bias)
+    d_sa, d_sb = f32(sa), f32(sb)
+    d_nt, d_nn = zeros((M, N), np.uint16), zeros((M, N), np.uint16)
+    g = fvk.GemmRunner()
+    tile = 128 if (M <= 256 and N % 256) else (256 if M <= 256 else 0)
+    if M <= 256:
+        g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_nt.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits, bias=d_b.ptr, tile_n=tile)
+        g.fp8_nn_dev(d_A.ptr, d_Wt.ptr, d_nn.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, splits=splits, bias=d_b.ptr, tile_n=tile)
+    else:
+        g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_nt.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr, cta_pair=False)
+        g.fp8_nn_dev(d_A.ptr, d_Wt.ptr, d_nn.ptr, M, N, K, d_sa.ptr, d_sb.ptr, 0, bias=d_b.ptr)
+    assert fvk.tensor_core_status() == 0
+    _check(d_nn.get(), _ref(A, W, sa, sb, bias))
+    assert np.array_equal(d_nt.get(), d_nn.get())
