@@ -91,8 +91,8 @@ def cpu_reference_loop(steps: int, warmup: int, layers: int = 18, inputs=None):
     import torch
     from oracle import block_ref as R
     from flashrt_b200.pi05_decoder import synthetic_state_dict
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
+    torch.set_num_threads(os.cpu_count() or 1)    # a launcher may have exported OMP_NUM_THREADS=1
+    cores = torch.get_num_threads()
     sd = synthetic_state_dict(0, layers)
     ck = R.from_hf_state_dict({k: v.to(torch.bfloat16).float() for k, v in sd.items()}, layers)
     if inputs is None:
@@ -218,7 +218,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
 
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import ACTION_DIM
@@ -285,30 +285,66 @@ def run_ours(args):
 
     from flashrt_b200 import flash_rt_kernels as fvk
     status = fvk.tensor_core_status()
-    line = None
-    if rank == 0 and args.lean:
-        print(json.dumps({"metric": METRIC, "value": round(ms, 4), "unit": "ms", "lean": True,
-                          "e2e_ms": round(e2e_ms, 4), "tensor_core_status": status}), flush=True)
-    elif rank == 0:
-        peak, peak_src = _peaks()
+    if args.lean:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": round(ms, 4), "unit": "ms", "lean": True,
+                              "e2e_ms": round(e2e_ms, 4), "tensor_core_status": status}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    M = fe.batch * fe.chunk_size
+    kernels_per_loop, num_steps, batch, use_pdl = fe.kernels_per_loop(), fe.num_steps, fe.batch, fe.use_pdl
+    gemm_us = gemm_bytes = None
+    if rank == 0:
         gemm_us, gemm_bytes, _ = gemm_roofline(fe)
-        M = fe.batch * fe.chunk_size
+    # ---- the other configurations of the benchmark definition, measured after the headline (never inside it).
+    # Whether an extra runs is decided on rank 0 and told to every rank: the video-DiT step is a collective.
+    extras = {}
+    if not args.no_extras:
+        del model, fe
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        go = torch.tensor([1 if time.perf_counter() - t_start < args.extras_budget_s else 0], device=f"cuda:{local}")
+        if world > 1:
+            dist.broadcast(go, src=0)
+        if int(go[0]):
+            try:
+                w = measure_wan(args, rank, world, local, steps=3, warm=1)
+                extras["video_dit"] = {"ms": w["ms"], "e2e_ms": w["e2e_ms"], "tp": world, "layers": w["layers"],
+                                       "frac_weighted": w["frac_weighted"], "finite": w["finite"],
+                                       "tensor_core_status": w["status"], "launches_per_step": w["launches"]}
+            except Exception as e:  # noqa: BLE001
+                extras["video_dit"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+        else:
+            extras["video_dit"] = {"skipped": "time budget of the default run"}
+        if world == 1 and rank == 0:
+            for name, fn in (("ops", lambda: ops_summary(args)), ("nvfp4", lambda: nvfp4_summary(args, local))):
+                if time.perf_counter() - t_start > args.extras_budget_s:
+                    extras[name] = {"skipped": "time budget of the default run"}
+                    continue
+                try:
+                    extras[name] = fn()
+                except Exception as e:  # noqa: BLE001
+                    extras[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
+    if rank == 0:
+        peak, peak_src = _peaks()
         gemm_out_bytes = 2 * M * (2560 + 1024 + 8192 + 1024) / 4
         achieved = gemm_bytes / (gemm_us * 1e-6) / 1e9
         # algorithmic HBM bytes of one loop: weights (FP8: 1 byte, NVFP4: 0.5625 byte per element with the
         # block scales) + prefix/fresh KV per layer per step (per batch element)
         wbytes = 17301504 * (0.5625 if nv else 1.0)
-        loop_bytes = int(fe.num_steps * L * (wbytes + fe.batch * 2 * (P + fe.chunk_size) * 256 * 2))
+        loop_bytes = int(num_steps * L * (wbytes + batch * 2 * (P + M // batch) * 256 * 2))
         # the CPU port of the reference math on the SAME prefix and noise: the baseline time, and the check that the
-        # timed output is right
-        cpu_ms, cores, ref = cpu_reference_loop(3, 1, L, inputs=(prefix_k, prefix_v, noise_t if fe.batch == 1 else noise_t[0]))
-        got = torch.from_numpy(out if fe.batch == 1 else out[0]).double().flatten()
+        # timed output is right (last, so that no other rank waits on it)
+        cpu_ms, cores, ref = cpu_reference_loop(3, 1, L, inputs=(prefix_k, prefix_v, noise_t if batch == 1 else noise_t[0]))
+        got = torch.from_numpy(out if batch == 1 else out[0]).double().flatten()
         refd = ref.double().flatten()
         rms = float(refd.pow(2).mean().sqrt())
         parity = {"cosine": round(float(got @ refd / (got.norm() * refd.norm())), 6),
                   "max_abs_over_rms": round(float((got - refd).abs().max()) / rms, 4),
                   "rms_err_over_rms": round(float((got - refd).pow(2).mean().sqrt()) / rms, 4),
-                  "layers": L, "steps": fe.num_steps,
+                  "layers": L, "steps": num_steps,
                   "against": "fp32 torch oracle (oracle.block_ref.denoise_loop) on the same weights, prefix and noise"}
         line = {
             "metric": METRIC, "value": round(ms, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
@@ -317,16 +353,16 @@ def run_ours(args):
             "dtype": ("nvfp4_e2m1 (ue4m3 block scales, fp32 accumulate, bf16 residual stream)" if nv
                       else "fp8_e4m3 (fp32 accumulate, bf16 residual stream)"),
             "data": "synthetic",
-            "config": {"workload": (WORKLOAD_NVFP4 % fe.batch) if nv else WORKLOAD,
+            "config": {"workload": (WORKLOAD_NVFP4 % batch) if nv else WORKLOAD,
                        "parallelism": f"replicas x{world} (no collective)",
                        "l2": ("working set %d MB per Euler step exceeds the 126 MB L2; no explicit flush"
-                              % (loop_bytes // fe.num_steps // 1000000)),
-                       "kernels_per_loop": fe.kernels_per_loop(), "pdl": fe.use_pdl,
+                              % (loop_bytes // num_steps // 1000000)),
+                       "kernels_per_loop": kernels_per_loop, "pdl": use_pdl,
                        "calibration_samples": args.calib_samples,
                        "tensor_core_status": status, "actions_finite": bool((out == out).all())},
             "e2e": {"value": round(e2e_ms, 4), "unit": "ms", "h2d_bytes_per_step": int(noise.nbytes),
                     "d2h_bytes_per_step": int(out.nbytes)},
-            "gpu_launches": fe.kernels_per_loop() * args.steps,
+            "gpu_launches": kernels_per_loop * args.steps,
             "aggregate_loops_per_s": round(world * 1e3 / ms, 2),
             "p50_ms": round(_pctl(per, 0.5), 4), "p95_ms": round(_pctl(per, 0.95), 4),
             "parity": parity,
@@ -347,34 +383,7 @@ def run_ours(args):
                              "sample": "3 full 10-step loops of the fp32 torch oracle, median"},
             "clocks": clocks,
         }
-    # ---- the other configurations of the benchmark definition, measured after the headline (never inside it)
-    if not args.lean and not args.no_extras:
-        del model, fe
-        import gc
-        gc.collect()
-        torch.cuda.empty_cache()
-        budget = args.extras_budget_s
-        extras = {}
-        if time.perf_counter() - t_start < budget:
-            try:
-                w = measure_wan(args, rank, world, local, steps=3, warm=1)
-                extras["video_dit"] = {"ms": w["ms"], "e2e_ms": w["e2e_ms"], "tp": world, "layers": w["layers"],
-                                       "frac_weighted": w["frac_weighted"], "finite": w["finite"],
-                                       "tensor_core_status": w["status"], "launches_per_step": w["launches"]}
-            except Exception as e:  # noqa: BLE001
-                extras["video_dit"] = {"error": f"{type(e).__name__}: {e}"[:200]}
-        if world == 1 and rank == 0:
-            for name, fn in (("ops", lambda: ops_summary(args)), ("nvfp4", lambda: nvfp4_summary(args, local))):
-                if time.perf_counter() - t_start > budget:
-                    extras[name] = {"skipped": "time budget of the default run"}
-                    continue
-                try:
-                    extras[name] = fn()
-                except Exception as e:  # noqa: BLE001
-                    extras[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
-        if line is not None:
-            line.update(extras)
-    if rank == 0 and line is not None:
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -523,7 +532,7 @@ def run_wan(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
     steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
     w = measure_wan(args, rank, world, local, steps, warm)
     if rank == 0:
