@@ -916,10 +916,12 @@ static inline int tok_bn_hint(int flags) {
 static inline int tok_split_hint(int splits) {
     return (splits == 1 || splits == 2 || splits == 4 || splits == 8) ? splits : 0;
 }
-// the token-major kernel serves M <= 256 rows, K in whole 128-byte k-blocks, 16-byte output rows; flags bit 4 keeps
-// the swapped (weights-on-lanes) kernel
-static inline bool tok_eligible(int M, int N, int K, int flags) {
-    return M <= 256 && (K % 128) == 0 && (N % 8) == 0 && !(flags & 16);
+// the token-major kernel serves up to 128 rows (one accumulator tile: the weights stream once), K in whole 128-byte
+// k-blocks, 16-byte output rows; flags bit 4 keeps the swapped (weights-on-lanes) kernel.  With a pinned tile width or
+// split it also takes 129..256 rows (two row tiles; measured slower than the swapped kernel there).
+static inline bool tok_eligible(int M, int N, int K, int flags, int splits = 0) {
+    const bool pinned = ((flags >> 8) & 3) != 0 || splits == 1 || splits == 2 || splits == 4 || splits == 8;
+    return (M <= 128 || (M <= 256 && pinned)) && (K % 128) == 0 && (N % 8) == 0 && !(flags & 16);
 }
 
 extern "C" {
@@ -946,7 +948,7 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     p.kb_total = (K + 127) / 128;
     cudaStream_t s = (cudaStream_t)stream;
     bool pdl = flags & 1;
-    if (tok_eligible(M, N, K, flags)) {
+    if (tok_eligible(M, N, K, flags, splits)) {
         TokParams t = {};
         t.M = M; t.N = N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = alpha_host;
         t.out = (__nv_bfloat16*)D; t.bias = (const __nv_bfloat16*)bias;

@@ -109,7 +109,7 @@ int frt_b200_qkv_split_rope(const void* qkv, const void* rope, void* Q, void* K,
  *   tile lists of at least two waves with K >= 2048 (or flags bit 3; M > 256, N >= 256, no split-K) run a kernel with
  *   one 256 x 256 tile per CTA pair (tcgen05 cta_group::2: each CTA stages its 128 rows of A and 128 of the 256 weight
  *   rows, the leader issues the MMAs for both); flags bit 5 keeps the one-CTA persistent kernel.
- *   M <= 256 with K % 128 == 0 and N % 8 == 0 runs the token-major kernel (activation rows on the 128 accumulator
+ *   M <= 128 (up to 256 with a pinned tile width or split) with K % 128 == 0 and N % 8 == 0 runs the token-major kernel (activation rows on the 128 accumulator
  *   lanes, up to 256 weight rows on the columns, split-K in {1, 2, 4, 8} over a cluster); flags bit 4 keeps the
  *   swapped kernel (weights on the lanes) instead; flags bits 8-9 pin the tile width (1 = 64, 2 = 128, 3 = 256). */
 int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, int K, const float* d_scale_a,
