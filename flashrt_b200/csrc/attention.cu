@@ -109,7 +109,7 @@ struct AttnParams {
     // split-KV through global scratch (same buffers and layouts as the reference's FA2 split-kv path):
     float* o_accum;              // (splits, B, Hq, Sq, D) fp32, each split's O already divided by its row sum
     float* lse_accum;            // (splits, B, Hq, Sq) fp32, log2-domain log-sum-exp of the split (-inf if empty)
-    unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals, readers; zero before first use
+    unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals (monotonic), spare; zero before first use
     float scale_log2;            // softmax_scale * log2(e)
     int flags;                   // the entry point's flags (bit 2: keep one CTA per (tile, split) in the head_dim-256 kernel)
 #ifdef FRT_PHASE_STAMPS
@@ -184,6 +184,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const bool via_scratch = p.o_accum != nullptr;
     const uint32_t C = via_scratch ? gridDim.z : tc::cluster_nctarank();
     const uint32_t rank = via_scratch ? blockIdx.z : tc::cluster_ctarank();
+    unsigned cnt_base = 0;       // thread 0, scratch path: the tile's arrival count when this launch started
     const int tile = blockIdx.x;
     const int hk = blockIdx.y % p.Hkv;
     const int b = blockIdx.y / p.Hkv;
@@ -281,6 +282,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     } else if (warp < 4) {
         // ---------------- softmax: thread = row (TMEM lane 32*warp + lane)
         pdl_wait();
+        if (via_scratch && threadIdx.x == 0) {
+            // The tile's arrival counter only ever grows, by 256 per launch (each of its C CTAs adds 256 / C, whatever
+            // C is, so launches of different shapes may share a counter); every earlier launch has completed here and
+            // this CTA has not arrived yet, so rounding down to a multiple of 256 gives the count this launch started from.
+            const unsigned tid = (unsigned)((b * p.Hkv + hk) * gridDim.x + tile);
+            unsigned seen;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.counters + 2 * tid) : "memory");
+            cnt_base = seen & ~255u;
+        }
         int kv_len = p.Skv;
         if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
         const int row = warp * 32 + lane;
@@ -438,12 +448,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
-            atomicAdd(cnt, 1u);
+            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(256u / C) : "memory");
             bool ok = false;
             for (uint32_t it = 0;; ++it) {
                 unsigned seen;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
-                if (seen >= C) { ok = true; break; }
+                if (seen - cnt_base >= 256u) { ok = true; break; }
                 if (*abort_flag) break;
                 if ((it & 15) == 15 && tc::global_timer_ns() > deadline) break;
                 __nanosleep(20);
@@ -509,12 +519,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (p.lse && rank == 0 && ch == 0)
                     p.lse[r0] = (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
             }
-        }
-        // the last CTA of the tile to finish reading re-arms the counters for the next launch
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned done = atomicAdd(cnt + 1, 1u);
-            if (done == C - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
         }
         tc::tc_fence_before_sync();
         __syncthreads();
@@ -696,8 +700,8 @@ extern "C" {
 // (they may be fetched before that kernel finishes when flags bit0 is set); 0 if unsure.
 // o_accum / lse_accum / counters: optional split-KV scratch, all three or none.  o_accum (splits, batch, heads_q,
 // seqlen_q, head_dim) fp32, lse_accum (splits, batch, heads_q, seqlen_q) fp32 (the reference's FA2 split-kv
-// buffers), counters: 2 unsigned per (128-row tile, kv head, batch), zeroed once by the caller (the kernel re-arms
-// them).  With scratch the kv splits are ordinary CTAs that combine through global memory (faster than the
+// buffers), counters: 2 unsigned per (128-row tile, kv head, batch), zeroed once by the caller (a tile's count only
+// grows, by 256 per launch; a launch reads where it starts).  With scratch the kv splits are ordinary CTAs that combine through global memory (faster than the
 // cluster exchange at the action-expert shape); the grid must fit the device in one wave (else -2).
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
@@ -792,7 +796,7 @@ static void* g_attn_static_ptr[64] = {nullptr};
 // array's device address (cudaGetSymbolAddress) and clears the arrival counters with a memset enqueued on the
 // caller's stream in front of the kernel: make that first call before any stream capture (inside a capture it is
 // refused with -1).  Every call uses the same array, which keeps whatever the previous call left in it (the kernel
-// overwrites the partials it reads and re-arms the counters itself), so two calls whose kernels can overlap on the
+// overwrites the partials it reads and its arrival counters only ever grow), so two calls whose kernels can overlap on the
 // GPU -- different streams, or graph branches -- would corrupt each other.  After a call whose bounded wait gave up
 // (frt_b200_attention_status != 0) the counters are stale: frt_b200_attention_status(1) clears them as well.
 int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, const void* V, void* O, void* O_fp8,

@@ -95,6 +95,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int c_begin = (int)((long long)p.chunks_total * rank / C);
     const int c_end = (int)((long long)p.chunks_total * (rank + 1) / C);
     const int nchunks = c_end - c_begin;
+    unsigned cnt_base = 0;                                          // thread 0, scratch path
 
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
@@ -204,6 +205,15 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     } else if (warp < 4) {
         // ---------------- softmax: thread = row
         pdl_wait();
+        if (via_scratch && threadIdx.x == 0) {
+            // Arrival counter of this tile: it only ever grows, by 256 per launch (each of the C * DQ CTAs adds
+            // 256 / (C * DQ)).  Every earlier launch has completed here and this CTA has not arrived yet, so rounding
+            // down to a multiple of 256 gives the count this launch started from.
+            const unsigned tid = (unsigned)((b * p.Hkv + hk) * ntiles + tile);
+            unsigned seen;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.counters + 2 * tid) : "memory");
+            cnt_base = seen & ~255u;
+        }
         int kv_len = p.Skv;
         if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
         const int row = warp * 32 + lane;
@@ -420,12 +430,13 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncthreads();
         ATT_STAMP(9);
         if (threadIdx.x == 0) {
-            atomicAdd(cnt, 1u);
+            // arrive without waiting for the old value (the partial was fenced above), then poll
+            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(256u / arrivals) : "memory");
             bool ok = false;
             for (uint32_t it = 0;; ++it) {
                 unsigned seen;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
-                if (seen >= arrivals) { ok = true; break; }
+                if (seen - cnt_base >= 256u) { ok = true; break; }
                 if (*abort_flag) break;
                 if ((it & 15) == 15 && tc::global_timer_ns() > deadline) break;
                 __nanosleep(20);
@@ -526,10 +537,6 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         __syncthreads();
         ATT_STAMP(11);
-        if (threadIdx.x == 0) {
-            const unsigned done = atomicAdd(cnt + 1, 1u);
-            if (done == arrivals - 1) { cnt[0] = 0u; cnt[1] = 0u; __threadfence(); }
-        }
     }
     tc::tc_fence_before_sync();
     __syncthreads();

@@ -117,6 +117,9 @@ __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
     return r;
 }
+__device__ __forceinline__ float4 ld_global_f4(const float* p) {
+    return *reinterpret_cast<const float4*>(p);
+}
 __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
     *reinterpret_cast<uint4*>(p) = v;
 }

@@ -1211,15 +1211,29 @@ int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8,
 //   squares of the UNROUNDED updated residual -- the first pass of gate_residual_ada_norm_fp8
 //   (csrc/kernels/fusion.cu:41-47); frt_b200_norm_gemm_fp8_nt_* finishes the norm inside the next projection.
 // *stat_tiles (host int, may be NULL) receives the number of statistics rows written.
-int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
-                                       const float* d_scale_b, void* residual, const void* gate, float* stats_out,
-                                       int* stat_tiles, int splits, int flags, void* stream) {
+// The same launch, which also leaves the next projection's FP8 operand WITHOUT the 1 / rms factor of the norm between
+// them (q8_out may be NULL: then exactly the entry point above):
+//   q8_out[m][n] = e4m3(clamp(bf16(residual[m][n]) * (1 + next_scale[n]) / *d_q8_scale, +-448)),
+// next_scale = the scale third of the NEXT adaRMS style row (N bf16).  A row's 1 / rms commutes with the projection
+//   W . (rms * x * (1 + scale) + shift) = rms * (W . (x * (1 + scale))) + W . shift,
+// so frt_b200_gemm_fp8_nt_*_rowscale applies it, and the precomputed W . shift, in its finish: no CTA of the next
+// projection waits for the row statistics before its MMAs.  Stands for gate_residual_ada_norm_fp8
+// (csrc/kernels/fusion.cu:15-81) with the quantisation point moved in front of the row scale; E4M3 is a floating-point
+// format, so the relative rounding error of an element is the same on either side of the scale.
+int frt_b200_gemm_fp8_nt_gate_residual_q8(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                          const float* d_scale_b, void* residual, const void* gate, float* stats_out,
+                                          int* stat_tiles, const void* next_scale, void* q8_out,
+                                          const float* d_q8_scale, int splits, int flags, void* stream) {
     if (!A || !W || !residual || !gate || M < 0 || N <= 0 || K <= 0) return FRT_ERR_INVALID;
+    if (q8_out && (!next_scale || !d_q8_scale)) return FRT_ERR_INVALID;
     if ((K % 128) || M > 128 || (N % 64)) return FRT_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(residual) & 15) || (reinterpret_cast<uintptr_t>(gate) & 15)) return FRT_ERR_INVALID;
+    if (q8_out && ((reinterpret_cast<uintptr_t>(q8_out) & 7) || (reinterpret_cast<uintptr_t>(next_scale) & 15)))
+        return FRT_ERR_INVALID;
     TokParams t = {};
     t.M = M; t.N = N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
     t.resid = (__nv_bfloat16*)residual; t.gate = (const __nv_bfloat16*)gate; t.stats_out = stats_out;
+    t.q8_out = (uint8_t*)q8_out; t.q8_mod = (const __nv_bfloat16*)next_scale; t.q8_scale = d_q8_scale;
     TokPlan pl;
     int bn = tok_bn_hint(flags);
     if (bn == 0 && (N % 128)) bn = 64;
@@ -1231,6 +1245,61 @@ int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int 
     if (pl.BN == 128)
         return launch_gemm_tok<128, TOK_PRO_TMA, TOK_EPI_RESID>(A, W, t, K, pl, flags & 1, (cudaStream_t)stream);
     return launch_gemm_tok<64, TOK_PRO_TMA, TOK_EPI_RESID>(A, W, t, K, pl, flags & 1, (cudaStream_t)stream);
+}
+
+// Without the extra operand.
+int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                       const float* d_scale_b, void* residual, const void* gate, float* stats_out,
+                                       int* stat_tiles, int splits, int flags, void* stream) {
+    return frt_b200_gemm_fp8_nt_gate_residual_q8(A, W, M, N, K, d_scale_a, d_scale_b, residual, gate, stats_out,
+                                                 stat_tiles, nullptr, nullptr, nullptr, splits, flags, stream);
+}
+
+// QKV projection of an operand written by frt_b200_gemm_fp8_nt_gate_residual_q8 (M <= 128, K % 128 == 0):
+//   row[m][n] = bf16(sa * sb * (A . W^T)[m][n] * rms[m] + col_term[n]),
+//   rms[m] = 1 / sqrt(sum_t stats_in[t][m] / K + eps)   (stats_in: n_stat rows of 128 floats, summed in order),
+//   col_term (N fp32) = W . shift of the norm's style row, computed once per (step, layer) by the caller;
+// then the RoPE + split + KV-append epilogue of frt_b200_gemm_fp8_nt_rope_split.
+int frt_b200_gemm_fp8_nt_rope_split_rowscale(const void* A, const void* W, int M, int K, const float* d_scale_a,
+                                             const float* d_scale_b, const float* stats_in, int n_stat, float eps,
+                                             const float* col_term, const void* rope, void* Q, void* Kout, void* Vout,
+                                             const int* devpos, int q_dim, int k_dim, int v_dim, int head_dim,
+                                             int splits, int flags, void* stream) {
+    if (!A || !W || !stats_in || !col_term || !rope || !Q || !Kout || !Vout || M < 0 || K <= 0 || n_stat <= 0)
+        return FRT_ERR_INVALID;
+    if (q_dim <= 0 || k_dim <= 0 || v_dim <= 0 || head_dim <= 0) return FRT_ERR_INVALID;
+    if ((K % 128) || M > 128 || (head_dim % 8) || (q_dim % head_dim) || (k_dim % head_dim) || (v_dim % 8))
+        return FRT_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(col_term) & 15) return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    TokParams t = {};
+    t.M = M; t.N = q_dim + k_dim + v_dim; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+    t.rope = (const __nv_bfloat16*)rope; t.outQ = (__nv_bfloat16*)Q; t.outK = (__nv_bfloat16*)Kout;
+    t.outV = (__nv_bfloat16*)Vout; t.devpos = devpos;
+    t.q_dim = q_dim; t.k_dim = k_dim; t.v_dim = v_dim; t.head_dim = head_dim;
+    t.stats_in = stats_in; t.n_stat = n_stat; t.eps = eps; t.col_term = col_term;
+    return dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_ROPE>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
+                                                       flags & 1, (cudaStream_t)stream);
+}
+
+// gate|up projection of such an operand: gate / up values = bf16(sa * sb * acc * rms[m] + col_term[n]) (col_term has
+// 2 * half entries, gate rows first), then the GeGLU -> FP8 epilogue of frt_b200_gemm_fp8_nt_geglu_fp8
+// (M <= 128, half % 64 == 0, K % 128 == 0).
+int frt_b200_gemm_fp8_nt_geglu_fp8_rowscale(const void* A, const void* W, void* out8, int M, int half, int K,
+                                            const float* d_scale_a, const float* d_scale_b, const float* stats_in,
+                                            int n_stat, float eps, const float* col_term, const float* d_out_scale,
+                                            int splits, int flags, void* stream) {
+    if (!A || !W || !out8 || !stats_in || !col_term || !d_out_scale || M < 0 || half <= 0 || K <= 0 || n_stat <= 0)
+        return FRT_ERR_INVALID;
+    if ((K % 128) || M > 128 || (half % 64)) return FRT_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(col_term) & 15) return FRT_ERR_INVALID;
+    if (M == 0) return FRT_OK;
+    TokParams t = {};
+    t.M = M; t.N = 2 * half; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
+    t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
+    t.stats_in = stats_in; t.n_stat = n_stat; t.eps = eps; t.col_term = col_term;
+    return dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
+                                                        flags & 1, (cudaStream_t)stream);
 }
 
 // QKV projection whose FP8 input is produced inside the kernel from the residual stream (M <= 128, K = 128, 256, 512

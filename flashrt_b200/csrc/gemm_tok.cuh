@@ -87,6 +87,16 @@ struct TokParams {
     const __nv_bfloat16* style;
     float eps;
     int w_kn;                  // weights stored (K, N) row-major (the MN-major B operand) instead of (N, K)
+    // Deferred row scale (TOK_PRO_TMA with TOK_EPI_ROPE / TOK_EPI_GEGLU, active when stats_in != NULL): the A operand
+    // holds e4m3(x * (1 + scale)) WITHOUT the 1 / rms factor; the finish applies it per token and adds the column
+    // term:  y[m][n] = bf16(alpha * acc[m][n] * rms[m] + col_term[n]),  rms from stats_in / n_stat / K / eps as above,
+    // col_term[n] = sum_k W[n][k] * shift[k] (fp32, N entries).
+    const float* col_term;
+    // TOK_EPI_RESID, optional (q8_out != NULL): the un-normalised operand of the next projection,
+    //   q8_out[m][n] = e4m3(clamp(bf16(residual[m][n]) * (1 + q8_mod[n]) / *q8_scale, +-448))
+    uint8_t* q8_out;
+    const __nv_bfloat16* q8_mod;
+    const float* q8_scale;
 #ifdef FRT_PHASE_STAMPS
     int trace_slot;
 #endif
@@ -408,13 +418,48 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const float inv_os = (EPI == TOK_EPI_GEGLU) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
     const int pos = (EPI == TOK_EPI_ROPE && p.devpos) ? *p.devpos : 0;
     uint4 pre0 = make_uint4(0, 0, 0, 0), pre1 = make_uint4(0, 0, 0, 0);   // first item's operands
+    uint4 pre2 = make_uint4(0, 0, 0, 0);
+    float4 ct0 = make_float4(0.f, 0.f, 0.f, 0.f), ct1 = ct0, ct2 = ct0, ct3 = ct0;   // first item's column terms
+    const bool rowscale = PRO == TOK_PRO_TMA && (EPI == TOK_EPI_ROPE || EPI == TOK_EPI_GEGLU) && p.stats_in != nullptr;
+    const bool emit_q8 = EPI == TOK_EPI_RESID && p.q8_out != nullptr;
+    const float inv_q8 = emit_q8 ? __fdiv_rn(1.0f, *p.q8_scale) : 0.0f;
+    if (rowscale && (int)threadIdx.x < ntok) {
+        // 1 / rms of this rank's tokens from the per-tile partial sums of squares (all partials in flight, summed in order)
+        const int m = m0 + tb + threadIdx.x;
+        float tot = 0.0f;
+        for (int t0 = 0; t0 < p.n_stat; t0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t)
+                v[t] = (t0 + t < p.n_stat) ? __ldcg(p.stats_in + (t0 + t) * TOK_STAT_STRIDE + m) : 0.0f;
+#pragma unroll
+            for (int t = 0; t < 16; ++t)
+                if (t0 + t < p.n_stat) tot = __fadd_rn(tot, v[t]);
+        }
+        const float var = __fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps);
+        s_rms[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(var));
+    }
     {
         const int it = threadIdx.x;
         if (it < items) {
             const int m = m0 + tb + it / G, n = n0 + (it % G) * 8;
+            if (rowscale) {
+                if (EPI == TOK_EPI_GEGLU) {
+                    if (n < p.half) {
+                        ct0 = ld_global_f4(p.col_term + n);
+                        ct1 = ld_global_f4(p.col_term + n + 4);
+                        ct2 = ld_global_f4(p.col_term + p.half + n);
+                        ct3 = ld_global_f4(p.col_term + p.half + n + 4);
+                    }
+                } else if (n < p.N) {
+                    ct0 = ld_global_f4(p.col_term + n);
+                    ct1 = ld_global_f4(p.col_term + n + 4);
+                }
+            }
             if (EPI == TOK_EPI_RESID && n < p.N) {
                 pre0 = ld_global_v4(p.resid + (size_t)m * p.N + n);
                 pre1 = ld_global_v4(p.gate + n);
+                if (emit_q8) pre2 = ld_global_v4(p.q8_mod + n);
             } else if (EPI == TOK_EPI_ROPE && n < p.q_dim + p.k_dim) {
                 const int nr = n < p.q_dim ? n : n - p.q_dim;
                 pre0 = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
@@ -466,6 +511,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         atomicCAS(&g_gemm_status, 0, ERR_EPILOGUE | (blockIdx.x << 8));
     }
     __syncwarp();
+    if (rowscale) __syncthreads();       // s_rms of this rank's tokens is complete
     TOK_STAMP(6);
 
     // ---------------- finish: sum the S slots in order and apply the epilogue
@@ -519,8 +565,21 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int n = n0 + g * 8;
                 if (act && n < p.N) {
                     float v[8];
+                    if (rowscale) {
+                        float4 c0 = ct0, c1 = ct1;
+                        if (!first) {
+                            c0 = ld_global_f4(p.col_term + n);
+                            c1 = ld_global_f4(p.col_term + n + 4);
+                        }
+                        const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                        const float rs = s_rms[t];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(a[j] * alpha));
+                        for (int j = 0; j < 8; ++j)
+                            v[j] = __bfloat162float(__float2bfloat16_rn(__fadd_rn(__fmul_rn(a[j] * alpha, rs), cc[j])));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(a[j] * alpha));
+                    }
                     const bool is_q = n < p.q_dim;
                     const bool is_k = !is_q && n < p.q_dim + p.k_dim;
                     const int nr = is_q ? n : (is_k ? n - p.q_dim : n - p.q_dim - p.k_dim);
@@ -555,10 +614,33 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     float b[8];
                     tok_sum8<BN>(recv, S, per, t, G + g, b);
                     float q[8];
+                    if (rowscale) {
+                        float4 c0 = ct0, c1 = ct1, c2 = ct2, c3 = ct3;
+                        if (!first) {
+                            c0 = ld_global_f4(p.col_term + h);
+                            c1 = ld_global_f4(p.col_term + h + 4);
+                            c2 = ld_global_f4(p.col_term + p.half + h);
+                            c3 = ld_global_f4(p.col_term + p.half + h + 4);
+                        }
+                        const float cg[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                        const float cu[8] = {c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
+                        const float rs = s_rms[t];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            a[j] = __fadd_rn(__fmul_rn(a[j] * alpha, rs), cg[j]);
+                            b[j] = __fadd_rn(__fmul_rn(b[j] * alpha, rs), cu[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            a[j] = a[j] * alpha;
+                            b[j] = b[j] * alpha;
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const float gt = __bfloat162float(__float2bfloat16_rn(a[j] * alpha));
-                        const float up = __bfloat162float(__float2bfloat16_rn(b[j] * alpha));
+                        const float gt = __bfloat162float(__float2bfloat16_rn(a[j]));
+                        const float up = __bfloat162float(__float2bfloat16_rn(b[j]));
                         q[j] = clamp448(__fmul_rn(__fmul_rn(det_gelu_tanh(gt), up), inv_os));
                     }
                     uint2 o8;
@@ -572,11 +654,14 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 float ssq = 0.0f;
                 if (act && n < p.N) {
                     __nv_bfloat16* rp = p.resid + (size_t)m * p.N + n;
-                    uint4 rv = pre0, gv = pre1;
+                    uint4 rv = pre0, gv = pre1, mv = pre2;
                     if (!first) {
                         rv = ld_global_v4(rp);
                         gv = ld_global_v4(p.gate + n);
+                        if (emit_q8) mv = ld_global_v4(p.q8_mod + n);
                     }
+                    const uint32_t* mw = &mv.x;
+                    float u[8];
                     const uint32_t* rw = &rv.x;
                     const uint32_t* gw = &gv.x;
                     uint4 ob;
@@ -593,8 +678,21 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         ssq = __fmaf_rn(r0, r0, ssq);
                         ssq = __fmaf_rn(r1, r1, ssq);
                         ow[k] = pack_bf16x2(r0, r1);
+                        if (emit_q8) {
+                            float b0, b1, s0, s1;
+                            unpack_bf16x2(ow[k], b0, b1);          // what the next reader of the residual sees
+                            unpack_bf16x2(mw[k], s0, s1);
+                            u[2 * k] = clamp448(__fmul_rn(__fmul_rn(b0, __fadd_rn(1.0f, s0)), inv_q8));
+                            u[2 * k + 1] = clamp448(__fmul_rn(__fmul_rn(b1, __fadd_rn(1.0f, s1)), inv_q8));
+                        }
                     }
                     st_global_v4(rp, ob);
+                    if (emit_q8) {
+                        uint2 o8;
+                        o8.x = f32x4_to_e4m3x4(u[0], u[1], u[2], u[3]);
+                        o8.y = f32x4_to_e4m3x4(u[4], u[5], u[6], u[7]);
+                        st_global_v2(p.q8_out + (size_t)m * p.N + n, o8);
+                    }
                 }
                 // the G lanes of a token are neighbours (G divides 32): butterfly inside the group, fixed order
 #pragma unroll

@@ -35,7 +35,7 @@ def _default_counters(n_words: int) -> int:
 
 def _fwd(Q, K, V, O, softmax_lse, seqused_k, lse_accum, o_accum, batch, seqlen_q, seqlen_k, num_heads_q,
          num_heads_kv, head_dim, q_strides, k_strides, v_strides, o_strides, softmax_scale, stream, *, pdl=False,
-         kv_splits=0, out_fp8=0, out_scale=0, kv_static_rows=0, counters=0):
+         kv_splits=0, out_fp8=0, out_scale=0, kv_static_rows=0, counters=0, flags=0):
     if lse_accum and o_accum and not counters:
         g = num_heads_q // num_heads_kv
         counters = _default_counters(2 * ((seqlen_q * g + 127) // 128) * num_heads_kv * batch)
@@ -46,7 +46,7 @@ def _fwd(Q, K, V, O, softmax_lse, seqused_k, lse_accum, o_accum, batch, seqlen_q
          C.cast(_s3(q_strides), C.c_void_p), C.cast(_s3(k_strides), C.c_void_p),
          C.cast(_s3(v_strides), C.c_void_p), C.cast(_s3(o_strides), C.c_void_p),
          softmax_scale, kv_splits, kv_static_rows, o_accum or None, lse_accum or None, counters or None,
-         1 if pdl else 0, stream)
+         (1 if pdl else 0) | (flags & ~1), stream)
 
 
 def fwd_bf16(Q, K, V, O, softmax_lse, softmax_lse_accum=0, o_accum=0, batch=1, seqlen_q=0, seqlen_k=0,

@@ -253,15 +253,33 @@ class GemmRunner:
 
     # -- the decoder's projections with the norm kernel between them folded in ------------------------------
     def fp8_nt_dev_gate_residual(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, stats_out, stream=0, *,
-                                 pdl=False, splits=0, tile_n=0) -> int:
+                                 pdl=False, splits=0, tile_n=0, next_scale=0, q8_out=0, d_scale_q8=0) -> int:
         """``fp8_nt_dev`` + the first pass of ``gate_residual_ada_norm_fp8``: residual <- residual + o * gate and
         the per-tile row sums of squares into ``stats_out`` (rows of 128 floats).  Returns the number of rows
-        written, which the consuming ``norm_fp8_nt_dev_*`` call takes as ``n_stat``."""
+        written, which the consuming ``norm_fp8_nt_dev_*`` / ``fp8_nt_dev_*_rowscale`` call takes as ``n_stat``.
+        With ``q8_out``: also the next projection's FP8 operand e4m3(residual * (1 + next_scale) / *d_scale_q8),
+        i.e. the norm's output without its per-row 1 / rms, which ``fp8_nt_dev_*_rowscale`` applies afterwards."""
         import ctypes
         n = ctypes.c_int(0)
-        call("frt_b200_gemm_fp8_nt_gate_residual", A, B, M, N, K, d_scale_a, d_scale_b, residual, gate,
-             stats_out or None, ctypes.addressof(n), splits, _f(pdl) | _tile_hint(tile_n), stream)
+        call("frt_b200_gemm_fp8_nt_gate_residual_q8", A, B, M, N, K, d_scale_a, d_scale_b, residual, gate,
+             stats_out or None, ctypes.addressof(n), next_scale or None, q8_out or None, d_scale_q8 or None, splits,
+             _f(pdl) | _tile_hint(tile_n), stream)
         return n.value
+
+    def fp8_nt_dev_rope_split_rowscale(self, A, B, M, K, d_scale_a, d_scale_b, stats, n_stat, col_term, rope_weights,
+                                       Q, Kc, Vc, q_dim, k_dim, v_dim, head_dim, stream=0, *, eps=1e-6, devpos=0,
+                                       pdl=False, splits=0, tile_n=0):
+        """QKV projection of an operand left by ``fp8_nt_dev_gate_residual(q8_out=...)``: the row's 1 / rms (from
+        ``stats``) and ``col_term`` = W . shift are applied in the finish, then ``qkv_split_rope[_devpos]``."""
+        call("frt_b200_gemm_fp8_nt_rope_split_rowscale", A, B, M, K, d_scale_a, d_scale_b, stats, n_stat, eps,
+             col_term, rope_weights, Q, Kc, Vc, devpos or None, q_dim, k_dim, v_dim, head_dim, splits,
+             _f(pdl) | _tile_hint(tile_n), stream)
+
+    def fp8_nt_dev_geglu_fp8_rowscale(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, stats, n_stat, col_term,
+                                      d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0, tile_n=0):
+        """gate|up projection of such an operand, ``gate_geglu_merged_fp8`` behind it."""
+        call("frt_b200_gemm_fp8_nt_geglu_fp8_rowscale", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, stats, n_stat,
+             eps, col_term, d_scale_out, splits, _f(pdl) | _tile_hint(tile_n), stream)
 
     def norm_fp8_nt_dev_rope_split(self, x, stats, n_stat, style, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc,
                                    Vc, q_dim, k_dim, v_dim, head_dim, stream=0, *, eps=1e-6, devpos=0, pdl=False,

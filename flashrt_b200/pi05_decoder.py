@@ -298,6 +298,19 @@ class Pi05DecoderPipeline(StepIO):
         self.act_scale = torch.ones(N, L, len(SITES), dtype=torch.float32, device=dev)
         # per-tile row sums of squares handed from a row-parallel projection to the next column-parallel one
         self.row_stats = torch.zeros(16, 128, dtype=torch.float32, device=dev)
+        # deferred row scale: scales of the un-normalised operands x * (1 + scale) ([..., 0]: QKV input of the layer,
+        # [..., 1]: gate|up input) and the column terms W . shift of both projections, per step and layer
+        self.raw_scale = torch.ones(N, L, 2, dtype=torch.float32, device=dev)
+        self.col_qkv = self.col_gu = None
+        if fe.defer_norm:
+            f8 = torch.float8_e4m3fn
+            self.col_qkv = torch.empty(N, L, (DEC_NH + 2 * DEC_NKV) * DEC_HD, dtype=torch.float32, device=dev)
+            self.col_gu = torch.empty(N, L, 2 * DEC_H, dtype=torch.float32, device=dev)
+            for i in range(L):
+                wq = fe.w_qkv[i].view(f8).float() * fe.ws_qkv_t[i]
+                wg = fe.w_gu[i].view(f8).float() * fe.ws_gu_t[i]
+                self.col_qkv[:, i] = fe.style_attn[:, i, DEC_D:2 * DEC_D].float() @ wq.T
+                self.col_gu[:, i] = fe.style_ffn[:, i, DEC_D:2 * DEC_D].float() @ wg.T
         self.scratch_scale = torch.zeros(1, dtype=torch.float32, device=dev)
         self.calibrated = False
         self.loop_args = None
@@ -335,6 +348,13 @@ class Pi05DecoderPipeline(StepIO):
     # ---- small helpers -------------------------------------------------
     def _scale_ptr(self, step, layer, site):
         return self.act_scale[step, layer, SITES.index(site)].data_ptr()
+
+    def _raw_ptr(self, step, layer, which):
+        return self.raw_scale[step, layer, which].data_ptr()
+
+    def scale_tables(self):
+        """Every calibrated table, in the order the on-disk cache stores them."""
+        return [self.act_scale, self.raw_scale]
 
     def _style(self, which, step, layer=None):
         fe = self.fe
@@ -468,6 +488,7 @@ class Pi05DecoderPipeline(StepIO):
         # (QKV 64 x 4, attention-out 64 x 4, gate|up 64 + 64 x 2, FFN-down 64 x 8); larger row counts use the
         # library's own choice
         tuned = S <= 64
+        defer = fe.defer_norm
         t_qkv = dict(splits=4, tile_n=64) if tuned else {}
         t_o = dict(splits=4, tile_n=64) if tuned else {}
         t_gu = dict(splits=2, tile_n=128) if tuned else {}
@@ -480,24 +501,40 @@ class Pi05DecoderPipeline(StepIO):
                                         self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                         fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, stream,
                                         devpos=dp, pdl=pdl, **t_qkv)
+            elif defer:
+                g.fp8_nt_dev_rope_split_rowscale(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
+                                                 self._raw_ptr(step, i, 0), fe.ws_qkv_t[i].data_ptr(), stats, n_stat,
+                                                 self.col_qkv[step, i].data_ptr(), fe.rope.data_ptr(),
+                                                 self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, stream, devpos=dp,
+                                                 pdl=pdl, **t_qkv)
             else:
                 g.norm_fp8_nt_dev_rope_split(x, stats, n_stat, self._style("attn", step, i), fe.w_qkv[i].data_ptr(),
                                              S, DEC_D, self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                              fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD,
                                              stream, devpos=dp, pdl=pdl, **t_qkv)
             self._attention(i, stream, pdl, self._scale_ptr(step, i, "o"))
+            q8 = (dict(next_scale=self._style("ffn", step, i), q8_out=self.act8.data_ptr(),
+                       d_scale_q8=self._raw_ptr(step, i, 1)) if defer else {})
             n_stat = g.fp8_nt_dev_gate_residual(self.attn8.data_ptr(), fe.w_o[i].data_ptr(), S, DEC_D, qd,
                                                 self._scale_ptr(step, i, "o"), fe.ws_o_t[i].data_ptr(), x,
                                                 self._style("attn", step, i) + gate_off, stats, stream, pdl=pdl,
-                                                **t_o)
-            g.norm_fp8_nt_dev_geglu_fp8(x, stats, n_stat, self._style("ffn", step, i), fe.w_gu[i].data_ptr(),
-                                        self.hid8.data_ptr(), S, DEC_H, DEC_D, self._scale_ptr(step, i, "gu"),
-                                        fe.ws_gu_t[i].data_ptr(), self._scale_ptr(step, i, "d"), stream, pdl=pdl,
-                                        **t_gu)
+                                                **t_o, **q8)
+            if defer:
+                g.fp8_nt_dev_geglu_fp8_rowscale(self.act8.data_ptr(), fe.w_gu[i].data_ptr(), self.hid8.data_ptr(), S,
+                                                DEC_H, DEC_D, self._raw_ptr(step, i, 1), fe.ws_gu_t[i].data_ptr(),
+                                                stats, n_stat, self.col_gu[step, i].data_ptr(),
+                                                self._scale_ptr(step, i, "d"), stream, pdl=pdl, **t_gu)
+            else:
+                g.norm_fp8_nt_dev_geglu_fp8(x, stats, n_stat, self._style("ffn", step, i), fe.w_gu[i].data_ptr(),
+                                            self.hid8.data_ptr(), S, DEC_H, DEC_D, self._scale_ptr(step, i, "gu"),
+                                            fe.ws_gu_t[i].data_ptr(), self._scale_ptr(step, i, "d"), stream, pdl=pdl,
+                                            **t_gu)
+            q8 = (dict(next_scale=self._style("attn", step, i + 1), q8_out=self.act8.data_ptr(),
+                       d_scale_q8=self._raw_ptr(step, i + 1, 0)) if defer and i < L - 1 else {})
             n_stat = g.fp8_nt_dev_gate_residual(self.hid8.data_ptr(), fe.w_d[i].data_ptr(), S, DEC_D, DEC_H,
                                                 self._scale_ptr(step, i, "d"), fe.ws_d_t[i].data_ptr(), x,
                                                 self._style("ffn", step, i) + gate_off, stats, stream, pdl=pdl,
-                                                **t_d)
+                                                **t_d, **q8)
 
     def launches_per_layer(self) -> float:
         """Average over the layers (the last layer keeps its separate residual kernel when the norms are fused)."""
@@ -524,6 +561,12 @@ class Pi05DecoderPipeline(StepIO):
         fvk.call("frt_b200_norm_bf16", self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
                  gate, 0, None, style, 0, self.h_bf16.data_ptr(), None, S, DEC_D, 1e-6, 0, stream)
         self._dyn_quant(self.h_bf16, self.act8, step, layer, site, stream)
+        if self.fe.defer_norm:
+            # amax / 448 of the updated residual times (1 + scale): the operand the deferred-row-scale launches read
+            rows = {"attn": self.fe.style_attn, "ffn": self.fe.style_ffn}[style_kind]
+            raw = (self.x.float() * (1.0 + rows[step, layer, :DEC_D].float())).abs().max() / 448.0
+            slot = self.raw_scale[step, layer, 0 if site == "qkv" else 1]
+            slot.copy_(torch.maximum(slot, raw))
 
     def _dyn_quant(self, src, dst8, step, layer, site, stream):
         """Dynamic quantisation used while calibrating (pipeline_rtx.py:804-821): scale of this call into the
@@ -546,7 +589,8 @@ class Pi05DecoderB200:
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
                  cfg_beta: float | None = None, fixed_shape: bool = False, attn_splits: int = 8,
-                 fuse_norm: bool = False, fold_norms: bool = True, persistent_loop: bool = False, **_ignored):
+                 fuse_norm: bool = False, fold_norms: bool = True, defer_norm: bool = True,
+                 persistent_loop: bool = False, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -562,6 +606,11 @@ class Pi05DecoderB200:
         # (attention-out, FFN-down) update the residual and leave per-tile sums of squares, the column-parallel ones
         # (QKV, gate|up) produce their own FP8 input from them: 5 launches per block instead of 7
         self.fold_norms = bool(fold_norms) and fuse_epilogues and not self.fuse_norm
+        # with the norms folded: the row-parallel projection also writes the next projection's FP8 operand, without the
+        # row's 1 / rms (which commutes with the projection and is applied, with the precomputed W . shift, in the
+        # next projection's finish) -- no CTA of QKV / gate|up then builds its operand behind the dependency wait.
+        # False keeps the reference's quantisation point (after the row scale) through the in-kernel norm producer.
+        self.defer_norm = bool(defer_norm) and self.fold_norms and precision == "fp8"
         # the whole loop as one cooperative kernel (phases separated by grid barriers) instead of 1300 launches
         self.persistent_loop = bool(persistent_loop)
         if self.persistent_loop and precision != "fp8":
@@ -687,37 +736,47 @@ class Pi05DecoderB200:
         from . import calibration_cache as cc
         cacheable = use_cache and self.checkpoint_path is not None
         if cacheable:
-            hit = cc.load_calibration(self.checkpoint_path, self.prefix_len, expected_count=p.act_scale.numel(),
-                                      cache_dir=cache_dir, metadata=self._cache_meta(len(noises), percentile))
+            tables = p.scale_tables()
+            hit = cc.load_calibration(self.checkpoint_path, self.prefix_len,
+                                      expected_count=sum(t.numel() for t in tables), cache_dir=cache_dir,
+                                      metadata=self._cache_meta(len(noises), percentile))
             if hit is not None:
-                p.act_scale.copy_(torch.tensor(hit["ae_scales"], dtype=torch.float32).reshape(p.act_scale.shape))
+                flat, at = torch.tensor(hit["ae_scales"], dtype=torch.float32), 0
+                for t in tables:
+                    t.copy_(flat[at:at + t.numel()].reshape(t.shape))
+                    at += t.numel()
                 torch.cuda.synchronize(self.device)
                 p.calibrated = True
                 self.graph = None
                 self.calibration_source = "cache"
                 return
         self.calibration_source = "measured"
-        per_sample = []
+        tables = p.scale_tables()
+        per_sample = [[] for _ in tables]
         with torch.cuda.stream(self.stream):
             for nz in noises:
-                p.act_scale.zero_()
+                for t in tables:
+                    t.zero_()
                 p.noise.copy_(nz.to(self.device, torch.float32).reshape(p.noise.shape))
                 p.transformer_decoder(self.stream.cuda_stream, calibrate=True)
                 self.stream.synchronize()
-                per_sample.append(p.act_scale.clone())
-            stack = torch.stack(per_sample, 0)
-            if percentile is None:
-                p.act_scale.copy_(stack.max(0).values)
-            else:
-                p.act_scale.copy_(torch.quantile(stack, percentile / 100.0, dim=0))
-            p.act_scale.clamp_(min=1e-12)
+                for t, acc in zip(tables, per_sample):
+                    acc.append(t.clone())
+            for t, acc in zip(tables, per_sample):
+                stack = torch.stack(acc, 0)
+                if percentile is None:
+                    t.copy_(stack.max(0).values)
+                else:
+                    t.copy_(torch.quantile(stack, percentile / 100.0, dim=0))
+                t.clamp_(min=1e-12)
         self.stream.synchronize()
         if fvk.tensor_core_status() != 0:
             raise RuntimeError("a tensor-core kernel reported a timed-out wait during calibration")
         p.calibrated = True
         self.graph = None
         if cacheable:
-            cc.save_calibration(self.checkpoint_path, self.prefix_len, p.act_scale.flatten().cpu().tolist(),
+            cc.save_calibration(self.checkpoint_path, self.prefix_len,
+                                torch.cat([t.flatten() for t in tables]).cpu().tolist(),
                                 metadata=self._cache_meta(len(noises), percentile), cache_dir=cache_dir)
 
     # ---- graph --------------------------------------------------------------

@@ -160,7 +160,9 @@ int frt_b200_gemm_status(int reset);
  *   num_heads_q, seqlen_q, head_dim) fp32 and lse_accum (splits, batch, num_heads_q, seqlen_q) fp32 -- the
  *   reference's FA2 split-kv buffers -- and counters = 2 unsigned per (128-row tile, kv head, batch), zeroed once
  *   by the caller.  Given scratch, the kv splits combine through global memory instead of the cluster; the grid
- *   (tiles x kv heads x batch x splits) must then fit the device in one wave, else -2 is returned. */
+ *   (tiles x kv heads x batch x splits) must then fit the device in one wave, else -2 is returned.
+ *   flags: bit 0 = programmatic dependent launch; bit 1 = keep the single-tile kernel; head_dim 256 with scratch:
+ *   bit 2 = one CTA per (tile, split) instead of four head-dim parts. */
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
                                 int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
@@ -174,8 +176,8 @@ int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, voi
  * (about 4.2 MB of device memory on every GPU that loads it, held until the process exits).
  * Limits: kv_splits <= 8, batch * num_heads_q * seqlen_q <= 512, head_dim <= 256, at most 64 (row tile, kv head,
  * batch) triples; beyond them the call returns -4 and launches nothing.  It allocates and frees nothing.
- * The first call on each device fetches the array's device address and clears its arrival counters with a blocking
- * memset -- make that call before any stream capture.  All calls share the one array and it keeps the last call's
+ * The first call on each device fetches the array's device address and clears its arrival counters with a memset
+ * on the caller's stream -- make that call before any stream capture (inside one it is refused with -1).  All calls share the one array and it keeps the last call's
  * contents; calls whose kernels may run at the same time (two streams, parallel graph branches) race on it. */
 int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                                const float* out_scale, float* lse, const int* seqused_k, int batch,
@@ -261,6 +263,31 @@ int frt_b200_gemm_fp8_nt_gate_res_norm_fp8(const void* A, const void* W, int M, 
 int frt_b200_gemm_fp8_nt_gate_residual(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
                                        const float* d_scale_b, void* residual, const void* gate, float* stats_out,
                                        int* stat_tiles, int splits, int flags, void* stream);
+/* The same launch, also leaving the NEXT projection's FP8 operand without the 1 / rms factor of the norm between them
+ * (second pass of gate_residual_ada_norm_fp8, csrc/kernels/fusion.cu:48-81, with the quantisation point moved in front of
+ * the row scale):  q8_out[m][n] = e4m3(clamp(bf16(residual[m][n]) * (1 + next_scale[n]) / *d_q8_scale, +-448)),
+ * next_scale = scale third of the next norm's style row (N bf16).  q8_out NULL: exactly the entry point above. */
+int frt_b200_gemm_fp8_nt_gate_residual_q8(const void* A, const void* W, int M, int N, int K, const float* d_scale_a,
+                                          const float* d_scale_b, void* residual, const void* gate, float* stats_out,
+                                          int* stat_tiles, const void* next_scale, void* q8_out,
+                                          const float* d_q8_scale, int splits, int flags, void* stream);
+/* Projections of such an operand (GemmRunner::fp8_nt_dev, csrc/bindings.cpp:717-727, with the row scale and the shift of
+ * the norm applied in the finish):  y[m][n] = bf16(sa * sb * (A . W^T)[m][n] * rms[m] + col_term[n]),
+ *   rms[m] = 1 / sqrt(sum_t stats_in[t][m] / K + eps), t = 0 .. n_stat-1 in order (the statistics rows written above),
+ *   col_term (fp32, one entry per output feature) = W . shift, which the caller computes once per (step, layer);
+ * followed by the epilogue of frt_b200_gemm_fp8_nt_rope_split (qkv_split_rope, csrc/kernels/rope.cu:135-277) or of
+ * frt_b200_gemm_fp8_nt_geglu_fp8 (gate_geglu_merged_fp8, csrc/kernels/activation.cu:249-279; col_term has 2 * half
+ * entries, gate rows first).  M <= 128, K % 128 == 0. */
+int frt_b200_gemm_fp8_nt_rope_split_rowscale(const void* A, const void* W, int M, int K, const float* d_scale_a,
+                                             const float* d_scale_b, const float* stats_in, int n_stat, float eps,
+                                             const float* col_term, const void* rope, void* Q, void* Kout, void* Vout,
+                                             const int* devpos, int q_dim, int k_dim, int v_dim, int head_dim,
+                                             int splits, int flags, void* stream);
+/* gate|up form of the row-scaled projection: gate_geglu_merged_fp8 (csrc/kernels/activation.cu:249-279) behind it. */
+int frt_b200_gemm_fp8_nt_geglu_fp8_rowscale(const void* A, const void* W, void* out8, int M, int half, int K,
+                                            const float* d_scale_a, const float* d_scale_b, const float* stats_in,
+                                            int n_stat, float eps, const float* col_term, const float* d_out_scale,
+                                            int splits, int flags, void* stream);
 /* Second pass of gate_residual_ada_norm_fp8 (csrc/kernels/fusion.cu:48-81) produced inside the next projection:
  *   rms[m] = 1 / sqrt(sum_t stats_in[t][m] / K + eps), t = 0 .. n_stat-1 in order;
  *   a = e4m3(clamp(((x * rms) * (1 + scale) + shift) / *d_scale_a, +-448)), style = [scale (K) | shift (K)] one bf16 row

@@ -185,7 +185,8 @@ def test_fixed_shape_graph_serves_every_prefix_length(precision):
         exact = load_model(sd, prefix_len=valid, **kw)
         exact.set_prefix(pk[:, :valid], pv[:, :valid])
         if precision == "fp8":      # same static scales, so that only the kernel path differs
-            exact.frontend.pipeline.act_scale.copy_(fe.pipeline.act_scale)
+            for dst, src in zip(exact.frontend.pipeline.scale_tables(), fe.pipeline.scale_tables()):
+                dst.copy_(src)
             exact.frontend.pipeline.calibrated = True
         ref = exact.predict(noise=noise)
         assert _cos(torch.from_numpy(got), torch.from_numpy(ref)) >= 0.9999, valid
@@ -197,9 +198,10 @@ def test_fixed_shape_graph_serves_every_prefix_length(precision):
 
 
 def test_compositions_of_the_norms_agree():
-    """Three compositions of the same block: norm kernels on their own (7 launches per block), folded into the
-    projections around them (the default, 5), and fuse_norm=True (projection + gated residual + adaRMS in one
-    16-CTA-cluster launch).  Same actions to within the FP8 code flips of the differently ordered row statistics."""
+    """Four compositions of the same block: norm kernels on their own (7 launches per block); folded into the
+    projections around them with the reference's quantisation point (in-kernel norm producer, 5); the default, which
+    quantises in front of the row scale and applies 1 / rms in the next projection's finish (5); and fuse_norm=True
+    (projection + gated residual + adaRMS in one 16-CTA-cluster launch).  Same actions to within FP8 rounding."""
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import synthetic_state_dict
     L = 3
@@ -208,7 +210,8 @@ def test_compositions_of_the_norms_agree():
     cal = [R.synthetic_noise(100 + j) for j in range(3)]
     noise = R.synthetic_noise(1).numpy()
     outs = []
-    for kw, per_step in ((dict(fold_norms=False), 2 + 7 * L + 2), (dict(), 2 + 5 * L + 2),
+    for kw, per_step in ((dict(fold_norms=False), 2 + 7 * L + 2), (dict(defer_norm=False), 2 + 5 * L + 2),
+                         (dict(), 2 + 5 * L + 2),
                          (dict(fuse_norm=True), 2 + 5 * L + 1 + 2)):
         m = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768, **kw)
         m.set_prefix(pk, pv)
