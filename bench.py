@@ -762,7 +762,7 @@ def run_timeline(args):
     model.set_prefix(torch.randn(L, fe.prefix_len, 256, generator=g), torch.randn(L, fe.prefix_len, 256, generator=g))
     model.calibrate([torch.randn(fe.chunk_size, ACTION_DIM, generator=g)])
     gb = (ctypes.c_ulonglong * (8 * 160 * 16))()
-    ab = (ctypes.c_ulonglong * (8 * 64 * 16))()
+    ab = (ctypes.c_ulonglong * (8 * 128 * 16))()
 
     def read(reset=1):
         rc = _lib.call_status("frt_b200_phase_stamps_read", ctypes.addressof(gb), ctypes.addressof(ab), reset)
@@ -770,7 +770,7 @@ def run_timeline(args):
             raise SystemExit("timeline: the library was built without -DFRT_PHASE_STAMPS "
                              "(FRT_NVCC_EXTRA=-DFRT_PHASE_STAMPS python -m flashrt_b200._build --force)")
         return (np.frombuffer(gb, dtype=np.uint64).reshape(8, 160, 16).astype(np.int64),
-                np.frombuffer(ab, dtype=np.uint64).reshape(8, 64, 16).astype(np.int64))
+                np.frombuffer(ab, dtype=np.uint64).reshape(8, 128, 16).astype(np.int64))
 
     s = fe.stream
     calls = {"n": 0}
@@ -797,8 +797,8 @@ def run_timeline(args):
             gr.replay()
         s.synchronize()
     tt, ta = read(0)
-    kinds = ["qkv (TMA-fed, layer 0)", "attention", "attention-out", "gate|up (norm producer)", "FFN-down",
-             "qkv (norm producer)", "attention", "attention-out", "gate|up (norm producer)", "FFN-down"]
+    kinds = ["qkv (layer 0)", "attention", "attention-out", "gate|up", "FFN-down",
+             "qkv", "attention", "attention-out", "gate|up", "FFN-down"]
     rows, gi, ai = [], 0, 0
     for k in kinds:
         if k == "attention":

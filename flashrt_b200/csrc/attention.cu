@@ -448,7 +448,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
-            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(256u / C) : "memory");
+            asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(256u / C) : "memory");
             bool ok = false;
             for (uint32_t it = 0;; ++it) {
                 unsigned seen;
@@ -873,7 +873,7 @@ int frt_b200_attention_status(int reset) {
 }
 
 // Diagnostics (no counterpart in the reference): device-timer phase stamps of the last 8 launches of the token-major
-// GEMM (gemm_host: 8 x 160 CTAs x 16 stamps) and of the head_dim-256 attention kernel (attn_host: 8 x 64 x 16), in
+// GEMM (gemm_host: 8 x 160 CTAs x 16 stamps) and of the head_dim-256 attention kernel (attn_host: 8 x 128 x 16), in
 // nanoseconds of %globaltimer.  Only a library built with -DFRT_PHASE_STAMPS records them; otherwise -2.
 // reset != 0 restarts the launch slots at 0 and clears the stamps (after copying them out).  Synchronises the device.
 #ifdef FRT_PHASE_STAMPS
@@ -888,14 +888,14 @@ int frt_b200_phase_stamps_read(unsigned long long* gemm_host, unsigned long long
         if (rc) return rc;
     }
     if (attn_host) {
-        e = cudaMemcpyFromSymbol(attn_host, g_attn_trace, sizeof(unsigned long long) * 8 * 64 * 16);
+        e = cudaMemcpyFromSymbol(attn_host, g_attn_trace, sizeof(unsigned long long) * 8 * 128 * 16);
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
     }
     if (reset) {
         g_attn_trace_slot = 0;
         void* ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_attn_trace) == cudaSuccess && ptr)
-            cudaMemset(ptr, 0, sizeof(unsigned long long) * 8 * 64 * 16);
+            cudaMemset(ptr, 0, sizeof(unsigned long long) * 8 * 128 * 16);
     }
     return FRT_OK;
 #else

@@ -19,10 +19,10 @@
 #pragma once
 
 #ifdef FRT_PHASE_STAMPS
-__device__ unsigned long long g_attn_trace[8][64][16];
+__device__ unsigned long long g_attn_trace[8][128][16];
 static int g_attn_trace_slot = 0;
-#define ATT_STAMP(i) do { if (threadIdx.x == 0) g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 64][i] = tc::global_timer_ns(); } while (0)
-#define ATT_STAMP_ANY(i) do { g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 64][i] = tc::global_timer_ns(); } while (0)
+#define ATT_STAMP(i) do { if (threadIdx.x == 0) g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 128][i] = tc::global_timer_ns(); } while (0)
+#define ATT_STAMP_ANY(i) do { g_attn_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 128][i] = tc::global_timer_ns(); } while (0)
 #else
 #define ATT_STAMP(i)
 #define ATT_STAMP_ANY(i)
@@ -312,13 +312,18 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     __stcg(p.lse_accum + rank * split_stride + row0 + row,
                            l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY);
                 // 64 columns per step, the next step's tensor-memory load in flight while this one is converted
+                // dper is a power of two (>= 8): slice = column >> dsh.  These threads run one warp per scheduler, so every
+                // instruction of the address arithmetic is exposed latency: shifts and 32-bit offsets, no divisions
+                const int dsh = 31 - __clz(dper);
+                const uint32_t slice_stride = (uint32_t)rows_valid * (uint32_t)dper * 2u;
+                uint8_t* rowp = blk + (uint32_t)row * (uint32_t)dper * 2u;
                 auto emit = [&](const uint32_t* v, int c) {
                     if (row < rows_valid) {
 #pragma unroll
                         for (int j8 = 0; j8 < 8; ++j8) {                // 8 columns = 16 bytes at a time
                             const int cc = c + 8 * j8;
-                            uint4* dst = reinterpret_cast<uint4*>(blk + ((size_t)(cc / dper) * rows_valid + row) * (dper * 2) +
-                                                                  (cc % dper) * 2);
+                            uint4* dst = reinterpret_cast<uint4*>(rowp + (uint32_t)(cc >> dsh) * slice_stride +
+                                                                  (uint32_t)(cc & (dper - 1)) * 2u);
                             const uint32_t* w = v + 8 * j8;
                             uint4 o;
                             o.x = pack_bf16x2(__uint_as_float(w[0]) * invl, __uint_as_float(w[1]) * invl);
@@ -349,7 +354,9 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     } else {
                         tc::tmem_ld_wait();
+                        ATT_STAMP(13);
                         emit(va, 0);
+                        ATT_STAMP(14);
                     }
                 } else {
 #pragma unroll
@@ -430,8 +437,9 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncthreads();
         ATT_STAMP(9);
         if (threadIdx.x == 0) {
-            // arrive without waiting for the old value (the partial was fenced above), then poll
-            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(256u / arrivals) : "memory");
+            // arrive without waiting for the old value (every thread fenced its part of the partial before the barrier
+            // above, so a relaxed add publishes it), then poll
+            asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(256u / arrivals) : "memory");
             bool ok = false;
             for (uint32_t it = 0;; ++it) {
                 unsigned seen;
@@ -504,8 +512,10 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 float a[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) a[i] = 0.0f;
-                for (uint32_t sidx = 0; sidx < C; ++sidx) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(cbuf + sidx * slice_bytes + ((size_t)r * cpr + ch) * 16);
+#pragma unroll
+                for (uint32_t sidx = 0; sidx < 8; ++sidx) {             // all loads of the row in flight at once
+                    if (sidx >= C) break;
+                    const uint4 x = *reinterpret_cast<const uint4*>(cbuf + sidx * slice_bytes + ((uint32_t)r * cpr + ch) * 16u);
                     const float ws = s_w[r * 8 + sidx];
                     float f0, f1;
                     unpack_bf16x2(x.x, f0, f1); a[0] += ws * f0; a[1] += ws * f1;

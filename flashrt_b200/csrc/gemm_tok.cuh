@@ -58,6 +58,8 @@ struct TokParams {
     int stages;                // shared-memory ring depth (>= nkb when the A operand is produced in the kernel)
     int per;                   // tokens finished by one rank of the cluster = ceil(tokens of an m-tile / S)
     int ring_bytes;            // bytes of the operand ring / staging area in front of the receive slots
+    int m64;                   // one m-tile of at most 64 tokens: M = 64 MMAs over a 64-row A tile (8 KB per k-block), token
+                               // 16 i + j on tensor-memory lane 32 i + j; a CTA then leaves room for a neighbour's CTA
     const float* sa;           // device scalars (may be null = 1): activation / weight scale
     const float* sb;
     float alpha_host;
@@ -104,17 +106,18 @@ struct TokParams {
 
 template <int BN>
 struct TokCfg {
-    static constexpr int A_BYTES = 128 * 128;                 // 128 token rows x 128 K-bytes
     static constexpr int W_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+    // A tile of a stage: 128 (or, for at most 64 tokens, 64) token rows x 128 K-bytes
+    static constexpr int a_bytes(bool m64) { return m64 ? 64 * 128 : 128 * 128; }
+    static constexpr int stage_bytes(bool m64) { return a_bytes(m64) + W_BYTES; }
     static constexpr int MAX_STAGES = BN == 256 ? 4 : BN == 128 ? 6 : 8;
     static constexpr int AUX_BYTES = 2048;                    // barriers, flags, per-token 1 / rms
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     // operand ring, then the receive slots [S][per][BN] fp32 of the split-K exchange (never aliased: a fast rank
     // pushes while a slow rank's MMAs still read its operands)
-    static int ring_bytes(int stages, int S, int per) { return stages * STAGE_BYTES; }
-    static int smem_bytes(int stages, int S, int per) {
-        return AUX_BYTES + 1024 + ring_bytes(stages, S, per) + S * per * BN * 4;
+    static int ring_bytes(int stages, bool m64) { return stages * stage_bytes(m64); }
+    static int smem_bytes(int stages, int S, int per, bool m64) {
+        return AUX_BYTES + 1024 + ring_bytes(stages, m64) + S * per * BN * 4;
     }
 };
 
@@ -138,14 +141,33 @@ __device__ __forceinline__ void tok_sum8(const float* recv, int S, int per, int 
     const float4* row = reinterpret_cast<const float4*>(recv + (size_t)t * BN);
     const int c0 = 2 * c8, c1 = 2 * c8 + 1;
     const size_t slot = (size_t)per * BN / 4;
-    float4 x = row[c0], y = row[c1];
-    a[0] = x.x; a[1] = x.y; a[2] = x.z; a[3] = x.w;
-    a[4] = y.x; a[5] = y.y; a[6] = y.z; a[7] = y.w;
-    for (int s = 1; s < S; ++s) {
-        x = row[s * slot + c0];
-        y = row[s * slot + c1];
-        a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
-        a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    // S is 1, 2, 4 or 8: the loads of four slots in flight at a time, the sums in slot order
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = 0.0f;
+#pragma unroll
+    for (int s0 = 0; s0 < 8; s0 += 4) {
+        if (s0 < S) {
+            float4 x[4], y[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                if (s0 + s < S) {
+                    x[s] = row[(s0 + s) * slot + c0];
+                    y[s] = row[(s0 + s) * slot + c1];
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                if (s0 + s < S) {
+                    if (s0 + s == 0) {
+                        a[0] = x[s].x; a[1] = x[s].y; a[2] = x[s].z; a[3] = x[s].w;
+                        a[4] = y[s].x; a[5] = y[s].y; a[6] = y[s].z; a[7] = y[s].w;
+                    } else {
+                        a[0] += x[s].x; a[1] += x[s].y; a[2] += x[s].z; a[3] += x[s].w;
+                        a[4] += y[s].x; a[5] += y[s].y; a[6] += y[s].z; a[7] += y[s].w;
+                    }
+                }
+            }
+        }
     }
 }
 
@@ -187,6 +209,8 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int kb0 = rank * nkb;
     const int STG = p.stages;
     const int per = p.per;
+    const bool m64 = p.m64 != 0;
+    const int A_BYTES = Cfg::a_bytes(m64), STAGE_BYTES = Cfg::stage_bytes(m64);
     // tokens this rank finishes: [tb, te) inside the m-tile
     const int tb = rank * per < Mt ? rank * per : Mt;
     const int te = tb + per < Mt ? tb + per : Mt;
@@ -225,9 +249,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer: the weights do not depend on the producer grid and start streaming now
-        const uint32_t tx = (PRO == TOK_PRO_TMA) ? Cfg::STAGE_BYTES : Cfg::W_BYTES;
+        const uint32_t tx = (PRO == TOK_PRO_TMA) ? STAGE_BYTES : Cfg::W_BYTES;
         auto load_w = [&](int stage, int kb) {
-            uint8_t* dst = tiles + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+            uint8_t* dst = tiles + stage * STAGE_BYTES + A_BYTES;
             if (p.w_kn) {
                 // (K, N) weights: boxes of 128 K-rows x 128 N-bytes, one per 128 output features; the tile is then an
                 // MN-major operand (128-byte rows along N, 8 K-rows per swizzle atom, 16 KB between the chunks)
@@ -251,7 +275,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         pdl_wait();
         if (PRO == TOK_PRO_TMA) {
             for (int i = 0; i < pre; ++i)
-                tc::tma_load_2d(tiles + i * Cfg::STAGE_BYTES, &tmA, &full[i], (kb0 + i) * 128, m0);
+                tc::tma_load_2d(tiles + i * STAGE_BYTES, &tmA, &full[i], (kb0 + i) * 128, m0);
         }
         *issued = pre;
         for (int i = pre; i < nkb; ++i) {
@@ -264,7 +288,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             tc::mbar_arrive_expect_tx(&full[s], tx);
             load_w(s, kb0 + i);
-            if (PRO == TOK_PRO_TMA) tc::tma_load_2d(tiles + s * Cfg::STAGE_BYTES, &tmA, &full[s], (kb0 + i) * 128, m0);
+            if (PRO == TOK_PRO_TMA) tc::tma_load_2d(tiles + s * STAGE_BYTES, &tmA, &full[s], (kb0 + i) * 128, m0);
             *issued = i + 1;
         }
     }
@@ -351,7 +375,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         q[i >> 1] = f32x4_to_e4m3x4(v[0], v[1], v[2], v[3]);
                     }
                     const int kb = c16 >> 3, c = c16 & 7;
-                    uint8_t* dst = tiles + kb * Cfg::STAGE_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                    uint8_t* dst = tiles + kb * STAGE_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
                     *reinterpret_cast<uint4*>(dst) = make_uint4(q[0], q[1], q[2], q[3]);
                 }
             }
@@ -363,7 +387,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        const uint32_t idesc = tc::make_idesc(0, 0, 0, 0, 128, BN) | (p.w_kn ? (1u << 16) : 0u);   // bit 16: B MN-major
+        const uint32_t idesc = tc::make_idesc(0, 0, 0, 0, m64 ? 64 : 128, BN) | (p.w_kn ? (1u << 16) : 0u);   // bit 16: B MN-major
         bool failed = false;
         if (PRO == TOK_PRO_NORM) {
             if (!tc::mbar_wait_until(a_ready, 0, deadline, abort_flag)) {
@@ -373,8 +397,8 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
         }
         const uint64_t dA0 = tc::make_desc_kmajor_sw128(tc::smem_u32(tiles));
-        const uint64_t dW0 = p.w_kn ? tc::make_desc_mnmajor_sw128(tc::smem_u32(tiles + Cfg::A_BYTES), 16384)
-                                    : tc::make_desc_kmajor_sw128(tc::smem_u32(tiles + Cfg::A_BYTES));
+        const uint64_t dW0 = p.w_kn ? tc::make_desc_mnmajor_sw128(tc::smem_u32(tiles + A_BYTES), 16384)
+                                    : tc::make_desc_kmajor_sw128(tc::smem_u32(tiles + A_BYTES));
         // one K = 32 step: 32 bytes along a K-major row, or 32 rows of 128 bytes of an MN-major tile
         const uint64_t wstep = p.w_kn ? (uint64_t)((32 * 128) >> 4) : 2u;
         for (int i = 0; i < nkb && !failed; ++i) {
@@ -390,7 +414,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #ifdef FRT_PHASE_STAMPS
             if (i == 0) g_tok_trace[p.trace_slot][(blockIdx.z * gridDim.x + blockIdx.x) % 160][10] = tc::global_timer_ns();
 #endif
-            const uint64_t so = (uint64_t)((s * Cfg::STAGE_BYTES) >> 4);
+            const uint64_t so = (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
             for (int k = 0; k < 4; ++k)   // 4 x (K = 32) per 128-byte k-block; +32 bytes = +2 in the address field
                 tc::mma_f8(tmem_d, dA0 + so + 2 * k, dW0 + so + wstep * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
@@ -483,8 +507,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     cluster_wait_acquire();          // every peer has initialised its receive barrier (arrived during its set-up)
     {
         const int quad = warp & 3, chalf = warp >> 2;
-        const int row = quad * 32 + lane;                      // token inside the m-tile
-        if (have_acc && quad * 32 < Mt) {
+        const int qrows = m64 ? 16 : 32;                       // accumulator rows per 32-lane quadrant
+        const int row = lane < qrows ? quad * qrows + lane : Mt;   // token inside the m-tile (none on the idle lanes)
+        if (have_acc && quad * qrows < Mt) {
             const uint32_t trow = tmem_d + ((uint32_t)(quad * 32) << 16);
             const int owner = row / per < S ? row / per : 0;
             const uint32_t dst_local = tc::smem_u32(recv) + (uint32_t)(((rank * per + (row % per)) * BN) * 4);
@@ -745,7 +770,7 @@ static bool tok_plan(int N, int K, int m_tiles, int mt, int epi, int pro, int sm
         if (w_kn && (BN == 64 || (epi == TOK_EPI_GEGLU && BN != 256))) continue;   // 128-feature boxes of (K, N) weights
         const int tiles = (epi == TOK_EPI_GEGLU ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN) * m_tiles;
         const int max_st = BN == 256 ? 4 : BN == 128 ? 6 : 8;
-        const int stage_bytes = 16384 + BN * 128;
+        const int stage_bytes = (m_tiles == 1 && mt <= 64 ? 8192 : 16384) + BN * 128;
         for (int S = 1; S <= 8; S *= 2) {
             if (want_s > 0 && S != want_s) continue;
             if (kbt % S) continue;
@@ -782,16 +807,18 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     p.nkb = pl.nkb;
     p.stages = pl.stages;
     p.per = (mt + pl.S - 1) / pl.S;
+    p.m64 = (m_tiles == 1 && mt <= 64) ? 1 : 0;
+    const bool m64 = p.m64 != 0;
     // the operand ring shrinks until it fits beside the receive slots
-    while (p.stages > 2 && Cfg::smem_bytes(p.stages, pl.S, p.per) > 227 * 1024) --p.stages;
+    while (p.stages > 2 && Cfg::smem_bytes(p.stages, pl.S, p.per, m64) > 227 * 1024) --p.stages;
     if (PRO == TOK_PRO_NORM && p.stages < pl.nkb) return FRT_ERR_UNSUPPORTED;
     p.K = K;
 #ifdef FRT_PHASE_STAMPS
     p.trace_slot = g_tok_trace_slot;
     g_tok_trace_slot = (g_tok_trace_slot + 1) % 8;
 #endif
-    const int smem = Cfg::smem_bytes(p.stages, pl.S, p.per);
-    p.ring_bytes = Cfg::ring_bytes(p.stages, pl.S, p.per);
+    const int smem = Cfg::smem_bytes(p.stages, pl.S, p.per, m64);
+    p.ring_bytes = Cfg::ring_bytes(p.stages, m64);
     if (smem > 227 * 1024) return FRT_ERR_UNSUPPORTED;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -805,7 +832,7 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     CUtensorMap tmA, tmW;
     int rc;
     if (PRO == TOK_PRO_TMA) {
-        rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, (uint64_t)K, (uint64_t)K, 128);
+        rc = get_tmap_2d_u8(&tmA, A, (uint64_t)p.M, (uint64_t)K, (uint64_t)K, m64 ? 64 : 128);
         if (rc) return rc;
     } else {
         memset(&tmA, 0, sizeof(tmA));

@@ -490,7 +490,7 @@ class Pi05DecoderPipeline(StepIO):
         tuned = S <= 64
         defer = fe.defer_norm
         t_qkv = dict(splits=4, tile_n=64) if tuned else {}
-        t_o = dict(splits=4, tile_n=64) if tuned else {}
+        t_o = dict(splits=8, tile_n=64) if tuned else {}
         t_gu = dict(splits=2, tile_n=128) if tuned else {}
         t_d = dict(splits=8, tile_n=64) if tuned else {}
         for i in range(L):

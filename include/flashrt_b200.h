@@ -190,7 +190,7 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
 int frt_b200_attention_status(int reset);
 /* Diagnostics, no counterpart in the reference: device-timer (%globaltimer, ns) phase stamps of the last 8 launches of
  * the token-major small-M GEMM (gemm_host: 8 launches x 160 CTAs x 16 stamps) and of the head_dim-256 attention kernel
- * (attn_host: 8 x 64 x 16); either pointer may be NULL.  Recorded only by a library built with -DFRT_PHASE_STAMPS
+ * (attn_host: 8 x 128 x 16); either pointer may be NULL.  Recorded only by a library built with -DFRT_PHASE_STAMPS
  * (FRT_NVCC_EXTRA=-DFRT_PHASE_STAMPS python -m flashrt_b200._build --force); a regular build returns -2.
  * reset != 0 restarts the launch slots and clears the stamps after copying them out.  Synchronises the device. */
 int frt_b200_phase_stamps_read(unsigned long long* gemm_host, unsigned long long* attn_host, int reset);
