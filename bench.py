@@ -132,11 +132,10 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------------------
 def gemm_roofline(fe, reps: int = 20):
     """Average duration of the dominant kernel family (the small-M FP8 projections that stream the weights): a graph
-    holding exactly the 4 x 18 projection launches of one Euler step in the form the loop uses them (norm producer /
-    fused epilogues included), each on its own layer's weights (311 MB > L2), timed with CUDA events on the
-    launching stream.  Returns (us per launch, algorithmic bytes per launch, launches)."""
+    holding exactly the 4 x 18 projection launches of one Euler step as the loop issues them (folded norms and fused
+    epilogues included), each on its own layer's weights (311 MB > L2), timed with CUDA events on the launching
+    stream.  Returns (us per launch, algorithmic bytes per launch, launches)."""
     import torch
-    from flashrt_b200.pi05_decoder import DEC_D, DEC_H, DEC_HD, DEC_NH, DEC_NKV
     p, s = fe.pipeline, fe.stream
     S, L = fe.chunk_size * fe.batch, fe.layers
     nv = fe.precision == "nvfp4"
@@ -151,24 +150,7 @@ def gemm_roofline(fe, reps: int = 20):
 
     def enqueue():
         if folded:
-            g, pdl = p.gemm, fe.use_pdl
-            x, stats = p.x.data_ptr(), p.row_stats.data_ptr()
-            qd, kd = DEC_NH * DEC_HD, DEC_NKV * DEC_HD
-            for i in range(L):
-                kp, vp, dp = p._kv_dst(i, 0)
-                g.norm_fp8_nt_dev_rope_split(x, stats, 16, p._style("attn", 0, i), fe.w_qkv[i].data_ptr(), S, DEC_D,
-                                             p._scale_ptr(0, i, "qkv"), fe.ws_qkv_t[i].data_ptr(), fe.rope.data_ptr(),
-                                             p.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, st, devpos=dp, pdl=pdl,
-                                             splits=4, tile_n=64)
-                g.fp8_nt_dev_gate_residual(p.attn8.data_ptr(), fe.w_o[i].data_ptr(), S, DEC_D, qd, p._scale_ptr(0, i, "o"),
-                                           fe.ws_o_t[i].data_ptr(), x, p._style("attn", 0, i) + 4 * DEC_D, stats, st,
-                                           pdl=pdl, splits=4, tile_n=64)
-                g.norm_fp8_nt_dev_geglu_fp8(x, stats, 16, p._style("ffn", 0, i), fe.w_gu[i].data_ptr(), p.hid8.data_ptr(),
-                                            S, DEC_H, DEC_D, p._scale_ptr(0, i, "gu"), fe.ws_gu_t[i].data_ptr(),
-                                            p._scale_ptr(0, i, "d"), st, pdl=pdl, splits=2, tile_n=128)
-                g.fp8_nt_dev_gate_residual(p.hid8.data_ptr(), fe.w_d[i].data_ptr(), S, DEC_D, DEC_H, p._scale_ptr(0, i, "d"),
-                                           fe.ws_d_t[i].data_ptr(), x, p._style("ffn", 0, i) + 4 * DEC_D, stats, st,
-                                           pdl=pdl, splits=8, tile_n=64)
+            p._folded_layers(0, st, fe.use_pdl, attention=False)
             return
         for i in range(L):
             for wn, sn, a8, out, N, K in shapes:
@@ -437,7 +419,8 @@ def measure_wan(args, rank, world, local, steps, warm):
     state = synthetic_wan_state(0, layers=1)
     grid, B, T = (13, 30, 52), 2, 512
     model = WanDiTB200(state, grid=grid, batch=B, text_len=T, device=local, tp_rank=rank, tp_size=world,
-                       repeat_blocks=layers, overlap_chunks=args.wan_overlap_chunks)
+                       repeat_blocks=layers, overlap_chunks=args.wan_overlap_chunks,
+                       sequence_parallel=not args.wan_replicated)
     L, D = model.L, model.dim
     g = torch.Generator().manual_seed(1)
     x_host = torch.randn(B, L, D, generator=g).to(torch.bfloat16).pin_memory()
@@ -919,6 +902,9 @@ def main():
                     help="pi05 workload: fp8 = configs[2] (default, the headline), nvfp4 = configs[3]")
     ap.add_argument("--batch", type=int, default=1, help="pi05 workload with --precision nvfp4: chunks per loop (1 or 4)")
     ap.add_argument("--wan-layers", type=int, default=30)
+    ap.add_argument("--wan-replicated", action="store_true",
+                    help="wan workload under TP: replicated residual stream with an all-reduce per row-parallel "
+                         "projection instead of the sequence-parallel stream (all-gather / reduce-scatter)")
     ap.add_argument("--wan-overlap-chunks", type=int, default=int(os.environ.get("FRT_WAN_CHUNKS", "4")),
                     help="wan workload under TP: pieces per row-parallel GEMM whose all-reduce overlaps the next piece")
     args = ap.parse_args()

@@ -72,7 +72,8 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t* o_full = bars + 11;     // PV of a chunk has completed (read only where the count is known to within one)
     uint64_t* o_done = bars + 12;     // every PV of this CTA has completed
     uint64_t* c_full = bars + 13;     // the C column slices of the combine have landed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* q_part = bars + 14;     // [3] the second .. fourth 64-column block of Q (q_full covers the first)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
@@ -110,6 +111,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc::mbar_init(o_full, 1);
         tc::mbar_init(o_done, 1);
         tc::mbar_init(c_full, 1);
+        for (int i = 0; i < 3; ++i) tc::mbar_init(&q_part[i], 1);
         *abort_flag = 0;
         tc::mbar_fence_init();
         tc::tma_prefetch_desc(&tmQ);
@@ -147,9 +149,13 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         pdl_wait();
         ATT_STAMP_ANY(1);
-        tc::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-        for (int db = 0; db < 4; ++db)
-            tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, q_full, db * 64, 0, hk, tok0, b);
+        // Q arrives as four 64-column blocks, each on its own barrier: the first chunk's Q.K^T starts on the first block
+        // while the others are still in flight
+        for (int db = 0; db < 4; ++db) {
+            uint64_t* qb = db == 0 ? q_full : &q_part[db - 1];
+            tc::mbar_arrive_expect_tx(qb, Cfg::Q_BYTES / 4);
+            tc::tma_load_5d(sQ + db * (128 * 128), &tmQ, qb, db * 64, 0, hk, tok0, b);
+        }
         for (int j = early; j < nchunks && !*abort_flag; ++j) {
             if (j >= 2) ATTN_WAIT(&kv_empty[j & 1], (uint32_t)(((j >> 1) - 1) & 1), AERR_PRODUCER);
             if (*abort_flag) break;
@@ -166,9 +172,15 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint64_t dk = dk_base + (uint64_t)((j & 1) * (Cfg::KV_BYTES >> 4));
             const uint32_t d_tm = tmem + Cfg::S_COL + (j & 1) * 64;
 #pragma unroll
-            for (int k = 0; k < D / 16; ++k)
+            for (int k = 0; k < D / 16; ++k) {
+                if (j == 0 && k > 0 && (k % 4) == 0) {          // next 64-column block of Q (first chunk only)
+                    ATTN_WAIT(&q_part[k / 4 - 1], 0u, AERR_MMA);
+                    if (*abort_flag) return;
+                    tc::tc_fence_after_sync();
+                }
                 tc::mma_f16(d_tm, dq_base + (uint64_t)((k / 4) * ((128 * 128) >> 4) + 2 * (k % 4)),
                             dk + (uint64_t)((k / 4) * ((BKV * 128) >> 4) + 2 * (k % 4)), idesc_s, k > 0 ? 1u : 0u);
+            }
             tc::mma_commit(&s_full[j & 1]);
         };
         ATTN_WAIT(q_full, 0u, AERR_MMA);

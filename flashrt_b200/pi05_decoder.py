@@ -473,11 +473,15 @@ class Pi05DecoderPipeline(StepIO):
         fe = self.fe
         return fe.fold_norms and fe.batch == 1 and self.M <= 128
 
-    def _folded_layers(self, step, stream, pdl) -> None:
-        """The 18 blocks of one Euler step with five launches each: QKV (adaRMS producer in front, RoPE + split + KV
-        append behind), attention (+ FP8 copy), attention-out (+ gated residual + row statistics), gate|up (adaRMS
-        producer, GeGLU -> FP8), FFN-down (+ gated residual + row statistics).  Layer 0 takes its FP8 input from
-        the norm kernel that follows the in-projection."""
+    def _folded_layers(self, step, stream, pdl, attention: bool = True) -> None:
+        """The 18 blocks of one Euler step with five launches each: QKV (RoPE + split + KV append behind), attention
+        (+ FP8 copy), attention-out (+ gated residual + row statistics), gate|up (GeGLU -> FP8), FFN-down (+ gated
+        residual + row statistics).  The norm in front of QKV / gate|up is folded in one of two ways: the row-parallel
+        projection before it also writes x * (1 + scale) as FP8 and the projection applies 1 / rms and W . shift in its
+        finish (``defer_norm``, the default), or the projection produces its own FP8 operand from the residual rows
+        (the reference's quantisation point).  Layer 0 takes its FP8 input from the norm kernel that follows the
+        in-projection.  ``attention=False`` leaves the attention launches out (the four weight-streaming launches of
+        every block exactly as the loop issues them: what ``bench.py`` times for the roofline)."""
         fe, g = self.fe, self.gemm
         S, L = self.M, fe.layers
         x, stats = self.x.data_ptr(), self.row_stats.data_ptr()
@@ -485,7 +489,7 @@ class Pi05DecoderPipeline(StepIO):
         gate_off = 2 * DEC_D * 2
         n_stat = 0
         # tile width / split-K of the four projections at <= 64 tokens, from per-launch timings of the captured chain
-        # (QKV 64 x 4, attention-out 64 x 4, gate|up 64 + 64 x 2, FFN-down 64 x 8); larger row counts use the
+        # (QKV 64 x 4, attention-out 64 x 8, gate|up 64 + 64 x 2, FFN-down 64 x 8); larger row counts use the
         # library's own choice
         tuned = S <= 64
         defer = fe.defer_norm
@@ -496,7 +500,8 @@ class Pi05DecoderPipeline(StepIO):
         for i in range(L):
             kp, vp, dp = self._kv_dst(i, 0)
             if i == 0:
-                self._norm(None, None, "attn", step, 0, "qkv", stream, pdl, False)
+                if attention:
+                    self._norm(None, None, "attn", step, 0, "qkv", stream, pdl, False)
                 g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
                                         self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                         fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD, stream,
@@ -512,7 +517,8 @@ class Pi05DecoderPipeline(StepIO):
                                              S, DEC_D, self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
                                              fe.rope.data_ptr(), self.q.data_ptr(), kp, vp, qd, kd, kd, DEC_HD,
                                              stream, devpos=dp, pdl=pdl, **t_qkv)
-            self._attention(i, stream, pdl, self._scale_ptr(step, i, "o"))
+            if attention:
+                self._attention(i, stream, pdl, self._scale_ptr(step, i, "o"))
             q8 = (dict(next_scale=self._style("ffn", step, i), q8_out=self.act8.data_ptr(),
                        d_scale_q8=self._raw_ptr(step, i, 1)) if defer else {})
             n_stat = g.fp8_nt_dev_gate_residual(self.attn8.data_ptr(), fe.w_o[i].data_ptr(), S, DEC_D, qd,

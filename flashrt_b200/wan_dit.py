@@ -13,10 +13,16 @@ kernel call sites the reference does contain, ``flash_rt/models/motus/_fp8_swap.
     x  += (gelu_tanh(adaLN(x; e4, e3) W_1 + b_1) W_2 + b_2) * e5         (FP8 GEMMs, GELU fused with the FP8 quantiser)
 
 Tensor parallelism (the reference has none): QKV / cross-Q / W_1 are column-parallel (heads / TP, FFN / TP per
-rank), W_o / W_co / W_2 row-parallel followed by an NCCL all-reduce of the (B*L, D) bf16 partial; the sequence and
-the residual stream are replicated.  The full-width q/k RMSNorms need the sum of squares over all heads: each rank
-forms its partial (one float per row) and a second, tiny all-reduce completes it.  The text keys / values do not
-depend on the latent, so they are projected once per prompt (``set_context``), not per step.
+rank), W_o / W_co / W_2 row-parallel.  The residual stream is SEQUENCE-parallel: every rank keeps M / TP rows of x,
+runs LayerNorm / adaLN / residual / gate on those rows only, all-gathers the FP8 producer output (1 byte per
+element) in front of a column-parallel projection and reduce-scatters the bf16 partial of a row-parallel one
+(half the bytes of the all-reduce it replaces, and no replicated row work).  Rows are owned in an interleaved
+pattern -- block c * TP + r of M / (TP * C) rows belongs to rank r -- so that piece c of the C pieces of a tensor
+is one contiguous range of rows on every rank: the collective of one piece (NCCL, side stream) runs while the
+GEMM of the next piece computes.  ``sequence_parallel=False`` keeps the replicated stream with an all-reduce per
+row-parallel projection.  The full-width q/k RMSNorms need the sum of squares over all heads: each rank forms its
+partial (one float per row) and a tiny all-reduce completes it.  The text keys / values do not depend on the latent,
+so they are projected once per prompt (``set_context``), not per step.
 
 PyTorch provides device memory, streams and ``torch.distributed``; every arithmetic step is a kernel of this library.
 """
@@ -98,7 +104,7 @@ SITES = ("qkv", "o", "cq", "co", "f1", "f2")
 class WanDiTB200:
     def __init__(self, state: dict, *, grid=(13, 30, 52), batch: int = 2, text_len: int = 512, device=0,
                  tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1,
-                 fuse_epilogues: bool = True, overlap_chunks: int = 4):
+                 fuse_epilogues: bool = True, overlap_chunks: int = 4, sequence_parallel: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device)
@@ -170,6 +176,19 @@ class WanDiTB200:
         # (NCCL, side stream) runs while the GEMM of piece c + 1 computes
         self.overlap_chunks = max(1, int(overlap_chunks)) if tp_size > 1 else 1
         self.comm_stream = torch.cuda.Stream(device=self.device) if tp_size > 1 else None
+        # sequence-parallel residual stream: C pieces of tp x Mb rows; needs whole blocks of rows per rank and piece,
+        # each inside one batch element (its modulation rows)
+        self.sp = False
+        if tp_size > 1 and sequence_parallel:
+            for C in (self.overlap_chunks, 4, 2, 1):
+                if C >= 1 and M % (tp_size * C) == 0 and self.L % (M // (tp_size * C)) == 0:
+                    self.sp, self.C, self.Mb = True, C, M // (tp_size * C)
+                    break
+        if self.sp:
+            Ml = self.Mb * self.C
+            self.xl, self.ol = z(Ml, D), z(Ml, D)
+            self.h8l = z(Ml, D, dtype=torch.uint8)
+            self.e2 = z(2, 6, self.B, D)
         self.calibrated = False
         self.launches_per_step = 0
 
@@ -209,6 +228,161 @@ class WanDiTB200:
         done = torch.cuda.Event()
         done.record(self.comm_stream)
         cur.wait_event(done)
+
+    # ---- sequence-parallel pieces ---------------------------------------------------
+    def _piece(self, t, c):
+        """Rows of piece c of a full (M, ...) tensor: the blocks c * tp .. c * tp + tp - 1, one per rank."""
+        n = self.tp * self.Mb
+        return t[c * n:(c + 1) * n]
+
+    def _local(self, t, c):
+        """Rows of this rank's block of piece c inside a local (C * Mb, ...) tensor."""
+        return t[c * self.Mb:(c + 1) * self.Mb]
+
+    def _batch_of(self, c):
+        """Batch element that this rank's block of piece c lies in."""
+        return ((c * self.tp + self.rank) * self.Mb) // self.L
+
+    def _gather_then(self, produce, consume, pending=None):
+        """produce(c) writes this rank's block of piece c into ``h8l``; the block is all-gathered into ``h8`` on the
+        communication stream; consume(c) (main stream) runs once piece c is complete, while piece c + 1 is in flight.
+        ``pending`` = what ``_scatter_after`` returned for the projection in front: its block c is awaited and
+        finished right before produce(c), so the first gather starts while later blocks are still being reduced."""
+        cur = torch.cuda.current_stream()
+        ready = []
+        for c in range(self.C):
+            if pending is not None:
+                cur.wait_event(pending[0][c])
+                pending[1](c)
+            produce(c)
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                torch.distributed.all_gather_into_tensor(self._piece(self.h8, c), self._local(self.h8l, c),
+                                                         group=self.group)
+                done = torch.cuda.Event()
+                done.record(self.comm_stream)
+            ready.append(done)
+        for c in range(self.C):
+            cur.wait_event(ready[c])
+            consume(c)
+
+    def _scatter_after(self, compute, finish):
+        """compute(c) (main stream) writes piece c of the bf16 partial ``o``; it is reduce-scattered into this rank's
+        block of ``ol`` on the communication stream while piece c + 1 computes.  Returns (events, finish) for
+        ``_gather_then`` / ``_flush``: finish(c) consumes block c once its event has fired."""
+        cur = torch.cuda.current_stream()
+        ready = []
+        for c in range(self.C):
+            compute(c)
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                torch.distributed.reduce_scatter_tensor(self._local(self.ol, c), self._piece(self.o, c),
+                                                        group=self.group)
+                done = torch.cuda.Event()
+                done.record(self.comm_stream)
+            ready.append(done)
+        return ready, finish
+
+    def _flush(self, pending):
+        cur = torch.cuda.current_stream()
+        for c in range(self.C):
+            cur.wait_event(pending[0][c])
+            pending[1](c)
+
+    def _step_sequence_parallel(self, x: torch.Tensor, tp_dev: torch.Tensor) -> torch.Tensor:
+        st = torch.cuda.current_stream().cuda_stream
+        B, L, M, D, dl, fl, hl, hd = self.B, self.L, self.M, self.dim, self.dl, self.fl, self.hl, self.hd
+        C, Mb, n = self.C, self.Mb, self.tp * self.Mb
+        xf = x.reshape(M, D)
+        for c in range(C):
+            g0 = (c * self.tp + self.rank) * Mb
+            self._local(self.xl, c).copy_(xf[g0:g0 + Mb])
+        kstr_self = (L * 3 * dl, 3 * dl, hd)
+        ks = (L * dl, dl, hd)
+        kc = (self.T * dl, dl, hd)
+        pending = None
+
+        def adaln(i, site, scale_rows, shift_rows):
+            def produce(c):
+                bi = self._batch_of(c)
+                fvk.ada_layer_norm_fp8(self._local(self.xl, c).data_ptr(), scale_rows[bi].data_ptr(),
+                                       shift_rows[bi].data_ptr(), self._local(self.h8l, c).data_ptr(),
+                                       self._sp(i, site), Mb, D, 1e-6, st)
+            return produce
+
+        def gated(gate_rows):
+            def finish(c):
+                fvk.bias_gate_mul_residual_bf16(self._local(self.xl, c).data_ptr(), self._local(self.ol, c).data_ptr(),
+                                                0, gate_rows[self._batch_of(c)].data_ptr(), Mb, D, st, gate_stride=0)
+            return finish
+
+        def row_parallel(a8, w8, ws, K, site, bias):
+            def compute(c):
+                self._gemm(self._piece(a8, c), w8, ws, self._piece(self.o, c), n, D, K, self._sp(i, site), st, bias=bias)
+            return compute
+
+        for i, b in enumerate(self.blocks):
+            # modulation rows alternate between two buffers: the FFN gate of the block before is still pending
+            e_out = [self.e2[i & 1, j] for j in range(6)]
+            fvk.adaln_modulation6_bf16(tp_dev.data_ptr(), b["modulation"].data_ptr(), *[t.data_ptr() for t in e_out],
+                                       B, 1, D, st)
+            # ---- self-attention
+            self._gather_then(adaln(i, "qkv", e_out[1], e_out[0]),
+                              lambda c: self._gemm(self._piece(self.h8, c), b["qkv8"], b["qkv_s"],
+                                                   self._piece(self.qkv, c), n, 3 * dl, D, self._sp(i, "qkv"), st,
+                                                   bias=b["qkv_b"]), pending)
+            fvk.row_sumsq(self.qkv.data_ptr(), 3 * dl, 0, dl, self.ssq[0].data_ptr(), M, st)
+            fvk.row_sumsq(self.qkv.data_ptr(), 3 * dl, dl, dl, self.ssq[1].data_ptr(), M, st)
+            self._allreduce(self.ssq)
+            fvk.qkv_split_norm_rope_bf16(self.qkv.data_ptr(), b["norm_q"].data_ptr(), b["norm_k"].data_ptr(),
+                                         self.fre.data_ptr(), self.fim.data_ptr(), self.q.data_ptr(),
+                                         self.k.data_ptr(), B, L, hl, hd, L, 1e-6, st,
+                                         ext_ssq_q=self.ssq[0].data_ptr(), ext_ssq_k=self.ssq[1].data_ptr(), full_dim=D)
+            self._attn(self.q, self.k, self.qkv[:, 2 * dl:], self.a, self.a8, self._sp(i, "o"), L, L, ks, kstr_self, st)
+            pending = self._scatter_after(row_parallel(self.a8, b["o8"], b["o_s"], dl, "o", b["o_b"]), gated(e_out[2]))
+            # ---- cross-attention to the text tokens
+            self._gather_then(
+                lambda c: fvk.call("frt_b200_layer_norm", self._local(self.xl, c).data_ptr(), b["norm3_w"].data_ptr(),
+                                   b["norm3_b"].data_ptr(), None, None, 0, self._local(self.h8l, c).data_ptr(), None,
+                                   self._sp(i, "cq"), Mb, D, 1e-6, 0, st),
+                lambda c: self._gemm(self._piece(self.h8, c), b["cq8"], b["cq_s"], self._piece(self.cq, c), n, dl, D,
+                                     self._sp(i, "cq"), st, bias=b["cq_b"]), pending)
+            fvk.row_sumsq(self.cq.data_ptr(), dl, 0, dl, self.ssq[0].data_ptr(), M, st)
+            self._allreduce(self.ssq[0])
+            fvk.rms_norm_ext(self.cq.data_ptr(), dl, b["norm_cq"].data_ptr(), self.ssq[0].data_ptr(),
+                             self.cqn.data_ptr(), dl, M, dl, D, 1e-6, st)
+            self._attn(self.cqn, self.ctx_k[i], self.ctx_v[i], self.a, self.a8, self._sp(i, "co"), L, self.T, kc, kc, st)
+            pending = self._scatter_after(row_parallel(self.a8, b["co8"], b["co_s"], dl, "co", b["co_b"]),
+                                          lambda c: fvk.residual_add(self._local(self.xl, c).data_ptr(),
+                                                                     self._local(self.ol, c).data_ptr(), Mb * D, st))
+            # ---- FFN
+            fused = self.fuse_epilogues and n > 256 and fl >= 128
+
+            def ffn_up(c):
+                if fused:
+                    self.gemm.fp8_nt_dev_bias_gelu_fp8(self._piece(self.h8, c).data_ptr(), b["f18"].data_ptr(),
+                                                       self._piece(self.f8, c).data_ptr(), n, fl, D, self._sp(i, "f1"),
+                                                       b["f1_s"].data_ptr(), b["f1_b"].data_ptr(), self._sp(i, "f2"), st)
+                    self.launches_per_step += 1
+                else:
+                    self._gemm(self._piece(self.h8, c), b["f18"], b["f1_s"], self._piece(self.f1, c), n, fl, D,
+                               self._sp(i, "f1"), st)
+                    fvk.bias_gelu_quantize_fp8_static_bf16(self._piece(self.f1, c).data_ptr(), b["f1_b"].data_ptr(),
+                                                           self._piece(self.f8, c).data_ptr(), self._sp(i, "f2"), n, fl, st)
+            self._gather_then(adaln(i, "f1", e_out[4], e_out[3]), ffn_up, pending)
+            pending = self._scatter_after(row_parallel(self.f8, b["f28"], b["f2_s"], fl, "f2", b["f2_b"]),
+                                          gated(e_out[5]))
+        self._flush(pending)
+        # the updated tokens, gathered once per step
+        out = torch.empty(M, D, dtype=BF16, device=self.device)
+        for c in range(C):
+            torch.distributed.all_gather_into_tensor(self._piece(out, c), self._local(self.xl, c).contiguous(),
+                                                     group=self.group)
+        return out.reshape(B, L, D)
 
     def _attn(self, q, k, v, out, out8, scale_ptr, Sq, Skv, kstr, vstr, st):
         hl, hd = self.hl, self.hd
@@ -257,9 +431,11 @@ class WanDiTB200:
         """x (B, L, D) latent tokens, time_proj (B, 6, D) fp32 -> updated tokens (B, L, D) bf16 (all 30 blocks)."""
         st = torch.cuda.current_stream().cuda_stream
         B, L, M, D, dl, fl, hl, hd = self.B, self.L, self.M, self.dim, self.dl, self.fl, self.hl, self.hd
-        self.x.copy_(x.reshape(M, D))
         self.launches_per_step = 0
         tp_dev = time_proj.to(self.device, torch.float32).reshape(B, 1, 6, D).contiguous()
+        if self.sp and not calibrate:
+            return self._step_sequence_parallel(x.to(self.device, BF16), tp_dev)
+        self.x.copy_(x.reshape(M, D))
         e_out = [self.e[j] for j in range(6)]
         kstr_self = (L * 3 * dl, 3 * dl, hd)
         for i, b in enumerate(self.blocks):
@@ -357,8 +533,9 @@ class WanDiTB200:
                                             0, gate_rows[bi].data_ptr(), L, D, st, gate_stride=0)
 
     def calibrate(self, x: torch.Tensor, time_proj: torch.Tensor) -> None:
-        """One eager pass that measures the per-site activation scales (amax / 448); under tensor parallelism the
-        scales of replicated activations agree across ranks by construction, those of sharded ones are local."""
+        """One eager pass that measures the per-site activation scales (amax / 448).  It runs on the replicated
+        residual stream (all-reduce form) also when the timed step is sequence-parallel: the scales of replicated
+        activations then agree across ranks by construction, those of head- / column-sharded ones are local."""
         self.scales.zero_()
         self.step(x, time_proj, calibrate=True)
         self.scales.clamp_(min=1e-12)

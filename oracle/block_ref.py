@@ -236,11 +236,17 @@ class Fp8Linears:
     activations: static per-site per-step scales, x * (1 / s) clamped to +-448 and rounded to E4M3,
     csrc/kernels/quantize.cu:61-75; product on the dequantised values in fp32, result rounded to bf16,
     csrc/gemm/gemm_runner.cu:263-272).  ``act_scale``: the (steps, layers, 4) table of the device model, sites in
-    the order qkv, o, gate|up, down."""
+    the order qkv, o, gate|up, down.
+
+    ``raw_scale`` ((steps, layers, 2), optional): restates the device loop's DEFERRED ROW SCALE instead of the
+    reference's quantisation point in front of QKV (layers >= 1) and gate|up: the operand is e4m3(x * (1 + scale) /
+    raw_scale) and the projection's result is bf16(acc * rms + W . shift) -- the same sum, since a row's rms commutes
+    with the projection: W . (rms * x * (1 + scale) + shift) = rms * (W . (x * (1 + scale))) + W . shift."""
     SITES = ("qkv", "o", "gu", "d")
 
-    def __init__(self, W: dict, layers: int, act_scale):
+    def __init__(self, W: dict, layers: int, act_scale, raw_scale=None):
         self.scale = torch.as_tensor(act_scale, dtype=torch.float32).cpu()
+        self.raw_scale = None if raw_scale is None else torch.as_tensor(raw_scale, dtype=torch.float32).cpu()
         self.w = {}
         gate_up = {}
         for name in ("decoder_attn_qkv_w", "decoder_attn_o_w", "decoder_ffn_gate_w", "decoder_ffn_up_w",
@@ -266,6 +272,16 @@ class Fp8Linears:
     def __call__(self, h_q: torch.Tensor, name: str, i: int) -> torch.Tensor:
         return (h_q @ self.w[(name, i)]).to(torch.bfloat16).float()
 
+    def deferred(self, x: torch.Tensor, style_row: torch.Tensor, step: int, i: int, which: int, names, eps=1e-6):
+        """Projections ``names`` of adaRMS(x; style) with the row scale applied behind the product (see the class
+        docstring); x is the bf16-rounded residual.  Returns one bf16-rounded result per name."""
+        scale, shift, _ = style_row.chunk(3, dim=-1)
+        rs = self.raw_scale[step, i, which]
+        inv = torch.tensor(1.0, dtype=torch.float32) / rs
+        u = ((x * (1.0 + scale)) * inv).clamp(-448, 448).to(torch.float8_e4m3fn).float() * rs
+        rms = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        return [((u @ self.w[(n, i)]) * rms + shift @ self.w[(n, i)]).to(torch.bfloat16).float() for n in names]
+
 
 def decoder_block_fp8(x, lin: "Fp8Linears", step: int, i: int, style_attn_row, style_ffn_row, prefix_k, prefix_v,
                       rope_tab):
@@ -275,7 +291,10 @@ def decoder_block_fp8(x, lin: "Fp8Linears", step: int, i: int, style_attn_row, s
     S = x.shape[0]
     bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
     h, gate_a = ada_rms(x, style_attn_row)
-    qkv = lin(lin.act(h, step, i, "qkv"), "decoder_attn_qkv_w", i)
+    if lin.raw_scale is not None and i > 0:
+        (qkv,) = lin.deferred(x, style_attn_row, step, i, 0, ("decoder_attn_qkv_w",))
+    else:
+        qkv = lin(lin.act(h, step, i, "qkv"), "decoder_attn_qkv_w", i)
     q = qkv[:, :DEC_NH * DEC_HD].reshape(S, DEC_NH, DEC_HD)
     k = qkv[:, DEC_NH * DEC_HD:(DEC_NH + DEC_NKV) * DEC_HD].reshape(S, DEC_NKV, DEC_HD)
     v = qkv[:, (DEC_NH + DEC_NKV) * DEC_HD:].reshape(S, DEC_NKV, DEC_HD)
@@ -287,8 +306,12 @@ def decoder_block_fp8(x, lin: "Fp8Linears", step: int, i: int, style_attn_row, s
     o = lin(lin.act(a, step, i, "o"), "decoder_attn_o_w", i)
     x1 = bf(x + o * gate_a)
     h2, gate_f = ada_rms(x1, style_ffn_row)
-    h2q = lin.act(h2, step, i, "gu")
-    hidden = gelu_tanh(lin(h2q, "decoder_ffn_gate_w", i)) * lin(h2q, "decoder_ffn_up_w", i)
+    if lin.raw_scale is not None:
+        g_, u_ = lin.deferred(x1, style_ffn_row, step, i, 1, ("decoder_ffn_gate_w", "decoder_ffn_up_w"))
+        hidden = gelu_tanh(g_) * u_
+    else:
+        h2q = lin.act(h2, step, i, "gu")
+        hidden = gelu_tanh(lin(h2q, "decoder_ffn_gate_w", i)) * lin(h2q, "decoder_ffn_up_w", i)
     f = lin(lin.act(hidden, step, i, "d"), "decoder_ffn_down_w", i)
     return bf(x1 + f * gate_f)
 

@@ -62,10 +62,14 @@ def test_full_depth_every_step_meets_the_bar(full_model):
 
 def test_full_depth_free_running_loop(full_model):
     """18 blocks, ten free-running steps: cosine >= 0.999 at every step; max-abs within 4e-2 x RMS of the fp32 oracle
-    and of the FP8-restated oracle (the E4M3 noise floor, see the module docstring); graph == eager, replays equal."""
+    and of the FP8-restated oracle, with the reference's quantisation points and with the device loop's deferred row
+    scale (the E4M3 noise floor, see the module docstring); graph == eager, replays equal."""
     m = full_model
     _loop_parity(m, max_abs=4e-2)
-    lin = R.Fp8Linears(m["ck"], m["L"], m["model"].frontend.pipeline.act_scale.cpu())
+    p = m["model"].frontend.pipeline
+    lin = R.Fp8Linears(m["ck"], m["L"], p.act_scale.cpu())                               # the reference's rounding points
+    _loop_parity(m, fp8=lin, max_abs=4e-2, replay=False)
+    lin = R.Fp8Linears(m["ck"], m["L"], p.act_scale.cpu(), raw_scale=p.raw_scale.cpu())  # the device loop's own
     _loop_parity(m, fp8=lin, max_abs=4e-2, replay=False)
 
 

@@ -1,5 +1,6 @@
 """GPU test of the tensor-parallel video-DiT step on 2 GPUs of one node (skipped with fewer): heads and FFN columns
-sharded, NCCL all-reduce after the row-parallel projections, result against the fp32 restatement."""
+sharded, residual stream sequence-parallel (all-gather / reduce-scatter per piece) and, for comparison, replicated
+with an NCCL all-reduce after the row-parallel projections; result against the fp32 restatement."""
 import os
 import subprocess
 import sys

@@ -72,6 +72,33 @@ def test_rope_interleave_identity():
     assert torch.allclose(q_il[..., 1::2], q_hf[..., hd // 2:], atol=1e-5)
 
 
+def test_deferred_row_scale_restatement(cfg0):
+    """``Fp8Linears.deferred`` (operand quantised in front of the row scale, 1 / rms and W . shift applied behind the
+    product) is the same sum as quantising the adaRMS output: equal to the un-quantised projection of the normalised
+    rows to FP8 accuracy, and no further from it than the reference's quantisation point."""
+    ck, x = cfg0["ck"], cfg0["x"].to(torch.bfloat16).float()
+    style = torch.randn(3 * R.DEC_D, generator=torch.Generator().manual_seed(5)) * 0.3
+    h, _ = R.ada_rms(x, style)
+    scale = style[:R.DEC_D]
+    act = torch.zeros(1, 1, 4)
+    act[0, 0, 0] = h.abs().max() / 448.0
+    raw = torch.zeros(1, 1, 2)
+    raw[0, 0, 0] = (x * (1 + scale)).abs().max() / 448.0
+    lin = R.Fp8Linears(ck, 1, act, raw_scale=raw)
+    w = lin.w[("decoder_attn_qkv_w", 0)]
+    want = h @ w
+    (got,) = lin.deferred(x, style, 0, 0, 0, ("decoder_attn_qkv_w",))
+    ref_point = lin(lin.act(h, 0, 0, "qkv"), "decoder_attn_qkv_w", 0)
+    rms = float(want.pow(2).mean().sqrt())
+    e_def = float((got - want).pow(2).mean().sqrt()) / rms
+    e_ref = float((ref_point - want).pow(2).mean().sqrt()) / rms
+    assert e_def <= 3e-2 and e_def <= 1.15 * e_ref + 1e-3
+    # without the FP8 rounding the two forms are the same number
+    rs = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+    exact = ((x * (1 + scale)) @ w) * rs + style[R.DEC_D:2 * R.DEC_D] @ w
+    assert torch.allclose(exact, want, rtol=1e-4, atol=1e-4 * rms)
+
+
 def test_time_schedule_and_embedding():
     ts = R.time_schedule(10)
     assert ts[0] == 1.0 and abs(ts[-1] - 0.1) < 1e-6 and len(ts) == 10

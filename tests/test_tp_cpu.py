@@ -1,6 +1,7 @@
 """CPU suite (gloo, world size 2): the host-side tensor-parallel logic of the video-DiT path — weight sharding,
-the all-reduce of row-parallel partial products and of the per-row sums of squares for the full-width q/k RMSNorm —
-reproduces the unsharded arithmetic."""
+the all-reduce of row-parallel partial products and of the per-row sums of squares for the full-width q/k RMSNorm,
+and the sequence-parallel form (interleaved row ownership, all-gather in front of a column-parallel layer,
+reduce-scatter behind a row-parallel one) — reproduces the unsharded arithmetic."""
 import os
 
 import torch
@@ -32,7 +33,22 @@ def _worker(rank, world, port, ret):
     qn = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6) * nq
     n = D // world
     ok2 = torch.allclose(qn_loc, qn[:, rank * n:(rank + 1) * n], atol=1e-5)
-    ret[rank] = bool(ok1 and ok2)
+    # sequence-parallel residual stream: interleaved row ownership (block c * world + r of Mb rows belongs to rank r),
+    # all-gather of piece c in front of a column-parallel layer, reduce-scatter of piece c behind a row-parallel one
+    C, Mb = 2, M // (world * 2)
+    xl = torch.stack([x[(c * world + rank) * Mb:(c * world + rank + 1) * Mb] for c in range(C)])      # (C, Mb, D)
+    out_l = torch.empty(C, Mb, D)
+    for c in range(C):
+        piece = torch.empty(world * Mb, D)
+        dist.all_gather_into_tensor(piece, xl[c].contiguous())
+        ok_piece = torch.equal(piece, x[c * world * Mb:(c + 1) * world * Mb])
+        part = torch.nn.functional.gelu(piece @ shard_rows(w1, rank, world).t(), approximate="tanh") \
+            @ shard_cols(w2, rank, world).t()
+        dist.reduce_scatter_tensor(out_l[c], part)
+        ok1 = ok1 and ok_piece
+    mine = torch.stack([ref[(c * world + rank) * Mb:(c * world + rank + 1) * Mb] for c in range(C)])
+    ok3 = torch.allclose(out_l, mine, atol=1e-4)
+    ret[rank] = bool(ok1 and ok2 and ok3)
     dist.destroy_process_group()
 
 

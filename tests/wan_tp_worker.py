@@ -22,17 +22,32 @@ def main():
     m = WanDiTB200(state, grid=grid, batch=B, text_len=T, device=local, tp_rank=rank, tp_size=world)
     m.set_context(ctx)
     m.calibrate(x, tproj)
-    got = m.step(x, tproj).float().cpu()
-    # the chunked form (all-reduce of one row piece overlapping the GEMM of the next, on a side stream) must give
-    # the same bytes as the plain GEMM -> all-reduce: force pieces small enough for this reduced shape
+    assert m.sp and m.C >= 2, "the reduced shape must exercise the sequence-parallel pieces"
+    got = m.step(x, tproj).float().cpu()                 # sequence-parallel residual stream (the default)
+    again = m.step(x, tproj).float().cpu()
+    ok = bool(torch.equal(got, again))
+    if not ok:
+        print(f"rank {rank}: two sequence-parallel steps differ", flush=True)
+    # replicated residual stream with an all-reduce per row-parallel projection: the chunked form (all-reduce of one
+    # row piece overlapping the GEMM of the next, on a side stream) must give the same bytes as GEMM -> all-reduce
+    m.sp = False
     m.overlap_chunks = 3
     m._min_chunk_rows = 128
     got_chunked = m.step(x, tproj).float().cpu()
     m.overlap_chunks = 1
     got_plain = m.step(x, tproj).float().cpu()
-    ok = bool(torch.equal(got_chunked, got_plain))
-    if not ok:
+    if not torch.equal(got_chunked, got_plain):
+        ok = False
         print(f"rank {rank}: chunked all-reduce differs from the plain one", flush=True)
+    # both forms compute the same sums, but a piece of 192 rows runs through the small-M GEMM kernels (split-K: another
+    # fp32 summation order), so single bf16 results -- and FP8 codes behind them -- differ in the last place
+    rms_plain = got_plain.pow(2).mean().sqrt()
+    d_max = float((got - got_plain).abs().max() / rms_plain)
+    d_rms = float((got - got_plain).pow(2).mean().sqrt() / rms_plain)
+    if rank == 0:
+        print(f"sequence-parallel vs replicated: rms {d_rms:.5f} max {d_max:.4f} (x RMS)", flush=True)
+    if d_rms > 1e-2 or d_max > 0.1:
+        ok = False
     if rank == 0:
         ref = wan_ref.step(x, state, tproj, ctx, cos, sin)
         rms = float(ref.pow(2).mean().sqrt())
