@@ -31,6 +31,11 @@ class VLAModel:
     def calibrated(self) -> bool:
         return bool(getattr(self._fe, "calibrated", False))
 
+    @property
+    def precision_spec(self):
+        """The frontend's quantisation record (``flash_rt/api.py:286-290``), ``None`` if it keeps none yet."""
+        return getattr(self._fe, "precision_spec", None)
+
     def set_prefix(self, prefix_k, prefix_v) -> None:
         self._fe.set_prefix(prefix_k, prefix_v)
 

@@ -87,6 +87,16 @@ __device__ __forceinline__ float det_gelu_tanh(float g) {
     return __fdiv_rn(g, __fadd_rn(1.0f, e));
 }
 
+// SiLU: g * sigmoid(g) = g / (1 + exp(-g))  (silu_mul_split_fp8_kernel, csrc/kernels/activation.cu:291-306)
+__device__ __forceinline__ float det_silu(float g) {
+    return __fdiv_rn(g, __fadd_rn(1.0f, det_expf(-g)));
+}
+// gate activation of the gated FFN epilogues: 0 = GELU(tanh) (GeGLU), 1 = SiLU (SwiGLU)
+template <int ACT>
+__device__ __forceinline__ float det_gate_act(float g) {
+    return ACT == 1 ? det_silu(g) : det_gelu_tanh(g);
+}
+
 // ---------------------------------------------------------------- reductions
 // xor-butterfly: every lane ends with the same value; tree order is fixed.
 __device__ __forceinline__ float warp_sum_butterfly(float v) {

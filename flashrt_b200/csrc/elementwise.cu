@@ -50,6 +50,7 @@ static int launch(K kernel, unsigned grid, unsigned block, cudaStream_t stream, 
 
 // ------------------------------------------------------------------ GeGLU -> FP8
 // merged row = [gate(0..H) | up(H..2H)] bf16; out (rows, H) fp8.
+template <int ACT>
 __global__ void __launch_bounds__(256)
 geglu_fp8_kernel(const __nv_bfloat16* __restrict__ merged, uint8_t* __restrict__ out, int rows, int H,
                  const float* __restrict__ d_scale) {
@@ -72,8 +73,8 @@ geglu_fp8_kernel(const __nv_bfloat16* __restrict__ merged, uint8_t* __restrict__
             float g0, g1, u0, u1;
             unpack_bf16x2(gw[k], g0, g1);
             unpack_bf16x2(uw[k], u0, u1);
-            o[2 * k] = clamp448(__fmul_rn(__fmul_rn(det_gelu_tanh(g0), u0), inv_scale));
-            o[2 * k + 1] = clamp448(__fmul_rn(__fmul_rn(det_gelu_tanh(g1), u1), inv_scale));
+            o[2 * k] = clamp448(__fmul_rn(__fmul_rn(det_gate_act<ACT>(g0), u0), inv_scale));
+            o[2 * k + 1] = clamp448(__fmul_rn(__fmul_rn(det_gate_act<ACT>(g1), u1), inv_scale));
         }
         uint2 ov;
         ov.x = f32x4_to_e4m3x4(o[0], o[1], o[2], o[3]);
@@ -84,6 +85,7 @@ geglu_fp8_kernel(const __nv_bfloat16* __restrict__ merged, uint8_t* __restrict__
 }
 
 // merged -> bf16 (non-quantised sibling, reference gate_geglu_merged)
+template <int ACT>
 __global__ void __launch_bounds__(256)
 geglu_bf16_kernel(const __nv_bfloat16* __restrict__ merged, __nv_bfloat16* __restrict__ out, int rows, int H) {
     pdl_wait();
@@ -105,7 +107,7 @@ geglu_bf16_kernel(const __nv_bfloat16* __restrict__ merged, __nv_bfloat16* __res
             float g0, g1, u0, u1;
             unpack_bf16x2(gw[k], g0, g1);
             unpack_bf16x2(uw[k], u0, u1);
-            ow[k] = pack_bf16x2(__fmul_rn(det_gelu_tanh(g0), u0), __fmul_rn(det_gelu_tanh(g1), u1));
+            ow[k] = pack_bf16x2(__fmul_rn(det_gate_act<ACT>(g0), u0), __fmul_rn(det_gate_act<ACT>(g1), u1));
         }
         st_global_v4(out + row * H + col, ov);
     }
@@ -303,7 +305,10 @@ int frt_b200_geglu_fp8(const void* merged, void* out_fp8, int rows, int half_dim
     if ((half_dim & 7) || mis16(merged) || (reinterpret_cast<uintptr_t>(out_fp8) & 7)) return FRT_ERR_UNSUPPORTED;
     if (rows == 0) return FRT_OK;
     long long items = (long long)rows * (half_dim >> 3);
-    return launch(geglu_fp8_kernel, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
+    if (flags & 2)      // SiLU gate (SwiGLU)
+        return launch(geglu_fp8_kernel<1>, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
+                      (const __nv_bfloat16*)merged, (uint8_t*)out_fp8, rows, half_dim, d_scale);
+    return launch(geglu_fp8_kernel<0>, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
                   (const __nv_bfloat16*)merged, (uint8_t*)out_fp8, rows, half_dim, d_scale);
 }
 
@@ -312,7 +317,10 @@ int frt_b200_geglu_bf16(const void* merged, void* out_bf16, int rows, int half_d
     if ((half_dim & 7) || mis16(merged) || mis16(out_bf16)) return FRT_ERR_UNSUPPORTED;
     if (rows == 0) return FRT_OK;
     long long items = (long long)rows * (half_dim >> 3);
-    return launch(geglu_bf16_kernel, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
+    if (flags & 2)
+        return launch(geglu_bf16_kernel<1>, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
+                      (const __nv_bfloat16*)merged, (__nv_bfloat16*)out_bf16, rows, half_dim);
+    return launch(geglu_bf16_kernel<0>, grid_for(items, 256, 8), 256, (cudaStream_t)stream, flags & 1,
                   (const __nv_bfloat16*)merged, (__nv_bfloat16*)out_bf16, rows, half_dim);
 }
 

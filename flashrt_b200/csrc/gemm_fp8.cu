@@ -1051,7 +1051,8 @@ int frt_b200_gemm_fp8_nt_rope_split(const void* A, const void* W, int M, int K, 
 // gate|up projection with the GeGLU -> FP8 epilogue fused (M <= 256):
 //   W (2*half, K): rows [0, half) = gate, [half, 2*half) = up.  out8 (M, half) =
 //   e4m3(clamp(gelu_tanh(bf16(gate)) * bf16(up) * (1 / *d_out_scale), +-448)).  half % 64 == 0.
-// Byte-identical to frt_b200_gemm_fp8_nt followed by frt_b200_geglu_fp8.
+// Byte-identical to frt_b200_gemm_fp8_nt followed by frt_b200_geglu_fp8.  flags bit 6: SiLU gate instead of GELU
+// (SwiGLU; M <= 128, K % 128 == 0: the token-major kernel), byte-identical to frt_b200_geglu_fp8 with its bit 1.
 int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int M, int half, int K,
                                    const float* d_scale_a, const float* d_scale_b, const float* d_out_scale,
                                    int splits, int flags, void* stream) {
@@ -1068,13 +1069,15 @@ int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int
     p.out8 = (uint8_t*)out8;
     p.out_scale = d_out_scale;
     p.half = half;
+    const bool silu = (flags & 64) != 0;     // SiLU gate: built in the token-major kernel only
+    if (silu && !(tok_eligible(M, p.N, K, flags) && M <= 128)) return FRT_ERR_UNSUPPORTED;
     if (tok_eligible(M, p.N, K, flags) && M <= 128 && (half % 64) == 0) {
         TokParams t = {};
         t.M = M; t.N = p.N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
-        t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
+        t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half; t.gate_act = silu ? 1 : 0;
         int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
                                                               flags & 1, (cudaStream_t)stream);
-        if (rc != FRT_ERR_UNSUPPORTED) return rc;
+        if (rc != FRT_ERR_UNSUPPORTED || silu) return rc;
     }
     return dispatch_small_m<EPI_GEGLU_FP8>(A, W, p, K, M, half / 64, splits, flags & 1, (cudaStream_t)stream);
 }

@@ -77,6 +77,7 @@ struct TokParams {
     uint8_t* out8;
     const float* out_scale;
     int half;
+    int gate_act;              // 0 = GELU(tanh) gate (GeGLU), 1 = SiLU gate (SwiGLU)
     // TOK_EPI_RESID: residual (M, N) bf16 in/out, gate (N,), stats_out [tile][TOK_STAT_STRIDE] (may be null)
     __nv_bfloat16* resid;
     const __nv_bfloat16* gate;
@@ -666,7 +667,8 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int j = 0; j < 8; ++j) {
                         const float gt = __bfloat162float(__float2bfloat16_rn(a[j]));
                         const float up = __bfloat162float(__float2bfloat16_rn(b[j]));
-                        q[j] = clamp448(__fmul_rn(__fmul_rn(det_gelu_tanh(gt), up), inv_os));
+                        const float act = p.gate_act ? det_silu(gt) : det_gelu_tanh(gt);
+                        q[j] = clamp448(__fmul_rn(__fmul_rn(act, up), inv_os));
                     }
                     uint2 o8;
                     o8.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);

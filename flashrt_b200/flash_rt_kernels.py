@@ -114,6 +114,18 @@ def gate_geglu_merged_fp8(merged, out, seq, half_dim, d_scale=0, stream=0, *, pd
     call("frt_b200_geglu_fp8", merged, out, seq, half_dim, d_scale, _f(pdl), stream)
 
 
+def gate_swiglu_merged(merged, out, seq, half_dim, stream=0, *, pdl=False):
+    """silu(gate) * up of a merged (seq, 2 * half_dim) bf16 buffer -> bf16: the arithmetic of the reference's
+    ``silu_mul_split_fp8_fp16`` family (csrc/kernels/activation.cu:291-306) on the [gate | up] layout of
+    ``gate_geglu_merged``."""
+    call("frt_b200_geglu_bf16", merged, out, seq, half_dim, _f(pdl) | 2, stream)
+
+
+def gate_swiglu_merged_fp8(merged, out, seq, half_dim, d_scale, stream=0, *, pdl=False):
+    """The same with the static FP8 quantisation of ``gate_geglu_merged_fp8`` behind it."""
+    call("frt_b200_geglu_fp8", merged, out, seq, half_dim, d_scale, _f(pdl) | 2, stream)
+
+
 # ------------------------------------------------------------------ RoPE (csrc/bindings.cpp:1071-1099)
 def qkv_split_rope(qkv, rope_weights, Q, K, V, seq, q_dim, k_dim, v_dim, head_dim, stream=0, *, pdl=False):
     call("frt_b200_qkv_split_rope", qkv, rope_weights, Q, K, V, None, seq, q_dim, k_dim, v_dim, head_dim, _f(pdl),
@@ -319,10 +331,11 @@ class GemmRunner:
              _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_geglu_fp8(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, stream=0, *,
-                             pdl=False, splits=0, swapped=False, tile_n=0):
-        """``fp8_nt_dev`` into a merged (M, 2*half) buffer followed by ``gate_geglu_merged_fp8``, in one launch."""
+                             pdl=False, splits=0, swapped=False, tile_n=0, silu_gate=False):
+        """``fp8_nt_dev`` into a merged (M, 2*half) buffer followed by ``gate_geglu_merged_fp8``, in one launch.
+        ``silu_gate``: SiLU instead of GELU on the gate (``gate_swiglu_merged_fp8`` behind the GEMM; M <= 128)."""
         call("frt_b200_gemm_fp8_nt_geglu_fp8", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, splits,
-             _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
+             _f(pdl) | (16 if swapped else 0) | (64 if silu_gate else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
                    tile_n=0):

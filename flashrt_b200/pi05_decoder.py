@@ -780,10 +780,31 @@ class Pi05DecoderB200:
             raise RuntimeError("a tensor-core kernel reported a timed-out wait during calibration")
         p.calibrated = True
         self.graph = None
+        self._calibration_record = dict(method="max" if percentile is None else "percentile", samples=len(noises),
+                                        percentile=percentile)
         if cacheable:
             cc.save_calibration(self.checkpoint_path, self.prefix_len,
                                 torch.cat([t.flatten() for t in tables]).cpu().tolist(),
                                 metadata=self._cache_meta(len(noises), percentile), cache_dir=cache_dir)
+
+    @property
+    def precision_spec(self):
+        """:class:`flashrt_b200.precision_spec.ModelPrecisionSpec` of the calibrated model (``None`` before), the record the
+        reference's frontend keeps at calibration time (flash_rt/frontends/torch/pi05_rtx.py:1480-1545)."""
+        if not self.calibrated:
+            return None
+        from .precision_spec import snapshot_decoder
+        p, rec = self.pipeline, getattr(self, "_calibration_record", dict(method="cache", samples=0, percentile=None))
+        if self.precision == "nvfp4":
+            names = {f"decoder_{k}_w_{i}": None for i in range(self.layers) for k in ("attn_qkv", "attn_o", "ffn_gate_up",
+                                                                                      "ffn_down")}
+            return snapshot_decoder(None, SITES, names, precision="nvfp4", method=rec["method"], samples=rec["samples"],
+                                    percentile=rec["percentile"])
+        weights = {"decoder_attn_qkv_w": self.ws_qkv_t.cpu().numpy(), "decoder_attn_o_w": self.ws_o_t.cpu().numpy(),
+                   "decoder_ffn_gate_up_w": self.ws_gu_t.cpu().numpy(), "decoder_ffn_down_w": self.ws_d_t.cpu().numpy()}
+        return snapshot_decoder(p.act_scale.cpu().numpy(), SITES, weights, precision="fp8", method=rec["method"],
+                                samples=rec["samples"], percentile=rec["percentile"],
+                                raw_scale=p.raw_scale.cpu().numpy() if self.defer_norm else None)
 
     # ---- graph --------------------------------------------------------------
     def record_infer_graph(self) -> None:

@@ -63,10 +63,13 @@ int frt_b200_norm_bf16(void* residual, const void* x, const void* gate_in, long 
 /* ---------------------------------------------------------------- activation / quantise
  * gate_geglu_merged_fp8        csrc/bindings.cpp:1037-1044 -> csrc/kernels/activation.cu:249-279
  *   merged (rows, 2*half_dim) bf16 = [gate | up];  out (rows, half_dim) e4m3 =
- *   e4m3(clamp(gelu_tanh(gate) * up * (1 / *d_scale), +-448)).  half_dim % 8 == 0. */
+ *   e4m3(clamp(gelu_tanh(gate) * up * (1 / *d_scale), +-448)).  half_dim % 8 == 0.
+ *   flags bit 1: SiLU gate, silu(gate) * up with silu(g) = g / (1 + exp(-g)) -- the arithmetic of
+ *   silu_mul_split_fp8_kernel (csrc/kernels/activation.cu:291-306; bindings csrc/bindings.cpp:1912-1918) on the merged
+ *   [gate | up] layout (SwiGLU). */
 int frt_b200_geglu_fp8(const void* merged, void* out_fp8, int rows, int half_dim, const float* d_scale,
                        int flags, void* stream);
-/* gate_geglu_merged            csrc/bindings.cpp:1031-1035 (bf16 result) */
+/* gate_geglu_merged            csrc/bindings.cpp:1031-1035 (bf16 result; flags bit 1: SiLU gate as above) */
 int frt_b200_geglu_bf16(const void* merged, void* out_bf16, int rows, int half_dim, int flags, void* stream);
 
 /* quantize_fp8_static          csrc/bindings.cpp:1191-1196 -> csrc/kernels/quantize.cu:61-75,297-304 */
@@ -135,7 +138,9 @@ int frt_b200_gemm_fp8_nt_rope_split(const void* A, const void* W, int M, int K, 
                                     int flags, void* stream);
 /* gate|up projection + gate_geglu_merged_fp8 (csrc/bindings.cpp:1037-1044 -> csrc/kernels/activation.cu:249-279):
  *   W (2*half, K), rows [0, half) = gate, [half, 2*half) = up; out8 (M, half) e4m3 with scale *d_out_scale.
- *   half % 64 == 0.  Byte-identical to frt_b200_gemm_fp8_nt (same `splits`) followed by frt_b200_geglu_fp8. */
+ *   half % 64 == 0.  Byte-identical to frt_b200_gemm_fp8_nt (same `splits`) followed by frt_b200_geglu_fp8.
+ *   flags bit 6: SiLU gate (SwiGLU; M <= 128 and K % 128 == 0 only, else -2), byte-identical to frt_b200_geglu_fp8
+ *   with its flags bit 1 behind the same GEMM. */
 int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int M, int half, int K,
                                    const float* d_scale_a, const float* d_scale_b, const float* d_out_scale,
                                    int splits, int flags, void* stream);

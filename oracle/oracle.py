@@ -135,6 +135,23 @@ def geglu_fp8(merged, scale):
     return out
 
 
+def swiglu_fp8(merged, scale):
+    """silu(gate) * up -> E4M3 on the merged [gate | up] layout (csrc/kernels/activation.cu:291-306)."""
+    merged = _u16(merged)
+    rows, two_h = merged.shape
+    out = np.zeros((rows, two_h // 2), np.uint8)
+    lib().orc_swiglu_fp8(_p(merged), _p(out), C.c_int(rows), C.c_int(two_h // 2), C.c_float(scale))
+    return out
+
+
+def swiglu_bf16(merged):
+    merged = _u16(merged)
+    rows, two_h = merged.shape
+    out = np.zeros((rows, two_h // 2), np.uint16)
+    lib().orc_swiglu_bf16(_p(merged), _p(out), C.c_int(rows), C.c_int(two_h // 2))
+    return out
+
+
 def geglu_bf16(merged):
     merged = _u16(merged)
     rows, two_h = merged.shape

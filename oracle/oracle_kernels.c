@@ -246,6 +246,26 @@ void orc_geglu_fp8(const uint16_t* merged, uint8_t* out, int rows, int H, float 
             out[(size_t)r * H + c] = f32_to_e4m3(clamp448(v));
         }
 }
+/* SiLU gate (SwiGLU): silu_mul_split_fp8_kernel, csrc/kernels/activation.cu:291-306, on the merged [gate | up] layout */
+static float det_silu(float g) { return g / (1.0f + det_expf(-g)); }
+void orc_swiglu_fp8(const uint16_t* merged, uint8_t* out, int rows, int H, float scale) {
+    float inv_scale = 1.0f / scale;
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < H; ++c) {
+            float g = bf16_to_f32(merged[(size_t)r * 2 * H + c]);
+            float u = bf16_to_f32(merged[(size_t)r * 2 * H + H + c]);
+            float v = (det_silu(g) * u) * inv_scale;
+            out[(size_t)r * H + c] = f32_to_e4m3(clamp448(v));
+        }
+}
+void orc_swiglu_bf16(const uint16_t* merged, uint16_t* out, int rows, int H) {
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < H; ++c) {
+            float g = bf16_to_f32(merged[(size_t)r * 2 * H + c]);
+            float u = bf16_to_f32(merged[(size_t)r * 2 * H + H + c]);
+            out[(size_t)r * H + c] = f32_to_bf16(det_silu(g) * u);
+        }
+}
 void orc_geglu_bf16(const uint16_t* merged, uint16_t* out, int rows, int H) {
     for (int r = 0; r < rows; ++r)
         for (int c = 0; c < H; ++c) {

@@ -148,6 +148,22 @@ def test_geglu_fp8_and_bf16(fvk, rows, H):
     assert np.array_equal(d_o16.get(), ref16)
 
 
+@pytest.mark.parametrize("rows,H", [(1, 8), (50, 4096), (333, 1024)])
+def test_swiglu_fp8_and_bf16(fvk, rows, H):
+    """SiLU gate on the merged [gate | up] layout: byte-exact against the C oracle."""
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(rows * 3 + H)
+    merged = _mk(rng, rows, 2 * H, 2.0)
+    merged.reshape(-1)[:6] = O.f32_to_bf16_bits(np.array([0.0, -0.0, 50.0, -50.0, 1e-30, -300.0], np.float32))
+    scale = 0.03
+    d_m, d_o8, d_o16, d_s = Dev(merged), zeros((rows, H), np.uint8), zeros((rows, H), np.uint16), f32(scale)
+    fvk.gate_swiglu_merged_fp8(d_m.ptr, d_o8.ptr, rows, H, d_s.ptr, 0)
+    fvk.gate_swiglu_merged(d_m.ptr, d_o16.ptr, rows, H, 0)
+    assert np.array_equal(d_o8.get(), O.swiglu_fp8(merged, scale))
+    assert np.array_equal(d_o16.get(), O.swiglu_bf16(merged))
+    assert not np.array_equal(d_o16.get(), O.geglu_bf16(merged))
+
+
 @pytest.mark.parametrize("n", [8, 50 * 2048, 50 * 2048 + 3, 1 << 22])
 def test_quantize_fp8_static_and_device(fvk, n):
     from gpu_util import Dev, f32, rand_bf16, zeros

@@ -190,6 +190,32 @@ def test_fused_geglu_epilogue_equals_two_kernels(M, splits):
     assert (d_o2.get() != 0).mean() > 0.5
 
 
+@pytest.mark.parametrize("M,splits", [(50, 2), (16, 4), (128, 1)])
+def test_fused_swiglu_epilogue_equals_two_kernels(M, splits):
+    """SiLU gate in the GEMM epilogue (token-major kernel): the bytes of GEMM -> gate_swiglu_merged_fp8; refused where
+    that kernel does not run."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from flashrt_b200._lib import KernelError
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(M * 5 + splits)
+    K, H = 1024, 2048
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, 2 * H, K, 0.03)
+    d_A, d_W, d_sa, d_sb, d_so = Dev(A), Dev(W), f32(sa), f32(sb), f32(0.004)
+    g = fvk.GemmRunner()
+    d_merged, d_o1, d_o2 = zeros((M, 2 * H), np.uint16), zeros((M, H), np.uint8), zeros((M, H), np.uint8)
+    g.fp8_nt_dev(d_A.ptr, d_W.ptr, d_merged.ptr, M, 2 * H, K, d_sa.ptr, d_sb.ptr, 0, splits=splits)
+    fvk.gate_swiglu_merged_fp8(d_merged.ptr, d_o1.ptr, M, H, d_so.ptr, 0)
+    g.fp8_nt_dev_geglu_fp8(d_A.ptr, d_W.ptr, d_o2.ptr, M, H, K, d_sa.ptr, d_sb.ptr, d_so.ptr, 0, splits=splits,
+                           silu_gate=True)
+    assert fvk.tensor_core_status() == 0
+    assert np.array_equal(d_o1.get(), d_o2.get())
+    assert np.array_equal(d_o2.get(), O.swiglu_fp8(d_merged.get(), 0.004))
+    assert (d_o2.get() != 0).mean() > 0.5
+    with pytest.raises(KernelError):       # more rows than the token-major kernel takes
+        g.fp8_nt_dev_geglu_fp8(d_A.ptr, d_W.ptr, d_o2.ptr, 200, H, K, d_sa.ptr, d_sb.ptr, d_so.ptr, 0, silu_gate=True)
+
+
 @pytest.mark.parametrize("N,K,splits", [(1024, 2048, 16), (1024, 4096, 16), (2560, 1024, 4)])
 def test_split_k_over_large_clusters(N, K, splits):
     from flashrt_b200 import flash_rt_kernels as fvk

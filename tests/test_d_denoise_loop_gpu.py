@@ -124,6 +124,14 @@ def test_full_depth_loop_runs_and_is_finite():
     assert 0.05 < float(np.abs(a).mean()) < 50
     # per step: in-projection, first norm, 18 x (qkv, attention, o, gate|up, down), final norm, out-projection
     assert model.frontend.kernels_per_loop() == 10 * (2 + 5 * 18 + 2)
+    # the quantisation record of the calibrated model: one FP8 entry per (step, layer, GEMM-input site), plus the two
+    # un-normalised operands of the deferred-row-scale loop, and the weight scales
+    spec = model.precision_spec
+    spec.validate()
+    assert len(spec.decoder_layer_specs) == 10 * 18 * (4 + 2) and len(spec.weight_specs) == 4 * 18
+    e = spec.decoder_layer_specs["decoder_ffn_down_w_17__step_9"]
+    assert e.dtype == "fp8_e4m3" and e.calibration_samples == 2
+    assert float(e.scale[0]) == float(model.frontend.pipeline.act_scale[9, 17, 3])
 
 
 def test_refuses_wrong_inputs():

@@ -1,8 +1,11 @@
-"""CPU tests of the on-disk formats: calibration cache (keying, validation, atomic write) and the synthetic
-safetensors checkpoint read back through the weight loader."""
+"""CPU tests of the on-disk formats: calibration cache (keying, validation, atomic write), the synthetic
+safetensors checkpoint read back through the weight loader, and the quantisation record (``precision_spec``) against a
+JSON document written by the reference's own classes."""
 import json
+import os
 
 import numpy as np
+import pytest
 import torch
 
 from flashrt_b200 import calibration_cache as cc
@@ -80,3 +83,45 @@ def test_synthetic_checkpoint_reads_back_through_the_weight_loader(tmp_path):
     c = Target()
     WeightLoader(src, target=c, spec=build_spec(L, 10, "nvfp4")).run()
     assert len(c.wb_qkv) == L and c.wb_qkv[0].shape == (2560, 1024) and c.wb_qkv[0].dtype == torch.bfloat16
+
+
+def test_precision_spec_reads_and_rewrites_the_references_json(tmp_path):
+    """``precision_spec_reference.json`` was written by the reference's own ``ModelPrecisionSpec.to_json``
+    (tests/golden/make_precision_spec_golden.py): the mirror loads it, keeps every field, and writes the same document."""
+    import json
+    from flashrt_b200.precision_spec import ModelPrecisionSpec, PrecisionSpec
+    gold = os.path.join(os.path.dirname(__file__), "golden", "precision_spec_reference.json")
+    m = ModelPrecisionSpec.from_json(gold)
+    m.validate()
+    e = m.decoder_layer_specs["decoder_attn_qkv_w_3__step_7"]
+    assert (e.dtype, e.granularity, e.scheme, e.scale_source) == ("fp8_e4m3", "per_tensor", "symmetric", "calibration")
+    assert e.scale.dtype == np.float32 and abs(float(e.scale[0]) - 0.0123) < 1e-7
+    assert (e.calibration_method, e.calibration_samples, e.calibration_percentile) == ("percentile", 8, 99.9)
+    assert set(m.encoder_layer_specs) == {"encoder_ffn_down_w_0"} and set(m.activation_specs) == {"vision_patch"}
+    assert m.weight_specs["decoder_ffn_down_w_1"].scale_source == "manual"
+    out = str(tmp_path / "again.json")
+    m.to_json(out)
+    assert json.load(open(out)) == json.load(open(gold))
+    # what no kernel computes is refused, as the reference's table refuses what its kernels lack
+    for bad in (dict(dtype="int8"), dict(granularity="per_channel"), dict(dtype="nvfp4"),
+                dict(dtype="nvfp4", granularity="per_group", group_size=32)):
+        with pytest.raises(NotImplementedError):
+            PrecisionSpec(**bad).validate()
+    with pytest.raises(ValueError):
+        PrecisionSpec(group_size=16).validate()
+    with pytest.raises(ValueError):
+        PrecisionSpec(scheme="asymmetric").validate()
+    PrecisionSpec(dtype="nvfp4", granularity="per_group", group_size=16).validate()
+
+
+def test_precision_spec_snapshot_of_a_decoder():
+    from flashrt_b200.precision_spec import snapshot_decoder
+    act = np.arange(2 * 3 * 4, dtype=np.float32).reshape(2, 3, 4) + 1
+    raw = np.ones((2, 3, 2), np.float32) * 0.5
+    spec = snapshot_decoder(act, ("qkv", "o", "gu", "d"), {"decoder_attn_qkv_w": np.array([0.1, 0.2, 0.3], np.float32)},
+                            precision="fp8", method="max", samples=8, percentile=None, raw_scale=raw)
+    spec.validate()
+    assert len(spec.decoder_layer_specs) == 2 * 3 * (4 + 2)
+    assert float(spec.decoder_layer_specs["decoder_ffn_gate_up_w_2__step_1"].scale[0]) == act[1, 2, 2]
+    assert float(spec.decoder_layer_specs["decoder_attn_qkv_w_1__step_0__unnormalised"].scale[0]) == 0.5
+    assert abs(float(spec.weight_specs["decoder_attn_qkv_w_2"].scale[0]) - 0.3) < 1e-7

@@ -174,6 +174,11 @@ def test_geglu_quantize_adds_oracle_vs_plain_formula():
     ref = torch.nn.functional.gelu(m[:, :64].double(), approximate="tanh") * m[:, 64:].double()
     got = torch.from_numpy(O.bf16_bits_to_f32(o16)).double()
     assert (got - ref).abs().max() <= ref.abs().max() * 2.0 ** -8
+    ref = torch.nn.functional.silu(m[:, :64].double()) * m[:, 64:].double()        # the SiLU-gated sibling
+    got = torch.from_numpy(O.bf16_bits_to_f32(O.swiglu_bf16(merged))).double()
+    assert (got - ref).abs().max() <= ref.abs().max() * 2.0 ** -8
+    q = O.e4m3_to_f32(O.swiglu_fp8(merged, 0.05)) * 0.05
+    assert np.abs(q - np.clip(ref.numpy(), -22.4, 22.4)).max() <= np.abs(ref.numpy()).max() * 2.0 ** -4
     x = _bf(rng, (1000,), 3.0)
     s = O.amax_scale(x)
     assert s == np.float32(np.abs(O.bf16_bits_to_f32(x)).max() / np.float32(448.0))
