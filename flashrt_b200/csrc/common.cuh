@@ -116,6 +116,12 @@ __device__ __forceinline__ float warp_max_butterfly(float v) {
     return v;
 }
 
+// Element of every bf16 GEMM epilogue: alpha * acc, or alpha * acc + bias with ONE rounding.  Written out so that every
+// kernel that can serve a shape produces the same bits (the compiler is otherwise free to fuse or not, site by site).
+__device__ __forceinline__ float scale_bias(float acc, float alpha, float bias, bool has_bias) {
+    return has_bias ? __fmaf_rn(acc, alpha, bias) : __fmul_rn(acc, alpha);
+}
+
 // ---------------------------------------------------------------- 16-byte I/O
 __device__ __forceinline__ uint4 ld_global_v4(const void* p) {
     return *reinterpret_cast<const uint4*>(p);

@@ -376,7 +376,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                         for (int j = 0; j < (BN >= 32 ? 32 : 16); ++j) {
                             const int m = col0 + c + j;
                             if (m < p.M)
-                                p.out[(size_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]) * alpha + b);
+                                p.out[(size_t)m * p.N + n] = __float2bfloat16_rn(scale_bias(__uint_as_float(v[j]), alpha, b, p.bias != nullptr));
                         }
                     }
                 }
@@ -396,8 +396,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                                 float f[8];
 #pragma unroll
                                 for (int q = 0; q < 8; ++q) {
-                                    f[q] = __uint_as_float(v[j + q]) * alpha;
-                                    if (p.bias) f[q] += __bfloat162float(p.bias[nb + j + q]);
+                                    f[q] = scale_bias(__uint_as_float(v[j + q]), alpha,
+                                                      p.bias ? __bfloat162float(p.bias[nb + j + q]) : 0.0f, p.bias != nullptr);
                                 }
                                 uint4 o;
                                 o.x = pack_bf16x2(f[0], f[1]);
@@ -408,8 +408,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                             } else {
                                 for (int q = 0; q < 8; ++q)
                                     if (nb + j + q < p.N) {
-                                        float f = __uint_as_float(v[j + q]) * alpha;
-                                        if (p.bias) f += __bfloat162float(p.bias[nb + j + q]);
+                                        const float f = scale_bias(__uint_as_float(v[j + q]), alpha,
+                                                                   p.bias ? __bfloat162float(p.bias[nb + j + q]) : 0.0f,
+                                                                   p.bias != nullptr);
                                         orow[j + q] = __float2bfloat16_rn(f);
                                     }
                             }
@@ -624,8 +625,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                     float f[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        f[j] = a[j] * alpha;
-                        if (p.bias && n + j < p.N) f[j] += __bfloat162float(p.bias[n + j]);
+                        const bool hb = p.bias && n + j < p.N;
+                        f[j] = scale_bias(a[j], alpha, hb ? __bfloat162float(p.bias[n + j]) : 0.0f, hb);
                     }
                     __nv_bfloat16* dst = p.out + (size_t)m * p.N + n;
                     if (n + 8 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
@@ -703,8 +704,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_constant__
                 if (gcol >= p.N) break;
                 const float acc = reduce_ranks<16>(rank_base, S, (uint32_t)(c * 128 + tl) * 4u);
                 if (lrow < p.M) {
-                    float f = acc * alpha;
-                    if (p.bias) f += __bfloat162float(p.bias[gcol]);
+                    const float f = scale_bias(acc, alpha, p.bias ? __bfloat162float(p.bias[gcol]) : 0.0f, p.bias != nullptr);
                     p.out[(size_t)lrow * p.N + gcol] = __float2bfloat16_rn(f);
                 }
             }

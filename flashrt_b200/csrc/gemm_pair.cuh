@@ -215,8 +215,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                             float f[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
-                                f[e] = __uint_as_float(v[j + e]) * alpha;
-                                if (p.bias) f[e] += __bfloat162float(p.bias[nb + j + e]);
+                                f[e] = scale_bias(__uint_as_float(v[j + e]), alpha,
+                                                  p.bias ? __bfloat162float(p.bias[nb + j + e]) : 0.0f, p.bias != nullptr);
                             }
                             uint4 o;
                             o.x = pack_bf16x2(f[0], f[1]);
@@ -227,8 +227,9 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         } else {
                             for (int e = 0; e < 8; ++e)
                                 if (nb + j + e < p.N) {
-                                    float f = __uint_as_float(v[j + e]) * alpha;
-                                    if (p.bias) f += __bfloat162float(p.bias[nb + j + e]);
+                                    const float f = scale_bias(__uint_as_float(v[j + e]), alpha,
+                                                               p.bias ? __bfloat162float(p.bias[nb + j + e]) : 0.0f,
+                                                               p.bias != nullptr);
                                     orow[j + e] = __float2bfloat16_rn(f);
                                 }
                         }

@@ -35,7 +35,10 @@ struct PGemmCfg {
     static constexpr int STAGE_BYTES = L_BYTES + C_BYTES + 2 * SF_BYTES;
     static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
     static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    // bf16 epilogue staging: every epilogue warp owns 32 rows x 128 bytes, through which its 32 x 64 block of results is
+    // turned from "thread = row" (what tcgen05.ld gives) into "8 threads = one 128-byte line" for the global store
+    static constexpr int EPI_STAGE_BYTES = FP4 ? 0 : 8 * 32 * 128;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES;
     static constexpr int SF_COL = 2 * BN;             // NVFP4: 16 scale columns per operand behind the accumulators
     static constexpr int TMEM_COLS = FP4 ? 512 : 2 * BN;   // BN in {128, 256}
     static constexpr int EPI_THREADS = 256;
@@ -184,6 +187,11 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         if (p.sa) alpha *= *p.sa;
         if (p.sb) alpha *= *p.sb;
         const float inv_os = (EPI == EPI_P_BIAS_GELU_FP8) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+        // whole 128-byte lines per store instruction when rows and column blocks are 16-byte aligned
+        const bool lines = EPI == EPI_P_BF16 && Cfg::EPI_STAGE_BYTES > 0 && (p.N % 8) == 0 &&
+                           (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+                           (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+        uint8_t* stg = smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * (32 * 128);
         int i = 0;
         for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
             const int buf = i & 1;
@@ -197,6 +205,51 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             const int m = (t % m_tiles) * 128 + q * 32 + lane;
             const int n0 = (t / m_tiles) * BN + half * (BN / 2);
             const uint32_t t_src = tmem + buf * BN + half * (BN / 2) + lane_off;
+            if (lines) {
+                const int m_base = (t % m_tiles) * 128 + q * 32;
+#pragma unroll 1
+                for (int c = 0; c < BN / 2; c += 64) {
+                    uint32_t v[64];
+                    tc::tmem_ld32(t_src + c, v);
+                    tc::tmem_ld32(t_src + c + 32, v + 32);
+                    tc::tmem_ld_wait();
+                    const int nb = n0 + c;
+                    // this thread's row: 64 results -> bf16 -> eight 16-byte chunks, chunk index xor (row & 7)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        float f[8];
+                        uint4 bv = make_uint4(0, 0, 0, 0);
+                        const bool has_b = p.bias && nb + 8 * k + 8 <= p.N;
+                        if (has_b) bv = ld_global_v4(p.bias + nb + 8 * k);
+                        const uint32_t* bw = &bv.x;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {           // the same expression as the direct path below
+                            f[e] = scale_bias(__uint_as_float(v[8 * k + e]), alpha,
+                                              bf16_bits_to_f32((bw[e >> 1] >> ((e & 1) * 16)) & 0xffffu), has_b);
+                        }
+                        uint4 o;
+                        o.x = pack_bf16x2(f[0], f[1]);
+                        o.y = pack_bf16x2(f[2], f[3]);
+                        o.z = pack_bf16x2(f[4], f[5]);
+                        o.w = pack_bf16x2(f[6], f[7]);
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + ((k ^ (lane & 7)) << 4)) = o;
+                    }
+                    __syncwarp();
+                    // four rows x 128 bytes per instruction
+                    const int ch = lane & 7;
+#pragma unroll
+                    for (int r4 = 0; r4 < 8; ++r4) {
+                        const int row = r4 * 4 + (lane >> 3);
+                        const uint4 o = *reinterpret_cast<const uint4*>(stg + row * 128 + ((ch ^ (row & 7)) << 4));
+                        const int mm = m_base + row, nn = nb + ch * 8;
+                        if (mm < p.M && nn + 8 <= p.N) st_global_v4(p.out + (size_t)mm * p.N + nn, o);
+                    }
+                    __syncwarp();
+                }
+                tc::tc_fence_before_sync();
+                tc::mbar_arrive(&acc_empty[buf]);
+                continue;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN / 2; c += 32) {
                 uint32_t v[32];
@@ -212,8 +265,8 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                                 float f[8];
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
-                                    f[e] = __uint_as_float(v[j + e]) * alpha;
-                                    if (p.bias) f[e] += __bfloat162float(p.bias[nb + j + e]);
+                                    f[e] = scale_bias(__uint_as_float(v[j + e]), alpha,
+                                                      p.bias ? __bfloat162float(p.bias[nb + j + e]) : 0.0f, p.bias != nullptr);
                                 }
                                 uint4 o;
                                 o.x = pack_bf16x2(f[0], f[1]);
@@ -224,8 +277,9 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                             } else {
                                 for (int e = 0; e < 8; ++e)
                                     if (nb + j + e < p.N) {
-                                        float f = __uint_as_float(v[j + e]) * alpha;
-                                        if (p.bias) f += __bfloat162float(p.bias[nb + j + e]);
+                                        const float f = scale_bias(__uint_as_float(v[j + e]), alpha,
+                                                                   p.bias ? __bfloat162float(p.bias[nb + j + e]) : 0.0f,
+                                                                   p.bias != nullptr);
                                         orow[j + e] = __float2bfloat16_rn(f);
                                     }
                             }

@@ -567,11 +567,10 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint32_t* bw = &bv.x;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        f[j] = a[j] * alpha;
-                        if (p.bias) {
-                            if (bvec) f[j] += bf16_bits_to_f32((bw[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
-                            else if (n + j < p.N) f[j] += __bfloat162float(p.bias[n + j]);
-                        }
+                        const bool hb = p.bias && (bvec || n + j < p.N);
+                        const float bj = !hb ? 0.0f : bvec ? bf16_bits_to_f32((bw[j >> 1] >> ((j & 1) * 16)) & 0xffffu)
+                                                         : __bfloat162float(p.bias[n + j]);
+                        f[j] = scale_bias(a[j], alpha, bj, hb);
                     }
                     __nv_bfloat16* dst = p.out + (size_t)m * p.N + n;
                     if (vec) {

@@ -104,7 +104,8 @@ SITES = ("qkv", "o", "cq", "co", "f1", "f2")
 class WanDiTB200:
     def __init__(self, state: dict, *, grid=(13, 30, 52), batch: int = 2, text_len: int = 512, device=0,
                  tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1,
-                 fuse_epilogues: bool = True, overlap_chunks: int = 4, sequence_parallel: bool = True):
+                 fuse_epilogues: bool = True, overlap_chunks: int = 4, sequence_parallel: bool = True,
+                 split_attention: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.device = torch.device("cuda", device)
@@ -179,9 +180,11 @@ class WanDiTB200:
         # sequence-parallel residual stream: C pieces of tp x Mb rows; needs whole blocks of rows per rank and piece,
         # each inside one batch element (its modulation rows)
         self.sp = False
+        self.split_attention = bool(split_attention)
         if tp_size > 1 and sequence_parallel:
             for C in (self.overlap_chunks, 4, 2, 1):
-                if C >= 1 and M % (tp_size * C) == 0 and self.L % (M // (tp_size * C)) == 0:
+                n = M // C if C >= 1 and M % C == 0 else 0          # rows of a piece: whole batch elements or a whole fraction
+                if n and M % (tp_size * C) == 0 and self.L % (M // (tp_size * C)) == 0 and (n % self.L == 0 or self.L % n == 0):
                     self.sp, self.C, self.Mb = True, C, M // (tp_size * C)
                     break
         if self.sp:
@@ -249,6 +252,14 @@ class WanDiTB200:
         ``pending`` = what ``_scatter_after`` returned for the projection in front: its block c is awaited and
         finished right before produce(c), so the first gather starts while later blocks are still being reduced."""
         cur = torch.cuda.current_stream()
+        ready = self._gather(produce, pending)
+        for c in range(self.C):
+            cur.wait_event(ready[c])
+            consume(c)
+
+    def _gather(self, produce, pending=None):
+        """The issuing half of ``_gather_then``: returns one event per piece (its all-gather has completed)."""
+        cur = torch.cuda.current_stream()
         ready = []
         for c in range(self.C):
             if pending is not None:
@@ -264,17 +275,18 @@ class WanDiTB200:
                 done = torch.cuda.Event()
                 done.record(self.comm_stream)
             ready.append(done)
-        for c in range(self.C):
-            cur.wait_event(ready[c])
-            consume(c)
+        return ready
 
-    def _scatter_after(self, compute, finish):
-        """compute(c) (main stream) writes piece c of the bf16 partial ``o``; it is reduce-scattered into this rank's
-        block of ``ol`` on the communication stream while piece c + 1 computes.  Returns (events, finish) for
-        ``_gather_then`` / ``_flush``: finish(c) consumes block c once its event has fired."""
+    def _scatter_after(self, compute, finish, wait=None):
+        """compute(c) (main stream; everything of piece c up to the row-parallel GEMM that writes piece c of the bf16
+        partial ``o``, started once ``wait[c]`` has fired); the piece is reduce-scattered into this rank's block of
+        ``ol`` on the communication stream while piece c + 1 computes.  Returns (events, finish) for ``_gather_then``
+        / ``_flush``: finish(c) consumes block c once its event has fired."""
         cur = torch.cuda.current_stream()
         ready = []
         for c in range(self.C):
+            if wait is not None:
+                cur.wait_event(wait[c])
             compute(c)
             ev = torch.cuda.Event()
             ev.record(cur)
@@ -305,6 +317,11 @@ class WanDiTB200:
         ks = (L * dl, dl, hd)
         kc = (self.T * dl, dl, hd)
         pending = None
+        # attention per piece, so that the reduce-scatter of a piece overlaps the attention of the next one: opt-in
+        # (``split_attention=True``) and only where a piece is whole batch elements.  Parts of a batch element cost the
+        # attention kernel more in partial waves than the overlap returns (2 GPUs, 4 pieces: 346 ms against 320 ms with
+        # one attention launch per block); with whole batch elements (2 pieces) 329 ms against 326 ms on 2 GPUs.
+        split_attn = self.split_attention and n % L == 0 and C > 1
 
         def adaln(i, site, scale_rows, shift_rows):
             def produce(c):
@@ -320,10 +337,23 @@ class WanDiTB200:
                                                 0, gate_rows[self._batch_of(c)].data_ptr(), Mb, D, st, gate_stride=0)
             return finish
 
-        def row_parallel(a8, w8, ws, K, site, bias):
+        def row_parallel(a8, w8, ws, K, site, bias, before=None):
             def compute(c):
+                if before is not None:
+                    before(c)
                 self._gemm(self._piece(a8, c), w8, ws, self._piece(self.o, c), n, D, K, self._sp(i, site), st, bias=bias)
             return compute
+
+        def attend(q, keys, vals, Skv, kstr, vstr, site):
+            """Attention of the query rows of piece c (whole batch elements, or a part of one) against the keys of
+            their batch element(s): its reduce-scatter then overlaps the attention of the next piece."""
+            def run(c):
+                r0 = c * n
+                bi = r0 // L
+                nb, sq = (n // L, L) if n >= L else (1, n)
+                self._attn(q[r0:r0 + n], keys[bi], vals[bi], self.a[r0:r0 + n], self.a8[r0:r0 + n], self._sp(i, site),
+                           sq, Skv, kstr, vstr, st, batch=nb)
+            return run
 
         for i, b in enumerate(self.blocks):
             # modulation rows alternate between two buffers: the FFN gate of the block before is still pending
@@ -342,8 +372,15 @@ class WanDiTB200:
                                          self.fre.data_ptr(), self.fim.data_ptr(), self.q.data_ptr(),
                                          self.k.data_ptr(), B, L, hl, hd, L, 1e-6, st,
                                          ext_ssq_q=self.ssq[0].data_ptr(), ext_ssq_k=self.ssq[1].data_ptr(), full_dim=D)
-            self._attn(self.q, self.k, self.qkv[:, 2 * dl:], self.a, self.a8, self._sp(i, "o"), L, L, ks, kstr_self, st)
-            pending = self._scatter_after(row_parallel(self.a8, b["o8"], b["o_s"], dl, "o", b["o_b"]), gated(e_out[2]))
+            k_b = [self.k[j * L:] for j in range(B)]
+            v_b = [self.qkv[j * L:, 2 * dl:] for j in range(B)]
+            if split_attn:
+                before = attend(self.q, k_b, v_b, L, ks, kstr_self, "o")
+            else:
+                before = None
+                self._attn(self.q, self.k, self.qkv[:, 2 * dl:], self.a, self.a8, self._sp(i, "o"), L, L, ks, kstr_self, st)
+            pending = self._scatter_after(row_parallel(self.a8, b["o8"], b["o_s"], dl, "o", b["o_b"], before=before),
+                                          gated(e_out[2]))
             # ---- cross-attention to the text tokens
             self._gather_then(
                 lambda c: fvk.call("frt_b200_layer_norm", self._local(self.xl, c).data_ptr(), b["norm3_w"].data_ptr(),
@@ -355,8 +392,15 @@ class WanDiTB200:
             self._allreduce(self.ssq[0])
             fvk.rms_norm_ext(self.cq.data_ptr(), dl, b["norm_cq"].data_ptr(), self.ssq[0].data_ptr(),
                              self.cqn.data_ptr(), dl, M, dl, D, 1e-6, st)
-            self._attn(self.cqn, self.ctx_k[i], self.ctx_v[i], self.a, self.a8, self._sp(i, "co"), L, self.T, kc, kc, st)
-            pending = self._scatter_after(row_parallel(self.a8, b["co8"], b["co_s"], dl, "co", b["co_b"]),
+            ck_b = [self.ctx_k[i][j * self.T:] for j in range(B)]
+            cv_b = [self.ctx_v[i][j * self.T:] for j in range(B)]
+            if split_attn:
+                before = attend(self.cqn, ck_b, cv_b, self.T, kc, kc, "co")
+            else:
+                before = None
+                self._attn(self.cqn, self.ctx_k[i], self.ctx_v[i], self.a, self.a8, self._sp(i, "co"), L, self.T, kc, kc,
+                           st)
+            pending = self._scatter_after(row_parallel(self.a8, b["co8"], b["co_s"], dl, "co", b["co_b"], before=before),
                                           lambda c: fvk.residual_add(self._local(self.xl, c).data_ptr(),
                                                                      self._local(self.ol, c).data_ptr(), Mb * D, st))
             # ---- FFN
@@ -373,6 +417,8 @@ class WanDiTB200:
                                self._sp(i, "f1"), st)
                     fvk.bias_gelu_quantize_fp8_static_bf16(self._piece(self.f1, c).data_ptr(), b["f1_b"].data_ptr(),
                                                            self._piece(self.f8, c).data_ptr(), self._sp(i, "f2"), n, fl, st)
+            # FFN-up of every piece, then FFN-down of every piece (running the two GEMMs of a piece back to back, so that its
+            # reduce-scatter overlaps both GEMMs of the next piece, measured slower: 326 against 320 ms on 2 GPUs)
             self._gather_then(adaln(i, "f1", e_out[4], e_out[3]), ffn_up, pending)
             pending = self._scatter_after(row_parallel(self.f8, b["f28"], b["f2_s"], fl, "f2", b["f2_b"]),
                                           gated(e_out[5]))
@@ -384,10 +430,11 @@ class WanDiTB200:
                                                      group=self.group)
         return out.reshape(B, L, D)
 
-    def _attn(self, q, k, v, out, out8, scale_ptr, Sq, Skv, kstr, vstr, st):
+    def _attn(self, q, k, v, out, out8, scale_ptr, Sq, Skv, kstr, vstr, st, batch=None):
         hl, hd = self.hl, self.hd
         qs = (Sq * hl * hd, hl * hd, hd)
-        fa2.fwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 0, 0, 0, self.B, Sq, Skv, hl, hl, hd,
+        fa2.fwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 0, 0, 0,
+                     self.B if batch is None else batch, Sq, Skv, hl, hl, hd,
                      qs, kstr, vstr, qs, 1.0 / math.sqrt(hd), 148, st,
                      out_fp8=out8.data_ptr() if scale_ptr else 0, out_scale=scale_ptr or 0)
         self.launches_per_step += 1

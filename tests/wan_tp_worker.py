@@ -28,6 +28,19 @@ def main():
     ok = bool(torch.equal(got, again))
     if not ok:
         print(f"rank {rank}: two sequence-parallel steps differ", flush=True)
+    # two pieces (whole batch elements) with the attention launched per piece: same arithmetic, other launch shapes
+    m2 = WanDiTB200(state, grid=grid, batch=B, text_len=T, device=local, tp_rank=rank, tp_size=world, overlap_chunks=2,
+                    split_attention=True)
+    m2.set_context(ctx)
+    m2.scales.copy_(m.scales)
+    m2.calibrated = True
+    got2 = m2.step(x, tproj).float().cpu()
+    assert m2.sp and m2.C == 2
+    d2 = float((got2 - got).abs().max() / got.pow(2).mean().sqrt())
+    if d2 > 0.1:
+        ok = False
+        print(f"rank {rank}: per-piece attention differs from the whole launch: {d2:.4f} x RMS", flush=True)
+    del m2
     # replicated residual stream with an all-reduce per row-parallel projection: the chunked form (all-reduce of one
     # row piece overlapping the GEMM of the next, on a side stream) must give the same bytes as GEMM -> all-reduce
     m.sp = False
