@@ -964,7 +964,12 @@ int frt_b200_gemm_fp8_nt(const void* A, const void* W, void* D, int M, int N, in
     const bool pair_pays = tiles256 >= 148 && K >= 2048 && !(flags & 32) && !(flags & 2);
     if (sp == 1 && ((flags & 8) || pair_pays) && N >= 256) return launch_gemm_pair(A, W, p, K, pdl, s);
     if (sp == 1 && !(flags & 2)) {      // flags bit1 keeps the one-tile-per-CTA kernel (for comparison runs)
-        if (N >= 256) return launch_gemm_persistent<256, EPI_P_BF16>(A, W, p, K, pdl, s);
+        // 128-column tiles only where the 256-column tile list leaves more than half of the SMs idle (2048 x 1024: 64
+        // wide tiles for 148 SMs: 9.6 -> 8.6 us); from one wave on the wide tile wins (2048 x 3072 x 3072: 24.9 us wide,
+        // 32.4 us narrow)
+        const long long wide_tiles = (long long)((M + 127) / 128) * ((N + 255) / 256);
+        const bool narrow = N > 64 && wide_tiles * 2 <= device_sm_count();
+        if (N >= 256 && !narrow) return launch_gemm_persistent<256, EPI_P_BF16>(A, W, p, K, pdl, s);
         if (N > 64) return launch_gemm_persistent<128, EPI_P_BF16>(A, W, p, K, pdl, s);
     }
     if (N >= 256) return launch_gemm<256, false, EPI_BF16>(A, W, p, K, sp, pdl, s);
