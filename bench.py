@@ -806,8 +806,23 @@ def run_timeline(args):
     print(hdr, file=sys.stderr)
     for r in rows:
         print(f"{r['kernel']:26s} {r['ctas']:4d}  " + "  ".join(f"{v:8.2f}" for v in r["us"]), file=sys.stderr)
+    # the last attention launch per kv split: medians over the CTAs of a split (4 row tiles x 4 head-dim parts), us since
+    # the launch's first CTA.  Stamps: dependency wait returned, first Q block landed, first S complete, first P written,
+    # P.V complete, partial in registers, partial stored, fenced + CTA barrier, all CTAs of the tile seen, combined, end.
+    a = ta[(ai - 1) % 8]
+    splits, cols = [], (1, 2, 4, 5, 7, 13, 14, 9, 10, 11, 12)
+    if (a[:, 0] > 0).sum() == 128:
+        a0 = a[:, 0].min()
+        print("attention launch per kv split (us): wait returned | Q block | first S | first P | P.V done | in registers | "
+              "stored | fenced | all seen | combined | end", file=sys.stderr)
+        for z in list(range(8)) + ["slowest"]:
+            blk = a if z == "slowest" else a[z * 16:(z + 1) * 16]
+            f = np.max if z == "slowest" else np.median
+            us = [round(float(f(blk[:, c]) - a0) / 1e3, 2) for c in cols]
+            splits.append({"split": z, "us": us})
+            print(f"  split {z!s:8s} " + "  ".join(f"{v:6.2f}" for v in us), file=sys.stderr)
     print(json.dumps({"metric": "operator-graph phase timeline (diagnostic)", "unit": "us", "rows": rows,
-                      "block_us": rows[-1]["us"][-1] - rows[4]["us"][-1]}), flush=True)
+                      "block_us": rows[-1]["us"][-1] - rows[4]["us"][-1], "attention_splits": splits}), flush=True)
 
 
 # ---------------------------------------------------------------------------------------------------------------
