@@ -846,6 +846,15 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
                                        base + FRT_STATIC_O_BYTES + FRT_STATIC_LSE_BYTES, flags, stream);
 }
 
+}  // extern "C"
+namespace frt {
+int* attention_status_device_ptr() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_attn_status) == cudaSuccess ? static_cast<int*>(p) : nullptr;
+}
+}  // namespace frt
+extern "C" {
+
 // returns (and optionally clears) the attention kernels' device status word; 0 = no bounded wait gave up.
 // code 0x11 = TMA producer, 0x12 = MMA issuer, 0x13 = softmax warps.  Synchronises the device.  Clearing a
 // non-zero status also clears the arrival counters of the built-in scratch on the current device (a kernel that

@@ -122,6 +122,11 @@ __device__ __forceinline__ float scale_bias(float acc, float alpha, float bias, 
     return has_bias ? __fmaf_rn(acc, alpha, bias) : __fmul_rn(acc, alpha);
 }
 
+// Device addresses of the three status words (each lives in the translation unit of its kernels); nullptr on error.
+int* gemm_status_device_ptr();
+int* attention_status_device_ptr();
+int* expert_loop_status_device_ptr();
+
 // ---------------------------------------------------------------- 16-byte I/O
 __device__ __forceinline__ uint4 ld_global_v4(const void* p) {
     return *reinterpret_cast<const uint4*>(p);

@@ -292,6 +292,17 @@ cfg_combine_kernel(T* __restrict__ residual, const T* __restrict__ v_cond, const
     pdl_launch_dependents();
 }
 
+// the three status words of the tensor-core kernels into one array (and optionally cleared), in stream order
+__global__ void status_gather_kernel(int* gemm, int* attn, int* loop, int* out, int reset) {
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        out[0] = *gemm;
+        out[1] = *attn;
+        out[2] = *loop;
+        if (reset) { *gemm = 0; *attn = 0; *loop = 0; }
+    }
+}
+
 }  // namespace frt
 
 using namespace frt;
@@ -412,6 +423,27 @@ int frt_b200_cfg_combine_into_residual(void* residual, const void* v_cond, const
                       (float*)residual, (const float*)v_cond, (const float*)v_uncond, beta, n);
     return launch(cfg_combine_kernel<__nv_bfloat16>, grid_for(n, 256, 8), 256, (cudaStream_t)stream, flags & 1,
                   (__nv_bfloat16*)residual, (const __nv_bfloat16*)v_cond, (const __nv_bfloat16*)v_uncond, beta, n);
+}
+
+// Status words of the GEMM, attention and one-launch loop kernels -> out3[0..2] (device ints), as a kernel in stream
+// order: capturable, so a graph can hand the words back together with its results and the host needs no blocking
+// status call after every replay.  reset != 0 clears the words after copying them.
+int frt_b200_status_words_async(int* out3, int reset, int flags, void* stream) {
+    if (!out3) return FRT_ERR_INVALID;
+    static int* ptrs[64][3] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+    if (dev < 0 || dev >= 64) return FRT_ERR_UNSUPPORTED;
+    if (!ptrs[dev][2]) {       // idempotent: concurrent first calls write the same addresses
+        int* a = gemm_status_device_ptr();
+        int* b = attention_status_device_ptr();
+        int* c = expert_loop_status_device_ptr();
+        if (!a || !b || !c) return FRT_ERR_INVALID;
+        ptrs[dev][0] = a; ptrs[dev][1] = b; ptrs[dev][2] = c;
+    }
+    return launch(status_gather_kernel, 1, 32, (cudaStream_t)stream, flags & 1, ptrs[dev][0], ptrs[dev][1], ptrs[dev][2],
+                  out3, reset);
 }
 
 int frt_b200_device_sm_count(void) { return sm_count(); }

@@ -1015,6 +1015,15 @@ int frt_b200_expert_loop_schedule(int G, int cta, int gl, int phase, int att_uni
     return FRT_OK;
 }
 
+}  // extern "C"
+namespace frt {
+int* expert_loop_status_device_ptr() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_loop_status) == cudaSuccess ? static_cast<int*>(p) : nullptr;
+}
+}  // namespace frt
+extern "C" {
+
 // device status word of the persistent loop kernel (0 = no bounded wait ever gave up); code 1 weight producer,
 // 2 MMA issuer, 3 worker, 4 grid barrier, | CTA index << 8.  Synchronises the device.
 int frt_b200_expert_loop_status(int reset) {

@@ -1360,6 +1360,15 @@ int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, in
                                                          flags & 1, (cudaStream_t)stream);
 }
 
+}  // extern "C"
+namespace frt {
+int* gemm_status_device_ptr() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_gemm_status) == cudaSuccess ? static_cast<int*>(p) : nullptr;
+}
+}  // namespace frt
+extern "C" {
+
 // returns and clears the device-side status word of the GEMM kernels (0 = no bounded wait ever gave up)
 int frt_b200_gemm_status(int reset) {
     int v = 0;

@@ -686,6 +686,10 @@ class Pi05DecoderB200:
         self._pinned_out = torch.zeros(rows, ACTION_DIM, dtype=torch.float32).pin_memory()
         self._dev_in = torch.zeros(rows, ACTION_DIM, dtype=torch.float32, device=dev)
         self._dev_out = torch.zeros(rows, ACTION_DIM, dtype=torch.float32, device=dev)
+        # status words of the tensor-core kernels, gathered by the last kernel of the captured loop and read back with
+        # the actions (no blocking status call per inference)
+        self._dev_status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self._pinned_status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.latency_records: list[float] = []
 
     # ---- prefix (what the encoder would have written) ---------------------
@@ -828,6 +832,7 @@ class Pi05DecoderB200:
         p = self.pipeline
         p.noise.copy_(self._dev_in)
         p.transformer_decoder(s.cuda_stream, calibrate=False)
+        fvk.call("frt_b200_status_words_async", self._dev_status.data_ptr(), 0, 0, s.cuda_stream)
         self._dev_out.copy_(p.noise)
 
     def forward_decode_only(self) -> None:
@@ -858,10 +863,12 @@ class Pi05DecoderB200:
         self.forward_decode_only()
         with torch.cuda.stream(self.stream):
             self._pinned_out.copy_(self._dev_out, non_blocking=True)
+            self._pinned_status.copy_(self._dev_status, non_blocking=True)
         self.stream.synchronize()
         # a bounded device-side wait that gave up leaves a status word and garbage actions: never return those
-        status = fvk.tensor_core_status()
+        status = int(self._pinned_status[0]) or int(self._pinned_status[1]) or int(self._pinned_status[2])
         if status != 0:
+            fvk.tensor_core_status()          # clear the sticky words for the next call
             raise fvk.KernelError(f"a tensor-core kernel of the denoise loop gave up a bounded wait (status {status:#x}); "
                                   "the actions of this call are invalid")
         return {"actions": self._pinned_out.numpy().reshape(shape).copy()}
@@ -871,6 +878,7 @@ class Pi05DecoderB200:
         L, N = self.layers, self.num_steps
         p = self.pipeline
         if getattr(p, "loop_args", None) is not None:
-            return 1
-        # in-projection(s), first norm, the blocks, final residual + final norm, out-projection (+ guidance combine)
-        return int(round(N * (p.step_io_launches() + 1 + p.launches_per_layer() * L + 1)))
+            return 2
+        # in-projection(s), first norm, the blocks, final residual + final norm, out-projection (+ guidance combine);
+        # one status-gather launch behind the last step
+        return int(round(N * (p.step_io_launches() + 1 + p.launches_per_layer() * L + 1))) + 1

@@ -193,6 +193,11 @@ int frt_b200_attention_fwd_bf16_static_scratch(const void* Q, const void* K, con
                                                void* stream);
 /* Status word of the attention kernels (0 = no bounded wait gave up); synchronises the device. */
 int frt_b200_attention_status(int reset);
+/* The status words of the GEMM, attention and one-launch loop kernels copied to out3[0..2] (device ints) by a kernel in
+ * stream order (no counterpart in the reference, whose kernels have no bounded waits): a captured graph can return them
+ * with its results instead of the host calling the three blocking status readers after every replay.  reset != 0
+ * clears the words after the copy.  flags bit 0: programmatic dependent launch. */
+int frt_b200_status_words_async(int* out3, int reset, int flags, void* stream);
 /* Diagnostics, no counterpart in the reference: device-timer (%globaltimer, ns) phase stamps of the last 8 launches of
  * the token-major small-M GEMM (gemm_host: 8 launches x 160 CTAs x 16 stamps) and of the head_dim-256 attention kernel
  * (attn_host: 8 x 128 x 16); either pointer may be NULL.  Recorded only by a library built with -DFRT_PHASE_STAMPS

@@ -79,7 +79,7 @@ def test_cfg_loop_matches_fp32_restatement(setup, precision):
     # guidance must matter on this input (the two prefixes differ) ...
     plain = R.denoise_loop(noise_b, s["ck"], cond[0], cond[1], num_steps=10, layers=s["L"])
     assert float((ref_final - plain).abs().max()) > 1e-2
-    assert fe.kernels_per_loop() == 10 * ((2 + 2) + 1 + p.launches_per_layer() * s["L"] + 1)
+    assert fe.kernels_per_loop() == 10 * ((2 + 2) + 1 + p.launches_per_layer() * s["L"] + 1) + 1
 
 
 def test_fp8_batch2_equals_two_single_runs(setup):

@@ -46,7 +46,7 @@ def test_persistent_loop_matches_oracle_and_operator_loop(L, steps, prefix_len, 
     want = ops.predict(noise=noise.numpy())
     got = loop.predict(noise=noise.numpy())
     assert _status() == 0, "a bounded wait inside the loop kernel gave up"
-    assert loop.frontend.kernels_per_loop() == 1
+    assert loop.frontend.kernels_per_loop() == 2        # the loop kernel and the status gather
     assert np.isfinite(got).all()
     ck = R.from_hf_state_dict({k: v.to(torch.bfloat16).float() for k, v in sd.items()}, layers=L)
     ref = R.denoise_loop(noise, ck, pk_b.float(), pv_b.float(), num_steps=steps, layers=L)
