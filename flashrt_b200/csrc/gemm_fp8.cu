@@ -1074,15 +1074,17 @@ int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int
     p.out8 = (uint8_t*)out8;
     p.out_scale = d_out_scale;
     p.half = half;
-    const bool silu = (flags & 64) != 0;     // SiLU gate: built in the token-major kernel only
-    if (silu && !(tok_eligible(M, p.N, K, flags) && M <= 128)) return FRT_ERR_UNSUPPORTED;
+    // SiLU gate (bit 6) and the hardware-tanh GELU (bit 7): built in the token-major kernel only
+    const bool silu = (flags & 64) != 0, fast = (flags & 128) != 0;
+    if (silu && fast) return FRT_ERR_INVALID;
+    if ((silu || fast) && !(tok_eligible(M, p.N, K, flags) && M <= 128)) return FRT_ERR_UNSUPPORTED;
     if (tok_eligible(M, p.N, K, flags) && M <= 128 && (half % 64) == 0) {
         TokParams t = {};
         t.M = M; t.N = p.N; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
-        t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half; t.gate_act = silu ? 1 : 0;
+        t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half; t.gate_act = silu ? 1 : fast ? 2 : 0;
         int rc = dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
                                                               flags & 1, (cudaStream_t)stream);
-        if (rc != FRT_ERR_UNSUPPORTED || silu) return rc;
+        if (rc != FRT_ERR_UNSUPPORTED || silu || fast) return rc;
     }
     return dispatch_small_m<EPI_GEGLU_FP8>(A, W, p, K, M, half / 64, splits, flags & 1, (cudaStream_t)stream);
 }
@@ -1304,7 +1306,7 @@ int frt_b200_gemm_fp8_nt_geglu_fp8_rowscale(const void* A, const void* W, void* 
     if (M == 0) return FRT_OK;
     TokParams t = {};
     t.M = M; t.N = 2 * half; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
-    t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
+    t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half; t.gate_act = (flags & 128) ? 2 : 0;
     t.stats_in = stats_in; t.n_stat = n_stat; t.eps = eps; t.col_term = col_term;
     return dispatch_gemm_tok<TOK_PRO_TMA, TOK_EPI_GEGLU>(A, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),
                                                         flags & 1, (cudaStream_t)stream);
@@ -1353,7 +1355,7 @@ int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, in
     if (M == 0) return FRT_OK;
     TokParams t = {};
     t.M = M; t.N = 2 * half; t.sa = d_scale_a; t.sb = d_scale_b; t.alpha_host = 1.0f;
-    t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half;
+    t.out8 = (uint8_t*)out8; t.out_scale = d_out_scale; t.half = half; t.gate_act = (flags & 128) ? 2 : 0;
     t.x = (const __nv_bfloat16*)x; t.stats_in = stats_in; t.n_stat = n_stat; t.style = (const __nv_bfloat16*)style;
     t.eps = eps;
     return dispatch_gemm_tok<TOK_PRO_NORM, TOK_EPI_GEGLU>(nullptr, W, t, K, tok_bn_hint(flags), tok_split_hint(splits),

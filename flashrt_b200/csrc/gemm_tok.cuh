@@ -57,6 +57,8 @@ struct TokParams {
     int nkb;                   // 128-byte k-blocks per split
     int stages;                // shared-memory ring depth (>= nkb when the A operand is produced in the kernel)
     int per;                   // tokens finished by one rank of the cluster = ceil(tokens of an m-tile / S)
+    int per_magic;             // ceil(65536 / per): row / per == (row * per_magic) >> 16 for row < 128 (no division on the
+                               // path between the last MMA and the first pushed row)
     int ring_bytes;            // bytes of the operand ring / staging area in front of the receive slots
     int m64;                   // one m-tile of at most 64 tokens: M = 64 MMAs over a 64-row A tile (8 KB per k-block), token
                                // 16 i + j on tensor-memory lane 32 i + j; a CTA then leaves room for a neighbour's CTA
@@ -77,7 +79,7 @@ struct TokParams {
     uint8_t* out8;
     const float* out_scale;
     int half;
-    int gate_act;              // 0 = GELU(tanh) gate (GeGLU), 1 = SiLU gate (SwiGLU)
+    int gate_act;              // 0 = GELU(tanh) gate (GeGLU), 1 = SiLU gate (SwiGLU), 2 = GELU(tanh) with the hardware tanh
     // TOK_EPI_RESID: residual (M, N) bf16 in/out, gate (N,), stats_out [tile][TOK_STAT_STRIDE] (may be null)
     __nv_bfloat16* resid;
     const __nv_bfloat16* gate;
@@ -134,6 +136,11 @@ __device__ __forceinline__ void cluster_arrive_release() {
 }
 __device__ __forceinline__ void cluster_wait_acquire() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// column inside a head: a mask for the usual power-of-two head sizes, a division otherwise
+__device__ __forceinline__ int rope_col(int n, int head_dim) {
+    return (head_dim & (head_dim - 1)) == 0 ? (n & (head_dim - 1)) : n % head_dim;
 }
 
 // Sum over the S slots (fixed order) of the 8 received fp32 values of (token t of this rank, columns c8*8 .. +7).
@@ -487,7 +494,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (emit_q8) pre2 = ld_global_v4(p.q8_mod + n);
             } else if (EPI == TOK_EPI_ROPE && n < p.q_dim + p.k_dim) {
                 const int nr = n < p.q_dim ? n : n - p.q_dim;
-                pre0 = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
+                pre0 = ld_global_v4(p.rope + (size_t)m * p.head_dim + rope_col(nr, p.head_dim));
             } else if (EPI == TOK_EPI_BF16 && p.bias && n + 8 <= p.N &&
                        (reinterpret_cast<uintptr_t>(p.bias + n) & 15) == 0) {
                 pre0 = ld_global_v4(p.bias + n);
@@ -512,8 +519,9 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int row = lane < qrows ? quad * qrows + lane : Mt;   // token inside the m-tile (none on the idle lanes)
         if (have_acc && quad * qrows < Mt) {
             const uint32_t trow = tmem_d + ((uint32_t)(quad * 32) << 16);
-            const int owner = row / per < S ? row / per : 0;
-            const uint32_t dst_local = tc::smem_u32(recv) + (uint32_t)(((rank * per + (row % per)) * BN) * 4);
+            const int rq = (row * p.per_magic) >> 16;           // row / per
+            const int owner = rq < S ? rq : 0;
+            const uint32_t dst_local = tc::smem_u32(recv) + (uint32_t)(((rank * per + (row - rq * per)) * BN) * 4);
             const uint32_t dst = tc::dsmem_map(dst_local, (uint32_t)owner);
             const uint32_t bar = tc::dsmem_map(tc::smem_u32(recv_bar), (uint32_t)owner);
 #pragma unroll 1
@@ -611,7 +619,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     uint4 o;
                     if (is_q || is_k) {
                         uint4 tq = pre0;
-                        if (!first) tq = ld_global_v4(p.rope + (size_t)m * p.head_dim + (nr % p.head_dim));
+                        if (!first) tq = ld_global_v4(p.rope + (size_t)m * p.head_dim + rope_col(nr, p.head_dim));
                         const uint32_t* tw = &tq.x;
                         uint32_t* ow = &o.x;
 #pragma unroll
@@ -666,7 +674,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int j = 0; j < 8; ++j) {
                         const float gt = __bfloat162float(__float2bfloat16_rn(a[j]));
                         const float up = __bfloat162float(__float2bfloat16_rn(b[j]));
-                        const float act = p.gate_act ? det_silu(gt) : det_gelu_tanh(gt);
+                        const float act = p.gate_act == 2 ? fast_gelu_tanh(gt) : p.gate_act == 1 ? det_silu(gt) : det_gelu_tanh(gt);
                         q[j] = clamp448(__fmul_rn(__fmul_rn(act, up), inv_os));
                     }
                     uint2 o8;
@@ -808,6 +816,7 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     p.nkb = pl.nkb;
     p.stages = pl.stages;
     p.per = (mt + pl.S - 1) / pl.S;
+    p.per_magic = (65536 + p.per - 1) / p.per;
     p.m64 = (m_tiles == 1 && mt <= 64) ? 1 : 0;
     const bool m64 = p.m64 != 0;
     // the operand ring shrinks until it fits beside the receive slots

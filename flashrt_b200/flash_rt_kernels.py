@@ -288,10 +288,11 @@ class GemmRunner:
              _f(pdl) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_geglu_fp8_rowscale(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, stats, n_stat, col_term,
-                                      d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0, tile_n=0):
-        """gate|up projection of such an operand, ``gate_geglu_merged_fp8`` behind it."""
+                                      d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0, tile_n=0, fast_gelu=False):
+        """gate|up projection of such an operand, ``gate_geglu_merged_fp8`` behind it (``fast_gelu``: the GELU through
+        the hardware tanh)."""
         call("frt_b200_gemm_fp8_nt_geglu_fp8_rowscale", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, stats, n_stat,
-             eps, col_term, d_scale_out, splits, _f(pdl) | _tile_hint(tile_n), stream)
+             eps, col_term, d_scale_out, splits, _f(pdl) | (128 if fast_gelu else 0) | _tile_hint(tile_n), stream)
 
     def norm_fp8_nt_dev_rope_split(self, x, stats, n_stat, style, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc,
                                    Vc, q_dim, k_dim, v_dim, head_dim, stream=0, *, eps=1e-6, devpos=0, pdl=False,
@@ -303,10 +304,10 @@ class GemmRunner:
              _f(pdl) | _tile_hint(tile_n), stream)
 
     def norm_fp8_nt_dev_geglu_fp8(self, x, stats, n_stat, style, B, out, M, half_dim, K, d_scale_a, d_scale_b,
-                                  d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0, tile_n=0):
+                                  d_scale_out, stream=0, *, eps=1e-6, pdl=False, splits=0, tile_n=0, fast_gelu=False):
         """The same producer in front of the gate|up projection, ``gate_geglu_merged_fp8`` behind it."""
         call("frt_b200_norm_gemm_fp8_nt_geglu_fp8", x, stats, n_stat, style, eps, B, out, M, half_dim, K, d_scale_a,
-             d_scale_b, d_scale_out, splits, _f(pdl) | _tile_hint(tile_n), stream)
+             d_scale_b, d_scale_out, splits, _f(pdl) | (128 if fast_gelu else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_gate_res_norm_fp8(self, A, B, M, N, K, d_scale_a, d_scale_b, residual, gate, style, out, d_scale_out,
                                      stream=0, *, eps=1e-6, pdl=False, splits=0):
@@ -331,11 +332,12 @@ class GemmRunner:
              _f(pdl) | (16 if swapped else 0) | _tile_hint(tile_n), stream)
 
     def fp8_nt_dev_geglu_fp8(self, A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, stream=0, *,
-                             pdl=False, splits=0, swapped=False, tile_n=0, silu_gate=False):
+                             pdl=False, splits=0, swapped=False, tile_n=0, silu_gate=False, fast_gelu=False):
         """``fp8_nt_dev`` into a merged (M, 2*half) buffer followed by ``gate_geglu_merged_fp8``, in one launch.
         ``silu_gate``: SiLU instead of GELU on the gate (``gate_swiglu_merged_fp8`` behind the GEMM; M <= 128)."""
         call("frt_b200_gemm_fp8_nt_geglu_fp8", A, B, out, M, half_dim, K, d_scale_a, d_scale_b, d_scale_out, splits,
-             _f(pdl) | (16 if swapped else 0) | (64 if silu_gate else 0) | _tile_hint(tile_n), stream)
+             _f(pdl) | (16 if swapped else 0) | (64 if silu_gate else 0) | (128 if fast_gelu else 0) | _tile_hint(tile_n),
+             stream)
 
     def fp8_nn_dev(self, A, B, D, M, N, K, d_scale_a, d_scale_b, stream=0, *, pdl=False, splits=0, bias=None,
                    tile_n=0):

@@ -140,7 +140,11 @@ int frt_b200_gemm_fp8_nt_rope_split(const void* A, const void* W, int M, int K, 
  *   W (2*half, K), rows [0, half) = gate, [half, 2*half) = up; out8 (M, half) e4m3 with scale *d_out_scale.
  *   half % 64 == 0.  Byte-identical to frt_b200_gemm_fp8_nt (same `splits`) followed by frt_b200_geglu_fp8.
  *   flags bit 6: SiLU gate (SwiGLU; M <= 128 and K % 128 == 0 only, else -2), byte-identical to frt_b200_geglu_fp8
- *   with its flags bit 1 behind the same GEMM. */
+ *   with its flags bit 1 behind the same GEMM.
+ *   flags bit 7 (here and in the _rowscale / norm_gemm forms): GELU(tanh) through the hardware tanh (tanh.approx.f32,
+ *   relative error 2^-11) instead of the explicitly rounded exp + division -- six instructions per value instead of
+ *   thirty in a finish that is bound by them; FP8 codes then agree with the exact form except for single last-place
+ *   flips (the reference's kernel uses the fast __expf itself); same limits as bit 6. */
 int frt_b200_gemm_fp8_nt_geglu_fp8(const void* A, const void* W, void* out8, int M, int half, int K,
                                    const float* d_scale_a, const float* d_scale_b, const float* d_out_scale,
                                    int splits, int flags, void* stream);

@@ -212,9 +212,10 @@ def test_fixed_shape_graph_serves_every_prefix_length(precision):
 
 
 def test_compositions_of_the_norms_agree():
-    """Four compositions of the same block: norm kernels on their own (7 launches per block); folded into the
-    projections around them with the reference's quantisation point (in-kernel norm producer, 5); the default, which
-    quantises in front of the row scale and applies 1 / rms in the next projection's finish (5); and fuse_norm=True
+    """Five compositions of the same block: norm kernels on their own (7 launches per block); folded into the
+    projections around them with the reference's quantisation point (in-kernel norm producer, 5); quantised in front of
+    the row scale with 1 / rms applied in the next projection's finish (5), with the exactly rounded GELU (the
+    default) and with the hardware tanh; and fuse_norm=True
     (projection + gated residual + adaRMS in one 16-CTA-cluster launch).  Same actions to within FP8 rounding."""
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import synthetic_state_dict
@@ -225,7 +226,7 @@ def test_compositions_of_the_norms_agree():
     noise = R.synthetic_noise(1).numpy()
     outs = []
     for kw, per_step in ((dict(fold_norms=False), 2 + 7 * L + 2), (dict(defer_norm=False), 2 + 5 * L + 2),
-                         (dict(), 2 + 5 * L + 2),
+                         (dict(), 2 + 5 * L + 2), (dict(fast_gelu=True), 2 + 5 * L + 2),
                          (dict(fuse_norm=True), 2 + 5 * L + 1 + 2)):
         m = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768, **kw)
         m.set_prefix(pk, pv)

@@ -367,6 +367,30 @@ def test_deferred_row_scale_reproduces_norm_then_projection():
     assert np.abs(got - want).max() <= 6.0 * err_deferred * out_rms + 1e-2
 
 
+@pytest.mark.parametrize("M,splits", [(50, 2), (128, 4)])
+def test_hardware_tanh_gelu_matches_the_exact_finish(M, splits):
+    """flags bit 7: GELU through tanh.approx (2^-11 relative).  The FP8 codes are those of the exact finish except for
+    last-place flips at rounding boundaries; no code moves by more than one step."""
+    from flashrt_b200 import flash_rt_kernels as fvk
+    from gpu_util import Dev, f32, zeros
+    rng = np.random.default_rng(M + splits)
+    K, H = 1024, 4096
+    A, sa = _fp8_operand(rng, M, K, 1.0)
+    W, sb = _fp8_operand(rng, 2 * H, K, 0.03)
+    d_A, d_W, d_sa, d_sb, d_so = Dev(A), Dev(W), f32(sa), f32(sb), f32(0.004)
+    d_exact, d_fast = zeros((M, H), np.uint8), zeros((M, H), np.uint8)
+    g = fvk.GemmRunner()
+    g.fp8_nt_dev_geglu_fp8(d_A.ptr, d_W.ptr, d_exact.ptr, M, H, K, d_sa.ptr, d_sb.ptr, d_so.ptr, 0, splits=splits)
+    g.fp8_nt_dev_geglu_fp8(d_A.ptr, d_W.ptr, d_fast.ptr, M, H, K, d_sa.ptr, d_sb.ptr, d_so.ptr, 0, splits=splits,
+                           fast_gelu=True)
+    assert fvk.tensor_core_status() == 0
+    e, f = d_exact.get(), d_fast.get()
+    assert (e != f).mean() <= 5e-3
+    ve, vf = O.e4m3_to_f32(e), O.e4m3_to_f32(f)
+    assert (np.abs(ve - vf) <= np.abs(ve) * 0.13 + 2.0 ** -9).all()        # one E4M3 step at most
+    assert (e != 0).mean() > 0.5
+
+
 def test_refusals():
     from flashrt_b200 import flash_rt_kernels as fvk
     from flashrt_b200._lib import KernelError
