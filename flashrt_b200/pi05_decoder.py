@@ -384,7 +384,14 @@ class Pi05DecoderPipeline(StepIO):
         S, L, B, CS = self.M, fe.layers, fe.batch, fe.chunk_size    # S = batch * chunk rows
         pdl = fe.use_pdl and not calibrate
         fold = self._folds_norms() and not calibrate
+        fused_io = fold and self._fuses_step_io() and step_hook is None
         for step in range(fe.num_steps):
+            if fused_io:
+                if step == 0:
+                    self._step_boundary(None, 0, stream, pdl)
+                self._folded_layers(step, stream, pdl, first_norm=False)
+                self._step_boundary(step, step + 1 if step + 1 < fe.num_steps else None, stream, pdl)
+                continue
             # C0: action tokens -> width D, + bias
             self._step_in(stream, pdl)
             if fold:
@@ -469,11 +476,26 @@ class Pi05DecoderPipeline(StepIO):
             if step_hook is not None:
                 step_hook(step)
 
+    def _fuses_step_io(self) -> bool:
+        fe = self.fe
+        return fe.fuse_step_io and self._folds_norms() and fe.cfg_beta is None and DEC_D % 256 == 0
+
+    def _step_boundary(self, ending, beginning, stream, pdl) -> None:
+        """One launch between two Euler steps: final norm + out-projection (+ Euler update) of step ``ending`` (None at
+        the start of the loop), in-projection + first norm -> FP8 of step ``beginning`` (None behind the last step)."""
+        fe = self.fe
+        fvk.call("frt_b200_step_boundary", self.x.data_ptr(), self.noise.data_ptr(),
+                 self._style("final", ending) if ending is not None else None, fe.action_out_w.data_ptr(),
+                 fe.action_out_b.data_ptr(), fe.action_in_w.data_ptr(), fe.action_in_b.data_ptr(),
+                 self._style("attn", beginning, 0) if beginning is not None else None, self.act8.data_ptr(),
+                 self._scale_ptr(beginning if beginning is not None else 0, 0, "qkv"), self.M, DEC_D, ACTION_DIM, 1e-6,
+                 1 if pdl else 0, stream)
+
     def _folds_norms(self) -> bool:
         fe = self.fe
         return fe.fold_norms and fe.batch == 1 and self.M <= 128
 
-    def _folded_layers(self, step, stream, pdl, attention: bool = True) -> None:
+    def _folded_layers(self, step, stream, pdl, attention: bool = True, first_norm: bool = True) -> None:
         """The 18 blocks of one Euler step with five launches each: QKV (RoPE + split + KV append behind), attention
         (+ FP8 copy), attention-out (+ gated residual + row statistics), gate|up (GeGLU -> FP8), FFN-down (+ gated
         residual + row statistics).  The norm in front of QKV / gate|up is folded in one of two ways: the row-parallel
@@ -501,7 +523,7 @@ class Pi05DecoderPipeline(StepIO):
         for i in range(L):
             kp, vp, dp = self._kv_dst(i, 0)
             if i == 0:
-                if attention:
+                if attention and first_norm:
                     self._norm(None, None, "attn", step, 0, "qkv", stream, pdl, False)
                 g.fp8_nt_dev_rope_split(self.act8.data_ptr(), fe.w_qkv[i].data_ptr(), S, DEC_D,
                                         self._scale_ptr(step, i, "qkv"), fe.ws_qkv_t[i].data_ptr(),
@@ -596,7 +618,7 @@ class Pi05DecoderB200:
                  prefix_len: int = 768, layers: int = DEC_L, device: int | str = 0, use_pdl: bool = True,
                  use_cuda_graph: bool = True, fuse_epilogues: bool = True, precision: str = "fp8", batch: int = 1,
                  cfg_beta: float | None = None, fixed_shape: bool = False, attn_splits: int = 8,
-                 fuse_norm: bool = False, fold_norms: bool = True, defer_norm: bool = True, fast_gelu: bool = False,
+                 fuse_norm: bool = False, fold_norms: bool = True, defer_norm: bool = True, fast_gelu: bool = False, fuse_step_io: bool = True,
                  persistent_loop: bool = False, **_ignored):
         if not torch.cuda.is_available():
             raise RuntimeError("flashrt_b200 needs a CUDA device (sm_100a); there is no CPU path")
@@ -622,6 +644,9 @@ class Pi05DecoderB200:
         # 6.23 ms), so off by default in favour of the explicitly rounded exp + division that the C oracle restates bit
         # for bit.  Only the folded (token-major) composition has the option.
         self.fast_gelu = bool(fast_gelu) and self.fold_norms
+        # the four launches between two Euler steps (final norm, action out-projection, action in-projection, first norm)
+        # as one launch per step boundary, bit-identical to the four (batch 1 without guidance, folded norms)
+        self.fuse_step_io = bool(fuse_step_io) and self.fold_norms
         # the whole loop as one cooperative kernel (phases separated by grid barriers) instead of 1300 launches
         self.persistent_loop = bool(persistent_loop)
         if self.persistent_loop and precision != "fp8":
@@ -884,6 +909,8 @@ class Pi05DecoderB200:
         p = self.pipeline
         if getattr(p, "loop_args", None) is not None:
             return 2
-        # in-projection(s), first norm, the blocks, final residual + final norm, out-projection (+ guidance combine);
-        # one status-gather launch behind the last step
+        # in-projection(s), first norm, the blocks, final residual + final norm, out-projection (+ guidance combine) --
+        # or one launch per step boundary; one status-gather launch behind the last step
+        if hasattr(p, "_fuses_step_io") and p._fuses_step_io():
+            return int(round(N * p.launches_per_layer() * L)) + (N + 1) + 1
         return int(round(N * (p.step_io_launches() + 1 + p.launches_per_layer() * L + 1))) + 1

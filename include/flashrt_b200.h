@@ -384,6 +384,17 @@ int frt_b200_gemm_nvfp4_nt_rope_split(const void* A, const void* SFA, const void
  *   bf16 (lets the Euler state x <- x + dt*v stay in fp32 across the denoise steps). */
 int frt_b200_gemm_bf16_nn_small(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                                 int accumulate, int io, int flags, void* stream);
+/* The launches between two Euler steps of Pi05Pipeline.transformer_decoder (flash_rt/models/pi05/pipeline_rtx.py:1451-1504)
+ * as one, one CTA per token: final adaRMS (bf16) of the step that ends, action out-projection (GemmRunner::bf16_nn,
+ * csrc/bindings.cpp:662-667) accumulated into the fp32 noise, action in-projection of the step that begins, first
+ * adaRMS -> FP8 of layer 0 (ada_rms_norm_style_fp8).  x (rows, dim) bf16 in/out; noise (rows, 32) fp32 in/out; style rows
+ * = [scale (dim) | shift (dim) | ...] bf16; w_out (dim, 32), w_in (32, dim), biases bf16.  style_prev NULL: second half
+ * only (first step); style_next NULL: first half only (last step).  The same bits as the four separate launches.
+ * action_dim == 32, dim % 256 == 0, dim <= 2048. */
+int frt_b200_step_boundary(void* x, float* noise, const void* style_prev, const void* w_out, const void* b_out,
+                           const void* w_in, const void* b_in, const void* style_next, void* act8,
+                           const float* d_act_scale, int rows, int dim, int action_dim, float eps, int flags,
+                           void* stream);
 /* gpu_copy                     csrc/bindings.cpp:2533-2537  (device-to-device, async on stream) */
 int frt_b200_copy(void* dst, const void* src, long long nbytes, void* stream);
 /* get_sm_version               csrc/bindings.cpp:2447-2453  (returns major*10+minor, 100 on B200) */

@@ -123,7 +123,8 @@ def test_full_depth_loop_runs_and_is_finite():
     assert np.array_equal(a, b)
     assert 0.05 < float(np.abs(a).mean()) < 50
     # per step: in-projection, first norm, 18 x (qkv, attention, o, gate|up, down), final norm, out-projection
-    assert model.frontend.kernels_per_loop() == 10 * (2 + 5 * 18 + 2) + 1       # + the status gather behind the last step
+    # per step 5 launches per block; one launch per step boundary (11); the status gather behind the last step
+    assert model.frontend.kernels_per_loop() == 10 * 5 * 18 + 11 + 1
     # the status words of the tensor-core kernels come back with the actions (gathered by the last kernel of the graph)
     assert model.frontend._pinned_status.tolist()[:3] == [0, 0, 0]
     # the quantisation record of the calibrated model: one FP8 entry per (step, layer, GEMM-input site), plus the two
@@ -212,10 +213,10 @@ def test_fixed_shape_graph_serves_every_prefix_length(precision):
 
 
 def test_compositions_of_the_norms_agree():
-    """Five compositions of the same block: norm kernels on their own (7 launches per block); folded into the
+    """Six compositions of the same block: norm kernels on their own (7 launches per block); folded into the
     projections around them with the reference's quantisation point (in-kernel norm producer, 5); quantised in front of
     the row scale with 1 / rms applied in the next projection's finish (5), with the exactly rounded GELU (the
-    default) and with the hardware tanh; and fuse_norm=True
+    default) and with the hardware tanh, and with the four launches between two steps kept apart; and fuse_norm=True
     (projection + gated residual + adaRMS in one 16-CTA-cluster launch).  Same actions to within FP8 rounding."""
     from flashrt_b200 import load_model
     from flashrt_b200.pi05_decoder import synthetic_state_dict
@@ -225,14 +226,19 @@ def test_compositions_of_the_norms_agree():
     cal = [R.synthetic_noise(100 + j) for j in range(3)]
     noise = R.synthetic_noise(1).numpy()
     outs = []
-    for kw, per_step in ((dict(fold_norms=False), 2 + 7 * L + 2), (dict(defer_norm=False), 2 + 5 * L + 2),
-                         (dict(), 2 + 5 * L + 2), (dict(fast_gelu=True), 2 + 5 * L + 2),
-                         (dict(fuse_norm=True), 2 + 5 * L + 1 + 2)):
+    # launches per loop: per step 2 projections + 2 norms around the blocks, or (folded compositions) one launch per
+    # step boundary; + the status gather behind the last step
+    for kw, launches in ((dict(fold_norms=False), 10 * (2 + 7 * L + 2)), (dict(defer_norm=False), 10 * 5 * L + 11),
+                         (dict(), 10 * 5 * L + 11), (dict(fast_gelu=True), 10 * 5 * L + 11),
+                         (dict(fuse_step_io=False), 10 * (2 + 5 * L + 2)),
+                         (dict(fuse_norm=True), 10 * (2 + 5 * L + 1 + 2))):
         m = load_model(sd, config="pi05", layers=L, num_steps=10, chunk_size=50, prefix_len=768, **kw)
         m.set_prefix(pk, pv)
         m.calibrate(cal)
         outs.append(m.predict(noise=noise))
-        assert m.frontend.kernels_per_loop() == 10 * per_step + 1
+        assert m.frontend.kernels_per_loop() == launches + 1
+    # the step-boundary launch forms every sum in the order of the four launches it replaces: the same bits
+    assert np.array_equal(outs[2], outs[4])
     a = torch.from_numpy(outs[0])
     for o in outs[1:]:
         b = torch.from_numpy(o)
