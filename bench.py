@@ -420,7 +420,7 @@ def measure_wan(args, rank, world, local, steps, warm):
     grid, B, T = (13, 30, 52), 2, 512
     model = WanDiTB200(state, grid=grid, batch=B, text_len=T, device=local, tp_rank=rank, tp_size=world,
                        repeat_blocks=layers, overlap_chunks=args.wan_overlap_chunks,
-                       sequence_parallel=not args.wan_replicated)
+                       sequence_parallel=not args.wan_replicated, fast_gelu=not args.wan_exact_gelu)
     L, D = model.L, model.dim
     g = torch.Generator().manual_seed(1)
     x_host = torch.randn(B, L, D, generator=g).to(torch.bfloat16).pin_memory()
@@ -917,6 +917,8 @@ def main():
                     help="pi05 workload: fp8 = configs[2] (default, the headline), nvfp4 = configs[3]")
     ap.add_argument("--batch", type=int, default=1, help="pi05 workload with --precision nvfp4: chunks per loop (1 or 4)")
     ap.add_argument("--wan-layers", type=int, default=30)
+    ap.add_argument("--wan-exact-gelu", action="store_true",
+                    help="wan workload: the exactly rounded GELU in the fused FFN-up epilogue instead of the hardware tanh")
     ap.add_argument("--wan-replicated", action="store_true",
                     help="wan workload under TP: replicated residual stream with an all-reduce per row-parallel "
                          "projection instead of the sequence-parallel stream (all-gather / reduce-scatter)")

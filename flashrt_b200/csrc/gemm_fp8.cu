@@ -96,6 +96,7 @@ struct GemmParams {
     uint8_t* out8;             // EPI_GEGLU_FP8: (M, half) e4m3 codes
     const float* out_scale;    //   device scalar: quantisation scale of the GeGLU result
     int half;                  //   hidden width; weight rows [0, half) = gate, [half, 2 half) = up
+    int fast_act;              // bias + GELU + FP8 epilogue: GELU through the hardware tanh instead of the exact form
     // NVFP4 kernels: unsigned-E4M3 block scales of both operands in 512-byte atoms (128 rows x 4 blocks)
     const uint8_t* sf_lane;
     const uint8_t* sf_col;
@@ -1211,6 +1212,7 @@ int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8,
     p.kb_total = (K + 127) / 128;
     p.out8 = (uint8_t*)out8;
     p.out_scale = d_out_scale;
+    p.fast_act = (flags & 128) ? 1 : 0;
     if (N >= 256) return launch_gemm_persistent<256, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
     return launch_gemm_persistent<128, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
 }

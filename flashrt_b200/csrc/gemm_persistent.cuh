@@ -295,7 +295,7 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                                 for (int e = 0; e < 8; ++e) {
                                     float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j + e]) * alpha));
                                     if (p.bias) x = __fadd_rn(x, __bfloat162float(p.bias[nb + j + e]));
-                                    g[e] = clamp448(__fmul_rn(gelu_tanh_form_rn(x), inv_os));
+                                    g[e] = clamp448(__fmul_rn(p.fast_act ? fast_gelu_tanh(x) : gelu_tanh_form_rn(x), inv_os));
                                 }
                                 uint2 o8;
                                 o8.x = f32x4_to_e4m3x4(g[0], g[1], g[2], g[3]);

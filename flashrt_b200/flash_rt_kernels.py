@@ -317,11 +317,11 @@ class GemmRunner:
              d_scale_out, eps, splits, _f(pdl), stream)
 
     def fp8_nt_dev_bias_gelu_fp8(self, A, B, out, M, N, K, d_scale_a, d_scale_b, bias, d_scale_out, stream=0, *,
-                                 pdl=False):
+                                 pdl=False, fast_gelu=False):
         """``fp8_nt_dev`` followed by ``bias_gelu_quantize_fp8_static_bf16`` (csrc/bindings.cpp:3427-3440) in one
         launch, M > 256: the video-DiT FFN-up projection writes its FP8 mid-activation directly."""
         call("frt_b200_gemm_fp8_nt_bias_gelu_fp8", A, B, out, M, N, K, d_scale_a, d_scale_b, bias or None,
-             d_scale_out, _f(pdl), stream)
+             d_scale_out, _f(pdl) | (128 if fast_gelu else 0), stream)
 
     # -- fused forms (no reference counterpart as single calls; each equals two reference calls) ------------
     def fp8_nt_dev_rope_split(self, A, B, M, K, d_scale_a, d_scale_b, rope_weights, Q, Kc, Vc, q_dim, k_dim, v_dim,

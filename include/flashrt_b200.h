@@ -322,7 +322,9 @@ int frt_b200_norm_gemm_fp8_nt_geglu_fp8(const void* x, const float* stats_in, in
 /* fp8 GEMM (GemmRunner::fp8_nt_dev, csrc/bindings.cpp:717-727) + bias_gelu_quantize_fp8_static_bf16
  * (csrc/bindings.cpp:3427-3440 -> csrc/quantize/bias_gelu_quantize_fp8.cu:24-49) in one launch, M > 256, N >= 128:
  *   out8 (M, N) e4m3 = clamp(gelu_tanh(bf16(sa * sb * A . W^T) + bias) * (1 / *d_out_scale), +-448)
- * byte-identical to the two separate calls. */
+ * byte-identical to the two separate calls.  flags bit 7: GELU through the hardware tanh (tanh.approx.f32, 2^-11
+ * relative) -- at K = 3072 the exact form (about 36 instructions per value on 8 epilogue warps) takes longer than the
+ * MMAs of the tile; codes then differ from the exact form by single last-place flips. */
 int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8, int M, int N, int K,
                                        const float* d_scale_a, const float* d_scale_b, const void* bias,
                                        const float* d_out_scale, int flags, void* stream);

@@ -292,6 +292,15 @@ def test_gemm_fp8_bias_gelu_epilogue_equals_pair(M, N, K):
     # and against the oracle
     ref = O.bias_gelu_quantize_fp8(d_mid.get(), bias, 0.013)
     assert np.array_equal(d_fused.get(), ref)
+    # GELU through the hardware tanh (flags bit 7): the same codes except for last-place flips at rounding boundaries
+    d_fast = zeros((M, N), np.uint8)
+    g.fp8_nt_dev_bias_gelu_fp8(d_A.ptr, d_W.ptr, d_fast.ptr, M, N, K, d_sa.ptr, d_sb.ptr, d_b.ptr, d_so.ptr, 0,
+                               fast_gelu=True)
+    assert fvk.tensor_core_status() == 0
+    f = d_fast.get()
+    assert (f != ref).mean() <= 5e-3
+    vr, vf = O.e4m3_to_f32(ref), O.e4m3_to_f32(f)
+    assert (np.abs(vr - vf) <= np.abs(vr) * 0.13 + 2.0 ** -9).all()
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(50, 1024, 2048, 0), (50, 1024, 4096, 2), (10, 512, 1024, 1), (64, 1024, 256, 1),
