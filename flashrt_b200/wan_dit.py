@@ -101,6 +101,28 @@ def _q8(w: torch.Tensor, device):
 SITES = ("qkv", "o", "cq", "co", "f1", "f2")
 
 
+# ------------------------------------------------------------------ sequence-parallel row ownership (host logic)
+def sp_layout(rows: int, rows_per_batch: int, tp: int, want_pieces: int):
+    """(pieces C, rows per block Mb) of the sequence-parallel residual stream, or None when the rows do not divide.
+    A tensor of ``rows`` rows is cut into C pieces of tp * Mb rows; block c * tp + r (Mb rows) belongs to rank r.
+    Required: whole blocks, every block inside one batch element (its modulation rows), and a piece made of whole
+    batch elements or a whole fraction of one (attention may be launched per piece).  The largest C not above
+    ``want_pieces`` out of (want_pieces, 4, 2, 1) that satisfies this is taken."""
+    for C in (want_pieces, 4, 2, 1):
+        if C < 1 or C > max(want_pieces, 1) or rows % (tp * C):
+            continue
+        n, mb = rows // C, rows // (tp * C)
+        if rows_per_batch % mb == 0 and (n % rows_per_batch == 0 or rows_per_batch % n == 0):
+            return C, mb
+    return None
+
+
+def sp_block_rows(c: int, rank: int, tp: int, mb: int):
+    """Global rows [first, last) of rank ``rank``'s block of piece ``c``."""
+    first = (c * tp + rank) * mb
+    return first, first + mb
+
+
 class WanDiTB200:
     def __init__(self, state: dict, *, grid=(13, 30, 52), batch: int = 2, text_len: int = 512, device=0,
                  tp_rank: int = 0, tp_size: int = 1, tp_group=None, repeat_blocks: int = 1,
@@ -186,11 +208,9 @@ class WanDiTB200:
         self.sp = False
         self.split_attention = bool(split_attention)
         if tp_size > 1 and sequence_parallel:
-            for C in (self.overlap_chunks, 4, 2, 1):
-                n = M // C if C >= 1 and M % C == 0 else 0          # rows of a piece: whole batch elements or a whole fraction
-                if n and M % (tp_size * C) == 0 and self.L % (M // (tp_size * C)) == 0 and (n % self.L == 0 or self.L % n == 0):
-                    self.sp, self.C, self.Mb = True, C, M // (tp_size * C)
-                    break
+            lay = sp_layout(M, self.L, tp_size, self.overlap_chunks)
+            if lay is not None:
+                self.sp, (self.C, self.Mb) = True, lay
         if self.sp:
             Ml = self.Mb * self.C
             self.xl, self.ol = z(Ml, D), z(Ml, D)
@@ -248,7 +268,7 @@ class WanDiTB200:
 
     def _batch_of(self, c):
         """Batch element that this rank's block of piece c lies in."""
-        return ((c * self.tp + self.rank) * self.Mb) // self.L
+        return sp_block_rows(c, self.rank, self.tp, self.Mb)[0] // self.L
 
     def _gather_then(self, produce, consume, pending=None):
         """produce(c) writes this rank's block of piece c into ``h8l``; the block is all-gathered into ``h8`` on the

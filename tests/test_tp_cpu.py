@@ -59,3 +59,28 @@ def test_tensor_parallel_host_logic_world_size_2():
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world))
+
+
+def test_sequence_parallel_row_ownership():
+    """Host logic of the sequence-parallel stream: every row is owned exactly once, a block never straddles a batch
+    element, a piece is one contiguous range on every rank, and the shapes of the benchmark pick the expected layout."""
+    from flashrt_b200.wan_dit import sp_block_rows, sp_layout
+    L = 13 * 30 * 52
+    assert sp_layout(2 * L, L, 2, 4) == (4, 2 * L // 8)
+    assert sp_layout(2 * L, L, 4, 4) == (4, 2 * L // 16)
+    assert sp_layout(2 * L, L, 8, 4) == (2, 2 * L // 16)         # 40 560 rows divide by 16, not by 32
+    assert sp_layout(2 * 384, 384, 2, 4) == (4, 96)
+    assert sp_layout(2 * 384, 384, 2, 2) == (2, 192)
+    assert sp_layout(2 * 385, 385, 4, 4) is None                  # rows that do not divide: replicated stream
+    for rows, per_batch, tp, want in ((2 * L, L, 8, 4), (2 * L, L, 4, 4), (768, 384, 2, 4), (768, 384, 2, 1)):
+        C, mb = sp_layout(rows, per_batch, tp, want)
+        seen = [0] * rows
+        for c in range(C):
+            piece_first = c * tp * mb
+            for r in range(tp):
+                a, b = sp_block_rows(c, r, tp, mb)
+                assert a == piece_first + r * mb and b - a == mb          # rank order inside the contiguous piece
+                assert a // per_batch == (b - 1) // per_batch              # one batch element per block
+                for i in range(a, b):
+                    seen[i] += 1
+        assert all(v == 1 for v in seen)
