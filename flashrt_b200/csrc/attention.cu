@@ -29,6 +29,7 @@
 #include "tc05.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace frt {
 
@@ -111,7 +112,7 @@ struct AttnParams {
     float* lse_accum;            // (splits, B, Hq, Sq) fp32, log2-domain log-sum-exp of the split (-inf if empty)
     unsigned* counters;          // 2 words per (row tile, kv head, batch): arrivals (monotonic), spare; zero before first use
     float scale_log2;            // softmax_scale * log2(e)
-    int flags;                   // the entry point's flags (bit 2: keep one CTA per (tile, split) in the head_dim-256 kernel)
+    int flags;                   // the entry point's flags (head_dim-256 kernel: bit 2 keeps one CTA per (tile, split), bit 3 the global-scratch combine)
 #ifdef FRT_PHASE_STAMPS
     int trace_slot;
 #endif

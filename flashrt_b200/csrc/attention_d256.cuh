@@ -38,7 +38,17 @@ struct D256Cfg {
     // dq = 1, 144 KB for dq = 4; the combine re-uses the first 74 KB after the last MMA)
     static constexpr int data_bytes(int dq) { return OFF_V + 2 * (KV_BYTES / dq); }
     static constexpr int ML_BYTES = 128 * 4;
-    static constexpr int smem_bytes(int dq) { return data_bytes(dq) + ML_BYTES + 256 + 1024; }
+    // cluster exchange (XC): one receive slot per kv split, [128 rows][64 / C columns] bf16 + 128 log-sum-exps
+    static constexpr int recv_bytes(int dq) { return 128 * (D / dq) * 2 + 8 * 512; }
+    static constexpr int OFF_RECV(int dq) { return data_bytes(dq) + ML_BYTES + 256; }
+    static constexpr int smem_bytes(int dq, bool xc = false) { return OFF_RECV(dq) + (xc ? recv_bytes(dq) : 0) + 1024; }
+    // ragged launch: full tiles in four parts, a last tile of at most RAGGED_ROWS rows in two (slots of
+    // rows x (128 / C columns bf16 + one float) from each of C splits: at most 8 x 32 x 36 bytes)
+    static constexpr int RAGGED_ROWS = 32;
+    static constexpr int ragged_smem_bytes() {
+        const int tail = OFF_RECV(2) + 8 * RAGGED_ROWS * 36 + 1024;
+        return tail > smem_bytes(4, true) ? tail : smem_bytes(4, true);
+    }
     static constexpr int S_COL = 0;                        // two S buffers of 64 columns
     static constexpr int O_COL = 128;
     static constexpr int TMEM_COLS = 512;
@@ -49,10 +59,19 @@ struct D256Cfg {
 // softmax of its (row tile, kv split) and computes P.V for D / DQ columns, so that the accumulator a CTA has to move
 // out of tensor memory -- the longest single step of the scratch path: 3 us for 128 x 256 fp32 -- shrinks by DQ and
 // the grid covers 4 x more SMs.
-template <int DQ>
-__global__ void __launch_bounds__(192, 1)
-attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+//
+// XC (with DQ = 4): the C kv splits of a (row tile, head-dim part) are the CTAs of one thread-block cluster (1 x 1 x C)
+// and exchange their partials through distributed shared memory instead of the global scratch: the thread of a row
+// pushes, straight from registers with st.async, the 64 / C columns that split s finishes (normalised, bf16) and the
+// row's log-sum-exp into split s's receive slot, the bytes counted on s's mbarrier; it then waits for its own slot to
+// fill and combines and stores its row.  No fence, no CTA barrier, no counter and no L2 round trip between the last
+// MMA and the result (measured per launch at the action-expert shape: publish 0.5 us + fence and barrier 0.7 + arrival
+// 1.9 + combine 1.4 through the scratch).  Nothing of a CTA is read by a peer and a CTA leaves only after every peer's
+// push has landed, so there is no cluster barrier at the end; the one at the start orders the peers' mbarrier
+// initialisation before the first push and is hidden behind the previous kernel.
+template <int DQ, bool XC>
+__device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                               const AttnParams& p, const int tile, const int dq, const int ntiles) {
     using Cfg = D256Cfg;
     constexpr int D = Cfg::D, BKV = Cfg::BKV;
     constexpr int DV = D / DQ;                             // columns of V / O of this CTA
@@ -83,9 +102,6 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool via_scratch = p.o_accum != nullptr;
     const uint32_t C = gridDim.z;
     const uint32_t rank = blockIdx.z;
-    const int tile = blockIdx.x / DQ;
-    const int dq = blockIdx.x % DQ;
-    const int ntiles = gridDim.x / DQ;
     const int hk = blockIdx.y % p.Hkv;
     const int b = blockIdx.y / p.Hkv;
     const int tok0 = tile * (128 / p.G);
@@ -114,6 +130,8 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 3; ++i) tc::mbar_init(&q_part[i], 1);
         *abort_flag = 0;
         tc::mbar_fence_init();
+        if constexpr (XC)       // every peer pushes rows_valid x (64 / C columns bf16 + one float) into this CTA
+            tc::mbar_arrive_expect_tx(c_full, (C - 1) * (uint32_t)rows_valid * ((uint32_t)(DV / C) * 2u + 4u));
         tc::tma_prefetch_desc(&tmQ);
         tc::tma_prefetch_desc(&tmK);
         tc::tma_prefetch_desc(&tmV);
@@ -126,6 +144,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if constexpr (XC) tc::cluster_sync_all();       // every peer's c_full is initialised before anyone pushes
 
     pdl_launch_dependents();
 
@@ -217,7 +236,7 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     } else if (warp < 4) {
         // ---------------- softmax: thread = row
         pdl_wait();
-        if (via_scratch && threadIdx.x == 0) {
+        if (!XC && via_scratch && threadIdx.x == 0) {
             // Arrival counter of this tile: it only ever grows, by 256 per launch (each of the C * DQ CTAs adds
             // 256 / (C * DQ)).  Every earlier launch has completed here and this CTA has not arrived yet, so rounding
             // down to a multiple of 256 gives the count this launch started from.
@@ -310,7 +329,65 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (alive) {
             tc::tc_fence_after_sync();
             const float invl = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            if (via_scratch) {
+            if constexpr (XC) {
+                // ---------------- cluster exchange: slice s of this partial (columns [s dper, (s + 1) dper) of the part)
+                // goes to split s's receive slot of this split
+                const float lse2 = l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY;
+                uint32_t pk[DV / 2];                            // the row of this part, normalised, as bf16 pairs
+#pragma unroll
+                for (int c = 0; c < DV; c += 64) {
+                    uint32_t va[64];
+                    if (nchunks > 0) {                          // warp-uniform: the loads are warp-collective
+                        tc::tmem_ld32(tmem_O + c, va);
+                        tc::tmem_ld32(tmem_O + c + 32, va + 32);
+                        tc::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 64; ++i) va[i] = 0u;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        pk[c / 2 + i] = pack_bf16x2(__uint_as_float(va[2 * i]) * invl, __uint_as_float(va[2 * i + 1]) * invl);
+                }
+                ATT_STAMP(13);
+                uint8_t* recv = smem + Cfg::OFF_RECV(DQ);
+                const uint32_t recv_u32 = tc::smem_u32(recv);
+                const uint32_t bar_u32 = tc::smem_u32(c_full);
+                const int dper = DV / (int)C;                   // 8 .. 64 columns per slice
+                // slot of a source split: [rows_valid][dper] bf16, then rows_valid log-sum-exps
+                const uint32_t slot = ((uint32_t)rows_valid * ((uint32_t)dper * 2u + 4u) + 15u) & ~15u;
+                const uint32_t my_data = rank * slot + (uint32_t)row * (uint32_t)dper * 2u;
+                const uint32_t my_lse = rank * slot + (uint32_t)rows_valid * (uint32_t)dper * 2u + (uint32_t)row * 4u;
+                auto push = [&](auto dper_c) {
+                    constexpr int DPER = decltype(dper_c)::value;
+#pragma unroll
+                    for (int s = 0; s < DV / DPER; ++s) {
+                        const uint32_t* w = pk + s * (DPER / 2);
+                        if (row >= rows_valid) {
+                        } else if ((uint32_t)s == rank) {       // the own slice: plain stores into the own slot
+#pragma unroll
+                            for (int q = 0; q < DPER / 8; ++q)
+                                *reinterpret_cast<uint4*>(recv + my_data + 16 * q) =
+                                    make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                            *reinterpret_cast<float*>(recv + my_lse) = lse2;
+                        } else {
+                            const uint32_t peer_bar = tc::dsmem_map(bar_u32, (uint32_t)s);
+                            const uint32_t peer_data = tc::dsmem_map(recv_u32 + my_data, (uint32_t)s);
+#pragma unroll
+                            for (int q = 0; q < DPER / 8; ++q)
+                                tc::st_async_v4(peer_data + 16 * q, peer_bar, w[4 * q], w[4 * q + 1], w[4 * q + 2],
+                                                w[4 * q + 3]);
+                            tc::st_async_b32(tc::dsmem_map(recv_u32 + my_lse, (uint32_t)s), peer_bar,
+                                             __float_as_uint(lse2));
+                        }
+                    }
+                };
+                if (C == 8) push(std::integral_constant<int, DV / 8>{});
+                else if (C == 4) push(std::integral_constant<int, DV / 4>{});
+                else push(std::integral_constant<int, DV / 2>{});
+                ATT_STAMP(14);
+                ATT_STAMP(8);
+            } else if (via_scratch) {
                 // O / l as bf16 straight from registers to the scratch in column slices [slice][row][D / C]: the 64
                 // bytes a thread writes per 32 columns are adjacent to its neighbours' (the rows of a slice are
                 // contiguous), so a warp's store covers 2 KB without gaps.  Log2-domain lse alongside.
@@ -424,9 +501,89 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         (l_run > 0.0f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
             }
         }
+        if constexpr (XC) {
+            // ---------------- every peer's slice of this split's columns has landed: combine and store.  One item =
+            // (row, 8 columns), spread over the four softmax warps whatever their rows (a short last tile has its rows in
+            // one warp), so a thread reads slots that other threads filled: a named barrier, reached by the four warps
+            // on every path, orders the plain stores of the own slice
+            if (!*abort_flag) ATTN_WAIT(c_full, 0u, AERR_SOFTMAX);
+            ATT_STAMP(10);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!*abort_flag) {
+                const uint8_t* recv = smem + Cfg::OFF_RECV(DQ);
+                const int dper = DV / (int)C;
+                const uint32_t slot = ((uint32_t)rows_valid * ((uint32_t)dper * 2u + 4u) + 15u) & ~15u;
+                const uint32_t lse_off = (uint32_t)rows_valid * (uint32_t)dper * 2u;
+                const int cshift = 31 - __clz(dper >> 3);        // 16-byte chunks per slice row: a power of two
+                const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+                for (int it = threadIdx.x; it < (rows_valid << cshift); it += 128) {
+                    const int r = it >> cshift, ch = it & ((1 << cshift) - 1);
+                    const int t = tok0 + (r >> gshift);
+                    const int hq = hk * p.G + (r & (p.G - 1));
+                    float w[8];
+#pragma unroll
+                    for (int sidx = 0; sidx < 8; ++sidx)
+                        w[sidx] = (uint32_t)sidx < C
+                                      ? *reinterpret_cast<const float*>(recv + sidx * slot + lse_off + (uint32_t)r * 4u)
+                                      : -INFINITY;
+                    float M = -INFINITY;
+#pragma unroll
+                    for (int sidx = 0; sidx < 8; ++sidx) M = fmaxf(M, w[sidx]);
+                    float Lw = 0.0f;
+#pragma unroll
+                    for (int sidx = 0; sidx < 8; ++sidx) {
+                        w[sidx] = (w[sidx] == -INFINITY) ? 0.0f : tc::ex2_approx(w[sidx] - M);
+                        Lw += w[sidx];
+                    }
+                    const float invL = Lw > 0.0f ? 1.0f / Lw : 0.0f;
+#pragma unroll
+                    for (int sidx = 0; sidx < 8; ++sidx) w[sidx] *= invL;
+                    float a[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) a[i] = 0.0f;
+#pragma unroll
+                    for (uint32_t sidx = 0; sidx < 8; ++sidx) {
+                        if (sidx >= C) break;
+                        const uint4 x = *reinterpret_cast<const uint4*>(recv + sidx * slot +
+                                                                        (uint32_t)r * (uint32_t)dper * 2u + ch * 16);
+                        const float ws = w[sidx];
+                        float f0, f1;
+                        unpack_bf16x2(x.x, f0, f1); a[0] += ws * f0; a[1] += ws * f1;
+                        unpack_bf16x2(x.y, f0, f1); a[2] += ws * f0; a[3] += ws * f1;
+                        unpack_bf16x2(x.z, f0, f1); a[4] += ws * f0; a[5] += ws * f1;
+                        unpack_bf16x2(x.w, f0, f1); a[6] += ws * f0; a[7] += ws * f1;
+                    }
+                    const size_t o = (size_t)b * p.o_bs + (size_t)t * p.o_rs + (size_t)hq * p.o_hs + dq * DV +
+                                     (int)rank * dper + ch * 8;
+                    uint4 ob;
+                    ob.x = pack_bf16x2(a[0], a[1]);
+                    ob.y = pack_bf16x2(a[2], a[3]);
+                    ob.z = pack_bf16x2(a[4], a[5]);
+                    ob.w = pack_bf16x2(a[6], a[7]);
+                    st_global_v4(p.O + o, ob);
+                    if (p.O_fp8) {
+                        float q[8];
+                        unpack_bf16x2(ob.x, q[0], q[1]);
+                        unpack_bf16x2(ob.y, q[2], q[3]);
+                        unpack_bf16x2(ob.z, q[4], q[5]);
+                        unpack_bf16x2(ob.w, q[6], q[7]);
+                        uint2 o8;
+                        o8.x = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[0], inv_os)), clamp448(__fmul_rn(q[1], inv_os)),
+                                               clamp448(__fmul_rn(q[2], inv_os)), clamp448(__fmul_rn(q[3], inv_os)));
+                        o8.y = f32x4_to_e4m3x4(clamp448(__fmul_rn(q[4], inv_os)), clamp448(__fmul_rn(q[5], inv_os)),
+                                               clamp448(__fmul_rn(q[6], inv_os)), clamp448(__fmul_rn(q[7], inv_os)));
+                        st_global_v2(p.O_fp8 + o, o8);
+                    }
+                    if (p.lse && rank == 0 && dq == 0 && ch == 0)
+                        p.lse[((size_t)b * p.Hq + hq) * p.Sq + t] =
+                            (Lw > 0.0f) ? (M + log2f(Lw)) * 0.6931471805599453f : -INFINITY;
+                }
+            }
+            ATT_STAMP(11);
+        }
     }
     __syncwarp();
-    if (via_scratch) {
+    if (!XC && via_scratch) {
         // ---------------- combine through global scratch.  Block of (batch, kv head, tile, split) in o_accum, as bf16:
         // rows_valid x D, stored [slice][row][D / C]; the rows of all tiles of one (split, batch, kv head) are packed
         // back to back, so the caller's (splits, batch, heads, seqlen_q, D) fp32 buffer is always large enough.
@@ -566,6 +723,29 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ATT_STAMP(12);
 }
 
+template <int DQ, bool XC>
+__global__ void __launch_bounds__(192, 1)
+attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+    attn_d256_body<DQ, XC>(tmQ, tmK, tmV, p, (int)blockIdx.x / DQ, (int)blockIdx.x % DQ, (int)gridDim.x / DQ);
+}
+
+// Cluster exchange with a ragged last row tile: the full tiles in four head-dim parts, the last one in two.  A CTA of
+// this size runs alone on its SM, and B200s hold 13-15 clusters of eight such CTAs (it depends on which SMs of the
+// part are enabled; the host asks the occupancy API): at the action-expert shape -- 400 query rows, 3 full tiles and
+// one of 16 rows -- 16 clusters do not fit but 3 x 4 + 2 do.  blockIdx.x 0 and 1: the halves of the last tile (they
+// have the longer way to go and start first); above: part (x - 2) % 4 of tile (x - 2) / 4.  The last tile has at most
+// RAGGED_ROWS rows, which keeps its receive slots, and with them the shared memory of the launch, small enough for a
+// CTA of the previous kernel to stay resident beside it (the early start under programmatic dependent launch).
+__global__ void __launch_bounds__(192, 1)
+attn_d256_ragged_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+    const int ntiles = ((int)gridDim.x - 2) / 4 + 1;
+    const int x = (int)blockIdx.x - 2;
+    if (x >= 0) attn_d256_body<4, true>(tmQ, tmK, tmV, p, x / 4, x % 4, ntiles);
+    else attn_d256_body<2, true>(tmQ, tmK, tmV, p, ntiles - 1, (int)blockIdx.x, ntiles);
+}
+
 static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
                             const long long* ks, const long long* vs, int splits, bool pdl, cudaStream_t stream) {
     using Cfg = D256Cfg;
@@ -574,10 +754,17 @@ static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnPar
     if (dev < 0 || dev >= 64) return FRT_ERR_UNSUPPORTED;
     static bool attr_done[64] = {false};                 // the attribute is per device
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_d256_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_d256_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes(1));
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
-        e = cudaFuncSetAttribute(attn_d256_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes(4));
+        e = cudaFuncSetAttribute(attn_d256_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::smem_bytes(4));
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        e = cudaFuncSetAttribute(attn_d256_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::smem_bytes(4, true));
+        if (e != cudaSuccess) return FRT_CUDA_ERR(e);
+        e = cudaFuncSetAttribute(attn_d256_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::ragged_smem_bytes());
         if (e != cudaSuccess) return FRT_CUDA_ERR(e);
         attr_done[dev] = true;
     }
@@ -617,17 +804,68 @@ static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnPar
         // four head-dim parts per (tile, split) while the whole grid still fits one wave and a slice keeps 8 columns
         if (ctas * 4 <= sms && 64 / splits >= 8 && !(p.flags & 4)) dq = 4;
     }
+    // with four head-dim parts the kv splits of a (tile, part) exchange their partials as one cluster (flags bit 3
+    // keeps the global scratch) -- when the device can hold all those clusters at once: CTAs of this size run one per
+    // SM and how many clusters of them fit depends on the part's enabled SMs.  Otherwise the last tile in two parts, if
+    // that fits; otherwise the scratch.
+    bool xc = dq == 4 && !(p.flags & 8);
+    bool ragged = false;
+    if (xc) {
+        int lg = 0;
+        while ((1 << lg) < splits) ++lg;                     // splits is 2, 4 or 8 here
+        static int max_clusters[64][4][2];                   // [device][log2 splits][ragged], 0 = not asked yet
+        auto fits = [&](bool rg, int need) {
+            int& m = max_clusters[dev][lg][rg ? 1 : 0];
+            if (m == 0) {
+                cudaLaunchConfig_t q = {};
+                q.gridDim = dim3(rg ? 4 * (tiles - 1) + 2 : tiles * 4, p.Hkv * p.B, splits);
+                q.blockDim = dim3(192);
+                q.dynamicSmemBytes = rg ? Cfg::ragged_smem_bytes() : Cfg::smem_bytes(4, true);
+                cudaLaunchAttribute qa[1];
+                qa[0].id = cudaLaunchAttributeClusterDimension;
+                qa[0].val.clusterDim.x = 1;
+                qa[0].val.clusterDim.y = 1;
+                qa[0].val.clusterDim.z = (unsigned)splits;
+                q.attrs = qa;
+                q.numAttrs = 1;
+                int n = 0;
+                cudaError_t qe = rg ? cudaOccupancyMaxActiveClusters(&n, attn_d256_ragged_kernel, &q)
+                                    : cudaOccupancyMaxActiveClusters(&n, attn_d256_kernel<4, true>, &q);
+                m = (qe == cudaSuccess && n > 0) ? n : -1;
+                if (qe != cudaSuccess) cudaGetLastError();
+            }
+            return need <= m;
+        };
+        if (!fits(false, tiles * 4 * p.Hkv * p.B)) {
+            const int tail_rows = p.Sq * p.G - 128 * (tiles - 1);
+            if (tail_rows <= Cfg::RAGGED_ROWS && fits(true, (4 * (tiles - 1) + 2) * p.Hkv * p.B)) ragged = true;
+            else xc = false;
+        }
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles * dq, p.Hkv * p.B, splits);
+    cfg.gridDim = dim3(ragged ? 4 * (tiles - 1) + 2 : tiles * dq, p.Hkv * p.B, splits);
     cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = Cfg::smem_bytes(dq);
+    cfg.dynamicSmemBytes = ragged ? Cfg::ragged_smem_bytes() : Cfg::smem_bytes(dq, xc);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (xc) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = (unsigned)splits;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = dq == 4 ? cudaLaunchKernelEx(&cfg, attn_d256_kernel<4>, tmQ, tmK, tmV, p)
-                            : cudaLaunchKernelEx(&cfg, attn_d256_kernel<1>, tmQ, tmK, tmV, p);
+    cfg.numAttrs = na;
+    cudaError_t e = ragged    ? cudaLaunchKernelEx(&cfg, attn_d256_ragged_kernel, tmQ, tmK, tmV, p)
+                    : xc      ? cudaLaunchKernelEx(&cfg, attn_d256_kernel<4, true>, tmQ, tmK, tmV, p)
+                    : dq == 4 ? cudaLaunchKernelEx(&cfg, attn_d256_kernel<4, false>, tmQ, tmK, tmV, p)
+                              : cudaLaunchKernelEx(&cfg, attn_d256_kernel<1, false>, tmQ, tmK, tmV, p);
     return e == cudaSuccess ? FRT_OK : FRT_CUDA_ERR(e);
 }

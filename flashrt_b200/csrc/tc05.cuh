@@ -307,6 +307,19 @@ __device__ __forceinline__ uint32_t dsmem_map(uint32_t local_smem_addr, uint32_t
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta_rank));
     return r;
 }
+// 16 / 4 bytes from registers into a cluster peer's shared memory; the bytes are counted on the peer's mbarrier
+// (both addresses are shared::cluster addresses from dsmem_map)
+__device__ __forceinline__ void st_async_v4(uint32_t peer_addr, uint32_t peer_bar, uint32_t a, uint32_t b, uint32_t c,
+                                            uint32_t d) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(peer_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(peer_bar)
+                 : "memory");
+}
+__device__ __forceinline__ void st_async_b32(uint32_t peer_addr, uint32_t peer_bar, uint32_t a) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(peer_addr), "r"(a), "r"(peer_bar)
+                 : "memory");
+}
 __device__ __forceinline__ float dsmem_ld_f32(uint32_t cluster_addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");

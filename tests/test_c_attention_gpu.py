@@ -55,8 +55,11 @@ def _run(B, Sq, Skv, Hq, Hkv, D, splits, seed, seqused=None, fused_fp8=False, kv
     if fused_fp8:
         # the fused FP8 copy is the bit-exact static quantisation of the bf16 result
         assert np.array_equal(d_o8.get(), O.quantize_fp8_static(got_bits, 0.01))
+    cnt = None
     if scratch:
-        assert (d_cnt.get()[0::2] % 256 == 0).all()     # every CTA of a tile has arrived: 256 per tile and launch
+        cnt = d_cnt.get()[0::2]
+        assert (cnt % 256 == 0).all()                   # every CTA of a tile has arrived: 256 per tile and launch
+    return got_bits, d_lse.get(), cnt
 
 
 @pytest.mark.parametrize("splits", [1, 2, 8, 0])
@@ -110,14 +113,27 @@ def test_split_kv_through_global_scratch(splits):
     _run(2, 130, 260, 8, 2, 128, 2, seed=50 + splits, scratch=True)
 
 
+@pytest.mark.parametrize("Sq,Skv,splits,extra", [(50, 818, 8, {}), (50, 818, 4, {}), (50, 818, 2, {}), (3, 130, 8, {}),
+                                                  (17, 500, 4, dict(seqused=333)), (50, 818, 8, dict(fused_fp8=True)),
+                                                  (50, 600, 8, dict(seqused=70))])
+def test_cluster_exchange_equals_scratch_combine(Sq, Skv, splits, extra):
+    """With four head-dim parts per (tile, split) the kv splits of a part are one thread-block cluster and exchange
+    their partials through distributed shared memory (the scratch and the counters stay untouched); flags bit 3 keeps
+    the combine through the global scratch.  Same partials, same weights, same order of the sum: the same bits."""
+    a, lse_a, cnt_a = _run(1, Sq, Skv, 8, 1, 256, splits, seed=7, scratch=True, **extra)
+    b, lse_b, cnt_b = _run(1, Sq, Skv, 8, 1, 256, splits, seed=7, scratch=True, flags=8, **extra)
+    assert np.array_equal(a, b) and np.array_equal(lse_a, lse_b)
+    assert (cnt_a == 0).all() and (cnt_b == 256).all()
+
+
 def test_launches_of_different_shapes_share_arrival_counters():
     """A tile's counter grows by 256 per launch whatever the number of CTAs of the tile (32, 8, 2 ...), so one zeroed
     buffer serves calls of any shape in any order."""
     from gpu_util import zeros
     cnt = zeros((64,), np.int32)
-    for i, (args, kw) in enumerate([((1, 50, 818, 8, 1, 256, 8), {}), ((1, 50, 818, 8, 1, 256, 2), {}),
+    for i, (args, kw) in enumerate([((1, 50, 818, 8, 1, 256, 8), dict(flags=8)), ((1, 50, 818, 8, 1, 256, 2), dict(flags=8)),
                                     ((2, 130, 260, 8, 2, 128, 2), {}), ((1, 50, 818, 8, 1, 256, 8), dict(flags=4)),
-                                    ((1, 17, 500, 8, 1, 256, 4), {}), ((1, 50, 818, 8, 1, 256, 8), {})]):
+                                    ((1, 17, 500, 8, 1, 256, 4), dict(flags=8)), ((1, 50, 818, 8, 1, 256, 8), {})]):
         _run(*args, seed=90 + i, scratch=True, counters=cnt, **kw)
 
 
