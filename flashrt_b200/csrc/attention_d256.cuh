@@ -247,6 +247,9 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
         }
         int kv_len = p.Skv;
         if (p.seqused_k) { int u = *p.seqused_k; kv_len = u < kv_len ? u : kv_len; }
+        // read here, not where it is used: the load is an L2 round trip (0.6-1.2 us, by the distance of the SM from the
+        // line's L2 slice) that would otherwise sit between the last partial's arrival and the result
+        const float inv_os_early = (XC && p.O_fp8) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
         const int row = warp * 32 + lane;
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
         const uint32_t tmem_O = tmem + Cfg::O_COL + lane_off;
@@ -515,7 +518,7 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
                 const uint32_t slot = ((uint32_t)rows_valid * ((uint32_t)dper * 2u + 4u) + 15u) & ~15u;
                 const uint32_t lse_off = (uint32_t)rows_valid * (uint32_t)dper * 2u;
                 const int cshift = 31 - __clz(dper >> 3);        // 16-byte chunks per slice row: a power of two
-                const float inv_os = p.O_fp8 ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+                const float inv_os = inv_os_early;
                 for (int it = threadIdx.x; it < (rows_valid << cshift); it += 128) {
                     const int r = it >> cshift, ch = it & ((1 << cshift) - 1);
                     const int t = tok0 + (r >> gshift);
