@@ -788,7 +788,8 @@ def run_timeline(args):
             a = ta[ai % 8]
             ai += 1
             a = a[a[:, 0] > 0]
-            cols = (a[:, 0].min(), np.median(a[:, 1]), np.median(a[:, 7]), np.median(a[:, 9]), np.median(a[:, 10]),
+            pub = 9 if (a[:, 9] > 0).all() else 8      # cluster exchange: no fence + barrier stamp, "pushed" instead
+            cols = (a[:, 0].min(), np.median(a[:, 1]), np.median(a[:, 7]), np.median(a[:, pub]), np.median(a[:, 10]),
                     a[:, 12].max())
         else:
             a = tt[gi % 8]
@@ -811,7 +812,28 @@ def run_timeline(args):
     # P.V complete, partial in registers, partial stored, fenced + CTA barrier, all CTAs of the tile seen, combined, end.
     a = ta[(ai - 1) % 8]
     splits, cols = [], (1, 2, 4, 5, 7, 13, 14, 9, 10, 11, 12)
-    if (a[:, 0] > 0).sum() == 128:
+    n_cta = int((a[:, 0] > 0).sum())
+    if n_cta in (112, 128) and not (a[:n_cta, 9] > 0).any():
+        # cluster exchange (no scratch): CTA (x, z) is row z * gx + x.  Ragged launch (gx = 14): x 0 and 1 are the two
+        # parts of the short last tile.  Stamps: dependency wait returned, first Q block landed, first S complete, first
+        # P written, P.V complete, partial packed in registers, pushed to the peers, all peers' slices received,
+        # combined + stored, end.
+        gx, a, a0 = n_cta // 8, a[:n_cta], a[:n_cta, 0].min()
+        xs = np.arange(n_cta) % gx
+        groups = ([("last tile, 2 parts", xs < 2), ("full tiles, 4 parts", xs >= 2)] if gx % 4 == 2
+                  else [("all", xs >= 0)])
+        for z in (0, 1, 7):
+            groups.append((f"kv split {z}", np.arange(n_cta) // gx == z))
+        groups.append(("slowest", None))
+        print("attention launch (us): wait returned | Q block | first S | first P | P.V done | packed | pushed | "
+              "received | combined | end", file=sys.stderr)
+        for name, m in groups:
+            blk = a if m is None else a[m]
+            f = np.max if m is None else np.median
+            us = [round(float(f(blk[:, c]) - a0) / 1e3, 2) for c in (1, 2, 4, 5, 7, 13, 14, 10, 11, 12)]
+            splits.append({"ctas": name, "us": us})
+            print(f"  {name:20s} " + "  ".join(f"{v:6.2f}" for v in us), file=sys.stderr)
+    elif n_cta == 128:
         a0 = a[:, 0].min()
         print("attention launch per kv split (us): wait returned | Q block | first S | first P | P.V done | in registers | "
               "stored | fenced | all seen | combined | end", file=sys.stderr)

@@ -67,8 +67,8 @@ struct D256Cfg {
 // fill and combines and stores its row.  No fence, no CTA barrier, no counter and no L2 round trip between the last
 // MMA and the result (measured per launch at the action-expert shape: publish 0.5 us + fence and barrier 0.7 + arrival
 // 1.9 + combine 1.4 through the scratch).  Nothing of a CTA is read by a peer and a CTA leaves only after every peer's
-// push has landed, so there is no cluster barrier at the end; the one at the start orders the peers' mbarrier
-// initialisation before the first push and is hidden behind the previous kernel.
+// push has landed, so there is no cluster barrier at the end; the one that orders the peers' mbarrier initialisation
+// before the first push is split: arrive after the set-up, wait just before pushing.
 template <int DQ, bool XC>
 __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                                                const AttnParams& p, const int tile, const int dq, const int ntiles) {
@@ -144,7 +144,10 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    if constexpr (XC) tc::cluster_sync_all();       // every peer's c_full is initialised before anyone pushes
+    // every peer's c_full must be initialised before anyone pushes into it: all threads arrive here, the softmax warps
+    // wait just before their first push (by then the barrier has long completed: nothing of it is on the way to the
+    // first MMA)
+    if constexpr (XC) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     pdl_launch_dependents();
 
@@ -385,6 +388,7 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
                         }
                     }
                 };
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
                 if (C == 8) push(std::integral_constant<int, DV / 8>{});
                 else if (C == 4) push(std::integral_constant<int, DV / 4>{});
                 else push(std::integral_constant<int, DV / 2>{});

@@ -170,10 +170,15 @@ int frt_b200_gemm_status(int reset);
  *   o_accum, lse_accum, counters: optional split-KV scratch (all three or none): o_accum (splits, batch,
  *   num_heads_q, seqlen_q, head_dim) fp32 and lse_accum (splits, batch, num_heads_q, seqlen_q) fp32 -- the
  *   reference's FA2 split-kv buffers -- and counters = 2 unsigned per (128-row tile, kv head, batch), zeroed once
- *   by the caller.  Given scratch, the kv splits combine through global memory instead of the cluster; the grid
- *   (tiles x kv heads x batch x splits) must then fit the device in one wave, else -2 is returned.
+ *   by the caller.  Given scratch, the head_dim-256 kernel may run more CTAs than (tiles x splits): the grid
+ *   (tiles x kv heads x batch x splits) must then fit the device in one wave, else -2 is returned.  When four times
+ *   that grid fits as well, every (tile, split) is cut into four head-dim parts, and the kv splits of a part
+ *   exchange their partials (a) as one thread-block cluster through distributed shared memory -- scratch and counters
+ *   stay untouched -- when the device can hold all those clusters at once (asked from the occupancy API once per
+ *   device; with a last tile of at most 32 rows that tile may run in two parts instead to make them fit), else
+ *   (b) through the scratch, published with an arrival counter per tile.  (a) and (b) give the same bits.
  *   flags: bit 0 = programmatic dependent launch; bit 1 = keep the single-tile kernel; head_dim 256 with scratch:
- *   bit 2 = one CTA per (tile, split) instead of four head-dim parts. */
+ *   bit 2 = one CTA per (tile, split) instead of four head-dim parts, bit 3 = always (b). */
 int frt_b200_attention_fwd_bf16(const void* Q, const void* K, const void* V, void* O, void* O_fp8,
                                 const float* out_scale, float* lse, const int* seqused_k, int batch, int seqlen_q,
                                 int seqlen_k, int num_heads_q, int num_heads_kv, int head_dim,
