@@ -69,13 +69,21 @@ struct D256Cfg {
 // 1.9 + combine 1.4 through the scratch).  Nothing of a CTA is read by a peer and a CTA leaves only after every peer's
 // push has landed, so there is no cluster barrier at the end; the one that orders the peers' mbarrier initialisation
 // before the first push is split: arrive after the set-up, wait just before pushing.
-template <int DQ, bool XC>
+// DQT = 0 (cluster exchange only): the number of parts is a run-time argument, so that the CTAs of a ragged launch --
+// full tiles in four parts, the last tile in two -- run the same instructions: with one body per part count the 16 CTAs
+// of the last tile found their variant cold in the instruction cache of whatever SM they landed on (every phase of them
+// ran 0.3-0.5 us behind the same phase of the other 96 CTAs on its first pass and at their speed on its second).
+template <int DQT, bool XC>
 __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
-                                               const AttnParams& p, const int tile, const int dq, const int ntiles) {
+                                               const AttnParams& p, const int tile, const int dq, const int ntiles,
+                                               const int parts) {
     using Cfg = D256Cfg;
+    static_assert(DQT != 0 || XC, "run-time part count: cluster exchange only");
     constexpr int D = Cfg::D, BKV = Cfg::BKV;
-    constexpr int DV = D / DQ;                             // columns of V / O of this CTA
-    constexpr int V_BYTES = BKV * DV * 2;                  // one V stage
+    constexpr int DVC = DQT ? D / DQT : 64;                // compile-time columns of V / O of this CTA (DQT != 0)
+    const int DQ = DQT ? DQT : parts;
+    const int DV = D / DQ;                                 // columns of V / O of this CTA
+    const int V_BYTES = BKV * DV * 2;                      // one V stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;
@@ -186,7 +194,7 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
     } else if (warp == 5 && lane == 0) {
         // ---------------- MMA issuer
         constexpr uint32_t idesc_s = tc::make_idesc(1, 1, 0, 0, 128, BKV);
-        constexpr uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, DV);    // A = P from TMEM, B = V MN-major
+        const uint32_t idesc_o = tc::make_idesc(1, 1, 0, 1, 128, (uint32_t)DV);    // A = P from TMEM, B = V MN-major
         const uint64_t dq_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sQ));
         const uint64_t dk_base = tc::make_desc_kmajor_sw128(tc::smem_u32(sK));
         const uint64_t dv_base = tc::make_desc_mnmajor_sw128(tc::smem_u32(sV), BKV * 128);
@@ -337,10 +345,26 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
             const float invl = l_run > 0.0f ? 1.0f / l_run : 0.0f;
             if constexpr (XC) {
                 // ---------------- cluster exchange: slice s of this partial (columns [s dper, (s + 1) dper) of the part)
-                // goes to split s's receive slot of this split
+                // goes to split s's receive slot of this split; 64 columns at a time (one or more whole slices, or half a
+                // slice of 128 / 2 columns)
                 const float lse2 = l_run > 0.0f ? m_run + log2f(l_run) : -INFINITY;
-                uint32_t pk[DV / 2];                            // the row of this part, normalised, as bf16 pairs
-#pragma unroll
+                uint8_t* recv = smem + Cfg::OFF_RECV(DQ);
+                const uint32_t recv_u32 = tc::smem_u32(recv);
+                const uint32_t bar_u32 = tc::smem_u32(c_full);
+                const int dper = DV / (int)C;                   // 8 .. 64 columns per slice
+                // slot of a source split: [rows_valid][dper] bf16, then rows_valid log-sum-exps
+                const uint32_t slot = ((uint32_t)rows_valid * ((uint32_t)dper * 2u + 4u) + 15u) & ~15u;
+                const uint32_t my_data = rank * slot + (uint32_t)row * (uint32_t)dper * 2u;
+                const uint32_t my_lse = rank * slot + (uint32_t)rows_valid * (uint32_t)dper * 2u + (uint32_t)row * 4u;
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+                if (row < rows_valid) {                         // the log-sum-exp of the row: once to every split
+                    for (uint32_t s = 0; s < C; ++s) {
+                        if (s == rank) *reinterpret_cast<float*>(recv + my_lse) = lse2;
+                        else tc::st_async_b32(tc::dsmem_map(recv_u32 + my_lse, s), tc::dsmem_map(bar_u32, s),
+                                              __float_as_uint(lse2));
+                    }
+                }
+#pragma unroll 1
                 for (int c = 0; c < DV; c += 64) {
                     uint32_t va[64];
                     if (nchunks > 0) {                          // warp-uniform: the loads are warp-collective
@@ -351,50 +375,44 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
 #pragma unroll
                         for (int i = 0; i < 64; ++i) va[i] = 0u;
                     }
+                    uint32_t pk[32];                            // 64 columns of the row, normalised, as bf16 pairs
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        pk[c / 2 + i] = pack_bf16x2(__uint_as_float(va[2 * i]) * invl, __uint_as_float(va[2 * i + 1]) * invl);
-                }
-                ATT_STAMP(13);
-                uint8_t* recv = smem + Cfg::OFF_RECV(DQ);
-                const uint32_t recv_u32 = tc::smem_u32(recv);
-                const uint32_t bar_u32 = tc::smem_u32(c_full);
-                const int dper = DV / (int)C;                   // 8 .. 64 columns per slice
-                // slot of a source split: [rows_valid][dper] bf16, then rows_valid log-sum-exps
-                const uint32_t slot = ((uint32_t)rows_valid * ((uint32_t)dper * 2u + 4u) + 15u) & ~15u;
-                const uint32_t my_data = rank * slot + (uint32_t)row * (uint32_t)dper * 2u;
-                const uint32_t my_lse = rank * slot + (uint32_t)rows_valid * (uint32_t)dper * 2u + (uint32_t)row * 4u;
-                auto push = [&](auto dper_c) {
-                    constexpr int DPER = decltype(dper_c)::value;
+                        pk[i] = pack_bf16x2(__uint_as_float(va[2 * i]) * invl, __uint_as_float(va[2 * i + 1]) * invl);
+                    if (c == 0) ATT_STAMP(13);
+                    auto push = [&](auto dper_c) {
+                        constexpr int DPER = decltype(dper_c)::value;        // columns of a slice inside this block
+                        constexpr int NS = 64 / DPER;                          // slices (or 1: half a 128-column slice)
 #pragma unroll
-                    for (int s = 0; s < DV / DPER; ++s) {
-                        const uint32_t* w = pk + s * (DPER / 2);
-                        if (row >= rows_valid) {
-                        } else if ((uint32_t)s == rank) {       // the own slice: plain stores into the own slot
+                        for (int i = 0; i < NS; ++i) {
+                            const uint32_t s = (uint32_t)((c + i * DPER) >> (31 - __clz(dper)));
+                            const uint32_t off = my_data + (uint32_t)(((c + i * DPER) & (dper - 1)) * 2);
+                            const uint32_t* w = pk + i * (DPER / 2);
+                            if (row >= rows_valid) {
+                            } else if (s == rank) {             // the own slice: plain stores into the own slot
 #pragma unroll
-                            for (int q = 0; q < DPER / 8; ++q)
-                                *reinterpret_cast<uint4*>(recv + my_data + 16 * q) =
-                                    make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-                            *reinterpret_cast<float*>(recv + my_lse) = lse2;
-                        } else {
-                            const uint32_t peer_bar = tc::dsmem_map(bar_u32, (uint32_t)s);
-                            const uint32_t peer_data = tc::dsmem_map(recv_u32 + my_data, (uint32_t)s);
+                                for (int q = 0; q < DPER / 8; ++q)
+                                    *reinterpret_cast<uint4*>(recv + off + 16 * q) =
+                                        make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                            } else {
+                                const uint32_t peer_bar = tc::dsmem_map(bar_u32, s);
+                                const uint32_t peer_data = tc::dsmem_map(recv_u32 + off, s);
 #pragma unroll
-                            for (int q = 0; q < DPER / 8; ++q)
-                                tc::st_async_v4(peer_data + 16 * q, peer_bar, w[4 * q], w[4 * q + 1], w[4 * q + 2],
-                                                w[4 * q + 3]);
-                            tc::st_async_b32(tc::dsmem_map(recv_u32 + my_lse, (uint32_t)s), peer_bar,
-                                             __float_as_uint(lse2));
+                                for (int q = 0; q < DPER / 8; ++q)
+                                    tc::st_async_v4(peer_data + 16 * q, peer_bar, w[4 * q], w[4 * q + 1], w[4 * q + 2],
+                                                    w[4 * q + 3]);
+                            }
                         }
-                    }
-                };
-                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-                if (C == 8) push(std::integral_constant<int, DV / 8>{});
-                else if (C == 4) push(std::integral_constant<int, DV / 4>{});
-                else push(std::integral_constant<int, DV / 2>{});
+                    };
+                    if (dper == 8) push(std::integral_constant<int, 8>{});
+                    else if (dper == 16) push(std::integral_constant<int, 16>{});
+                    else if (dper == 32) push(std::integral_constant<int, 32>{});
+                    else push(std::integral_constant<int, 64>{});
+                }
                 ATT_STAMP(14);
                 ATT_STAMP(8);
             } else if (via_scratch) {
+                constexpr int DV = DVC;                         // compile-time here (never the run-time-parts variant)
                 // O / l as bf16 straight from registers to the scratch in column slices [slice][row][D / C]: the 64
                 // bytes a thread writes per 32 columns are adjacent to its neighbours' (the rows of a slice are
                 // contiguous), so a warp's store covers 2 KB without gaps.  Log2-domain lse alongside.
@@ -734,7 +752,8 @@ template <int DQ, bool XC>
 __global__ void __launch_bounds__(192, 1)
 attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-    attn_d256_body<DQ, XC>(tmQ, tmK, tmV, p, (int)blockIdx.x / DQ, (int)blockIdx.x % DQ, (int)gridDim.x / DQ);
+    attn_d256_body<XC ? 0 : DQ, XC>(tmQ, tmK, tmV, p, (int)blockIdx.x / DQ, (int)blockIdx.x % DQ, (int)gridDim.x / DQ,
+                                    DQ);
 }
 
 // Cluster exchange with a ragged last row tile: the full tiles in four head-dim parts, the last one in two.  A CTA of
@@ -749,8 +768,9 @@ attn_d256_ragged_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                         const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
     const int ntiles = ((int)gridDim.x - 2) / 4 + 1;
     const int x = (int)blockIdx.x - 2;
-    if (x >= 0) attn_d256_body<4, true>(tmQ, tmK, tmV, p, x / 4, x % 4, ntiles);
-    else attn_d256_body<2, true>(tmQ, tmK, tmV, p, ntiles - 1, (int)blockIdx.x, ntiles);
+    const bool last = x < 0;
+    attn_d256_body<0, true>(tmQ, tmK, tmV, p, last ? ntiles - 1 : x / 4, last ? (int)blockIdx.x : x % 4, ntiles,
+                            last ? 2 : 4);
 }
 
 static int launch_attn_d256(const void* Q, const void* K, const void* V, AttnParams p, const long long* qs,
