@@ -757,8 +757,8 @@ attn_d256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // Cluster exchange with a ragged last row tile: the full tiles in four head-dim parts, the last one in two.  A CTA of
-// this size runs alone on its SM, and B200s hold 13-15 clusters of eight such CTAs (it depends on which SMs of the
-// part are enabled; the host asks the occupancy API): at the action-expert shape -- 400 query rows, 3 full tiles and
+// this size runs alone on its SM, and the B200s measured hold 15 clusters of eight such CTAs (the number depends on which
+// SMs of a part are enabled; the host asks the occupancy API): at the action-expert shape -- 400 query rows, 3 full tiles and
 // one of 16 rows -- 16 clusters do not fit but 3 x 4 + 2 do.  blockIdx.x 0 and 1: the halves of the last tile (they
 // have the longer way to go and start first); above: part (x - 2) % 4 of tile (x - 2) / 4.  The last tile has at most
 // RAGGED_ROWS rows, which keeps its receive slots, and with them the shared memory of the launch, small enough for a
