@@ -179,7 +179,10 @@ __device__ __forceinline__ void tok_sum8(const float* recv, int S, int per, int 
     }
 }
 
-template <int BN, int PRO, int EPI>
+// ACT (GeGLU epilogue only): the gate activation, 0 exact GELU(tanh), 1 SiLU, 2 GELU through the hardware tanh.  A
+// template argument, not a field of the parameters: selected at run time inside the unrolled finish the choice cost
+// 0.55 us per gate|up launch of the action-expert loop (0.10 ms per loop), a third of that epilogue's arithmetic.
+template <int BN, int PRO, int EPI, int ACT = 0>
 __global__ void __launch_bounds__(256, 2)
 gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, TokParams p) {
     static_assert(EPI != TOK_EPI_GEGLU || BN >= 128, "GeGLU tiles are BN / 2 gate rows + the matching up rows");
@@ -674,7 +677,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int j = 0; j < 8; ++j) {
                         const float gt = __bfloat162float(__float2bfloat16_rn(a[j]));
                         const float up = __bfloat162float(__float2bfloat16_rn(b[j]));
-                        const float act = p.gate_act == 2 ? fast_gelu_tanh(gt) : p.gate_act == 1 ? det_silu(gt) : det_gelu_tanh(gt);
+                        const float act = ACT == 2 ? fast_gelu_tanh(gt) : ACT == 1 ? det_silu(gt) : det_gelu_tanh(gt);
                         q[j] = clamp448(__fmul_rn(__fmul_rn(act, up), inv_os));
                     }
                     uint2 o8;
@@ -806,11 +809,11 @@ static bool tok_plan(int N, int K, int m_tiles, int mt, int epi, int pro, int sm
     return found;
 }
 
-template <int BN, int PRO, int EPI>
+template <int BN, int PRO, int EPI, int ACT = 0>
 static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, const TokPlan& pl, bool pdl,
                            cudaStream_t stream) {
     using Cfg = TokCfg<BN>;
-    auto kern = gemm_tok_kernel<BN, PRO, EPI>;
+    auto kern = gemm_tok_kernel<BN, PRO, EPI, ACT>;
     const int m_tiles = (p.M + 127) / 128;
     const int mt = p.M < 128 ? p.M : 128;
     p.nkb = pl.nkb;
@@ -890,6 +893,15 @@ static int dispatch_gemm_tok(const void* A, const void* W, TokParams p, int K, i
     if (!tok_plan(EPI == TOK_EPI_GEGLU ? 2 * p.half : p.N, K, (p.M + 127) / 128, p.M < 128 ? p.M : 128, EPI, PRO,
                   tok_sm_count(), want_bn, want_s, &pl, p.w_kn != 0))
         return FRT_ERR_UNSUPPORTED;
+    if constexpr (EPI == TOK_EPI_GEGLU) {
+        if (pl.BN != 256 && pl.BN != 128) return FRT_ERR_UNSUPPORTED;
+        if (p.gate_act == 2)
+            return pl.BN == 256 ? launch_gemm_tok<256, PRO, EPI, 2>(A, W, p, K, pl, pdl, s)
+                                : launch_gemm_tok<128, PRO, EPI, 2>(A, W, p, K, pl, pdl, s);
+        if (p.gate_act == 1)
+            return pl.BN == 256 ? launch_gemm_tok<256, PRO, EPI, 1>(A, W, p, K, pl, pdl, s)
+                                : launch_gemm_tok<128, PRO, EPI, 1>(A, W, p, K, pl, pdl, s);
+    }
     if (pl.BN == 256) return launch_gemm_tok<256, PRO, EPI>(A, W, p, K, pl, pdl, s);
     if (pl.BN == 128) return launch_gemm_tok<128, PRO, EPI>(A, W, p, K, pl, pdl, s);
     if constexpr (EPI != TOK_EPI_GEGLU) return launch_gemm_tok<64, PRO, EPI>(A, W, p, K, pl, pdl, s);
