@@ -528,8 +528,11 @@ def run_wan(args):
             "metric": WAN_METRIC, "value": w["ms"], "unit": "ms", "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": w["ms"], "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 GEMMs (fp32 accumulate), bf16 attention", "data": "synthetic",
-            "config": {"workload": WAN_WORKLOAD, "layers": w["layers"], "parallelism": f"tp{world} (heads + FFN columns, "
-                       "NCCL all-reduce after attention-out, cross-attention-out and FFN-down)",
+            "config": {"workload": WAN_WORKLOAD, "layers": w["layers"], "parallelism": f"tp{world} (heads + FFN columns; " + (
+                           "replicated residual stream, NCCL all-reduce after attention-out, cross-attention-out and "
+                           "FFN-down)" if args.wan_replicated or world == 1 else
+                           "sequence-parallel residual stream: NCCL all-gather of the FP8 operand in front of QKV / "
+                           "cross-Q / FFN-up, reduce-scatter after attention-out, cross-attention-out and FFN-down)"),
                        "l2": "activations of one step (> 1 GB) exceed the 126 MB L2; no explicit flush",
                        "tensor_core_status": w["status"], "finite": w["finite"]},
             "e2e": {"value": w["e2e_ms"], "unit": "ms", "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"]},
