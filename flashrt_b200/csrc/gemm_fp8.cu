@@ -1213,6 +1213,11 @@ int frt_b200_gemm_fp8_nt_bias_gelu_fp8(const void* A, const void* W, void* out8,
     p.out8 = (uint8_t*)out8;
     p.out_scale = d_out_scale;
     p.fast_act = (flags & 128) ? 1 : 0;
+    if (p.fast_act) {
+        if (N >= 256)
+            return launch_gemm_persistent<256, EPI_P_BIAS_GELU_FAST_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
+        return launch_gemm_persistent<128, EPI_P_BIAS_GELU_FAST_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
+    }
     if (N >= 256) return launch_gemm_persistent<256, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
     return launch_gemm_persistent<128, EPI_P_BIAS_GELU_FP8>(A, W, p, K, flags & 1, (cudaStream_t)stream);
 }

@@ -14,7 +14,9 @@
 // leave their loops.
 #pragma once
 
-enum { EPI_P_BF16 = 0, EPI_P_BIAS_GELU_FP8 = 1 };
+// EPI_P_BIAS_GELU_FAST_FP8: the same epilogue with the GELU through the hardware tanh -- a template value, not a run-time
+// flag: a select inside the unrolled loop over a thread's values costs as much as the arithmetic it chooses between
+enum { EPI_P_BF16 = 0, EPI_P_BIAS_GELU_FP8 = 1, EPI_P_BIAS_GELU_FAST_FP8 = 2 };
 
 // tanh-form GELU with explicitly rounded fp32 operations, the same sequence as bias_gelu_fp8_kernel
 // (csrc/quantize/bias_gelu_quantize_fp8.cu:24-49 in the reference)
@@ -186,7 +188,7 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         float alpha = p.alpha_host;
         if (p.sa) alpha *= *p.sa;
         if (p.sb) alpha *= *p.sb;
-        const float inv_os = (EPI == EPI_P_BIAS_GELU_FP8) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
+        const float inv_os = (EPI != EPI_P_BF16) ? __fdiv_rn(1.0f, *p.out_scale) : 0.0f;
         // whole 128-byte lines per store instruction when rows and column blocks are 16-byte aligned
         const bool lines = EPI == EPI_P_BF16 && Cfg::EPI_STAGE_BYTES > 0 && (p.N % 8) == 0 &&
                            (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
@@ -290,12 +292,25 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             if (nb + j + 8 <= p.N) {
-                                float g[8];
+                                float g[8], bj[8];
+                                // 8 bias values with one load when they are 16-byte aligned (nb + j is a multiple of 8)
+                                if (p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
+                                    const uint4 bv = ld_global_v4(p.bias + nb + j);
+                                    unpack_bf16x2(bv.x, bj[0], bj[1]);
+                                    unpack_bf16x2(bv.y, bj[2], bj[3]);
+                                    unpack_bf16x2(bv.z, bj[4], bj[5]);
+                                    unpack_bf16x2(bv.w, bj[6], bj[7]);
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) bj[e] = p.bias ? __bfloat162float(p.bias[nb + j + e]) : 0.0f;
+                                }
+                                const bool hb = p.bias != nullptr;
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j + e]) * alpha));
-                                    if (p.bias) x = __fadd_rn(x, __bfloat162float(p.bias[nb + j + e]));
-                                    g[e] = clamp448(__fmul_rn(p.fast_act ? fast_gelu_tanh(x) : gelu_tanh_form_rn(x), inv_os));
+                                    if (hb) x = __fadd_rn(x, bj[e]);
+                                    g[e] = clamp448(__fmul_rn(EPI == EPI_P_BIAS_GELU_FAST_FP8 ? fast_gelu_tanh(x) : gelu_tanh_form_rn(x),
+                                                              inv_os));
                                 }
                                 uint2 o8;
                                 o8.x = f32x4_to_e4m3x4(g[0], g[1], g[2], g[3]);
