@@ -49,6 +49,10 @@ static int g_tok_trace_slot = 0;
 #endif
 
 enum { TOK_EPI_BF16 = 0, TOK_EPI_ROPE = 1, TOK_EPI_GEGLU = 2, TOK_EPI_RESID = 3 };
+// A token's row in a receive slot is BN + 4 floats long: the finish reads 32 bytes per thread, 8 threads per token, and
+// with rows of BN floats (a multiple of 32 banks) the four tokens of a warp hit the same banks (8 wavefronts per 16-byte
+// load instead of 4); four floats of padding rotate them apart.
+constexpr int TOK_ROW_PAD = 4;
 enum { TOK_PRO_TMA = 0, TOK_PRO_NORM = 1 };
 enum { TOK_STAT_STRIDE = 128 };          // floats between the per-tile rows of a statistics buffer
 
@@ -57,6 +61,8 @@ struct TokParams {
     int nkb;                   // 128-byte k-blocks per split
     int stages;                // shared-memory ring depth (>= nkb when the A operand is produced in the kernel)
     int per;                   // tokens finished by one rank of the cluster = ceil(tokens of an m-tile / S)
+    int row_pad;               // floats of padding behind a token's BN floats in a receive slot (TOK_ROW_PAD, or 0 when
+                               // the padded slots would not fit)
     int per_magic;             // ceil(65536 / per): row / per == (row * per_magic) >> 16 for row < 128 (no division on the
                                // path between the last MMA and the first pushed row)
     int ring_bytes;            // bytes of the operand ring / staging area in front of the receive slots
@@ -119,8 +125,8 @@ struct TokCfg {
     // operand ring, then the receive slots [S][per][BN] fp32 of the split-K exchange (never aliased: a fast rank
     // pushes while a slow rank's MMAs still read its operands)
     static int ring_bytes(int stages, bool m64) { return stages * stage_bytes(m64); }
-    static int smem_bytes(int stages, int S, int per, bool m64) {
-        return AUX_BYTES + 1024 + ring_bytes(stages, m64) + S * per * BN * 4;
+    static int smem_bytes(int stages, int S, int per, bool m64, int pad) {
+        return AUX_BYTES + 1024 + ring_bytes(stages, m64) + S * per * (BN + pad) * 4;
     }
 };
 
@@ -145,10 +151,10 @@ __device__ __forceinline__ int rope_col(int n, int head_dim) {
 
 // Sum over the S slots (fixed order) of the 8 received fp32 values of (token t of this rank, columns c8*8 .. +7).
 template <int BN>
-__device__ __forceinline__ void tok_sum8(const float* recv, int S, int per, int t, int c8, float* a) {
-    const float4* row = reinterpret_cast<const float4*>(recv + (size_t)t * BN);
+__device__ __forceinline__ void tok_sum8(const float* recv, int S, int per, int pad, int t, int c8, float* a) {
+    const float4* row = reinterpret_cast<const float4*>(recv + (size_t)t * (BN + pad));
     const int c0 = 2 * c8, c1 = 2 * c8 + 1;
-    const size_t slot = (size_t)per * BN / 4;
+    const size_t slot = (size_t)per * (BN + pad) / 4;
     // S is 1, 2, 4 or 8: the loads of four slots in flight at a time, the sums in slot order
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = 0.0f;
@@ -200,7 +206,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     volatile int* issued = abort_flag + 1;
     volatile int* consumed = abort_flag + 2;
     float* s_rms = reinterpret_cast<float*>(aux + 512);          // [128]
-    float* recv = reinterpret_cast<float*>(tiles + p.ring_bytes);   // [S][per][BN]
+    float* recv = reinterpret_cast<float*>(tiles + p.ring_bytes);   // [S][per][BN + p.row_pad]
 
     const uint64_t deadline = tc::global_timer_ns() + FRT_KERNEL_DEADLINE_NS;
     const int warp = threadIdx.x >> 5;
@@ -524,7 +530,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t trow = tmem_d + ((uint32_t)(quad * 32) << 16);
             const int rq = (row * p.per_magic) >> 16;           // row / per
             const int owner = rq < S ? rq : 0;
-            const uint32_t dst_local = tc::smem_u32(recv) + (uint32_t)(((rank * per + (row - rq * per)) * BN) * 4);
+            const uint32_t dst_local = tc::smem_u32(recv) + (uint32_t)(((rank * per + (row - rq * per)) * (BN + p.row_pad)) * 4);
             const uint32_t dst = tc::dsmem_map(dst_local, (uint32_t)owner);
             const uint32_t bar = tc::dsmem_map(tc::smem_u32(recv_bar), (uint32_t)owner);
 #pragma unroll 1
@@ -562,7 +568,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const bool first = it < 256;
             float a[8];
             if (act) {
-                tok_sum8<BN>(recv, S, per, t, g, a);
+                tok_sum8<BN>(recv, S, per, p.row_pad, t, g, a);
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) a[j] = 0.0f;
@@ -648,7 +654,7 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int h = n0 + g * 8;
                 if (act && h < p.half) {
                     float b[8];
-                    tok_sum8<BN>(recv, S, per, t, G + g, b);
+                    tok_sum8<BN>(recv, S, per, p.row_pad, t, G + g, b);
                     float q[8];
                     if (rowscale) {
                         float4 c0 = ct0, c1 = ct1, c2 = ct2, c3 = ct3;
@@ -791,8 +797,10 @@ static bool tok_plan(int N, int K, int m_tiles, int mt, int epi, int pro, int sm
             const int ctas = tiles * S;
             const int stages = nkb < max_st ? nkb : max_st;
             const int per = (mt + S - 1) / S;
-            const int smem = 3072 + stages * stage_bytes + S * per * BN * 4;
-            if (pro == TOK_PRO_NORM && smem > 227 * 1024) continue;
+            const int smem = 3072 + stages * stage_bytes + S * per * (BN + TOK_ROW_PAD) * 4;
+            if (pro == TOK_PRO_NORM && smem - S * per * TOK_ROW_PAD * 4 > 227 * 1024) continue;
+            // the launcher shortens the ring down to two stages, not further
+            if (3072 + (stages < 2 ? stages : 2) * stage_bytes + S * per * BN * 4 > 227 * 1024) continue;
             const double pushed_kb = (double)(S - 1) / S * mt * BN * 4 / 1024.0;
             double cost = nkb * 0.33 + pushed_kb * 0.06 + (S > 1 ? 0.05 * S : 0.0);
             if (pro == TOK_PRO_NORM) cost += 0.6 * nkb;
@@ -822,15 +830,18 @@ static int launch_gemm_tok(const void* A, const void* W, TokParams p, int K, con
     p.per_magic = (65536 + p.per - 1) / p.per;
     p.m64 = (m_tiles == 1 && mt <= 64) ? 1 : 0;
     const bool m64 = p.m64 != 0;
+    // padded receive rows unless even a two-stage ring would not fit beside them
+    const int need_stages = PRO == TOK_PRO_NORM ? pl.nkb : (p.stages < 2 ? p.stages : 2);   // the ring's lower bound
+    p.row_pad = Cfg::smem_bytes(need_stages, pl.S, p.per, m64, TOK_ROW_PAD) > 227 * 1024 ? 0 : TOK_ROW_PAD;
     // the operand ring shrinks until it fits beside the receive slots
-    while (p.stages > 2 && Cfg::smem_bytes(p.stages, pl.S, p.per, m64) > 227 * 1024) --p.stages;
+    while (p.stages > 2 && Cfg::smem_bytes(p.stages, pl.S, p.per, m64, p.row_pad) > 227 * 1024) --p.stages;
     if (PRO == TOK_PRO_NORM && p.stages < pl.nkb) return FRT_ERR_UNSUPPORTED;
     p.K = K;
 #ifdef FRT_PHASE_STAMPS
     p.trace_slot = g_tok_trace_slot;
     g_tok_trace_slot = (g_tok_trace_slot + 1) % 8;
 #endif
-    const int smem = Cfg::smem_bytes(p.stages, pl.S, p.per, m64);
+    const int smem = Cfg::smem_bytes(p.stages, pl.S, p.per, m64, p.row_pad);
     p.ring_bytes = Cfg::ring_bytes(p.stages, m64);
     if (smem > 227 * 1024) return FRT_ERR_UNSUPPORTED;
     int dev = 0;
