@@ -123,7 +123,8 @@ def test_cluster_exchange_equals_scratch_combine(Sq, Skv, splits, extra):
     a, lse_a, cnt_a = _run(1, Sq, Skv, 8, 1, 256, splits, seed=7, scratch=True, **extra)
     b, lse_b, cnt_b = _run(1, Sq, Skv, 8, 1, 256, splits, seed=7, scratch=True, flags=8, **extra)
     assert np.array_equal(a, b) and np.array_equal(lse_a, lse_b)
-    assert (cnt_a == 0).all() and (cnt_b == 256).all()
+    # the default call leaves the counters alone when the device can hold the clusters (else it is the scratch path too)
+    assert ((cnt_a == 0).all() or (cnt_a == 256).all()) and (cnt_b == 256).all()
 
 
 def test_launches_of_different_shapes_share_arrival_counters():
