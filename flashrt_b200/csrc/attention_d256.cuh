@@ -358,7 +358,9 @@ __device__ __forceinline__ void attn_d256_body(const CUtensorMap& tmQ, const CUt
                 const uint32_t my_lse = rank * slot + (uint32_t)rows_valid * (uint32_t)dper * 2u + (uint32_t)row * 4u;
                 asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
                 if (row < rows_valid) {                         // the log-sum-exp of the row: once to every split
-                    for (uint32_t s = 0; s < C; ++s) {
+#pragma unroll
+                    for (uint32_t s = 0; s < 8; ++s) {
+                        if (s >= C) break;
                         if (s == rank) *reinterpret_cast<float*>(recv + my_lse) = lse2;
                         else tc::st_async_b32(tc::dsmem_map(recv_u32 + my_lse, s), tc::dsmem_map(bar_u32, s),
                                               __float_as_uint(lse2));

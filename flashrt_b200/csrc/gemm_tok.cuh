@@ -721,16 +721,17 @@ gemm_tok_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         ssq = __fmaf_rn(r0, r0, ssq);
                         ssq = __fmaf_rn(r1, r1, ssq);
                         ow[k] = pack_bf16x2(r0, r1);
-                        if (emit_q8) {
+                    }
+                    st_global_v4(rp, ob);
+                    if (emit_q8) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
                             float b0, b1, s0, s1;
                             unpack_bf16x2(ow[k], b0, b1);          // what the next reader of the residual sees
                             unpack_bf16x2(mw[k], s0, s1);
                             u[2 * k] = clamp448(__fmul_rn(__fmul_rn(b0, __fadd_rn(1.0f, s0)), inv_q8));
                             u[2 * k + 1] = clamp448(__fmul_rn(__fmul_rn(b1, __fadd_rn(1.0f, s1)), inv_q8));
                         }
-                    }
-                    st_global_v4(rp, ob);
-                    if (emit_q8) {
                         uint2 o8;
                         o8.x = f32x4_to_e4m3x4(u[0], u[1], u[2], u[3]);
                         o8.y = f32x4_to_e4m3x4(u[4], u[5], u[6], u[7]);
